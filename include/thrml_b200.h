@@ -1,0 +1,227 @@
+/*
+ * thrml_b200.h — C ABI of libthrml_b200: a block-Gibbs sampling engine for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces, for thrml-rs's sampling path, everything from
+ * BlockSamplingProgram::sample_single_block downward (crates/thrml-samplers/src/program.rs:324-393),
+ * i.e. the Burn/WGPU tensor dispatch, the per-block samplers and the observers' per-sample work.
+ * The Rust-level types (Node, Block, BlockSpec, InteractionGroup, BlockGibbsSpec, ...) stay the
+ * caller's; they are flattened to the integer arrays this header takes.
+ *
+ * Conventions
+ *  - every function returns an int32 status: THRML_OK or a negative THRML_ERR_*; nothing throws or
+ *    aborts.  thrml_last_error() returns a thread-local message for the last failing call; the
+ *    messages keep the substrings thrml-rs's own tests look for ("same type", "twice",
+ *    "leading dimension", "tail node blocks", "n_spin", "empty", "Number of samplers", ...).
+ *  - the caller owns every host buffer it passes; the library copies during the call and owns all
+ *    device memory until the matching *_destroy.
+ *  - a handle is used by one host thread at a time; distinct handles are independent.
+ *  - no function falls back to the CPU: without a usable CUDA device every device function returns
+ *    THRML_ERR_CUDA.  The thrml_rng_*, thrml_builder_*, thrml_lattice_* and thrml_greedy_coloring
+ *    functions are host-only and work without a GPU.
+ *
+ * Node ids are dense per builder: 0 .. n_nodes-1.  A node kind is 0 for NodeType::Spin and K >= 1 for
+ * NodeType::Categorical{n_categories: K} (crates/thrml-core/src/node.rs:8-21).
+ *
+ * State values follow the reference: a spin is 0 or 1 (1 means +1), a categorical node holds its
+ * category index (crates/thrml-samplers/src/spin_gibbs.rs:618-637, softmax.rs:60-97).  On the device a
+ * node's state is one byte per chain, chains innermost: state[class][global position][chain].
+ */
+#ifndef THRML_B200_H
+#define THRML_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define THRML_OK 0
+#define THRML_ERR_INVALID_ARG (-1)
+#define THRML_ERR_BAD_COLOURING (-2)
+#define THRML_ERR_CUDA (-3)
+#define THRML_ERR_NCCL (-4)
+#define THRML_ERR_TIMEOUT (-5)
+#define THRML_ERR_OOM (-6)
+#define THRML_ERR_UNSUPPORTED (-7)
+
+/* sampler kinds, one per free block (crates/thrml-samplers/src/sampler.rs:58-71 is the trait they implement) */
+#define THRML_SAMPLER_SPIN_GIBBS 0        /* SpinGibbsConditional, spin_gibbs.rs:59-100 */
+#define THRML_SAMPLER_CATEGORICAL_GIBBS 1 /* CategoricalGibbsConditional, softmax.rs:228-271 */
+
+typedef struct thrml_ctx thrml_ctx;
+typedef struct thrml_builder thrml_builder;
+typedef struct thrml_program thrml_program;
+typedef struct thrml_state thrml_state;
+typedef struct thrml_moments thrml_moments;
+
+/* Message of the last failing call on this thread (empty string if none). */
+const char* thrml_last_error(void);
+/* Library version string. */
+const char* thrml_version(void);
+
+/* ------------------------------------------------------------------------------------------------
+ * RngKey — crates/thrml-samplers/src/rng.rs:10-51
+ * split(n): n == 0 -> nothing written; n == 1 -> out[0] = key (rng.rs:24-26); else a ChaCha8 stream
+ * seeded with rand_core 0.6's seed_from_u64(key) gives n successive next_u64() values (rng.rs:29-36).
+ * ---------------------------------------------------------------------------------------------- */
+int32_t thrml_rng_split(uint64_t key, int64_t n, uint64_t* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Input generators used by the benchmark configurations (host only).
+ * thrml_lattice_edges: nearest-neighbour square lattice of make_nearest_neighbor_lattice
+ *   (crates/thrml-models/src/graph_utils.rs:177-243): side rounded up to even, nodes row-major, one edge
+ *   (min,max) per neighbour pair; the reference's HashSet order is replaced by ascending (min,max).
+ *   edges_out holds 2*n_edges ids; pass NULL to query the count only.  colour_out[i] = (row+col)%2.
+ * thrml_greedy_coloring: greedy_coloring of crates/thrml-examples/src/lib.rs:114-147 — nodes visited in
+ *   index order, smallest colour not used by an already coloured neighbour.
+ * ---------------------------------------------------------------------------------------------- */
+int32_t thrml_lattice_edges(int64_t side_len, int32_t torus, int64_t* side_out, int64_t* n_edges_out,
+                            int64_t* edges_out, int32_t* colour_out);
+int32_t thrml_greedy_coloring(int64_t n_nodes, int64_t n_edges, const int64_t* edges, int32_t* colour_out,
+                              int32_t* n_colours_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Program builder = the host-side index compiler.
+ *   BlockGibbsSpec::new           crates/thrml-samplers/src/program.rs:28-64
+ *   BlockSpec::new                crates/thrml-core/src/blockspec.rs:15-66
+ *   InteractionGroup::new         crates/thrml-core/src/interaction.rs:128-181
+ *   to_interaction_groups         crates/thrml-models/src/discrete_ebm.rs:379-510
+ *   BlockSamplingProgram::new     crates/thrml-samplers/src/program.rs:88-318
+ * ---------------------------------------------------------------------------------------------- */
+/* kinds[n_nodes]; dtype_order lists node kinds in the insertion order of the caller's
+ * node_shape_dtypes map: it fixes the numbering of the global-state classes (blockspec.rs:19-28). */
+int32_t thrml_builder_create(const int32_t* kinds, int64_t n_nodes, const int32_t* dtype_order,
+                             int32_t n_dtype_order, thrml_builder** out);
+void thrml_builder_destroy(thrml_builder* b);
+/* Free blocks are appended in order; blocks that share `superblock` are updated from the same
+ * pre-update state (sampling.rs:40-59).  superblock ids must be non-decreasing. */
+int32_t thrml_builder_add_free_block(thrml_builder* b, const int64_t* nodes, int64_t n, int32_t superblock,
+                                     int32_t sampler_kind);
+int32_t thrml_builder_add_clamped_block(thrml_builder* b, const int64_t* nodes, int64_t n);
+/* One InteractionGroup: head[rows]; tails[n_tails][rows] (the first n_spin tails are spin blocks, the
+ * rest categorical); w[rows][d1][d2] f32. */
+int32_t thrml_builder_add_interaction_group(thrml_builder* b, const int64_t* head, int64_t rows,
+                                            const int64_t* tails, int32_t n_tails, int32_t n_spin,
+                                            const float* w, int32_t d1, int32_t d2);
+/* One DiscreteEBMFactor (SpinEBMFactor / CategoricalEBMFactor are the special cases):
+ * spin_groups[n_spin_groups][rows], cat_groups[n_cat_groups][rows], w[rows][d1][d2]; appends the directed
+ * interaction groups the reference derives (discrete_ebm.rs:379-510). n_groups_out may be NULL. */
+int32_t thrml_builder_add_discrete_factor(thrml_builder* b, const int64_t* spin_groups, int32_t n_spin_groups,
+                                          const int64_t* cat_groups, int32_t n_cat_groups, int64_t rows,
+                                          const float* w, int32_t d1, int32_t d2, int32_t* n_groups_out);
+/* IsingEBM::get_factors (crates/thrml-models/src/ising.rs:105-143): bias factor over `nodes` with beta*b,
+ * edge factor with beta*J; either may be empty. */
+int32_t thrml_builder_add_ising(thrml_builder* b, const int64_t* nodes, int64_t n_nodes, const float* biases,
+                                const int64_t* edges, int64_t n_edges, const float* weights, float beta);
+/* Runs BlockSpec::new + BlockSamplingProgram::new. */
+int32_t thrml_builder_compile(thrml_builder* b);
+
+/* Introspection of the compiled tables (the bit-exact parity surface). */
+int32_t thrml_builder_counts(const thrml_builder* b, int32_t* n_free, int32_t* n_clamped, int32_t* n_groups_total,
+                             int32_t* n_classes);
+int32_t thrml_builder_node_location(const thrml_builder* b, int64_t node, int32_t* sd_index, int64_t* position);
+/* Interaction group g of the builder's flat list: sizes, then contents (any out pointer may be NULL). */
+int32_t thrml_builder_group_shape(const thrml_builder* b, int32_t g, int64_t* rows, int32_t* n_tails,
+                                  int32_t* n_spin, int32_t* d1, int32_t* d2);
+int32_t thrml_builder_group_data(const thrml_builder* b, int32_t g, int64_t* head, int64_t* tails, float* w);
+/* Number of compiled (non-empty) tables of free block `block`, then table t of that block:
+ * k = padded slot count, wdim = d1*d2, n = block length. */
+int32_t thrml_builder_block_tables(const thrml_builder* b, int32_t block, int32_t* n_tables, int64_t* n_nodes);
+int32_t thrml_builder_table_shape(const thrml_builder* b, int32_t block, int32_t t, int32_t* k, int32_t* wdim,
+                                  int32_t* n_spin, int32_t* n_tails, int32_t* source_group);
+/* rows[n*k] (interaction_slices), active[n*k], w[n*k*wdim], idx[n_tails][n*k] (global positions),
+ * tail_sd[n_tails] (class of each tail) — program.rs:159-300. */
+int32_t thrml_builder_table_data(const thrml_builder* b, int32_t block, int32_t t, int32_t* rows, uint8_t* active,
+                                 float* w, int32_t* idx, int32_t* tail_sd);
+
+/* ------------------------------------------------------------------------------------------------
+ * Device context, program, state.
+ * ---------------------------------------------------------------------------------------------- */
+/* One context = one CUDA device + one stream (one process per GPU is the intended deployment). */
+int32_t thrml_ctx_create(int32_t device_id, thrml_ctx** out);
+void thrml_ctx_destroy(thrml_ctx* ctx);
+int32_t thrml_ctx_synchronize(thrml_ctx* ctx);
+/* cudaStream_t of the context, for callers that time with their own events. */
+void* thrml_ctx_stream(thrml_ctx* ctx);
+
+/* Uploads the compiled tables.  The program snapshots the weights (as the reference does,
+ * program.rs:216-235); thrml_program_update_weights refreshes table t of a block explicitly. */
+int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out);
+void thrml_program_destroy(thrml_program* p);
+int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w);
+/* Which kernel a free block runs: 0 generic gather kernel, 1 threshold-table kernel (spin blocks whose
+ * nodes have at most 8 single-spin-tail slots), 2 categorical kernel. */
+int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out);
+
+/* n_chains chains held on this device; chain_offset = global id of local chain 0 (the in-kernel random
+ * stream is a function of the global chain id, so results do not depend on how chains are sharded). */
+int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_offset, thrml_state** out);
+void thrml_state_destroy(thrml_state* s);
+/* Block index runs over free blocks then clamped blocks.  Host layout [chain][node], f32 as in the
+ * reference (0/1 or category index) or raw bytes. */
+int32_t thrml_state_upload_f32(thrml_state* s, int32_t block, const float* host);
+int32_t thrml_state_download_f32(thrml_state* s, int32_t block, float* host);
+int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host);
+int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host);
+
+/* hinton_init (crates/thrml-models/src/ising.rs:602-673): for each listed block, P(s=1) = sigmoid(beta*b)
+ * (not 2*beta*b, ising.rs:650), s = (u <= p).  biases = concatenation of the listed blocks' biases.
+ * inj_u (nullable, host): uniforms [block][chain][node] to use instead of the in-kernel stream. */
+int32_t thrml_hinton_init(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const float* biases, float beta,
+                          uint64_t key, const float* inj_u);
+/* Uniform random state for every free block (spins: fair bits; categorical: uniform category). */
+int32_t thrml_state_randomize(thrml_state* s, uint64_t key);
+
+/* Injected noise (host pointer, f32), consumed in update order: for every sweep, for every free block in
+ * sampling order, a spin block takes u[node][chain] and a categorical block takes u[node][category][chain].
+ * Both sides of a parity test feed the same stream. */
+typedef struct thrml_noise {
+    const float* u;
+    int64_t len;
+} thrml_noise;
+
+/* sample_blocks (sampling.rs:28-63): one sweep; per-block keys = key.split(n_free_blocks). */
+int32_t thrml_sample_blocks(thrml_state* s, uint64_t key, const thrml_noise* inj);
+/* run_blocks (sampling.rs:81-106): n_iters sweeps with keys = key.split(n_iters). */
+int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const thrml_noise* inj);
+/* Local field gamma[chain][node] (spin block) or logits theta[chain][node][K] (categorical block) of a free
+ * block in the current state — spin_gibbs.rs:512-611 / softmax.rs:586-709. */
+int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Observers.
+ * MomentAccumulatorObserver (crates/thrml-observers/src/moment.rs:52-148,157-237): running sums of
+ * prod f(x) over listed node tuples, f = 2x-1 when transform_to_spin.  spec = n_types moment types,
+ * rows_per_type[t] rows each, row r holds members[row_ptr[r] .. row_ptr[r+1]) (node ids).  Sums run over
+ * samples and over this device's chains, exactly (int64).
+ * ---------------------------------------------------------------------------------------------- */
+int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* rows_per_type, const int64_t* row_ptr,
+                             const int64_t* members, int32_t transform_to_spin, thrml_moments** out);
+void thrml_moments_destroy(thrml_moments* m);
+int32_t thrml_moments_reset(thrml_moments* m);
+/* observe(): add the current state's products (moment.rs:205-233). */
+int32_t thrml_moments_observe(thrml_moments* m, thrml_state* s);
+/* sums_out[rows_per_type[type]] as int64 totals; n_obs_out = observations * local chains. */
+int32_t thrml_moments_read(thrml_moments* m, int32_t type, int64_t* sums_out, int64_t* n_obs_out);
+/* Device pointer of the int64 accumulators of all types, concatenated, and their count — the buffer a
+ * multi-GPU host hands to its single allreduce(sum). */
+int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_t* count_out);
+int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs);
+
+/* Per-node category counts for the nodes of the listed blocks (counts[node][category], int64), the
+ * category-marginal observable of the Potts configuration.  K = table width. */
+int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t n_blocks, int32_t K,
+                               thrml_moments** out);
+
+/* sample_with_observation (sampling.rs:178-320): key.split_two -> warm-up, observe, then n_samples-1 times
+ * (steps_per_sample sweeps, observe).  moments may be NULL.  obs_blocks/obs_out (nullable) = StateObserver
+ * (state_observer.rs:25-47): obs_out[sample][observed node][chain] bytes, observed nodes = concatenation of
+ * the listed blocks.  Total sweeps = n_warmup + (n_samples-1)*steps_per_sample. */
+int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_warmup, int64_t n_samples,
+                                      int64_t steps_per_sample, thrml_moments* moments, const int32_t* obs_blocks,
+                                      int32_t n_obs_blocks, uint8_t* obs_out, const thrml_noise* inj);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THRML_B200_H */

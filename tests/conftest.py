@@ -1,0 +1,26 @@
+import os
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import __graft_entry__ as graft  # noqa: E402
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box)")
+    graft.build()
+
+
+@pytest.fixture(scope="session")
+def T():
+    return graft.load_package()
+
+
+@pytest.fixture(scope="session")
+def O():
+    from oracle import oracle
+    return oracle

@@ -1,0 +1,16 @@
+"""thrml_rs_b200 — B200-native block-Gibbs sampling engine behind the thrml-rs sampling API.
+
+The directory name contains a hyphen, so the package is imported under the module name `thrml_rs_b200` through
+`__graft_entry__.load_package()` (tests and bench.py do this) or by putting an importlib spec on it directly.
+"""
+from ._ffi import ThrmlError, lib  # noqa: F401
+from .engine import (Builder, ChainState, Context, Moments, Program, default_context, greedy_coloring_arrays,  # noqa: F401
+                     lattice_edges, rng_split)
+from .api import (Block, BlockGibbsSpec, BlockSamplingProgram, BlockSpec, CategoricalEBMFactor,  # noqa: F401
+                  CategoricalGibbsConditional, DiscreteEBMFactor, FactorSamplingProgram, InteractionGroup, IsingEBM,
+                  IsingSamplingProgram, MomentAccumulatorObserver, Node, NodeType, RngKey, SamplingSchedule,
+                  SpinEBMFactor, SpinGibbsConditional, StateObserver, coloring_to_blocks, estimate_moments,
+                  greedy_coloring, hinton_init, make_nearest_neighbor_lattice, run_blocks, sample_blocks,
+                  sample_states, sample_with_observation)
+
+lib()  # fail at import time when the compiled library is absent: there is no other compute path

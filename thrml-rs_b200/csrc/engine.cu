@@ -1,0 +1,1115 @@
+// Device side of libthrml_b200: context, program upload, chain state, the block-update kernels, the observers and
+// the sweep / schedule drivers.  sm_100a only; there is no CPU path in this file — without a CUDA device every entry
+// point returns THRML_ERR_CUDA.
+//
+// State layout: one byte per node and chain, chains innermost: state[class][global position][ld], ld = chains rounded
+// up to 16 bytes.  A neighbour gather therefore reads one contiguous row segment per neighbour, whatever the graph.
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+
+#include "device_math.cuh"
+#include "tables.h"
+
+using namespace thrml;
+
+#define CU_TRY(expr)                                                                                               \
+    do {                                                                                                           \
+        cudaError_t e__ = (expr);                                                                                  \
+        if (e__ != cudaSuccess) return fail(THRML_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
+    } while (0)
+
+constexpr int MAX_TAILS = 8;
+constexpr int LUT_BITS = 8;              // a threshold table covers at most 8 neighbour spins
+constexpr int LUT_SIZE = 1 << LUT_BITS;  // entries per node
+
+// Device view of one slot table.
+struct DevTable {
+    int32_t k, wdim, n_spin, n_tails;
+    const int32_t* idx[MAX_TAILS];
+    const uint8_t* active;
+    const float* w;
+};
+
+struct DevBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    DevBuf() = default;
+    DevBuf(const DevBuf&) = delete;
+    DevBuf& operator=(const DevBuf&) = delete;
+    DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
+    ~DevBuf() { if (p) cudaFree(p); }
+    int32_t alloc(size_t n) {
+        if (p) { cudaFree(p); p = nullptr; }
+        bytes = n;
+        if (n == 0) return THRML_OK;
+        cudaError_t e = cudaMalloc(&p, n);
+        if (e != cudaSuccess) { p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
+        return THRML_OK;
+    }
+    template <class T> T* as() const { return static_cast<T*>(p); }
+};
+
+struct thrml_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 148;
+};
+
+struct BlockProg {
+    int32_t kind = 0;     // 0 spin, K categorical
+    int32_t sd = 0;       // class index
+    int32_t is_cat = 0;
+    int64_t n = 0, offset = 0;
+    int32_t kernel = 0;   // 0 generic spin, 1 threshold table, 2 categorical
+    int32_t n_tabs = 0;
+    std::vector<std::unique_ptr<DevBuf>> bufs;  // idx/active/w storage
+    std::vector<DevTable> host_tabs;
+    std::vector<DevBuf*> w_bufs;                // per table, for update_weights
+    std::vector<size_t> w_len;
+    DevBuf d_tabs;   // DevTable[n_tabs]
+    DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
+    DevBuf d_lut;    // uint32 [n][256]
+};
+
+struct thrml_program {
+    thrml_ctx* ctx = nullptr;
+    int32_t n_free = 0, n_clamped = 0, n_classes = 0, sd_spin = -1, sd_cat = -1;
+    std::vector<int64_t> class_size;
+    std::vector<BlockProg> blocks;  // free ++ clamped
+    std::vector<std::vector<int32_t>> sampling_order;
+    std::vector<uint8_t> staged;    // per superblock: 1 when its blocks read positions the superblock itself writes
+    int64_t max_stage_rows = 0;
+    std::vector<int8_t> loc_sd;     // node -> class / position (host copy, for observers)
+    std::vector<int64_t> loc_pos;
+};
+
+struct thrml_state {
+    thrml_program* prog = nullptr;
+    int64_t n_chains = 0, chain_offset = 0, ld = 0;
+    DevBuf cls[2];      // state rows per class
+    DevBuf stage;       // staging rows for superblocks that cannot be updated in place
+    DevBuf scratch;     // transposes, injected noise, debug fields
+    uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
+};
+
+struct thrml_moments {
+    thrml_program* prog = nullptr;
+    int32_t mode = 0;  // 0 products over tuples, 1 per-node category counts
+    int32_t spin_transform = 1;
+    std::vector<int64_t> rows_per_type;
+    int64_t total_rows = 0;
+    int32_t K = 0;
+    DevBuf d_row_ptr, d_mem_sd, d_mem_pos;  // mode 0: CSR of members (class, position)
+    DevBuf d_node_sd, d_node_pos;           // mode 1: observed nodes
+    DevBuf d_sums;                          // int64 [total_rows] (mode 0) or [nodes*K] (mode 1)
+    int64_t n_obs = 0;
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// Kernels.
+// ---------------------------------------------------------------------------------------------------------
+struct UpdateArgs {
+    const DevTable* tabs;
+    int32_t n_tabs;
+    int32_t n;            // nodes in the block
+    int32_t K;            // categories (categorical kernel)
+    int64_t ld;           // bytes per state row
+    int64_t n_chains;
+    uint32_t chain_word0; // global chain id of local chain 0, divided by 4
+    const uint8_t* spin;  // class rows (may be null when the class is absent)
+    const uint8_t* cat;
+    uint8_t* dst;         // first row of the block's output (state rows or staging rows)
+    uint32_t k0, k1;      // block key
+    const float* inj;     // injected uniforms or null
+    float* fields;        // debug output or null
+};
+
+__device__ __forceinline__ uint32_t ld_word(const uint8_t* base, int64_t row, int64_t ld, int quad) {
+    return *reinterpret_cast<const uint32_t*>(base + row * ld + 4 * static_cast<int64_t>(quad));
+}
+
+// Generic spin update: any number of tables, spin tails and one optional categorical tail per table.
+// One thread = one node x four consecutive chains.  MODE 0 in-kernel noise, 1 injected noise, 2 write gamma only.
+// Field accumulation order: per table, slots left to right from zero; tables left to right (spin_gibbs.rs:527-582).
+template <int MODE>
+__global__ void __launch_bounds__(256) k_spin_generic(UpdateArgs a) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    float gamma[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t = 0; t < a.n_tabs; ++t) {
+        const DevTable T = a.tabs[t];
+        float gs[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+            if (!T.active[flat]) continue;
+            float sp[4] = {1.f, 1.f, 1.f, 1.f};
+            for (int tl = 0; tl < T.n_spin; ++tl) {
+                const uint32_t wd = ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sp[c] = __fmul_rn(sp[c], ((wd >> (8 * c)) & 1u) ? 1.0f : -1.0f);
+            }
+            if (T.n_tails > T.n_spin) {  // first categorical tail selects the weight (spin_gibbs.rs:556-577)
+                const uint32_t wd = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t x = (wd >> (8 * c)) & 0xffu;
+                    const float wv = x < static_cast<uint32_t>(T.wdim) ? T.w[flat * T.wdim + x] : 0.0f;
+                    gs[c] = __fadd_rn(gs[c], __fmul_rn(wv, sp[c]));
+                }
+            } else {
+                const float wv = T.w[flat * T.wdim];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) gs[c] = __fadd_rn(gs[c], __fmul_rn(wv, sp[c]));
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) gamma[c] = __fadd_rn(gamma[c], gs[c]);
+    }
+    if (MODE == 2) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+            if (chain < a.n_chains) a.fields[chain * a.n + node] = gamma[c];
+        }
+        return;
+    }
+    U4 r{0, 0, 0, 0};
+    if (MODE == 0) r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, a.k0, a.k1);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+        float u;
+        if (MODE == 1) u = chain < a.n_chains ? a.inj[static_cast<int64_t>(node) * a.n_chains + chain] : 2.0f;
+        else u = u24(pick(r, c));
+        const float p = det_sigmoid(__fmul_rn(gamma[c], 2.0f));  // spin_gibbs.rs:95
+        if (u <= p && chain < a.n_chains) out |= 1u << (8 * c);   // spin_gibbs.rs:97
+    }
+    *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// Generic categorical update (softmax.rs:586-709 + 60-97): logits theta[c] = sum over tables and slots of
+// active * prod(2s-1) * W[own c, neighbour category]; draw = argmax_c(theta[c] - ln(-ln u_c)), first maximum wins.
+template <int MODE>
+__global__ void __launch_bounds__(256) k_cat_generic(UpdateArgs a) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const int K = a.K;
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t arg[4] = {0, 0, 0, 0};
+    U4 r[4];
+    for (int cat = 0; cat < K; ++cat) {
+        float th[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int t = 0; t < a.n_tabs; ++t) {
+            const DevTable T = a.tabs[t];
+            const bool has_cat = T.n_tails > T.n_spin;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < T.k; ++j) {
+                const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+                if (!T.active[flat]) continue;
+                float sp[4] = {1.f, 1.f, 1.f, 1.f};
+                for (int tl = 0; tl < T.n_spin; ++tl) {
+                    const uint32_t wd = ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sp[c] = __fmul_rn(sp[c], ((wd >> (8 * c)) & 1u) ? 1.0f : -1.0f);
+                }
+                if (has_cat) {
+                    const uint32_t wd = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t x = (wd >> (8 * c)) & 0xffu;
+                        if (x >= static_cast<uint32_t>(K)) x = K - 1;
+                        sum[c] = __fadd_rn(sum[c], __fmul_rn(sp[c], T.w[flat * T.wdim + cat * K + x]));
+                    }
+                } else {
+                    const float wv = T.w[flat * T.wdim + cat];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sum[c] = __fadd_rn(sum[c], __fmul_rn(sp[c], wv));
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) th[c] = __fadd_rn(th[c], sum[c]);
+        }
+        if (MODE == 2) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+                if (chain < a.n_chains) a.fields[(chain * a.n + node) * K + cat] = th[c];
+            }
+            continue;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+            float u;
+            if (MODE == 1) {
+                u = chain < a.n_chains ? a.inj[(static_cast<int64_t>(node) * K + cat) * a.n_chains + chain] : 0.5f;
+            } else {
+                if ((cat & 3) == 0)
+                    r[c] = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+                u = u23_open(pick(r[c], cat & 3));
+            }
+            const float g = -det_log(-det_log(u));  // softmax.rs:84
+            const float p = __fadd_rn(th[c], g);
+            if (cat == 0 || p > best[c]) {  // strict >: the first maximum wins (gumbel_argmax/kernel.rs:81-83)
+                best[c] = p;
+                arg[c] = cat;
+            }
+        }
+    }
+    if (MODE == 2) return;
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
+    *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// Threshold tables for spin blocks whose nodes see at most 8 neighbour spins through single-spin-tail tables:
+// lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
+// (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
+// k_spin_generic, and u <= p  <=>  (r >> 8) <= floor(p * 2^24)  <=>  r <= (floor(p * 2^24) << 8 | 0xff).
+__global__ void __launch_bounds__(256) k_build_lut(const DevTable* tabs, int32_t n_tabs, int32_t n, uint32_t* lut) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t node = gid >> LUT_BITS;
+    const uint32_t cfg = static_cast<uint32_t>(gid) & (LUT_SIZE - 1);
+    if (node >= n) return;
+    float gamma = 0.f;
+    int bit = 0;
+    for (int t = 0; t < n_tabs; ++t) {
+        const DevTable T = tabs[t];
+        float gs = 0.f;
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = node * T.k + j;
+            if (!T.active[flat]) continue;
+            float sp = 1.0f;
+            if (T.n_spin == 1) {
+                sp = ((cfg >> bit) & 1u) ? 1.0f : -1.0f;
+                ++bit;
+            }
+            gs = __fadd_rn(gs, __fmul_rn(T.w[flat], sp));
+        }
+        gamma = __fadd_rn(gamma, gs);
+    }
+    const float p = det_sigmoid(__fmul_rn(gamma, 2.0f));
+    const uint32_t fl = static_cast<uint32_t>(__fmul_rn(p, 16777216.0f));  // exact: p*2^24 <= 2^24
+    lut[gid] = fl >= 16777216u ? 0xffffffffu : ((fl << 8) | 0xffu);
+}
+
+struct LutArgs {
+    const int32_t* nbr;    // [n][8] global spin positions, -1 = unused slot
+    const uint32_t* lut;   // [n][256]
+    const uint8_t* spin;
+    uint8_t* dst;
+    int64_t ld;
+    int32_t n;
+    int32_t n_chunks;      // ld / 16
+    uint32_t chain_word0;
+    uint32_t k0, k1;
+};
+
+// Threshold-table spin update: one warp per node, each lane 16 chains per pass.  The neighbour configuration of four
+// chains is assembled with shifts inside one 32-bit word (state bytes are 0/1), then one shared-memory lookup and one
+// compare per chain replace the field accumulation and the sigmoid.
+__global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    uint32_t* my = s_lut[wid];
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.lut + static_cast<int64_t>(node) * LUT_SIZE);
+        __syncwarp();
+        reinterpret_cast<uint4*>(my)[lane] = __ldg(src + lane);
+        reinterpret_cast<uint4*>(my)[lane + 32] = __ldg(src + lane + 32);
+        int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
+        __syncwarp();
+        int32_t nbj[LUT_BITS];
+#pragma unroll
+        for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
+        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+        for (int ch = lane; ch < a.n_chunks; ch += 32) {
+            uint4 v[LUT_BITS];
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j) {
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (nbj[j] >= 0) v[j] = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch);
+            }
+            uint32_t cfg[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j) {
+                cfg[0] += v[j].x << j;
+                cfg[1] += v[j].y << j;
+                cfg[2] += v[j].z << j;
+                cfg[3] += v[j].w << j;
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.k0, a.k1);
+                uint32_t w = 0;
+                w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
+                w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
+                w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
+                w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
+                o[q] = w;
+            }
+            reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+// hinton_init (ising.rs:602-673) and uniform start.  One thread = one node x four chains.
+__global__ void __launch_bounds__(256) k_hinton(uint8_t* dst, int64_t ld, int64_t n_chains, int32_t n, const float* bias, float beta,
+                                                uint32_t chain_word0, uint32_t k0, uint32_t k1, const float* inj) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= n || 4 * static_cast<int64_t>(quad) >= ld) return;
+    const float p = det_sigmoid(__fmul_rn(bias[node], beta));  // ising.rs:650
+    const U4 r = philox4x32_10(static_cast<uint32_t>(node), chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_HINT, k0, k1);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+        if (chain >= n_chains) continue;
+        const float u = inj ? inj[chain * n + node] : u24(pick(r, c));
+        if (u <= p) out |= 1u << (8 * c);  // ising.rs:667
+    }
+    *reinterpret_cast<uint32_t*>(dst + static_cast<int64_t>(node) * ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+__global__ void __launch_bounds__(256) k_randomize(uint8_t* dst, int64_t ld, int64_t n_chains, int32_t n, int32_t kind, uint32_t chain_word0,
+                                                   uint32_t k0, uint32_t k1) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= n || 4 * static_cast<int64_t>(quad) >= ld) return;
+    const U4 r = philox4x32_10(static_cast<uint32_t>(node), chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_RAND, k0, k1);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        if (4 * static_cast<int64_t>(quad) + c >= n_chains) continue;
+        const uint32_t x = pick(r, c);
+        const uint32_t v = kind == 0 ? (x >> 31) : static_cast<uint32_t>((static_cast<uint64_t>(x >> 8) * static_cast<uint64_t>(kind)) >> 24);
+        out |= v << (8 * c);
+    }
+    *reinterpret_cast<uint32_t*>(dst + static_cast<int64_t>(node) * ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// [chain][node] (host order) <-> [node][chain] (device order), through a 32x32 shared-memory tile.
+__global__ void k_transpose_in(const uint8_t* src, uint8_t* dst, int64_t n, int64_t n_chains, int64_t ld) {
+    __shared__ uint8_t tile[32][33];
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
+        tile[r][threadIdx.x] = (chain < n_chains && node < n) ? src[chain * n + node] : 0;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
+        if (node < n && chain < ld) dst[node * ld + chain] = chain < n_chains ? tile[threadIdx.x][r] : 0;
+    }
+}
+__global__ void k_transpose_out(const uint8_t* src, uint8_t* dst, int64_t n, int64_t n_chains, int64_t ld) {
+    __shared__ uint8_t tile[32][33];
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
+        tile[r][threadIdx.x] = (node < n && chain < n_chains) ? src[node * ld + chain] : 0;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
+        if (chain < n_chains && node < n) dst[chain * n + node] = tile[threadIdx.x][r];
+    }
+}
+
+// Moment observer (moment.rs:205-233): per row the product of f(x) over its members, summed over chains.
+// One warp-row = one moment row; lanes stride over chain words; exact int64 accumulation.
+__global__ void __launch_bounds__(256) k_moments(const int64_t* row_ptr, const int32_t* mem_sd, const int32_t* mem_pos, int64_t n_rows,
+                                                 const uint8_t* cls0, const uint8_t* cls1, int64_t ld, int64_t n_chains, int32_t spin_transform,
+                                                 unsigned long long* sums) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (row >= n_rows) return;
+    const int64_t b = row_ptr[row], e = row_ptr[row + 1];
+    long long acc = 0;
+    for (int64_t quad = threadIdx.x; 4 * quad < n_chains; quad += 32) {
+        long long prod[4] = {1, 1, 1, 1};
+        for (int64_t q = b; q < e; ++q) {
+            const uint8_t* base = mem_sd[q] == 0 ? cls0 : cls1;
+            const uint32_t wd = *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(mem_pos[q]) * ld + 4 * quad);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const long long x = (wd >> (8 * c)) & 0xffu;
+                prod[c] *= spin_transform ? 2 * x - 1 : x;
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (4 * quad + c < n_chains) acc += prod[c];
+    }
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
+    if (threadIdx.x == 0) atomicAdd(sums + row, static_cast<unsigned long long>(acc));
+}
+// Category counts per observed node.
+__global__ void __launch_bounds__(256) k_marginals(const int32_t* node_sd, const int32_t* node_pos, int64_t n_nodes, int32_t K, const uint8_t* cls0,
+                                                   const uint8_t* cls1, int64_t ld, int64_t n_chains, unsigned long long* counts) {
+    const int64_t node = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (node >= n_nodes) return;
+    const uint8_t* row = (node_sd[node] == 0 ? cls0 : cls1) + static_cast<int64_t>(node_pos[node]) * ld;
+    for (int cat = 0; cat < K; ++cat) {
+        int cnt = 0;
+        for (int64_t chain = threadIdx.x; chain < n_chains; chain += 32) cnt += row[chain] == cat;
+        for (int off = 16; off > 0; off >>= 1) cnt += __shfl_down_sync(0xffffffffu, cnt, off);
+        if (threadIdx.x == 0 && cnt) atomicAdd(counts + node * K + cat, static_cast<unsigned long long>(cnt));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Host helpers.
+// ---------------------------------------------------------------------------------------------------------
+static int32_t upload(DevBuf& buf, const void* host, size_t bytes, cudaStream_t st) {
+    if (int32_t rc = buf.alloc(bytes)) return rc;
+    if (bytes) CU_TRY(cudaMemcpyAsync(buf.p, host, bytes, cudaMemcpyHostToDevice, st));
+    return THRML_OK;
+}
+static dim3 grid_nq(int64_t n, int64_t ld) { return dim3(static_cast<unsigned>((n + 7) / 8), static_cast<unsigned>((ld / 4 + 31) / 32)); }
+static int32_t need_scratch(thrml_state* s, size_t bytes) {
+    if (s->scratch.bytes >= bytes) return THRML_OK;
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return s->scratch.alloc(bytes);
+}
+
+extern "C" {
+
+int32_t thrml_ctx_create(int32_t device_id, thrml_ctx** out) {
+    if (!out) return fail(THRML_ERR_INVALID_ARG, "null output");
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) return fail(THRML_ERR_CUDA, std::string("no usable CUDA device: ") + cudaGetErrorString(e));
+    if (device_id < 0 || device_id >= count) return fail(THRML_ERR_INVALID_ARG, "device id out of range");
+    CU_TRY(cudaSetDevice(device_id));
+    auto ctx = std::make_unique<thrml_ctx>();
+    ctx->device = device_id;
+    CU_TRY(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
+    cudaDeviceProp prop;
+    CU_TRY(cudaGetDeviceProperties(&prop, device_id));
+    ctx->sm_count = prop.multiProcessorCount;
+    *out = ctx.release();
+    return THRML_OK;
+}
+void thrml_ctx_destroy(thrml_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+}
+int32_t thrml_ctx_synchronize(thrml_ctx* ctx) {
+    if (!ctx) return fail(THRML_ERR_INVALID_ARG, "null context");
+    CU_TRY(cudaStreamSynchronize(ctx->stream));
+    return THRML_OK;
+}
+void* thrml_ctx_stream(thrml_ctx* ctx) { return ctx ? static_cast<void*>(ctx->stream) : nullptr; }
+
+// ---------------------------------------------------------------------------------------------------------
+// Program.
+// ---------------------------------------------------------------------------------------------------------
+static int32_t rebuild_lut(thrml_program* p, BlockProg& bp) {
+    const int64_t total = bp.n * LUT_SIZE;
+    k_build_lut<<<static_cast<unsigned>((total + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
+                                                                                         bp.d_lut.as<uint32_t>());
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
+
+int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out) {
+    if (!ctx || !b || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (!b->compiled) return fail(THRML_ERR_INVALID_ARG, "builder is not compiled");
+    CU_TRY(cudaSetDevice(ctx->device));
+    auto p = std::make_unique<thrml_program>();
+    p->ctx = ctx;
+    p->n_free = static_cast<int32_t>(b->free_blocks.size());
+    p->n_clamped = static_cast<int32_t>(b->clamped_blocks.size());
+    p->n_classes = b->n_classes;
+    p->sd_spin = b->sd_spin;
+    p->sd_cat = b->sd_cat;
+    p->class_size = b->class_size;
+    p->sampling_order = b->sampling_order;
+    p->loc_sd = b->loc_sd;
+    p->loc_pos = b->loc_pos;
+    p->blocks.resize(p->n_free + p->n_clamped);
+    for (int32_t i = 0; i < p->n_free + p->n_clamped; ++i) {
+        const BlockInfo& bi = i < p->n_free ? b->free_blocks[i] : b->clamped_blocks[i - p->n_free];
+        BlockProg& bp = p->blocks[i];
+        bp.kind = bi.kind;
+        bp.sd = bi.sd;
+        bp.is_cat = bi.kind != 0;
+        bp.n = static_cast<int64_t>(bi.nodes.size());
+        bp.offset = bi.offset;
+        if (i >= p->n_free) continue;
+        const auto& tabs = b->tables[i];
+        bp.n_tabs = static_cast<int32_t>(tabs.size());
+        bp.kernel = bp.is_cat ? 2 : 0;
+        bool lut_ok = !bp.is_cat && !tabs.empty();
+        for (const SlotTable& t : tabs) {
+            const int32_t n_tails = static_cast<int32_t>(t.idx.size());
+            if (n_tails > MAX_TAILS) return fail(THRML_ERR_UNSUPPORTED, "an interaction group has more than 8 tail node blocks");
+            if (n_tails - t.n_spin > 1) return fail(THRML_ERR_UNSUPPORTED, "only the first categorical tail of a group is honoured by the reference samplers; groups with two or more are not supported");
+            const bool has_cat = n_tails > t.n_spin;
+            if (bp.is_cat) {
+                if (t.wdim != (has_cat ? bp.kind * bp.kind : bp.kind))
+                    return fail(THRML_ERR_UNSUPPORTED, "categorical block weights must be [rows, K, 1] or [rows, K, K] with K the block's category count");
+            } else if (!has_cat && t.wdim != 1) {
+                return fail(THRML_ERR_UNSUPPORTED, "spin block weights without a categorical tail must be [rows, 1, 1]");
+            }
+            if (has_cat || t.wdim != 1 || n_tails != t.n_spin || t.n_spin > 1) lut_ok = false;
+            DevTable d{};
+            d.k = t.k; d.wdim = t.wdim; d.n_spin = t.n_spin; d.n_tails = n_tails;
+            for (int32_t tl = 0; tl < n_tails; ++tl) {
+                bp.bufs.emplace_back(new DevBuf());
+                if (int32_t rc = upload(*bp.bufs.back(), t.idx[tl].data(), t.idx[tl].size() * 4, ctx->stream)) return rc;
+                d.idx[tl] = bp.bufs.back()->as<int32_t>();
+            }
+            bp.bufs.emplace_back(new DevBuf());
+            if (int32_t rc = upload(*bp.bufs.back(), t.active.data(), t.active.size(), ctx->stream)) return rc;
+            d.active = bp.bufs.back()->as<uint8_t>();
+            bp.bufs.emplace_back(new DevBuf());
+            if (int32_t rc = upload(*bp.bufs.back(), t.w.data(), t.w.size() * 4, ctx->stream)) return rc;
+            d.w = bp.bufs.back()->as<float>();
+            bp.w_bufs.push_back(bp.bufs.back().get());
+            bp.w_len.push_back(t.w.size());
+            bp.host_tabs.push_back(d);
+        }
+        if (int32_t rc = upload(bp.d_tabs, bp.host_tabs.data(), bp.host_tabs.size() * sizeof(DevTable), ctx->stream)) return rc;
+        if (lut_ok) {
+            // compact neighbour list in table order, slot order; a node with more than 8 neighbour slots rules the kernel out
+            std::vector<int32_t> nbr(static_cast<size_t>(bp.n) * LUT_BITS, -1);
+            for (int64_t i2 = 0; i2 < bp.n && lut_ok; ++i2) {
+                int cnt = 0;
+                for (const SlotTable& t : tabs) {
+                    if (t.n_spin != 1) continue;
+                    for (int32_t j = 0; j < t.k; ++j) {
+                        const size_t flat = static_cast<size_t>(i2) * t.k + j;
+                        if (!t.active[flat]) continue;
+                        if (cnt == LUT_BITS) { lut_ok = false; break; }
+                        nbr[static_cast<size_t>(i2) * LUT_BITS + cnt++] = t.idx[0][flat];
+                    }
+                    if (!lut_ok) break;
+                }
+            }
+            if (lut_ok) {
+                if (int32_t rc = upload(bp.d_nbr, nbr.data(), nbr.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = bp.d_lut.alloc(static_cast<size_t>(bp.n) * LUT_SIZE * 4)) return rc;
+                if (int32_t rc = rebuild_lut(p.get(), bp)) return rc;
+                bp.kernel = 1;
+            }
+        }
+        CU_TRY(cudaStreamSynchronize(ctx->stream));  // host vectors above go out of scope
+    }
+    // A superblock is updated in place unless one of its blocks reads a position that the superblock writes
+    // (several blocks updated "at the same time", sampling.rs:40-59, or a block with edges inside itself).
+    p->staged.assign(p->sampling_order.size(), 0);
+    for (size_t g = 0; g < p->sampling_order.size(); ++g) {
+        const auto& members = p->sampling_order[g];
+        int64_t rows = 0;
+        bool hit = false;
+        for (int32_t m : members) rows += p->blocks[m].n;
+        for (int32_t m : members) {
+            for (const SlotTable& t : b->tables[m]) {
+                for (size_t tl = 0; tl < t.idx.size() && !hit; ++tl)
+                    for (int32_t o : members) {
+                        const BlockProg& ob = p->blocks[o];
+                        if (ob.sd != t.tail_sd[tl]) continue;
+                        const int32_t lo = static_cast<int32_t>(ob.offset), hi = static_cast<int32_t>(ob.offset + ob.n);
+                        const auto& ix = t.idx[tl];
+                        for (size_t f = 0; f < ix.size(); ++f)
+                            if (t.active[f] && ix[f] >= lo && ix[f] < hi) { hit = true; break; }
+                        if (hit) break;
+                    }
+                if (hit) break;
+            }
+            if (hit) break;
+        }
+        if (hit) {
+            p->staged[g] = 1;
+            p->max_stage_rows = std::max(p->max_stage_rows, rows);
+        }
+    }
+    *out = p.release();
+    return THRML_OK;
+}
+void thrml_program_destroy(thrml_program* p) {
+    if (!p) return;
+    cudaSetDevice(p->ctx->device);
+    cudaStreamSynchronize(p->ctx->stream);
+    delete p;
+}
+int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w) {
+    if (!p || !w) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (block < 0 || block >= p->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+    BlockProg& bp = p->blocks[block];
+    if (t < 0 || t >= bp.n_tabs) return fail(THRML_ERR_INVALID_ARG, "table index out of range");
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    CU_TRY(cudaMemcpyAsync(bp.w_bufs[t]->p, w, bp.w_len[t] * 4, cudaMemcpyHostToDevice, p->ctx->stream));
+    if (bp.kernel == 1)
+        if (int32_t rc = rebuild_lut(p, bp)) return rc;
+    CU_TRY(cudaStreamSynchronize(p->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out) {
+    if (!p || !kind_out || block < 0 || block >= p->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+    *kind_out = p->blocks[block].kernel;
+    return THRML_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// State.
+// ---------------------------------------------------------------------------------------------------------
+int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_offset, thrml_state** out) {
+    if (!p || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (n_chains <= 0) return fail(THRML_ERR_INVALID_ARG, "n_chains must be positive");
+    if (chain_offset < 0 || (chain_offset & 15)) return fail(THRML_ERR_INVALID_ARG, "chain_offset must be a non-negative multiple of 16");
+    if (chain_offset + n_chains > (1LL << 32)) return fail(THRML_ERR_INVALID_ARG, "global chain ids must stay below 2^32");
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    auto s = std::make_unique<thrml_state>();
+    s->prog = p;
+    s->n_chains = n_chains;
+    s->chain_offset = chain_offset;
+    s->ld = (n_chains + 15) / 16 * 16;
+    for (int32_t c = 0; c < p->n_classes; ++c) {
+        if (int32_t rc = s->cls[c].alloc(static_cast<size_t>(p->class_size[c]) * s->ld)) return rc;
+        CU_TRY(cudaMemsetAsync(s->cls[c].p, 0, s->cls[c].bytes, p->ctx->stream));
+    }
+    if (p->max_stage_rows > 0)
+        if (int32_t rc = s->stage.alloc(static_cast<size_t>(p->max_stage_rows) * s->ld)) return rc;
+    CU_TRY(cudaStreamSynchronize(p->ctx->stream));
+    *out = s.release();
+    return THRML_OK;
+}
+void thrml_state_destroy(thrml_state* s) {
+    if (!s) return;
+    cudaSetDevice(s->prog->ctx->device);
+    cudaStreamSynchronize(s->prog->ctx->stream);
+    delete s;
+}
+
+static int32_t check_block(const thrml_state* s, int32_t block) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (block < 0 || block >= s->prog->n_free + s->prog->n_clamped) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+    return THRML_OK;
+}
+int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    const BlockProg& bp = s->prog->blocks[block];
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const size_t bytes = static_cast<size_t>(bp.n) * s->n_chains;
+    if (int32_t rc = need_scratch(s, bytes)) return rc;
+    CU_TRY(cudaMemcpyAsync(s->scratch.p, host, bytes, cudaMemcpyHostToDevice, st));
+    dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((s->ld + 31) / 32));
+    k_transpose_in<<<grid, dim3(32, 8), 0, st>>>(s->scratch.as<uint8_t>(), s->rows(bp.sd) + bp.offset * s->ld, bp.n, s->n_chains, s->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    const BlockProg& bp = s->prog->blocks[block];
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const size_t bytes = static_cast<size_t>(bp.n) * s->n_chains;
+    if (int32_t rc = need_scratch(s, bytes)) return rc;
+    dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((s->n_chains + 31) / 32));
+    k_transpose_out<<<grid, dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->scratch.as<uint8_t>(), bp.n, s->n_chains, s->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(host, s->scratch.p, bytes, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+int32_t thrml_state_upload_f32(thrml_state* s, int32_t block, const float* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    const BlockProg& bp = s->prog->blocks[block];
+    const size_t cnt = static_cast<size_t>(bp.n) * s->n_chains;
+    std::vector<uint8_t> tmp(cnt);
+    const float top = bp.is_cat ? static_cast<float>(bp.kind - 1) : 1.0f;
+    for (size_t i = 0; i < cnt; ++i) {
+        const float v = host[i];
+        if (!(v >= 0.0f && v <= top) || v != static_cast<float>(static_cast<int>(v)))
+            return fail(THRML_ERR_INVALID_ARG, bp.is_cat ? "categorical state must be an integer in [0, K)" : "spin state must be 0 or 1");
+        tmp[i] = static_cast<uint8_t>(v);
+    }
+    return thrml_state_upload_u8(s, block, tmp.data());
+}
+int32_t thrml_state_download_f32(thrml_state* s, int32_t block, float* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    const BlockProg& bp = s->prog->blocks[block];
+    const size_t cnt = static_cast<size_t>(bp.n) * s->n_chains;
+    std::vector<uint8_t> tmp(cnt);
+    if (int32_t rc = thrml_state_download_u8(s, block, tmp.data())) return rc;
+    for (size_t i = 0; i < cnt; ++i) host[i] = static_cast<float>(tmp[i]);
+    return THRML_OK;
+}
+
+int32_t thrml_hinton_init(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const float* biases, float beta, uint64_t key, const float* inj_u) {
+    if (!s || n_blocks < 0 || (n_blocks > 0 && (!blocks || !biases))) return fail(THRML_ERR_INVALID_ARG, "bad hinton_init arguments");
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    std::vector<uint64_t> keys(static_cast<size_t>(n_blocks));
+    rng_split(key, n_blocks, keys.data());  // ising.rs:618
+    int64_t total = 0;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        if (int32_t rc = check_block(s, blocks[i])) return rc;
+        if (s->prog->blocks[blocks[i]].is_cat) return fail(THRML_ERR_INVALID_ARG, "hinton_init applies to spin blocks");
+        total += s->prog->blocks[blocks[i]].n;
+    }
+    const size_t bias_bytes = static_cast<size_t>(total) * 4, inj_bytes = inj_u ? static_cast<size_t>(total) * s->n_chains * 4 : 0;
+    if (int32_t rc = need_scratch(s, bias_bytes + inj_bytes)) return rc;
+    float* d_bias = s->scratch.as<float>();
+    float* d_inj = inj_u ? d_bias + total : nullptr;
+    CU_TRY(cudaMemcpyAsync(d_bias, biases, bias_bytes, cudaMemcpyHostToDevice, st));
+    if (inj_u) CU_TRY(cudaMemcpyAsync(d_inj, inj_u, inj_bytes, cudaMemcpyHostToDevice, st));
+    int64_t boff = 0;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        const BlockProg& bp = s->prog->blocks[blocks[i]];
+        k_hinton<<<grid_nq(bp.n, s->ld), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), d_bias + boff, beta,
+                                                                 static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[i]),
+                                                                 static_cast<uint32_t>(keys[i] >> 32), d_inj ? d_inj + boff * s->n_chains : nullptr);
+        CU_TRY(cudaGetLastError());
+        boff += bp.n;
+    }
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+int32_t thrml_state_randomize(thrml_state* s, uint64_t key) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const int32_t nf = s->prog->n_free;
+    std::vector<uint64_t> keys(static_cast<size_t>(nf));
+    rng_split(key, nf, keys.data());
+    for (int32_t b = 0; b < nf; ++b) {
+        const BlockProg& bp = s->prog->blocks[b];
+        k_randomize<<<grid_nq(bp.n, s->ld), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), bp.kind,
+                                                                    static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[b]),
+                                                                    static_cast<uint32_t>(keys[b] >> 32));
+        CU_TRY(cudaGetLastError());
+    }
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Sweeps.
+// ---------------------------------------------------------------------------------------------------------
+struct NoiseCursor {
+    const float* u = nullptr;
+    int64_t len = 0, pos = 0;
+};
+
+// One block update (program.rs:324-393 + the sampler), asynchronous on the context's stream.  mode 0 sample, 2 fields.
+static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCursor* inj, uint8_t* dst, float* fields) {
+    thrml_program* p = s->prog;
+    const BlockProg& bp = p->blocks[block];
+    cudaStream_t st = p->ctx->stream;
+    const uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
+    const uint32_t word0 = static_cast<uint32_t>(s->chain_offset >> 2);
+    if (bp.kernel == 1 && !inj && !fields) {
+        LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, k0, k1};
+        const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
+        k_spin_lut<<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        CU_TRY(cudaGetLastError());
+        return THRML_OK;
+    }
+    UpdateArgs a{};
+    a.tabs = bp.d_tabs.as<DevTable>();
+    a.n_tabs = bp.n_tabs;
+    a.n = static_cast<int32_t>(bp.n);
+    a.K = bp.kind;
+    a.ld = s->ld;
+    a.n_chains = s->n_chains;
+    a.chain_word0 = word0;
+    a.spin = p->sd_spin >= 0 ? s->rows(p->sd_spin) : nullptr;
+    a.cat = p->sd_cat >= 0 ? s->rows(p->sd_cat) : nullptr;
+    a.dst = dst;
+    a.k0 = k0;
+    a.k1 = k1;
+    a.fields = fields;
+    if (inj) {
+        const int64_t need = bp.n * s->n_chains * (bp.is_cat ? bp.kind : 1);
+        if (inj->pos + need > inj->len) return fail(THRML_ERR_INVALID_ARG, "injected noise is shorter than the updates it must feed");
+        if (int32_t rc = need_scratch(s, static_cast<size_t>(need) * 4)) return rc;
+        CU_TRY(cudaMemcpyAsync(s->scratch.p, inj->u + inj->pos, static_cast<size_t>(need) * 4, cudaMemcpyHostToDevice, st));
+        inj->pos += need;
+        a.inj = s->scratch.as<float>();
+    }
+    const dim3 grid = grid_nq(bp.n, s->ld), blk(32, 8);
+    if (bp.is_cat) {
+        if (fields) k_cat_generic<2><<<grid, blk, 0, st>>>(a);
+        else if (inj) k_cat_generic<1><<<grid, blk, 0, st>>>(a);
+        else k_cat_generic<0><<<grid, blk, 0, st>>>(a);
+    } else {
+        if (fields) k_spin_generic<2><<<grid, blk, 0, st>>>(a);
+        else if (inj) k_spin_generic<1><<<grid, blk, 0, st>>>(a);
+        else k_spin_generic<0><<<grid, blk, 0, st>>>(a);
+    }
+    CU_TRY(cudaGetLastError());
+    if (inj) CU_TRY(cudaStreamSynchronize(st));  // the scratch slice is reused by the next block
+    return THRML_OK;
+}
+
+// sample_blocks (sampling.rs:28-63), asynchronous.
+static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj) {
+    thrml_program* p = s->prog;
+    std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
+    rng_split(key, p->n_free, keys.data());
+    cudaStream_t st = p->ctx->stream;
+    for (size_t g = 0; g < p->sampling_order.size(); ++g) {
+        const auto& members = p->sampling_order[g];
+        if (!p->staged[g]) {
+            for (int32_t m : members) {
+                const BlockProg& bp = p->blocks[m];
+                if (int32_t rc = launch_block(s, m, keys[m], inj, s->rows(bp.sd) + bp.offset * s->ld, nullptr)) return rc;
+            }
+            continue;
+        }
+        int64_t row = 0;
+        for (int32_t m : members) {
+            if (int32_t rc = launch_block(s, m, keys[m], inj, s->stage.as<uint8_t>() + row * s->ld, nullptr)) return rc;
+            row += p->blocks[m].n;
+        }
+        row = 0;
+        for (int32_t m : members) {  // all members written back together (sampling.rs:57-59)
+            const BlockProg& bp = p->blocks[m];
+            CU_TRY(cudaMemcpyAsync(s->rows(bp.sd) + bp.offset * s->ld, s->stage.as<uint8_t>() + row * s->ld, static_cast<size_t>(bp.n) * s->ld, cudaMemcpyDeviceToDevice, st));
+            row += bp.n;
+        }
+    }
+    return THRML_OK;
+}
+// run_blocks (sampling.rs:81-106), asynchronous.
+static int32_t run(thrml_state* s, uint64_t key, int64_t n_iters, NoiseCursor* inj) {
+    if (n_iters <= 0) return THRML_OK;
+    std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
+    rng_split(key, n_iters, keys.data());
+    for (uint64_t k : keys)
+        if (int32_t rc = sweep(s, k, inj)) return rc;
+    return THRML_OK;
+}
+
+int32_t thrml_sample_blocks(thrml_state* s, uint64_t key, const thrml_noise* inj) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    NoiseCursor nc;
+    if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
+    if (int32_t rc = sweep(s, key, nc.u ? &nc : nullptr)) return rc;
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const thrml_noise* inj) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (n_iters < 0) return fail(THRML_ERR_INVALID_ARG, "n_iters must be non-negative");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    NoiseCursor nc;
+    if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
+    if (int32_t rc = run(s, key, n_iters, nc.u ? &nc : nullptr)) return rc;
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out) {
+    if (!s || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (block < 0 || block >= s->prog->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const BlockProg& bp = s->prog->blocks[block];
+    const size_t cnt = static_cast<size_t>(bp.n) * s->n_chains * (bp.is_cat ? bp.kind : 1);
+    DevBuf tmp;
+    if (int32_t rc = tmp.alloc(cnt * 4)) return rc;
+    if (int32_t rc = launch_block(s, block, 0, nullptr, nullptr, tmp.as<float>())) return rc;
+    CU_TRY(cudaMemcpyAsync(out, tmp.p, cnt * 4, cudaMemcpyDeviceToHost, s->prog->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return THRML_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Observers.
+// ---------------------------------------------------------------------------------------------------------
+int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* rows_per_type, const int64_t* row_ptr, const int64_t* members,
+                             int32_t transform_to_spin, thrml_moments** out) {
+    if (!p || !out || n_types < 0 || (n_types > 0 && (!rows_per_type || !row_ptr))) return fail(THRML_ERR_INVALID_ARG, "bad moment spec");
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    auto m = std::make_unique<thrml_moments>();
+    m->prog = p;
+    m->spin_transform = transform_to_spin ? 1 : 0;
+    m->rows_per_type.assign(rows_per_type, rows_per_type + n_types);
+    for (int64_t r : m->rows_per_type) {
+        if (r < 0) return fail(THRML_ERR_INVALID_ARG, "negative row count");
+        m->total_rows += r;
+    }
+    const int64_t n_mem = m->total_rows ? row_ptr[m->total_rows] : 0;
+    std::vector<int32_t> sd(static_cast<size_t>(n_mem)), pos(static_cast<size_t>(n_mem));
+    for (int64_t q = 0; q < n_mem; ++q) {
+        const int64_t nd = members[q];
+        if (nd < 0 || nd >= static_cast<int64_t>(p->loc_sd.size()) || p->loc_sd[nd] < 0) return fail(THRML_ERR_INVALID_ARG, "Node not found in global location map");
+        sd[q] = p->loc_sd[nd];
+        pos[q] = static_cast<int32_t>(p->loc_pos[nd]);
+    }
+    cudaStream_t st = p->ctx->stream;
+    const int64_t zero = 0;
+    if (int32_t rc = upload(m->d_row_ptr, m->total_rows ? row_ptr : &zero, static_cast<size_t>(m->total_rows + 1) * 8, st)) return rc;
+    if (int32_t rc = upload(m->d_mem_sd, sd.data(), sd.size() * 4, st)) return rc;
+    if (int32_t rc = upload(m->d_mem_pos, pos.data(), pos.size() * 4, st)) return rc;
+    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(std::max<int64_t>(m->total_rows, 1)) * 8)) return rc;
+    CU_TRY(cudaMemsetAsync(m->d_sums.p, 0, m->d_sums.bytes, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    *out = m.release();
+    return THRML_OK;
+}
+int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t n_blocks, int32_t K, thrml_moments** out) {
+    if (!p || !out || !blocks || n_blocks <= 0 || K < 1 || K > 255) return fail(THRML_ERR_INVALID_ARG, "bad marginal spec");
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    auto m = std::make_unique<thrml_moments>();
+    m->prog = p;
+    m->mode = 1;
+    m->K = K;
+    std::vector<int32_t> sd, pos;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        if (blocks[i] < 0 || blocks[i] >= p->n_free + p->n_clamped) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+        const BlockProg& bp = p->blocks[blocks[i]];
+        for (int64_t j = 0; j < bp.n; ++j) {
+            sd.push_back(bp.sd);
+            pos.push_back(static_cast<int32_t>(bp.offset + j));
+        }
+    }
+    m->total_rows = static_cast<int64_t>(sd.size()) * K;
+    m->rows_per_type.assign(1, m->total_rows);
+    cudaStream_t st = p->ctx->stream;
+    if (int32_t rc = upload(m->d_node_sd, sd.data(), sd.size() * 4, st)) return rc;
+    if (int32_t rc = upload(m->d_node_pos, pos.data(), pos.size() * 4, st)) return rc;
+    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(m->total_rows) * 8)) return rc;
+    CU_TRY(cudaMemsetAsync(m->d_sums.p, 0, m->d_sums.bytes, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    *out = m.release();
+    return THRML_OK;
+}
+void thrml_moments_destroy(thrml_moments* m) {
+    if (!m) return;
+    cudaSetDevice(m->prog->ctx->device);
+    cudaStreamSynchronize(m->prog->ctx->stream);
+    delete m;
+}
+int32_t thrml_moments_reset(thrml_moments* m) {
+    if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
+    CU_TRY(cudaSetDevice(m->prog->ctx->device));
+    CU_TRY(cudaMemsetAsync(m->d_sums.p, 0, m->d_sums.bytes, m->prog->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(m->prog->ctx->stream));
+    m->n_obs = 0;
+    return THRML_OK;
+}
+static int32_t observe_async(thrml_moments* m, thrml_state* s) {
+    if (m->prog != s->prog) return fail(THRML_ERR_INVALID_ARG, "observer and state belong to different programs");
+    cudaStream_t st = s->prog->ctx->stream;
+    const uint8_t* c0 = s->cls[0].as<uint8_t>();
+    const uint8_t* c1 = s->cls[1].as<uint8_t>();
+    if (m->mode == 0) {
+        if (m->total_rows > 0) {
+            k_moments<<<static_cast<unsigned>((m->total_rows + 7) / 8), dim3(32, 8), 0, st>>>(m->d_row_ptr.as<int64_t>(), m->d_mem_sd.as<int32_t>(), m->d_mem_pos.as<int32_t>(),
+                                                                                               m->total_rows, c0, c1, s->ld, s->n_chains, m->spin_transform,
+                                                                                               m->d_sums.as<unsigned long long>());
+            CU_TRY(cudaGetLastError());
+        }
+    } else {
+        const int64_t nodes = m->total_rows / m->K;
+        k_marginals<<<static_cast<unsigned>((nodes + 7) / 8), dim3(32, 8), 0, st>>>(m->d_node_sd.as<int32_t>(), m->d_node_pos.as<int32_t>(), nodes, m->K, c0, c1, s->ld,
+                                                                                     s->n_chains, m->d_sums.as<unsigned long long>());
+        CU_TRY(cudaGetLastError());
+    }
+    m->n_obs += s->n_chains;
+    return THRML_OK;
+}
+int32_t thrml_moments_observe(thrml_moments* m, thrml_state* s) {
+    if (!m || !s) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    if (int32_t rc = observe_async(m, s)) return rc;
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_moments_read(thrml_moments* m, int32_t type, int64_t* sums_out, int64_t* n_obs_out) {
+    if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
+    if (type < 0 || type >= static_cast<int32_t>(m->rows_per_type.size())) return fail(THRML_ERR_INVALID_ARG, "moment type out of range");
+    CU_TRY(cudaSetDevice(m->prog->ctx->device));
+    int64_t start = 0;
+    for (int32_t t = 0; t < type; ++t) start += m->rows_per_type[t];
+    if (sums_out && m->rows_per_type[type] > 0) {
+        CU_TRY(cudaMemcpyAsync(sums_out, m->d_sums.as<int64_t>() + start, static_cast<size_t>(m->rows_per_type[type]) * 8, cudaMemcpyDeviceToHost, m->prog->ctx->stream));
+        CU_TRY(cudaStreamSynchronize(m->prog->ctx->stream));
+    }
+    if (n_obs_out) *n_obs_out = m->n_obs;
+    return THRML_OK;
+}
+int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_t* count_out) {
+    if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
+    if (dev_ptr_out) *dev_ptr_out = m->d_sums.p;
+    if (count_out) *count_out = m->total_rows;
+    return THRML_OK;
+}
+int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs) {
+    if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
+    m->n_obs += n_obs;
+    return THRML_OK;
+}
+
+// StateObserver (state_observer.rs:25-47): copy the listed blocks' rows, [observed node][chain].
+static int32_t observe_states(thrml_state* s, const int32_t* obs_blocks, int32_t n_obs_blocks, uint8_t* dst) {
+    cudaStream_t st = s->prog->ctx->stream;
+    int64_t row = 0;
+    for (int32_t i = 0; i < n_obs_blocks; ++i) {
+        const BlockProg& bp = s->prog->blocks[obs_blocks[i]];
+        CU_TRY(cudaMemcpy2DAsync(dst + row * s->n_chains, static_cast<size_t>(s->n_chains), s->rows(bp.sd) + bp.offset * s->ld, static_cast<size_t>(s->ld),
+                                 static_cast<size_t>(s->n_chains), static_cast<size_t>(bp.n), cudaMemcpyDeviceToHost, st));
+        row += bp.n;
+    }
+    return THRML_OK;
+}
+
+int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample, thrml_moments* moments,
+                                      const int32_t* obs_blocks, int32_t n_obs_blocks, uint8_t* obs_out, const thrml_noise* inj) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
+    if (obs_out && (!obs_blocks || n_obs_blocks <= 0)) return fail(THRML_ERR_INVALID_ARG, "obs_out needs a block list");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    int64_t obs_rows = 0;
+    for (int32_t i = 0; i < n_obs_blocks; ++i) {
+        if (int32_t rc = check_block(s, obs_blocks[i])) return rc;
+        obs_rows += s->prog->blocks[obs_blocks[i]].n;
+    }
+    NoiseCursor nc;
+    if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
+    NoiseCursor* ncp = nc.u ? &nc : nullptr;
+    uint64_t two[2];
+    rng_split(key, 2, two);  // split_two, sampling.rs:189
+    if (int32_t rc = run(s, two[0], n_warmup, ncp)) return rc;
+    if (moments)
+        if (int32_t rc = observe_async(moments, s)) return rc;
+    if (obs_out)
+        if (int32_t rc = observe_states(s, obs_blocks, n_obs_blocks, obs_out)) return rc;
+    if (n_samples > 1) {  // sampling.rs:215-217,249-257: nothing more for n_samples <= 1
+        std::vector<uint64_t> keys(static_cast<size_t>(n_samples - 1));
+        rng_split(two[1], n_samples - 1, keys.data());
+        const int64_t stride = obs_rows * s->n_chains;
+        for (int64_t i = 0; i < n_samples - 1; ++i) {
+            if (int32_t rc = run(s, keys[i], steps_per_sample, ncp)) return rc;
+            if (moments)
+                if (int32_t rc = observe_async(moments, s)) return rc;
+            if (obs_out)
+                if (int32_t rc = observe_states(s, obs_blocks, n_obs_blocks, obs_out + (i + 1) * stride)) return rc;
+        }
+    }
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return THRML_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,340 @@
+"""Thin object wrappers over the C ABI handles: Context, Builder (host index compiler), Program, ChainState, Moments.
+
+These keep device state resident between calls; the reference-shaped functions in samplers.py / models.py are
+written on top of them.
+"""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import _ffi
+from ._ffi import check, f32, i32, i64, lib, ptr
+
+SAMPLER_SPIN = 0
+SAMPLER_CATEGORICAL = 1
+
+_default_ctx = {}
+
+
+class Context:
+    """One CUDA device + one stream (thrml_ctx)."""
+
+    def __init__(self, device_id=0):
+        self.h = C.c_void_p()
+        check(lib().thrml_ctx_create(C.c_int32(device_id), C.byref(self.h)))
+        self.device_id = device_id
+
+    def synchronize(self):
+        check(lib().thrml_ctx_synchronize(self.h))
+
+    @property
+    def stream(self):
+        return lib().thrml_ctx_stream(self.h)
+
+    def close(self):
+        if self.h:
+            lib().thrml_ctx_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def default_context(device_id=None):
+    """Process-wide context; one process drives one GPU (LOCAL_RANK selects it under torchrun)."""
+    if device_id is None:
+        device_id = int(os.environ.get("LOCAL_RANK", "0"))
+    if device_id not in _default_ctx:
+        _default_ctx[device_id] = Context(device_id)
+    return _default_ctx[device_id]
+
+
+def rng_split(key, n):
+    out = np.zeros(max(int(n), 0), dtype=np.uint64)
+    check(lib().thrml_rng_split(C.c_uint64(int(key)), C.c_int64(int(n)), ptr(out)))
+    return out
+
+
+def lattice_edges(side_len, torus):
+    side, ne = C.c_int64(), C.c_int64()
+    check(lib().thrml_lattice_edges(C.c_int64(side_len), C.c_int32(int(torus)), C.byref(side), C.byref(ne), None, None))
+    edges = np.zeros((ne.value, 2), dtype=np.int64)
+    colour = np.zeros(side.value * side.value, dtype=np.int32)
+    check(lib().thrml_lattice_edges(C.c_int64(side_len), C.c_int32(int(torus)), C.byref(side), C.byref(ne), ptr(edges), ptr(colour)))
+    return side.value, edges, colour
+
+
+def greedy_coloring_arrays(n_nodes, edges):
+    edges = i64(edges).reshape(-1, 2)
+    colour = np.zeros(n_nodes, dtype=np.int32)
+    nc = C.c_int32()
+    check(lib().thrml_greedy_coloring(C.c_int64(n_nodes), C.c_int64(len(edges)), ptr(edges), ptr(colour), C.byref(nc)))
+    return colour, nc.value
+
+
+class Builder:
+    """Host-side index compiler (thrml_builder): blocks + interaction groups -> per-block slot tables."""
+
+    def __init__(self, kinds, dtype_order=None):
+        self.kinds = i32(kinds)
+        if dtype_order is None:
+            dtype_order = list(dict.fromkeys(int(k) for k in self.kinds))
+        order = i32(dtype_order)
+        self.h = C.c_void_p()
+        check(lib().thrml_builder_create(ptr(self.kinds), C.c_int64(len(self.kinds)), ptr(order), C.c_int32(len(order)), C.byref(self.h)))
+        self.free_blocks = []
+        self.clamped_blocks = []
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().thrml_builder_destroy(self.h)
+            self.h = None
+
+    def add_free_block(self, nodes, superblock=None, sampler=None):
+        nodes = i64(nodes)
+        if superblock is None:
+            superblock = len(self.free_blocks)
+        if sampler is None:
+            sampler = SAMPLER_SPIN if (len(nodes) == 0 or self.kinds[nodes[0]] == 0) else SAMPLER_CATEGORICAL
+        check(lib().thrml_builder_add_free_block(self.h, ptr(nodes), C.c_int64(len(nodes)), C.c_int32(superblock), C.c_int32(sampler)))
+        self.free_blocks.append(nodes)
+
+    def add_clamped_block(self, nodes):
+        nodes = i64(nodes)
+        check(lib().thrml_builder_add_clamped_block(self.h, ptr(nodes), C.c_int64(len(nodes))))
+        self.clamped_blocks.append(nodes)
+
+    def add_group(self, head, tails, n_spin, w):
+        head = i64(head)
+        rows = len(head)
+        tails = i64(np.array(tails, dtype=np.int64).reshape(-1, rows)) if len(tails) else np.zeros((0, rows), dtype=np.int64)
+        w = f32(w)
+        if w.ndim != 3:
+            w = w.reshape(rows, 1, 1) if w.size == rows else w.reshape(rows, -1, 1)
+        check(lib().thrml_builder_add_interaction_group(self.h, ptr(head), C.c_int64(rows), ptr(tails), C.c_int32(tails.shape[0]), C.c_int32(n_spin), ptr(w),
+                                                        C.c_int32(w.shape[1]), C.c_int32(w.shape[2])))
+
+    def add_discrete_factor(self, spin_groups, cat_groups, w):
+        w = f32(w)
+        rows = w.shape[0]
+        sg = i64(np.array(spin_groups, dtype=np.int64).reshape(-1, rows)) if len(spin_groups) else np.zeros((0, rows), dtype=np.int64)
+        cg = i64(np.array(cat_groups, dtype=np.int64).reshape(-1, rows)) if len(cat_groups) else np.zeros((0, rows), dtype=np.int64)
+        n_out = C.c_int32()
+        check(lib().thrml_builder_add_discrete_factor(self.h, ptr(sg), C.c_int32(sg.shape[0]), ptr(cg), C.c_int32(cg.shape[0]), C.c_int64(rows), ptr(w),
+                                                      C.c_int32(w.shape[1]), C.c_int32(w.shape[2]), C.byref(n_out)))
+        return n_out.value
+
+    def add_ising(self, nodes, biases, edges, weights, beta):
+        nodes, biases = i64(nodes), f32(biases)
+        edges, weights = i64(edges).reshape(-1, 2), f32(weights)
+        check(lib().thrml_builder_add_ising(self.h, ptr(nodes), C.c_int64(len(nodes)), ptr(biases), ptr(edges), C.c_int64(len(edges)), ptr(weights), C.c_float(beta)))
+
+    def compile(self):
+        check(lib().thrml_builder_compile(self.h))
+
+    def counts(self):
+        a, b, c, d = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        check(lib().thrml_builder_counts(self.h, C.byref(a), C.byref(b), C.byref(c), C.byref(d)))
+        return a.value, b.value, c.value, d.value
+
+    def node_location(self, node):
+        sd, pos = C.c_int32(), C.c_int64()
+        check(lib().thrml_builder_node_location(self.h, C.c_int64(int(node)), C.byref(sd), C.byref(pos)))
+        return sd.value, pos.value
+
+    def group(self, g):
+        rows, nt, ns, d1, d2 = C.c_int64(), C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+        check(lib().thrml_builder_group_shape(self.h, C.c_int32(g), C.byref(rows), C.byref(nt), C.byref(ns), C.byref(d1), C.byref(d2)))
+        head = np.zeros(rows.value, dtype=np.int64)
+        tails = np.zeros((nt.value, rows.value), dtype=np.int64)
+        w = np.zeros((rows.value, d1.value, d2.value), dtype=np.float32)
+        check(lib().thrml_builder_group_data(self.h, C.c_int32(g), ptr(head), ptr(tails), ptr(w)))
+        return dict(head=head, tails=tails, n_spin=ns.value, w=w)
+
+    def tables(self, block):
+        nt, n = C.c_int32(), C.c_int64()
+        check(lib().thrml_builder_block_tables(self.h, C.c_int32(block), C.byref(nt), C.byref(n)))
+        out = []
+        for t in range(nt.value):
+            k, wdim, ns, ntl, src = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()
+            check(lib().thrml_builder_table_shape(self.h, C.c_int32(block), C.c_int32(t), C.byref(k), C.byref(wdim), C.byref(ns), C.byref(ntl), C.byref(src)))
+            nk = n.value * k.value
+            rows = np.zeros(nk, dtype=np.int32)
+            active = np.zeros(nk, dtype=np.uint8)
+            w = np.zeros(nk * wdim.value, dtype=np.float32)
+            idx = np.zeros((ntl.value, nk), dtype=np.int32)
+            tsd = np.zeros(ntl.value, dtype=np.int32)
+            check(lib().thrml_builder_table_data(self.h, C.c_int32(block), C.c_int32(t), ptr(rows), ptr(active), ptr(w), ptr(idx), ptr(tsd)))
+            out.append(dict(k=k.value, wdim=wdim.value, n_spin=ns.value, source_group=src.value, rows=rows.reshape(n.value, k.value),
+                            active=active.reshape(n.value, k.value), w=w.reshape(n.value, k.value, wdim.value), idx=idx.reshape(ntl.value, n.value, k.value), tail_sd=tsd))
+        return out
+
+
+class Program:
+    """Compiled tables resident on the device (thrml_program)."""
+
+    def __init__(self, builder, ctx=None):
+        self.ctx = ctx or default_context()
+        self.builder = builder
+        self.h = C.c_void_p()
+        check(lib().thrml_program_create(self.ctx.h, builder.h, C.byref(self.h)))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().thrml_program_destroy(self.h)
+            self.h = None
+
+    def update_weights(self, block, table, w):
+        w = f32(w)
+        check(lib().thrml_program_update_weights(self.h, C.c_int32(block), C.c_int32(table), ptr(w)))
+
+    def block_kernel(self, block):
+        k = C.c_int32()
+        check(lib().thrml_program_block_kernel(self.h, C.c_int32(block), C.byref(k)))
+        return k.value
+
+    def block_len(self, block):
+        nf = len(self.builder.free_blocks)
+        return len(self.builder.free_blocks[block]) if block < nf else len(self.builder.clamped_blocks[block - nf])
+
+    def block_kind(self, block):
+        nf = len(self.builder.free_blocks)
+        nodes = self.builder.free_blocks[block] if block < nf else self.builder.clamped_blocks[block - nf]
+        return int(self.builder.kinds[nodes[0]])
+
+
+class ChainState:
+    """n_chains chains of the program's global state on the device (thrml_state)."""
+
+    def __init__(self, program, n_chains, chain_offset=0):
+        self.program = program
+        self.n_chains = int(n_chains)
+        self.h = C.c_void_p()
+        check(lib().thrml_state_create(program.h, C.c_int64(n_chains), C.c_int64(chain_offset), C.byref(self.h)))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().thrml_state_destroy(self.h)
+            self.h = None
+
+    def upload(self, block, host):
+        n = self.program.block_len(block)
+        host = np.asarray(host)
+        if host.dtype == np.uint8:
+            host = np.ascontiguousarray(host).reshape(self.n_chains, n)
+            check(lib().thrml_state_upload_u8(self.h, C.c_int32(block), ptr(host)))
+        else:
+            host = f32(host).reshape(self.n_chains, n)
+            check(lib().thrml_state_upload_f32(self.h, C.c_int32(block), ptr(host)))
+
+    def download(self, block, dtype=np.float32):
+        n = self.program.block_len(block)
+        out = np.zeros((self.n_chains, n), dtype=dtype)
+        if dtype == np.uint8:
+            check(lib().thrml_state_download_u8(self.h, C.c_int32(block), ptr(out)))
+        else:
+            check(lib().thrml_state_download_f32(self.h, C.c_int32(block), ptr(out)))
+        return out
+
+    def hinton_init(self, blocks, biases, beta, key, inj_u=None):
+        blocks, biases = i32(blocks), f32(biases)
+        inj = f32(inj_u).ravel() if inj_u is not None else None
+        check(lib().thrml_hinton_init(self.h, ptr(blocks), C.c_int32(len(blocks)), ptr(biases), C.c_float(beta), C.c_uint64(int(key)), ptr(inj)))
+
+    def randomize(self, key):
+        check(lib().thrml_state_randomize(self.h, C.c_uint64(int(key))))
+
+    def sample_blocks(self, key, inj=None):
+        nz, keep = _ffi.make_noise(inj)
+        check(lib().thrml_sample_blocks(self.h, C.c_uint64(int(key)), C.byref(nz) if nz else None))
+
+    def run_blocks(self, key, n_iters, inj=None):
+        nz, keep = _ffi.make_noise(inj)
+        check(lib().thrml_run_blocks(self.h, C.c_uint64(int(key)), C.c_int64(n_iters), C.byref(nz) if nz else None))
+
+    def fields(self, block):
+        n = self.program.block_len(block)
+        kind = self.program.block_kind(block)
+        shape = (self.n_chains, n, kind) if kind > 0 else (self.n_chains, n)
+        out = np.zeros(shape, dtype=np.float32)
+        check(lib().thrml_fields_debug(self.h, C.c_int32(block), ptr(out)))
+        return out
+
+    def sample_with_observation(self, key, n_warmup, n_samples, steps_per_sample, moments=None, obs_blocks=None, inj=None):
+        nz, keep = _ffi.make_noise(inj)
+        obs, ob = None, None
+        if obs_blocks is not None:
+            ob = i32(obs_blocks)
+            rows = sum(self.program.block_len(int(b)) for b in ob)
+            obs = np.zeros((max(int(n_samples), 1), rows, self.n_chains), dtype=np.uint8)
+        check(lib().thrml_sample_with_observation(self.h, C.c_uint64(int(key)), C.c_int64(n_warmup), C.c_int64(n_samples), C.c_int64(steps_per_sample),
+                                                  moments.h if moments is not None else None, ptr(ob), C.c_int32(0 if ob is None else len(ob)), ptr(obs),
+                                                  C.byref(nz) if nz else None))
+        return obs
+
+
+class Moments:
+    """Moment accumulator on the device (thrml_moments).  spec: list of moment types, each a list of node-id tuples."""
+
+    def __init__(self, program, spec, transform_to_spin=True):
+        self.program = program
+        self.rows_per_type = np.array([len(t) for t in spec], dtype=np.int64)
+        flat, ptrs = [], [0]
+        for t in spec:
+            for row in t:
+                flat.extend(int(x) for x in row)
+                ptrs.append(len(flat))
+        self.row_ptr = np.array(ptrs, dtype=np.int64)
+        self.members = np.array(flat, dtype=np.int64) if flat else np.zeros(1, dtype=np.int64)
+        self.h = C.c_void_p()
+        check(lib().thrml_moments_create(program.h, C.c_int32(len(spec)), ptr(self.rows_per_type), ptr(self.row_ptr), ptr(self.members),
+                                         C.c_int32(int(transform_to_spin)), C.byref(self.h)))
+
+    @classmethod
+    def from_arrays(cls, program, rows_per_type, row_ptr, members, transform_to_spin=True):
+        self = cls.__new__(cls)
+        self.program = program
+        self.rows_per_type = i64(rows_per_type)
+        self.row_ptr = i64(row_ptr)
+        self.members = i64(members)
+        self.h = C.c_void_p()
+        check(lib().thrml_moments_create(program.h, C.c_int32(len(self.rows_per_type)), ptr(self.rows_per_type), ptr(self.row_ptr), ptr(self.members),
+                                         C.c_int32(int(transform_to_spin)), C.byref(self.h)))
+        return self
+
+    @classmethod
+    def marginals(cls, program, blocks, K):
+        self = cls.__new__(cls)
+        self.program = program
+        blocks = i32(blocks)
+        n = sum(program.block_len(int(b)) for b in blocks)
+        self.rows_per_type = np.array([n * K], dtype=np.int64)
+        self.h = C.c_void_p()
+        check(lib().thrml_marginals_create(program.h, ptr(blocks), C.c_int32(len(blocks)), C.c_int32(K), C.byref(self.h)))
+        return self
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().thrml_moments_destroy(self.h)
+            self.h = None
+
+    def reset(self):
+        check(lib().thrml_moments_reset(self.h))
+
+    def observe(self, state):
+        check(lib().thrml_moments_observe(self.h, state.h))
+
+    def read(self, t):
+        out = np.zeros(int(self.rows_per_type[t]), dtype=np.int64)
+        n = C.c_int64()
+        check(lib().thrml_moments_read(self.h, C.c_int32(t), ptr(out), C.byref(n)))
+        return out, n.value
+
+    def device_buffer(self):
+        p, cnt = C.c_void_p(), C.c_int64()
+        check(lib().thrml_moments_device_buffer(self.h, C.byref(p), C.byref(cnt)))
+        return p.value, cnt.value
