@@ -1,0 +1,309 @@
+"""Benchmark of the block-Gibbs hot path on the sparse random 8-regular Ising workload
+(2^20 spins, ~4.19 M edges, greedy-coloured blocks, 4096 chains per GPU, first and second moments every sweep).
+
+    python bench.py --gpus N --steps K --warmup W            # this repository's CUDA path
+    python bench.py --impl reference --gpus N --steps K ...   # the CPU restatement of the reference's path (oracle/)
+
+One step = one Gibbs sweep over every block for every chain, followed by the moment observer.  `value` is site
+updates per second with the chain state resident in HBM; `e2e` is the same metric through one estimate-moments call
+that uploads the initial chain state from pinned host memory and reads the moment sums back.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_NODES = 1 << 20
+DEGREE = 8
+CHAINS_PER_GPU = 4096
+SEED = 0x5EED0002
+METRIC = "gibbs_site_updates_per_sec"
+UNIT = "site-updates/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--nodes", type=int, default=N_NODES, help="graph size (default: the benchmark configuration)")
+    ap.add_argument("--chains", type=int, default=CHAINS_PER_GPU, help="chains per GPU")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, device):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(device), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 + 0.3] or [r for _, r in self.rows]
+        sm, mx, reasons = [], [], set()
+        for r in rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def cpu_baseline(model, threads, target_seconds=12.0):
+    """The oracle (a C++ restatement of the reference's per-block op sequence, f32 0/1 state, materialised gathers,
+    per-sample moment loop) on this box's host cores: `threads` chains, one per thread, sweeps + moment observation."""
+    from oracle import oracle as O
+    from thrml_rs_b200 import workloads as W
+    om = W.fill_ising(O.Model(np.zeros(model["n"], np.int32)), model)
+    st = O.State(om, threads, 0, threads=threads)
+    st.randomize(1)
+    mom = O.Moments.from_arrays(om, *W.ising_moment_arrays(model))
+    st.run_blocks(2, 1)  # warm caches
+    sweeps, t0 = 0, time.time()
+    while True:
+        st.run_blocks(3 + sweeps, 1)
+        mom.observe(st)
+        sweeps += 1
+        if time.time() - t0 > target_seconds or sweeps >= 200:
+            break
+    dt = time.time() - t0
+    return {"value": model["n"] * threads * sweeps / dt, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{threads} chains x {sweeps} sweeps of the full {model['n']}-spin graph with moment observation every sweep, {dt:.1f} s"}
+
+
+def run_reference(args, model):
+    threads = os.cpu_count() or 1
+    steps = max(args.steps, 1)
+    from oracle import oracle as O
+    from thrml_rs_b200 import workloads as W
+    om = W.fill_ising(O.Model(np.zeros(model["n"], np.int32)), model)
+    st = O.State(om, threads, 0, threads=threads)
+    st.randomize(1)
+    mom = O.Moments.from_arrays(om, *W.ising_moment_arrays(model))
+    budget_steps = min(steps, 40)
+    for i in range(min(args.warmup, 2)):
+        st.run_blocks(100 + i, 1)
+        mom.observe(st)
+    t0 = time.time()
+    for i in range(budget_steps):
+        st.run_blocks(200 + i, 1)
+        mom.observe(st)
+    dt = time.time() - t0
+    value = model["n"] * threads * budget_steps / dt
+    sample = f"each step = one sweep + moment observation of {threads} chains (one per host thread) on the full graph; {budget_steps} steps timed"
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": budget_steps, "warmup": min(args.warmup, 2),
+            "ms_per_step": 1e3 * dt / budget_steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(model, threads, args.gpus),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def workload_config(model, chains, gpus):
+    return {"workload": "sparse random 8-regular Ising graph, greedy-coloured blocks, <s_i> and <s_i s_j> accumulated every sweep",
+            "nodes": int(model["n"]), "edges": int(len(model["edges"])), "blocks": len(model["blocks"]), "chains_per_gpu": int(chains),
+            "global_chains": int(chains * gpus), "state_format": "int8 (one byte per spin and chain, chains innermost)",
+            "parallelism": f"chains sharded over {gpus} GPU(s), one allreduce of the moment sums", "l2": "inputs larger than L2 (state is nodes x chains bytes)"}
+
+
+def main():
+    args = parse()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    import __graft_entry__ as graft
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        T = graft.load_package()
+        from thrml_rs_b200 import workloads as W
+        model = W.sparse_ising(args.nodes, DEGREE, SEED)
+        print(json.dumps(run_reference(args, model)), flush=True)
+        return
+
+    import torch
+    T = graft.load_package()
+    from thrml_rs_b200 import workloads as W
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    model = W.sparse_ising(args.nodes, DEGREE, SEED)
+    n, chains = model["n"], args.chains
+    ctx = T.default_context(local_rank)
+    builder = W.fill_ising(T.Builder(np.zeros(n, np.int32)), model)
+    program = T.Program(builder, ctx)
+    n_blocks = len(model["blocks"])
+    state = T.ChainState(program, chains, chain_offset=rank * chains)
+    moments = T.Moments.from_arrays(program, *W.ising_moment_arrays(model))
+    biases = np.concatenate([model["b"][blk] for blk in model["blocks"]])
+    state.hinton_init(list(range(n_blocks)), biases, model["beta"], SEED)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def step(i):
+        state.sample_with_observation(1000 + i, 1, 1, 1, moments=moments)  # one sweep, then observe
+
+    def barrier():
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t_wall0 = time.time()
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(100 + i)
+    if dist:  # the single allreduce of the moment sums, ordered after the sweeps on the engine's stream
+        with torch.cuda.stream(stream):
+            dist.all_reduce(moment_tensor(torch, moments))
+    ev1.record(stream)
+    barrier()
+    t_wall1 = time.time()
+    ms = ev0.elapsed_time(ev1)
+    if dist:
+        t = torch.tensor([ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    # dominant kernel alone: sweeps without the observer, timed with events on the launching stream
+    sweep_iters = max(5, min(args.steps, 20))
+    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev2.record(stream)
+    state.run_blocks(7, sweep_iters)
+    ev3.record(stream)
+    barrier()
+    sweep_ms = ev2.elapsed_time(ev3) / sweep_iters
+
+    updates_per_step = float(n) * chains
+    value = updates_per_step * world * args.steps / (ms * 1e-3)
+    result = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+              "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+              "config": workload_config(model, chains, world), "clocks": clocks,
+              "gpu_launches": args.steps * (n_blocks + 1)}
+
+    # roofline of the block-update kernel: 9 bytes per site update (8 neighbour bytes read, 1 written) + parameters
+    peak, peak_src = measured_peak()
+    kinds = [program.block_kernel(b) for b in range(n_blocks)]
+    param_bytes = n * (8 * 4 + 256 * 4) if all(k == 1 for k in kinds) else n * 80
+    algo_bytes = updates_per_step * (DEGREE + 1) + param_bytes
+    achieved = algo_bytes / (sweep_ms * 1e-3) / 1e9
+    result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                          "kernel": "k_spin_lut" if all(k == 1 for k in kinds) else "k_spin_generic", "launches_per_sweep": n_blocks, "sweep_ms": sweep_ms,
+                          "bytes_per_update": algo_bytes / updates_per_step}
+
+    if not args.no_e2e:
+        del state, moments
+        e2e = end_to_end(T, torch, program, model, chains, rank, ctx, args, dist)
+        result["e2e"] = e2e
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline(model, os.cpu_count() or 1)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(result), flush=True)
+
+
+def moment_tensor(torch, moments):
+    """The library's int64 moment accumulators viewed as a torch tensor (no copy), for the NCCL allreduce."""
+    ptr, cnt = moments.device_buffer()
+
+    class _View:
+        __cuda_array_interface__ = {"shape": (cnt,), "typestr": "<i8", "data": (ptr, False), "version": 3}
+
+    return torch.as_tensor(_View(), device="cuda")
+
+
+def end_to_end(T, torch, program, model, chains, rank, ctx, args, dist):
+    """estimate-moments through the public engine calls with host buffers: upload the initial chain state of every block
+    from pinned memory, run `steps` sweeps with the moment observer, (allreduce,) read the sums back."""
+    n_blocks = len(model["blocks"])
+    from thrml_rs_b200 import workloads as W
+    rng = np.random.default_rng(1)
+    host = []
+    for blk in model["blocks"]:
+        t = torch.empty((chains, len(blk)), dtype=torch.uint8, pin_memory=True)
+        t.numpy()[:] = rng.integers(0, 2, (chains, len(blk)), dtype=np.uint8)
+        host.append(t)
+    steps = args.steps
+    h2d = sum(int(t.numel()) for t in host)
+    d2h = (model["n"] + len(model["edges"])) * 8
+    best = None
+    for rep in range(2):
+        state = T.ChainState(program, chains, chain_offset=rank * chains)
+        moments = T.Moments.from_arrays(program, *W.ising_moment_arrays(model))
+        ctx.synchronize()
+        if dist:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for b, t in enumerate(host):
+            state.upload(b, t.numpy())
+        state.sample_with_observation(5, 0, steps + 1, 1, moments=moments)  # observe, then `steps` x (sweep, observe)
+        if dist:
+            dist.all_reduce(moment_tensor(torch, moments))
+            torch.cuda.synchronize()
+        m1, _ = moments.read(0)
+        m2, _ = moments.read(1)
+        ctx.synchronize()
+        dt = time.perf_counter() - t0
+        if dist:
+            t = torch.tensor([dt], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        best = dt if best is None else min(best, dt)
+        del state, moments
+    world = dist.get_world_size() if dist else 1
+    return {"value": float(model["n"]) * chains * world * steps / best, "unit": UNIT, "h2d_bytes_per_step": h2d / steps, "d2h_bytes_per_step": d2h / steps,
+            "seconds": best, "call": "upload initial state (pinned host -> device) + sample_with_observation(moments) + moments.read"}
+
+
+if __name__ == "__main__":
+    main()

@@ -321,6 +321,17 @@ class Moments:
         _chk(lib().orc_moments_create(model.h, C.c_int32(len(spec)), _p(self.rows_per_type, C.c_int64), _p(self.row_ptr, C.c_int64), _p(self.members, C.c_int64),
                                       C.c_int32(int(transform_to_spin)), C.byref(self.h)))
 
+    @classmethod
+    def from_arrays(cls, model, rows_per_type, row_ptr, members, transform_to_spin=True):
+        self = cls.__new__(cls)
+        self.rows_per_type = _i64(rows_per_type)
+        self.row_ptr = _i64(row_ptr)
+        self.members = _i64(members)
+        self.h = C.c_void_p()
+        _chk(lib().orc_moments_create(model.h, C.c_int32(len(self.rows_per_type)), _p(self.rows_per_type, C.c_int64), _p(self.row_ptr, C.c_int64),
+                                      _p(self.members, C.c_int64), C.c_int32(int(transform_to_spin)), C.byref(self.h)))
+        return self
+
     def __del__(self):
         if getattr(self, "h", None):
             lib().orc_moments_destroy(self.h)

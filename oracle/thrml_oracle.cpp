@@ -886,6 +886,8 @@ ORC_API int orc_state_randomize(OState* s, uint64_t key) {
 struct OMoments {  // MomentAccumulatorObserver, moment.rs:29-121
     Model* m;
     std::vector<int64_t> rows_per_type, row_ptr, members;
+    std::vector<int32_t> mem_sd;
+    std::vector<int64_t> mem_pos;
     bool spin_transform;
     std::vector<int64_t> sums;  // all types concatenated
     int64_t n_obs = 0;
@@ -899,8 +901,12 @@ ORC_API int orc_moments_create(Model* m, int32_t n_types, const int64_t* rows_pe
     for (int t = 0; t < n_types; t++) rows += rows_per_type[t];
     o->row_ptr.assign(row_ptr, row_ptr + rows + 1);
     o->members.assign(members, members + row_ptr[rows]);
-    for (int64_t nd : o->members)
-        if (!m->loc.count(nd)) { delete o; return fail("Node not found in global location map"); }
+    for (int64_t nd : o->members) {
+        auto it = m->loc.find(nd);
+        if (it == m->loc.end()) { delete o; return fail("Node not found in global location map"); }
+        o->mem_sd.push_back(it->second.first);
+        o->mem_pos.push_back(it->second.second);
+    }
     o->spin_transform = transform_to_spin != 0;
     o->sums.assign(rows, 0);
     *out = o;
@@ -909,14 +915,12 @@ ORC_API int orc_moments_create(Model* m, int32_t n_types, const int64_t* rows_pe
 ORC_API void orc_moments_destroy(OMoments* o) { delete o; }
 // observe — moment.rs:157-237: product of f(x) over each row's members, added to the running sums.
 ORC_API int orc_moments_observe(OMoments* o, const OState* s) {
-    const Model* m = o->m;
     size_t rows = o->sums.size();
     for (int64_t c = 0; c < s->n_chains; c++)
         for (size_t r = 0; r < rows; r++) {
             float prod = 1.0f;
             for (int64_t q = o->row_ptr[r]; q < o->row_ptr[r + 1]; q++) {
-                auto lc = m->loc.at(o->members[q]);
-                float x = s->g[c][lc.first][lc.second];
+                float x = s->g[c][o->mem_sd[q]][o->mem_pos[q]];
                 prod *= o->spin_transform ? x * 2.0f - 1.0f : x;
             }
             o->sums[r] += (int64_t)prod;

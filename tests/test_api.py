@@ -1,0 +1,152 @@
+"""The host-side mirror of the reference API: constructor validation with the reference's error strings (CPU), and the
+reference's own smoke tests re-run through the CUDA path (GPU)."""
+import numpy as np
+import pytest
+
+
+def spins(T, n):
+    return [T.Node(T.NodeType.Spin()) for _ in range(n)]
+
+
+def test_block_validation(T):
+    # crates/thrml-core/tests/test_block.rs:11-153
+    with pytest.raises(T.ThrmlError, match="empty"):
+        T.Block([])
+    with pytest.raises(T.ThrmlError, match="same type"):
+        T.Block([T.Node(T.NodeType.Spin()), T.Node(T.NodeType.Categorical(3))])
+    a, b = T.Block(spins(T, 2)), T.Block(spins(T, 3))
+    assert len(a + b) == 5
+    with pytest.raises(T.ThrmlError, match="different node types"):
+        a + T.Block([T.Node(T.NodeType.Categorical(3))])
+    with pytest.raises(T.ThrmlError, match="twice"):
+        T.BlockSpec([a, a], [T.NodeType.Spin()])
+    with pytest.raises(T.ThrmlError, match="not found"):
+        T.BlockSpec([a], [T.NodeType.Categorical(2)])
+    n1, n2 = T.Node(T.NodeType.Spin()), T.Node(T.NodeType.Spin())
+    assert n1 != n2 and n1.id != n2.id and n1 == n1
+
+
+def test_interaction_group_validation(T):
+    # crates/thrml-core/tests/test_interaction.rs:17-121
+    head = T.Block(spins(T, 3))
+    with pytest.raises(T.ThrmlError, match="tail node blocks"):
+        T.InteractionGroup(np.zeros((3, 1, 1)), head, [T.Block(spins(T, 2))], 1)
+    with pytest.raises(T.ThrmlError, match="leading dimension"):
+        T.InteractionGroup(np.zeros((4, 1, 1)), head, [T.Block(spins(T, 3))], 1)
+    with pytest.raises(T.ThrmlError, match="n_spin"):
+        T.InteractionGroup(np.zeros((3, 1, 1)), head, [T.Block(spins(T, 3))], 2)
+
+
+def test_factor_validation(T):
+    # crates/thrml-models/tests/test_factor.rs:10-49, test_discrete_ebm.rs:20-184
+    g3, g2 = T.Block(spins(T, 3)), T.Block(spins(T, 2))
+    with pytest.raises(T.ThrmlError, match="same number"):
+        T.SpinEBMFactor([g3, g2], np.zeros((3, 1, 1)))
+    with pytest.raises(T.ThrmlError, match="leading dimension"):
+        T.SpinEBMFactor([g3], np.zeros((4, 1, 1)))
+    with pytest.raises(T.ThrmlError, match="At least one"):
+        T.DiscreteEBMFactor([], [], np.zeros((1, 1, 1)))
+    cat = T.Block([T.Node(T.NodeType.Categorical(4)) for _ in range(3)])
+    with pytest.raises(T.ThrmlError, match="shape of the weight tensor"):
+        T.CategoricalEBMFactor([cat, cat], np.zeros((3, 4, 1)))
+
+
+def test_program_validation(T):
+    # crates/thrml-samplers/tests/test_program.rs:65-138: sampler count must match the free blocks
+    blocks = [T.Block(spins(T, 3)), T.Block(spins(T, 3))]
+    spec = T.BlockGibbsSpec([[blocks[0]], [blocks[1]]], [], [T.NodeType.Spin()])
+    assert spec.sampling_order == [[0], [1]] and len(spec.free_blocks) == 2
+    with pytest.raises(T.ThrmlError, match="Number of samplers"):
+        T.BlockSamplingProgram(spec, [T.SpinGibbsConditional()], [])
+    spec2 = T.BlockGibbsSpec([[blocks[0], blocks[1]]], [], [T.NodeType.Spin()])
+    assert spec2.sampling_order == [[0, 1]]
+
+
+def test_rng_key_and_schedule(T):
+    # crates/thrml-samplers/src/rng.rs:52-86
+    keys = T.RngKey.new(42).split(5)
+    assert len({k.seed() for k in keys}) == 5
+    assert T.RngKey(42).split(10) == T.RngKey(42).split(10)
+    assert T.RngKey(9).split(1) == [T.RngKey(9)] and T.RngKey(9).split(0) == []
+    a, b = T.RngKey(1).split_two()
+    assert a != b
+    s = T.SamplingSchedule.new(10, 5, 2)
+    assert (s.n_warmup, s.n_samples, s.steps_per_sample) == (10, 5, 2)
+
+
+def chain_model(T, n=5):
+    nodes = spins(T, n)
+    edges = [(nodes[i], nodes[i + 1]) for i in range(n - 1)]
+    ebm = T.IsingEBM(nodes, edges, np.linspace(-0.2, 0.2, n), np.full(n - 1, 0.5), 1.0)
+    even, odd = T.Block(nodes[0::2]), T.Block(nodes[1::2])
+    return nodes, edges, ebm, even, odd
+
+
+@pytest.mark.gpu
+def test_run_blocks_shapes(T):
+    # crates/thrml-samplers/tests/test_program.rs:141-186: 5 sweeps, shapes preserved
+    nodes, edges, ebm, even, odd = chain_model(T)
+    prog = T.IsingSamplingProgram(ebm, [even, odd], []).program
+    init = [np.zeros(3, np.float32), np.ones(2, np.float32)]
+    out = T.run_blocks(T.RngKey(0), prog, init, [], 5)
+    assert [o.shape for o in out] == [(3,), (2,)] and all(set(np.unique(o)) <= {0.0, 1.0} for o in out)
+    assert T.run_blocks(T.RngKey(0), prog, init, [], 0)[0] is init[0]
+    state = [a.copy() for a in init]
+    T.sample_blocks(T.RngKey(1), state, [], prog)
+    assert [s.shape for s in state] == [(3,), (2,)]
+
+
+@pytest.mark.gpu
+def test_sample_states_and_moments_api(T, O):
+    nodes, edges, ebm, even, odd = chain_model(T)
+    prog = T.IsingSamplingProgram(ebm, [even, odd], []).program
+    sched = T.SamplingSchedule(3, 6, 2)
+    init = [np.zeros((4, 3), np.float32), np.ones((4, 2), np.float32)]
+    samples = T.sample_states(T.RngKey(5), prog, sched, init, [], [odd, even])
+    assert [s.shape for s in samples] == [(6, 4, 2), (6, 4, 3)]
+    single = T.sample_states(T.RngKey(5), prog, sched, [a[0] for a in init], [], [even])
+    assert single[0].shape == (6, 3) and np.array_equal(single[0], samples[1][:, 0, :])
+    m1, m2 = T.estimate_moments(T.RngKey(5), nodes, edges, prog, sched, init, [])
+    assert m1.shape == (5,) and m2.shape == (4,)
+    # the same schedule through the state observer gives the same averages
+    full = np.zeros((6, 4, 5))
+    full[:, :, 0::2] = samples[1]
+    full[:, :, 1::2] = samples[0]
+    sp = 2 * full - 1
+    assert np.allclose(m1, sp.mean(axis=(0, 1)), atol=1e-6)
+    assert np.allclose(m2, (sp[:, :, :-1] * sp[:, :, 1:]).mean(axis=(0, 1)), atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_clamped_blocks_and_hinton_api(T):
+    nodes, edges, ebm, even, odd = chain_model(T)
+    prog = T.IsingSamplingProgram(ebm, [even], [odd]).program
+    clamp = [np.array([1, 0], np.float32)]
+    out = T.run_blocks(T.RngKey(3), prog, [np.zeros(3, np.float32)], clamp, 4)
+    assert out[0].shape == (3,)
+    # crates/thrml-models/tests/test_ising.rs:57-98: bias 10 -> at least 7 of 10 ones
+    big = spins(T, 10)
+    ebm2 = T.IsingEBM(big, [], np.full(10, 10.0), np.zeros(0), 1.0)
+    init = T.hinton_init(T.RngKey(0), ebm2, [T.Block(big)], [1])
+    assert init[0].shape == (1, 10) and init[0].sum() >= 7
+    init = T.hinton_init(T.RngKey(0), ebm2, [T.Block(big[:4]), T.Block(big[4:])], [2, 3])
+    assert [a.shape for a in init] == [(6, 4), (6, 6)]
+
+
+@pytest.mark.gpu
+def test_potts_factor_program_api(T):
+    # crates/thrml-examples/examples/categorical_sampling.rs:108-124: W = beta*I favours equal neighbours
+    K, n = 3, 6
+    nodes = [T.Node(T.NodeType.Categorical(K)) for _ in range(n)]
+    u, v = T.Block(nodes[:-1]), T.Block(nodes[1:])
+    w = np.broadcast_to(3.0 * np.eye(K, dtype=np.float32), (n - 1, K, K)).copy()
+    factor = T.CategoricalEBMFactor([u, v], w)
+    even, odd = T.Block(nodes[0::2]), T.Block(nodes[1::2])
+    spec = T.BlockGibbsSpec([[even], [odd]], [], [T.NodeType.Categorical(K)])
+    prog = T.FactorSamplingProgram(spec, [T.CategoricalGibbsConditional(K), T.CategoricalGibbsConditional(K)], [factor]).program
+    init = [np.zeros((256, 3), np.float32), np.zeros((256, 3), np.float32)]
+    out = T.run_blocks(T.RngKey(2), prog, init, [], 30)
+    full = np.zeros((256, n))
+    full[:, 0::2], full[:, 1::2] = out[0], out[1]
+    agree = (full[:, :-1] == full[:, 1:]).mean()
+    assert agree > 0.8  # exact: e^3/(e^3+2) = 0.909 per bond

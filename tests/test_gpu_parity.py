@@ -1,0 +1,248 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle on the same seeded inputs.
+
+Bars: index work bit-exact; local fields within 1e-5 relative of the oracle's f64 field (and bit-identical to its f32
+field); sampled states bit-exact both with injected noise and with the in-kernel stream — the engine's exp/log are
+fixed IEEE sequences, so no |logit - threshold| < 1e-6 escape is needed and none is taken; moment sums exact.
+"""
+import numpy as np
+import pytest
+
+import models as M
+
+pytestmark = pytest.mark.gpu
+
+
+def make_pair(T, O, desc, chains, seed, chain_offset=0):
+    gb, ob = M.build_both(T, O, desc)
+    prog = T.Program(gb)
+    gs = T.ChainState(prog, chains, chain_offset)
+    os_ = O.State(ob, chains, chain_offset)
+    init = M.random_states(desc, chains, seed)
+    for i, a in enumerate(init):
+        gs.upload(i, a)
+        os_.set_block(i, a.astype(np.float32))
+    return prog, gs, os_, gb, ob
+
+
+def assert_states_equal(gs, os_, n_blocks):
+    for i in range(n_blocks):
+        g = gs.download(i)
+        o = os_.get_block(i)
+        assert np.array_equal(g, o), f"block {i}: {(g != o).sum()} of {g.size} states differ"
+
+
+def n_blocks_of(desc):
+    return len(desc["free"]) + len(desc.get("clamped", []))
+
+
+def model_cases(T):
+    return {
+        "lattice": M.ising_lattice(T, 8, True, 1)[0],
+        "graph8": M.ising_random_graph(T, 300, 8, 2)[0],
+        "graph12": M.ising_random_graph(T, 200, 12, 3)[0],
+        "mixed": M.mixed_model(4)[0],
+        "mixed_free": M.mixed_model(5, with_clamped=False)[0],
+        "mixed_superblock": M.mixed_model(6, superblock_pair=True)[0],
+        "potts": M.potts_lattice(T, 6, 5, 7)[0],
+    }
+
+
+CASES = ["lattice", "graph8", "graph12", "mixed", "mixed_free", "mixed_superblock", "potts"]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("chains", [1, 37, 64])
+def test_fields(T, O, case, chains):
+    desc = model_cases(T)[case]
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 11)
+    for blk in range(len(desc["free"])):
+        g = gs.fields(blk)
+        o64, o32 = os_.fields(blk)
+        assert np.array_equal(g, o32.reshape(g.shape)), f"block {blk}: f32 fields differ"
+        scale = np.maximum(np.abs(o64), 1e-3)
+        assert np.max(np.abs(g - o64.reshape(g.shape)) / scale.reshape(g.shape)) < 1e-5  # north-star tolerance: 1e-5 relative
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_noise_injection_states(T, O, case):
+    desc = model_cases(T)[case]
+    chains, sweeps = 24, 3
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 12)
+    per_sweep = sum(len(nodes) * max(int(desc["kinds"][nodes[0]]), 1) for nodes, _ in desc["free"]) * chains
+    u = np.random.default_rng(5).random(per_sweep * sweeps, dtype=np.float32)
+    u = np.clip(u, 1e-7, 1 - 1e-7).astype(np.float32)
+    gs.run_blocks(99, sweeps, inj=u)
+    os_.run_blocks(99, sweeps, inj=u)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    # one more sweep through sample_blocks
+    u1 = u[:per_sweep]
+    gs.sample_blocks(7, inj=u1)
+    os_.sample_blocks(7, inj=u1)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("chains", [5, 64, 272])
+def test_in_kernel_stream_states(T, O, case, chains):
+    desc = model_cases(T)[case]
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 13)
+    gs.run_blocks(1234, 4)
+    os_.run_blocks(1234, 4)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+
+
+def test_kernel_selection(T, O):
+    cases = model_cases(T)
+    prog = T.Program(M.fill(T.Builder(cases["graph8"]["kinds"]), cases["graph8"]))
+    assert all(prog.block_kernel(b) == 1 for b in range(len(cases["graph8"]["free"])))
+    prog = T.Program(M.fill(T.Builder(cases["graph12"]["kinds"]), cases["graph12"]))
+    assert any(prog.block_kernel(b) == 0 for b in range(len(cases["graph12"]["free"])))
+    prog = T.Program(M.fill(T.Builder(cases["potts"]["kinds"]), cases["potts"]))
+    assert all(prog.block_kernel(b) == 2 for b in range(2))
+
+
+def test_chain_sharding_is_invisible(T, O):
+    """Two states holding chains [0,32) and [32,64) reproduce one state holding [0,64)."""
+    desc = model_cases(T)["graph8"]
+    gb = M.fill(T.Builder(desc["kinds"]), desc)
+    prog = T.Program(gb)
+    init = M.random_states(desc, 64, 3)
+    full = T.ChainState(prog, 64, 0)
+    lo, hi = T.ChainState(prog, 32, 0), T.ChainState(prog, 32, 32)
+    for i, a in enumerate(init):
+        full.upload(i, a)
+        lo.upload(i, a[:32])
+        hi.upload(i, a[32:])
+    for s in (full, lo, hi):
+        s.run_blocks(77, 5)
+    for i in range(len(init)):
+        f = full.download(i)
+        assert np.array_equal(f[:32], lo.download(i)) and np.array_equal(f[32:], hi.download(i))
+
+
+def test_hinton_init(T, O):
+    desc, info = M.ising_lattice(T, 8, True, 21, bias_sigma=1.0, beta=0.7)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 40, 14)
+    biases = np.concatenate([info["b"][blk] for blk in info["blocks"]])
+    gs.hinton_init([0, 1], biases, 0.7, 5)
+    os_.hinton_init([0, 1], biases, 0.7, 5)
+    assert_states_equal(gs, os_, 2)
+    u = np.random.default_rng(1).random(40 * 64, dtype=np.float32)
+    gs.hinton_init([1, 0], np.concatenate([info["b"][info["blocks"][1]], info["b"][info["blocks"][0]]]), 0.7, 5, inj_u=u)
+    os_.hinton_init([1, 0], np.concatenate([info["b"][info["blocks"][1]], info["b"][info["blocks"][0]]]), 0.7, 5, inj_u=u)
+    assert_states_equal(gs, os_, 2)
+    # crates/thrml-models/tests/test_ising.rs:57-98: bias 10 -> (almost) all ones
+    gs.hinton_init([0], np.full(32, 10.0, np.float32), 1.0, 9)
+    assert gs.download(0).mean() > 0.99
+    gs.randomize(3)
+    os_.randomize(3)
+    assert_states_equal(gs, os_, 2)
+
+
+def moment_spec(desc, info):
+    nodes = list(range(info["n"]))
+    return [[(i,) for i in nodes], [tuple(e) for e in info["edges"]]]
+
+
+@pytest.mark.parametrize("chains", [1, 33])
+def test_moments_and_schedule(T, O, chains):
+    desc, info = M.ising_random_graph(T, 120, 6, 31)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 15)
+    spec = moment_spec(desc, info)
+    gm = T.Moments(prog, spec, True)
+    om = O.Moments(ob, spec, True)
+    gs.sample_with_observation(2024, 3, 5, 2, moments=gm)
+    os_.sample_with_observation(2024, 3, 5, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(2):
+        a, na = gm.read(t)
+        b, nb = om.read(t)
+        assert na == nb == 5 * chains
+        assert np.array_equal(a, b)
+    # raw products (no spin transform) and a three-node row
+    spec2 = [[(0, 1, 2), (5,), (7, 9)]]
+    gm2, om2 = T.Moments(prog, spec2, False), O.Moments(ob, spec2, False)
+    gm2.observe(gs)
+    om2.observe(os_)
+    assert np.array_equal(gm2.read(0)[0], om2.read(0)[0])
+    gm.reset()
+    assert gm.read(0)[0].sum() == 0 and gm.read(0)[1] == 0
+
+
+def test_state_observer_schedule(T, O):
+    desc = model_cases(T)["mixed"]
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 9, 16)
+    for sched in [(2, 4, 3), (0, 1, 5), (4, 0, 1), (0, 3, 0)]:
+        g = gs.sample_with_observation(31, *sched, obs_blocks=[2, 0, 3])
+        o = os_.sample_with_observation(31, *sched, obs_blocks=[2, 0, 3])
+        assert g.shape == o.shape and np.array_equal(g, o)
+        assert_states_equal(gs, os_, n_blocks_of(desc))
+
+
+def test_marginals(T, O):
+    desc, info = M.potts_lattice(T, 6, 5, 41)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 50, 17)
+    mg = T.Moments.marginals(prog, [0, 1], 5)
+    want = np.zeros((36, 5), dtype=np.int64)
+    for _ in range(3):
+        gs.run_blocks(8, 1)
+        os_.run_blocks(8, 1)
+        mg.observe(gs)
+        st = np.concatenate([os_.get_block(0), os_.get_block(1)], axis=1).astype(np.int64)  # [chains, node]
+        for c in range(5):
+            want[:, c] += (st == c).sum(axis=0)
+    got, n_obs = mg.read(0)
+    assert n_obs == 150 and np.array_equal(got.reshape(36, 5), want)
+
+
+def test_update_weights_reaches_the_kernels(T, O):
+    desc, info = M.ising_random_graph(T, 150, 8, 51)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 32, 18)
+    J2 = (info["J"] * -1.5).astype(np.float32)
+    desc2 = dict(desc, ops=[("add_ising", np.arange(info["n"]), info["b"], info["edges"], J2, info["beta"])])
+    gb2, ob2 = M.build_both(T, O, desc2)
+    for blk in range(len(desc["free"])):
+        prog.update_weights(blk, 1, gb2.tables(blk)[1]["w"].ravel())
+    os2 = O.State(ob2, 32)
+    for i in range(n_blocks_of(desc)):
+        os2.set_block(i, os_.get_block(i))
+    gs.run_blocks(5, 3)
+    os2.run_blocks(5, 3)
+    assert_states_equal(gs, os2, n_blocks_of(desc))
+
+
+def test_boltzmann_moments_within_4_sigma(T):
+    """Exhaustive enumeration of a 3x4 open lattice vs long-run GPU moments: 4 sigma of the Monte-Carlo standard error
+    (independent chains, so the error of a chain-average is the across-chain standard deviation / sqrt(chains))."""
+    rng = np.random.default_rng(3)
+    rows, cols = 3, 4
+    n = rows * cols
+    edges = np.array([(r * cols + c, r * cols + c + 1) for r in range(rows) for c in range(cols - 1)] + [(r * cols + c, (r + 1) * cols + c) for r in range(rows - 1) for c in range(cols)])
+    b = rng.normal(0, 0.3, n).astype(np.float32)
+    J = rng.normal(0, 0.5, len(edges)).astype(np.float32)
+    colour = np.array([(i // cols + i % cols) % 2 for i in range(n)])
+    bld = T.Builder(np.zeros(n, np.int32))
+    for c in (0, 1):
+        bld.add_free_block(np.flatnonzero(colour == c))
+    bld.add_ising(np.arange(n), b, edges, J, 1.0)
+    bld.compile()
+    prog = T.Program(bld)
+    s = np.array([[1 if (cfg >> i) & 1 else -1 for i in range(n)] for cfg in range(1 << n)], dtype=np.float64)
+    energy = -(s @ b.astype(np.float64) + ((s[:, edges[:, 0]] * s[:, edges[:, 1]]) @ J.astype(np.float64)))
+    p = np.exp(-(energy - energy.min()))
+    p /= p.sum()
+    exact1 = p @ s
+    exact2 = p @ (s[:, edges[:, 0]] * s[:, edges[:, 1]])
+    chains, samples = 2048, 200
+    st = T.ChainState(prog, chains)
+    st.randomize(1)
+    obs = st.sample_with_observation(17, 100, samples, 2, obs_blocks=[0, 1])  # [samples, node, chain]
+    order = np.concatenate([np.flatnonzero(colour == 0), np.flatnonzero(colour == 1)])
+    spins = np.zeros((samples, n, chains))
+    spins[:, order, :] = 2.0 * obs - 1.0
+    per_chain1 = spins.mean(axis=0)  # [node, chain]
+    per_chain2 = (spins[:, edges[:, 0], :] * spins[:, edges[:, 1], :]).mean(axis=0)
+    for est, exact in ((per_chain1, exact1), (per_chain2, exact2)):
+        mean = est.mean(axis=1)
+        sem = est.std(axis=1, ddof=1) / np.sqrt(chains)
+        assert np.all(np.abs(mean - exact) < 4 * sem + 1e-9), np.max(np.abs(mean - exact) / sem)

@@ -1,0 +1,46 @@
+"""Seeded synthetic inputs for the benchmark configurations (the reference ships no datasets for this path)."""
+import numpy as np
+
+from . import engine as _eng
+
+
+def random_regular_edges(n_nodes, degree, seed):
+    """Configuration model: `degree` stubs per node, seeded Fisher-Yates shuffle of the stub list, consecutive stubs
+    paired, self-loops and duplicate edges erased.  Edges come back sorted by (min, max)."""
+    rng = np.random.default_rng(seed)
+    stubs = np.repeat(np.arange(n_nodes, dtype=np.int64), degree)
+    rng.shuffle(stubs)
+    a, b = stubs[0::2], stubs[1::2]
+    lo, hi = np.minimum(a, b), np.maximum(a, b)
+    code = np.unique(lo[lo != hi] * n_nodes + hi[lo != hi])
+    return np.stack([code // n_nodes, code % n_nodes], axis=1)
+
+
+def sparse_ising(n_nodes=1 << 20, degree=8, seed=0x5EED0002, bias_sigma=0.05, beta=1.0):
+    """Sparse random `degree`-regular Ising model: couplings N(0, 1/degree), biases N(0, bias_sigma^2), blocks from
+    greedy colouring in node order (ascending node index inside each colour)."""
+    edges = random_regular_edges(n_nodes, degree, seed)
+    rng = np.random.default_rng(seed + 1)
+    J = rng.normal(0.0, np.sqrt(1.0 / degree), len(edges)).astype(np.float32)
+    b = rng.normal(0.0, bias_sigma, n_nodes).astype(np.float32)
+    colour, n_colours = _eng.greedy_coloring_arrays(n_nodes, edges)
+    blocks = [np.flatnonzero(colour == c).astype(np.int64) for c in range(n_colours)]
+    return dict(n=n_nodes, edges=edges, J=J, b=b, beta=float(beta), colour=colour, blocks=blocks)
+
+
+def fill_ising(builder, model):
+    """Feed a sparse_ising() model to a builder (the library's or any object with the same methods)."""
+    for i, blk in enumerate(model["blocks"]):
+        builder.add_free_block(blk, superblock=i)
+    builder.add_ising(np.arange(model["n"], dtype=np.int64), model["b"], model["edges"], model["J"], model["beta"])
+    builder.compile()
+    return builder
+
+
+def ising_moment_arrays(model):
+    """CSR form of MomentAccumulatorObserver::ising_moment_spec(all nodes, all edges)."""
+    n, e = model["n"], len(model["edges"])
+    rows_per_type = np.array([n, e], dtype=np.int64)
+    row_ptr = np.concatenate([np.arange(n + 1, dtype=np.int64), n + 2 * np.arange(1, e + 1, dtype=np.int64)])
+    members = np.concatenate([np.arange(n, dtype=np.int64), model["edges"].astype(np.int64).ravel()])
+    return rows_per_type, row_ptr, members
