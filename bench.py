@@ -200,8 +200,9 @@ def main():
     for i in range(args.steps):
         step(100 + i)
     if dist:  # the single allreduce of the moment sums, ordered after the sweeps on the engine's stream
+        from thrml_rs_b200 import sharding
         with torch.cuda.stream(stream):
-            dist.all_reduce(moment_tensor(torch, moments))
+            sharding.allreduce_sums(moment_tensor(torch, moments), dist)
     ev1.record(stream)
     barrier()
     t_wall1 = time.time()

@@ -59,8 +59,14 @@ def test_fields(T, O, case, chains):
         g = gs.fields(blk)
         o64, o32 = os_.fields(blk)
         assert np.array_equal(g, o32.reshape(g.shape)), f"block {blk}: f32 fields differ"
-        scale = np.maximum(np.abs(o64), 1e-3)
-        assert np.max(np.abs(g - o64.reshape(g.shape)) / scale.reshape(g.shape)) < 1e-5  # north-star tolerance: 1e-5 relative
+        # against the f64 field: 1e-5 relative (the north-star tolerance) wherever the sum does not cancel, and 1e-6 of the
+        # summed term magnitudes everywhere (an f32 sum of a dozen terms cannot do better where they cancel)
+        terms = sum(np.abs(t["w"]).max(axis=2).__mul__(t["active"]).sum(axis=1) for t in gb.tables(blk))  # [n]
+        terms = terms.reshape((1, -1) + (1,) * (g.ndim - 2))
+        err = np.abs(g - o64.reshape(g.shape))
+        assert np.all(err <= 1e-6 * terms + 1e-30)
+        solid = np.abs(o64.reshape(g.shape)) >= 0.01 * terms
+        assert np.all(err[solid] <= 1e-5 * np.abs(o64.reshape(g.shape))[solid])
 
 
 @pytest.mark.parametrize("case", CASES)
@@ -167,6 +173,29 @@ def test_moments_and_schedule(T, O, chains):
     assert np.array_equal(gm2.read(0)[0], om2.read(0)[0])
     gm.reset()
     assert gm.read(0)[0].sum() == 0 and gm.read(0)[1] == 0
+
+
+def test_fused_moments_with_leftover_rows(T, O):
+    """Rows the update kernels accumulate themselves (single spins, neighbour pairs) mixed with rows they cannot:
+    clamped nodes, pairs of clamped nodes, non-neighbours, a triple, repeated rows."""
+    desc, info = M.ising_random_graph(T, 160, 8, 61)
+    # turn the last block into a clamped block
+    clamp_nodes = desc["free"][-1][0]
+    desc = dict(desc, free=desc["free"][:-1], clamped=[clamp_nodes])
+    edges = [tuple(e) for e in info["edges"]]
+    spec = [[(i,) for i in range(info["n"])] + [(3,), (3,)],
+            edges + edges[:5] + [(0, 1), (int(clamp_nodes[0]), int(clamp_nodes[-1])), (7, 7)],
+            [(0, 5, 9), (2,), edges[0]]]
+    for chains, sched in [(33, (2, 4, 3)), (16, (0, 3, 1)), (5, (1, 1, 1))]:
+        prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 19)
+        gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+        gs.sample_with_observation(77, *sched, moments=gm)
+        os_.sample_with_observation(77, *sched, moments=om)
+        assert_states_equal(gs, os_, n_blocks_of(desc))
+        for t in range(3):
+            a, na = gm.read(t)
+            b, nb = om.read(t)
+            assert na == nb and np.array_equal(a, b), (chains, sched, t, int((a != b).sum()))
 
 
 def test_state_observer_schedule(T, O):

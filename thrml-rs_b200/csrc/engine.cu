@@ -71,10 +71,13 @@ struct BlockProg {
     DevBuf d_tabs;   // DevTable[n_tabs]
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
+    std::vector<int32_t> h_nbr;  // host copy of d_nbr
+    int32_t order = -1;          // position of the block's superblock in the sweep; -1 for clamped blocks
 };
 
 struct thrml_program {
     thrml_ctx* ctx = nullptr;
+    int device = 0;
     int32_t n_free = 0, n_clamped = 0, n_classes = 0, sd_spin = -1, sd_cat = -1;
     std::vector<int64_t> class_size;
     std::vector<BlockProg> blocks;  // free ++ clamped
@@ -87,6 +90,7 @@ struct thrml_program {
 
 struct thrml_state {
     thrml_program* prog = nullptr;
+    int device = 0;
     int64_t n_chains = 0, chain_offset = 0, ld = 0;
     DevBuf cls[2];      // state rows per class
     DevBuf stage;       // staging rows for superblocks that cannot be updated in place
@@ -94,8 +98,19 @@ struct thrml_state {
     uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
 };
 
+struct FusedMaps {
+    DevBuf m1;  // int32 [n]: row of <s_i>, -1 when not accumulated by the block's update kernel
+    DevBuf m2;  // int32 [n][8]: row of <s_i s_j> per neighbour slot, -1 when not owned by this node
+};
+
 struct thrml_moments {
     thrml_program* prog = nullptr;
+    int device = 0;
+    // rows the threshold-table kernels accumulate while they update (per free block), and the rest
+    std::vector<std::unique_ptr<FusedMaps>> fused;
+    bool any_fused = false;
+    int64_t n_left = 0;
+    DevBuf d_left_ptr, d_left_sd, d_left_pos, d_left_rows;
     int32_t mode = 0;  // 0 products over tuples, 1 per-node category counts
     int32_t spin_transform = 1;
     std::vector<int64_t> rows_per_type;
@@ -310,11 +325,28 @@ struct LutArgs {
     int32_t n_chunks;      // ld / 16
     uint32_t chain_word0;
     uint32_t k0, k1;
+    // fused moment observer (ACC only): row of <s_i> per node, row of <s_i s_j> per (node, slot), -1 = not owned here
+    int64_t n_chains;
+    const int32_t* m1_row;
+    const int32_t* m2_row;
+    long long* sums;
 };
+
+// Bytes 0x01 for the chains of word q of chunk ch that exist (chain index < n_chains).
+__device__ __forceinline__ uint32_t valid_bytes(int64_t n_chains, int ch, int q) {
+    const int64_t left = n_chains - (16 * static_cast<int64_t>(ch) + 4 * q);
+    if (left >= 4) return 0x01010101u;
+    if (left <= 0) return 0u;
+    return 0x01010101u >> (8 * (4 - static_cast<int>(left)));
+}
 
 // Threshold-table spin update: one warp per node, each lane 16 chains per pass.  The neighbour configuration of four
 // chains is assembled with shifts inside one 32-bit word (state bytes are 0/1), then one shared-memory lookup and one
 // compare per chain replace the field accumulation and the sigmoid.
+// ACC: the moment observer fused into the update (moment.rs:205-233 for first moments and pair products): the warp
+// that updates node i is the only one that touches i's rows, so the sums are updated without atomics.  A pair row is
+// owned by the endpoint updated later in the sweep, when both values are final.
+template <bool ACC>
 __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
     __shared__ uint32_t s_lut[8][LUT_SIZE];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
@@ -326,10 +358,21 @@ __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
         reinterpret_cast<uint4*>(my)[lane] = __ldg(src + lane);
         reinterpret_cast<uint4*>(my)[lane + 32] = __ldg(src + lane + 32);
         int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
+        int32_t my_row = -1;
+        uint32_t own = 0;
+        if (ACC) {
+            if (lane < LUT_BITS) my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * LUT_BITS + lane);
+            else if (lane == LUT_BITS) my_row = __ldg(a.m1_row + node);
+            own = __ballot_sync(0xffffffffu, my_row >= 0);
+        }
         __syncwarp();
         int32_t nbj[LUT_BITS];
 #pragma unroll
         for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
+        uint32_t dis[LUT_BITS];
+        uint32_t ones = 0;
+#pragma unroll
+        for (int j = 0; j < LUT_BITS; ++j) dis[j] = 0;
         uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
         for (int ch = lane; ch < a.n_chunks; ch += 32) {
             uint4 v[LUT_BITS];
@@ -358,6 +401,29 @@ __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
                 o[q] = w;
             }
             reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+            if (ACC && own) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t vm = valid_bytes(a.n_chains, ch, q);
+                    ones += __popc(o[q] & vm);
+                    const uint32_t d = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+#pragma unroll
+                    for (int j = 0; j < LUT_BITS; ++j)
+                        if ((own >> j) & 1u) dis[j] += __popc(d & (vm << j));
+                }
+            }
+        }
+        if (ACC && own) {
+            long long val = 0;
+            ones = __reduce_add_sync(0xffffffffu, ones);
+            if (lane == LUT_BITS) val = 2ll * ones - a.n_chains;
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j)
+                if ((own >> j) & 1u) {
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, dis[j]);
+                    if (lane == j) val = a.n_chains - 2ll * t;
+                }
+            if (my_row >= 0) a.sums[my_row] += val;
         }
     }
 }
@@ -429,7 +495,7 @@ __global__ void k_transpose_out(const uint8_t* src, uint8_t* dst, int64_t n, int
 // One warp-row = one moment row; lanes stride over chain words; exact int64 accumulation.
 __global__ void __launch_bounds__(256) k_moments(const int64_t* row_ptr, const int32_t* mem_sd, const int32_t* mem_pos, int64_t n_rows,
                                                  const uint8_t* cls0, const uint8_t* cls1, int64_t ld, int64_t n_chains, int32_t spin_transform,
-                                                 unsigned long long* sums) {
+                                                 unsigned long long* sums, const int64_t* row_ids) {
     const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
     if (row >= n_rows) return;
     const int64_t b = row_ptr[row], e = row_ptr[row + 1];
@@ -450,7 +516,7 @@ __global__ void __launch_bounds__(256) k_moments(const int64_t* row_ptr, const i
             if (4 * quad + c < n_chains) acc += prod[c];
     }
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
-    if (threadIdx.x == 0) atomicAdd(sums + row, static_cast<unsigned long long>(acc));
+    if (threadIdx.x == 0) atomicAdd(sums + (row_ids ? row_ids[row] : row), static_cast<unsigned long long>(acc));
 }
 // Category counts per observed node.
 __global__ void __launch_bounds__(256) k_marginals(const int32_t* node_sd, const int32_t* node_pos, int64_t n_nodes, int32_t K, const uint8_t* cls0,
@@ -502,6 +568,7 @@ int32_t thrml_ctx_create(int32_t device_id, thrml_ctx** out) {
 void thrml_ctx_destroy(thrml_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
     if (ctx->stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
 }
@@ -529,6 +596,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
     CU_TRY(cudaSetDevice(ctx->device));
     auto p = std::make_unique<thrml_program>();
     p->ctx = ctx;
+    p->device = ctx->device;
     p->n_free = static_cast<int32_t>(b->free_blocks.size());
     p->n_clamped = static_cast<int32_t>(b->clamped_blocks.size());
     p->n_classes = b->n_classes;
@@ -600,6 +668,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
             }
             if (lut_ok) {
                 if (int32_t rc = upload(bp.d_nbr, nbr.data(), nbr.size() * 4, ctx->stream)) return rc;
+                bp.h_nbr = nbr;
                 if (int32_t rc = bp.d_lut.alloc(static_cast<size_t>(bp.n) * LUT_SIZE * 4)) return rc;
                 if (int32_t rc = rebuild_lut(p.get(), bp)) return rc;
                 bp.kernel = 1;
@@ -612,6 +681,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
     p->staged.assign(p->sampling_order.size(), 0);
     for (size_t g = 0; g < p->sampling_order.size(); ++g) {
         const auto& members = p->sampling_order[g];
+        for (int32_t m : members) p->blocks[m].order = static_cast<int32_t>(g);
         int64_t rows = 0;
         bool hit = false;
         for (int32_t m : members) rows += p->blocks[m].n;
@@ -639,10 +709,12 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
     *out = p.release();
     return THRML_OK;
 }
+// Handles may be destroyed in any order (a garbage collector does not promise one): no destroy function touches
+// its parent handle; each waits for the whole device instead of for the parent's stream.
 void thrml_program_destroy(thrml_program* p) {
     if (!p) return;
-    cudaSetDevice(p->ctx->device);
-    cudaStreamSynchronize(p->ctx->stream);
+    cudaSetDevice(p->device);
+    cudaDeviceSynchronize();
     delete p;
 }
 int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w) {
@@ -674,6 +746,7 @@ int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_off
     CU_TRY(cudaSetDevice(p->ctx->device));
     auto s = std::make_unique<thrml_state>();
     s->prog = p;
+    s->device = p->device;
     s->n_chains = n_chains;
     s->chain_offset = chain_offset;
     s->ld = (n_chains + 15) / 16 * 16;
@@ -689,8 +762,8 @@ int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_off
 }
 void thrml_state_destroy(thrml_state* s) {
     if (!s) return;
-    cudaSetDevice(s->prog->ctx->device);
-    cudaStreamSynchronize(s->prog->ctx->stream);
+    cudaSetDevice(s->device);
+    cudaDeviceSynchronize();
     delete s;
 }
 
@@ -812,16 +885,24 @@ struct NoiseCursor {
 };
 
 // One block update (program.rs:324-393 + the sampler), asynchronous on the context's stream.  mode 0 sample, 2 fields.
-static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCursor* inj, uint8_t* dst, float* fields) {
+static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCursor* inj, uint8_t* dst, float* fields, thrml_moments* acc = nullptr) {
     thrml_program* p = s->prog;
     const BlockProg& bp = p->blocks[block];
     cudaStream_t st = p->ctx->stream;
     const uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
     const uint32_t word0 = static_cast<uint32_t>(s->chain_offset >> 2);
     if (bp.kernel == 1 && !inj && !fields) {
-        LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, k0, k1};
+        LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, k0, k1,
+                  s->n_chains, nullptr, nullptr, nullptr};
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
-        k_spin_lut<<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        if (acc && acc->fused[block]) {
+            a.m1_row = acc->fused[block]->m1.as<int32_t>();
+            a.m2_row = acc->fused[block]->m2.as<int32_t>();
+            a.sums = acc->d_sums.as<long long>();
+            k_spin_lut<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else {
+            k_spin_lut<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        }
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
@@ -862,8 +943,12 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     return THRML_OK;
 }
 
-// sample_blocks (sampling.rs:28-63), asynchronous.
-static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj) {
+static int32_t observe_async(thrml_moments* m, thrml_state* s);
+
+// sample_blocks (sampling.rs:28-63), asynchronous.  With `acc` the sweep is followed by an observation of `acc`:
+// the threshold-table kernels accumulate their rows while they update, one k_moments launch covers the other rows.
+static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_moments* acc = nullptr) {
+    const bool fuse = acc && acc->mode == 0 && acc->any_fused && !inj;
     thrml_program* p = s->prog;
     std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
     rng_split(key, p->n_free, keys.data());
@@ -873,13 +958,13 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj) {
         if (!p->staged[g]) {
             for (int32_t m : members) {
                 const BlockProg& bp = p->blocks[m];
-                if (int32_t rc = launch_block(s, m, keys[m], inj, s->rows(bp.sd) + bp.offset * s->ld, nullptr)) return rc;
+                if (int32_t rc = launch_block(s, m, keys[m], inj, s->rows(bp.sd) + bp.offset * s->ld, nullptr, fuse ? acc : nullptr)) return rc;
             }
             continue;
         }
         int64_t row = 0;
         for (int32_t m : members) {
-            if (int32_t rc = launch_block(s, m, keys[m], inj, s->stage.as<uint8_t>() + row * s->ld, nullptr)) return rc;
+            if (int32_t rc = launch_block(s, m, keys[m], inj, s->stage.as<uint8_t>() + row * s->ld, nullptr, fuse ? acc : nullptr)) return rc;
             row += p->blocks[m].n;
         }
         row = 0;
@@ -889,15 +974,24 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj) {
             row += bp.n;
         }
     }
+    if (!acc) return THRML_OK;
+    if (!fuse) return observe_async(acc, s);
+    if (acc->n_left > 0) {
+        k_moments<<<static_cast<unsigned>((acc->n_left + 7) / 8), dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_sd.as<int32_t>(), acc->d_left_pos.as<int32_t>(),
+                                                                                     acc->n_left, s->cls[0].as<uint8_t>(), s->cls[1].as<uint8_t>(), s->ld, s->n_chains,
+                                                                                     acc->spin_transform, acc->d_sums.as<unsigned long long>(), acc->d_left_rows.as<int64_t>());
+        CU_TRY(cudaGetLastError());
+    }
+    acc->n_obs += s->n_chains;
     return THRML_OK;
 }
-// run_blocks (sampling.rs:81-106), asynchronous.
-static int32_t run(thrml_state* s, uint64_t key, int64_t n_iters, NoiseCursor* inj) {
-    if (n_iters <= 0) return THRML_OK;
+// run_blocks (sampling.rs:81-106), asynchronous; `acc` (nullable) is observed after the last sweep.
+static int32_t run(thrml_state* s, uint64_t key, int64_t n_iters, NoiseCursor* inj, thrml_moments* acc = nullptr) {
+    if (n_iters <= 0) return acc ? observe_async(acc, s) : THRML_OK;
     std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
     rng_split(key, n_iters, keys.data());
-    for (uint64_t k : keys)
-        if (int32_t rc = sweep(s, k, inj)) return rc;
+    for (int64_t i = 0; i < n_iters; ++i)
+        if (int32_t rc = sweep(s, keys[i], inj, i + 1 == n_iters ? acc : nullptr)) return rc;
     return THRML_OK;
 }
 
@@ -943,6 +1037,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
     CU_TRY(cudaSetDevice(p->ctx->device));
     auto m = std::make_unique<thrml_moments>();
     m->prog = p;
+    m->device = p->device;
     m->spin_transform = transform_to_spin ? 1 : 0;
     m->rows_per_type.assign(rows_per_type, rows_per_type + n_types);
     for (int64_t r : m->rows_per_type) {
@@ -959,6 +1054,69 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
     }
     cudaStream_t st = p->ctx->stream;
     const int64_t zero = 0;
+    // Split the rows: single spins and neighbour pairs of threshold-table blocks are accumulated by the update kernel
+    // itself; every other row (clamped nodes, other kernels, longer tuples, repeated rows, raw products) goes to k_moments.
+    {
+        std::vector<std::vector<int32_t>> m1(p->n_free), m2(p->n_free);
+        std::vector<int32_t> block_of_pos;  // spin class only
+        if (p->sd_spin >= 0) {
+            block_of_pos.assign(static_cast<size_t>(p->class_size[p->sd_spin]), -1);
+            for (size_t bi = 0; bi < p->blocks.size(); ++bi)
+                if (!p->blocks[bi].is_cat)
+                    for (int64_t j = 0; j < p->blocks[bi].n; ++j) block_of_pos[p->blocks[bi].offset + j] = static_cast<int32_t>(bi);
+        }
+        auto lut_block = [&](int32_t bi) { return bi >= 0 && bi < p->n_free && p->blocks[bi].kernel == 1; };
+        for (int32_t bi = 0; bi < p->n_free; ++bi)
+            if (lut_block(bi)) {
+                m1[bi].assign(static_cast<size_t>(p->blocks[bi].n), -1);
+                m2[bi].assign(static_cast<size_t>(p->blocks[bi].n) * LUT_BITS, -1);
+            }
+        std::vector<int64_t> left_ptr(1, 0), left_rows;
+        std::vector<int32_t> left_sd, left_pos;
+        for (int64_t r = 0; r < m->total_rows; ++r) {
+            const int64_t b0 = row_ptr[r], len = row_ptr[r + 1] - b0;
+            bool taken = false;
+            if (m->spin_transform && len == 1 && sd[b0] == p->sd_spin) {
+                const int32_t bi = block_of_pos[pos[b0]];
+                if (lut_block(bi)) {
+                    int32_t& slot = m1[bi][pos[b0] - p->blocks[bi].offset];
+                    if (slot < 0) { slot = static_cast<int32_t>(r); taken = true; }
+                }
+            } else if (m->spin_transform && len == 2 && sd[b0] == p->sd_spin && sd[b0 + 1] == p->sd_spin && r <= 0x7fffffff) {
+                int32_t pa = pos[b0], pb = pos[b0 + 1];
+                int32_t ba = block_of_pos[pa], bb = block_of_pos[pb];
+                if (p->blocks[ba].order < p->blocks[bb].order) { std::swap(pa, pb); std::swap(ba, bb); }  // (pa, ba) is updated later
+                if (p->blocks[ba].order > p->blocks[bb].order && lut_block(ba)) {
+                    const int64_t i = pa - p->blocks[ba].offset;
+                    for (int j = 0; j < LUT_BITS; ++j)
+                        if (p->blocks[ba].h_nbr[i * LUT_BITS + j] == pb && m2[ba][i * LUT_BITS + j] < 0) {
+                            m2[ba][i * LUT_BITS + j] = static_cast<int32_t>(r);
+                            taken = true;
+                            break;
+                        }
+                }
+            }
+            if (taken) { m->any_fused = true; continue; }
+            for (int64_t q = b0; q < b0 + len; ++q) { left_sd.push_back(sd[q]); left_pos.push_back(pos[q]); }
+            left_ptr.push_back(static_cast<int64_t>(left_sd.size()));
+            left_rows.push_back(r);
+        }
+        m->n_left = static_cast<int64_t>(left_rows.size());
+        m->fused.resize(p->n_free);
+        if (m->any_fused) {
+            for (int32_t bi = 0; bi < p->n_free; ++bi) {
+                if (!lut_block(bi)) continue;
+                m->fused[bi].reset(new FusedMaps());
+                if (int32_t rc = upload(m->fused[bi]->m1, m1[bi].data(), m1[bi].size() * 4, st)) return rc;
+                if (int32_t rc = upload(m->fused[bi]->m2, m2[bi].data(), m2[bi].size() * 4, st)) return rc;
+            }
+            if (int32_t rc = upload(m->d_left_ptr, left_ptr.data(), left_ptr.size() * 8, st)) return rc;
+            if (int32_t rc = upload(m->d_left_sd, left_sd.data(), left_sd.size() * 4, st)) return rc;
+            if (int32_t rc = upload(m->d_left_pos, left_pos.data(), left_pos.size() * 4, st)) return rc;
+            if (int32_t rc = upload(m->d_left_rows, left_rows.data(), left_rows.size() * 8, st)) return rc;
+            CU_TRY(cudaStreamSynchronize(st));
+        }
+    }
     if (int32_t rc = upload(m->d_row_ptr, m->total_rows ? row_ptr : &zero, static_cast<size_t>(m->total_rows + 1) * 8, st)) return rc;
     if (int32_t rc = upload(m->d_mem_sd, sd.data(), sd.size() * 4, st)) return rc;
     if (int32_t rc = upload(m->d_mem_pos, pos.data(), pos.size() * 4, st)) return rc;
@@ -973,6 +1131,7 @@ int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t 
     CU_TRY(cudaSetDevice(p->ctx->device));
     auto m = std::make_unique<thrml_moments>();
     m->prog = p;
+    m->device = p->device;
     m->mode = 1;
     m->K = K;
     std::vector<int32_t> sd, pos;
@@ -997,8 +1156,8 @@ int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t 
 }
 void thrml_moments_destroy(thrml_moments* m) {
     if (!m) return;
-    cudaSetDevice(m->prog->ctx->device);
-    cudaStreamSynchronize(m->prog->ctx->stream);
+    cudaSetDevice(m->device);
+    cudaDeviceSynchronize();
     delete m;
 }
 int32_t thrml_moments_reset(thrml_moments* m) {
@@ -1018,7 +1177,7 @@ static int32_t observe_async(thrml_moments* m, thrml_state* s) {
         if (m->total_rows > 0) {
             k_moments<<<static_cast<unsigned>((m->total_rows + 7) / 8), dim3(32, 8), 0, st>>>(m->d_row_ptr.as<int64_t>(), m->d_mem_sd.as<int32_t>(), m->d_mem_pos.as<int32_t>(),
                                                                                                m->total_rows, c0, c1, s->ld, s->n_chains, m->spin_transform,
-                                                                                               m->d_sums.as<unsigned long long>());
+                                                                                               m->d_sums.as<unsigned long long>(), nullptr);
             CU_TRY(cudaGetLastError());
         }
     } else {
@@ -1091,9 +1250,8 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
     NoiseCursor* ncp = nc.u ? &nc : nullptr;
     uint64_t two[2];
     rng_split(key, 2, two);  // split_two, sampling.rs:189
-    if (int32_t rc = run(s, two[0], n_warmup, ncp)) return rc;
-    if (moments)
-        if (int32_t rc = observe_async(moments, s)) return rc;
+    if (moments && moments->prog != s->prog) return fail(THRML_ERR_INVALID_ARG, "observer and state belong to different programs");
+    if (int32_t rc = run(s, two[0], n_warmup, ncp, moments)) return rc;
     if (obs_out)
         if (int32_t rc = observe_states(s, obs_blocks, n_obs_blocks, obs_out)) return rc;
     if (n_samples > 1) {  // sampling.rs:215-217,249-257: nothing more for n_samples <= 1
@@ -1101,9 +1259,7 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
         rng_split(two[1], n_samples - 1, keys.data());
         const int64_t stride = obs_rows * s->n_chains;
         for (int64_t i = 0; i < n_samples - 1; ++i) {
-            if (int32_t rc = run(s, keys[i], steps_per_sample, ncp)) return rc;
-            if (moments)
-                if (int32_t rc = observe_async(moments, s)) return rc;
+            if (int32_t rc = run(s, keys[i], steps_per_sample, ncp, moments)) return rc;
             if (obs_out)
                 if (int32_t rc = observe_states(s, obs_blocks, n_obs_blocks, obs_out + (i + 1) * stride)) return rc;
         }
