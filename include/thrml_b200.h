@@ -163,6 +163,15 @@ int32_t thrml_state_upload_f32(thrml_state* s, int32_t block, const float* host)
 int32_t thrml_state_download_f32(thrml_state* s, int32_t block, float* host);
 int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host);
 int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host);
+/* Same result as thrml_state_upload_u8, for hosts that must not allocate device memory while running (their GPU memory
+ * is already committed to another runtime's pool, or a cudaMalloc's device-wide synchronisation would stall them).
+ * No counterpart in the reference.  The [chain][node] bytes are staged in a fixed 4 MiB array inside the library image
+ * (held on every GPU that loads the library until exit) instead of a growable buffer: nodes x chains of the block must
+ * not exceed 4 MiB (4194304), larger blocks are rejected with THRML_ERR_INVALID_ARG.  The call allocates nothing.  The
+ * first call on a device looks up the array's device address; make it before any stream capture begins.  All calls
+ * share the array (it keeps the previous call's bytes, none of which are read): calls whose GPU work could overlap on
+ * one device race and must be issued one after the other. */
+int32_t thrml_state_upload_u8_static(thrml_state* s, int32_t block, const uint8_t* host);
 
 /* hinton_init (crates/thrml-models/src/ising.rs:602-673): for each listed block, P(s=1) = sigmoid(beta*b)
  * (not 2*beta*b, ising.rs:650), s = (u <= p).  biases = concatenation of the listed blocks' biases.

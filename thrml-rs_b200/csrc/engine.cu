@@ -787,6 +787,51 @@ int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host
     CU_TRY(cudaStreamSynchronize(st));
     return THRML_OK;
 }
+// ---------------------------------------------------------------------------------------------------------
+// Upload without any allocation.
+//
+// Some hosts must not allocate device memory once they are running: the GPU's memory was handed to another runtime's
+// pool at start-up so a late cudaMalloc can fail, or the host sits in a latency-sensitive loop where cudaMalloc's
+// device-wide synchronisation would stall its other streams.  thrml_state_upload_u8 may grow its staging buffer with
+// cudaMalloc; this variant stages the [chain][node] bytes in a fixed array that is part of the library image instead.
+//
+// The array costs THRML_STATIC_SCRATCH_BYTES on every GPU that loads the library, until the process exits.  In host
+// code its name is only a handle for the runtime, not a device address, so the address is looked up once per device
+// with cudaGetSymbolAddress (with that device current) on the first call there; make that first call before starting
+// any stream capture.  All calls share the array and it keeps whatever the last call left in it; the transpose reads
+// only the bytes this call has just copied, so nothing needs clearing.  Two calls whose GPU work overlaps (different
+// contexts or threads on the same device) would race on it: issue them one after the other.
+// ---------------------------------------------------------------------------------------------------------
+constexpr size_t THRML_STATIC_SCRATCH_BYTES = size_t(4) << 20;
+constexpr int THRML_STATIC_MAX_DEVICES = 64;
+static __device__ __align__(256) uint8_t g_static_scratch[THRML_STATIC_SCRATCH_BYTES];
+static uint8_t* g_static_scratch_addr[THRML_STATIC_MAX_DEVICES] = {};
+
+int32_t thrml_state_upload_u8_static(thrml_state* s, int32_t block, const uint8_t* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    const BlockProg& bp = s->prog->blocks[block];
+    const size_t bytes = static_cast<size_t>(bp.n) * s->n_chains;
+    if (bytes > THRML_STATIC_SCRATCH_BYTES)
+        return fail(THRML_ERR_INVALID_ARG, "block of " + std::to_string(bytes) + " bytes (nodes x chains) exceeds the static scratch of " +
+                                               std::to_string(THRML_STATIC_SCRATCH_BYTES) + " bytes; use thrml_state_upload_u8");
+    const int dev = s->device;
+    if (dev < 0 || dev >= THRML_STATIC_MAX_DEVICES) return fail(THRML_ERR_UNSUPPORTED, "device index beyond the static scratch table");
+    CU_TRY(cudaSetDevice(dev));
+    if (!g_static_scratch_addr[dev]) {
+        uint8_t* addr = nullptr;
+        CU_TRY(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_static_scratch));
+        g_static_scratch_addr[dev] = addr;
+    }
+    uint8_t* scratch = g_static_scratch_addr[dev];
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaMemcpyAsync(scratch, host, bytes, cudaMemcpyHostToDevice, st));
+    dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((s->ld + 31) / 32));
+    k_transpose_in<<<grid, dim3(32, 8), 0, st>>>(scratch, s->rows(bp.sd) + bp.offset * s->ld, bp.n, s->n_chains, s->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
 int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host) {
     if (int32_t rc = check_block(s, block)) return rc;
     if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");

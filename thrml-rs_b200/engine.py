@@ -231,6 +231,13 @@ class ChainState:
             host = f32(host).reshape(self.n_chains, n)
             check(lib().thrml_state_upload_f32(self.h, C.c_int32(block), ptr(host)))
 
+    def upload_static(self, block, host):
+        """thrml_state_upload_u8_static: the same upload staged in the library's fixed 4 MiB device array, for hosts that
+        must not allocate device memory while running.  Blocks above 4 MiB (nodes x chains) raise ThrmlError."""
+        n = self.program.block_len(block)
+        host = np.ascontiguousarray(host, dtype=np.uint8).reshape(self.n_chains, n)
+        check(lib().thrml_state_upload_u8_static(self.h, C.c_int32(block), ptr(host)))
+
     def download(self, block, dtype=np.float32):
         n = self.program.block_len(block)
         out = np.zeros((self.n_chains, n), dtype=dtype)
