@@ -150,7 +150,7 @@ def moment_spec(desc, info):
     return [[(i,) for i in nodes], [tuple(e) for e in info["edges"]]]
 
 
-@pytest.mark.parametrize("chains", [1, 33])
+@pytest.mark.parametrize("chains", [1, 33, 8100])  # 8100 chains: more than one bit-sliced counter segment per node
 def test_moments_and_schedule(T, O, chains):
     desc, info = M.ising_random_graph(T, 120, 6, 31)
     prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 15)

@@ -332,20 +332,51 @@ struct LutArgs {
     long long* sums;
 };
 
-// Bytes 0x01 for the chains of word q of chunk ch that exist (chain index < n_chains).
-__device__ __forceinline__ uint32_t valid_bytes(int64_t n_chains, int ch, int q) {
+// Bytes 0xff for the chains of word q of chunk ch that exist (chain index < n_chains).
+__device__ __forceinline__ uint32_t valid_mask(int64_t n_chains, int ch, int q) {
     const int64_t left = n_chains - (16 * static_cast<int64_t>(ch) + 4 * q);
-    if (left >= 4) return 0x01010101u;
+    if (left >= 4) return 0xffffffffu;
     if (left <= 0) return 0u;
-    return 0x01010101u >> (8 * (4 - static_cast<int>(left)));
+    return 0xffffffffu >> (8 * (4 - static_cast<int>(left)));
 }
+__device__ __forceinline__ uint32_t maj3(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | (c & (a | b)); }
+
+// Bit-sliced counters: plane[p] holds bit p of 32 independent counts, one per bit position of a state word
+// (bit j of byte b = "neighbour slot j differs from the new spin" for the chain in byte b).  Adding the four words of a
+// pass costs 17 logic ops for all 8 slots and 4 chains at once; counts up to 63 fit, i.e. 15 passes of 4 words.
+struct SliceCounter {
+    uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0, p4 = 0, p5 = 0;
+    __device__ __forceinline__ void add4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        const uint32_t s1 = a ^ b ^ c, c1 = maj3(a, b, c);  // a+b+c = s1 + 2 c1
+        const uint32_t ones = s1 ^ d, c2 = s1 & d;           // + d
+        const uint32_t twos = c1 ^ c2, fours = c1 & c2;
+        uint32_t k = p0 & ones;
+        p0 ^= ones;
+        uint32_t k2 = maj3(p1, twos, k);
+        p1 ^= twos ^ k;
+        k = maj3(p2, fours, k2);
+        p2 ^= fours ^ k2;
+        k2 = p3 & k;
+        p3 ^= k;
+        k = p4 & k2;
+        p4 ^= k2;
+        p5 ^= k;
+    }
+    // count of bit position `j` summed over the four bytes of the word
+    __device__ __forceinline__ uint32_t total(int j) const {
+        const uint32_t m = 0x01010101u << j;
+        return __popc(p0 & m) + 2 * __popc(p1 & m) + 4 * __popc(p2 & m) + 8 * __popc(p3 & m) + 16 * __popc(p4 & m) + 32 * __popc(p5 & m);
+    }
+};
+constexpr int ACC_SEGMENT_PASSES = 15;  // 15 passes x 4 words = 60 <= 63
 
 // Threshold-table spin update: one warp per node, each lane 16 chains per pass.  The neighbour configuration of four
 // chains is assembled with shifts inside one 32-bit word (state bytes are 0/1), then one shared-memory lookup and one
 // compare per chain replace the field accumulation and the sigmoid.
 // ACC: the moment observer fused into the update (moment.rs:205-233 for first moments and pair products): the warp
 // that updates node i is the only one that touches i's rows, so the sums are updated without atomics.  A pair row is
-// owned by the endpoint updated later in the sweep, when both values are final.
+// owned by the endpoint updated later in the sweep, when both values are final.  Disagreements with each neighbour
+// slot are counted in bit-sliced counters and reduced once per node.
 template <bool ACC>
 __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
     __shared__ uint32_t s_lut[8][LUT_SIZE];
@@ -369,61 +400,69 @@ __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
         int32_t nbj[LUT_BITS];
 #pragma unroll
         for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
-        uint32_t dis[LUT_BITS];
-        uint32_t ones = 0;
-#pragma unroll
-        for (int j = 0; j < LUT_BITS; ++j) dis[j] = 0;
         uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
-        for (int ch = lane; ch < a.n_chunks; ch += 32) {
-            uint4 v[LUT_BITS];
+        uint32_t mine = 0;  // lane j < 8: disagreements with slot j; lane 8: number of ones
+        for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {
+            const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
+            SliceCounter cnt;
+            uint32_t ones = 0;
+            for (int ch = seg + lane; ch < seg_end; ch += 32) {
+                uint4 v[LUT_BITS];
 #pragma unroll
-            for (int j = 0; j < LUT_BITS; ++j) {
-                v[j] = make_uint4(0, 0, 0, 0);
-                if (nbj[j] >= 0) v[j] = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch);
-            }
-            uint32_t cfg[4] = {0, 0, 0, 0};
+                for (int j = 0; j < LUT_BITS; ++j) {
+                    v[j] = make_uint4(0, 0, 0, 0);
+                    if (nbj[j] >= 0) v[j] = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch);
+                }
+                uint32_t cfg[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int j = 0; j < LUT_BITS; ++j) {
-                cfg[0] += v[j].x << j;
-                cfg[1] += v[j].y << j;
-                cfg[2] += v[j].z << j;
-                cfg[3] += v[j].w << j;
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const U4 r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.k0, a.k1);
-                uint32_t w = 0;
-                w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
-                w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
-                w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
-                w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
-                o[q] = w;
-            }
-            reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
-            if (ACC && own) {
+                for (int j = 0; j < LUT_BITS; ++j) {
+                    cfg[0] += v[j].x << j;
+                    cfg[1] += v[j].y << j;
+                    cfg[2] += v[j].z << j;
+                    cfg[3] += v[j].w << j;
+                }
+                uint32_t o[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const uint32_t vm = valid_bytes(a.n_chains, ch, q);
-                    ones += __popc(o[q] & vm);
-                    const uint32_t d = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+                    const U4 r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.k0, a.k1);
+                    uint32_t w = 0;
+                    w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
+                    w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
+                    w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
+                    w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
+                    o[q] = w;
+                }
+                reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+                if (ACC && own) {
+                    uint32_t d[4];
 #pragma unroll
-                    for (int j = 0; j < LUT_BITS; ++j)
-                        if ((own >> j) & 1u) dis[j] += __popc(d & (vm << j));
+                    for (int q = 0; q < 4; ++q) d[q] = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+                    if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {        // ragged last chunk: drop chains that do not exist
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t vm = valid_mask(a.n_chains, ch, q);
+                            d[q] &= vm;
+                            o[q] &= vm;
+                        }
+                    }
+                    cnt.add4(d[0], d[1], d[2], d[3]);
+                    ones += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
                 }
             }
-        }
-        if (ACC && own) {
-            long long val = 0;
-            ones = __reduce_add_sync(0xffffffffu, ones);
-            if (lane == LUT_BITS) val = 2ll * ones - a.n_chains;
+            if (ACC && own) {
+                ones = __reduce_add_sync(0xffffffffu, ones);
+                if (lane == LUT_BITS) mine += ones;
 #pragma unroll
-            for (int j = 0; j < LUT_BITS; ++j)
-                if ((own >> j) & 1u) {
-                    const uint32_t t = __reduce_add_sync(0xffffffffu, dis[j]);
-                    if (lane == j) val = a.n_chains - 2ll * t;
-                }
-            if (my_row >= 0) a.sums[my_row] += val;
+                for (int j = 0; j < LUT_BITS; ++j)
+                    if ((own >> j) & 1u) {
+                        const uint32_t t = __reduce_add_sync(0xffffffffu, cnt.total(j));
+                        if (lane == j) mine += t;
+                    }
+            }
+        }
+        if (ACC && my_row >= 0) {
+            const long long val = lane == LUT_BITS ? 2ll * mine - a.n_chains : a.n_chains - 2ll * mine;
+            a.sums[my_row] += val;
         }
     }
 }
