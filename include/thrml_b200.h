@@ -149,8 +149,15 @@ void* thrml_ctx_stream(thrml_ctx* ctx);
 int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out);
 void thrml_program_destroy(thrml_program* p);
 int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w);
+/* Dense bipartite path.  A spin block whose neighbours all lie in one other spin block (a layer of an RBM-style model:
+ * IsingEBM with bipartite edges, crates/thrml-models/src/ising.rs:105-143, which the reference samples as a padded
+ * gather, program.rs:159-300) can compute its local fields as one tensor-core GEMM against the other block's +-1 states
+ * instead.  Couplings are held as bf16 with f32 accumulation; allow_bf16_rounding = 0 refuses blocks whose couplings are
+ * not already bf16 values.  The sum order differs from the gather kernel's, so a draw can differ where the uniform falls
+ * within rounding distance of the threshold.  n_blocks_out = number of blocks switched (kernel kind 3). */
+int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding, int32_t* n_blocks_out);
 /* Which kernel a free block runs: 0 generic gather kernel, 1 threshold-table kernel (spin blocks whose
- * nodes have at most 8 single-spin-tail slots), 2 categorical kernel. */
+ * nodes have at most 8 single-spin-tail slots), 2 categorical kernel, 3 dense tensor-core kernel. */
 int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out);
 
 /* n_chains chains held on this device; chain_offset = global id of local chain 0 (the in-kernel random
@@ -193,6 +200,18 @@ typedef struct thrml_noise {
 int32_t thrml_sample_blocks(thrml_state* s, uint64_t key, const thrml_noise* inj);
 /* run_blocks (sampling.rs:81-106): n_iters sweeps with keys = key.split(n_iters). */
 int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const thrml_noise* inj);
+/* sample_single_block (program.rs:324-393): update one free block in place; `key` is the block's own key. */
+int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key);
+/* <s_a s_b> over this device's chains for every node pair of two spin blocks (s = 2x-1): host_out[n_a][n_b] f32, computed
+ * exactly from integer counts on the tensor cores.  The pairwise form of the second moments of
+ * MomentAccumulatorObserver::ising_moment_spec (moment.rs:125-148) for a complete bipartite edge set. */
+int32_t thrml_pair_correlation(thrml_state* s, int32_t block_a, int32_t block_b, float* host_out);
+/* One CD-1 step on a two-layer model (the data/model phases of estimate_kl_grad, ising.rs:531-594, collapsed to one
+ * sweep): upload v0 (host [chain][visible node] 0/1, nullable = keep the current visible state), h0 ~ P(h|v0) with
+ * key.split(2)[0], pos = <v0 h0>, one sweep sample_blocks(key.split(2)[1]), neg = <v1 h1>.  pos/neg: host
+ * [n_visible][n_hidden] f32, nullable. */
+int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_block, const uint8_t* v0_host, uint64_t key,
+                       float* pos_host, float* neg_host);
 /* Local field gamma[chain][node] (spin block) or logits theta[chain][node][K] (categorical block) of a free
  * block in the current state — spin_gibbs.rs:512-611 / softmax.rs:586-709. */
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out);

@@ -279,6 +279,9 @@ class State:
         inj = _f32(inj).ravel() if inj is not None else None
         _chk(lib().orc_sample_blocks(self.h, C.c_uint64(key), _p(inj, C.c_float), C.c_int64(0 if inj is None else inj.size)))
 
+    def sample_single_block(self, block, key):
+        _chk(lib().orc_sample_single_block(self.h, C.c_int32(block), C.c_uint64(key)))
+
     def run_blocks(self, key, n_iters, inj=None):
         inj = _f32(inj).ravel() if inj is not None else None
         _chk(lib().orc_run_blocks(self.h, C.c_uint64(key), C.c_int64(n_iters), _p(inj, C.c_float), C.c_int64(0 if inj is None else inj.size)))

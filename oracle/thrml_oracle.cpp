@@ -821,6 +821,17 @@ static int run_blocks(OState* s, uint64_t key, int64_t n_iters, Noise* inj) {
         if (sample_blocks(s, k, inj)) return -1;
     return 0;
 }
+// sample_single_block — program.rs:324-393: one free block, written back immediately.
+ORC_API int orc_sample_single_block(OState* s, int32_t block, uint64_t key) {
+    const Model* m = s->m;
+    if (block < 0 || block >= (int)m->free_blocks.size()) return fail("block index out of range");
+    std::vector<std::vector<float>> upd;
+    if (update_block(s, block, key, nullptr, upd)) return -1;
+    int cls = m->class_of_block[block];
+    int64_t off = m->block_offset[block];
+    for (int64_t c = 0; c < s->n_chains; c++) memcpy(&s->g[c][cls][off], upd[c].data(), upd[c].size() * 4);
+    return 0;
+}
 ORC_API int orc_sample_blocks(OState* s, uint64_t key, const float* inj_u, int64_t inj_len) {
     Noise nz{inj_u, inj_len, 0};
     return sample_blocks(s, key, inj_u ? &nz : nullptr);

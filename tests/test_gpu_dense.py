@@ -1,0 +1,168 @@
+"""The dense bipartite (RBM-style) path: tcgen05 GEMM + sampling epilogue, integer tensor-core pair correlations, CD-1.
+
+Tolerances.  The tensor cores add the same exact products (bf16 coupling x +-1) as the gather kernel but in another order,
+so a local field can differ from the oracle's f64 field by about 1e-6 of the summed coupling magnitudes.  A sampled spin
+may therefore differ from the oracle's only where the uniform lies within that distance of the threshold:
+|logit(u) - 2*gamma| <= 2*(2e-6 * sum|w|) + 1e-6.  Pair correlations are integer counts and must match exactly.
+"""
+import numpy as np
+import pytest
+
+import models as M
+
+pytestmark = pytest.mark.gpu
+
+
+def to_bf16(x):
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def philox(c0, c1, c2, c3, k0, k1):
+    c0, c1, c2, c3 = [np.asarray(x, dtype=np.uint64) for x in np.broadcast_arrays(c0, c1, c2, c3)]
+    k0, k1 = np.uint64(k0), np.uint64(k1)
+    m32 = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        c0, c1, c2, c3 = ((p1 >> np.uint64(32)) ^ c1 ^ k0) & m32, p1 & m32, ((p0 >> np.uint64(32)) ^ c3 ^ k1) & m32, p0 & m32
+        k0 = (k0 + np.uint64(0x9E3779B9)) & m32
+        k1 = (k1 + np.uint64(0xBB67AE85)) & m32
+    return c0, c1, c2, c3
+
+
+def spin_uniforms(n_nodes, chains, key, chain_offset=0):
+    """u[chain][node] of the engine's spin noise mapping."""
+    node = np.arange(n_nodes, dtype=np.uint64)[None, :]
+    chain = (np.arange(chains, dtype=np.uint64) + np.uint64(chain_offset))[:, None]
+    words = philox(node, chain >> np.uint64(2), 0, 0x5350494E, key & 0xFFFFFFFF, key >> 32)
+    sel = (chain & np.uint64(3)) + np.zeros_like(node)
+    r = np.choose(sel.astype(np.int64), words)
+    return (r >> np.uint64(8)).astype(np.float64) * 2.0 ** -24
+
+
+def rbm(T, n_v, n_h, seed, sigma=0.1):
+    rng = np.random.default_rng(seed)
+    W = to_bf16(rng.normal(0, sigma, (n_v, n_h)))
+    b = rng.normal(0, 0.2, n_v + n_h).astype(np.float32)
+    vis, hid = np.arange(n_v), np.arange(n_v, n_v + n_h)
+    edges = np.stack([np.repeat(vis, n_h), np.tile(hid, n_v)], axis=1)
+    desc = dict(kinds=np.zeros(n_v + n_h, np.int32), free=[(vis, 0), (hid, 1)], ops=[("add_ising", np.arange(n_v + n_h), b, edges, W.ravel(), 1.0)])
+    return desc, W, b
+
+
+def check_update(gs, os_, block, key, W_in, chains, n_blocks):
+    """GPU dense update of `block` vs the oracle from the same state; returns the mismatch count."""
+    o64, _ = os_.fields(block)
+    gs.sample_single_block(block, key)
+    os_.sample_single_block(block, key)
+    g, o = gs.download(block), os_.get_block(block)
+    bad = np.argwhere(g != o)
+    if len(bad):
+        u = spin_uniforms(g.shape[1], chains, key)
+        scale = np.abs(W_in).sum(axis=0) if block == 1 else np.abs(W_in).sum(axis=1)
+        for c, i in bad:
+            uu = min(max(u[c, i], 1e-12), 1 - 1e-12)
+            gap = abs(np.log(uu / (1 - uu)) - 2 * o64[c, i])
+            assert gap <= 2 * (2e-6 * scale[i]) + 1e-6, (c, i, gap)
+    assert len(bad) <= max(2, g.size // 2000)
+    # resynchronise so later steps compare like with like
+    gs.upload(block, o.astype(np.uint8))
+    return len(bad)
+
+
+@pytest.mark.parametrize("n_v,n_h,chains", [(100, 200, 200), (784, 300, 256), (64, 128, 128), (130, 70, 37)])
+def test_dense_update_matches_oracle(T, O, n_v, n_h, chains):
+    desc, W, b = rbm(T, n_v, n_h, 3)
+    gb, ob = M.build_both(T, O, desc)
+    prog = T.Program(gb)
+    assert prog.enable_dense(False) == 2
+    assert [prog.block_kernel(i) for i in range(2)] == [3, 3]
+    gs, os_ = T.ChainState(prog, chains), O.State(ob, chains)
+    for i, a in enumerate(M.random_states(desc, chains, 5)):
+        gs.upload(i, a)
+        os_.set_block(i, a.astype(np.float32))
+    total = 0
+    for step, blk in enumerate([1, 0, 1, 0, 1]):
+        total += check_update(gs, os_, blk, 1000 + step, W, chains, 2)
+    # the conditional means follow the logistic law: mean_c h_j ~ mean_c sigmoid(2 gamma_j)
+    o64, _ = os_.fields(1)
+    gs.sample_single_block(1, 77)
+    h = gs.download(1)
+    p = 1 / (1 + np.exp(-2 * o64))
+    z = (h.mean(axis=0) - p.mean(axis=0)) / np.sqrt((p * (1 - p)).mean(axis=0) / chains + 1e-12)
+    assert np.abs(z).max() < 5.5
+
+
+def test_dense_refuses_inexact_weights_unless_allowed(T, O):
+    desc, W, b = rbm(T, 40, 48, 9)
+    desc["ops"][0] = ("add_ising", np.arange(88), b, desc["ops"][0][3], (W.ravel() * np.float32(1.0001)).astype(np.float32), 1.0)
+    prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
+    with pytest.raises(T.ThrmlError, match="bf16"):
+        prog.enable_dense(False)
+    assert prog.enable_dense(True) == 2
+
+
+def test_sparse_blocks_do_not_qualify(T):
+    desc, _ = M.ising_random_graph(T, 300, 8, 2)
+    prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
+    assert prog.enable_dense(True) == 0
+
+
+@pytest.mark.parametrize("n_a,n_b,chains", [(100, 200, 200), (784, 130, 1000), (64, 64, 4096), (5, 300, 33)])
+def test_pair_correlation_is_exact(T, n_a, n_b, chains):
+    kinds = np.zeros(n_a + n_b, np.int32)
+    bld = T.Builder(kinds)
+    bld.add_free_block(np.arange(n_a))
+    bld.add_free_block(np.arange(n_a, n_a + n_b))
+    bld.compile()
+    st = T.ChainState(T.Program(bld), chains)
+    rng = np.random.default_rng(n_a + chains)
+    a = (rng.random((chains, n_a)) < 0.13).astype(np.uint8)
+    b = (rng.random((chains, n_b)) < 0.6).astype(np.uint8)
+    st.upload(0, a)
+    st.upload(1, b)
+    got = st.pair_correlation(0, 1)
+    sa, sb = 2 * a.astype(np.int64) - 1, 2 * b.astype(np.int64) - 1
+    want = ((sa.T @ sb).astype(np.float32) / np.float32(chains)).astype(np.float32)
+    assert np.array_equal(got, want)
+    got_t = st.pair_correlation(1, 0)
+    assert np.array_equal(got_t, want.T)
+
+
+def test_cd1_step_composition_and_statistics(T, O):
+    n_v, n_h, chains = 96, 160, 512
+    desc, W, b = rbm(T, n_v, n_h, 11)
+    gb, ob = M.build_both(T, O, desc)
+    prog = T.Program(gb)
+    prog.enable_dense(False)
+    rng = np.random.default_rng(2)
+    v0 = (rng.random((chains, n_v)) < 0.13).astype(np.uint8)
+    st = T.ChainState(prog, chains)
+    pos, neg = st.cd1_step(0, 1, v0, 99)
+    v1, h1 = st.download(0, np.uint8), st.download(1, np.uint8)
+    # the same step composed from its parts
+    k0, k1 = [int(k) for k in T.rng_split(99, 2)]
+    st2 = T.ChainState(prog, chains)
+    st2.upload(0, v0)
+    st2.sample_single_block(1, k0)
+    h0 = st2.download(1, np.uint8)
+    pos2 = st2.pair_correlation(0, 1)
+    st2.sample_blocks(k1)
+    neg2 = st2.pair_correlation(0, 1)
+    assert np.array_equal(pos, pos2) and np.array_equal(neg, neg2)
+    assert np.array_equal(v1, st2.download(0, np.uint8)) and np.array_equal(h1, st2.download(1, np.uint8))
+    s = lambda x: 2.0 * x - 1.0
+    assert np.array_equal(pos, (s(v0).T @ s(h0) / chains).astype(np.float32))
+    assert np.array_equal(neg, (s(v1).T @ s(h1) / chains).astype(np.float32))
+    # against the oracle's chain (same keys, same noise mapping): statistics agree within Monte-Carlo error
+    os_ = O.State(ob, chains)
+    os_.set_block(0, v0.astype(np.float32))
+    os_.set_block(1, np.zeros((chains, n_h), np.float32))
+    os_.sample_single_block(1, k0)
+    oh0 = os_.get_block(1)
+    assert (oh0 != h0).mean() < 1e-3
+    os_.sample_blocks(k1)
+    oneg = s(os_.get_block(0)).T @ s(os_.get_block(1)) / chains
+    assert np.abs(oneg - neg).max() < 6 / np.sqrt(chains)

@@ -1,0 +1,336 @@
+// Dense bipartite path: tcgen05 tensor-core GEMMs with TMEM accumulators, operands staged by TMA.
+//
+// A spin block whose every neighbour lies in one other block (an RBM layer) has the local field
+//     gamma[chain][i] = bias[i] + sum_j W[i][j] * (2 s[chain][j] - 1)            (spin_gibbs.rs:512-611 for a complete bipartite table)
+// which is the GEMM  D[chains x n_out] = S[chains x n_in] * W^T  with S = +-1 in bf16 and W in bf16, f32 accumulation.
+// k_dense_gemm<EPI_SAMPLE> runs that GEMM and finishes each output tile in registers: bias, sigmoid, the same
+// counter-based noise as every other kernel, Bernoulli draw, and stores of the new state (bytes, engine layout) and
+// of its +-1 bf16 image (the next layer's S operand).
+// k_dense_gemm<EPI_CORR> computes pair correlations <s_a s_b> over chains straight from the engine's byte state
+// (0/1 bytes, chains contiguous = K-major) with the 8-bit integer MMA: N11 = sum_c x_a x_b, then
+// sum_c s_a s_b = 4 N11 - 2 N1a - 2 N1b + C exactly.
+//
+// One CTA per SM, persistent over output tiles.  Warp 0: TMA producer.  Warp 1: MMA issuer and TMEM owner.
+// Warps 2-5: epilogue (each reads the 32 TMEM lanes its warp index modulo 4 selects).  Shared-memory stages and the
+// two TMEM accumulators are handed over through mbarriers; every wait is bounded and reports through an error flag.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "device_math.cuh"
+
+namespace thrml {
+namespace dense {
+
+constexpr int BM = 128;          // tile rows (TMEM lanes)
+constexpr int BK_BYTES = 128;    // one 128-byte swizzle atom along K per stage
+constexpr int STAGES = 6;
+constexpr int ACC_BUFS = 2;
+constexpr int THREADS = 192;
+constexpr uint32_t SPIN_LIMIT = 1u << 24;  // bounded waits: non-blocking polls, about a second in total, then give up
+
+enum Epilogue { EPI_SAMPLE = 0, EPI_CORR = 1 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait on a phase parity.  Returns false (and raises *err) when the limit runs out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < SPIN_LIMIT; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((spin & 1023u) == 1023u && *reinterpret_cast<volatile int*>(err) != 0) return false;  // another role gave up
+    }
+    atomicCAS(err, 0, code);
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint64_t* bar, int32_t x, int32_t y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_dst),
+                 "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+                 : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes, 128-byte swizzled, groups of 8 rows
+// 1024 bytes apart: start address, leading offset 16 B (unused for this layout), stride offset 1024 B, descriptor
+// version 1, layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3fffu);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// Instruction descriptor: accumulator format (1 f32, 2 s32), A/B formats, both K-major, N/8 at bit 17, M/16 at bit 24.
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t c_fmt, uint32_t ab_fmt, uint32_t m, uint32_t n) {
+    return (c_fmt << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+template <int KIND_I8>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    if (KIND_I8) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+            "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+            : "memory");
+    }
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]),
+          "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct GemmArgs {
+    int32_t m_total, n_total, k_bytes;  // problem size; k in bytes along the contiguous dimension
+    int32_t tiles_m, tiles_n;
+    int* err;
+    // EPI_SAMPLE
+    const float* bias;        // [n_total]
+    uint8_t* state_out;       // first state row of the updated block, [n_total][ld]
+    int64_t ld;
+    __nv_bfloat16* image_out; // +-1 bf16 image [m_total rows = chains][image_pitch], or null
+    int64_t image_pitch;      // elements
+    uint32_t chain_word0, k0, k1;
+    // EPI_CORR
+    const int32_t* ones_a;    // [m_total] number of ones per row of A
+    const int32_t* ones_b;    // [n_total]
+    float* corr_out;          // [m_total][n_total]
+    int32_t n_chains;
+};
+
+// In-quad 4x4 transpose: on return x[k] is the word this lane's position in its quad selects, taken from quad lane k.
+__device__ __forceinline__ void quad_transpose(uint32_t (&x)[4], int lane) {
+    uint32_t a = (lane & 1) ? x[0] : x[1], b = (lane & 1) ? x[2] : x[3];
+    a = __shfl_xor_sync(0xffffffffu, a, 1);
+    b = __shfl_xor_sync(0xffffffffu, b, 1);
+    if (lane & 1) { x[0] = a; x[2] = b; } else { x[1] = a; x[3] = b; }
+    uint32_t c = (lane & 2) ? x[0] : x[2], d = (lane & 2) ? x[1] : x[3];
+    c = __shfl_xor_sync(0xffffffffu, c, 2);
+    d = __shfl_xor_sync(0xffffffffu, d, 2);
+    if (lane & 2) { x[0] = c; x[1] = d; } else { x[2] = c; x[3] = d; }
+}
+
+template <int EPI, int BN>
+__global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+    constexpr int KIND_I8 = EPI == EPI_CORR;
+    constexpr uint32_t A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = ACC_BUFS * BN;  // 128 or 256: a power of two >= 32
+    constexpr uint32_t IDESC = KIND_I8 ? make_idesc(2, 0, BM, BN) : make_idesc(1, 1, BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACC_BUFS], acc_empty[ACC_BUFS];
+    __shared__ uint32_t tmem_base_slot;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = g.tiles_m * g.tiles_n;
+    const int k_tiles = (g.k_bytes + BK_BYTES - 1) / BK_BYTES;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---- TMA producer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x) {
+                const int tm = tile / g.tiles_n, tn = tile % g.tiles_n;
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1u, g.err, 1)) { alive = false; break; }
+                    mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+                    const uint32_t dst = smem_u32(smem + stage * STAGE_BYTES);
+                    const int32_t kx = kt * (BK_BYTES / (KIND_I8 ? 1 : 2));  // tensor-map coordinates count elements
+                    tma_load_2d(dst, &map_a, &full_bar[stage], kx, tm * BM);
+                    tma_load_2d(dst + A_BYTES, &map_b, &full_bar[stage], kx, tn * BN);
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0, it = 0;
+            bool alive = true;
+            for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++it) {
+                const uint32_t buf = it & 1u, use = it >> 1;
+                if (!mbar_wait(&acc_empty[buf], (use & 1u) ^ 1u, g.err, 2)) { alive = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + buf * BN;
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!mbar_wait(&full_bar[stage], phase, g.err, 3)) { alive = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a_addr = smem_u32(smem + stage * STAGE_BYTES);
+                    const uint64_t da = make_smem_desc(a_addr), db = make_smem_desc(a_addr + A_BYTES);
+#pragma unroll
+                    for (int ks = 0; ks < BK_BYTES / 32; ++ks)  // one MMA consumes 32 bytes of K (16 bf16 or 32 int8)
+                        umma<KIND_I8>(tmem_d, da + static_cast<uint64_t>(ks * 2), db + static_cast<uint64_t>(ks * 2), IDESC, (kt | ks) ? 1u : 0u);
+                    umma_commit(&empty_bar[stage]);  // frees the stage when these MMAs have read it
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (alive) umma_commit(&acc_full[buf]);
+            }
+        }
+    } else {
+        // ---- epilogue warps 2..5
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+        uint32_t it = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++it) {
+            const int tm = tile / g.tiles_n, tn = tile % g.tiles_n;
+            const uint32_t buf = it & 1u, use = it >> 1;
+            if (!mbar_wait(&acc_full[buf], use & 1u, g.err, 4)) { alive = false; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = tm * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 16; ++c) {
+                uint32_t acc[16];
+                tmem_ld16(taddr + c * 16, acc);
+                const int col0 = tn * BN + c * 16;
+                if (EPI == EPI_SAMPLE) {
+                    // row = chain, columns = nodes of the updated block
+                    uint32_t bits = 0;
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const int my_col = col0 + 4 * t + (lane & 3);
+                        const U4 r = philox4x32_10(static_cast<uint32_t>(my_col), g.chain_word0 + static_cast<uint32_t>(row >> 2), 0u, TAG_SPIN, g.k0, g.k1);
+                        uint32_t x[4] = {r.x, r.y, r.z, r.w};
+                        quad_transpose(x, lane);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int col = col0 + 4 * t + j;
+                            const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
+                            const float gamma = __fadd_rn(b, __uint_as_float(acc[4 * t + j]));
+                            const float p = det_sigmoid(__fmul_rn(gamma, 2.0f));
+                            if (u24(x[j]) <= p) bits |= 1u << (4 * t + j);
+                        }
+                    }
+                    if (row < g.m_total) {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (col0 + j < g.n_total) g.state_out[static_cast<int64_t>(col0 + j) * g.ld + row] = (bits >> j) & 1u;
+                        if (g.image_out) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)  // bf16 +1 = 0x3f80, -1 = 0xbf80
+                                w[j] = (((bits >> (2 * j)) & 1u) ? 0x3f80u : 0xbf80u) | ((((bits >> (2 * j + 1)) & 1u) ? 0x3f80u : 0xbf80u) << 16);
+                            uint4* dst = reinterpret_cast<uint4*>(g.image_out + static_cast<int64_t>(row) * g.image_pitch + col0);
+                            if (col0 + 16 <= g.image_pitch) {
+                                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                            }
+                        }
+                    }
+                } else {
+                    // row = node of block a, columns = nodes of block b; acc = N11 (int32)
+                    if (row < g.m_total) {
+                        const int32_t na = __ldg(g.ones_a + row);
+                        float out[16];
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int col = col0 + j;
+                            const int32_t nb = col < g.n_total ? __ldg(g.ones_b + col) : 0;
+                            const int32_t sum = 4 * static_cast<int32_t>(acc[j]) - 2 * na - 2 * nb + g.n_chains;
+                            out[j] = __fdiv_rn(static_cast<float>(sum), static_cast<float>(g.n_chains));
+                        }
+                        float* dst = g.corr_out + static_cast<int64_t>(row) * g.n_total + col0;
+                        if (col0 + 16 <= g.n_total && (g.n_total & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) reinterpret_cast<float4*>(dst)[j] = make_float4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if (col0 + j < g.n_total) dst[j] = out[j];
+                        }
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// 0/1 byte state [node][chain] of one block -> +-1 bf16 image [chain][node] (32x32 tiles through shared memory).
+__global__ void k_make_image(const uint8_t* rows, int64_t ld, int64_t n_chains, int32_t n, __nv_bfloat16* image, int64_t pitch) {
+    __shared__ uint8_t tile[32][33];
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
+        tile[r][threadIdx.x] = (node < n && chain < n_chains) ? rows[node * ld + chain] : 0;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
+        if (chain < n_chains && node < pitch) image[chain * pitch + node] = __float2bfloat16(node < n ? (tile[threadIdx.x][r] ? 1.0f : -1.0f) : 0.0f);
+    }
+}
+// Number of ones per state row (over existing chains).
+__global__ void k_row_ones(const uint8_t* rows, int64_t ld, int64_t n_chains, int32_t n, int32_t* out) {
+    const int64_t node = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (node >= n) return;
+    int cnt = 0;
+    for (int64_t quad = threadIdx.x; 4 * quad < n_chains; quad += 32) {
+        uint32_t wd = *reinterpret_cast<const uint32_t*>(rows + node * ld + 4 * quad);
+        const int64_t left = n_chains - 4 * quad;
+        if (left < 4) wd &= 0xffffffffu >> (8 * (4 - static_cast<int>(left)));
+        cnt += __popc(wd & 0x01010101u);
+    }
+    cnt = __reduce_add_sync(0xffffffffu, cnt);
+    if (threadIdx.x == 0) out[node] = cnt;
+}
+
+}  // namespace dense
+}  // namespace thrml

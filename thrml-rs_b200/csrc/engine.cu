@@ -10,6 +10,7 @@
 #include <memory>
 
 #include "device_math.cuh"
+#include "dense.cuh"
 #include "tables.h"
 
 using namespace thrml;
@@ -73,6 +74,16 @@ struct BlockProg {
     DevBuf d_lut;    // uint32 [n][256]
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
     int32_t order = -1;          // position of the block's superblock in the sweep; -1 for clamped blocks
+    // dense bipartite path (kernel 3): every neighbour of every node lies in block `dense_src`
+    int32_t dense_src = -1;      // candidate source block, -1 when the block does not qualify
+    bool dense_on = false;
+    int32_t base_kernel = 0;     // kernel used when the dense path is off or cannot serve a call
+    int64_t dense_pitch = 0;     // elements per row of d_dense_w
+    std::vector<float> h_dense_w;  // [n][n_src] f32, canonical weights (0 where there is no edge)
+    std::vector<float> h_dense_bias;
+    DevBuf d_dense_w;            // bf16 [n][dense_pitch], K-major (K = source nodes)
+    DevBuf d_dense_bias;         // f32 [n]
+    CUtensorMap map_w;
 };
 
 struct thrml_program {
@@ -86,6 +97,8 @@ struct thrml_program {
     int64_t max_stage_rows = 0;
     std::vector<int8_t> loc_sd;     // node -> class / position (host copy, for observers)
     std::vector<int64_t> loc_pos;
+    std::vector<uint8_t> is_dense_source;  // per block: some dense block reads its +-1 image
+    bool any_dense = false;
 };
 
 struct thrml_state {
@@ -95,6 +108,14 @@ struct thrml_state {
     DevBuf cls[2];      // state rows per class
     DevBuf stage;       // staging rows for superblocks that cannot be updated in place
     DevBuf scratch;     // transposes, injected noise, debug fields
+    // dense path: +-1 bf16 image [chain][node] of source blocks, tensor maps, per-row one counts, error flag
+    std::vector<std::unique_ptr<DevBuf>> image;
+    std::vector<uint8_t> image_fresh;
+    std::vector<CUtensorMap> map_image;
+    std::vector<std::unique_ptr<DevBuf>> ones;
+    DevBuf d_err, d_corr;
+    int64_t image_rows = 0;
+    void touch(int32_t block) { if (!image_fresh.empty()) image_fresh[block] = 0; }
     uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
 };
 
@@ -574,6 +595,44 @@ __global__ void __launch_bounds__(256) k_marginals(const int32_t* node_sd, const
 // ---------------------------------------------------------------------------------------------------------
 // Host helpers.
 // ---------------------------------------------------------------------------------------------------------
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+// 2-D K-major operand: `rows` rows of `k_elems` contiguous elements, row pitch in bytes; box = 128 bytes of K x box_rows,
+// 128-byte swizzle, out-of-range elements read as zero.
+static int32_t make_operand_map(CUtensorMap* map, void* base, bool is_u8, int64_t k_elems, int64_t rows, int64_t pitch_bytes, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(THRML_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k_elems), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_bytes)};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(is_u8 ? 128 : 64), static_cast<cuuint32_t>(box_rows)};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, is_u8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(THRML_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
+    return THRML_OK;
+}
+static inline uint16_t f32_to_bf16_rn(float f) {
+    uint32_t u;
+    std::memcpy(&u, &f, 4);
+    u += 0x7fffu + ((u >> 16) & 1u);
+    return static_cast<uint16_t>(u >> 16);
+}
+static inline float bf16_to_f32(uint16_t h) {
+    uint32_t u = static_cast<uint32_t>(h) << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
 static int32_t upload(DevBuf& buf, const void* host, size_t bytes, cudaStream_t st) {
     if (int32_t rc = buf.alloc(bytes)) return rc;
     if (bytes) CU_TRY(cudaMemcpyAsync(buf.p, host, bytes, cudaMemcpyHostToDevice, st));
@@ -713,8 +772,48 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 bp.kernel = 1;
             }
         }
+        bp.base_kernel = bp.kernel;
+        // Dense bipartite candidate: a spin block whose neighbours all lie in one other spin block, densely enough
+        // that the field is a GEMM against that block's +-1 image.
+        if (!bp.is_cat && !tabs.empty()) {
+            bool ok = true;
+            int64_t lo = INT64_MAX, hi = -1, slots = 0;
+            for (const SlotTable& t : tabs) {
+                if (t.wdim != 1 || t.idx.size() != static_cast<size_t>(t.n_spin) || t.n_spin > 1) { ok = false; break; }
+                if (t.n_spin == 0) continue;
+                for (size_t f = 0; f < t.active.size(); ++f)
+                    if (t.active[f]) { lo = std::min<int64_t>(lo, t.idx[0][f]); hi = std::max<int64_t>(hi, t.idx[0][f]); ++slots; }
+            }
+            int32_t src = -1;
+            if (ok && hi >= 0)
+                for (int32_t o = 0; o < p->n_free + p->n_clamped; ++o) {
+                    const BlockInfo& ob = o < p->n_free ? b->free_blocks[o] : b->clamped_blocks[o - p->n_free];
+                    if (ob.kind == 0 && o != i && lo >= ob.offset && hi < ob.offset + static_cast<int64_t>(ob.nodes.size())) src = o;
+                }
+            if (src >= 0) {
+                const BlockInfo& ob = src < p->n_free ? b->free_blocks[src] : b->clamped_blocks[src - p->n_free];
+                const int64_t n_src = static_cast<int64_t>(ob.nodes.size());
+                if (n_src >= 16 && bp.n * n_src <= (int64_t(1) << 28) && 4 * slots >= bp.n * n_src) {
+                    bp.dense_src = src;
+                    bp.h_dense_w.assign(static_cast<size_t>(bp.n * n_src), 0.0f);
+                    bp.h_dense_bias.assign(static_cast<size_t>(bp.n), 0.0f);
+                    for (const SlotTable& t : tabs)
+                        for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                            float sum = 0.0f;
+                            for (int32_t j = 0; j < t.k; ++j) {
+                                const size_t f = static_cast<size_t>(i2) * t.k + j;
+                                if (!t.active[f]) continue;
+                                if (t.n_spin == 0) sum += t.w[f];
+                                else bp.h_dense_w[static_cast<size_t>(i2 * n_src + (t.idx[0][f] - ob.offset))] += t.w[f];
+                            }
+                            if (t.n_spin == 0) bp.h_dense_bias[i2] += sum;
+                        }
+                }
+            }
+        }
         CU_TRY(cudaStreamSynchronize(ctx->stream));  // host vectors above go out of scope
     }
+    p->is_dense_source.assign(p->blocks.size(), 0);
     // A superblock is updated in place unless one of its blocks reads a position that the superblock writes
     // (several blocks updated "at the same time", sampling.rs:40-59, or a block with edges inside itself).
     p->staged.assign(p->sampling_order.size(), 0);
@@ -761,11 +860,45 @@ int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t,
     if (block < 0 || block >= p->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
     BlockProg& bp = p->blocks[block];
     if (t < 0 || t >= bp.n_tabs) return fail(THRML_ERR_INVALID_ARG, "table index out of range");
+    if (bp.dense_on) return fail(THRML_ERR_UNSUPPORTED, "weights of a block on the dense path are fixed; create a new program to change them");
+    bp.dense_src = -1;  // the cached dense matrix no longer matches the tables
     CU_TRY(cudaSetDevice(p->ctx->device));
     CU_TRY(cudaMemcpyAsync(bp.w_bufs[t]->p, w, bp.w_len[t] * 4, cudaMemcpyHostToDevice, p->ctx->stream));
     if (bp.kernel == 1)
         if (int32_t rc = rebuild_lut(p, bp)) return rc;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding, int32_t* n_blocks_out) {
+    if (!p) return fail(THRML_ERR_INVALID_ARG, "null program");
+    CU_TRY(cudaSetDevice(p->device));
+    cudaStream_t st = p->ctx->stream;
+    int32_t switched = 0;
+    for (int32_t bi = 0; bi < p->n_free; ++bi) {
+        BlockProg& bp = p->blocks[bi];
+        if (bp.dense_src < 0 || bp.dense_on) continue;
+        if (p->staged[bp.order]) continue;  // blocks updated through staging rows keep the gather kernel
+        const int64_t n_src = p->blocks[bp.dense_src].n;
+        bool exact = true;
+        for (float w : bp.h_dense_w)
+            if (bf16_to_f32(f32_to_bf16_rn(w)) != w) { exact = false; break; }
+        if (!exact && !allow_bf16_rounding)
+            return fail(THRML_ERR_INVALID_ARG, "the dense path stores couplings as bf16 and block " + std::to_string(bi) + " has couplings that are not bf16 values; pass allow_bf16_rounding = 1 to round them");
+        bp.dense_pitch = (n_src + 63) / 64 * 64;
+        std::vector<uint16_t> wb(static_cast<size_t>(bp.n * bp.dense_pitch), 0);
+        for (int64_t i = 0; i < bp.n; ++i)
+            for (int64_t j = 0; j < n_src; ++j) wb[static_cast<size_t>(i * bp.dense_pitch + j)] = f32_to_bf16_rn(bp.h_dense_w[static_cast<size_t>(i * n_src + j)]);
+        if (int32_t rc = upload(bp.d_dense_w, wb.data(), wb.size() * 2, st)) return rc;
+        if (int32_t rc = upload(bp.d_dense_bias, bp.h_dense_bias.data(), bp.h_dense_bias.size() * 4, st)) return rc;
+        CU_TRY(cudaStreamSynchronize(st));
+        if (int32_t rc = make_operand_map(&bp.map_w, bp.d_dense_w.p, false, n_src, bp.n, bp.dense_pitch * 2, 128)) return rc;
+        bp.dense_on = true;
+        bp.kernel = 3;
+        p->is_dense_source[bp.dense_src] = 1;
+        p->any_dense = true;
+        ++switched;
+    }
+    if (n_blocks_out) *n_blocks_out = switched;
     return THRML_OK;
 }
 int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out) {
@@ -795,6 +928,12 @@ int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_off
     }
     if (p->max_stage_rows > 0)
         if (int32_t rc = s->stage.alloc(static_cast<size_t>(p->max_stage_rows) * s->ld)) return rc;
+    const size_t nb_all = p->blocks.size();
+    s->image.resize(nb_all);
+    s->ones.resize(nb_all);
+    s->image_fresh.assign(nb_all, 0);
+    s->map_image.resize(nb_all);
+    s->image_rows = (n_chains + 127) / 128 * 128;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
     *out = s.release();
     return THRML_OK;
@@ -824,6 +963,7 @@ int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host
     k_transpose_in<<<grid, dim3(32, 8), 0, st>>>(s->scratch.as<uint8_t>(), s->rows(bp.sd) + bp.offset * s->ld, bp.n, s->n_chains, s->ld);
     CU_TRY(cudaGetLastError());
     CU_TRY(cudaStreamSynchronize(st));
+    s->touch(block);
     return THRML_OK;
 }
 // ---------------------------------------------------------------------------------------------------------
@@ -869,6 +1009,7 @@ int32_t thrml_state_upload_u8_static(thrml_state* s, int32_t block, const uint8_
     k_transpose_in<<<grid, dim3(32, 8), 0, st>>>(scratch, s->rows(bp.sd) + bp.offset * s->ld, bp.n, s->n_chains, s->ld);
     CU_TRY(cudaGetLastError());
     CU_TRY(cudaStreamSynchronize(st));
+    s->touch(block);
     return THRML_OK;
 }
 int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host) {
@@ -937,6 +1078,7 @@ int32_t thrml_hinton_init(thrml_state* s, const int32_t* blocks, int32_t n_block
                                                                  static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[i]),
                                                                  static_cast<uint32_t>(keys[i] >> 32), d_inj ? d_inj + boff * s->n_chains : nullptr);
         CU_TRY(cudaGetLastError());
+        s->touch(blocks[i]);
         boff += bp.n;
     }
     CU_TRY(cudaStreamSynchronize(st));
@@ -955,6 +1097,7 @@ int32_t thrml_state_randomize(thrml_state* s, uint64_t key) {
                                                                     static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[b]),
                                                                     static_cast<uint32_t>(keys[b] >> 32));
         CU_TRY(cudaGetLastError());
+        s->touch(b);
     }
     CU_TRY(cudaStreamSynchronize(st));
     return THRML_OK;
@@ -968,6 +1111,86 @@ struct NoiseCursor {
     int64_t len = 0, pos = 0;
 };
 
+// ---- dense path plumbing -------------------------------------------------------------------------------
+static int32_t ensure_err_flag(thrml_state* s) {
+    if (s->d_err.p) return THRML_OK;
+    if (int32_t rc = s->d_err.alloc(sizeof(int))) return rc;
+    CU_TRY(cudaMemsetAsync(s->d_err.p, 0, sizeof(int), s->prog->ctx->stream));
+    return THRML_OK;
+}
+// Reads the kernels' error flag after a synchronisation; a non-zero value means a bounded wait ran out.
+static int32_t check_err_flag(thrml_state* s) {
+    if (!s->d_err.p) return THRML_OK;
+    int code = 0;
+    CU_TRY(cudaMemcpy(&code, s->d_err.p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code == 0) return THRML_OK;
+    CU_TRY(cudaMemset(s->d_err.p, 0, sizeof(int)));
+    return fail(THRML_ERR_TIMEOUT, "a tensor-core kernel gave up waiting on a pipeline barrier (role " + std::to_string(code) + ")");
+}
+// +-1 bf16 image [chain][node] of a block, rebuilt from the byte state when stale.
+static int32_t ensure_image(thrml_state* s, int32_t block, bool need_fresh) {
+    const BlockProg& bp = s->prog->blocks[block];
+    const int64_t pitch = (bp.n + 63) / 64 * 64;
+    if (!s->image[block]) {
+        s->image[block].reset(new DevBuf());
+        if (int32_t rc = s->image[block]->alloc(static_cast<size_t>(s->image_rows * pitch) * 2)) return rc;
+        CU_TRY(cudaMemsetAsync(s->image[block]->p, 0, s->image[block]->bytes, s->prog->ctx->stream));
+        if (int32_t rc = make_operand_map(&s->map_image[block], s->image[block]->p, false, bp.n, s->n_chains, pitch * 2, dense::BM)) return rc;
+        s->image_fresh[block] = 0;
+    }
+    if (need_fresh && !s->image_fresh[block]) {
+        dim3 grid(static_cast<unsigned>((pitch + 31) / 32), static_cast<unsigned>((s->n_chains + 31) / 32));
+        dense::k_make_image<<<grid, dim3(32, 8), 0, s->prog->ctx->stream>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
+                                                                           s->image[block]->as<__nv_bfloat16>(), pitch);
+        CU_TRY(cudaGetLastError());
+        s->image_fresh[block] = 1;
+    }
+    return THRML_OK;
+}
+extern "C++" {
+template <int EPI, int BN>
+static int32_t launch_dense(thrml_state* s, const CUtensorMap& ma, const CUtensorMap& mb, dense::GemmArgs g) {
+    constexpr size_t smem = dense::STAGES * (dense::BM + BN) * dense::BK_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        CU_TRY(cudaFuncSetAttribute(dense::k_dense_gemm<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured = true;
+    }
+    g.tiles_m = (g.m_total + dense::BM - 1) / dense::BM;
+    g.tiles_n = (g.n_total + BN - 1) / BN;
+    g.err = s->d_err.as<int>();
+    const int ctas = std::min(s->prog->ctx->sm_count, g.tiles_m * g.tiles_n);
+    dense::k_dense_gemm<EPI, BN><<<ctas, dense::THREADS, smem, s->prog->ctx->stream>>>(ma, mb, g);
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
+}  // extern "C++"
+// Tensor-core update of a dense bipartite block, in place.
+static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t k1) {
+    thrml_program* p = s->prog;
+    const BlockProg& bp = p->blocks[block];
+    if (int32_t rc = ensure_err_flag(s)) return rc;
+    if (int32_t rc = ensure_image(s, bp.dense_src, true)) return rc;
+    const bool write_image = p->is_dense_source[block] != 0;
+    if (write_image)
+        if (int32_t rc = ensure_image(s, block, false)) return rc;
+    dense::GemmArgs g{};
+    g.m_total = static_cast<int32_t>(s->n_chains);
+    g.n_total = static_cast<int32_t>(bp.n);
+    g.k_bytes = static_cast<int32_t>(p->blocks[bp.dense_src].n * 2);
+    g.bias = bp.d_dense_bias.as<float>();
+    g.state_out = s->rows(bp.sd) + bp.offset * s->ld;
+    g.ld = s->ld;
+    g.image_out = write_image ? s->image[block]->as<__nv_bfloat16>() : nullptr;
+    g.image_pitch = (bp.n + 63) / 64 * 64;
+    g.chain_word0 = static_cast<uint32_t>(s->chain_offset >> 2);
+    g.k0 = k0;
+    g.k1 = k1;
+    if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g)) return rc;
+    s->image_fresh[block] = write_image ? 1 : 0;
+    return THRML_OK;
+}
+
 // One block update (program.rs:324-393 + the sampler), asynchronous on the context's stream.  mode 0 sample, 2 fields.
 static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCursor* inj, uint8_t* dst, float* fields, thrml_moments* acc = nullptr) {
     thrml_program* p = s->prog;
@@ -975,7 +1198,13 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     cudaStream_t st = p->ctx->stream;
     const uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
     const uint32_t word0 = static_cast<uint32_t>(s->chain_offset >> 2);
-    if (bp.kernel == 1 && !inj && !fields) {
+    const bool to_state = dst == s->rows(bp.sd) + bp.offset * s->ld;
+    if (bp.kernel == 3 && !inj && !fields && to_state) {
+        if (int32_t rc = dense_update(s, block, k0, k1)) return rc;
+        return THRML_OK;
+    }
+    if (!fields) s->touch(block);
+    if (bp.base_kernel == 1 && !inj && !fields) {
         LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, k0, k1,
                   s->n_chains, nullptr, nullptr, nullptr};
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
@@ -1055,6 +1284,7 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_momen
         for (int32_t m : members) {  // all members written back together (sampling.rs:57-59)
             const BlockProg& bp = p->blocks[m];
             CU_TRY(cudaMemcpyAsync(s->rows(bp.sd) + bp.offset * s->ld, s->stage.as<uint8_t>() + row * s->ld, static_cast<size_t>(bp.n) * s->ld, cudaMemcpyDeviceToDevice, st));
+            s->touch(m);
             row += bp.n;
         }
     }
@@ -1086,7 +1316,7 @@ int32_t thrml_sample_blocks(thrml_state* s, uint64_t key, const thrml_noise* inj
     if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
     if (int32_t rc = sweep(s, key, nc.u ? &nc : nullptr)) return rc;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
-    return THRML_OK;
+    return check_err_flag(s);
 }
 int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const thrml_noise* inj) {
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
@@ -1096,8 +1326,97 @@ int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const th
     if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
     if (int32_t rc = run(s, key, n_iters, nc.u ? &nc : nullptr)) return rc;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
-    return THRML_OK;
+    return check_err_flag(s);
 }
+// sample_single_block (program.rs:324-393): update one free block in place with the given block key.
+int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (block < 0 || block >= s->prog->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const BlockProg& bp = s->prog->blocks[block];
+    cudaStream_t st = s->prog->ctx->stream;
+    if (s->prog->staged[bp.order]) {
+        if (int32_t rc = launch_block(s, block, key, nullptr, s->stage.as<uint8_t>(), nullptr)) return rc;
+        CU_TRY(cudaMemcpyAsync(s->rows(bp.sd) + bp.offset * s->ld, s->stage.p, static_cast<size_t>(bp.n) * s->ld, cudaMemcpyDeviceToDevice, st));
+        s->touch(block);
+    } else if (int32_t rc = launch_block(s, block, key, nullptr, s->rows(bp.sd) + bp.offset * s->ld, nullptr)) {
+        return rc;
+    }
+    CU_TRY(cudaStreamSynchronize(st));
+    return check_err_flag(s);
+}
+
+// <s_a s_b> over this device's chains for every node pair of two spin blocks, on the tensor cores (asynchronous; result in
+// s->d_corr as f32 [n_a][n_b]).
+static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t block_b, float* d_out) {
+    thrml_program* p = s->prog;
+    const BlockProg& ba = p->blocks[block_a];
+    const BlockProg& bb = p->blocks[block_b];
+    if (ba.is_cat || bb.is_cat) return fail(THRML_ERR_INVALID_ARG, "pair correlations are defined for spin blocks");
+    cudaStream_t st = p->ctx->stream;
+    if (int32_t rc = ensure_err_flag(s)) return rc;
+    CUtensorMap map_a, map_b;  // encoded per call: kernel parameters are copied at launch
+    if (int32_t rc = make_operand_map(&map_a, s->rows(ba.sd) + ba.offset * s->ld, true, s->n_chains, ba.n, s->ld, dense::BM)) return rc;
+    if (int32_t rc = make_operand_map(&map_b, s->rows(bb.sd) + bb.offset * s->ld, true, s->n_chains, bb.n, s->ld, 64)) return rc;
+    for (int32_t blk : {block_a, block_b}) {
+        const BlockProg& bp = p->blocks[blk];
+        if (!s->ones[blk]) {
+            s->ones[blk].reset(new DevBuf());
+            if (int32_t rc = s->ones[blk]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+        }
+        dense::k_row_ones<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
+                                                                                         s->ones[blk]->as<int32_t>());
+        CU_TRY(cudaGetLastError());
+    }
+    dense::GemmArgs g{};
+    g.m_total = static_cast<int32_t>(ba.n);
+    g.n_total = static_cast<int32_t>(bb.n);
+    g.k_bytes = static_cast<int32_t>(s->n_chains);
+    g.ones_a = s->ones[block_a]->as<int32_t>();
+    g.ones_b = s->ones[block_b]->as<int32_t>();
+    g.corr_out = d_out;
+    g.n_chains = static_cast<int32_t>(s->n_chains);
+    return launch_dense<dense::EPI_CORR, 64>(s, map_a, map_b, g);
+}
+int32_t thrml_pair_correlation(thrml_state* s, int32_t block_a, int32_t block_b, float* host_out) {
+    if (!s || !host_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (int32_t rc = check_block(s, block_a)) return rc;
+    if (int32_t rc = check_block(s, block_b)) return rc;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const size_t cnt = static_cast<size_t>(s->prog->blocks[block_a].n) * s->prog->blocks[block_b].n;
+    if (s->d_corr.bytes < 2 * cnt * 4)
+        if (int32_t rc = s->d_corr.alloc(2 * cnt * 4)) return rc;
+    if (int32_t rc = pair_correlation_async(s, block_a, block_b, s->d_corr.as<float>())) return rc;
+    CU_TRY(cudaMemcpyAsync(host_out, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, s->prog->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return check_err_flag(s);
+}
+// One contrastive-divergence step on a two-layer model: load the visible data, h0 ~ P(h | v0), positive correlations
+// <v0 h0>, one Gibbs sweep (sample_blocks), negative correlations <v1 h1>.
+int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_block, const uint8_t* v0_host, uint64_t key, float* pos_host, float* neg_host) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (visible_block < 0 || visible_block >= s->prog->n_free || hidden_block < 0 || hidden_block >= s->prog->n_free || visible_block == hidden_block)
+        return fail(THRML_ERR_INVALID_ARG, "visible and hidden must be two distinct free blocks");
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    cudaStream_t st = s->prog->ctx->stream;
+    const size_t cnt = static_cast<size_t>(s->prog->blocks[visible_block].n) * s->prog->blocks[hidden_block].n;
+    if (s->d_corr.bytes < 2 * cnt * 4)
+        if (int32_t rc = s->d_corr.alloc(2 * cnt * 4)) return rc;
+    if (v0_host)
+        if (int32_t rc = thrml_state_upload_u8(s, visible_block, v0_host)) return rc;
+    uint64_t keys[2];
+    rng_split(key, 2, keys);
+    const BlockProg& hb = s->prog->blocks[hidden_block];
+    if (int32_t rc = launch_block(s, hidden_block, keys[0], nullptr, s->rows(hb.sd) + hb.offset * s->ld, nullptr)) return rc;
+    if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>())) return rc;
+    if (int32_t rc = sweep(s, keys[1], nullptr)) return rc;
+    if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>() + cnt)) return rc;
+    if (pos_host) CU_TRY(cudaMemcpyAsync(pos_host, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, st));
+    if (neg_host) CU_TRY(cudaMemcpyAsync(neg_host, s->d_corr.as<float>() + cnt, cnt * 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return check_err_flag(s);
+}
+
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out) {
     if (!s || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
     if (block < 0 || block >= s->prog->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
@@ -1349,7 +1668,7 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
         }
     }
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
-    return THRML_OK;
+    return check_err_flag(s);
 }
 
 }  // extern "C"

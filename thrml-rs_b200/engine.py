@@ -192,6 +192,12 @@ class Program:
         w = f32(w)
         check(lib().thrml_program_update_weights(self.h, C.c_int32(block), C.c_int32(table), ptr(w)))
 
+    def enable_dense(self, allow_bf16_rounding=False):
+        """Switch every qualifying bipartite spin block to the tensor-core kernel; returns how many were switched."""
+        n = C.c_int32()
+        check(lib().thrml_program_enable_dense(self.h, C.c_int32(int(allow_bf16_rounding)), C.byref(n)))
+        return n.value
+
     def block_kernel(self, block):
         k = C.c_int32()
         check(lib().thrml_program_block_kernel(self.h, C.c_int32(block), C.byref(k)))
@@ -262,6 +268,22 @@ class ChainState:
     def run_blocks(self, key, n_iters, inj=None):
         nz, keep = _ffi.make_noise(inj)
         check(lib().thrml_run_blocks(self.h, C.c_uint64(int(key)), C.c_int64(n_iters), C.byref(nz) if nz else None))
+
+    def sample_single_block(self, block, key):
+        check(lib().thrml_sample_single_block(self.h, C.c_int32(block), C.c_uint64(int(key))))
+
+    def pair_correlation(self, block_a, block_b):
+        out = np.zeros((self.program.block_len(block_a), self.program.block_len(block_b)), dtype=np.float32)
+        check(lib().thrml_pair_correlation(self.h, C.c_int32(block_a), C.c_int32(block_b), ptr(out)))
+        return out
+
+    def cd1_step(self, visible_block, hidden_block, v0, key, want_stats=True):
+        nv, nh = self.program.block_len(visible_block), self.program.block_len(hidden_block)
+        v0 = np.ascontiguousarray(v0, dtype=np.uint8).reshape(self.n_chains, nv) if v0 is not None else None
+        pos = np.zeros((nv, nh), dtype=np.float32) if want_stats else None
+        neg = np.zeros((nv, nh), dtype=np.float32) if want_stats else None
+        check(lib().thrml_cd1_step(self.h, C.c_int32(visible_block), C.c_int32(hidden_block), ptr(v0), C.c_uint64(int(key)), ptr(pos), ptr(neg)))
+        return pos, neg
 
     def fields(self, block):
         n = self.program.block_len(block)
