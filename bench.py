@@ -39,6 +39,8 @@ def parse():
     ap.add_argument("--chains", type=int, default=CHAINS_PER_GPU, help="chains per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm"],
+                    help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores (1 GPU)")
     return ap.parse_args()
 
 
@@ -163,6 +165,10 @@ def main():
     T = graft.load_package()
     from thrml_rs_b200 import workloads as W
     torch.cuda.set_device(local_rank)
+    if args.workload == "rbm":
+        if rank == 0:
+            print(json.dumps(run_rbm(T, torch, W, args, local_rank)), flush=True)
+        return
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
@@ -251,6 +257,66 @@ def main():
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps(result), flush=True)
+
+
+def run_rbm(T, torch, W, args, device):
+    """Dense bipartite configuration: 784 visible x 4096 hidden spins, bf16 couplings, 8192 chains, CD-1 per step
+    (h0 | v0, one Gibbs sweep, positive and negative correlations).  Reported against the measured bf16 GEMM peak."""
+    model = W.rbm_ising()
+    nv, nh, chains = model["n_visible"], model["n_hidden"], 8192
+    ctx = T.default_context(device)
+    builder = W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model)
+    program = T.Program(builder, ctx)
+    assert program.enable_dense(False) == 2
+    rng = np.random.default_rng(3)
+    v0 = (rng.random((chains, nv)) < 0.13).astype(np.uint8)
+    data, state = T.ChainState(program, chains), T.ChainState(program, chains)
+    data.upload(0, v0)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def step(i):
+        state.copy_block_from(data, 0)
+        state.cd1_step(0, 1, None, 500 + i, want_stats=False)
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    ctx.synchronize()
+    sampler = ClockSampler(device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(100 + i)
+    ev1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.stop(t0, t1)
+    flop = 5 * 2.0 * chains * nv * nh  # 3 field GEMMs + 2 correlation GEMMs
+    updates = chains * (nh + nv + nh)
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = float(peaks.get("bf16_tflops", 1590.0))
+    achieved = flop / (ms * 1e-3) / 1e12
+    # end to end: upload v0 from pinned host memory, CD-1, read both correlation matrices back
+    hv = torch.empty((chains, nv), dtype=torch.uint8, pin_memory=True)
+    hv.numpy()[:] = v0
+    best = None
+    for rep in range(3):
+        ctx.synchronize()
+        ta = time.perf_counter()
+        pos, neg = state.cd1_step(0, 1, hv.numpy(), 900 + rep)
+        dt = time.perf_counter() - ta
+        best = dt if best is None else min(best, dt)
+    return {"metric": METRIC, "value": updates / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 couplings x +-1 states, f32 accumulate; u8 x u8 -> s32 correlations", "data": "synthetic",
+            "config": {"workload": "bipartite RBM-style Ising EBM, CD-1 per step", "visible": nv, "hidden": nh, "chains": chains,
+                       "l2": "operands (6.4 MB couplings, 13-67 MB states) fit in L2: a tensor-pipe measurement, not an HBM one"},
+            "clocks": clocks, "gpu_launches": args.steps * 10,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                         "peak_source": "measured burst bf16 GEMM (MEASURED_PEAKS.json)" if peaks else "fallback 1590", "flop_per_step": flop,
+                         "note": "3 bf16 field GEMMs + 2 int8 correlation GEMMs counted at 2*M*N*K each"},
+            "e2e": {"value": updates / best, "unit": UNIT, "h2d_bytes_per_step": chains * nv, "d2h_bytes_per_step": 2 * nv * nh * 4, "seconds": best}}
 
 
 def moment_tensor(torch, moments):

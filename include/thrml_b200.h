@@ -170,6 +170,9 @@ int32_t thrml_state_upload_f32(thrml_state* s, int32_t block, const float* host)
 int32_t thrml_state_download_f32(thrml_state* s, int32_t block, float* host);
 int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host);
 int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host);
+/* Device-to-device copy of one block's state between two states of the same program and chain count (asynchronous on
+ * the context's stream; the reference's equivalent is cloning a state tensor, e.g. sampling.rs:237). */
+int32_t thrml_state_copy_block(thrml_state* dst, const thrml_state* src, int32_t block);
 /* Same result as thrml_state_upload_u8, for hosts that must not allocate device memory while running (their GPU memory
  * is already committed to another runtime's pool, or a cudaMalloc's device-wide synchronisation would stall them).
  * No counterpart in the reference.  The [chain][node] bytes are staged in a fixed 4 MiB array inside the library image

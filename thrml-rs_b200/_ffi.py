@@ -55,6 +55,7 @@ _SIGNATURES = {
     "thrml_state_upload_u8": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_state_download_u8": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_state_upload_u8_static": (C.c_int32, [_P, C.c_int32, _P]),
+    "thrml_state_copy_block": (C.c_int32, [_P, _P, C.c_int32]),
     "thrml_hinton_init": (C.c_int32, [_P, _P, C.c_int32, _P, C.c_float, C.c_uint64, _P]),
     "thrml_state_randomize": (C.c_int32, [_P, C.c_uint64]),
     "thrml_sample_blocks": (C.c_int32, [_P, C.c_uint64, _P]),

@@ -11,8 +11,11 @@
 // sum_c s_a s_b = 4 N11 - 2 N1a - 2 N1b + C exactly.
 //
 // One CTA per SM, persistent over output tiles.  Warp 0: TMA producer.  Warp 1: MMA issuer and TMEM owner.
-// Warps 2-5: epilogue (each reads the 32 TMEM lanes its warp index modulo 4 selects).  Shared-memory stages and the
-// two TMEM accumulators are handed over through mbarriers; every wait is bounded and reports through an error flag.
+// Warps 2-17: epilogue; a warp reads the 32 TMEM lanes its warp index modulo 4 selects, and the four warps that share a
+// lane quarter split the tile's columns.  Sixteen epilogue warps keep four warps on every scheduler: with fewer the
+// per-element math (noise, sigmoid, compare) runs at dependent-issue latency and hides the tensor pipe behind it.
+// Shared-memory stages and the two TMEM accumulators are handed over through mbarriers; every wait is bounded and
+// reports through an error flag.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -25,9 +28,10 @@ namespace dense {
 
 constexpr int BM = 128;          // tile rows (TMEM lanes)
 constexpr int BK_BYTES = 128;    // one 128-byte swizzle atom along K per stage
-constexpr int STAGES = 6;
+constexpr int STAGE_BUDGET = 192 * 1024;  // shared memory spent on operand stages
 constexpr int ACC_BUFS = 2;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 16;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;  // bounded waits: non-blocking polls, about a second in total, then give up
 
 enum Epilogue { EPI_SAMPLE = 0, EPI_CORR = 1 };
@@ -113,6 +117,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// u <= sigmoid(x) decided with the approximate exponential and reciprocal when u is clearly on one side, and with the
+// exact sequence otherwise: same answer as det_sigmoid always.  4e-6 is four times the largest absolute error the
+// approximate path can make (relative error of ex2.approx and rcp.approx about 2^-22 each, times p(1-p) <= 1/4, plus
+// the rounding of x*log2(e) which scales with |x| p(1-p) <= 0.23).
+__device__ __forceinline__ bool bernoulli_sigmoid(float u, float x) {
+    const float e = __expf(-fabsf(x));
+    const float q = __fdividef(1.0f, 1.0f + e);          // sigmoid(|x|)
+    const float p = x >= 0.0f ? q : 1.0f - q;
+    if (u < p - 4e-6f) return true;
+    if (u > p + 4e-6f) return false;
+    return u <= det_sigmoid(x);
+}
+
 struct GemmArgs {
     int32_t m_total, n_total, k_bytes;  // problem size; k in bytes along the contiguous dimension
     int32_t tiles_m, tiles_n;
@@ -143,9 +160,13 @@ __device__ __forceinline__ void quad_transpose(uint32_t (&x)[4], int lane) {
     if (lane & 2) { x[0] = c; x[1] = d; } else { x[2] = c; x[3] = d; }
 }
 
+template <int BN>
+__host__ __device__ constexpr int stages_for() { return STAGE_BUDGET / ((BM + BN) * BK_BYTES); }
+
 template <int EPI, int BN>
 __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
     constexpr int KIND_I8 = EPI == EPI_CORR;
+    constexpr int STAGES = stages_for<BN>();
     constexpr uint32_t A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = ACC_BUFS * BN;  // 128 or 256: a power of two >= 32
     constexpr uint32_t IDESC = KIND_I8 ? make_idesc(2, 0, BM, BN) : make_idesc(1, 1, BM, BN);
@@ -161,7 +182,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        for (int b = 0; b < ACC_BUFS; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -216,8 +237,9 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
             }
         }
     } else {
-        // ---- epilogue warps 2..5
-        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
+        // ---- epilogue warps
+        const int quarter = warp & 3;         // TMEM lanes [32*quarter, 32*quarter+32)
+        const int col_group = (warp - 2) >> 2;  // which quarter of the tile's 16-column chunks this warp finishes
         uint32_t it = 0;
         bool alive = true;
         for (int tile = blockIdx.x; tile < n_tiles && alive; tile += gridDim.x, ++it) {
@@ -228,7 +250,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
             const int row = tm * BM + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < BN / 16; ++c) {
+            for (int c = col_group; c < BN / 16; c += EPI_WARPS / 4) {
                 uint32_t acc[16];
                 tmem_ld16(taddr + c * 16, acc);
                 const int col0 = tn * BN + c * 16;
@@ -246,8 +268,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                             const int col = col0 + 4 * t + j;
                             const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
                             const float gamma = __fadd_rn(b, __uint_as_float(acc[4 * t + j]));
-                            const float p = det_sigmoid(__fmul_rn(gamma, 2.0f));
-                            if (u24(x[j]) <= p) bits |= 1u << (4 * t + j);
+                            if (bernoulli_sigmoid(u24(x[j]), __fmul_rn(gamma, 2.0f))) bits |= 1u << (4 * t + j);
                         }
                     }
                     if (row < g.m_total) {

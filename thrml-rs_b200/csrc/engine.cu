@@ -79,6 +79,7 @@ struct BlockProg {
     bool dense_on = false;
     int32_t base_kernel = 0;     // kernel used when the dense path is off or cannot serve a call
     int64_t dense_pitch = 0;     // elements per row of d_dense_w
+    int32_t dense_bn = 128;      // tile width of the update GEMM
     std::vector<float> h_dense_w;  // [n][n_src] f32, canonical weights (0 where there is no edge)
     std::vector<float> h_dense_bias;
     DevBuf d_dense_w;            // bf16 [n][dense_pitch], K-major (K = source nodes)
@@ -891,7 +892,8 @@ int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding
         if (int32_t rc = upload(bp.d_dense_w, wb.data(), wb.size() * 2, st)) return rc;
         if (int32_t rc = upload(bp.d_dense_bias, bp.h_dense_bias.data(), bp.h_dense_bias.size() * 4, st)) return rc;
         CU_TRY(cudaStreamSynchronize(st));
-        if (int32_t rc = make_operand_map(&bp.map_w, bp.d_dense_w.p, false, n_src, bp.n, bp.dense_pitch * 2, 128)) return rc;
+        bp.dense_bn = bp.n >= 2048 ? 256 : 128;  // wide output blocks take 128x256 tiles: fewer operand bytes per flop
+        if (int32_t rc = make_operand_map(&bp.map_w, bp.d_dense_w.p, false, n_src, bp.n, bp.dense_pitch * 2, bp.dense_bn)) return rc;
         bp.dense_on = true;
         bp.kernel = 3;
         p->is_dense_source[bp.dense_src] = 1;
@@ -1150,7 +1152,7 @@ static int32_t ensure_image(thrml_state* s, int32_t block, bool need_fresh) {
 extern "C++" {
 template <int EPI, int BN>
 static int32_t launch_dense(thrml_state* s, const CUtensorMap& ma, const CUtensorMap& mb, dense::GemmArgs g) {
-    constexpr size_t smem = dense::STAGES * (dense::BM + BN) * dense::BK_BYTES + 1024;
+    constexpr size_t smem = dense::stages_for<BN>() * (dense::BM + BN) * dense::BK_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         CU_TRY(cudaFuncSetAttribute(dense::k_dense_gemm<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -1186,7 +1188,11 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     g.chain_word0 = static_cast<uint32_t>(s->chain_offset >> 2);
     g.k0 = k0;
     g.k1 = k1;
-    if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g)) return rc;
+    if (bp.dense_bn == 256) {
+        if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w, g)) return rc;
+    } else if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g)) {
+        return rc;
+    }
     s->image_fresh[block] = write_image ? 1 : 0;
     return THRML_OK;
 }
@@ -1328,6 +1334,18 @@ int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const th
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
     return check_err_flag(s);
 }
+// Device-to-device copy of one block's state between two states of the same program and chain count.
+int32_t thrml_state_copy_block(thrml_state* dst, const thrml_state* src, int32_t block) {
+    if (!dst || !src) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (dst->prog != src->prog || dst->n_chains != src->n_chains) return fail(THRML_ERR_INVALID_ARG, "states must share the program and the chain count");
+    if (int32_t rc = check_block(dst, block)) return rc;
+    CU_TRY(cudaSetDevice(dst->device));
+    const BlockProg& bp = dst->prog->blocks[block];
+    CU_TRY(cudaMemcpyAsync(dst->rows(bp.sd) + bp.offset * dst->ld, src->rows(bp.sd) + bp.offset * src->ld, static_cast<size_t>(bp.n) * dst->ld, cudaMemcpyDeviceToDevice,
+                           dst->prog->ctx->stream));
+    dst->touch(block);
+    return THRML_OK;
+}
 // sample_single_block (program.rs:324-393): update one free block in place with the given block key.
 int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key) {
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
@@ -1357,7 +1375,8 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
     if (int32_t rc = ensure_err_flag(s)) return rc;
     CUtensorMap map_a, map_b;  // encoded per call: kernel parameters are copied at launch
     if (int32_t rc = make_operand_map(&map_a, s->rows(ba.sd) + ba.offset * s->ld, true, s->n_chains, ba.n, s->ld, dense::BM)) return rc;
-    if (int32_t rc = make_operand_map(&map_b, s->rows(bb.sd) + bb.offset * s->ld, true, s->n_chains, bb.n, s->ld, 64)) return rc;
+    const int bn = bb.n >= 2048 ? 256 : 64;
+    if (int32_t rc = make_operand_map(&map_b, s->rows(bb.sd) + bb.offset * s->ld, true, s->n_chains, bb.n, s->ld, bn)) return rc;
     for (int32_t blk : {block_a, block_b}) {
         const BlockProg& bp = p->blocks[blk];
         if (!s->ones[blk]) {
@@ -1376,6 +1395,7 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
     g.ones_b = s->ones[block_b]->as<int32_t>();
     g.corr_out = d_out;
     g.n_chains = static_cast<int32_t>(s->n_chains);
+    if (bn == 256) return launch_dense<dense::EPI_CORR, 256>(s, map_a, map_b, g);
     return launch_dense<dense::EPI_CORR, 64>(s, map_a, map_b, g);
 }
 int32_t thrml_pair_correlation(thrml_state* s, int32_t block_a, int32_t block_b, float* host_out) {

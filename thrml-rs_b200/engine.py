@@ -244,6 +244,9 @@ class ChainState:
         host = np.ascontiguousarray(host, dtype=np.uint8).reshape(self.n_chains, n)
         check(lib().thrml_state_upload_u8_static(self.h, C.c_int32(block), ptr(host)))
 
+    def copy_block_from(self, other, block):
+        check(lib().thrml_state_copy_block(self.h, other.h, C.c_int32(block)))
+
     def download(self, block, dtype=np.float32):
         n = self.program.block_len(block)
         out = np.zeros((self.n_chains, n), dtype=dtype)

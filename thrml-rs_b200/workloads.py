@@ -44,3 +44,22 @@ def ising_moment_arrays(model):
     row_ptr = np.concatenate([np.arange(n + 1, dtype=np.int64), n + 2 * np.arange(1, e + 1, dtype=np.int64)])
     members = np.concatenate([np.arange(n, dtype=np.int64), model["edges"].astype(np.int64).ravel()])
     return rows_per_type, row_ptr, members
+
+
+def to_bf16(x):
+    """Round f32 values to the nearest bf16 value (ties to even), returned as f32."""
+    u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def rbm_ising(n_visible=784, n_hidden=4096, seed=0x5EED0003, w_sigma=0.01, bias_sigma=0.01):
+    """Bipartite RBM-style Ising model: dense couplings N(0, w_sigma^2) held as bf16 values, biases N(0, bias_sigma^2);
+    two blocks (visible, hidden); edges (v, h) in row-major order."""
+    rng = np.random.default_rng(seed)
+    W = to_bf16(rng.normal(0.0, w_sigma, (n_visible, n_hidden)))
+    b = rng.normal(0.0, bias_sigma, n_visible + n_hidden).astype(np.float32)
+    vis = np.arange(n_visible, dtype=np.int64)
+    hid = np.arange(n_visible, n_visible + n_hidden, dtype=np.int64)
+    edges = np.stack([np.repeat(vis, n_hidden), np.tile(hid, n_visible)], axis=1)
+    return dict(n=n_visible + n_hidden, n_visible=n_visible, n_hidden=n_hidden, W=W, b=b, edges=edges, J=W.ravel().copy(), beta=1.0, blocks=[vis, hid])
