@@ -117,19 +117,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-// u <= sigmoid(x) decided with the approximate exponential and reciprocal when u is clearly on one side, and with the
-// exact sequence otherwise: same answer as det_sigmoid always.  4e-6 is four times the largest absolute error the
-// approximate path can make (relative error of ex2.approx and rcp.approx about 2^-22 each, times p(1-p) <= 1/4, plus
-// the rounding of x*log2(e) which scales with |x| p(1-p) <= 0.23).
-__device__ __forceinline__ bool bernoulli_sigmoid(float u, float x) {
-    const float e = __expf(-fabsf(x));
-    const float q = __fdividef(1.0f, 1.0f + e);          // sigmoid(|x|)
-    const float p = x >= 0.0f ? q : 1.0f - q;
-    if (u < p - 4e-6f) return true;
-    if (u > p + 4e-6f) return false;
-    return u <= det_sigmoid(x);
-}
-
 struct GemmArgs {
     int32_t m_total, n_total, k_bytes;  // problem size; k in bytes along the contiguous dimension
     int32_t tiles_m, tiles_n;
@@ -141,6 +128,7 @@ struct GemmArgs {
     __nv_bfloat16* image_out; // +-1 bf16 image [m_total rows = chains][image_pitch], or null
     int64_t image_pitch;      // elements
     uint32_t chain_word0, k0, k1;
+    int32_t* ones_out;        // [n_total] number of ones per updated node, accumulated with atomics (zeroed by the caller), or null
     // EPI_CORR
     const int32_t* ones_a;    // [m_total] number of ones per row of A
     const int32_t* ones_b;    // [n_total]
@@ -256,7 +244,8 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                 const int col0 = tn * BN + c * 16;
                 if (EPI == EPI_SAMPLE) {
                     // row = chain, columns = nodes of the updated block
-                    uint32_t bits = 0;
+                    uint32_t bits = 0, unsure = 0;
+                    uint32_t rnd[16];
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
                         const int my_col = col0 + 4 * t + (lane & 3);
@@ -264,27 +253,64 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                         uint32_t x[4] = {r.x, r.y, r.z, r.w};
                         quad_transpose(x, lane);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int col = col0 + 4 * t + j;
-                            const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
-                            const float gamma = __fadd_rn(b, __uint_as_float(acc[4 * t + j]));
-                            if (bernoulli_sigmoid(u24(x[j]), __fmul_rn(gamma, 2.0f))) bits |= 1u << (4 * t + j);
-                        }
+                        for (int j = 0; j < 4; ++j) rnd[4 * t + j] = x[j];
                     }
-                    if (row < g.m_total) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int col = col0 + j;
+                        const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
+                        const float xx = __fmul_rn(__fadd_rn(b, __uint_as_float(acc[j])), 2.0f);
+                        // approximate sigmoid first; draws within 4e-6 of it (four times its worst error) are redone exactly
+                        const float e = __expf(-fabsf(xx));
+                        const float q = __fdividef(1.0f, 1.0f + e);
+                        const float p = xx >= 0.0f ? q : 1.0f - q;
+                        const float u = u24(rnd[j]);
+                        bits |= (u < p ? 1u : 0u) << j;
+                        unsure |= (fabsf(u - p) <= 4e-6f ? 1u : 0u) << j;
+                    }
+                    if (unsure) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
-                            if (col0 + j < g.n_total) g.state_out[static_cast<int64_t>(col0 + j) * g.ld + row] = (bits >> j) & 1u;
-                        if (g.image_out) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)  // bf16 +1 = 0x3f80, -1 = 0xbf80
-                                w[j] = (((bits >> (2 * j)) & 1u) ? 0x3f80u : 0xbf80u) | ((((bits >> (2 * j + 1)) & 1u) ? 0x3f80u : 0xbf80u) << 16);
-                            uint4* dst = reinterpret_cast<uint4*>(g.image_out + static_cast<int64_t>(row) * g.image_pitch + col0);
-                            if (col0 + 16 <= g.image_pitch) {
-                                dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-                                dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                            if ((unsure >> j) & 1u) {
+                                const int col = col0 + j;
+                                const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
+                                const float xx = __fmul_rn(__fadd_rn(b, __uint_as_float(acc[j])), 2.0f);
+                                const uint32_t one = u24(rnd[j]) <= det_sigmoid(xx) ? 1u : 0u;
+                                bits = (bits & ~(1u << j)) | (one << j);
                             }
+                    }
+                    if (row >= g.m_total) bits = 0;
+                    // state bytes: lane L takes column L&15 and the 16 chains of half L>>4 of this warp's 32 rows
+                    uint32_t mine = 0;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const uint32_t m = __ballot_sync(0xffffffffu, (bits >> j) & 1u);
+                        if ((lane & 15) == j) mine = m;
+                    }
+                    {
+                        const int col = col0 + (lane & 15);
+                        const int row_base = tm * BM + quarter * 32;
+                        const uint32_t half = (mine >> (16 * (lane >> 4))) & 0xffffu;
+                        if (col < g.n_total && row_base < g.m_total) {
+                            uint4 v;
+                            v.x = ((half & 0xfu) * 0x00204081u) & 0x01010101u;
+                            v.y = (((half >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
+                            v.z = (((half >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
+                            v.w = (((half >> 12) & 0xfu) * 0x00204081u) & 0x01010101u;
+                            uint8_t* dst = g.state_out + static_cast<int64_t>(col) * g.ld + row_base + 16 * (lane >> 4);
+                            if (row_base + 16 * (lane >> 4) < g.ld) *reinterpret_cast<uint4*>(dst) = v;  // ld is a multiple of 16
+                            if (g.ones_out && (lane >> 4) == 0) atomicAdd(g.ones_out + col, __popc(mine));
+                        }
+                    }
+                    if (row < g.m_total && g.image_out) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)  // bf16 +1 = 0x3f80, -1 = 0xbf80
+                            w[j] = (((bits >> (2 * j)) & 1u) ? 0x3f80u : 0xbf80u) | ((((bits >> (2 * j + 1)) & 1u) ? 0x3f80u : 0xbf80u) << 16);
+                        uint4* dst = reinterpret_cast<uint4*>(g.image_out + static_cast<int64_t>(row) * g.image_pitch + col0);
+                        if (col0 + 16 <= g.image_pitch) {
+                            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
                         }
                     }
                 } else {

@@ -111,12 +111,12 @@ struct thrml_state {
     DevBuf scratch;     // transposes, injected noise, debug fields
     // dense path: +-1 bf16 image [chain][node] of source blocks, tensor maps, per-row one counts, error flag
     std::vector<std::unique_ptr<DevBuf>> image;
-    std::vector<uint8_t> image_fresh;
+    std::vector<uint8_t> image_fresh, ones_fresh;
     std::vector<CUtensorMap> map_image;
     std::vector<std::unique_ptr<DevBuf>> ones;
     DevBuf d_err, d_corr;
     int64_t image_rows = 0;
-    void touch(int32_t block) { if (!image_fresh.empty()) image_fresh[block] = 0; }
+    void touch(int32_t block) { if (!image_fresh.empty()) { image_fresh[block] = 0; ones_fresh[block] = 0; } }
     uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
 };
 
@@ -934,6 +934,7 @@ int32_t thrml_state_create(thrml_program* p, int64_t n_chains, int64_t chain_off
     s->image.resize(nb_all);
     s->ones.resize(nb_all);
     s->image_fresh.assign(nb_all, 0);
+    s->ones_fresh.assign(nb_all, 0);
     s->map_image.resize(nb_all);
     s->image_rows = (n_chains + 127) / 128 * 128;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
@@ -1188,12 +1189,19 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     g.chain_word0 = static_cast<uint32_t>(s->chain_offset >> 2);
     g.k0 = k0;
     g.k1 = k1;
+    if (!s->ones[block]) {
+        s->ones[block].reset(new DevBuf());
+        if (int32_t rc = s->ones[block]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+    }
+    CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, p->ctx->stream));
+    g.ones_out = s->ones[block]->as<int32_t>();
     if (bp.dense_bn == 256) {
         if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w, g)) return rc;
     } else if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g)) {
         return rc;
     }
     s->image_fresh[block] = write_image ? 1 : 0;
+    s->ones_fresh[block] = 1;
     return THRML_OK;
 }
 
@@ -1383,9 +1391,12 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
             s->ones[blk].reset(new DevBuf());
             if (int32_t rc = s->ones[blk]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
         }
-        dense::k_row_ones<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
-                                                                                         s->ones[blk]->as<int32_t>());
-        CU_TRY(cudaGetLastError());
+        if (!s->ones_fresh[blk]) {
+            dense::k_row_ones<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
+                                                                                             s->ones[blk]->as<int32_t>());
+            CU_TRY(cudaGetLastError());
+            s->ones_fresh[blk] = 1;
+        }
     }
     dense::GemmArgs g{};
     g.m_total = static_cast<int32_t>(ba.n);
