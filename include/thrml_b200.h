@@ -252,6 +252,40 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
                                       int64_t steps_per_sample, thrml_moments* moments, const int32_t* obs_blocks,
                                       int32_t n_obs_blocks, uint8_t* obs_out, const thrml_noise* inj);
 
+/* ------------------------------------------------------------------------------------------------
+ * Implicit lattice: a height x width periodic nearest-neighbour Ising lattice with one coupling and one bias, sampled
+ * with the two checkerboard blocks, state bit-packed (32 spins per word, chains innermost), held as a stripe of rows
+ * [row_begin, row_begin + n_rows) plus one halo row above and below.  It samples exactly what IsingSamplingProgram
+ * (crates/thrml-models/src/ising.rs:342-388) would on make_nearest_neighbor_lattice's torus
+ * (crates/thrml-models/src/graph_utils.rs:177-243) with blocks [(row+col) even, (row+col) odd] — same fields, same
+ * noise, same states — for lattices whose per-node tables (program.rs:101-134) could never be built.
+ * One sweep (sampling.rs:28-63): keys = key.split(2); update colour 0 with keys[0], refresh colour 0's halo rows in the
+ * neighbouring stripes, update colour 1 with keys[1], refresh colour 1's halos.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct thrml_lattice thrml_lattice;
+int32_t thrml_lattice_create(thrml_ctx* ctx, int64_t height, int64_t width, int64_t row_begin, int64_t n_rows, float coupling,
+                             float bias, float beta, int64_t n_chains, int64_t chain_offset, thrml_lattice** out);
+void thrml_lattice_destroy(thrml_lattice* lat);
+/* Uniform random spins (asynchronous). */
+int32_t thrml_lattice_randomize(thrml_lattice* lat, uint64_t key);
+/* Stripe state as bytes 0/1, host layout [chain][stripe row][column]. */
+int32_t thrml_lattice_upload(thrml_lattice* lat, const uint8_t* host);
+int32_t thrml_lattice_download(thrml_lattice* lat, uint8_t* host);
+/* Update one colour of stripe rows [row_begin, row_end) with the block key (asynchronous).  The other colour's halo
+ * rows must be current. */
+int32_t thrml_lattice_update(thrml_lattice* lat, int32_t colour, uint64_t block_key, int64_t row_begin, int64_t row_end);
+/* Device pointers of the rows a stripe sends (its first and last row of `colour`) and of its two halo rows, and their
+ * size: what a multi-process host hands to its point-to-point exchange. */
+int32_t thrml_lattice_halo_info(thrml_lattice* lat, int32_t colour, void** send_top, void** send_bottom, void** recv_top,
+                                void** recv_bottom, int64_t* row_bytes);
+/* Halo refresh between stripes of one process (device-to-device copy), and for a stripe that holds the whole lattice. */
+int32_t thrml_lattice_copy_halo(thrml_lattice* dst, int32_t which_dst, const thrml_lattice* src, int32_t which_src, int32_t colour);
+int32_t thrml_lattice_wrap_halo(thrml_lattice* lat, int32_t colour);
+/* sums_out[2][n_chains] (host, int64): per chain the sum of spins and the sum of s_i s_j over the bonds this stripe owns
+ * (each bond is owned by its colour-0 end), from which magnetisation and energy follow. */
+int32_t thrml_lattice_observe(thrml_lattice* lat, int64_t* sums_out);
+int32_t thrml_lattice_synchronize(thrml_lattice* lat);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,73 @@
+"""Implicit bit-packed lattice engine against the oracle's explicit Ising program on the same torus: same states bit for
+bit, whole or in stripes; observables against numpy."""
+import numpy as np
+import pytest
+
+import models as M
+
+pytestmark = pytest.mark.gpu
+
+
+def torus_model(H, W, J, b, beta):
+    idx = np.arange(H * W).reshape(H, W)
+    pairs = np.concatenate([np.stack([idx.ravel(), np.roll(idx, -1, axis=1).ravel()], 1), np.stack([idx.ravel(), np.roll(idx, -1, axis=0).ravel()], 1)])
+    e = np.unique(np.sort(pairs, axis=1), axis=0)  # ascending (min, max), duplicates erased: make_nearest_neighbor_lattice's edge set
+    colour = (np.add.outer(np.arange(H), np.arange(W)) % 2).ravel()
+    blocks = [np.flatnonzero(colour == c) for c in (0, 1)]
+    n = H * W
+    desc = dict(kinds=np.zeros(n, np.int32), free=[(blocks[0], 0), (blocks[1], 1)],
+                ops=[("add_ising", np.arange(n), np.full(n, b, np.float32), e, np.full(len(e), J, np.float32), beta)])
+    return desc, blocks, e
+
+
+@pytest.mark.parametrize("H,W,chains,stripes", [(8, 64, 16, 1), (6, 128, 4, 1), (8, 64, 16, 2), (12, 64, 8, 3), (4, 192, 32, 2)])
+def test_lattice_matches_explicit_program(T, O, H, W, chains, stripes):
+    from thrml_rs_b200 import lattice
+    J, b, beta = 0.4407, 0.07, 0.9
+    desc, blocks, edges = torus_model(H, W, J, b, beta)
+    om = M.fill(O.Model(desc["kinds"]), desc)
+    os_ = O.State(om, chains)
+    rng = np.random.default_rng(H * W + chains)
+    spins = rng.integers(0, 2, (chains, H, W)).astype(np.uint8)
+    flat = spins.reshape(chains, H * W)
+    for bi, blk in enumerate(blocks):
+        os_.set_block(bi, flat[:, blk].astype(np.float32))
+    lat = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=stripes)
+    lat.upload(spins)
+    assert np.array_equal(lat.download(), spins)
+    for step, n_iters in enumerate([1, 3]):
+        lat.run_blocks(40 + step, n_iters)
+        os_.run_blocks(40 + step, n_iters)
+        got = lat.download().reshape(chains, H * W)
+        for bi, blk in enumerate(blocks):
+            assert np.array_equal(got[:, blk], os_.get_block(bi)), (step, bi)
+    # observables
+    s = 2.0 * lat.download().astype(np.int64) - 1
+    want_m = s.sum(axis=(1, 2))
+    want_b = (s * np.roll(s, -1, axis=1)).sum(axis=(1, 2)) + (s * np.roll(s, -1, axis=2)).sum(axis=(1, 2))
+    obs = lat.observe()
+    assert np.array_equal(obs[0], want_m) and np.array_equal(obs[1], want_b)
+
+
+def test_lattice_randomize_matches_explicit_randomize(T, O):
+    from thrml_rs_b200 import lattice
+    H, W, chains = 4, 64, 8
+    desc, blocks, _ = torus_model(H, W, 0.3, 0.0, 1.0)
+    prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
+    st = T.ChainState(prog, chains)
+    st.randomize(5)
+    lat = lattice.StripedLattice(H, W, 0.3, 0.0, 1.0, chains)
+    lat.randomize(5)
+    got = lat.download().reshape(chains, H * W)
+    for bi, blk in enumerate(blocks):
+        assert np.array_equal(got[:, blk], st.download(bi, np.uint8))
+
+
+def test_lattice_argument_checks(T):
+    from thrml_rs_b200 import lattice
+    with pytest.raises(T.ThrmlError, match="multiple of 64"):
+        lattice.LatticeStripe(8, 60, 0, 8, 0.4, 0.0, 1.0, 16)
+    with pytest.raises(T.ThrmlError, match="n_chains"):
+        lattice.LatticeStripe(8, 64, 0, 8, 0.4, 0.0, 1.0, 6)
+    with pytest.raises(T.ThrmlError, match="out of range"):
+        lattice.LatticeStripe(8, 64, 4, 8, 0.4, 0.0, 1.0, 16)

@@ -69,6 +69,17 @@ _SIGNATURES = {
     "thrml_moments_device_buffer": (C.c_int32, [_P, _P, _P]),
     "thrml_moments_add_observations": (C.c_int32, [_P, C.c_int64]),
     "thrml_marginals_create": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P]),
+    "thrml_lattice_create": (C.c_int32, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int64, C.c_int64, _P]),
+    "thrml_lattice_destroy": (None, [_P]),
+    "thrml_lattice_randomize": (C.c_int32, [_P, C.c_uint64]),
+    "thrml_lattice_upload": (C.c_int32, [_P, _P]),
+    "thrml_lattice_download": (C.c_int32, [_P, _P]),
+    "thrml_lattice_update": (C.c_int32, [_P, C.c_int32, C.c_uint64, C.c_int64, C.c_int64]),
+    "thrml_lattice_halo_info": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P]),
+    "thrml_lattice_copy_halo": (C.c_int32, [_P, C.c_int32, _P, C.c_int32, C.c_int32]),
+    "thrml_lattice_wrap_halo": (C.c_int32, [_P, C.c_int32]),
+    "thrml_lattice_observe": (C.c_int32, [_P, _P]),
+    "thrml_lattice_synchronize": (C.c_int32, [_P]),
     "thrml_sample_with_observation": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, _P, _P, C.c_int32, _P, _P]),
 }
 

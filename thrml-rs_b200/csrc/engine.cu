@@ -15,11 +15,7 @@
 
 using namespace thrml;
 
-#define CU_TRY(expr)                                                                                               \
-    do {                                                                                                           \
-        cudaError_t e__ = (expr);                                                                                  \
-        if (e__ != cudaSuccess) return fail(THRML_ERR_CUDA, std::string(#expr) + ": " + cudaGetErrorString(e__)); \
-    } while (0)
+#include "ctx.h"
 
 constexpr int MAX_TAILS = 8;
 constexpr int LUT_BITS = 8;              // a threshold table covers at most 8 neighbour spins
@@ -50,12 +46,6 @@ struct DevBuf {
         return THRML_OK;
     }
     template <class T> T* as() const { return static_cast<T*>(p); }
-};
-
-struct thrml_ctx {
-    int device = 0;
-    cudaStream_t stream = nullptr;
-    int sm_count = 148;
 };
 
 struct BlockProg {

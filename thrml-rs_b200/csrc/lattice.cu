@@ -1,0 +1,364 @@
+// Implicit 2-D periodic Ising lattice with bit-packed state, for lattices too large for per-node tables
+// (32768 x 32768 spins and beyond), sharded by row stripes.
+//
+// Semantics = IsingSamplingProgram (crates/thrml-models/src/ising.rs:342-388) on the nearest-neighbour torus of
+// make_nearest_neighbor_lattice (crates/thrml-models/src/graph_utils.rs:177-243) with one coupling J, one bias b and the two
+// checkerboard blocks [(row+col) even, (row+col) odd]; the field of a spin is accumulated in the reference's slot order
+// (edges where the node is the smaller endpoint first, then those where it is the larger, each in (min,max) edge order)
+// so the sampled states equal those of the explicit program bit for bit.  That order differs at the lattice seams, hence
+// one 16-entry threshold table per seam class.
+//
+// Layout: plane[colour][stripe row + 1][word][chain] u32, 32 spins of one colour and one row per word, chains innermost;
+// stripe rows 0 and n_rows+1 are halo rows holding the neighbouring stripes' boundary rows.
+#include <algorithm>
+#include <memory>
+#include <vector>
+
+#include "ctx.h"
+#include "device_math.cuh"
+
+using namespace thrml;
+
+namespace {
+
+// neighbour bit positions inside a 4-bit configuration
+constexpr int NB_UP = 0, NB_LEFT = 1, NB_RIGHT = 2, NB_DOWN = 3;
+
+struct LatArgs {
+    uint32_t* own;          // plane of the colour being updated (with halo rows)
+    const uint32_t* other;  // plane of the other colour
+    const uint32_t* lut;    // [9][16] thresholds
+    int64_t H, W;           // whole lattice
+    int64_t row0;           // first global row of the stripe
+    int32_t n_rows, words, chains, colour;
+    uint32_t chain_word0, k0, k1;
+};
+
+// One thread = one word (32 spins of one row and colour) x four chains.
+__global__ void __launch_bounds__(128) k_lattice_update(LatArgs a, int32_t row_begin, int32_t row_end) {
+    __shared__ uint32_t s_lut[9 * 16];
+    for (int i = threadIdx.x; i < 9 * 16; i += blockDim.x) s_lut[i] = a.lut[i];
+    __syncthreads();
+    const int quads = a.chains >> 2;
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t per_row = static_cast<int64_t>(a.words) * quads;
+    const int64_t total = static_cast<int64_t>(row_end - row_begin) * per_row;
+    if (gid >= total) return;
+    const int r = row_begin + static_cast<int>(gid / per_row);  // stripe row 0..n_rows-1
+    const int w = static_cast<int>((gid % per_row) / quads);
+    const int q = static_cast<int>(gid % quads);
+    const int64_t gi = a.row0 + r;                               // global row
+    const int p = static_cast<int>((gi + a.colour) & 1);         // column parity of this colour in this row: col = 2*jj + p
+    auto at = [&](const uint32_t* plane, int srow, int word) {
+        return *reinterpret_cast<const uint4*>(plane + (static_cast<int64_t>(srow) * a.words + word) * a.chains + 4 * q);
+    };
+    const uint4 up = at(a.other, r, w), down = at(a.other, r + 2, w), same = at(a.other, r + 1, w);
+    const int wadj = p == 0 ? (w == 0 ? a.words - 1 : w - 1) : (w == a.words - 1 ? 0 : w + 1);
+    const uint4 adj = at(a.other, r + 1, wadj);
+    // p == 0: left neighbour is jj-1 (shifted in from the previous word), right neighbour is jj; p == 1: left is jj, right is jj+1
+    uint32_t U[4] = {up.x, up.y, up.z, up.w}, D[4] = {down.x, down.y, down.z, down.w}, L[4], R[4];
+    const uint32_t S[4] = {same.x, same.y, same.z, same.w}, A[4] = {adj.x, adj.y, adj.z, adj.w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        if (p == 0) { L[c] = (S[c] << 1) | (A[c] >> 31); R[c] = S[c]; }
+        else { L[c] = S[c]; R[c] = (S[c] >> 1) | (A[c] << 31); }
+    }
+    const int row_cls = gi == 0 ? 1 : (gi == a.H - 1 ? 2 : 0);
+    const bool first_col = p == 0 && w == 0, last_col = p == 1 && w == a.words - 1;
+    const uint32_t node_base = static_cast<uint32_t>(gi * (a.W >> 1) + 32 * static_cast<int64_t>(w));
+    uint32_t out[4] = {0, 0, 0, 0};
+#pragma unroll 4
+    for (int k = 0; k < 32; ++k) {
+        const U4 rr = philox4x32_10(node_base + k, a.chain_word0 + q, 0u, TAG_SPIN, a.k0, a.k1);
+        const uint32_t rnd[4] = {rr.x, rr.y, rr.z, rr.w};
+        const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
+        const uint32_t* T = s_lut + (row_cls * 3 + col_cls) * 16;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t cfg = ((U[c] >> k) & 1u) << NB_UP | ((L[c] >> k) & 1u) << NB_LEFT | ((R[c] >> k) & 1u) << NB_RIGHT | ((D[c] >> k) & 1u) << NB_DOWN;
+            out[c] |= (rnd[c] <= T[cfg] ? 1u : 0u) << k;
+        }
+    }
+    *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// Threshold tables: gamma = (0 + b) + (((0 + t1) + t2) + t3) + t4 with the neighbours taken in `order`, exactly as the
+// explicit program accumulates them; threshold as in the table kernel of the explicit engine.
+__global__ void k_lattice_build_lut(float J, float b, const int32_t* order /*[9][4]*/, uint32_t* lut) {
+    const int cls = threadIdx.x >> 4, cfg = threadIdx.x & 15;
+    if (cls >= 9) return;
+    float gs = 0.0f;
+    for (int s = 0; s < 4; ++s) {
+        const int bit = order[cls * 4 + s];
+        gs = __fadd_rn(gs, __fmul_rn(J, ((cfg >> bit) & 1) ? 1.0f : -1.0f));
+    }
+    const float gamma = __fadd_rn(__fadd_rn(0.0f, b), gs);
+    const float pr = det_sigmoid(__fmul_rn(gamma, 2.0f));
+    const uint32_t fl = static_cast<uint32_t>(__fmul_rn(pr, 16777216.0f));
+    lut[threadIdx.x] = fl >= 16777216u ? 0xffffffffu : ((fl << 8) | 0xffu);
+}
+
+// Uniform random start, same stream as thrml_state_randomize on the explicit program (spin = top bit of the word).
+__global__ void __launch_bounds__(128) k_lattice_randomize(uint32_t* plane, int64_t W, int64_t row0, int32_t n_rows, int32_t words, int32_t chains,
+                                                          uint32_t chain_word0, uint32_t k0, uint32_t k1) {
+    const int quads = chains >> 2;
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t per_row = static_cast<int64_t>(words) * quads;
+    if (gid >= static_cast<int64_t>(n_rows) * per_row) return;
+    const int r = static_cast<int>(gid / per_row), w = static_cast<int>((gid % per_row) / quads), q = static_cast<int>(gid % quads);
+    const uint32_t node_base = static_cast<uint32_t>((row0 + r) * (W >> 1) + 32 * static_cast<int64_t>(w));
+    uint32_t out[4] = {0, 0, 0, 0};
+    for (int k = 0; k < 32; ++k) {
+        const U4 rr = philox4x32_10(node_base + k, chain_word0 + q, 0u, TAG_RAND, k0, k1);
+        out[0] |= (rr.x >> 31) << k;
+        out[1] |= (rr.y >> 31) << k;
+        out[2] |= (rr.z >> 31) << k;
+        out[3] |= (rr.w >> 31) << k;
+    }
+    *reinterpret_cast<uint4*>(plane + (static_cast<int64_t>(r + 1) * words + w) * chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// Per chain: sum of spins (both colours) and sum over bonds of s_i s_j, each bond counted from its colour-0 end.
+__global__ void __launch_bounds__(256) k_lattice_observe(const uint32_t* p0, const uint32_t* p1, int64_t row0, int32_t n_rows, int32_t words, int32_t chains,
+                                                        long long* out /*[2][chains]*/) {
+    const int chain = threadIdx.x % chains;  // blockDim.x is a multiple of chains
+    const int lanes_per_chain = blockDim.x / chains;
+    const int64_t cells = static_cast<int64_t>(n_rows) * words;
+    long long spins = 0, bonds = 0;
+    for (int64_t cell = static_cast<int64_t>(blockIdx.x) * lanes_per_chain + threadIdx.x / chains; cell < cells; cell += static_cast<int64_t>(gridDim.x) * lanes_per_chain) {
+        const int r = static_cast<int>(cell / words), w = static_cast<int>(cell % words);
+        const int p = static_cast<int>((row0 + r) & 1);  // colour 0: col = 2*jj + p
+        auto at = [&](const uint32_t* plane, int srow, int word) { return plane[(static_cast<int64_t>(srow) * words + word) * chains + chain]; };
+        const uint32_t s0 = at(p0, r + 1, w), s1 = at(p1, r + 1, w);
+        spins += 2 * (__popc(s0) + __popc(s1)) - 64;
+        const int wadj = p == 0 ? (w == 0 ? words - 1 : w - 1) : (w == words - 1 ? 0 : w + 1);
+        const uint32_t adj = at(p1, r + 1, wadj);
+        const uint32_t left = p == 0 ? ((s1 << 1) | (adj >> 31)) : s1, right = p == 0 ? s1 : ((s1 >> 1) | (adj << 31));
+        const int agree = __popc(~(s0 ^ at(p1, r, w))) + __popc(~(s0 ^ at(p1, r + 2, w))) + __popc(~(s0 ^ left)) + __popc(~(s0 ^ right));
+        bonds += 2 * agree - 128;
+    }
+    atomicAdd(reinterpret_cast<unsigned long long*>(out + chain), static_cast<unsigned long long>(spins));
+    atomicAdd(reinterpret_cast<unsigned long long*>(out + chains + chain), static_cast<unsigned long long>(bonds));
+}
+
+// host layout [chain][row][col] bytes (0/1) <-> bit planes, one thread per (row, word, chain)
+__global__ void k_lattice_pack(const uint8_t* host_order, uint32_t* p0, uint32_t* p1, int64_t W, int64_t row0, int32_t n_rows, int32_t words, int32_t chains) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= static_cast<int64_t>(n_rows) * words * chains) return;
+    const int chain = static_cast<int>(gid % chains), w = static_cast<int>((gid / chains) % words), r = static_cast<int>(gid / (static_cast<int64_t>(chains) * words));
+    const uint8_t* src = host_order + (static_cast<int64_t>(chain) * n_rows + r) * W;
+    for (int colour = 0; colour < 2; ++colour) {
+        const int p = static_cast<int>((row0 + r + colour) & 1);
+        uint32_t word = 0;
+        for (int k = 0; k < 32; ++k) word |= static_cast<uint32_t>(src[2 * (32 * w + k) + p] & 1u) << k;
+        (colour ? p1 : p0)[(static_cast<int64_t>(r + 1) * words + w) * chains + chain] = word;
+    }
+}
+__global__ void k_lattice_unpack(const uint32_t* p0, const uint32_t* p1, uint8_t* host_order, int64_t W, int64_t row0, int32_t n_rows, int32_t words, int32_t chains) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= static_cast<int64_t>(n_rows) * words * chains) return;
+    const int chain = static_cast<int>(gid % chains), w = static_cast<int>((gid / chains) % words), r = static_cast<int>(gid / (static_cast<int64_t>(chains) * words));
+    uint8_t* dst = host_order + (static_cast<int64_t>(chain) * n_rows + r) * W;
+    for (int colour = 0; colour < 2; ++colour) {
+        const int p = static_cast<int>((row0 + r + colour) & 1);
+        const uint32_t word = (colour ? p1 : p0)[(static_cast<int64_t>(r + 1) * words + w) * chains + chain];
+        for (int k = 0; k < 32; ++k) dst[2 * (32 * w + k) + p] = (word >> k) & 1u;
+    }
+}
+
+struct Buf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    ~Buf() { if (p) cudaFree(p); }
+};
+
+}  // namespace
+
+struct thrml_lattice {
+    thrml_ctx* ctx = nullptr;
+    int device = 0;
+    int64_t H = 0, W = 0, row0 = 0, n_rows = 0, n_chains = 0, chain_offset = 0;
+    int32_t words = 0;
+    Buf plane[2], lut, order, obs, scratch;
+    size_t row_bytes = 0;  // one row of one colour
+    uint32_t* p(int c) const { return static_cast<uint32_t*>(plane[c].p); }
+};
+
+static int32_t lat_alloc(Buf& b, size_t bytes) {
+    cudaError_t e = cudaMalloc(&b.p, bytes);
+    if (e != cudaSuccess) { b.p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
+    b.bytes = bytes;
+    return THRML_OK;
+}
+
+extern "C" {
+
+int32_t thrml_lattice_create(thrml_ctx* ctx, int64_t height, int64_t width, int64_t row_begin, int64_t n_rows, float coupling, float bias, float beta,
+                             int64_t n_chains, int64_t chain_offset, thrml_lattice** out) {
+    if (!ctx || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (height < 4 || (height & 1) || width < 64 || (width & 63)) return fail(THRML_ERR_INVALID_ARG, "lattice height must be even and >= 4, width a multiple of 64");
+    if (row_begin < 0 || n_rows < 1 || row_begin + n_rows > height) return fail(THRML_ERR_INVALID_ARG, "stripe rows out of range");
+    if (n_rows < 2 && n_rows != height) return fail(THRML_ERR_INVALID_ARG, "a stripe needs at least two rows");
+    if (n_chains < 4 || (n_chains & 3) || n_chains > 256 || (256 % n_chains) != 0) return fail(THRML_ERR_INVALID_ARG, "n_chains must be 4, 8, 16, 32, 64, 128 or 256");
+    if (chain_offset < 0 || (chain_offset & 3)) return fail(THRML_ERR_INVALID_ARG, "chain_offset must be a non-negative multiple of 4");
+    if (height * (width / 2) > (int64_t(1) << 32)) return fail(THRML_ERR_UNSUPPORTED, "more than 2^32 spins per colour");
+    CU_TRY(cudaSetDevice(ctx->device));
+    auto L = std::make_unique<thrml_lattice>();
+    L->ctx = ctx;
+    L->device = ctx->device;
+    L->H = height; L->W = width; L->row0 = row_begin; L->n_rows = n_rows; L->n_chains = n_chains; L->chain_offset = chain_offset;
+    L->words = static_cast<int32_t>(width / 64);
+    L->row_bytes = static_cast<size_t>(L->words) * n_chains * 4;
+    for (int c = 0; c < 2; ++c) {
+        if (int32_t rc = lat_alloc(L->plane[c], L->row_bytes * (n_rows + 2))) return rc;
+        CU_TRY(cudaMemsetAsync(L->plane[c].p, 0, L->plane[c].bytes, ctx->stream));
+    }
+    if (int32_t rc = lat_alloc(L->lut, 9 * 16 * 4)) return rc;
+    if (int32_t rc = lat_alloc(L->order, 9 * 4 * 4)) return rc;
+    if (int32_t rc = lat_alloc(L->obs, 2 * n_chains * 8)) return rc;
+    // canonical slot order per seam class: partners with a larger node index first (ascending), then the smaller ones
+    // (ascending) — the order in which BlockSamplingProgram::new lists a node's edge rows (program.rs:101-134).
+    std::vector<int32_t> order(9 * 4);
+    for (int rc = 0; rc < 3; ++rc)
+        for (int cc = 0; cc < 3; ++cc) {
+            const int64_t i = rc == 1 ? 0 : (rc == 2 ? height - 1 : 1), j = cc == 1 ? 0 : (cc == 2 ? width - 1 : 1);
+            const int64_t idx = i * width + j;
+            std::pair<int64_t, int> nb[4] = {{((i + height - 1) % height) * width + j, NB_UP}, {i * width + (j + width - 1) % width, NB_LEFT},
+                                             {i * width + (j + 1) % width, NB_RIGHT}, {((i + 1) % height) * width + j, NB_DOWN}};
+            std::sort(nb, nb + 4);
+            int s = 0;
+            for (auto& n : nb) if (n.first > idx) order[(rc * 3 + cc) * 4 + s++] = n.second;
+            for (auto& n : nb) if (n.first < idx) order[(rc * 3 + cc) * 4 + s++] = n.second;
+        }
+    CU_TRY(cudaMemcpyAsync(L->order.p, order.data(), order.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
+    k_lattice_build_lut<<<1, 9 * 16, 0, ctx->stream>>>(beta * coupling, beta * bias, static_cast<const int32_t*>(L->order.p), static_cast<uint32_t*>(L->lut.p));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(ctx->stream));
+    *out = L.release();
+    return THRML_OK;
+}
+void thrml_lattice_destroy(thrml_lattice* L) {
+    if (!L) return;
+    cudaSetDevice(L->device);
+    cudaDeviceSynchronize();
+    delete L;
+}
+
+int32_t thrml_lattice_randomize(thrml_lattice* L, uint64_t key) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(L->device));
+    uint64_t keys[2];
+    rng_split(key, 2, keys);
+    const int64_t threads = L->n_rows * L->words * (L->n_chains / 4);
+    for (int c = 0; c < 2; ++c) {
+        k_lattice_randomize<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(L->p(c), L->W, L->row0, static_cast<int32_t>(L->n_rows), L->words,
+                                                                                                    static_cast<int32_t>(L->n_chains), static_cast<uint32_t>(L->chain_offset >> 2),
+                                                                                                    static_cast<uint32_t>(keys[c]), static_cast<uint32_t>(keys[c] >> 32));
+        CU_TRY(cudaGetLastError());
+    }
+    return THRML_OK;
+}
+
+static int32_t lat_scratch(thrml_lattice* L, size_t bytes) {
+    if (L->scratch.bytes >= bytes) return THRML_OK;
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    if (L->scratch.p) { cudaFree(L->scratch.p); L->scratch.p = nullptr; L->scratch.bytes = 0; }
+    return lat_alloc(L->scratch, bytes);
+}
+int32_t thrml_lattice_upload(thrml_lattice* L, const uint8_t* host) {
+    if (!L || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(L->device));
+    const size_t bytes = static_cast<size_t>(L->n_chains) * L->n_rows * L->W;
+    if (int32_t rc = lat_scratch(L, bytes)) return rc;
+    CU_TRY(cudaMemcpyAsync(L->scratch.p, host, bytes, cudaMemcpyHostToDevice, L->ctx->stream));
+    const int64_t threads = L->n_rows * L->words * L->n_chains;
+    k_lattice_pack<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, L->ctx->stream>>>(static_cast<const uint8_t*>(L->scratch.p), L->p(0), L->p(1), L->W, L->row0,
+                                                                                           static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_lattice_download(thrml_lattice* L, uint8_t* host) {
+    if (!L || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(L->device));
+    const size_t bytes = static_cast<size_t>(L->n_chains) * L->n_rows * L->W;
+    if (int32_t rc = lat_scratch(L, bytes)) return rc;
+    const int64_t threads = L->n_rows * L->words * L->n_chains;
+    k_lattice_unpack<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), static_cast<uint8_t*>(L->scratch.p), L->W, L->row0,
+                                                                                             static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(host, L->scratch.p, bytes, cudaMemcpyDeviceToHost, L->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+
+int32_t thrml_lattice_halo_info(thrml_lattice* L, int32_t colour, void** send_top, void** send_bottom, void** recv_top, void** recv_bottom, int64_t* row_bytes) {
+    if (!L || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad halo query");
+    uint8_t* base = static_cast<uint8_t*>(L->plane[colour].p);
+    if (send_top) *send_top = base + L->row_bytes;                       // first stripe row
+    if (send_bottom) *send_bottom = base + L->row_bytes * L->n_rows;     // last stripe row
+    if (recv_top) *recv_top = base;                                      // halo above the stripe
+    if (recv_bottom) *recv_bottom = base + L->row_bytes * (L->n_rows + 1);
+    if (row_bytes) *row_bytes = static_cast<int64_t>(L->row_bytes);
+    return THRML_OK;
+}
+// A stripe that holds the whole lattice is its own neighbour: wrap its boundary rows into its halo rows.
+int32_t thrml_lattice_wrap_halo(thrml_lattice* L, int32_t colour) {
+    if (!L || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad colour");
+    if (L->n_rows != L->H) return fail(THRML_ERR_INVALID_ARG, "only a stripe that holds the whole lattice wraps onto itself");
+    CU_TRY(cudaSetDevice(L->device));
+    uint8_t* base = static_cast<uint8_t*>(L->plane[colour].p);
+    CU_TRY(cudaMemcpyAsync(base, base + L->row_bytes * L->n_rows, L->row_bytes, cudaMemcpyDeviceToDevice, L->ctx->stream));
+    CU_TRY(cudaMemcpyAsync(base + L->row_bytes * (L->n_rows + 1), base + L->row_bytes, L->row_bytes, cudaMemcpyDeviceToDevice, L->ctx->stream));
+    return THRML_OK;
+}
+// Update one colour of stripe rows [row_begin, row_end) (stripe-relative).  The other colour's halo rows must hold the
+// neighbouring stripes' current boundary rows.  Asynchronous on the context's stream.
+int32_t thrml_lattice_update(thrml_lattice* L, int32_t colour, uint64_t block_key, int64_t row_begin, int64_t row_end) {
+    if (!L || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad colour");
+    if (row_begin < 0 || row_end > L->n_rows || row_begin > row_end) return fail(THRML_ERR_INVALID_ARG, "row range out of the stripe");
+    if (row_begin == row_end) return THRML_OK;
+    CU_TRY(cudaSetDevice(L->device));
+    LatArgs a{L->p(colour), L->p(1 - colour), static_cast<const uint32_t*>(L->lut.p), L->H, L->W, L->row0, static_cast<int32_t>(L->n_rows), L->words,
+              static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
+    const int64_t threads = (row_end - row_begin) * L->words * (L->n_chains / 4);
+    k_lattice_update<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(a, static_cast<int32_t>(row_begin), static_cast<int32_t>(row_end));
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
+// Per chain: sum of spins and sum of bond products over this stripe (bonds counted from their colour-0 end, so stripes
+// add up without double counting).  Both colours' halo rows must be current.  sums_out[2][n_chains] on the host.
+int32_t thrml_lattice_observe(thrml_lattice* L, int64_t* sums_out) {
+    if (!L || !sums_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(L->device));
+    CU_TRY(cudaMemsetAsync(L->obs.p, 0, L->obs.bytes, L->ctx->stream));
+    const int64_t cells = L->n_rows * L->words;
+    const int ctas = static_cast<int>(std::min<int64_t>((cells * L->n_chains + 255) / 256, 4096));
+    k_lattice_observe<<<ctas, 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), L->row0, static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains),
+                                                        static_cast<long long*>(L->obs.p));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(sums_out, L->obs.p, L->obs.bytes, cudaMemcpyDeviceToHost, L->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+// Copy a boundary row of `src` (which_src: 0 = its first stripe row, 1 = its last) into a halo row of `dst` (which_dst:
+// 0 = the halo above its stripe, 1 = the halo below), for one colour; device-to-device on dst's stream.  Both stripes
+// must belong to lattices of the same width and chain count.  This is the halo exchange of stripes held by one process;
+// stripes held by different processes exchange the same rows through the pointers of thrml_lattice_halo_info.
+int32_t thrml_lattice_copy_halo(thrml_lattice* dst, int32_t which_dst, const thrml_lattice* src, int32_t which_src, int32_t colour) {
+    if (!dst || !src || colour < 0 || colour > 1 || which_dst < 0 || which_dst > 1 || which_src < 0 || which_src > 1) return fail(THRML_ERR_INVALID_ARG, "bad halo copy");
+    if (dst->row_bytes != src->row_bytes) return fail(THRML_ERR_INVALID_ARG, "stripes differ in width or chain count");
+    CU_TRY(cudaSetDevice(dst->device));
+    uint8_t* d = static_cast<uint8_t*>(dst->plane[colour].p) + (which_dst ? dst->row_bytes * (dst->n_rows + 1) : 0);
+    const uint8_t* s_ = static_cast<const uint8_t*>(src->plane[colour].p) + (which_src ? src->row_bytes * src->n_rows : src->row_bytes);
+    CU_TRY(cudaMemcpyAsync(d, s_, dst->row_bytes, cudaMemcpyDeviceToDevice, dst->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_lattice_synchronize(thrml_lattice* L) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(L->device));
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+
+}  // extern "C"
