@@ -141,6 +141,10 @@ int32_t thrml_builder_table_data(const thrml_builder* b, int32_t block, int32_t 
 int32_t thrml_ctx_create(int32_t device_id, thrml_ctx** out);
 void thrml_ctx_destroy(thrml_ctx* ctx);
 int32_t thrml_ctx_synchronize(thrml_ctx* ctx);
+/* Failure-detection self test (no reference counterpart; the reference's errors are Result<_, String> / panics): a
+ * kernel waits on a pipeline barrier that nothing signals; its bounded wait runs out, it returns, and this call
+ * reports THRML_ERR_TIMEOUT.  The context remains usable. */
+int32_t thrml_debug_wait_timeout(thrml_ctx* ctx);
 /* cudaStream_t of the context, for callers that time with their own events. */
 void* thrml_ctx_stream(thrml_ctx* ctx);
 

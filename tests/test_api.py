@@ -150,3 +150,43 @@ def test_potts_factor_program_api(T):
     full[:, 0::2], full[:, 1::2] = out[0], out[1]
     agree = (full[:, :-1] == full[:, 1:]).mean()
     assert agree > 0.8  # exact: e^3/(e^3+2) = 0.909 per bond
+
+
+@pytest.mark.gpu
+def test_bounded_wait_reports_timeout_and_context_survives(T):
+    ctx = T.default_context()
+    rc = T.lib().thrml_debug_wait_timeout(ctx.h)
+    assert rc == -5  # THRML_ERR_TIMEOUT
+    assert b"bounded wait ran out" in T.lib().thrml_last_error()
+    # the context still works
+    nodes, edges, ebm, even, odd = chain_model(T)
+    prog = T.IsingSamplingProgram(ebm, [even, odd], []).program
+    out = T.run_blocks(T.RngKey(0), prog, [np.zeros(3, np.float32), np.ones(2, np.float32)], [], 2)
+    assert out[0].shape == (3,)
+
+
+@pytest.mark.gpu
+def test_estimate_kl_grad_api(T):
+    # crates/thrml-models/src/ising.rs:392-433,531-594: visible data block + hidden block, two phases
+    vis, hid = spins(T, 6), spins(T, 4)
+    nodes = vis + hid
+    edges = [(v, h) for v in vis for h in hid]
+    rng = np.random.default_rng(0)
+    ebm = T.IsingEBM(nodes, edges, rng.normal(0, 0.1, 10), rng.normal(0, 0.3, 24), 1.0)
+    bv, bh = T.Block(vis), T.Block(hid)
+    spec = T.IsingTrainingSpec(ebm, [bv], [], [bh], [bv, bh], T.SamplingSchedule(5, 20, 1), T.SamplingSchedule(5, 20, 1))
+    data = [rng.integers(0, 2, (8, 6)).astype(np.float32)]
+    chains = 64
+    init_pos = [np.zeros((chains, 4), np.float32)]
+    init_neg = [np.zeros((chains, 6), np.float32), np.zeros((chains, 4), np.float32)]
+    key = T.RngKey(3)
+    gw, gb = T.estimate_kl_grad(key, spec, nodes, edges, data, [], init_pos, init_neg)
+    assert gw.shape == (24,) and gb.shape == (10,)
+    # the same gradient from the two estimate_moments calls it is made of
+    kp, kn = key.split_two()
+    row = data[0][kp.seed() % 8]
+    bp, wp = T.estimate_moments(kp, nodes, edges, spec.program_positive.program, spec.schedule_positive, init_pos, [np.broadcast_to(row, (chains, 6)).copy()])
+    bn, wn = T.estimate_moments(kn, nodes, edges, spec.program_negative.program, spec.schedule_negative, init_neg, [])
+    assert np.array_equal(gw, -(wp - wn)) and np.array_equal(gb, -(bp - bn))
+    # clamped visible units reproduce the data row exactly in the positive phase
+    assert np.allclose(bp[:6], 2 * row - 1)

@@ -525,6 +525,36 @@ def estimate_moments(key, first_moment_nodes, second_moment_edges, program, sche
     return node_m.astype(np.float32), edge_m.astype(np.float32)
 
 
+class IsingTrainingSpec:
+    """ising.rs:392-433: the positive program clamps data + conditioning blocks, the negative one only conditioning."""
+
+    def __init__(self, ebm, data_blocks, conditioning_blocks, positive_sampling_blocks, negative_sampling_blocks, schedule_positive, schedule_negative, ctx=None):
+        self.ebm = ebm
+        self.program_positive = IsingSamplingProgram(ebm, list(positive_sampling_blocks), list(data_blocks) + list(conditioning_blocks), ctx)
+        self.program_negative = IsingSamplingProgram(ebm, list(negative_sampling_blocks), list(conditioning_blocks), ctx)
+        self.schedule_positive = schedule_positive
+        self.schedule_negative = schedule_negative
+
+
+def estimate_kl_grad(key, training_spec, bias_nodes, weight_edges, data, conditioning_values, init_state_positive, init_state_negative):
+    """ising.rs:531-594: grad = -beta (<.>_data - <.>_model), returned as (grad_weights, grad_biases).  `data` is one
+    `[batch, n]` array per data block; like the reference, the positive phase clamps the single row `key_pos % batch`
+    (ising.rs:549-559).  Chains batch through the init states as everywhere else."""
+    key_pos, key_neg = key.split_two()
+    beta = training_spec.ebm.beta_value()
+    chains, batched = _batch_of(list(init_state_positive) + list(init_state_negative))
+    clamped_pos = []
+    for d in data:
+        d = np.asarray(d)
+        row = d[key_pos.seed() % d.shape[0]]
+        clamped_pos.append(np.broadcast_to(row, (chains, row.shape[0])).copy() if batched else row)
+    cond = [np.asarray(c) for c in conditioning_values]
+    clamped_pos += cond
+    b_pos, w_pos = estimate_moments(key_pos, bias_nodes, weight_edges, training_spec.program_positive.program, training_spec.schedule_positive, init_state_positive, clamped_pos)
+    b_neg, w_neg = estimate_moments(key_neg, bias_nodes, weight_edges, training_spec.program_negative.program, training_spec.schedule_negative, init_state_negative, cond)
+    return (w_pos - w_neg) * np.float32(-beta), (b_pos - b_neg) * np.float32(-beta)
+
+
 # ---------------------------------------------------------------------------------------------------------
 # Input builders: crates/thrml-models/src/graph_utils.rs:177-243, crates/thrml-examples/src/lib.rs:114-205
 # ---------------------------------------------------------------------------------------------------------

@@ -1438,6 +1438,33 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
     return check_err_flag(s);
 }
 
+// Failure-detection self test: one warp waits, with the same bounded wait the tensor-core pipeline uses, on a barrier
+// nothing ever arrives on.  The wait runs out, the kernel raises its error flag and returns, and the host reports
+// THRML_ERR_TIMEOUT; the context stays usable.
+__global__ void k_wait_on_nothing(int* err, uint32_t* polls) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        dense::mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const bool ok = dense::mbar_wait(&bar, 0, err, 7);
+        *polls = ok ? 0u : 1u;
+    }
+}
+int32_t thrml_debug_wait_timeout(thrml_ctx* ctx) {
+    if (!ctx) return fail(THRML_ERR_INVALID_ARG, "null context");
+    CU_TRY(cudaSetDevice(ctx->device));
+    DevBuf flag;
+    if (int32_t rc = flag.alloc(8)) return rc;
+    CU_TRY(cudaMemsetAsync(flag.p, 0, 8, ctx->stream));
+    k_wait_on_nothing<<<1, 32, 0, ctx->stream>>>(flag.as<int>(), flag.as<uint32_t>() + 1);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(ctx->stream));
+    int host[2] = {0, 0};
+    CU_TRY(cudaMemcpy(host, flag.p, 8, cudaMemcpyDeviceToHost));
+    if (host[0] != 0) return fail(THRML_ERR_TIMEOUT, "a bounded wait ran out (role " + std::to_string(host[0]) + "); the kernel returned and the context is intact");
+    return THRML_OK;
+}
+
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out) {
     if (!s || !out) return fail(THRML_ERR_INVALID_ARG, "null argument");
     if (block < 0 || block >= s->prog->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
