@@ -290,6 +290,30 @@ int32_t thrml_lattice_wrap_halo(thrml_lattice* lat, int32_t colour);
 int32_t thrml_lattice_observe(thrml_lattice* lat, int64_t* sums_out);
 int32_t thrml_lattice_synchronize(thrml_lattice* lat);
 
+/* ------------------------------------------------------------------------------------------------
+ * Implicit Potts lattice: an nx x ny x nz periodic lattice of categorical nodes (K categories), one K x K table per
+ * direction shared by all edges of that direction, per-node unary terms, checkerboard blocks [(x+y+z) even, odd],
+ * CategoricalGibbsConditional updates (crates/thrml-samplers/src/softmax.rs:228-271,586-709).  It samples exactly what
+ * FactorSamplingProgram (crates/thrml-models/src/factor.rs:153-184) would with the factors
+ * CategoricalEBMFactor([nodes], unary[N,K,1]) and CategoricalEBMFactor([u, u+e_d], T_d) for d = x, y, z
+ * (crates/thrml-models/src/discrete_ebm.rs:792-851), whose [N,6,K*K] per-block weight tensors never have to exist.
+ * tables[3][K][K] (energy term T_d[x_u][x_{u+e_d}]), unary[N][K] (nullable = zeros), node index (x*ny + y)*nz + z.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct thrml_potts thrml_potts;
+int32_t thrml_potts_create(thrml_ctx* ctx, int32_t nx, int32_t ny, int32_t nz, int32_t n_categories, const float* tables,
+                           const float* unary, float beta, int64_t n_chains, int64_t chain_offset, thrml_potts** out);
+void thrml_potts_destroy(thrml_potts* p);
+int32_t thrml_potts_randomize(thrml_potts* p, uint64_t key);
+/* Category bytes, host layout [chain][node]. */
+int32_t thrml_potts_upload(thrml_potts* p, const uint8_t* host);
+int32_t thrml_potts_download(thrml_potts* p, uint8_t* host);
+/* Update one colour with its block key (asynchronous); a sweep is colour 0 with key.split(2)[0], then colour 1. */
+int32_t thrml_potts_update(thrml_potts* p, int32_t colour, uint64_t block_key);
+/* Category-marginal observer: counts[node][category] += chains in that category (asynchronous); read as int32. */
+int32_t thrml_potts_observe_marginals(thrml_potts* p);
+int32_t thrml_potts_read_marginals(thrml_potts* p, int32_t* counts_out, int64_t* n_obs_out);
+int32_t thrml_potts_synchronize(thrml_potts* p);
+
 #ifdef __cplusplus
 }
 #endif

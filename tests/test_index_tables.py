@@ -125,3 +125,19 @@ def test_factor_group_structure(T):
     nodes = [T.Node(T.NodeType.Spin()) for _ in range(3)]
     ebm = T.IsingEBM(nodes, [(nodes[0], nodes[1]), (nodes[1], nodes[2])], np.zeros(3), np.ones(2), 1.0)
     assert len(ebm.get_factors()) == 2
+
+
+def test_square_factor_merges_groups(T):
+    # crates/thrml-models/tests/test_discrete_ebm.rs:63-66,180-183 ("square"), discrete_ebm.rs:902-987 (merge by (tails, n_spin))
+    import pytest
+    cg = [T.Block([T.Node(T.NodeType.Categorical(3)) for _ in range(4)]) for _ in range(2)]
+    with pytest.raises(T.ThrmlError, match="square"):
+        T.SquareDiscreteEBMFactor([], cg, np.zeros((4, 3, 2), np.float32))
+    w = np.arange(36, dtype=np.float32).reshape(4, 3, 3)
+    plain = T.CategoricalEBMFactor(cg, w).to_interaction_groups()
+    merged = T.SquareDiscreteEBMFactor([], cg, w).to_interaction_groups()
+    assert len(plain) == 2 and len(merged) == 1
+    m = merged[0]
+    assert len(m.head_nodes) == 8 and len(m.tail_nodes) == 1 and m.n_spin == 0
+    assert m.head_nodes.nodes() == cg[0].nodes() + cg[1].nodes() and m.tail_nodes[0].nodes() == cg[1].nodes() + cg[0].nodes()
+    assert np.array_equal(m.interaction[:4], w) and np.array_equal(m.interaction[4:], w.transpose(0, 2, 1))

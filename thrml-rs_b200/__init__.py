@@ -9,7 +9,7 @@ from .engine import (Builder, ChainState, Context, Moments, Program, default_con
 from .api import (Block, BlockGibbsSpec, BlockSamplingProgram, BlockSpec, CategoricalEBMFactor,  # noqa: F401
                   CategoricalGibbsConditional, DiscreteEBMFactor, FactorSamplingProgram, InteractionGroup, IsingEBM,
                   IsingSamplingProgram, IsingTrainingSpec, MomentAccumulatorObserver, Node, NodeType, RngKey, SamplingSchedule,
-                  SpinEBMFactor, SpinGibbsConditional, StateObserver, coloring_to_blocks, estimate_kl_grad, estimate_moments,
+                  SpinEBMFactor, SpinGibbsConditional, SquareDiscreteEBMFactor, StateObserver, coloring_to_blocks, estimate_kl_grad, estimate_moments,
                   greedy_coloring, hinton_init, make_nearest_neighbor_lattice, run_blocks, sample_blocks,
                   sample_states, sample_with_observation)
 

@@ -81,6 +81,15 @@ _SIGNATURES = {
     "thrml_lattice_wrap_halo": (C.c_int32, [_P, C.c_int32]),
     "thrml_lattice_observe": (C.c_int32, [_P, _P]),
     "thrml_lattice_synchronize": (C.c_int32, [_P]),
+    "thrml_potts_create": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, C.c_float, C.c_int64, C.c_int64, _P]),
+    "thrml_potts_destroy": (None, [_P]),
+    "thrml_potts_randomize": (C.c_int32, [_P, C.c_uint64]),
+    "thrml_potts_upload": (C.c_int32, [_P, _P]),
+    "thrml_potts_download": (C.c_int32, [_P, _P]),
+    "thrml_potts_update": (C.c_int32, [_P, C.c_int32, C.c_uint64]),
+    "thrml_potts_observe_marginals": (C.c_int32, [_P]),
+    "thrml_potts_read_marginals": (C.c_int32, [_P, _P, _P]),
+    "thrml_potts_synchronize": (C.c_int32, [_P]),
     "thrml_sample_with_observation": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, _P, _P, C.c_int32, _P, _P]),
 }
 

@@ -447,6 +447,33 @@ class CategoricalEBMFactor(DiscreteEBMFactor):
         super().__init__([], node_groups, weights)
 
 
+class SquareDiscreteEBMFactor(DiscreteEBMFactor):
+    """discrete_ebm.rs:858-987: a factor whose category dimensions are all equal; its interaction groups with the same
+    (number of tails, n_spin) are concatenated into one.  The reference iterates a HashMap of buckets; here buckets
+    come out in first-seen order."""
+
+    def __init__(self, spin_node_groups, categorical_node_groups, weights):
+        w = np.asarray(weights, dtype=np.float32)
+        if w.ndim == 3 and any(d != w.shape[1] for d in w.shape[1:]):
+            raise ThrmlError(-1, "Interaction tensor is not square")
+        super().__init__(spin_node_groups, categorical_node_groups, w)
+
+    def to_interaction_groups(self):
+        base = super().to_interaction_groups()
+        buckets = {}
+        for g in base:
+            buckets.setdefault((len(g.tail_nodes), g.n_spin), []).append(g)
+        merged = []
+        for (n_tail, n_spin), bucket in buckets.items():
+            if len(bucket) == 1:
+                merged.append(bucket[0])
+                continue
+            head = Block([n for g in bucket for n in g.head_nodes.nodes()])
+            tails = [Block([n for g in bucket for n in g.tail_nodes[i].nodes()]) for i in range(n_tail)]
+            merged.append(InteractionGroup(np.concatenate([g.interaction for g in bucket], axis=0), head, tails, n_spin))
+        return merged
+
+
 class FactorSamplingProgram:
     """factor.rs:133-185."""
 

@@ -1,0 +1,288 @@
+// Implicit 3-D periodic Potts-like lattice: K categories per node, one K x K interaction table per lattice direction
+// (shared by every edge of that direction), per-node unary terms, two checkerboard blocks, Gumbel-argmax updates.
+//
+// Semantics = FactorSamplingProgram (crates/thrml-models/src/factor.rs:153-184) over the factors
+//   CategoricalEBMFactor([all nodes], unary[N,K,1]),
+//   CategoricalEBMFactor([U, U + e_d], T_d broadcast to [N,K,K])  for d = x, y, z            (discrete_ebm.rs:792-851)
+// with blocks [(x+y+z) even, (x+y+z) odd] and CategoricalGibbsConditional (softmax.rs:228-271, 586-709): a node's logits are
+//   theta[c] = unary[c] + Tx[c][s(+x)] + Tx[s(-x)][c] + Ty[c][s(+y)] + Ty[s(-y)][c] + Tz[c][s(+z)] + Tz[s(-z)][c]
+// added left to right in f32 — the order in which the reference's per-block tables (each with one slot) are summed — so
+// the sampled states equal the explicit program's bit for bit, without its [N,6,K*K] weight tensors (2.5 GB per block at
+// 128^3, K = 10).  Node index = (x*ny + y)*nz + z; state = one byte per node and chain, chains innermost.
+#include <algorithm>
+#include <memory>
+#include <vector>
+
+#include "ctx.h"
+#include "device_math.cuh"
+
+using namespace thrml;
+
+namespace {
+
+constexpr int MAX_K = 32;
+
+struct PottsArgs {
+    uint8_t* state;        // [N][ld]
+    const float* tables;   // [3][K][K], beta already applied
+    const float* unary;    // [N][K], beta already applied
+    int32_t nx, ny, nz, K, colour;
+    int64_t ld, n_chains;
+    uint32_t chain_word0, k0, k1;
+};
+
+__global__ void __launch_bounds__(256) k_potts_update(PottsArgs a) {
+    extern __shared__ float s_tab[];  // [3][K][K]
+    for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[i] = a.tables[i];
+    __syncthreads();
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int64_t in_block = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;  // index among the nodes of this colour
+    const int half_z = a.nz >> 1;
+    const int64_t n_block = static_cast<int64_t>(a.nx) * a.ny * half_z;
+    if (in_block >= n_block || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const int zz = static_cast<int>(in_block % half_z);
+    const int y = static_cast<int>((in_block / half_z) % a.ny);
+    const int x = static_cast<int>(in_block / (static_cast<int64_t>(half_z) * a.ny));
+    const int z = 2 * zz + ((x + y + a.colour) & 1);
+    auto node_of = [&](int xx, int yy, int zz2) { return (static_cast<int64_t>(xx) * a.ny + yy) * a.nz + zz2; };
+    auto word = [&](int64_t node) { return *reinterpret_cast<const uint32_t*>(a.state + node * a.ld + 4 * static_cast<int64_t>(quad)); };
+    const int64_t node = node_of(x, y, z);
+    const uint32_t px = word(node_of(x + 1 == a.nx ? 0 : x + 1, y, z)), mx = word(node_of(x == 0 ? a.nx - 1 : x - 1, y, z));
+    const uint32_t py = word(node_of(x, y + 1 == a.ny ? 0 : y + 1, z)), my = word(node_of(x, y == 0 ? a.ny - 1 : y - 1, z));
+    const uint32_t pz = word(node_of(x, y, z + 1 == a.nz ? 0 : z + 1)), mz = word(node_of(x, y, z == 0 ? a.nz - 1 : z - 1));
+    const int K = a.K, KK = K * K;
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t arg[4] = {0, 0, 0, 0};
+    U4 r[4];
+    for (int cat = 0; cat < K; ++cat) {
+        const float un = __ldg(a.unary + node * K + cat);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int sh = 8 * c;
+            float th = un;  // 0 + unary
+            th = __fadd_rn(th, s_tab[cat * K + ((px >> sh) & 0xffu)]);            // this node is U of its +x edge: T[c][s_v]
+            th = __fadd_rn(th, s_tab[((mx >> sh) & 0xffu) * K + cat]);            // and V of its -x edge: T[s_u][c]
+            th = __fadd_rn(th, s_tab[KK + cat * K + ((py >> sh) & 0xffu)]);
+            th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
+            th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
+            th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
+            if ((cat & 3) == 0)
+                r[c] = philox4x32_10(static_cast<uint32_t>(in_block), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+            const float u = u23_open(pick(r[c], cat & 3));
+            const float p = __fadd_rn(th, -det_log(-det_log(u)));  // softmax.rs:84
+            if (cat == 0 || p > best[c]) { best[c] = p; arg[c] = cat; }  // first maximum wins (gumbel_argmax/kernel.rs:81-83)
+        }
+    }
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
+    *reinterpret_cast<uint32_t*>(a.state + node * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+__global__ void __launch_bounds__(256) k_potts_randomize(uint8_t* state, int32_t nx, int32_t ny, int32_t nz, int32_t K, int32_t colour, int64_t ld, int64_t n_chains,
+                                                        uint32_t chain_word0, uint32_t k0, uint32_t k1) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int64_t in_block = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    const int half_z = nz >> 1;
+    if (in_block >= static_cast<int64_t>(nx) * ny * half_z || 4 * static_cast<int64_t>(quad) >= ld) return;
+    const int zz = static_cast<int>(in_block % half_z), y = static_cast<int>((in_block / half_z) % ny), x = static_cast<int>(in_block / (static_cast<int64_t>(half_z) * ny));
+    const int64_t node = (static_cast<int64_t>(x) * ny + y) * nz + 2 * zz + ((x + y + colour) & 1);
+    const U4 r = philox4x32_10(static_cast<uint32_t>(in_block), chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_RAND, k0, k1);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (4 * static_cast<int64_t>(quad) + c < n_chains) out |= static_cast<uint32_t>((static_cast<uint64_t>(pick(r, c) >> 8) * static_cast<uint64_t>(K)) >> 24) << (8 * c);
+    *reinterpret_cast<uint32_t*>(state + node * ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// counts[node][category] += number of chains in that category (the category-marginal observer).
+__global__ void __launch_bounds__(256) k_potts_marginals(const uint8_t* state, int64_t n_nodes, int32_t K, int64_t ld, int64_t n_chains, int32_t* counts) {
+    const int64_t node = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (node >= n_nodes) return;
+    int total = 0;  // lane k keeps the total of category k (K <= 32)
+    for (int64_t base = 0; base < n_chains; base += 128) {
+        const int64_t chain = base + 4 * threadIdx.x;
+        uint32_t wd = 0xffffffffu;
+        if (chain < n_chains) {
+            wd = *reinterpret_cast<const uint32_t*>(state + node * ld + chain);
+            const int64_t left = n_chains - chain;
+            if (left < 4) wd |= 0xffffffffu << (8 * static_cast<int>(left));  // padding -> 0xff, matches no category
+        }
+        for (int k = 0; k < K; ++k) {
+            const int c = ((wd & 0xffu) == static_cast<uint32_t>(k)) + (((wd >> 8) & 0xffu) == static_cast<uint32_t>(k)) + (((wd >> 16) & 0xffu) == static_cast<uint32_t>(k)) +
+                          ((wd >> 24) == static_cast<uint32_t>(k));
+            const int sum = __reduce_add_sync(0xffffffffu, c);
+            if (threadIdx.x == k) total += sum;
+        }
+    }
+    if (threadIdx.x < K) counts[node * K + threadIdx.x] += total;  // one warp owns the node: no atomics
+}
+
+__global__ void k_potts_transpose_in(const uint8_t* src, uint8_t* dst, int64_t n, int64_t n_chains, int64_t ld) {
+    __shared__ uint8_t tile[32][33];
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
+        tile[r][threadIdx.x] = (chain < n_chains && node < n) ? src[chain * n + node] : 0;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
+        if (node < n && chain < ld) dst[node * ld + chain] = chain < n_chains ? tile[threadIdx.x][r] : 0;
+    }
+}
+__global__ void k_potts_transpose_out(const uint8_t* src, uint8_t* dst, int64_t n, int64_t n_chains, int64_t ld) {
+    __shared__ uint8_t tile[32][33];
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
+        tile[r][threadIdx.x] = (node < n && chain < n_chains) ? src[node * ld + chain] : 0;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
+        if (chain < n_chains && node < n) dst[chain * n + node] = tile[threadIdx.x][r];
+    }
+}
+
+struct PBuf {
+    void* p = nullptr;
+    size_t bytes = 0;
+    ~PBuf() { if (p) cudaFree(p); }
+};
+int32_t palloc(PBuf& b, size_t bytes) {
+    if (b.p) { cudaFree(b.p); b.p = nullptr; b.bytes = 0; }
+    cudaError_t e = cudaMalloc(&b.p, bytes);
+    if (e != cudaSuccess) { b.p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
+    b.bytes = bytes;
+    return THRML_OK;
+}
+
+}  // namespace
+
+struct thrml_potts {
+    thrml_ctx* ctx = nullptr;
+    int device = 0;
+    int32_t nx = 0, ny = 0, nz = 0, K = 0;
+    int64_t n = 0, n_chains = 0, chain_offset = 0, ld = 0, n_obs = 0;
+    PBuf state, tables, unary, counts, scratch;
+};
+
+extern "C" {
+
+int32_t thrml_potts_create(thrml_ctx* ctx, int32_t nx, int32_t ny, int32_t nz, int32_t n_categories, const float* tables, const float* unary, float beta,
+                           int64_t n_chains, int64_t chain_offset, thrml_potts** out) {
+    if (!ctx || !out || !tables) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (nx < 2 || ny < 2 || nz < 2 || (nx & 1) || (ny & 1) || (nz & 1)) return fail(THRML_ERR_INVALID_ARG, "lattice sides must be even and at least 2 (a two-colouring of the torus needs even sides)");
+    if (n_categories < 1 || n_categories > MAX_K) return fail(THRML_ERR_INVALID_ARG, "n_categories must be between 1 and 32");
+    if (n_chains < 1 || chain_offset < 0 || (chain_offset & 15)) return fail(THRML_ERR_INVALID_ARG, "n_chains must be positive and chain_offset a non-negative multiple of 16");
+    const int64_t n = static_cast<int64_t>(nx) * ny * nz;
+    if (n / 2 > (int64_t(1) << 32)) return fail(THRML_ERR_UNSUPPORTED, "more than 2^32 nodes per colour");
+    CU_TRY(cudaSetDevice(ctx->device));
+    auto P = std::make_unique<thrml_potts>();
+    P->ctx = ctx; P->device = ctx->device;
+    P->nx = nx; P->ny = ny; P->nz = nz; P->K = n_categories; P->n = n;
+    P->n_chains = n_chains; P->chain_offset = chain_offset; P->ld = (n_chains + 15) / 16 * 16;
+    const int K = n_categories;
+    std::vector<float> tab(static_cast<size_t>(3) * K * K), un(static_cast<size_t>(n) * K, 0.0f);
+    for (size_t i = 0; i < tab.size(); ++i) tab[i] = beta * tables[i];
+    if (unary) for (size_t i = 0; i < un.size(); ++i) un[i] = beta * unary[i];
+    if (int32_t rc = palloc(P->state, static_cast<size_t>(n) * P->ld)) return rc;
+    if (int32_t rc = palloc(P->tables, tab.size() * 4)) return rc;
+    if (int32_t rc = palloc(P->unary, un.size() * 4)) return rc;
+    if (int32_t rc = palloc(P->counts, static_cast<size_t>(n) * K * 4)) return rc;
+    cudaStream_t st = ctx->stream;
+    CU_TRY(cudaMemsetAsync(P->state.p, 0, P->state.bytes, st));
+    CU_TRY(cudaMemsetAsync(P->counts.p, 0, P->counts.bytes, st));
+    CU_TRY(cudaMemcpyAsync(P->tables.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(P->unary.p, un.data(), un.size() * 4, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    *out = P.release();
+    return THRML_OK;
+}
+void thrml_potts_destroy(thrml_potts* P) {
+    if (!P) return;
+    cudaSetDevice(P->device);
+    cudaDeviceSynchronize();
+    delete P;
+}
+static dim3 potts_grid(const thrml_potts* P) { return dim3(static_cast<unsigned>((P->n / 2 + 7) / 8), static_cast<unsigned>((P->ld / 4 + 31) / 32)); }
+
+int32_t thrml_potts_randomize(thrml_potts* P, uint64_t key) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(P->device));
+    uint64_t keys[2];
+    rng_split(key, 2, keys);
+    for (int c = 0; c < 2; ++c) {
+        k_potts_randomize<<<potts_grid(P), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<uint8_t*>(P->state.p), P->nx, P->ny, P->nz, P->K, c, P->ld, P->n_chains,
+                                                                            static_cast<uint32_t>(P->chain_offset >> 2), static_cast<uint32_t>(keys[c]), static_cast<uint32_t>(keys[c] >> 32));
+        CU_TRY(cudaGetLastError());
+    }
+    return THRML_OK;
+}
+// Update one colour with its block key (asynchronous).
+int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
+    if (!P || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad colour");
+    CU_TRY(cudaSetDevice(P->device));
+    PottsArgs a{static_cast<uint8_t*>(P->state.p), static_cast<const float*>(P->tables.p), static_cast<const float*>(P->unary.p), P->nx, P->ny, P->nz, P->K, colour, P->ld, P->n_chains,
+                static_cast<uint32_t>(P->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
+    k_potts_update<<<potts_grid(P), dim3(32, 8), static_cast<size_t>(3) * P->K * P->K * 4, P->ctx->stream>>>(a);
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
+int32_t thrml_potts_observe_marginals(thrml_potts* P) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(P->device));
+    k_potts_marginals<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld, P->n_chains,
+                                                                                                static_cast<int32_t*>(P->counts.p));
+    CU_TRY(cudaGetLastError());
+    P->n_obs += P->n_chains;
+    return THRML_OK;
+}
+int32_t thrml_potts_read_marginals(thrml_potts* P, int32_t* counts_out, int64_t* n_obs_out) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(P->device));
+    if (counts_out) CU_TRY(cudaMemcpyAsync(counts_out, P->counts.p, P->counts.bytes, cudaMemcpyDeviceToHost, P->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    if (n_obs_out) *n_obs_out = P->n_obs;
+    return THRML_OK;
+}
+static int32_t potts_scratch(thrml_potts* P, size_t bytes) {
+    if (P->scratch.bytes >= bytes) return THRML_OK;
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    return palloc(P->scratch, bytes);
+}
+// State as category bytes, host layout [chain][node].
+int32_t thrml_potts_upload(thrml_potts* P, const uint8_t* host) {
+    if (!P || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(P->device));
+    const size_t bytes = static_cast<size_t>(P->n) * P->n_chains;
+    if (int32_t rc = potts_scratch(P, bytes)) return rc;
+    CU_TRY(cudaMemcpyAsync(P->scratch.p, host, bytes, cudaMemcpyHostToDevice, P->ctx->stream));
+    dim3 grid(static_cast<unsigned>((P->n + 31) / 32), static_cast<unsigned>((P->ld + 31) / 32));
+    k_potts_transpose_in<<<grid, dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->scratch.p), static_cast<uint8_t*>(P->state.p), P->n, P->n_chains, P->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_potts_download(thrml_potts* P, uint8_t* host) {
+    if (!P || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(P->device));
+    const size_t bytes = static_cast<size_t>(P->n) * P->n_chains;
+    if (int32_t rc = potts_scratch(P, bytes)) return rc;
+    dim3 grid(static_cast<unsigned>((P->n + 31) / 32), static_cast<unsigned>((P->n_chains + 31) / 32));
+    k_potts_transpose_out<<<grid, dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), static_cast<uint8_t*>(P->scratch.p), P->n, P->n_chains, P->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(host, P->scratch.p, bytes, cudaMemcpyDeviceToHost, P->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_potts_synchronize(thrml_potts* P) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(P->device));
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    return THRML_OK;
+}
+
+}  // extern "C"
