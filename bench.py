@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--chains", type=int, default=CHAINS_PER_GPU, help="chains per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice"],
+    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts"],
                     help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores (1 GPU); "
                          "lattice = one bit-packed 2-D Ising lattice sharded by row stripes with halo exchange")
     ap.add_argument("--side", type=int, default=32768, help="lattice side (lattice workload)")
@@ -171,6 +171,10 @@ def main():
         if rank == 0:
             print(json.dumps(run_rbm(T, torch, W, args, local_rank)), flush=True)
         return
+    if args.workload == "potts":
+        if rank == 0:
+            print(json.dumps(run_potts(T, torch, args, local_rank)), flush=True)
+        return
     if args.workload == "lattice":
         out = run_lattice(T, torch, args, rank, world, local_rank)
         if rank == 0:
@@ -249,7 +253,12 @@ def main():
     param_bytes = n * (8 * 4 + 256 * 4) if all(k == 1 for k in kinds) else n * 80
     algo_bytes = updates_per_step * (DEGREE + 1) + param_bytes
     achieved = algo_bytes / (sweep_ms * 1e-3) / 1e9
-    result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+    # DRAM traffic per launch: 8.92 B per site update, measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on a
+    # 2^18-spin case of the same kernel and scaled by the site updates of an average full-size launch (traffic grows in
+    # proportion: a random graph has no cross-node reuse); see profiles/k_spin_lut_sparse_ising.md.
+    traffic = 8.92 * updates_per_step / n_blocks if all(k == 1 for k in kinds) else None
+    result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
+                          "algorithmic_bytes_per_launch": algo_bytes / n_blocks,
                           "kernel": "k_spin_lut" if all(k == 1 for k in kinds) else "k_spin_generic", "launches_per_sweep": n_blocks, "sweep_ms": sweep_ms,
                           "bytes_per_update": algo_bytes / updates_per_step}
 
@@ -324,6 +333,54 @@ def run_rbm(T, torch, W, args, device):
                          "peak_source": "measured burst bf16 GEMM (MEASURED_PEAKS.json)" if peaks else "fallback 1590", "flop_per_step": flop,
                          "note": "3 bf16 field GEMMs + 2 int8 correlation GEMMs counted at 2*M*N*K each"},
             "e2e": {"value": updates / best, "unit": UNIT, "h2d_bytes_per_step": chains * nv, "d2h_bytes_per_step": 2 * nv * nh * 4, "seconds": best}}
+
+
+def run_potts(T, torch, args, device):
+    """Categorical (Potts-like) EBM on a 128^3 periodic lattice, K = 10, three direction tables N(0, 0.3^2), unary terms
+    N(0, 0.1^2), beta = 1, 1024 chains, Gumbel-argmax updates, category marginals observed every sweep."""
+    from thrml_rs_b200 import potts
+    side, K, chains = args.side if args.side != 32768 else 128, 10, 1024
+    rng = np.random.default_rng(0x5EED0004)
+    tables = rng.normal(0, 0.3, (3, K, K)).astype(np.float32)
+    unary = rng.normal(0, 0.1, (side ** 3, K)).astype(np.float32)
+    ctx = T.default_context(device)
+    lat = potts.PottsLattice(side, side, side, K, tables, unary, 1.0, chains, 0, ctx)
+    lat.randomize(5)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def step(i):
+        lat.sample_blocks(300 + i)
+        lat.observe_marginals()
+
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    ctx.synchronize()
+    sampler = ClockSampler(device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.time()
+    ev0.record(stream)
+    for i in range(args.steps):
+        step(100 + i)
+    ev1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    t1 = time.time()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    clocks = sampler.stop(t0, t1)
+    counts, n_obs = lat.read_marginals()
+    updates = float(side) ** 3 * chains
+    peak, peak_src = measured_peak()
+    bytes_per_update = 2 + 120.0 / chains
+    achieved = updates * bytes_per_update / (ms * 1e-3) / 1e9
+    return {"metric": METRIC, "value": updates / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 categories, f32 logits", "data": "synthetic",
+            "config": {"workload": "3-D periodic Potts-like lattice, shared direction tables, category marginals every sweep", "side": side, "categories": K, "chains": chains,
+                       "l2": "state (2 GiB at side 128) larger than L2"},
+            "clocks": clocks, "gpu_launches": args.steps * 3,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "bytes_per_update": bytes_per_update, "note": "instruction-bound by construction: 2 logarithms and a 23-bit uniform per category and update"},
+            "marginal_check": {"observations_per_node": int(n_obs), "rows_sum_to_observations": bool(np.all(counts.sum(axis=1) == n_obs))},
+            "e2e": None}
 
 
 def run_lattice(T, torch, args, rank, world, device):
