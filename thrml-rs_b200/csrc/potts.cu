@@ -31,57 +31,6 @@ struct PottsArgs {
     uint32_t chain_word0, k0, k1;
 };
 
-// Gumbel noise -ln(-ln u).  The approximate version uses the hardware logarithm: for u <= 1 - 2^-7 its error is below 6e-5
-// (the inner logarithm has absolute error 2^-21.41 on [0.5, 2] and 3 ulp elsewhere, i.e. relative error <= 4.6e-5 of
-// -ln u >= 7.8e-3; the outer one adds at most 1.4e-6); closer to 1 the exact sequence is used.
-__device__ __forceinline__ float gumbel_exact(float u) { return -det_log(-det_log(u)); }
-__device__ __forceinline__ float gumbel_fast(float u) {
-    if (u > 0.9921875f) return gumbel_exact(u);
-    return -__logf(-__logf(u));
-}
-constexpr float GUMBEL_MARGIN = 2e-4f;  // > 2 * (6e-5 + rounding of the f32 add): a larger gap fixes the arg-max
-
-// Scan the K categories of four chains: theta accumulated left to right (unary, +x, -x, +y, -y, +z, -z), Gumbel noise
-// added, first maximum wins.  EXACT = false also reports in `unsure` the chains whose two best values are closer than
-// the margin; those are rescanned with EXACT = true, so the result always equals the exact scan's.
-template <bool EXACT>
-__device__ __forceinline__ void potts_scan(const PottsArgs& a, const float* s_tab, int64_t node, uint32_t in_block, int quad, const uint32_t (&nb)[6], uint32_t (&arg)[4],
-                                           uint32_t& unsure) {
-    const int K = a.K, KK = K * K;
-    float best[4], second[4];
-    U4 r[4];
-#pragma unroll
-    for (int c = 0; c < 4; ++c) { best[c] = -3.0e38f; second[c] = -3.0e38f; arg[c] = 0; }
-    for (int cat = 0; cat < K; ++cat) {
-        const float un = __ldg(a.unary + node * K + cat);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const int sh = 8 * c;
-            float th = un;  // 0 + unary
-            th = __fadd_rn(th, s_tab[cat * K + ((nb[0] >> sh) & 0xffu)]);            // this node is U of its +x edge: T[c][s_v]
-            th = __fadd_rn(th, s_tab[((nb[1] >> sh) & 0xffu) * K + cat]);            // and V of its -x edge: T[s_u][c]
-            th = __fadd_rn(th, s_tab[KK + cat * K + ((nb[2] >> sh) & 0xffu)]);
-            th = __fadd_rn(th, s_tab[KK + ((nb[3] >> sh) & 0xffu) * K + cat]);
-            th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((nb[4] >> sh) & 0xffu)]);
-            th = __fadd_rn(th, s_tab[2 * KK + ((nb[5] >> sh) & 0xffu) * K + cat]);
-            if ((cat & 3) == 0)
-                r[c] = philox4x32_10(in_block, 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
-            const float u = u23_open(pick(r[c], cat & 3));
-            const float p = __fadd_rn(th, EXACT ? gumbel_exact(u) : gumbel_fast(u));  // softmax.rs:84
-            const bool gt = p > best[c];  // strict >: the first maximum wins (gumbel_argmax/kernel.rs:81-83)
-            if (!EXACT) second[c] = gt ? best[c] : fmaxf(second[c], p);
-            arg[c] = gt ? static_cast<uint32_t>(cat) : arg[c];
-            best[c] = gt ? p : best[c];
-        }
-    }
-    unsure = 0;
-    if (!EXACT) {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            if (best[c] - second[c] <= GUMBEL_MARGIN) unsure |= 1u << c;
-    }
-}
-
 __global__ void __launch_bounds__(256) k_potts_update(PottsArgs a) {
     extern __shared__ float s_tab[];  // [3][K][K]
     for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[i] = a.tables[i];
@@ -98,17 +47,31 @@ __global__ void __launch_bounds__(256) k_potts_update(PottsArgs a) {
     auto node_of = [&](int xx, int yy, int zz2) { return (static_cast<int64_t>(xx) * a.ny + yy) * a.nz + zz2; };
     auto word = [&](int64_t node) { return *reinterpret_cast<const uint32_t*>(a.state + node * a.ld + 4 * static_cast<int64_t>(quad)); };
     const int64_t node = node_of(x, y, z);
-    const uint32_t nb[6] = {word(node_of(x + 1 == a.nx ? 0 : x + 1, y, z)), word(node_of(x == 0 ? a.nx - 1 : x - 1, y, z)),
-                            word(node_of(x, y + 1 == a.ny ? 0 : y + 1, z)), word(node_of(x, y == 0 ? a.ny - 1 : y - 1, z)),
-                            word(node_of(x, y, z + 1 == a.nz ? 0 : z + 1)), word(node_of(x, y, z == 0 ? a.nz - 1 : z - 1))};
-    uint32_t arg[4], unsure;
-    potts_scan<false>(a, s_tab, node, static_cast<uint32_t>(in_block), quad, nb, arg, unsure);
-    if (unsure) {
-        uint32_t arg2[4], dummy;
-        potts_scan<true>(a, s_tab, node, static_cast<uint32_t>(in_block), quad, nb, arg2, dummy);
+    const uint32_t px = word(node_of(x + 1 == a.nx ? 0 : x + 1, y, z)), mx = word(node_of(x == 0 ? a.nx - 1 : x - 1, y, z));
+    const uint32_t py = word(node_of(x, y + 1 == a.ny ? 0 : y + 1, z)), my = word(node_of(x, y == 0 ? a.ny - 1 : y - 1, z));
+    const uint32_t pz = word(node_of(x, y, z + 1 == a.nz ? 0 : z + 1)), mz = word(node_of(x, y, z == 0 ? a.nz - 1 : z - 1));
+    const int K = a.K, KK = K * K;
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t arg[4] = {0, 0, 0, 0};
+    U4 r[4];
+    for (int cat = 0; cat < K; ++cat) {
+        const float un = __ldg(a.unary + node * K + cat);
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-            if ((unsure >> c) & 1u) arg[c] = arg2[c];
+        for (int c = 0; c < 4; ++c) {
+            const int sh = 8 * c;
+            float th = un;  // 0 + unary
+            th = __fadd_rn(th, s_tab[cat * K + ((px >> sh) & 0xffu)]);            // this node is U of its +x edge: T[c][s_v]
+            th = __fadd_rn(th, s_tab[((mx >> sh) & 0xffu) * K + cat]);            // and V of its -x edge: T[s_u][c]
+            th = __fadd_rn(th, s_tab[KK + cat * K + ((py >> sh) & 0xffu)]);
+            th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
+            th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
+            th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
+            if ((cat & 3) == 0)
+                r[c] = philox4x32_10(static_cast<uint32_t>(in_block), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+            const float u = u23_open(pick(r[c], cat & 3));
+            const float p = __fadd_rn(th, -det_log(-det_log(u)));  // softmax.rs:84
+            if (cat == 0 || p > best[c]) { best[c] = p; arg[c] = cat; }  // first maximum wins (gumbel_argmax/kernel.rs:81-83)
+        }
     }
     uint32_t out = 0;
 #pragma unroll
