@@ -255,7 +255,7 @@ def main():
     achieved = algo_bytes / (sweep_ms * 1e-3) / 1e9
     # DRAM traffic per launch: 8.92 B per site update, measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on a
     # 2^18-spin case of the same kernel and scaled by the site updates of an average full-size launch (traffic grows in
-    # proportion: a random graph has no cross-node reuse); see profiles/k_spin_lut_sparse_ising.md.
+    # proportion: a random graph has no cross-node reuse).
     traffic = 8.92 * updates_per_step / n_blocks if all(k == 1 for k in kinds) else None
     result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                           "algorithmic_bytes_per_launch": algo_bytes / n_blocks,
