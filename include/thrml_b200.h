@@ -207,6 +207,11 @@ typedef struct thrml_noise {
 int32_t thrml_sample_blocks(thrml_state* s, uint64_t key, const thrml_noise* inj);
 /* run_blocks (sampling.rs:81-106): n_iters sweeps with keys = key.split(n_iters). */
 int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const thrml_noise* inj);
+/* IsingEBM::energy / energy_batched (crates/thrml-models/src/ising.rs:150-321): per chain
+ * E = -beta (sum_i b_i s_i + sum_(i,j) J_ij s_i s_j) with s = 2x - 1, accumulated in f64.  nodes[n_nodes] with biases,
+ * edges[2*n_edges] (node id pairs) with weights; energy_out[n_chains] on the host. */
+int32_t thrml_ising_energy(thrml_state* s, int64_t n_nodes, const int64_t* nodes, const float* biases, int64_t n_edges,
+                           const int64_t* edges, const float* weights, float beta, double* energy_out);
 /* sample_single_block (program.rs:324-393): update one free block in place; `key` is the block's own key. */
 int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key);
 /* <s_a s_b> over this device's chains for every node pair of two spin blocks (s = 2x-1): host_out[n_a][n_b] f32, computed

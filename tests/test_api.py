@@ -190,3 +190,27 @@ def test_estimate_kl_grad_api(T):
     assert np.array_equal(gw, -(wp - wn)) and np.array_equal(gb, -(bp - bn))
     # clamped visible units reproduce the data row exactly in the positive phase
     assert np.allclose(bp[:6], 2 * row - 1)
+
+
+@pytest.mark.gpu
+def test_ising_energy(T):
+    # crates/thrml-models/tests/test_ising.rs:17-55: 3-node chain, b = (0.1, 0.2, 0.3), J = (0.5, -0.5), state (1,0,1):
+    # E = -(0.1 - 0.2 + 0.3 - 0.5 + 0.5) = -0.2 (the test's comment says 0.8; the code it calls gives -0.2)
+    nodes = spins(T, 3)
+    ebm = T.IsingEBM(nodes, [(nodes[0], nodes[1]), (nodes[1], nodes[2])], [0.1, 0.2, 0.3], [0.5, -0.5], 1.0)
+    e = ebm.energy([np.array([1.0, 0.0, 1.0], np.float32)])
+    assert e.shape == (1,) and abs(e[0] + 0.2) < 1e-6
+    # crates/thrml-models/tests/test_ising.rs:185-222: batched energies equal single-state energies within 1e-5
+    rng = np.random.default_rng(4)
+    big = spins(T, 40)
+    edges = [(big[i], big[j]) for i in range(40) for j in range(i + 1, 40) if rng.random() < 0.2]
+    b, J = rng.normal(0, 0.5, 40).astype(np.float32), rng.normal(0, 0.5, len(edges)).astype(np.float32)
+    ebm = T.IsingEBM(big, edges, b, J, 0.7)
+    states = rng.integers(0, 2, (300, 40)).astype(np.float32)
+    batched = ebm.energy_batched(states)
+    s = 2 * states.astype(np.float64) - 1
+    idx = {n: i for i, n in enumerate(big)}
+    ea = np.array([idx[a] for a, _ in edges]); eb = np.array([idx[c] for _, c in edges])
+    want = -0.7 * (s @ b.astype(np.float64) + (s[:, ea] * s[:, eb]) @ J.astype(np.float64))
+    assert np.allclose(batched, want, rtol=1e-6, atol=1e-6)
+    assert abs(ebm.energy([states[5]])[0] - batched[5]) < 1e-5

@@ -516,6 +516,23 @@ class IsingEBM:
     def node_shape_dtypes(self):
         return [self._node_type]
 
+    def energy_batched(self, states, ctx=None):
+        """ising.rs:227-321: states `[batch, n_nodes]` (0/1, node order = self.nodes) -> energies `[batch]`."""
+        states = np.asarray(states, dtype=np.float32)
+        states = states.reshape(-1, len(self.nodes))
+        spec = BlockGibbsSpec([[Block(self.nodes)]], [], self.node_shape_dtypes())
+        prog = BlockSamplingProgram(spec, [SpinGibbsConditional()], [], ctx)
+        st = _eng.ChainState(prog.device_program, states.shape[0])
+        st.upload(0, states)
+        ids = [prog.dense_id(n) for n in self.nodes]
+        edges = np.array([[prog.dense_id(a), prog.dense_id(b)] for a, b in self.edges], dtype=np.int64).reshape(-1, 2)
+        return st.ising_energy(ids, self.biases, edges, self.weights, self.beta_value()).astype(np.float32)
+
+    def energy(self, state, blocks=None, ctx=None):
+        """ising.rs:150-225: energy of one state given as the first block's tensor in node order."""
+        first = state[0] if isinstance(state, (list, tuple)) else state
+        return self.energy_batched(np.asarray(first).reshape(1, -1), ctx)
+
 
 class IsingSamplingProgram:
     """ising.rs:329-389: every free block is its own superblock; SpinGibbsConditional everywhere."""

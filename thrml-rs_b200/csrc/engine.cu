@@ -583,6 +583,49 @@ __global__ void __launch_bounds__(256) k_marginals(const int32_t* node_sd, const
     }
 }
 
+// Ising energy per chain, E = -beta (sum b_i s_i + sum J_ij s_i s_j) (ising.rs:227-321), in f64.  Terms are cut into
+// chunks; each CTA sums one chunk for 128 chains (8 term lanes x 32 chain quads, combined in a fixed order), a second
+// pass adds the chunks in order, so the result does not depend on scheduling.
+constexpr int ENERGY_CHUNK = 2048;
+__global__ void __launch_bounds__(256) k_energy_partial(const int32_t* pos_a, const int32_t* pos_b, const float* w, int64_t n_terms, const uint8_t* spin, int64_t ld,
+                                                        int64_t n_chains, double* partial /*[chunks][ld]*/) {
+    __shared__ double red[8][32][4];
+    const int64_t quad = static_cast<int64_t>(blockIdx.y) * 32 + threadIdx.x;
+    const int64_t t0 = static_cast<int64_t>(blockIdx.x) * ENERGY_CHUNK, t1 = min(n_terms, t0 + ENERGY_CHUNK);
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    if (4 * quad < ld) {
+        for (int64_t t = t0 + threadIdx.y; t < t1; t += 8) {
+            const uint32_t a = *reinterpret_cast<const uint32_t*>(spin + static_cast<int64_t>(pos_a[t]) * ld + 4 * quad);
+            const int32_t pb = pos_b[t];
+            const uint32_t b = pb >= 0 ? *reinterpret_cast<const uint32_t*>(spin + static_cast<int64_t>(pb) * ld + 4 * quad) : 0x01010101u;
+            const double wt = static_cast<double>(w[t]);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t agree = ~(a ^ b) >> (8 * c) & 1u;  // s_a s_b = +1 when the bits agree
+                acc[c] += agree ? wt : -wt;
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[threadIdx.y][threadIdx.x][c] = acc[c];
+    __syncthreads();
+    if (threadIdx.y == 0 && 4 * quad < ld) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            double sum = 0.0;
+            for (int y = 0; y < 8; ++y) sum += red[y][threadIdx.x][c];
+            partial[static_cast<int64_t>(blockIdx.x) * ld + 4 * quad + c] = sum;
+        }
+    }
+}
+__global__ void k_energy_final(const double* partial, int64_t n_chunks, int64_t ld, int64_t n_chains, double neg_beta, double* out) {
+    const int64_t chain = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (chain >= n_chains) return;
+    double sum = 0.0;
+    for (int64_t k = 0; k < n_chunks; ++k) sum += partial[k * ld + chain];
+    out[chain] = neg_beta * sum;
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Host helpers.
 // ---------------------------------------------------------------------------------------------------------
@@ -1344,6 +1387,54 @@ int32_t thrml_state_copy_block(thrml_state* dst, const thrml_state* src, int32_t
     dst->touch(block);
     return THRML_OK;
 }
+int32_t thrml_ising_energy(thrml_state* s, int64_t n_nodes, const int64_t* nodes, const float* biases, int64_t n_edges, const int64_t* edges, const float* weights,
+                           float beta, double* energy_out) {
+    if (!s || !energy_out || n_nodes < 0 || n_edges < 0 || (n_nodes > 0 && (!nodes || !biases)) || (n_edges > 0 && (!edges || !weights)))
+        return fail(THRML_ERR_INVALID_ARG, "bad energy arguments");
+    thrml_program* p = s->prog;
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    cudaStream_t st = p->ctx->stream;
+    const int64_t n_terms = n_nodes + n_edges;
+    std::vector<int32_t> pa(static_cast<size_t>(n_terms)), pb(static_cast<size_t>(n_terms));
+    std::vector<float> w(static_cast<size_t>(n_terms));
+    auto locate = [&](int64_t nd, int32_t* pos) -> int32_t {
+        if (nd < 0 || nd >= static_cast<int64_t>(p->loc_sd.size()) || p->loc_sd[nd] < 0) return fail(THRML_ERR_INVALID_ARG, "Node not found in global location map");
+        if (p->loc_sd[nd] != p->sd_spin) return fail(THRML_ERR_INVALID_ARG, "the Ising energy is defined on spin nodes");
+        *pos = static_cast<int32_t>(p->loc_pos[nd]);
+        return THRML_OK;
+    };
+    for (int64_t i = 0; i < n_nodes; ++i) {
+        if (int32_t rc = locate(nodes[i], &pa[i])) return rc;
+        pb[i] = -1;
+        w[i] = biases[i];
+    }
+    for (int64_t e = 0; e < n_edges; ++e) {
+        if (int32_t rc = locate(edges[2 * e], &pa[n_nodes + e])) return rc;
+        if (int32_t rc = locate(edges[2 * e + 1], &pb[n_nodes + e])) return rc;
+        w[n_nodes + e] = weights[e];
+    }
+    const int64_t n_chunks = std::max<int64_t>(1, (n_terms + ENERGY_CHUNK - 1) / ENERGY_CHUNK);
+    DevBuf d_pa, d_pb, d_w, d_partial, d_out;
+    if (int32_t rc = upload(d_pa, pa.data(), pa.size() * 4, st)) return rc;
+    if (int32_t rc = upload(d_pb, pb.data(), pb.size() * 4, st)) return rc;
+    if (int32_t rc = upload(d_w, w.data(), w.size() * 4, st)) return rc;
+    if (int32_t rc = d_partial.alloc(static_cast<size_t>(n_chunks * s->ld) * 8)) return rc;
+    if (int32_t rc = d_out.alloc(static_cast<size_t>(s->n_chains) * 8)) return rc;
+    CU_TRY(cudaMemsetAsync(d_partial.p, 0, d_partial.bytes, st));
+    if (n_terms > 0) {
+        dim3 grid(static_cast<unsigned>(n_chunks), static_cast<unsigned>((s->ld / 4 + 31) / 32));
+        k_energy_partial<<<grid, dim3(32, 8), 0, st>>>(d_pa.as<int32_t>(), d_pb.as<int32_t>(), d_w.as<float>(), n_terms, s->rows(p->sd_spin), s->ld, s->n_chains,
+                                                       d_partial.as<double>());
+        CU_TRY(cudaGetLastError());
+    }
+    k_energy_final<<<static_cast<unsigned>((s->n_chains + 255) / 256), 256, 0, st>>>(d_partial.as<double>(), n_chunks, s->ld, s->n_chains, -static_cast<double>(beta),
+                                                                                     d_out.as<double>());
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(energy_out, d_out.p, static_cast<size_t>(s->n_chains) * 8, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+
 // sample_single_block (program.rs:324-393): update one free block in place with the given block key.
 int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key) {
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");

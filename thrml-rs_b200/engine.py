@@ -272,6 +272,14 @@ class ChainState:
         nz, keep = _ffi.make_noise(inj)
         check(lib().thrml_run_blocks(self.h, C.c_uint64(int(key)), C.c_int64(n_iters), C.byref(nz) if nz else None))
 
+    def ising_energy(self, nodes, biases, edges, weights, beta):
+        """Per-chain Ising energy of the current state (f64)."""
+        nodes, biases = i64(nodes), f32(biases)
+        edges, weights = i64(edges).reshape(-1, 2), f32(weights)
+        out = np.zeros(self.n_chains, dtype=np.float64)
+        check(lib().thrml_ising_energy(self.h, C.c_int64(len(nodes)), ptr(nodes), ptr(biases), C.c_int64(len(edges)), ptr(edges), ptr(weights), C.c_float(beta), ptr(out)))
+        return out
+
     def sample_single_block(self, block, key):
         check(lib().thrml_sample_single_block(self.h, C.c_int32(block), C.c_uint64(int(key))))
 
