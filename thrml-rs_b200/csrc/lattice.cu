@@ -31,13 +31,37 @@ struct LatArgs {
     int64_t H, W;           // whole lattice
     int64_t row0;           // first global row of the stripe
     int32_t n_rows, words, chains, colour;
-    uint32_t chain_word0, k0, k1;
+    uint32_t chain_word0;
+    uint32_t rk0[10], rk1[10];  // Philox round keys of the block key (k + r * Weyl constant), computed once on the host
 };
 
-// One thread = one word (32 spins of one row and colour) x four chains.
-__global__ void __launch_bounds__(128) k_lattice_update(LatArgs a, int32_t row_begin, int32_t row_end) {
+// Philox4x32-10 with the round keys taken from kernel parameters (constant bank) instead of being re-derived per call.
+__device__ __forceinline__ U4 philox_rk(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const LatArgs& a) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        c0 = hi1 ^ c1 ^ a.rk0[r];
+        c1 = lo1;
+        c2 = hi0 ^ c3 ^ a.rk1[r];
+        c3 = lo0;
+    }
+    return U4{c0, c1, c2, c3};
+}
+
+// One thread = one word (32 spins of one row and colour) x four chains.  The four neighbour bits of each spin are
+// gathered eight spins at a time: a 256-entry shared table spreads a byte of a neighbour word to one bit per nibble, the
+// four spread words are combined with multiply-adds, and each nibble then indexes the threshold table directly.
+__global__ void __launch_bounds__(128) k_lattice_update(const __grid_constant__ LatArgs a, int32_t row_begin, int32_t row_end) {
     __shared__ uint32_t s_lut[9 * 16];
+    __shared__ uint32_t s_spread[256];
     for (int i = threadIdx.x; i < 9 * 16; i += blockDim.x) s_lut[i] = a.lut[i];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+        uint32_t v = 0;
+#pragma unroll
+        for (int bit = 0; bit < 8; ++bit) v |= ((static_cast<uint32_t>(i) >> bit) & 1u) << (4 * bit);
+        s_spread[i] = v;
+    }
     __syncthreads();
     const int quads = a.chains >> 2;
     const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -67,16 +91,30 @@ __global__ void __launch_bounds__(128) k_lattice_update(LatArgs a, int32_t row_b
     const bool first_col = p == 0 && w == 0, last_col = p == 1 && w == a.words - 1;
     const uint32_t node_base = static_cast<uint32_t>(gi * (a.W >> 1) + 32 * static_cast<int64_t>(w));
     uint32_t out[4] = {0, 0, 0, 0};
-#pragma unroll 4
-    for (int k = 0; k < 32; ++k) {
-        const U4 rr = philox4x32_10(node_base + k, a.chain_word0 + q, 0u, TAG_SPIN, a.k0, a.k1);
-        const uint32_t rnd[4] = {rr.x, rr.y, rr.z, rr.w};
-        const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
-        const uint32_t* T = s_lut + (row_cls * 3 + col_cls) * 16;
+#pragma unroll 1
+    for (int g = 0; g < 4; ++g) {
+        // nibble j of P[c] = configuration (up | left<<1 | right<<2 | down<<3) of spin 8g+j of chain c
+        uint32_t P[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const uint32_t cfg = ((U[c] >> k) & 1u) << NB_UP | ((L[c] >> k) & 1u) << NB_LEFT | ((R[c] >> k) & 1u) << NB_RIGHT | ((D[c] >> k) & 1u) << NB_DOWN;
-            out[c] |= (rnd[c] <= T[cfg] ? 1u : 0u) << k;
+            const uint32_t su = s_spread[(U[c] >> (8 * g)) & 0xffu], sl = s_spread[(L[c] >> (8 * g)) & 0xffu];
+            const uint32_t sr = s_spread[(R[c] >> (8 * g)) & 0xffu], sd = s_spread[(D[c] >> (8 * g)) & 0xffu];
+            P[c] = su + 2u * sl + 4u * sr + 8u * sd;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int k = 8 * g + j;
+            const U4 rr = philox_rk(node_base + k, a.chain_word0 + q, 0u, TAG_SPIN, a);
+            const uint32_t rnd[4] = {rr.x, rr.y, rr.z, rr.w};
+            int col_cls = 0;
+            if (j == 0) col_cls = (g == 0 && first_col) ? 1 : 0;
+            if (j == 7) col_cls = (g == 3 && last_col) ? 2 : 0;
+            const uint32_t* T = s_lut + (row_cls * 3 + col_cls) * 16;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t cfg = (P[c] >> (4 * j)) & 15u;
+                out[c] |= (rnd[c] <= T[cfg] ? 1u : 0u) << k;
+            }
         }
     }
     *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
@@ -320,7 +358,11 @@ int32_t thrml_lattice_update(thrml_lattice* L, int32_t colour, uint64_t block_ke
     if (row_begin == row_end) return THRML_OK;
     CU_TRY(cudaSetDevice(L->device));
     LatArgs a{L->p(colour), L->p(1 - colour), static_cast<const uint32_t*>(L->lut.p), L->H, L->W, L->row0, static_cast<int32_t>(L->n_rows), L->words,
-              static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
+              static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), {}, {}};
+    for (int r = 0; r < 10; ++r) {
+        a.rk0[r] = static_cast<uint32_t>(block_key) + static_cast<uint32_t>(r) * 0x9E3779B9u;
+        a.rk1[r] = static_cast<uint32_t>(block_key >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
+    }
     const int64_t threads = (row_end - row_begin) * L->words * (L->n_chains / 4);
     k_lattice_update<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(a, static_cast<int32_t>(row_begin), static_cast<int32_t>(row_end));
     CU_TRY(cudaGetLastError());
