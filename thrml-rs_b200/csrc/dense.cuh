@@ -127,7 +127,8 @@ struct GemmArgs {
     int64_t ld;
     __nv_bfloat16* image_out; // +-1 bf16 image [m_total rows = chains][image_pitch], or null
     int64_t image_pitch;      // elements
-    uint32_t chain_word0, k0, k1;
+    uint32_t chain_word0;
+    PhiloxRoundKeys rk;       // round keys of the block key
     int32_t* ones_out;        // [n_total] number of ones per updated node, accumulated with atomics (zeroed by the caller), or null
     // EPI_CORR
     const int32_t* ones_a;    // [m_total] number of ones per row of A
@@ -152,7 +153,8 @@ template <int BN>
 __host__ __device__ constexpr int stages_for() { return STAGE_BUDGET / ((BM + BN) * BK_BYTES); }
 
 template <int EPI, int BN>
-__global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmArgs g) {
+__global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                                           const __grid_constant__ GemmArgs g) {
     constexpr int KIND_I8 = EPI == EPI_CORR;
     constexpr int STAGES = stages_for<BN>();
     constexpr uint32_t A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -249,7 +251,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
                         const int my_col = col0 + 4 * t + (lane & 3);
-                        const U4 r = philox4x32_10(static_cast<uint32_t>(my_col), g.chain_word0 + static_cast<uint32_t>(row >> 2), 0u, TAG_SPIN, g.k0, g.k1);
+                        const U4 r = philox4x32_10_rk(static_cast<uint32_t>(my_col), g.chain_word0 + static_cast<uint32_t>(row >> 2), 0u, TAG_SPIN, g.rk);
                         uint32_t x[4] = {r.x, r.y, r.z, r.w};
                         quad_transpose(x, lane);
 #pragma unroll

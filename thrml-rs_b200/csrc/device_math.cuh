@@ -37,6 +37,32 @@ __device__ __forceinline__ U4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c
     return U4{c0, c1, c2, c3};
 }
 
+// The same function with the ten round keys (key + r * Weyl constant) supplied by the caller: kernels whose block key is
+// a launch parameter keep them in the parameter (constant) bank, which removes two integer adds per round.
+struct PhiloxRoundKeys {
+    uint32_t k0[10], k1[10];
+};
+inline PhiloxRoundKeys make_round_keys(uint64_t key) {
+    PhiloxRoundKeys rk;
+    for (int r = 0; r < 10; ++r) {
+        rk.k0[r] = static_cast<uint32_t>(key) + static_cast<uint32_t>(r) * 0x9E3779B9u;
+        rk.k1[r] = static_cast<uint32_t>(key >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
+    }
+    return rk;
+}
+__device__ __forceinline__ U4 philox4x32_10_rk(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const PhiloxRoundKeys& rk) {
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        c0 = hi1 ^ c1 ^ rk.k0[r];
+        c1 = lo1;
+        c2 = hi0 ^ c3 ^ rk.k1[r];
+        c3 = lo0;
+    }
+    return U4{c0, c1, c2, c3};
+}
+
 __device__ __forceinline__ uint32_t pick(const U4& v, uint32_t i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
 // 24-bit uniform in [0,1) and 23-bit uniform strictly inside (0,1).

@@ -336,7 +336,7 @@ struct LutArgs {
     int32_t n;
     int32_t n_chunks;      // ld / 16
     uint32_t chain_word0;
-    uint32_t k0, k1;
+    PhiloxRoundKeys rk;    // round keys of the block key
     // fused moment observer (ACC only): row of <s_i> per node, row of <s_i s_j> per (node, slot), -1 = not owned here
     int64_t n_chains;
     const int32_t* m1_row;
@@ -390,7 +390,7 @@ constexpr int ACC_SEGMENT_PASSES = 15;  // 15 passes x 4 words = 60 <= 63
 // owned by the endpoint updated later in the sweep, when both values are final.  Disagreements with each neighbour
 // slot are counted in bit-sliced counters and reduced once per node.
 template <bool ACC>
-__global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
+__global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ LutArgs a) {
     __shared__ uint32_t s_lut[8][LUT_SIZE];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -436,7 +436,7 @@ __global__ void __launch_bounds__(256) k_spin_lut(LutArgs a) {
                 uint32_t o[4];
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    const U4 r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.k0, a.k1);
+                    const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
                     uint32_t w = 0;
                     w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
                     w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
@@ -1220,8 +1220,7 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     g.image_out = write_image ? s->image[block]->as<__nv_bfloat16>() : nullptr;
     g.image_pitch = (bp.n + 63) / 64 * 64;
     g.chain_word0 = static_cast<uint32_t>(s->chain_offset >> 2);
-    g.k0 = k0;
-    g.k1 = k1;
+    g.rk = make_round_keys(static_cast<uint64_t>(k0) | (static_cast<uint64_t>(k1) << 32));
     if (!s->ones[block]) {
         s->ones[block].reset(new DevBuf());
         if (int32_t rc = s->ones[block]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
@@ -1252,8 +1251,8 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     }
     if (!fields) s->touch(block);
     if (bp.base_kernel == 1 && !inj && !fields) {
-        LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, k0, k1,
-                  s->n_chains, nullptr, nullptr, nullptr};
+        LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
+                  make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
             a.m1_row = acc->fused[block]->m1.as<int32_t>();

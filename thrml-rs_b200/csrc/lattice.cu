@@ -32,22 +32,8 @@ struct LatArgs {
     int64_t row0;           // first global row of the stripe
     int32_t n_rows, words, chains, colour;
     uint32_t chain_word0;
-    uint32_t rk0[10], rk1[10];  // Philox round keys of the block key (k + r * Weyl constant), computed once on the host
+    PhiloxRoundKeys rk;  // round keys of the block key, computed once on the host
 };
-
-// Philox4x32-10 with the round keys taken from kernel parameters (constant bank) instead of being re-derived per call.
-__device__ __forceinline__ U4 philox_rk(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, const LatArgs& a) {
-#pragma unroll
-    for (int r = 0; r < 10; ++r) {
-        const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-        const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-        c0 = hi1 ^ c1 ^ a.rk0[r];
-        c1 = lo1;
-        c2 = hi0 ^ c3 ^ a.rk1[r];
-        c3 = lo0;
-    }
-    return U4{c0, c1, c2, c3};
-}
 
 // One thread = one word (32 spins of one row and colour) x four chains.  The four neighbour bits of each spin are
 // gathered eight spins at a time: a 256-entry shared table spreads a byte of a neighbour word to one bit per nibble, the
@@ -104,7 +90,7 @@ __global__ void __launch_bounds__(128) k_lattice_update(const __grid_constant__ 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int k = 8 * g + j;
-            const U4 rr = philox_rk(node_base + k, a.chain_word0 + q, 0u, TAG_SPIN, a);
+            const U4 rr = philox4x32_10_rk(node_base + k, a.chain_word0 + q, 0u, TAG_SPIN, a.rk);
             const uint32_t rnd[4] = {rr.x, rr.y, rr.z, rr.w};
             int col_cls = 0;
             if (j == 0) col_cls = (g == 0 && first_col) ? 1 : 0;
@@ -358,11 +344,7 @@ int32_t thrml_lattice_update(thrml_lattice* L, int32_t colour, uint64_t block_ke
     if (row_begin == row_end) return THRML_OK;
     CU_TRY(cudaSetDevice(L->device));
     LatArgs a{L->p(colour), L->p(1 - colour), static_cast<const uint32_t*>(L->lut.p), L->H, L->W, L->row0, static_cast<int32_t>(L->n_rows), L->words,
-              static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), {}, {}};
-    for (int r = 0; r < 10; ++r) {
-        a.rk0[r] = static_cast<uint32_t>(block_key) + static_cast<uint32_t>(r) * 0x9E3779B9u;
-        a.rk1[r] = static_cast<uint32_t>(block_key >> 32) + static_cast<uint32_t>(r) * 0xBB67AE85u;
-    }
+              static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), make_round_keys(block_key)};
     const int64_t threads = (row_end - row_begin) * L->words * (L->n_chains / 4);
     k_lattice_update<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(a, static_cast<int32_t>(row_begin), static_cast<int32_t>(row_end));
     CU_TRY(cudaGetLastError());
