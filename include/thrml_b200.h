@@ -261,6 +261,12 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
                                       int64_t steps_per_sample, thrml_moments* moments, const int32_t* obs_blocks,
                                       int32_t n_obs_blocks, uint8_t* obs_out, const thrml_noise* inj);
 
+/* sample_states (sampling.rs:128-156) with the StateObserver output (state_observer.rs:25-47) streamed bit-packed:
+ * bits_out[sample][observed node][word] (host, u32), word w = chains 32w .. 32w+31, bit c & 31; observed nodes = the
+ * listed spin blocks concatenated; max(n_samples, 1) samples are written. */
+int32_t thrml_sample_states_packed(thrml_state* s, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample,
+                                   const int32_t* obs_blocks, int32_t n_obs_blocks, uint32_t* bits_out);
+
 /* ------------------------------------------------------------------------------------------------
  * Implicit lattice: a height x width periodic nearest-neighbour Ising lattice with one coupling and one bias, sampled
  * with the two checkerboard blocks, state bit-packed (32 spins per word, chains innermost), held as a stripe of rows

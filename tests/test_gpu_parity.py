@@ -275,3 +275,17 @@ def test_boltzmann_moments_within_4_sigma(T):
         mean = est.mean(axis=1)
         sem = est.std(axis=1, ddof=1) / np.sqrt(chains)
         assert np.all(np.abs(mean - exact) < 4 * sem + 1e-9), np.max(np.abs(mean - exact) / sem)
+
+
+def test_packed_state_streaming_matches_byte_observer(T, O):
+    desc = model_cases(T)["graph8"]
+    for chains in (37, 64, 200):
+        prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 23)
+        prog2, gs2, _, _, _ = make_pair(T, O, desc, chains, 23)
+        blocks = [1, 0, 3]
+        bytes_ = gs.sample_with_observation(11, 2, 5, 2, obs_blocks=blocks)  # [samples][node][chain]
+        bits = gs2.sample_states_packed(11, 2, 5, 2, blocks)
+        assert bits.shape == (5, bytes_.shape[1], (chains + 31) // 32)
+        unpacked = ((bits[:, :, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(5, bytes_.shape[1], -1)[:, :, :chains]
+        assert np.array_equal(unpacked.astype(np.uint8), bytes_)
+        assert np.all(((bits[:, :, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(5, bytes_.shape[1], -1)[:, :, chains:] == 0)

@@ -626,6 +626,19 @@ __global__ void k_energy_final(const double* partial, int64_t n_chunks, int64_t 
     out[chain] = neg_beta * sum;
 }
 
+// Bit-packs spin rows for streaming to the host: out[row][word] bit (c & 31) = state of chain 32*word + c.
+// One warp per (row, group of 32 words); a ballot turns 32 chains into one word.
+__global__ void __launch_bounds__(256) k_pack_rows(const uint8_t* rows, int64_t ld, int64_t n_chains, int64_t n_rows, int64_t words, uint32_t* out) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (row >= n_rows) return;
+    for (int64_t wd = 0; wd < words; ++wd) {
+        const int64_t chain = 32 * wd + threadIdx.x;
+        const uint32_t bit = chain < n_chains ? (rows[row * ld + chain] & 1u) : 0u;
+        const uint32_t word = __ballot_sync(0xffffffffu, bit);
+        if (threadIdx.x == 0) out[row * words + wd] = word;
+    }
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Host helpers.
 // ---------------------------------------------------------------------------------------------------------
@@ -1806,6 +1819,63 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
         }
     }
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    return check_err_flag(s);
+}
+
+// sample_states (sampling.rs:128-156) with the samples streamed to the host bit-packed: bits_out[sample][observed node][word],
+// word w holds chains 32w..32w+31 (bit c & 31).  Spin blocks only.  Samples are packed on the device into a staging
+// buffer and copied out in chunks, so the host link carries one bit per spin instead of one byte (or the reference's f32).
+int32_t thrml_sample_states_packed(thrml_state* s, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample, const int32_t* obs_blocks,
+                                   int32_t n_obs_blocks, uint32_t* bits_out) {
+    if (!s || !obs_blocks || n_obs_blocks <= 0 || !bits_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
+    thrml_program* p = s->prog;
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    cudaStream_t st = p->ctx->stream;
+    int64_t rows = 0;
+    for (int32_t i = 0; i < n_obs_blocks; ++i) {
+        if (int32_t rc = check_block(s, obs_blocks[i])) return rc;
+        if (p->blocks[obs_blocks[i]].is_cat) return fail(THRML_ERR_UNSUPPORTED, "bit-packed streaming is for spin blocks");
+        rows += p->blocks[obs_blocks[i]].n;
+    }
+    const int64_t words = (s->n_chains + 31) / 32;
+    const int64_t per_sample = rows * words;  // u32 per sample
+    const int64_t total_samples = std::max<int64_t>(n_samples, 1);
+    const int64_t chunk = std::max<int64_t>(1, std::min<int64_t>(total_samples, (int64_t(64) << 20) / std::max<int64_t>(per_sample * 4, 1)));
+    DevBuf stage;
+    if (int32_t rc = stage.alloc(static_cast<size_t>(chunk * per_sample) * 4)) return rc;
+    int64_t in_chunk = 0, flushed = 0;
+    auto pack = [&]() -> int32_t {
+        uint32_t* dst = stage.as<uint32_t>() + in_chunk * per_sample;
+        int64_t row = 0;
+        for (int32_t i = 0; i < n_obs_blocks; ++i) {
+            const BlockProg& bp = p->blocks[obs_blocks[i]];
+            k_pack_rows<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, bp.n, words, dst + row * words);
+            CU_TRY(cudaGetLastError());
+            row += bp.n;
+        }
+        if (++in_chunk == chunk) {
+            CU_TRY(cudaMemcpyAsync(bits_out + flushed * per_sample, stage.p, static_cast<size_t>(in_chunk * per_sample) * 4, cudaMemcpyDeviceToHost, st));
+            CU_TRY(cudaStreamSynchronize(st));  // the staging buffer is reused by the next chunk
+            flushed += in_chunk;
+            in_chunk = 0;
+        }
+        return THRML_OK;
+    };
+    uint64_t two[2];
+    rng_split(key, 2, two);
+    if (int32_t rc = run(s, two[0], n_warmup, nullptr)) return rc;
+    if (int32_t rc = pack()) return rc;
+    if (n_samples > 1) {
+        std::vector<uint64_t> keys(static_cast<size_t>(n_samples - 1));
+        rng_split(two[1], n_samples - 1, keys.data());
+        for (int64_t i = 0; i < n_samples - 1; ++i) {
+            if (int32_t rc = run(s, keys[i], steps_per_sample, nullptr)) return rc;
+            if (int32_t rc = pack()) return rc;
+        }
+    }
+    if (in_chunk > 0) CU_TRY(cudaMemcpyAsync(bits_out + flushed * per_sample, stage.p, static_cast<size_t>(in_chunk * per_sample) * 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
     return check_err_flag(s);
 }
 

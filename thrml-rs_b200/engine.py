@@ -304,6 +304,15 @@ class ChainState:
         check(lib().thrml_fields_debug(self.h, C.c_int32(block), ptr(out)))
         return out
 
+    def sample_states_packed(self, key, n_warmup, n_samples, steps_per_sample, obs_blocks):
+        """Samples of the listed spin blocks as bits: uint32 [samples][observed node][ceil(chains/32)]."""
+        ob = i32(obs_blocks)
+        rows = sum(self.program.block_len(int(b)) for b in ob)
+        out = np.zeros((max(int(n_samples), 1), rows, (self.n_chains + 31) // 32), dtype=np.uint32)
+        check(lib().thrml_sample_states_packed(self.h, C.c_uint64(int(key)), C.c_int64(n_warmup), C.c_int64(n_samples), C.c_int64(steps_per_sample), ptr(ob),
+                                               C.c_int32(len(ob)), ptr(out)))
+        return out
+
     def sample_with_observation(self, key, n_warmup, n_samples, steps_per_sample, moments=None, obs_blocks=None, inj=None):
         nz, keep = _ffi.make_noise(inj)
         obs, ob = None, None
