@@ -103,6 +103,16 @@ def batch_gather(w, idx_lists):
     return out
 
 
+def batch_gather_strided(w, idx, strides, batch_stride):
+    w = _f32(w).ravel()
+    idx = np.ascontiguousarray(idx, dtype=np.int32)
+    strides = _i64(strides)
+    out = np.zeros(idx.shape[0], dtype=np.float32)
+    _chk(lib().orc_batch_gather_strided(_p(w, C.c_float), C.c_int64(w.size), C.c_int64(idx.shape[0]), C.c_int32(idx.shape[1]), _p(idx, C.c_int32), _p(strides, C.c_int64),
+                                        C.c_int64(batch_stride), _p(out, C.c_float)))
+    return out
+
+
 def lattice_edges(side_len, torus):
     side = C.c_int64()
     ne = C.c_int64()

@@ -517,6 +517,17 @@ ORC_API int orc_batch_gather(const float* w, int64_t batch, const int32_t* dims,
     }
     return 0;
 }
+// batch_gather_fused with explicit strides — crates/thrml-kernels/src/batch_gather/kernel.rs:38-62,256-280:
+// out[b] = W_flat[b*batch_stride + sum_i idx[b][i]*stride_i]; an index that leaves the tensor yields 0 here.
+ORC_API int orc_batch_gather_strided(const float* w, int64_t w_len, int64_t batch, int32_t n_idx, const int32_t* idx /*[batch][n_idx]*/, const int64_t* strides,
+                                     int64_t batch_stride, float* out) {
+    for (int64_t b = 0; b < batch; b++) {
+        int64_t lin = b * batch_stride;
+        for (int i = 0; i < n_idx; i++) lin += (int64_t)idx[b * n_idx + i] * strides[i];
+        out[b] = (lin >= 0 && lin < w_len) ? w[lin] : 0.0f;
+    }
+    return 0;
+}
 // make_nearest_neighbor_lattice — graph_utils.rs:177-243 (edge order canonicalised to ascending (min,max)).
 ORC_API int orc_lattice_edges(int64_t side_len, int32_t torus, int64_t* side_out, int64_t* n_edges_out, int64_t* edges_out, int32_t* colour_out) {
     if (side_len <= 0) return fail("side_len must be positive");

@@ -96,3 +96,27 @@ def test_deterministic_math_close_to_libm(O):
     for u in np.concatenate([rng.random(2000), 1 - 2.0 ** -np.arange(1, 25), 2.0 ** -np.arange(1, 30), np.linspace(1e-7, 17, 500)]).astype(np.float32):
         if u > 0 and u != 1:
             assert abs(O.det_log(float(u)) - math.log(float(u))) <= 2e-7 * abs(math.log(float(u)))
+
+
+def test_batch_gather_strided_shapes(O):
+    # crates/thrml-kernels/tests/test_batch_gather_extended.rs:12-117: 3 to 8 index dimensions, explicit strides; the
+    # reference asserts the output length only.  Values follow out[b] = W_flat[b*batch_stride + sum idx*stride].
+    w = np.arange(120, dtype=np.float32)
+    out = O.batch_gather_strided(w, [[0, 1, 2], [1, 0, 3]], [60, 20, 1], 60)
+    assert len(out) == 2 and out[0] == 22.0
+    for batch, n_idx, strides, bstride, size in [(4, 4, [16, 4, 2, 1], 64, 4 * 64), (3, 5, [32, 16, 8, 4, 1], 160, 3 * 160), (2, 6, [64, 32, 16, 8, 4, 1], 384, 2 * 384),
+                                                 (4, 7, [64, 32, 16, 8, 4, 2, 1], 256, 4 * 256), (2, 8, [128, 64, 32, 16, 8, 4, 2, 1], 512, 2 * 512)]:
+        out = O.batch_gather_strided(np.ones(size, np.float32), np.zeros((batch, n_idx), np.int32), strides, bstride)
+        assert len(out) == batch and np.all(out == 1.0)
+
+
+def test_gumbel_argmax_scan_equals_tensor_ops(O):
+    # crates/thrml-kernels/src/gumbel_argmax/mod.rs:35-59: the serial scan (fused kernel) and the tensor-op formulation
+    # argmax(logits - ln(-ln u)) pick the same categories on identical uniforms
+    rng = np.random.default_rng(3)
+    logits = rng.normal(0, 5, (100, 100)).astype(np.float32)
+    u = rng.uniform(1e-6, 1 - 1e-6, (100, 100)).astype(np.float32)
+    scan = O.categorical_sample(logits, u, use_libm=True)
+    tensor_ops = np.argmax(logits - np.log(-np.log(u.astype(np.float64))), axis=1)
+    assert np.array_equal(scan.astype(np.int64), tensor_ops)
+    assert np.array_equal(O.categorical_sample(logits, u, use_libm=False).astype(np.int64), tensor_ops)
