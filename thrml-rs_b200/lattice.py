@@ -142,6 +142,7 @@ class DistributedStripe:
         r0, n = stripe_rows(height, self.world)[self.rank]
         self.stripe = LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx)
         self.stream = torch.cuda.ExternalStream(self.stripe.ctx.stream)
+        self.side = torch.cuda.Stream()
         self.views = []
         for colour in (0, 1):
             info = self.stripe.halo_info(colour)
@@ -169,10 +170,31 @@ class DistributedStripe:
         self.refresh_halos(1)
 
     def sample_blocks(self, key):
+        """One sweep.  Per colour the two boundary rows are updated first and sent while the interior rows are still
+        being updated: the exchange runs on a side stream and the next colour waits for it."""
         k = _eng.rng_split(key, 2)
+        n = self.stripe.n_rows
+        torch = self.torch
         for colour in (0, 1):
-            self.stripe.update(colour, int(k[colour]))
-            self.refresh_halos(colour)
+            if self.world == 1 or n < 4:
+                self.stripe.update(colour, int(k[colour]))
+                self.refresh_halos(colour)
+                continue
+            self.stripe.update(colour, int(k[colour]), 0, 1)
+            self.stripe.update(colour, int(k[colour]), n - 1, n)
+            self.side.wait_stream(self.stream)             # boundary rows are final
+            self._exchange(colour, self.side)
+            self.stripe.update(colour, int(k[colour]), 1, n - 1)
+            self.stream.wait_stream(self.side)             # halos of this colour are in place before the other colour reads them
+
+    def _exchange(self, colour, stream):
+        v, dist = self.views[colour], self.dist
+        up, down = (self.rank - 1) % self.world, (self.rank + 1) % self.world
+        with self.torch.cuda.stream(stream):
+            ops = [dist.P2POp(dist.isend, v["send_top"], up), dist.P2POp(dist.isend, v["send_bottom"], down),
+                   dist.P2POp(dist.irecv, v["recv_bottom"], down), dist.P2POp(dist.irecv, v["recv_top"], up)]
+            for req in dist.batch_isend_irecv(ops):
+                req.wait()
 
     def run_blocks(self, key, n_iters):
         for k in _eng.rng_split(key, n_iters) if n_iters > 0 else []:
@@ -180,6 +202,7 @@ class DistributedStripe:
 
     def observe(self):
         """Whole-lattice sums: the stripes' sums added with one small allreduce."""
+        self.stream.synchronize()
         local = self.torch.from_numpy(self.stripe.observe()).cuda()
         if self.world > 1:
             self.dist.all_reduce(local)
