@@ -166,3 +166,32 @@ def test_cd1_step_composition_and_statistics(T, O):
     os_.sample_blocks(k1)
     oneg = s(os_.get_block(0)).T @ s(os_.get_block(1)) / chains
     assert np.abs(oneg - neg).max() < 6 / np.sqrt(chains)
+
+
+def test_moment_observer_survives_enabling_the_dense_path(T, O):
+    """An observer built while the blocks still ran the gather kernels keeps giving exact sums after the program switches
+    them to the tensor-core kernel (its fused row maps are then ignored)."""
+    desc, W, b = rbm(T, 48, 64, 21)
+    gb, ob = M.build_both(T, O, desc)
+    prog = T.Program(gb)
+    spec = [[(i,) for i in range(112)], [(0, 48), (5, 60), (47, 111)]]
+    mom = T.Moments(prog, spec, True)
+    assert prog.enable_dense(False) == 2
+    st = T.ChainState(prog, 64)
+    for i, a in enumerate(M.random_states(desc, 64, 2)):
+        st.upload(i, a)
+    st.sample_with_observation(8, 1, 3, 1, moments=mom)
+    v, h = st.download(0).astype(np.int64), st.download(1).astype(np.int64)
+    # the last observation is the current state; check its contribution through a fresh observer
+    mom2 = T.Moments(prog, spec, True)
+    mom2.observe(st)
+    s_all = 2 * np.concatenate([v, h], axis=1) - 1
+    assert np.array_equal(mom2.read(0)[0], s_all.sum(axis=0))
+    # an identical chain observed by an observer built after the switch accumulates the same sums
+    st_b, mom_b = T.ChainState(prog, 64), T.Moments(prog, spec, True)
+    for i, a in enumerate(M.random_states(desc, 64, 2)):
+        st_b.upload(i, a)
+    st_b.sample_with_observation(8, 1, 3, 1, moments=mom_b)
+    for t in range(2):
+        assert np.array_equal(mom.read(t)[0], mom_b.read(t)[0]) and mom.read(t)[1] == mom_b.read(t)[1] == 3 * 64
+    assert np.array_equal(mom2.read(1)[0], np.array([(s_all[:, a] * s_all[:, c]).sum() for a, c in spec[1]]))

@@ -90,6 +90,7 @@ struct thrml_program {
     std::vector<int64_t> loc_pos;
     std::vector<uint8_t> is_dense_source;  // per block: some dense block reads its +-1 image
     bool any_dense = false;
+    int32_t kernel_epoch = 0;  // bumped whenever a block changes kernel; observers built before that stop fusing
 };
 
 struct thrml_state {
@@ -121,6 +122,7 @@ struct thrml_moments {
     // rows the threshold-table kernels accumulate while they update (per free block), and the rest
     std::vector<std::unique_ptr<FusedMaps>> fused;
     bool any_fused = false;
+    int32_t kernel_epoch = 0;  // program epoch the fused maps were built for
     int64_t n_left = 0;
     DevBuf d_left_ptr, d_left_sd, d_left_pos, d_left_rows;
     int32_t mode = 0;  // 0 products over tuples, 1 per-node category counts
@@ -944,6 +946,7 @@ int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding
         bp.kernel = 3;
         p->is_dense_source[bp.dense_src] = 1;
         p->any_dense = true;
+        ++p->kernel_epoch;
         ++switched;
     }
     if (n_blocks_out) *n_blocks_out = switched;
@@ -1200,10 +1203,11 @@ extern "C++" {
 template <int EPI, int BN>
 static int32_t launch_dense(thrml_state* s, const CUtensorMap& ma, const CUtensorMap& mb, dense::GemmArgs g) {
     constexpr size_t smem = dense::stages_for<BN>() * (dense::BM + BN) * dense::BK_BYTES + 1024;
-    static bool configured = false;
-    if (!configured) {
+    static bool configured[64] = {};  // the attribute is per device
+    const int dev = s->device & 63;
+    if (!configured[dev]) {
         CU_TRY(cudaFuncSetAttribute(dense::k_dense_gemm<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        configured = true;
+        configured[dev] = true;
     }
     g.tiles_m = (g.m_total + dense::BM - 1) / dense::BM;
     g.tiles_n = (g.n_total + BN - 1) / BN;
@@ -1320,7 +1324,7 @@ static int32_t observe_async(thrml_moments* m, thrml_state* s);
 // sample_blocks (sampling.rs:28-63), asynchronous.  With `acc` the sweep is followed by an observation of `acc`:
 // the threshold-table kernels accumulate their rows while they update, one k_moments launch covers the other rows.
 static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_moments* acc = nullptr) {
-    const bool fuse = acc && acc->mode == 0 && acc->any_fused && !inj;
+    const bool fuse = acc && acc->mode == 0 && acc->any_fused && !inj && acc->kernel_epoch == s->prog->kernel_epoch;
     thrml_program* p = s->prog;
     std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
     rng_split(key, p->n_free, keys.data());
@@ -1592,6 +1596,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
     auto m = std::make_unique<thrml_moments>();
     m->prog = p;
     m->device = p->device;
+    m->kernel_epoch = p->kernel_epoch;
     m->spin_transform = transform_to_spin ? 1 : 0;
     m->rows_per_type.assign(rows_per_type, rows_per_type + n_types);
     for (int64_t r : m->rows_per_type) {
