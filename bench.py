@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--chains", type=int, default=CHAINS_PER_GPU, help="chains per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts"],
+    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts", "small_lattice"],
                     help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores (1 GPU); "
                          "lattice = one bit-packed 2-D Ising lattice sharded by row stripes with halo exchange")
     ap.add_argument("--side", type=int, default=32768, help="lattice side (lattice workload)")
@@ -171,6 +171,10 @@ def main():
         if rank == 0:
             print(json.dumps(run_rbm(T, torch, W, args, local_rank)), flush=True)
         return
+    if args.workload == "small_lattice":
+        if rank == 0:
+            print(json.dumps(run_small_lattice(T, torch, args, local_rank)), flush=True)
+        return
     if args.workload == "potts":
         if rank == 0:
             print(json.dumps(run_potts(T, torch, args, local_rank)), flush=True)
@@ -245,7 +249,7 @@ def main():
     result = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
               "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
               "config": workload_config(model, chains, world), "clocks": clocks,
-              "gpu_launches": args.steps * (n_blocks + 1)}
+              "gpu_launches": args.steps * (n_blocks + (1 if moments.fused_info()[1] > 0 else 0))}
 
     # roofline of the block-update kernel: 9 bytes per site update (8 neighbour bytes read, 1 written) + parameters
     peak, peak_src = measured_peak()
@@ -333,6 +337,55 @@ def run_rbm(T, torch, W, args, device):
                          "peak_source": "measured burst bf16 GEMM (MEASURED_PEAKS.json)" if peaks else "fallback 1590", "flop_per_step": flop,
                          "note": "3 bf16 field GEMMs + 2 int8 correlation GEMMs counted at 2*M*N*K each"},
             "e2e": {"value": updates / best, "unit": UNIT, "h2d_bytes_per_step": chains * nv, "d2h_bytes_per_step": 2 * nv * nh * 4, "seconds": best}}
+
+
+def run_small_lattice(T, torch, args, device):
+    """32 x 32 periodic Ising lattice (J = 0.44, biases N(0, 0.1^2), beta = 1), 256 chains, hinton_init, schedule
+    (200 warm-up, 801 samples, 1 step) = 1000 sweeps with <s_i> and <s_i s_j> observed: the whole problem is cache-resident,
+    so this measures launch latency, not bandwidth.  One timed step = the whole 1000-sweep schedule."""
+    rng = np.random.default_rng(0x5EED0001)
+    side, edges, colour = T.lattice_edges(32, True)
+    n = side * side
+    b = rng.normal(0, 0.1, n).astype(np.float32)
+    J = np.full(len(edges), 0.44, np.float32)
+    blocks = [np.flatnonzero(colour == c) for c in (0, 1)]
+    ctx = T.default_context(device)
+    bld = T.Builder(np.zeros(n, np.int32))
+    for blk in blocks:
+        bld.add_free_block(blk)
+    bld.add_ising(np.arange(n), b, edges, J, 1.0)
+    bld.compile()
+    program = T.Program(bld, ctx)
+    chains = 256
+    state = T.ChainState(program, chains)
+    rows_per_type = np.array([n, len(edges)], dtype=np.int64)
+    row_ptr = np.concatenate([np.arange(n + 1), n + 2 * np.arange(1, len(edges) + 1)]).astype(np.int64)
+    members = np.concatenate([np.arange(n), edges.ravel()]).astype(np.int64)
+    moments = T.Moments.from_arrays(program, rows_per_type, row_ptr, members)
+    biases = np.concatenate([b[blk] for blk in blocks])
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def step(i):
+        state.hinton_init([0, 1], biases, 1.0, 7 + i)
+        state.sample_with_observation(2026 + i, 200, 801, 1, moments=moments)
+
+    for i in range(3):
+        step(i)
+    ctx.synchronize()
+    reps = max(1, min(args.steps, 20))
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(reps):
+        step(10 + i)
+    ev1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / reps
+    updates = float(n) * chains * 1000
+    return {"metric": METRIC, "value": updates / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": reps, "warmup": 3, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+            "config": {"workload": "32 x 32 periodic Ising lattice, 256 chains, 1000 sweeps per step with moments", "l2": "cache-resident (256 KiB of state): launch-latency bound"},
+            "gpu_launches": reps * 2001, "e2e": None}
 
 
 def run_potts(T, torch, args, device):

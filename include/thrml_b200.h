@@ -247,6 +247,9 @@ int32_t thrml_moments_read(thrml_moments* m, int32_t type, int64_t* sums_out, in
  * multi-GPU host hands to its single allreduce(sum). */
 int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_t* count_out);
 int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs);
+/* How the rows are served when the observer follows a sweep: rows the update kernels accumulate themselves (single
+ * spins and neighbour pairs of threshold-table blocks) and rows left to the separate observer kernel. */
+int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, int64_t* n_other_rows);
 
 /* Per-node category counts for the nodes of the listed blocks (counts[node][category], int64), the
  * category-marginal observable of the Potts configuration.  K = table width. */

@@ -1774,6 +1774,13 @@ int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_
     if (count_out) *count_out = m->total_rows;
     return THRML_OK;
 }
+int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, int64_t* n_other_rows) {
+    if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
+    const int64_t other = m->any_fused ? m->n_left : m->total_rows;
+    if (n_fused_rows) *n_fused_rows = m->total_rows - other;
+    if (n_other_rows) *n_other_rows = other;
+    return THRML_OK;
+}
 int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs) {
     if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
     m->n_obs += n_obs;

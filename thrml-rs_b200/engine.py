@@ -383,6 +383,12 @@ class Moments:
         check(lib().thrml_moments_read(self.h, C.c_int32(t), ptr(out), C.byref(n)))
         return out, n.value
 
+    def fused_info(self):
+        """(rows accumulated by the update kernels, rows left to the observer kernel)."""
+        a, b = C.c_int64(), C.c_int64()
+        check(lib().thrml_moments_fused_info(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def device_buffer(self):
         p, cnt = C.c_void_p(), C.c_int64()
         check(lib().thrml_moments_device_buffer(self.h, C.byref(p), C.byref(cnt)))
