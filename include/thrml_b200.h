@@ -250,6 +250,11 @@ int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs);
 /* How the rows are served when the observer follows a sweep: rows the update kernels accumulate themselves (single
  * spins and neighbour pairs of threshold-table blocks) and rows left to the separate observer kernel. */
 int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, int64_t* n_other_rows);
+/* Kernel launches this state has issued for block updates so far: ordinary per-block launches, and launches of the
+ * persistent multi-sweep kernel that small all-threshold-table programs use inside thrml_run_blocks /
+ * thrml_sample_with_observation / thrml_sample_states_packed (one launch covers up to 4096 block updates).
+ * No counterpart in the reference; hosts use it to count launches and tests to see which path ran. */
+int32_t thrml_state_launch_counts(const thrml_state* s, int64_t* block_launches, int64_t* persistent_launches);
 
 /* Per-node category counts for the nodes of the listed blocks (counts[node][category], int64), the
  * category-marginal observable of the Potts configuration.  K = table width. */

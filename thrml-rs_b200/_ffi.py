@@ -71,6 +71,7 @@ _SIGNATURES = {
     "thrml_moments_device_buffer": (C.c_int32, [_P, _P, _P]),
     "thrml_moments_add_observations": (C.c_int32, [_P, C.c_int64]),
     "thrml_moments_fused_info": (C.c_int32, [_P, _P, _P]),
+    "thrml_state_launch_counts": (C.c_int32, [_P, _P, _P]),
     "thrml_marginals_create": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P]),
     "thrml_sample_states_packed": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, _P, C.c_int32, _P]),
     "thrml_lattice_create": (C.c_int32, [_P, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_int64, C.c_int64, _P]),

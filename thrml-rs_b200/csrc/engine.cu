@@ -15,6 +15,8 @@
 
 using namespace thrml;
 
+#include <cooperative_groups.h>
+
 #include "ctx.h"
 
 constexpr int MAX_TAILS = 8;
@@ -63,6 +65,7 @@ struct BlockProg {
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
+    int32_t max_deg = 0;         // largest number of neighbour slots any node of the block uses (threshold-table blocks)
     int32_t order = -1;          // position of the block's superblock in the sweep; -1 for clamped blocks
     // dense bipartite path (kernel 3): every neighbour of every node lies in block `dense_src`
     int32_t dense_src = -1;      // candidate source block, -1 when the block does not qualify
@@ -106,6 +109,13 @@ struct thrml_state {
     std::vector<CUtensorMap> map_image;
     std::vector<std::unique_ptr<DevBuf>> ones;
     DevBuf d_err, d_corr;
+    // sweeps queued for the persistent kernel (cache-resident programs): (sweep key, observer to accumulate or null)
+    std::vector<std::pair<uint64_t, thrml_moments*>> pending;
+    DevBuf d_plan, d_plan_acc, d_slice_blocks;
+    int persist_grid = 0;  // CTAs of the persistent kernel (all co-resident), 0 = not eligible
+    bool sliced = false;   // the chain-sliced kernel serves the queue instead (four chains of every spin fit in shared memory)
+    int64_t persist_epoch = -1;  // program kernel_epoch persist_grid was computed for
+    int64_t persistent_launches = 0, block_launches = 0;
     int64_t image_rows = 0;
     void touch(int32_t block) { if (!image_fresh.empty()) { image_fresh[block] = 0; ones_fresh[block] = 0; } }
     uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
@@ -391,12 +401,12 @@ constexpr int ACC_SEGMENT_PASSES = 15;  // 15 passes x 4 words = 60 <= 63
 // that updates node i is the only one that touches i's rows, so the sums are updated without atomics.  A pair row is
 // owned by the endpoint updated later in the sweep, when both values are final.  Disagreements with each neighbour
 // slot are counted in bit-sliced counters and reduced once per node.
-template <bool ACC>
-__global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ LutArgs a) {
-    __shared__ uint32_t s_lut[8][LUT_SIZE];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+// COHERENT: neighbour rows may have been written earlier in the same launch (persistent multi-sweep kernel), so they are
+// read through L2 (ld.global.cg) instead of the read-only path.
+template <bool ACC, bool COHERENT>
+__device__ __forceinline__ void lut_block_update(const LutArgs& a, uint32_t* my) {
+    const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
-    uint32_t* my = s_lut[wid];
     for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
         const uint4* src = reinterpret_cast<const uint4*>(a.lut + static_cast<int64_t>(node) * LUT_SIZE);
         __syncwarp();
@@ -425,7 +435,10 @@ __global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ Lut
 #pragma unroll
                 for (int j = 0; j < LUT_BITS; ++j) {
                     v[j] = make_uint4(0, 0, 0, 0);
-                    if (nbj[j] >= 0) v[j] = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch);
+                    if (nbj[j] >= 0) {
+                        const uint4* src_row = reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch;
+                        v[j] = COHERENT ? __ldcg(src_row) : __ldg(src_row);
+                    }
                 }
                 uint32_t cfg[4] = {0, 0, 0, 0};
 #pragma unroll
@@ -476,9 +489,200 @@ __global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ Lut
         }
         if (ACC && my_row >= 0) {
             const long long val = lane == LUT_BITS ? 2ll * mine - a.n_chains : a.n_chains - 2ll * mine;
-            a.sums[my_row] += val;
+            if (COHERENT) __stcg(a.sums + my_row, __ldcg(a.sums + my_row) + val);
+            else a.sums[my_row] += val;
         }
     }
+}
+
+template <bool ACC>
+__global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ LutArgs a) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    lut_block_update<ACC, false>(a, s_lut[threadIdx.x >> 5]);
+}
+
+// Persistent multi-sweep variant for cache-resident programs: one cooperative launch walks a list of block updates
+// (sweep-major, blocks in sampling order) with a grid-wide barrier after each, instead of one launch per block update.
+// For small models a block update takes a microsecond or two and the launches themselves dominate.
+__global__ void __launch_bounds__(256, 2) k_spin_lut_persistent(const LutArgs* steps, const uint8_t* acc, int32_t n_steps) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    for (int32_t i = 0; i < n_steps; ++i) {
+        const LutArgs a = steps[i];  // by value: the round keys stay in registers across the update's stores
+        if (__ldg(acc + i)) lut_block_update<true, true>(a, s_lut[threadIdx.x >> 5]);
+        else lut_block_update<false, true>(a, s_lut[threadIdx.x >> 5]);
+        grid.sync();
+    }
+}
+
+// Chain-sliced variant for programs small enough that four chains of every spin fit in one CTA's shared memory.
+// Chains never interact, so a CTA that owns chains 4q..4q+3 can run a whole schedule on its own: it loads one 32-bit
+// word per spin (4 chains), walks the list of block updates with a CTA barrier after each, and stores the words back.
+// No grid barrier, no launch per block.  One thread updates one node for the four chains with exactly one Philox call
+// (the four output words are the four chains' draws), so the states are the bits the other kernels produce.
+// The fused observer keeps signed per-row partial sums in shared memory (each row is owned by one node, hence by one
+// thread) and adds them to the global sums once at the end.
+struct SliceBlock {
+    const int32_t* nbr;    // [n][8]
+    const uint32_t* lut;   // [n][256]
+    const int32_t* m1_row; // [n] or null
+    const int32_t* m2_row; // [n][8] or null
+    int32_t n;
+    int32_t offset;        // first global spin position of the block
+    int32_t lut_shift;     // resident copy: 2^lut_shift table entries per node (the block's largest neighbour count)
+    int32_t smem_word;     // resident copy: first word of this block's tables in dynamic shared memory
+};
+struct SliceStep {
+    int32_t block;
+    int32_t acc;
+    PhiloxRoundKeys rk;
+};
+static_assert(sizeof(SliceStep) == 88, "SliceStep is copied word by word");
+constexpr int SLICE_MAX_BLOCKS = 32;
+struct SliceArgs {
+    const SliceBlock* blocks;
+    const SliceStep* steps;
+    int32_t n_blocks;
+    int32_t n_steps;
+    int32_t n_spin;    // spins of the class (free and clamped)
+    int32_t n_rows;    // observer rows (0 without observer)
+    int32_t resident;  // 1: neighbour lists, the reachable part of the threshold tables and the observer's row maps are copied to shared memory first
+    uint32_t chain_word0;
+    uint8_t* spin;
+    int64_t ld;
+    int64_t n_chains;
+    unsigned long long* sums;
+};
+constexpr int SLICE_STEP_WORDS = sizeof(SliceStep) / 4;
+// words of dynamic shared memory a block's resident tables take: neighbours, compact thresholds, observer row maps
+// (rounded to 16 bytes; the two arrays read with 16-byte loads come first)
+inline int64_t slice_block_words(int64_t n, int lut_shift, bool acc) {
+    const int64_t n_pad = (n + 31) / 32 * 32;
+    return (n * LUT_BITS + (n_pad << lut_shift) + (acc ? n * (1 + LUT_BITS) : 0) + 3) / 4 * 4;
+}
+
+// RESIDENT: neighbour lists, the reachable part of the threshold tables and the observer's row maps are copied into
+// shared memory first (word offsets into s_dyn; thresholds entry-major with a node stride that is a multiple of 32, so
+// consecutive nodes hit distinct banks whatever their configurations); otherwise they are read from global memory.
+struct SliceView {
+    const int32_t* nbr;
+    const uint32_t* lut;
+    const int32_t* m1;
+    const int32_t* m2;
+    int32_t nbr_w, lut_w, m1_w, m2_w;  // resident: first words in s_dyn (m1_w < 0: no observer rows)
+    int32_t n, offset, n_pad;
+};
+template <bool RESIDENT>
+__global__ void __launch_bounds__(512) k_spin_lut_sliced(const __grid_constant__ SliceArgs a) {
+    extern __shared__ __align__(16) uint32_t s_dyn[];
+    __shared__ SliceStep s_step[2];
+    __shared__ SliceView s_blk[SLICE_MAX_BLOCKS];
+    uint32_t* st = s_dyn;                                          // [n_spin]
+    int32_t* part = reinterpret_cast<int32_t*>(s_dyn + a.n_spin);  // [n_rows]
+    const int32_t* sw = reinterpret_cast<const int32_t*>(s_dyn);
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int quad = blockIdx.x;
+    const int64_t remaining = a.n_chains - 4ll * quad;
+    const int left = remaining >= 4 ? 4 : static_cast<int>(remaining);  // chains of this slice that exist
+    const uint32_t vm = left >= 4 ? 0xffffffffu : (0xffffffffu >> (8 * (4 - left)));
+    for (int i = tid; i < a.n_spin; i += T) st[i] = *reinterpret_cast<const uint32_t*>(a.spin + static_cast<int64_t>(i) * a.ld + 4 * quad);
+    for (int i = tid; i < a.n_rows; i += T) part[i] = 0;
+    if (tid < SLICE_STEP_WORDS) reinterpret_cast<uint32_t*>(&s_step[0])[tid] = __ldg(reinterpret_cast<const uint32_t*>(a.steps) + tid);
+    if (tid < a.n_blocks) {
+        const SliceBlock b = a.blocks[tid];
+        SliceView v;
+        v.nbr = b.nbr; v.lut = b.lut; v.m1 = b.m1_row; v.m2 = b.m2_row;
+        v.n = b.n; v.offset = b.offset; v.n_pad = (b.n + 31) / 32 * 32;
+        v.nbr_w = b.smem_word;
+        v.m2_w = v.nbr_w + b.n * LUT_BITS;
+        v.lut_w = b.m1_row ? v.m2_w + b.n * LUT_BITS : v.m2_w;
+        v.m1_w = b.m1_row ? v.lut_w + (v.n_pad << b.lut_shift) : -1;
+        s_blk[tid] = v;
+    }
+    __syncthreads();
+    if (RESIDENT) {
+        for (int bi = 0; bi < a.n_blocks; ++bi) {
+            const SliceView& v = s_blk[bi];
+            const int shift = a.blocks[bi].lut_shift, per = 1 << shift;
+            int32_t* w = reinterpret_cast<int32_t*>(s_dyn);
+            for (int i = tid; i < v.n * LUT_BITS; i += T) w[v.nbr_w + i] = __ldg(v.nbr + i);
+            for (int i = tid; i < v.n * per; i += T) {
+                const int node = i >> shift, c = i & (per - 1);
+                s_dyn[v.lut_w + c * v.n_pad + node] = __ldg(v.lut + static_cast<int64_t>(node) * LUT_SIZE + c);
+            }
+            if (v.m1_w >= 0) {
+                for (int i = tid; i < v.n; i += T) w[v.m1_w + i] = __ldg(v.m1 + i);
+                for (int i = tid; i < v.n * LUT_BITS; i += T) w[v.m2_w + i] = __ldg(v.m2 + i);
+            }
+        }
+        __syncthreads();
+    }
+    for (int32_t i = 0; i < a.n_steps; ++i) {
+        const SliceStep& sp = s_step[i & 1];
+        const SliceView& v = s_blk[sp.block];
+        const int32_t n = v.n;
+        const bool acc = sp.acc != 0;
+        for (int node = tid; node < n; node += T) {
+            int4 n0, n1;
+            if (RESIDENT) {
+                n0 = *reinterpret_cast<const int4*>(sw + v.nbr_w + node * LUT_BITS);
+                n1 = *reinterpret_cast<const int4*>(sw + v.nbr_w + node * LUT_BITS + 4);
+            } else {
+                n0 = __ldg(reinterpret_cast<const int4*>(v.nbr + static_cast<int64_t>(node) * LUT_BITS));
+                n1 = __ldg(reinterpret_cast<const int4*>(v.nbr + static_cast<int64_t>(node) * LUT_BITS) + 1);
+            }
+            const int32_t nb[LUT_BITS] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+            uint32_t cfg = 0;
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j)
+                if (nb[j] >= 0) cfg += st[nb[j]] << j;
+            uint32_t t0, t1, t2, t3;
+            if (RESIDENT) {  // configuration bytes stay below 2^(neighbour count), inside the copied part of the table
+                const uint32_t* L = s_dyn + v.lut_w + node;
+                t0 = L[(cfg & 0xffu) * v.n_pad];
+                t1 = L[((cfg >> 8) & 0xffu) * v.n_pad];
+                t2 = L[((cfg >> 16) & 0xffu) * v.n_pad];
+                t3 = L[(cfg >> 24) * v.n_pad];
+            } else {
+                const uint32_t* L = v.lut + static_cast<int64_t>(node) * LUT_SIZE;
+                t0 = __ldg(L + (cfg & 0xffu));
+                t1 = __ldg(L + ((cfg >> 8) & 0xffu));
+                t2 = __ldg(L + ((cfg >> 16) & 0xffu));
+                t3 = __ldg(L + (cfg >> 24));
+            }
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, sp.rk);
+            uint32_t o = (r.x <= t0) ? 1u : 0u;
+            o |= (r.y <= t1) ? 0x100u : 0u;
+            o |= (r.z <= t2) ? 0x10000u : 0u;
+            o |= (r.w <= t3) ? 0x1000000u : 0u;
+            st[v.offset + node] = o;  // neighbours are never in the block being updated, so nobody reads this word before the barrier
+            if (acc && v.m1_w >= 0) {
+                int32_t row1;
+                int4 r0, r1;
+                if (RESIDENT) {
+                    row1 = sw[v.m1_w + node];
+                    r0 = *reinterpret_cast<const int4*>(sw + v.m2_w + node * LUT_BITS);
+                    r1 = *reinterpret_cast<const int4*>(sw + v.m2_w + node * LUT_BITS + 4);
+                } else {
+                    row1 = __ldg(v.m1 + node);
+                    r0 = __ldg(reinterpret_cast<const int4*>(v.m2 + static_cast<int64_t>(node) * LUT_BITS));
+                    r1 = __ldg(reinterpret_cast<const int4*>(v.m2 + static_cast<int64_t>(node) * LUT_BITS) + 1);
+                }
+                if (row1 >= 0) part[row1] += 2 * __popc(o & vm) - left;
+                const int32_t rows[LUT_BITS] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+                const uint32_t d = (cfg ^ (o * 255u)) & vm;  // bit j of a byte: neighbour j differs from the new spin
+#pragma unroll
+                for (int j = 0; j < LUT_BITS; ++j)
+                    if (rows[j] >= 0) part[rows[j]] += left - 2 * __popc(d & (0x01010101u << j));
+            }
+        }
+        if (i + 1 < a.n_steps && tid < SLICE_STEP_WORDS)
+            reinterpret_cast<uint32_t*>(&s_step[(i + 1) & 1])[tid] = __ldg(reinterpret_cast<const uint32_t*>(a.steps + i + 1) + tid);
+        __syncthreads();
+    }
+    for (int i = tid; i < a.n_spin; i += T) *reinterpret_cast<uint32_t*>(a.spin + static_cast<int64_t>(i) * a.ld + 4 * quad) = st[i];
+    for (int i = tid; i < a.n_rows; i += T)
+        if (part[i] != 0) atomicAdd(a.sums + i, static_cast<unsigned long long>(static_cast<long long>(part[i])));
 }
 
 // hinton_init (ising.rs:602-673) and uniform start.  One thread = one node x four chains.
@@ -812,6 +1016,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                     }
                     if (!lut_ok) break;
                 }
+                bp.max_deg = std::max(bp.max_deg, cnt);
             }
             if (lut_ok) {
                 if (int32_t rc = upload(bp.d_nbr, nbr.data(), nbr.size() * 4, ctx->stream)) return rc;
@@ -1262,6 +1467,7 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     const uint32_t k0 = static_cast<uint32_t>(key), k1 = static_cast<uint32_t>(key >> 32);
     const uint32_t word0 = static_cast<uint32_t>(s->chain_offset >> 2);
     const bool to_state = dst == s->rows(bp.sd) + bp.offset * s->ld;
+    if (!fields) ++s->block_launches;
     if (bp.kernel == 3 && !inj && !fields && to_state) {
         if (int32_t rc = dense_update(s, block, k0, k1)) return rc;
         return THRML_OK;
@@ -1362,13 +1568,176 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_momen
     acc->n_obs += s->n_chains;
     return THRML_OK;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Persistent sweeps for small programs.
+//
+// When every free block runs the threshold-table kernel, nothing is staged and one sweep touches little enough
+// state to live in L2, a block update takes a microsecond or two and a schedule of thousands of sweeps is bound
+// by its launches.  run() then queues its sweeps instead of launching them, and the queue is flushed as ONE
+// cooperative launch of k_spin_lut_persistent per PERSIST_MAX_STEPS block updates.  Results are the same bits:
+// the same per-block keys, the same update function, a grid-wide barrier where a kernel boundary used to be.
+constexpr int64_t PERSIST_MAX_SWEEP_BYTES = int64_t(8) << 20;  // nodes x chains updated by one sweep
+constexpr size_t PERSIST_MAX_STEPS = 4096;
+constexpr size_t SLICE_MAX_STEPS = 16384;     // block updates per launch of the chain-sliced kernel
+constexpr size_t SLICE_MAX_SMEM = 200 * 1024;  // state words + observer partial sums of one chain slice
+
+static int persistent_grid(thrml_state* s) {
+    thrml_program* p = s->prog;
+    if (s->persist_epoch == p->kernel_epoch) return s->persist_grid;
+    s->persist_epoch = p->kernel_epoch;
+    s->persist_grid = 0;
+    int64_t bytes = 0, max_n = 0;
+    for (size_t g = 0; g < p->sampling_order.size(); ++g) {
+        if (p->staged[g]) return 0;
+        for (int32_t m : p->sampling_order[g]) {
+            const BlockProg& bp = p->blocks[m];
+            if (bp.kernel != 1 || bp.base_kernel != 1) return 0;
+            bytes += bp.n * s->ld;
+            max_n = std::max(max_n, bp.n);
+        }
+    }
+    if (p->n_free < 1 || bytes > PERSIST_MAX_SWEEP_BYTES) return 0;
+    s->sliced = static_cast<size_t>(p->class_size[p->sd_spin]) * 4 <= SLICE_MAX_SMEM && p->n_free <= SLICE_MAX_BLOCKS;
+    if (s->sliced) return s->persist_grid = 1;
+    int coop = 0, per_sm = 0;
+    if (cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, p->ctx->device) != cudaSuccess || !coop) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_spin_lut_persistent, 256, 0) != cudaSuccess || per_sm < 1) return 0;
+    const int64_t resident = static_cast<int64_t>(per_sm) * p->ctx->sm_count;
+    s->persist_grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(resident, (max_n + 7) / 8)));
+    return s->persist_grid;
+}
+static bool observer_rides_along(const thrml_moments* acc, const thrml_state* s) {
+    if (!(acc->mode == 0 && acc->any_fused && acc->n_left == 0 && acc->kernel_epoch == s->prog->kernel_epoch && acc->prog == s->prog)) return false;
+    if (s->sliced && static_cast<size_t>(s->prog->class_size[s->prog->sd_spin] + acc->total_rows) * 4 > SLICE_MAX_SMEM) return false;
+    for (const auto& sw : s->pending)  // one observer per queue
+        if (sw.second && sw.second != acc) return false;
+    return true;
+}
+static int32_t flush_sliced(thrml_state* s) {
+    thrml_program* p = s->prog;
+    cudaStream_t st = p->ctx->stream;
+    thrml_moments* acc = nullptr;
+    for (const auto& sw : s->pending)
+        if (sw.second) acc = sw.second;
+    std::vector<SliceBlock> blocks(static_cast<size_t>(p->n_free));
+    const int64_t n_spin = p->class_size[p->sd_spin], n_rows = acc ? acc->total_rows : 0;
+    int64_t max_n = 0, words = (n_spin + n_rows + 3) / 4 * 4;
+    const int64_t base_words = words;
+    for (int32_t m = 0; m < p->n_free; ++m) {
+        const BlockProg& bp = p->blocks[m];
+        const bool f = acc && acc->fused[m];
+        blocks[m] = SliceBlock{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), f ? acc->fused[m]->m1.as<int32_t>() : nullptr, f ? acc->fused[m]->m2.as<int32_t>() : nullptr,
+                               static_cast<int32_t>(bp.n), static_cast<int32_t>(bp.offset), bp.max_deg, static_cast<int32_t>(words)};
+        words += slice_block_words(bp.n, bp.max_deg, f);
+        max_n = std::max(max_n, bp.n);
+    }
+    const bool resident = static_cast<size_t>(words) * 4 <= SLICE_MAX_SMEM;
+    std::vector<SliceStep> steps;
+    std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
+    steps.reserve(s->pending.size() * static_cast<size_t>(p->n_free));
+    for (const auto& sw : s->pending) {
+        rng_split(sw.first, p->n_free, keys.data());
+        for (const auto& members : p->sampling_order)
+            for (int32_t m : members) steps.push_back(SliceStep{m, sw.second && blocks[m].m1_row ? 1 : 0, make_round_keys(keys[m])});
+        if (sw.second) sw.second->n_obs += s->n_chains;
+    }
+    s->pending.clear();
+    for (int32_t m = 0; m < p->n_free; ++m) s->touch(m);
+    if (s->d_slice_blocks.bytes < blocks.size() * sizeof(SliceBlock))
+        if (int32_t rc = s->d_slice_blocks.alloc(blocks.size() * sizeof(SliceBlock))) return rc;
+    if (s->d_plan.bytes < steps.size() * sizeof(SliceStep))
+        if (int32_t rc = s->d_plan.alloc(std::max(steps.size() * sizeof(SliceStep), PERSIST_MAX_STEPS * sizeof(LutArgs)))) return rc;
+    // pageable sources: the copies have been staged by the time the calls return
+    CU_TRY(cudaMemcpyAsync(s->d_slice_blocks.p, blocks.data(), blocks.size() * sizeof(SliceBlock), cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(s->d_plan.p, steps.data(), steps.size() * sizeof(SliceStep), cudaMemcpyHostToDevice, st));
+    SliceArgs a{s->d_slice_blocks.as<SliceBlock>(), s->d_plan.as<SliceStep>(), p->n_free, static_cast<int32_t>(steps.size()), static_cast<int32_t>(n_spin),
+                static_cast<int32_t>(n_rows), resident ? 1 : 0, static_cast<uint32_t>(s->chain_offset >> 2), s->rows(p->sd_spin), s->ld, s->n_chains,
+                acc ? acc->d_sums.as<unsigned long long>() : nullptr};
+    const size_t smem = static_cast<size_t>(resident ? words : base_words) * 4;
+    static bool configured[64] = {};  // the attribute is per device
+    if (!configured[s->device & 63]) {
+        CU_TRY(cudaFuncSetAttribute(k_spin_lut_sliced<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SLICE_MAX_SMEM)));
+        CU_TRY(cudaFuncSetAttribute(k_spin_lut_sliced<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(SLICE_MAX_SMEM)));
+        configured[s->device & 63] = true;
+    }
+    const int threads = static_cast<int>(std::min<int64_t>(512, std::max<int64_t>(64, (max_n + 31) / 32 * 32)));
+    const unsigned grid = static_cast<unsigned>((s->n_chains + 3) / 4);
+    if (resident) k_spin_lut_sliced<true><<<grid, threads, smem, st>>>(a);
+    else k_spin_lut_sliced<false><<<grid, threads, smem, st>>>(a);
+    CU_TRY(cudaGetLastError());
+    ++s->persistent_launches;
+    return THRML_OK;
+}
+static int32_t flush_pending(thrml_state* s) {
+    if (s->pending.empty()) return THRML_OK;
+    if (s->sliced) return flush_sliced(s);
+    thrml_program* p = s->prog;
+    cudaStream_t st = p->ctx->stream;
+    const uint32_t word0 = static_cast<uint32_t>(s->chain_offset >> 2);
+    std::vector<LutArgs> steps;
+    std::vector<uint8_t> accf;
+    std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
+    steps.reserve(s->pending.size() * static_cast<size_t>(p->n_free));
+    for (const auto& sw : s->pending) {
+        rng_split(sw.first, p->n_free, keys.data());
+        thrml_moments* acc = sw.second;
+        for (const auto& members : p->sampling_order)
+            for (int32_t m : members) {
+                const BlockProg& bp = p->blocks[m];
+                LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), s->rows(bp.sd) + bp.offset * s->ld, s->ld, static_cast<int32_t>(bp.n),
+                          static_cast<int32_t>(s->ld / 16), word0, make_round_keys(keys[m]), s->n_chains, nullptr, nullptr, nullptr};
+                uint8_t f = 0;
+                if (acc && acc->fused[m]) {
+                    a.m1_row = acc->fused[m]->m1.as<int32_t>();
+                    a.m2_row = acc->fused[m]->m2.as<int32_t>();
+                    a.sums = acc->d_sums.as<long long>();
+                    f = 1;
+                }
+                steps.push_back(a);
+                accf.push_back(f);
+            }
+        if (acc) acc->n_obs += s->n_chains;
+    }
+    s->pending.clear();
+    for (int32_t m = 0; m < p->n_free; ++m) s->touch(m);
+    const int grid = s->persist_grid;
+    for (size_t at = 0; at < steps.size(); at += PERSIST_MAX_STEPS) {
+        const size_t cnt = std::min(PERSIST_MAX_STEPS, steps.size() - at);
+        if (s->d_plan.bytes < cnt * sizeof(LutArgs))
+            if (int32_t rc = s->d_plan.alloc(PERSIST_MAX_STEPS * sizeof(LutArgs))) return rc;
+        if (s->d_plan_acc.bytes < cnt)
+            if (int32_t rc = s->d_plan_acc.alloc(PERSIST_MAX_STEPS)) return rc;
+        // pageable sources: both copies have been staged by the time the calls return, so `steps` may be reused
+        CU_TRY(cudaMemcpyAsync(s->d_plan.p, steps.data() + at, cnt * sizeof(LutArgs), cudaMemcpyHostToDevice, st));
+        CU_TRY(cudaMemcpyAsync(s->d_plan_acc.p, accf.data() + at, cnt, cudaMemcpyHostToDevice, st));
+        const LutArgs* d_steps = s->d_plan.as<LutArgs>();
+        const uint8_t* d_acc = s->d_plan_acc.as<uint8_t>();
+        int32_t n_steps = static_cast<int32_t>(cnt);
+        void* args[] = {&d_steps, &d_acc, &n_steps};
+        CU_TRY(cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(k_spin_lut_persistent), dim3(static_cast<unsigned>(grid)), dim3(256), args, 0, st));
+        ++s->persistent_launches;
+    }
+    return THRML_OK;
+}
+
 // run_blocks (sampling.rs:81-106), asynchronous; `acc` (nullable) is observed after the last sweep.
 static int32_t run(thrml_state* s, uint64_t key, int64_t n_iters, NoiseCursor* inj, thrml_moments* acc = nullptr) {
     if (n_iters <= 0) return acc ? observe_async(acc, s) : THRML_OK;
     std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
     rng_split(key, n_iters, keys.data());
-    for (int64_t i = 0; i < n_iters; ++i)
-        if (int32_t rc = sweep(s, keys[i], inj, i + 1 == n_iters ? acc : nullptr)) return rc;
+    const bool queue = !inj && persistent_grid(s) > 0;
+    for (int64_t i = 0; i < n_iters; ++i) {
+        thrml_moments* a = i + 1 == n_iters ? acc : nullptr;
+        if (queue && (!a || observer_rides_along(a, s))) {
+            s->pending.emplace_back(keys[i], a);
+            if (s->pending.size() * static_cast<size_t>(s->prog->n_free) >= (s->sliced ? SLICE_MAX_STEPS : PERSIST_MAX_STEPS))
+                if (int32_t rc = flush_pending(s)) return rc;
+            continue;
+        }
+        if (int32_t rc = flush_pending(s)) return rc;
+        if (int32_t rc = sweep(s, keys[i], inj, a)) return rc;
+    }
     return THRML_OK;
 }
 
@@ -1388,6 +1757,7 @@ int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const th
     NoiseCursor nc;
     if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
     if (int32_t rc = run(s, key, n_iters, nc.u ? &nc : nullptr)) return rc;
+    if (int32_t rc = flush_pending(s)) return rc;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
     return check_err_flag(s);
 }
@@ -1729,6 +2099,7 @@ int32_t thrml_moments_reset(thrml_moments* m) {
 }
 static int32_t observe_async(thrml_moments* m, thrml_state* s) {
     if (m->prog != s->prog) return fail(THRML_ERR_INVALID_ARG, "observer and state belong to different programs");
+    if (int32_t rc = flush_pending(s)) return rc;
     cudaStream_t st = s->prog->ctx->stream;
     const uint8_t* c0 = s->cls[0].as<uint8_t>();
     const uint8_t* c1 = s->cls[1].as<uint8_t>();
@@ -1781,6 +2152,12 @@ int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, 
     if (n_other_rows) *n_other_rows = other;
     return THRML_OK;
 }
+int32_t thrml_state_launch_counts(const thrml_state* s, int64_t* block_launches, int64_t* persistent_launches) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (block_launches) *block_launches = s->block_launches;
+    if (persistent_launches) *persistent_launches = s->persistent_launches;
+    return THRML_OK;
+}
 int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs) {
     if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
     m->n_obs += n_obs;
@@ -1789,6 +2166,7 @@ int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs) {
 
 // StateObserver (state_observer.rs:25-47): copy the listed blocks' rows, [observed node][chain].
 static int32_t observe_states(thrml_state* s, const int32_t* obs_blocks, int32_t n_obs_blocks, uint8_t* dst) {
+    if (int32_t rc = flush_pending(s)) return rc;
     cudaStream_t st = s->prog->ctx->stream;
     int64_t row = 0;
     for (int32_t i = 0; i < n_obs_blocks; ++i) {
@@ -1830,6 +2208,7 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
                 if (int32_t rc = observe_states(s, obs_blocks, n_obs_blocks, obs_out + (i + 1) * stride)) return rc;
         }
     }
+    if (int32_t rc = flush_pending(s)) return rc;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
     return check_err_flag(s);
 }
@@ -1858,6 +2237,7 @@ int32_t thrml_sample_states_packed(thrml_state* s, uint64_t key, int64_t n_warmu
     if (int32_t rc = stage.alloc(static_cast<size_t>(chunk * per_sample) * 4)) return rc;
     int64_t in_chunk = 0, flushed = 0;
     auto pack = [&]() -> int32_t {
+        if (int32_t rc = flush_pending(s)) return rc;
         uint32_t* dst = stage.as<uint32_t>() + in_chunk * per_sample;
         int64_t row = 0;
         for (int32_t i = 0; i < n_obs_blocks; ++i) {

@@ -90,9 +90,9 @@ class Builder:
         self.clamped_blocks = []
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().thrml_builder_destroy(self.h)
-            self.h = None
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:  # module globals are already cleared when the interpreter is shutting down
+            lib().thrml_builder_destroy(h)
 
     def add_free_block(self, nodes, superblock=None, sampler=None):
         nodes = i64(nodes)
@@ -184,9 +184,9 @@ class Program:
         check(lib().thrml_program_create(self.ctx.h, builder.h, C.byref(self.h)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().thrml_program_destroy(self.h)
-            self.h = None
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:  # module globals are already cleared when the interpreter is shutting down
+            lib().thrml_program_destroy(h)
 
     def update_weights(self, block, table, w):
         w = f32(w)
@@ -223,9 +223,9 @@ class ChainState:
         check(lib().thrml_state_create(program.h, C.c_int64(n_chains), C.c_int64(chain_offset), C.byref(self.h)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().thrml_state_destroy(self.h)
-            self.h = None
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:  # module globals are already cleared when the interpreter is shutting down
+            lib().thrml_state_destroy(h)
 
     def upload(self, block, host):
         n = self.program.block_len(block)
@@ -304,6 +304,12 @@ class ChainState:
         check(lib().thrml_fields_debug(self.h, C.c_int32(block), ptr(out)))
         return out
 
+    def launch_counts(self):
+        """(per-block update launches, persistent multi-sweep launches) issued by this state so far."""
+        a, b = C.c_int64(), C.c_int64()
+        check(lib().thrml_state_launch_counts(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
+
     def sample_states_packed(self, key, n_warmup, n_samples, steps_per_sample, obs_blocks):
         """Samples of the listed spin blocks as bits: uint32 [samples][observed node][ceil(chains/32)]."""
         ob = i32(obs_blocks)
@@ -367,9 +373,9 @@ class Moments:
         return self
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().thrml_moments_destroy(self.h)
-            self.h = None
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:  # module globals are already cleared when the interpreter is shutting down
+            lib().thrml_moments_destroy(h)
 
     def reset(self):
         check(lib().thrml_moments_reset(self.h))

@@ -23,9 +23,9 @@ class LatticeStripe:
                                          C.c_float(bias), C.c_float(beta), C.c_int64(n_chains), C.c_int64(chain_offset), C.byref(self.h)))
 
     def __del__(self):
-        if getattr(self, "h", None):
-            lib().thrml_lattice_destroy(self.h)
-            self.h = None
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:  # module globals are already cleared when the interpreter is shutting down
+            lib().thrml_lattice_destroy(h)
 
     def randomize(self, key):
         check(lib().thrml_lattice_randomize(self.h, C.c_uint64(int(key))))
