@@ -212,6 +212,14 @@ int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const th
  * edges[2*n_edges] (node id pairs) with weights; energy_out[n_chains] on the host. */
 int32_t thrml_ising_energy(thrml_state* s, int64_t n_nodes, const int64_t* nodes, const float* biases, int64_t n_edges,
                            const int64_t* edges, const float* weights, float beta, double* energy_out);
+/* DiscreteEBMFactor::factor_energy (crates/thrml-models/src/discrete_ebm.rs:552-592) for every chain of the state:
+ * E = -sum over rows of W[row][c_1][c_2] * prod over the spin groups of (2x - 1), accumulated in f64 in a fixed order.
+ * nodes[(n_spin_groups + n_cat_groups) * rows]: node ids, one run of `rows` per group, spin groups first; w[rows*d1*d2];
+ * categorical group k indexes axis k (no categorical group: d1 = d2 = 1; one: d2 = 1; at most two, the weights being
+ * rank 3).  A category at or beyond the axis length reads the last entry.  energy_out[n_chains] on the host.
+ * The energy of a FactorizedEBM (ebm.rs:109-130) is the sum of this over its factors. */
+int32_t thrml_factor_energy(thrml_state* s, int64_t rows, int32_t n_spin_groups, int32_t n_cat_groups, const int64_t* nodes, const float* w, int32_t d1, int32_t d2,
+                            double* energy_out);
 /* sample_single_block (program.rs:324-393): update one free block in place; `key` is the block's own key. */
 int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key);
 /* <s_a s_b> over this device's chains for every node pair of two spin blocks (s = 2x-1): host_out[n_a][n_b] f32, computed

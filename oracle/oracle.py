@@ -113,6 +113,26 @@ def batch_gather_strided(w, idx, strides, batch_stride):
     return out
 
 
+def factor_energy(weights, spin_vals, cat_vals):
+    """DiscreteEBMFactor::factor_energy (crates/thrml-models/src/discrete_ebm.rs:552-592) restated with numpy in f64:
+    E = -sum_rows W[row, c_1, ...] * prod_groups (2 s - 1).  spin_vals / cat_vals: lists of `[rows]` (or
+    `[chains, rows]`) arrays gathered per node group; weights `[rows, d1, d2]`.  Returns a scalar or `[chains]`."""
+    w = np.asarray(weights, dtype=np.float64)
+    rows = w.shape[0]
+    w = w.reshape(rows, -1) if len(cat_vals) == 0 else w
+    idx = np.arange(rows)
+    if len(cat_vals) == 0:
+        g = w[:, 0]
+    elif len(cat_vals) == 1:
+        g = w.reshape(rows, w.shape[1], -1)[idx, np.asarray(cat_vals[0], dtype=np.int64), 0]
+    else:
+        g = w[idx, np.asarray(cat_vals[0], dtype=np.int64), np.asarray(cat_vals[1], dtype=np.int64)]
+    prod = 1.0
+    for sv in spin_vals:
+        prod = prod * (2.0 * np.asarray(sv, dtype=np.float64) - 1.0)
+    return -np.sum(g * prod, axis=-1)
+
+
 def lattice_edges(side_len, torus):
     side = C.c_int64()
     ne = C.c_int64()

@@ -120,3 +120,22 @@ def test_gumbel_argmax_scan_equals_tensor_ops(O):
     tensor_ops = np.argmax(logits - np.log(-np.log(u.astype(np.float64))), axis=1)
     assert np.array_equal(scan.astype(np.int64), tensor_ops)
     assert np.array_equal(O.categorical_sample(logits, u, use_libm=False).astype(np.int64), tensor_ops)
+
+
+def test_factor_energy_restatement(O):
+    # crates/thrml-models/tests/test_ising.rs:23-48: 3-spin chain, biases (0.1, 0.2, 0.3), weights (0.5, -0.5), beta 1,
+    # state (1, 0, 1): E = -(0.1 - 0.2 + 0.3 - 0.5 + 0.5) = -0.2 = bias factor + edge factor (discrete_ebm.rs:552-592 per
+    # factor).  The comment in that test slips a sign and says 0.8; the test itself only asserts a finite value.
+    state = np.array([1, 0, 1])
+    e_bias = O.factor_energy(np.array([0.1, 0.2, 0.3]).reshape(3, 1, 1), [state], [])
+    e_edge = O.factor_energy(np.array([0.5, -0.5]).reshape(2, 1, 1), [state[[0, 1]], state[[1, 2]]], [])
+    assert abs(e_bias - (-0.2)) < 1e-12 and abs(e_edge) < 1e-12
+    assert abs(O.factor_energy(np.array([0.5, -0.5]).reshape(2, 1, 1), [np.array([1, 0]), np.array([1, 1])], []) + 1.0) < 1e-12
+    assert abs(O.factor_energy(np.array([0.5, -0.5]).reshape(2, 1, 1), [np.array([1, 0]), np.array([1, 0])], []) - 0.0) < 1e-12
+    assert abs(O.factor_energy(np.array([0.5, -0.25]).reshape(2, 1, 1), [np.array([1, 0]), np.array([0, 0])], []) - 0.75) < 1e-12
+    # categorical axes: W[row, c1, c2] picked per row, spins as signs; a batch of two chains
+    w = np.arange(2 * 3 * 3, dtype=np.float64).reshape(2, 3, 3)
+    e = O.factor_energy(w, [np.array([[1, 0], [0, 0]])], [np.array([[2, 0], [1, 1]]), np.array([[1, 2], [0, 2]])])
+    assert np.allclose(e, [-(w[0, 2, 1] - w[1, 0, 2]), -(-w[0, 1, 0] - w[1, 1, 2])])
+    w1 = np.arange(6, dtype=np.float64).reshape(2, 3, 1)
+    assert O.factor_energy(w1, [], [np.array([2, 1])]) == -(w1[0, 2, 0] + w1[1, 1, 0])

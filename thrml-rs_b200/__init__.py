@@ -7,7 +7,7 @@ from ._ffi import ThrmlError, lib  # noqa: F401
 from .engine import (Builder, ChainState, Context, Moments, Program, default_context, greedy_coloring_arrays,  # noqa: F401
                      lattice_edges, rng_split)
 from .api import (Block, BlockGibbsSpec, BlockSamplingProgram, BlockSpec, CategoricalEBMFactor,  # noqa: F401
-                  CategoricalGibbsConditional, DiscreteEBMFactor, FactorSamplingProgram, InteractionGroup, IsingEBM,
+                  CategoricalGibbsConditional, DiscreteEBMFactor, FactorizedEBM, FactorSamplingProgram, InteractionGroup, IsingEBM,
                   IsingSamplingProgram, IsingTrainingSpec, MomentAccumulatorObserver, Node, NodeType, RngKey, SamplingSchedule,
                   SpinEBMFactor, SpinGibbsConditional, SquareDiscreteEBMFactor, StateObserver, coloring_to_blocks, estimate_kl_grad, estimate_moments,
                   greedy_coloring, hinton_init, make_nearest_neighbor_lattice, run_blocks, sample_blocks,

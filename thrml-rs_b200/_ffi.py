@@ -47,6 +47,7 @@ _SIGNATURES = {
     "thrml_program_block_kernel": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_program_enable_dense": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_ising_energy": (C.c_int32, [_P, C.c_int64, _P, _P, C.c_int64, _P, _P, C.c_float, _P]),
+    "thrml_factor_energy": (C.c_int32, [_P, C.c_int64, C.c_int32, C.c_int32, _P, _P, C.c_int32, C.c_int32, _P]),
     "thrml_sample_single_block": (C.c_int32, [_P, C.c_int32, C.c_uint64]),
     "thrml_pair_correlation": (C.c_int32, [_P, C.c_int32, C.c_int32, _P]),
     "thrml_cd1_step": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, C.c_uint64, _P, _P]),

@@ -433,6 +433,63 @@ class DiscreteEBMFactor:
         return out
 
 
+def _energy_state(state, blocks, node_shape_dtypes, ctx):
+    """A device state holding `state` (one array per block, `[n]` or `[chains, n]`) (no interactions; the blocks only
+    give the layout): the block_state_to_global step of ebm.rs:117-121 for energy evaluation."""
+    blocks = list(blocks)
+    arrays = [np.atleast_2d(np.asarray(a)) for a in state]
+    if len(arrays) != len(blocks):
+        raise ThrmlError(-1, "Number of states not equal to number of blocks")
+    spec = BlockGibbsSpec([[b] for b in blocks], [], node_shape_dtypes)
+    samplers = [SpinGibbsConditional() if b.node_type().kind == 0 else CategoricalGibbsConditional(b.node_type().kind) for b in blocks]
+    prog = BlockSamplingProgram(spec, samplers, [], ctx)
+    st = _eng.ChainState(prog.device_program, arrays[0].shape[0])
+    for i, (a, b) in enumerate(zip(arrays, blocks)):
+        if a.shape[1] != len(b):
+            raise ThrmlError(-1, "Block/state length mismatch")
+        st.upload(i, a)
+    return prog, st
+
+
+def _factor_energy_on(factor, prog, st):
+    sg = [[prog.dense_id(n) for n in g.nodes()] for g in factor.spin_node_groups]
+    cg = [[prog.dense_id(n) for n in g.nodes()] for g in factor.categorical_node_groups]
+    w = factor.weights
+    if len(cg) < 2:  # a trailing axis of length 1 carries no index (discrete_ebm.rs:577-583)
+        w = w.reshape(w.shape[0], -1, 1)
+    return st.factor_energy(sg, cg, w)
+
+
+def _factor_energy(self, state, blocks, node_shape_dtypes=None, ctx=None):
+    """discrete_ebm.rs:552-592: E = -sum_rows W[row, categories...] * prod(2 s - 1) for the state given per block
+    (`blocks` plays the BlockSpec's role).  `[n]` block states give a one-element array like the reference; `[chains, n]`
+    states give one energy per chain."""
+    types = node_shape_dtypes or list(dict.fromkeys(b.node_type() for b in blocks))
+    prog, st = _energy_state(state, blocks, types, ctx)
+    return _factor_energy_on(self, prog, st).astype(np.float32)
+
+
+DiscreteEBMFactor.factor_energy = _factor_energy
+
+
+class FactorizedEBM:
+    """ebm.rs:93-130: an EBM that is the sum of its factors' energies."""
+
+    def __init__(self, factors, node_shape_dtypes):
+        self.factor_list = list(factors)
+        self.node_shape_dtypes = list(node_shape_dtypes)
+
+    def factors(self):
+        return self.factor_list
+
+    def energy(self, state, blocks, ctx=None):
+        prog, st = _energy_state(state, blocks, self.node_shape_dtypes, ctx)
+        total = np.zeros(st.n_chains, dtype=np.float64)
+        for f in self.factor_list:
+            total += _factor_energy_on(f, prog, st)
+        return total.astype(np.float32)
+
+
 class SpinEBMFactor(DiscreteEBMFactor):
     """discrete_ebm.rs:742-790."""
 

@@ -824,6 +824,44 @@ __global__ void __launch_bounds__(256) k_energy_partial(const int32_t* pos_a, co
         }
     }
 }
+// DiscreteEBMFactor::factor_energy (discrete_ebm.rs:552-592) for every chain: sum over rows of
+// W[row][c1][c2] * prod over spin groups of (2x - 1), in f64, with the chunking of k_energy_partial.
+// pos: [n_spin + n_cat][n_terms] positions in the spin / categorical class arrays.
+__global__ void __launch_bounds__(256) k_factor_energy_partial(const int32_t* pos, int32_t n_spin, int32_t n_cat, const float* w, int32_t d1, int32_t d2, int64_t n_terms,
+                                                               const uint8_t* spin, const uint8_t* cat, int64_t ld, double* partial /*[chunks][ld]*/) {
+    __shared__ double red[8][32][4];
+    const int64_t quad = static_cast<int64_t>(blockIdx.y) * 32 + threadIdx.x;
+    const int64_t t0 = static_cast<int64_t>(blockIdx.x) * ENERGY_CHUNK, t1 = min(n_terms, t0 + ENERGY_CHUNK);
+    double acc[4] = {0.0, 0.0, 0.0, 0.0};
+    if (4 * quad < ld) {
+        for (int64_t t = t0 + threadIdx.y; t < t1; t += 8) {
+            uint32_t zeros = 0;  // per chain byte: parity of the number of spin tails that are 0 (each contributes a factor -1)
+            for (int32_t g = 0; g < n_spin; ++g)
+                zeros ^= ~*reinterpret_cast<const uint32_t*>(spin + static_cast<int64_t>(pos[g * n_terms + t]) * ld + 4 * quad);
+            uint32_t c1 = 0, c2 = 0;
+            if (n_cat > 0) c1 = *reinterpret_cast<const uint32_t*>(cat + static_cast<int64_t>(pos[n_spin * n_terms + t]) * ld + 4 * quad);
+            if (n_cat > 1) c2 = *reinterpret_cast<const uint32_t*>(cat + static_cast<int64_t>(pos[(n_spin + 1) * n_terms + t]) * ld + 4 * quad);
+            const float* wt = w + t * d1 * d2;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int32_t i1 = min(static_cast<int32_t>((c1 >> (8 * c)) & 0xffu), d1 - 1), i2 = min(static_cast<int32_t>((c2 >> (8 * c)) & 0xffu), d2 - 1);
+                const double v = static_cast<double>(wt[i1 * d2 + i2]);
+                acc[c] += ((zeros >> (8 * c)) & 1u) ? -v : v;
+            }
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) red[threadIdx.y][threadIdx.x][c] = acc[c];
+    __syncthreads();
+    if (threadIdx.y == 0 && 4 * quad < ld) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            double sum = 0.0;
+            for (int y = 0; y < 8; ++y) sum += red[y][threadIdx.x][c];
+            partial[static_cast<int64_t>(blockIdx.x) * ld + 4 * quad + c] = sum;
+        }
+    }
+}
 __global__ void k_energy_final(const double* partial, int64_t n_chunks, int64_t ld, int64_t n_chains, double neg_beta, double* out) {
     const int64_t chain = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (chain >= n_chains) return;
@@ -1815,6 +1853,50 @@ int32_t thrml_ising_energy(thrml_state* s, int64_t n_nodes, const int64_t* nodes
     }
     k_energy_final<<<static_cast<unsigned>((s->n_chains + 255) / 256), 256, 0, st>>>(d_partial.as<double>(), n_chunks, s->ld, s->n_chains, -static_cast<double>(beta),
                                                                                      d_out.as<double>());
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(energy_out, d_out.p, static_cast<size_t>(s->n_chains) * 8, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+
+// DiscreteEBMFactor::factor_energy (discrete_ebm.rs:552-592) per chain; see the header for the argument layout.
+int32_t thrml_factor_energy(thrml_state* s, int64_t rows, int32_t n_spin_groups, int32_t n_cat_groups, const int64_t* nodes, const float* w, int32_t d1, int32_t d2,
+                            double* energy_out) {
+    if (!s || !energy_out || rows < 0 || n_spin_groups < 0 || n_cat_groups < 0 || d1 < 1 || d2 < 1 || (rows > 0 && (!w || (n_spin_groups + n_cat_groups > 0 && !nodes))))
+        return fail(THRML_ERR_INVALID_ARG, "bad factor energy arguments");
+    if (n_cat_groups > 2) return fail(THRML_ERR_UNSUPPORTED, "weights are rank 3: at most two categorical node groups per factor");
+    if ((n_cat_groups < 2 && d2 != 1) || (n_cat_groups < 1 && d1 != 1))
+        return fail(THRML_ERR_INVALID_ARG, "The shape of the weight tensor must be [b, x_1, ..., x_k], where k is the length of categorical_node_groups");
+    thrml_program* p = s->prog;
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    cudaStream_t st = p->ctx->stream;
+    const int32_t n_groups = n_spin_groups + n_cat_groups;
+    std::vector<int32_t> pos(static_cast<size_t>(std::max<int64_t>(1, n_groups * rows)));
+    for (int32_t g = 0; g < n_groups; ++g) {
+        const int32_t want = g < n_spin_groups ? p->sd_spin : p->sd_cat;
+        for (int64_t t = 0; t < rows; ++t) {
+            const int64_t nd = nodes[g * rows + t];
+            if (nd < 0 || nd >= static_cast<int64_t>(p->loc_sd.size()) || p->loc_sd[nd] < 0) return fail(THRML_ERR_INVALID_ARG, "Node not found in global location map");
+            if (p->loc_sd[nd] != want) return fail(THRML_ERR_INVALID_ARG, "All nodes in a block must be of the same type: a spin group holds a categorical node or the reverse");
+            pos[g * rows + t] = static_cast<int32_t>(p->loc_pos[nd]);
+        }
+    }
+    const int64_t n_chunks = std::max<int64_t>(1, (rows + ENERGY_CHUNK - 1) / ENERGY_CHUNK);
+    DevBuf d_pos, d_w, d_partial, d_out;
+    if (int32_t rc = upload(d_pos, pos.data(), pos.size() * 4, st)) return rc;
+    if (rows > 0)
+        if (int32_t rc = upload(d_w, w, static_cast<size_t>(rows) * d1 * d2 * 4, st)) return rc;
+    if (int32_t rc = d_partial.alloc(static_cast<size_t>(n_chunks * s->ld) * 8)) return rc;
+    if (int32_t rc = d_out.alloc(static_cast<size_t>(s->n_chains) * 8)) return rc;
+    CU_TRY(cudaMemsetAsync(d_partial.p, 0, d_partial.bytes, st));
+    if (rows > 0) {
+        dim3 grid(static_cast<unsigned>(n_chunks), static_cast<unsigned>((s->ld / 4 + 31) / 32));
+        k_factor_energy_partial<<<grid, dim3(32, 8), 0, st>>>(d_pos.as<int32_t>(), n_spin_groups, n_cat_groups, d_w.as<float>(), d1, d2, rows,
+                                                              p->sd_spin >= 0 ? s->rows(p->sd_spin) : nullptr, p->sd_cat >= 0 ? s->rows(p->sd_cat) : nullptr, s->ld,
+                                                              d_partial.as<double>());
+        CU_TRY(cudaGetLastError());
+    }
+    k_energy_final<<<static_cast<unsigned>((s->n_chains + 255) / 256), 256, 0, st>>>(d_partial.as<double>(), n_chunks, s->ld, s->n_chains, -1.0, d_out.as<double>());
     CU_TRY(cudaGetLastError());
     CU_TRY(cudaMemcpyAsync(energy_out, d_out.p, static_cast<size_t>(s->n_chains) * 8, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));

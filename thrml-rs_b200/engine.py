@@ -280,6 +280,17 @@ class ChainState:
         check(lib().thrml_ising_energy(self.h, C.c_int64(len(nodes)), ptr(nodes), ptr(biases), C.c_int64(len(edges)), ptr(edges), ptr(weights), C.c_float(beta), ptr(out)))
         return out
 
+    def factor_energy(self, spin_groups, cat_groups, weights):
+        """Per-chain energy of one discrete factor (f64): node-id lists per group, weights `[rows, d1, d2]`."""
+        w = f32(weights)
+        w = w.reshape(w.shape[0], -1, 1) if w.ndim < 3 else w
+        groups = [i64(g) for g in list(spin_groups) + list(cat_groups)]
+        nodes = np.ascontiguousarray(np.stack(groups)) if groups else np.zeros((0, w.shape[0]), dtype=np.int64)
+        out = np.zeros(self.n_chains, dtype=np.float64)
+        check(lib().thrml_factor_energy(self.h, C.c_int64(w.shape[0]), C.c_int32(len(spin_groups)), C.c_int32(len(cat_groups)), ptr(nodes), ptr(w),
+                                        C.c_int32(w.shape[1]), C.c_int32(w.shape[2]), ptr(out)))
+        return out
+
     def sample_single_block(self, block, key):
         check(lib().thrml_sample_single_block(self.h, C.c_int32(block), C.c_uint64(int(key))))
 
