@@ -248,6 +248,17 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                     // row = chain, columns = nodes of the updated block
                     uint32_t bits = 0, unsure = 0;
                     uint32_t rnd[16];
+                    float bias[16];
+                    if (col0 + 16 <= g.n_total) {
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const float4 b4 = __ldg(reinterpret_cast<const float4*>(g.bias + col0) + q);
+                            bias[4 * q] = b4.x; bias[4 * q + 1] = b4.y; bias[4 * q + 2] = b4.z; bias[4 * q + 3] = b4.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) bias[j] = col0 + j < g.n_total ? __ldg(g.bias + col0 + j) : 0.0f;
+                    }
 #pragma unroll
                     for (int t = 0; t < 4; ++t) {
                         const int my_col = col0 + 4 * t + (lane & 3);
@@ -259,13 +270,12 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                     }
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int col = col0 + j;
-                        const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
-                        const float xx = __fmul_rn(__fadd_rn(b, __uint_as_float(acc[j])), 2.0f);
-                        // approximate sigmoid first; draws within 4e-6 of it (four times its worst error) are redone exactly
-                        const float e = __expf(-fabsf(xx));
-                        const float q = __fdividef(1.0f, 1.0f + e);
-                        const float p = xx >= 0.0f ? q : 1.0f - q;
+                        // approximate sigmoid first, p = 1 / (1 + 2^(-2 log2(e) gamma)); draws within 4e-6 of it (four times its
+                        // worst error) are redone exactly.  A huge exponential gives p = 0, a vanishing one p = 1.
+                        const float gamma = __fadd_rn(bias[j], __uint_as_float(acc[j]));
+                        float e;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gamma * -2.885390081777927f));
+                        const float p = __fdividef(1.0f, 1.0f + e);
                         const float u = u24(rnd[j]);
                         bits |= (u < p ? 1u : 0u) << j;
                         unsure |= (fabsf(u - p) <= 4e-6f ? 1u : 0u) << j;
@@ -274,9 +284,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
                             if ((unsure >> j) & 1u) {
-                                const int col = col0 + j;
-                                const float b = col < g.n_total ? __ldg(g.bias + col) : 0.0f;
-                                const float xx = __fmul_rn(__fadd_rn(b, __uint_as_float(acc[j])), 2.0f);
+                                const float xx = __fmul_rn(__fadd_rn(bias[j], __uint_as_float(acc[j])), 2.0f);
                                 const uint32_t one = u24(rnd[j]) <= det_sigmoid(xx) ? 1u : 0u;
                                 bits = (bits & ~(1u << j)) | (one << j);
                             }
@@ -352,18 +360,42 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
     }
 }
 
-// 0/1 byte state [node][chain] of one block -> +-1 bf16 image [chain][node] (32x32 tiles through shared memory).
-__global__ void k_make_image(const uint8_t* rows, int64_t ld, int64_t n_chains, int32_t n, __nv_bfloat16* image, int64_t pitch) {
-    __shared__ uint8_t tile[32][33];
-    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 32;
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int64_t node = node0 + r, chain = chain0 + threadIdx.x;
-        tile[r][threadIdx.x] = (node < n && chain < n_chains) ? rows[node * ld + chain] : 0;
+// 0/1 byte state [node][chain] of one block -> +-1 bf16 image [chain][node] (columns from n up to the pitch are zero)
+// and, when `ones` is given, the number of ones per node over the existing chains, added with atomics (the caller
+// zeroes it).  A CTA moves a tile of 32 nodes x 128 chains: 128-byte row segments in, 64-byte image segments out.
+__global__ void __launch_bounds__(256) k_make_image(const uint8_t* rows, int64_t ld, int64_t n_chains, int32_t n, __nv_bfloat16* image, int64_t pitch, int32_t* ones) {
+    __shared__ uint32_t tile[32][33];  // [node][word of four chains]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t node0 = static_cast<int64_t>(blockIdx.x) * 32, chain0 = static_cast<int64_t>(blockIdx.y) * 128;
+    for (int r = warp; r < 32; r += 8) {
+        const int64_t node = node0 + r, chain = chain0 + 4 * lane;
+        uint32_t w = 0;
+        if (node < n && chain < n_chains) {  // ld is a multiple of 16, so a word that starts below n_chains lies inside the row
+            w = *reinterpret_cast<const uint32_t*>(rows + node * ld + chain);
+            const int64_t left = n_chains - chain;
+            if (left < 4) w &= 0xffffffffu >> (8 * (4 - static_cast<int>(left)));
+        }
+        tile[r][lane] = w;
+        if (ones) {
+            const int cnt = __reduce_add_sync(0xffffffffu, __popc(w & 0x01010101u));
+            if (lane == 0 && cnt) atomicAdd(ones + node, cnt);
+        }
     }
     __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
-        const int64_t chain = chain0 + r, node = node0 + threadIdx.x;
-        if (chain < n_chains && node < pitch) image[chain * pitch + node] = __float2bfloat16(node < n ? (tile[threadIdx.x][r] ? 1.0f : -1.0f) : 0.0f);
+    const int c = threadIdx.x >> 1, h = threadIdx.x & 1;  // chain of the tile, which 16 of the 32 nodes
+    const int64_t chain = chain0 + c;
+    if (chain < n_chains && node0 + 16 * h + 16 <= pitch) {
+        uint32_t out[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int r0 = 16 * h + 2 * j;
+            const uint32_t b0 = (tile[r0][c >> 2] >> (8 * (c & 3))) & 1u, b1 = (tile[r0 + 1][c >> 2] >> (8 * (c & 3))) & 1u;
+            const uint32_t v0 = node0 + r0 < n ? (b0 ? 0x3f80u : 0xbf80u) : 0u, v1 = node0 + r0 + 1 < n ? (b1 ? 0x3f80u : 0xbf80u) : 0u;  // bf16 +1 / -1
+            out[j] = v0 | (v1 << 16);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(image + chain * pitch + node0 + 16 * h);
+        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
     }
 }
 // Number of ones per state row (over existing chains).

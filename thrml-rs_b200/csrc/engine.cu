@@ -113,6 +113,7 @@ struct thrml_state {
     std::vector<std::pair<uint64_t, thrml_moments*>> pending;
     DevBuf d_plan, d_plan_acc, d_slice_blocks;
     int persist_grid = 0;  // CTAs of the persistent kernel (all co-resident), 0 = not eligible
+    int32_t no_image_block = -1;  // a dense update of this block skips its +-1 image (nobody reads it before the next update)
     bool sliced = false;   // the chain-sliced kernel serves the queue instead (four chains of every spin fit in shared memory)
     int64_t persist_epoch = -1;  // program kernel_epoch persist_grid was computed for
     int64_t persistent_launches = 0, block_launches = 0;
@@ -1434,11 +1435,22 @@ static int32_t ensure_image(thrml_state* s, int32_t block, bool need_fresh) {
         s->image_fresh[block] = 0;
     }
     if (need_fresh && !s->image_fresh[block]) {
-        dim3 grid(static_cast<unsigned>((pitch + 31) / 32), static_cast<unsigned>((s->n_chains + 31) / 32));
-        dense::k_make_image<<<grid, dim3(32, 8), 0, s->prog->ctx->stream>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
-                                                                           s->image[block]->as<__nv_bfloat16>(), pitch);
+        // the same pass counts the ones per node when those are stale too (the correlation epilogue wants them)
+        int32_t* ones = nullptr;
+        if (!s->ones_fresh[block]) {
+            if (!s->ones[block]) {
+                s->ones[block].reset(new DevBuf());
+                if (int32_t rc = s->ones[block]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+            }
+            CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, s->prog->ctx->stream));
+            ones = s->ones[block]->as<int32_t>();
+        }
+        dim3 grid(static_cast<unsigned>(pitch / 32), static_cast<unsigned>((s->n_chains + 127) / 128));
+        dense::k_make_image<<<grid, 256, 0, s->prog->ctx->stream>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
+                                                                    s->image[block]->as<__nv_bfloat16>(), pitch, ones);
         CU_TRY(cudaGetLastError());
         s->image_fresh[block] = 1;
+        if (ones) s->ones_fresh[block] = 1;
     }
     return THRML_OK;
 }
@@ -1467,7 +1479,7 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     const BlockProg& bp = p->blocks[block];
     if (int32_t rc = ensure_err_flag(s)) return rc;
     if (int32_t rc = ensure_image(s, bp.dense_src, true)) return rc;
-    const bool write_image = p->is_dense_source[block] != 0;
+    const bool write_image = p->is_dense_source[block] != 0 && block != s->no_image_block;
     if (write_image)
         if (int32_t rc = ensure_image(s, block, false)) return rc;
     dense::GemmArgs g{};
@@ -1989,7 +2001,10 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
     const BlockProg& hb = s->prog->blocks[hidden_block];
     if (int32_t rc = launch_block(s, hidden_block, keys[0], nullptr, s->rows(hb.sd) + hb.offset * s->ld, nullptr)) return rc;
     if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>())) return rc;
-    if (int32_t rc = sweep(s, keys[1], nullptr)) return rc;
+    s->no_image_block = hidden_block;  // h1 feeds only the correlations, which read the byte state
+    const int32_t rc_sweep = sweep(s, keys[1], nullptr);
+    s->no_image_block = -1;
+    if (rc_sweep) return rc_sweep;
     if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>() + cnt)) return rc;
     if (pos_host) CU_TRY(cudaMemcpyAsync(pos_host, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, st));
     if (neg_host) CU_TRY(cudaMemcpyAsync(neg_host, s->d_corr.as<float>() + cnt, cnt * 4, cudaMemcpyDeviceToHost, st));
