@@ -43,6 +43,8 @@ def parse():
                     help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores (1 GPU); "
                          "lattice = one bit-packed 2-D Ising lattice sharded by row stripes with halo exchange")
     ap.add_argument("--side", type=int, default=32768, help="lattice side (lattice workload)")
+    ap.add_argument("--dense-tiles", default="auto", choices=["auto", "pair", "single"],
+                    help="rbm workload: CTA pairs sharing 256-row tiles (tcgen05 cta_group::2), one CTA per 128-row tile, or chosen per launch")
     return ap.parse_args()
 
 
@@ -288,6 +290,7 @@ def run_rbm(T, torch, W, args, device):
     builder = W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model)
     program = T.Program(builder, ctx)
     assert program.enable_dense(False) == 2
+    T.lib().thrml_debug_dense_pair_mode({"single": 0, "pair": 1, "auto": 2}[args.dense_tiles])
     rng = np.random.default_rng(3)
     v0 = (rng.random((chains, nv)) < 0.13).astype(np.uint8)
     data, state = T.ChainState(program, chains), T.ChainState(program, chains)

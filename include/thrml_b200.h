@@ -145,6 +145,11 @@ int32_t thrml_ctx_synchronize(thrml_ctx* ctx);
  * kernel waits on a pipeline barrier that nothing signals; its bounded wait runs out, it returns, and this call
  * reports THRML_ERR_TIMEOUT.  The context remains usable. */
 int32_t thrml_debug_wait_timeout(thrml_ctx* ctx);
+/* Tile shape of the dense (tensor-core) kernels, process-wide: 1 = CTA pairs sharing 256-row tiles through
+ * tcgen05 cta_group::2 (each CTA stages half of the B operand), 0 = one CTA per 128-row tile, 2 (the default) = chosen
+ * per launch from the shape (pairs for long reductions without much row padding).  All give the same results; tests
+ * run both tilings.  Returns the previous setting.  No counterpart in the reference. */
+int32_t thrml_debug_dense_pair_mode(int32_t mode);
 /* cudaStream_t of the context, for callers that time with their own events. */
 void* thrml_ctx_stream(thrml_ctx* ctx);
 

@@ -13,6 +13,14 @@ import models as M
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True)
+def single_cta_tiles(T):
+    """This file exercises the one-CTA tiles; tests/test_gpu_dense_pair.py re-runs the same checks with CTA pairs."""
+    before = T.lib().thrml_debug_dense_pair_mode(0)
+    yield
+    T.lib().thrml_debug_dense_pair_mode(before)
+
+
 def to_bf16(x):
     u = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
     u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000

@@ -73,11 +73,13 @@ struct BlockProg {
     int32_t base_kernel = 0;     // kernel used when the dense path is off or cannot serve a call
     int64_t dense_pitch = 0;     // elements per row of d_dense_w
     int32_t dense_bn = 128;      // tile width of the update GEMM
+    int32_t dense_bn_pair = 128; // tile width when CTA pairs share 256-row tiles
     std::vector<float> h_dense_w;  // [n][n_src] f32, canonical weights (0 where there is no edge)
     std::vector<float> h_dense_bias;
     DevBuf d_dense_w;            // bf16 [n][dense_pitch], K-major (K = source nodes)
     DevBuf d_dense_bias;         // f32 [n]
     CUtensorMap map_w;
+    CUtensorMap map_w_pair;      // same operand, box of dense_bn_pair / 2 rows
 };
 
 struct thrml_program {
@@ -108,7 +110,7 @@ struct thrml_state {
     std::vector<uint8_t> image_fresh, ones_fresh;
     std::vector<CUtensorMap> map_image;
     std::vector<std::unique_ptr<DevBuf>> ones;
-    DevBuf d_err, d_corr;
+    DevBuf d_err, d_corr, d_dense_debug;
     // sweeps queued for the persistent kernel (cache-resident programs): (sweep key, observer to accumulate or null)
     std::vector<std::pair<uint64_t, thrml_moments*>> pending;
     DevBuf d_plan, d_plan_acc, d_slice_blocks;
@@ -913,6 +915,22 @@ static int32_t make_operand_map(CUtensorMap* map, void* base, bool is_u8, int64_
     if (r != CUDA_SUCCESS) return fail(THRML_ERR_CUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)));
     return THRML_OK;
 }
+// Width of a CTA pair's tile for n output columns: the candidate that pads n the least, the wider one on ties.
+static int32_t pair_tile_width(int64_t n) {
+    int32_t best = 256;
+    for (int32_t w : {208, 128})
+        if ((n + w - 1) / w * w < (n + best - 1) / best * best) best = w;
+    return best;
+}
+// 0 = one CTA per 128-row tile, 1 = CTA pairs on 256-row tiles, 2 = per launch, whichever suits the shape: pairs halve the
+// B-operand traffic per SM, which pays when the GEMM is bound by its operand feed (long K); a short-K update is bound
+// by its sampling epilogue and runs a little faster without the cluster hand-overs.
+static int g_dense_pair_mode = 2;
+static bool use_pair_tiles(int64_t m_rows, int64_t k_elems) {
+    if (g_dense_pair_mode != 2) return g_dense_pair_mode == 1;
+    const int64_t pad_pair = (m_rows + 255) / 256 * 256, pad_single = (m_rows + 127) / 128 * 128;
+    return k_elems >= 2048 && pad_pair * 10 <= pad_single * 11;
+}
 static inline uint16_t f32_to_bf16_rn(float f) {
     uint32_t u;
     std::memcpy(&u, &f, 4);
@@ -1186,6 +1204,8 @@ int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding
         CU_TRY(cudaStreamSynchronize(st));
         bp.dense_bn = bp.n >= 2048 ? 256 : 128;  // wide output blocks take 128x256 tiles: fewer operand bytes per flop
         if (int32_t rc = make_operand_map(&bp.map_w, bp.d_dense_w.p, false, n_src, bp.n, bp.dense_pitch * 2, bp.dense_bn)) return rc;
+        bp.dense_bn_pair = pair_tile_width(bp.n);
+        if (int32_t rc = make_operand_map(&bp.map_w_pair, bp.d_dense_w.p, false, n_src, bp.n, bp.dense_pitch * 2, bp.dense_bn_pair / 2)) return rc;
         bp.dense_on = true;
         bp.kernel = 3;
         p->is_dense_source[bp.dense_src] = 1;
@@ -1412,6 +1432,8 @@ static int32_t ensure_err_flag(thrml_state* s) {
     if (s->d_err.p) return THRML_OK;
     if (int32_t rc = s->d_err.alloc(sizeof(int))) return rc;
     CU_TRY(cudaMemsetAsync(s->d_err.p, 0, sizeof(int), s->prog->ctx->stream));
+    if (int32_t rc = s->d_dense_debug.alloc(2 * sizeof(uint32_t))) return rc;
+    CU_TRY(cudaMemsetAsync(s->d_dense_debug.p, 0xff, 2 * sizeof(uint32_t), s->prog->ctx->stream));
     return THRML_OK;
 }
 // Reads the kernels' error flag after a synchronisation; a non-zero value means a bounded wait ran out.
@@ -1419,6 +1441,12 @@ static int32_t check_err_flag(thrml_state* s) {
     if (!s->d_err.p) return THRML_OK;
     int code = 0;
     CU_TRY(cudaMemcpy(&code, s->d_err.p, sizeof(int), cudaMemcpyDeviceToHost));
+    if (g_dense_pair_mode) {  // both CTAs of a pair must hold the accumulators at the same TMEM address
+        uint32_t base[2] = {0, 0};
+        CU_TRY(cudaMemcpy(base, s->d_dense_debug.p, sizeof(base), cudaMemcpyDeviceToHost));
+        if (base[0] != base[1])
+            return fail(THRML_ERR_CUDA, "the two CTAs of a pair got different tensor-memory addresses (" + std::to_string(base[0]) + ", " + std::to_string(base[1]) + ")");
+    }
     if (code == 0) return THRML_OK;
     CU_TRY(cudaMemset(s->d_err.p, 0, sizeof(int)));
     return fail(THRML_ERR_TIMEOUT, "a tensor-core kernel gave up waiting on a pipeline barrier (role " + std::to_string(code) + ")");
@@ -1472,6 +1500,24 @@ static int32_t launch_dense(thrml_state* s, const CUtensorMap& ma, const CUtenso
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }
+template <int EPI, int BN>
+static int32_t launch_dense_pair(thrml_state* s, const CUtensorMap& ma, const CUtensorMap& mb, dense::GemmArgs g) {
+    constexpr size_t smem = dense::pair_stages_for<BN>() * (dense::BM + BN / 2) * dense::BK_BYTES + 1024;
+    static bool configured[64] = {};  // the attribute is per device
+    const int dev = s->device & 63;
+    if (!configured[dev]) {
+        CU_TRY(cudaFuncSetAttribute(dense::k_dense_gemm_pair<EPI, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        configured[dev] = true;
+    }
+    g.tiles_m = (g.m_total + dense::PAIR_BM - 1) / dense::PAIR_BM;
+    g.tiles_n = (g.n_total + BN - 1) / BN;
+    g.err = s->d_err.as<int>();
+    g.debug = s->d_dense_debug.as<uint32_t>();
+    const int pairs = std::max(1, std::min(s->prog->ctx->sm_count / 2, g.tiles_m * g.tiles_n));
+    dense::k_dense_gemm_pair<EPI, BN><<<2 * pairs, dense::THREADS, smem, s->prog->ctx->stream>>>(ma, mb, g);
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
 }  // extern "C++"
 // Tensor-core update of a dense bipartite block, in place.
 static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t k1) {
@@ -1499,11 +1545,17 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     }
     CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, p->ctx->stream));
     g.ones_out = s->ones[block]->as<int32_t>();
-    if (bp.dense_bn == 256) {
-        if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w, g)) return rc;
-    } else if (int32_t rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g)) {
-        return rc;
+    int32_t rc = THRML_OK;
+    if (use_pair_tiles(s->n_chains, p->blocks[bp.dense_src].n)) {
+        if (bp.dense_bn_pair == 256) rc = launch_dense_pair<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+        else if (bp.dense_bn_pair == 208) rc = launch_dense_pair<dense::EPI_SAMPLE, 208>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+        else rc = launch_dense_pair<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+    } else if (bp.dense_bn == 256) {
+        rc = launch_dense<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w, g);
+    } else {
+        rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g);
     }
+    if (rc) return rc;
     s->image_fresh[block] = write_image ? 1 : 0;
     s->ones_fresh[block] = 1;
     return THRML_OK;
@@ -1937,15 +1989,20 @@ int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key) {
 // s->d_corr as f32 [n_a][n_b]).
 static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t block_b, float* d_out) {
     thrml_program* p = s->prog;
-    const BlockProg& ba = p->blocks[block_a];
-    const BlockProg& bb = p->blocks[block_b];
-    if (ba.is_cat || bb.is_cat) return fail(THRML_ERR_INVALID_ARG, "pair correlations are defined for spin blocks");
+    if (p->blocks[block_a].is_cat || p->blocks[block_b].is_cat) return fail(THRML_ERR_INVALID_ARG, "pair correlations are defined for spin blocks");
     cudaStream_t st = p->ctx->stream;
     if (int32_t rc = ensure_err_flag(s)) return rc;
+    // Rows of the GEMM come from block a unless only block b fills 256-row pair tiles well: then the operands swap
+    // and the epilogue writes the transposed result, which lands in the same [n_a][n_b] layout.
+    bool pair = use_pair_tiles(p->blocks[block_a].n, s->n_chains), swapped = false;
+    if (!pair && g_dense_pair_mode == 2 && use_pair_tiles(p->blocks[block_b].n, s->n_chains)) pair = swapped = true;
+    const int32_t row_block = swapped ? block_b : block_a, col_block = swapped ? block_a : block_b;
+    const BlockProg& br = p->blocks[row_block];
+    const BlockProg& bc = p->blocks[col_block];
     CUtensorMap map_a, map_b;  // encoded per call: kernel parameters are copied at launch
-    if (int32_t rc = make_operand_map(&map_a, s->rows(ba.sd) + ba.offset * s->ld, true, s->n_chains, ba.n, s->ld, dense::BM)) return rc;
-    const int bn = bb.n >= 2048 ? 256 : 64;
-    if (int32_t rc = make_operand_map(&map_b, s->rows(bb.sd) + bb.offset * s->ld, true, s->n_chains, bb.n, s->ld, bn)) return rc;
+    if (int32_t rc = make_operand_map(&map_a, s->rows(br.sd) + br.offset * s->ld, true, s->n_chains, br.n, s->ld, dense::BM)) return rc;
+    const int bn = pair ? pair_tile_width(bc.n) : (bc.n >= 2048 ? 256 : 64);
+    if (int32_t rc = make_operand_map(&map_b, s->rows(bc.sd) + bc.offset * s->ld, true, s->n_chains, bc.n, s->ld, pair ? bn / 2 : bn)) return rc;
     for (int32_t blk : {block_a, block_b}) {
         const BlockProg& bp = p->blocks[blk];
         if (!s->ones[blk]) {
@@ -1960,13 +2017,19 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
         }
     }
     dense::GemmArgs g{};
-    g.m_total = static_cast<int32_t>(ba.n);
-    g.n_total = static_cast<int32_t>(bb.n);
+    g.m_total = static_cast<int32_t>(br.n);
+    g.n_total = static_cast<int32_t>(bc.n);
     g.k_bytes = static_cast<int32_t>(s->n_chains);
-    g.ones_a = s->ones[block_a]->as<int32_t>();
-    g.ones_b = s->ones[block_b]->as<int32_t>();
+    g.ones_a = s->ones[row_block]->as<int32_t>();
+    g.ones_b = s->ones[col_block]->as<int32_t>();
     g.corr_out = d_out;
+    g.corr_transposed = swapped ? 1 : 0;
     g.n_chains = static_cast<int32_t>(s->n_chains);
+    if (pair) {
+        if (bn == 256) return launch_dense_pair<dense::EPI_CORR, 256>(s, map_a, map_b, g);
+        if (bn == 208) return launch_dense_pair<dense::EPI_CORR, 208>(s, map_a, map_b, g);
+        return launch_dense_pair<dense::EPI_CORR, 128>(s, map_a, map_b, g);
+    }
     if (bn == 256) return launch_dense<dense::EPI_CORR, 256>(s, map_a, map_b, g);
     return launch_dense<dense::EPI_CORR, 64>(s, map_a, map_b, g);
 }
@@ -2248,6 +2311,11 @@ int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, 
     if (n_fused_rows) *n_fused_rows = m->total_rows - other;
     if (n_other_rows) *n_other_rows = other;
     return THRML_OK;
+}
+int32_t thrml_debug_dense_pair_mode(int32_t mode) {
+    const int32_t before = g_dense_pair_mode;
+    g_dense_pair_mode = mode < 0 || mode > 2 ? 2 : mode;
+    return before;
 }
 int32_t thrml_state_launch_counts(const thrml_state* s, int64_t* block_launches, int64_t* persistent_launches) {
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
