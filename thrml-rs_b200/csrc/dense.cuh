@@ -195,25 +195,26 @@ __device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[
 #pragma unroll
             for (int j = 0; j < 4; ++j) rnd[4 * t + j] = x[j];
         }
-        // d = u - p with the approximate sigmoid p = 1 / (1 + 2^(-2 log2(e) gamma)) (a huge exponential gives p = 0, a
-        // vanishing one p = 1); the spin is the sign of d.  Draws within 4e-6 of p (four times the approximation's
-        // worst error) are redone with the exact sigmoid.  The integer pipe is the busy one here, so the decisions stay
-        // in the sign bits of d: no per-element bit masks are built.
+        // d = 2^24 (u - p) with the approximate sigmoid p = 1 / (1 + 2^(-2 log2(e) gamma)), as (r >> 8) - 1 / (2^-24 (1 + e))
+        // (a huge exponential gives p = 0, a vanishing one p = 1); the spin is the sign of d.  Draws within 4e-6 of p (four
+        // times the approximation's worst error) are redone with the exact sigmoid.  The integer pipe is the busy one
+        // here, so the decisions stay in the sign bits of d: no per-element bit masks are built.
+        constexpr float NEAR = 67.2f;  // 4e-6 * 2^24
         float d[16];
-        float nearest = 1.0f;
+        float nearest = 16777216.0f;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float gamma = __fadd_rn(bias[j], __uint_as_float(acc[j]));
-            float e;
+            float e, p24;
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gamma * -2.885390081777927f));
-            const float p = __fdividef(1.0f, 1.0f + e);
-            d[j] = u24(rnd[j]) - p;
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(e, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));
+            d[j] = __uint2float_rn(rnd[j] >> 8) - p24;
             nearest = fminf(nearest, fabsf(d[j]));
         }
-        if (__any_sync(0xffffffffu, nearest <= 4e-6f)) {
+        if (__any_sync(0xffffffffu, nearest <= NEAR)) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                if (fabsf(d[j]) <= 4e-6f) {
+                if (fabsf(d[j]) <= NEAR) {
                     const float xx = __fmul_rn(__fadd_rn(bias[j], __uint_as_float(acc[j])), 2.0f);
                     d[j] = u24(rnd[j]) <= det_sigmoid(xx) ? -1.0f : 1.0f;
                 }
