@@ -169,9 +169,8 @@ __device__ __forceinline__ void quad_transpose(uint32_t (&x)[4], int lane) {
 
 // Finishes 16 accumulator columns of one warp's 32 rows: `acc` holds this lane's row (row_base + lane), columns
 // col0..col0+15 of the whole problem.
-// `xpose` is 512 bytes of shared memory private to the warp.
 template <int EPI>
-__device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[16], int row_base, int col0, int lane, uint32_t* xpose) {
+__device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[16], int row_base, int col0, int lane) {
     const int row = row_base + lane;
     if (EPI == EPI_SAMPLE) {
         // row = chain, columns = nodes of the updated block
@@ -191,14 +190,10 @@ __device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[
         for (int t = 0; t < 4; ++t) {
             const int my_col = col0 + 4 * t + (lane & 3);
             const U4 r = philox4x32_10_rk(static_cast<uint32_t>(my_col), g.chain_word0 + static_cast<uint32_t>(row >> 2), 0u, TAG_SPIN, g.rk);
-            // 4x4 transpose inside each quad (word k of quad lane q -> word q of quad lane k) through shared memory: the
-            // load/store pipe is idle here, the integer pipe a shuffle-and-select transpose would use is the busy one
-            __syncwarp();
-            // quad lane q of quad Q stores its four words at word 32 q + 4 Q, so word (lane & 3) of quad lane j is at 32 j + lane
-            reinterpret_cast<uint4*>(xpose)[8 * (lane & 3) + (lane >> 2)] = make_uint4(r.x, r.y, r.z, r.w);
-            __syncwarp();
+            uint32_t x[4] = {r.x, r.y, r.z, r.w};
+            quad_transpose(x, lane);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) rnd[4 * t + j] = xpose[32 * j + lane];
+            for (int j = 0; j < 4; ++j) rnd[4 * t + j] = x[j];
         }
         // d = 2^24 (u - p) with the approximate sigmoid p = 1 / (1 + 2^(-2 log2(e) gamma)), as (r >> 8) - 1 / (2^-24 (1 + e))
         // (a huge exponential gives p = 0, a vanishing one p = 1); the spin is the sign of d.  Draws within 4e-6 of p (four
@@ -305,7 +300,6 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACC_BUFS], acc_empty[ACC_BUFS];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ __align__(16) uint32_t xpose[EPI == EPI_SAMPLE ? EPI_WARPS : 1][128];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tiles = g.tiles_m * g.tiles_n;
@@ -384,7 +378,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
                 uint32_t acc[16];
                 tmem_ld16_issue(taddr + c * 16, acc);
                 tmem_ld_wait();
-                finish_chunk<EPI>(g, acc, tm * BM + quarter * 32, tn * BN + c * 16, lane, xpose[EPI == EPI_SAMPLE ? warp - 2 : 0]);
+                finish_chunk<EPI>(g, acc, tm * BM + quarter * 32, tn * BN + c * 16, lane);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
@@ -476,7 +470,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
     __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[ACC_BUFS], acc_empty[ACC_BUFS];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ __align__(16) uint32_t xpose[EPI == EPI_SAMPLE ? EPI_WARPS : 1][128];
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_rank();
@@ -567,7 +560,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
                 uint32_t acc[16];
                 tmem_ld16_issue(taddr + c * 16, acc);
                 tmem_ld_wait();
-                finish_chunk<EPI>(g, acc, row_base, tn * BN + c * 16, lane, xpose[EPI == EPI_SAMPLE ? warp - 2 : 0]);
+                finish_chunk<EPI>(g, acc, row_base, tn * BN + c * 16, lane);
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

@@ -31,7 +31,34 @@ struct PottsArgs {
     uint32_t chain_word0, k0, k1;
 };
 
-__global__ void __launch_bounds__(256) k_potts_update(PottsArgs a) {
+// Exact Gumbel-argmax of one chain (byte `sh / 8` of the neighbour words): the rule of softmax.rs:60-97 with the
+// deterministic logarithm.  Kept out of line: the update kernel calls it for about one update in 10^4.
+__device__ __noinline__ uint32_t potts_exact_argmax(const float* s_tab, const float* unary_row, int K, int sh, uint32_t px, uint32_t mx, uint32_t py, uint32_t my,
+                                                    uint32_t pz, uint32_t mz, uint32_t in_block, uint32_t chain, uint32_t k0, uint32_t k1) {
+    const int KK = K * K;
+    float top = 0.f;
+    uint32_t arg = 0;
+    U4 rr;
+    for (int cat = 0; cat < K; ++cat) {
+        float th = __ldg(unary_row + cat);
+        th = __fadd_rn(th, s_tab[cat * K + ((px >> sh) & 0xffu)]);
+        th = __fadd_rn(th, s_tab[((mx >> sh) & 0xffu) * K + cat]);
+        th = __fadd_rn(th, s_tab[KK + cat * K + ((py >> sh) & 0xffu)]);
+        th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
+        th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
+        th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
+        if ((cat & 3) == 0) rr = philox4x32_10(in_block, chain, static_cast<uint32_t>(cat >> 2), TAG_CAT, k0, k1);
+        const float u = u23_open(pick(rr, cat & 3));
+        const float p = __fadd_rn(th, -det_log(-det_log(u)));
+        if (cat == 0 || p > top) { top = p; arg = cat; }
+    }
+    return arg;
+}
+
+// KT > 0: the category count as a compile-time constant.  The category loop then unrolls completely, which turns the
+// table offsets cat * K and the choice of the Philox word into immediates (the integer pipe is the busy one here).
+template <int KT>
+__global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     extern __shared__ float s_tab[];  // [3][K][K]
     for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[i] = a.tables[i];
     __syncthreads();
@@ -50,29 +77,52 @@ __global__ void __launch_bounds__(256) k_potts_update(PottsArgs a) {
     const uint32_t px = word(node_of(x + 1 == a.nx ? 0 : x + 1, y, z)), mx = word(node_of(x == 0 ? a.nx - 1 : x - 1, y, z));
     const uint32_t py = word(node_of(x, y + 1 == a.ny ? 0 : y + 1, z)), my = word(node_of(x, y == 0 ? a.ny - 1 : y - 1, z));
     const uint32_t pz = word(node_of(x, y, z + 1 == a.nz ? 0 : z + 1)), mz = word(node_of(x, y, z == 0 ? a.nz - 1 : z - 1));
-    const int K = a.K, KK = K * K;
-    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    const int K = KT > 0 ? KT : a.K, KK = K * K;
+    auto theta = [&](int cat, int sh, float un) {
+        float th = un;  // 0 + unary
+        th = __fadd_rn(th, s_tab[cat * K + ((px >> sh) & 0xffu)]);            // this node is U of its +x edge: T[c][s_v]
+        th = __fadd_rn(th, s_tab[((mx >> sh) & 0xffu) * K + cat]);            // and V of its -x edge: T[s_u][c]
+        th = __fadd_rn(th, s_tab[KK + cat * K + ((py >> sh) & 0xffu)]);
+        th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
+        th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
+        th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
+        return th;
+    };
+    auto noise = [&](int c, int cat) {
+        return philox4x32_10(static_cast<uint32_t>(in_block), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+    };
+    // First pass with fast logarithms.  The exact rule is argmax_c fl(theta_c - ln(-ln u_c)) with the deterministic
+    // logarithm (softmax.rs:84) and the first maximum winning (gumbel_argmax/kernel.rs:81-83).  Here -ln u comes from
+    // its series in w = 1 - u (exact in f32) when w < 2^-5, else from the intrinsic, whose absolute error of 2^-21.41
+    // then is at most 1.2e-5 of -ln u >= 0.0317; the outer intrinsic adds at most 3.6e-6.  Each score is therefore
+    // within 2e-5 of the exact one, and a leader more than 6e-5 ahead of the runner-up is the exact argmax.  Anything
+    // closer (about one update in 10^4) is recomputed exactly for that chain.
+    constexpr float MARGIN = 6e-5f;
+    float best[4], second[4];
     uint32_t arg[4] = {0, 0, 0, 0};
     U4 r[4];
-    for (int cat = 0; cat < K; ++cat) {
+#pragma unroll
+    for (int cat = 0; cat < (KT > 0 ? KT : K); ++cat) {
         const float un = __ldg(a.unary + node * K + cat);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const int sh = 8 * c;
-            float th = un;  // 0 + unary
-            th = __fadd_rn(th, s_tab[cat * K + ((px >> sh) & 0xffu)]);            // this node is U of its +x edge: T[c][s_v]
-            th = __fadd_rn(th, s_tab[((mx >> sh) & 0xffu) * K + cat]);            // and V of its -x edge: T[s_u][c]
-            th = __fadd_rn(th, s_tab[KK + cat * K + ((py >> sh) & 0xffu)]);
-            th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
-            th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
-            th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
-            if ((cat & 3) == 0)
-                r[c] = philox4x32_10(static_cast<uint32_t>(in_block), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+            const float th = theta(cat, 8 * c, un);
+            if ((cat & 3) == 0) r[c] = noise(c, cat);
             const float u = u23_open(pick(r[c], cat & 3));
-            const float p = __fadd_rn(th, -det_log(-det_log(u)));  // softmax.rs:84
-            if (cat == 0 || p > best[c]) { best[c] = p; arg[c] = cat; }  // first maximum wins (gumbel_argmax/kernel.rs:81-83)
+            const float w = 1.0f - u;
+            const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
+            const float l1 = w < 0.03125f ? series : -__logf(u);
+            const float p = th - __logf(l1);
+            if (cat == 0) { best[c] = p; second[c] = -3.0e38f; }
+            else if (p > best[c]) { second[c] = best[c]; best[c] = p; arg[c] = cat; }
+            else if (p > second[c]) second[c] = p;
         }
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (!(best[c] - second[c] > MARGIN))
+            arg[c] = potts_exact_argmax(s_tab, a.unary + node * K, K, 8 * c, px, mx, py, my, pz, mz, static_cast<uint32_t>(in_block),
+                                        4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1);
     uint32_t out = 0;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
@@ -227,7 +277,16 @@ int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
     CU_TRY(cudaSetDevice(P->device));
     PottsArgs a{static_cast<uint8_t*>(P->state.p), static_cast<const float*>(P->tables.p), static_cast<const float*>(P->unary.p), P->nx, P->ny, P->nz, P->K, colour, P->ld, P->n_chains,
                 static_cast<uint32_t>(P->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
-    k_potts_update<<<potts_grid(P), dim3(32, 8), static_cast<size_t>(3) * P->K * P->K * 4, P->ctx->stream>>>(a);
+    const dim3 grid = potts_grid(P), block(32, 8);
+    const size_t smem = static_cast<size_t>(3) * P->K * P->K * 4;
+    switch (P->K) {
+        case 3: k_potts_update<3><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 4: k_potts_update<4><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 5: k_potts_update<5><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 8: k_potts_update<8><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 10: k_potts_update<10><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        default: k_potts_update<0><<<grid, block, smem, P->ctx->stream>>>(a); break;
+    }
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }

@@ -1,0 +1,576 @@
+// Block-update kernels: generic spin and categorical updates for any slot-table structure, the threshold-table spin
+// update (one launch per block), and its two multi-sweep variants for small programs.
+//
+// State layout: one byte per node and chain, chains innermost: state[class][global position][ld], ld = chains rounded
+// up to 16 bytes.  A neighbour gather therefore reads one contiguous row segment per neighbour, whatever the graph.
+#pragma once
+#include <cooperative_groups.h>
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "device_math.cuh"
+
+using namespace thrml;
+
+constexpr int MAX_TAILS = 8;
+constexpr int LUT_BITS = 8;              // a threshold table covers at most 8 neighbour spins
+constexpr int LUT_SIZE = 1 << LUT_BITS;  // entries per node
+
+// Device view of one slot table.
+struct DevTable {
+    int32_t k, wdim, n_spin, n_tails;
+    const int32_t* idx[MAX_TAILS];
+    const uint8_t* active;
+    const float* w;
+};
+
+struct UpdateArgs {
+    const DevTable* tabs;
+    int32_t n_tabs;
+    int32_t n;            // nodes in the block
+    int32_t K;            // categories (categorical kernel)
+    int64_t ld;           // bytes per state row
+    int64_t n_chains;
+    uint32_t chain_word0; // global chain id of local chain 0, divided by 4
+    const uint8_t* spin;  // class rows (may be null when the class is absent)
+    const uint8_t* cat;
+    uint8_t* dst;         // first row of the block's output (state rows or staging rows)
+    uint32_t k0, k1;      // block key
+    const float* inj;     // injected uniforms or null
+    float* fields;        // debug output or null
+};
+
+__device__ __forceinline__ uint32_t ld_word(const uint8_t* base, int64_t row, int64_t ld, int quad) {
+    return *reinterpret_cast<const uint32_t*>(base + row * ld + 4 * static_cast<int64_t>(quad));
+}
+
+// Generic spin update: any number of tables, spin tails and one optional categorical tail per table.
+// One thread = one node x four consecutive chains.  MODE 0 in-kernel noise, 1 injected noise, 2 write gamma only.
+// Field accumulation order: per table, slots left to right from zero; tables left to right (spin_gibbs.rs:527-582).
+template <int MODE>
+__global__ void __launch_bounds__(256) k_spin_generic(UpdateArgs a) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    float gamma[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int t = 0; t < a.n_tabs; ++t) {
+        const DevTable T = a.tabs[t];
+        float gs[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+            if (!T.active[flat]) continue;
+            float sp[4] = {1.f, 1.f, 1.f, 1.f};
+            for (int tl = 0; tl < T.n_spin; ++tl) {
+                const uint32_t wd = ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sp[c] = __fmul_rn(sp[c], ((wd >> (8 * c)) & 1u) ? 1.0f : -1.0f);
+            }
+            if (T.n_tails > T.n_spin) {  // first categorical tail selects the weight (spin_gibbs.rs:556-577)
+                const uint32_t wd = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t x = (wd >> (8 * c)) & 0xffu;
+                    const float wv = x < static_cast<uint32_t>(T.wdim) ? T.w[flat * T.wdim + x] : 0.0f;
+                    gs[c] = __fadd_rn(gs[c], __fmul_rn(wv, sp[c]));
+                }
+            } else {
+                const float wv = T.w[flat * T.wdim];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) gs[c] = __fadd_rn(gs[c], __fmul_rn(wv, sp[c]));
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) gamma[c] = __fadd_rn(gamma[c], gs[c]);
+    }
+    if (MODE == 2) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+            if (chain < a.n_chains) a.fields[chain * a.n + node] = gamma[c];
+        }
+        return;
+    }
+    U4 r{0, 0, 0, 0};
+    if (MODE == 0) r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, a.k0, a.k1);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+        const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+        float u;
+        if (MODE == 1) u = chain < a.n_chains ? a.inj[static_cast<int64_t>(node) * a.n_chains + chain] : 2.0f;
+        else u = u24(pick(r, c));
+        const float p = det_sigmoid(__fmul_rn(gamma[c], 2.0f));  // spin_gibbs.rs:95
+        if (u <= p && chain < a.n_chains) out |= 1u << (8 * c);   // spin_gibbs.rs:97
+    }
+    *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// Generic categorical update (softmax.rs:586-709 + 60-97): logits theta[c] = sum over tables and slots of
+// active * prod(2s-1) * W[own c, neighbour category]; draw = argmax_c(theta[c] - ln(-ln u_c)), first maximum wins.
+template <int MODE>
+__global__ void __launch_bounds__(256) k_cat_generic(UpdateArgs a) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const int K = a.K;
+    float best[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t arg[4] = {0, 0, 0, 0};
+    U4 r[4];
+    for (int cat = 0; cat < K; ++cat) {
+        float th[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int t = 0; t < a.n_tabs; ++t) {
+            const DevTable T = a.tabs[t];
+            const bool has_cat = T.n_tails > T.n_spin;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int j = 0; j < T.k; ++j) {
+                const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+                if (!T.active[flat]) continue;
+                float sp[4] = {1.f, 1.f, 1.f, 1.f};
+                for (int tl = 0; tl < T.n_spin; ++tl) {
+                    const uint32_t wd = ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sp[c] = __fmul_rn(sp[c], ((wd >> (8 * c)) & 1u) ? 1.0f : -1.0f);
+                }
+                if (has_cat) {
+                    const uint32_t wd = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t x = (wd >> (8 * c)) & 0xffu;
+                        if (x >= static_cast<uint32_t>(K)) x = K - 1;
+                        sum[c] = __fadd_rn(sum[c], __fmul_rn(sp[c], T.w[flat * T.wdim + cat * K + x]));
+                    }
+                } else {
+                    const float wv = T.w[flat * T.wdim + cat];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) sum[c] = __fadd_rn(sum[c], __fmul_rn(sp[c], wv));
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) th[c] = __fadd_rn(th[c], sum[c]);
+        }
+        if (MODE == 2) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+                if (chain < a.n_chains) a.fields[(chain * a.n + node) * K + cat] = th[c];
+            }
+            continue;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
+            float u;
+            if (MODE == 1) {
+                u = chain < a.n_chains ? a.inj[(static_cast<int64_t>(node) * K + cat) * a.n_chains + chain] : 0.5f;
+            } else {
+                if ((cat & 3) == 0)
+                    r[c] = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+                u = u23_open(pick(r[c], cat & 3));
+            }
+            const float g = -det_log(-det_log(u));  // softmax.rs:84
+            const float p = __fadd_rn(th[c], g);
+            if (cat == 0 || p > best[c]) {  // strict >: the first maximum wins (gumbel_argmax/kernel.rs:81-83)
+                best[c] = p;
+                arg[c] = cat;
+            }
+        }
+    }
+    if (MODE == 2) return;
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
+    *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
+// Threshold tables for spin blocks whose nodes see at most 8 neighbour spins through single-spin-tail tables:
+// lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
+// (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
+// k_spin_generic, and u <= p  <=>  (r >> 8) <= floor(p * 2^24)  <=>  r <= (floor(p * 2^24) << 8 | 0xff).
+__global__ void __launch_bounds__(256) k_build_lut(const DevTable* tabs, int32_t n_tabs, int32_t n, uint32_t* lut) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t node = gid >> LUT_BITS;
+    const uint32_t cfg = static_cast<uint32_t>(gid) & (LUT_SIZE - 1);
+    if (node >= n) return;
+    float gamma = 0.f;
+    int bit = 0;
+    for (int t = 0; t < n_tabs; ++t) {
+        const DevTable T = tabs[t];
+        float gs = 0.f;
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = node * T.k + j;
+            if (!T.active[flat]) continue;
+            float sp = 1.0f;
+            if (T.n_spin == 1) {
+                sp = ((cfg >> bit) & 1u) ? 1.0f : -1.0f;
+                ++bit;
+            }
+            gs = __fadd_rn(gs, __fmul_rn(T.w[flat], sp));
+        }
+        gamma = __fadd_rn(gamma, gs);
+    }
+    const float p = det_sigmoid(__fmul_rn(gamma, 2.0f));
+    const uint32_t fl = static_cast<uint32_t>(__fmul_rn(p, 16777216.0f));  // exact: p*2^24 <= 2^24
+    lut[gid] = fl >= 16777216u ? 0xffffffffu : ((fl << 8) | 0xffu);
+}
+
+struct LutArgs {
+    const int32_t* nbr;    // [n][8] global spin positions, -1 = unused slot
+    const uint32_t* lut;   // [n][256]
+    const uint8_t* spin;
+    uint8_t* dst;
+    int64_t ld;
+    int32_t n;
+    int32_t n_chunks;      // ld / 16
+    uint32_t chain_word0;
+    PhiloxRoundKeys rk;    // round keys of the block key
+    // fused moment observer (ACC only): row of <s_i> per node, row of <s_i s_j> per (node, slot), -1 = not owned here
+    int64_t n_chains;
+    const int32_t* m1_row;
+    const int32_t* m2_row;
+    long long* sums;
+};
+
+// Bytes 0xff for the chains of word q of chunk ch that exist (chain index < n_chains).
+__device__ __forceinline__ uint32_t valid_mask(int64_t n_chains, int ch, int q) {
+    const int64_t left = n_chains - (16 * static_cast<int64_t>(ch) + 4 * q);
+    if (left >= 4) return 0xffffffffu;
+    if (left <= 0) return 0u;
+    return 0xffffffffu >> (8 * (4 - static_cast<int>(left)));
+}
+__device__ __forceinline__ uint32_t maj3(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | (c & (a | b)); }
+
+// Bit-sliced counters: plane[p] holds bit p of 32 independent counts, one per bit position of a state word
+// (bit j of byte b = "neighbour slot j differs from the new spin" for the chain in byte b).  Adding the four words of a
+// pass costs 17 logic ops for all 8 slots and 4 chains at once; counts up to 63 fit, i.e. 15 passes of 4 words.
+struct SliceCounter {
+    uint32_t p0 = 0, p1 = 0, p2 = 0, p3 = 0, p4 = 0, p5 = 0;
+    __device__ __forceinline__ void add4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+        const uint32_t s1 = a ^ b ^ c, c1 = maj3(a, b, c);  // a+b+c = s1 + 2 c1
+        const uint32_t ones = s1 ^ d, c2 = s1 & d;           // + d
+        const uint32_t twos = c1 ^ c2, fours = c1 & c2;
+        uint32_t k = p0 & ones;
+        p0 ^= ones;
+        uint32_t k2 = maj3(p1, twos, k);
+        p1 ^= twos ^ k;
+        k = maj3(p2, fours, k2);
+        p2 ^= fours ^ k2;
+        k2 = p3 & k;
+        p3 ^= k;
+        k = p4 & k2;
+        p4 ^= k2;
+        p5 ^= k;
+    }
+    // count of bit position `j` summed over the four bytes of the word
+    __device__ __forceinline__ uint32_t total(int j) const {
+        const uint32_t m = 0x01010101u << j;
+        return __popc(p0 & m) + 2 * __popc(p1 & m) + 4 * __popc(p2 & m) + 8 * __popc(p3 & m) + 16 * __popc(p4 & m) + 32 * __popc(p5 & m);
+    }
+};
+constexpr int ACC_SEGMENT_PASSES = 15;  // 15 passes x 4 words = 60 <= 63
+
+// Threshold-table spin update: one warp per node, each lane 16 chains per pass.  The neighbour configuration of four
+// chains is assembled with shifts inside one 32-bit word (state bytes are 0/1), then one shared-memory lookup and one
+// compare per chain replace the field accumulation and the sigmoid.
+// ACC: the moment observer fused into the update (moment.rs:205-233 for first moments and pair products): the warp
+// that updates node i is the only one that touches i's rows, so the sums are updated without atomics.  A pair row is
+// owned by the endpoint updated later in the sweep, when both values are final.  Disagreements with each neighbour
+// slot are counted in bit-sliced counters and reduced once per node.
+// COHERENT: neighbour rows may have been written earlier in the same launch (persistent multi-sweep kernel), so they are
+// read through L2 (ld.global.cg) instead of the read-only path.
+template <bool ACC, bool COHERENT>
+__device__ __forceinline__ void lut_block_update(const LutArgs& a, uint32_t* my) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
+        const uint4* src = reinterpret_cast<const uint4*>(a.lut + static_cast<int64_t>(node) * LUT_SIZE);
+        __syncwarp();
+        reinterpret_cast<uint4*>(my)[lane] = __ldg(src + lane);
+        reinterpret_cast<uint4*>(my)[lane + 32] = __ldg(src + lane + 32);
+        int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
+        int32_t my_row = -1;
+        uint32_t own = 0;
+        if (ACC) {
+            if (lane < LUT_BITS) my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * LUT_BITS + lane);
+            else if (lane == LUT_BITS) my_row = __ldg(a.m1_row + node);
+            own = __ballot_sync(0xffffffffu, my_row >= 0);
+        }
+        __syncwarp();
+        int32_t nbj[LUT_BITS];
+#pragma unroll
+        for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
+        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+        uint32_t mine = 0;  // lane j < 8: disagreements with slot j; lane 8: number of ones
+        for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {
+            const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
+            SliceCounter cnt;
+            uint32_t ones = 0;
+            for (int ch = seg + lane; ch < seg_end; ch += 32) {
+                uint4 v[LUT_BITS];
+#pragma unroll
+                for (int j = 0; j < LUT_BITS; ++j) {
+                    v[j] = make_uint4(0, 0, 0, 0);
+                    if (nbj[j] >= 0) {
+                        const uint4* src_row = reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch;
+                        v[j] = COHERENT ? __ldcg(src_row) : __ldg(src_row);
+                    }
+                }
+                uint32_t cfg[4] = {0, 0, 0, 0};
+#pragma unroll
+                for (int j = 0; j < LUT_BITS; ++j) {
+                    cfg[0] += v[j].x << j;
+                    cfg[1] += v[j].y << j;
+                    cfg[2] += v[j].z << j;
+                    cfg[3] += v[j].w << j;
+                }
+                uint32_t o[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                    uint32_t w = 0;
+                    w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
+                    w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
+                    w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
+                    w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
+                    o[q] = w;
+                }
+                reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+                if (ACC && own) {
+                    uint32_t d[4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) d[q] = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+                    if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {        // ragged last chunk: drop chains that do not exist
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const uint32_t vm = valid_mask(a.n_chains, ch, q);
+                            d[q] &= vm;
+                            o[q] &= vm;
+                        }
+                    }
+                    cnt.add4(d[0], d[1], d[2], d[3]);
+                    ones += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
+                }
+            }
+            if (ACC && own) {
+                ones = __reduce_add_sync(0xffffffffu, ones);
+                if (lane == LUT_BITS) mine += ones;
+#pragma unroll
+                for (int j = 0; j < LUT_BITS; ++j)
+                    if ((own >> j) & 1u) {
+                        const uint32_t t = __reduce_add_sync(0xffffffffu, cnt.total(j));
+                        if (lane == j) mine += t;
+                    }
+            }
+        }
+        if (ACC && my_row >= 0) {
+            const long long val = lane == LUT_BITS ? 2ll * mine - a.n_chains : a.n_chains - 2ll * mine;
+            if (COHERENT) __stcg(a.sums + my_row, __ldcg(a.sums + my_row) + val);
+            else a.sums[my_row] += val;
+        }
+    }
+}
+
+template <bool ACC>
+__global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ LutArgs a) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    lut_block_update<ACC, false>(a, s_lut[threadIdx.x >> 5]);
+}
+
+// Persistent multi-sweep variant for cache-resident programs: one cooperative launch walks a list of block updates
+// (sweep-major, blocks in sampling order) with a grid-wide barrier after each, instead of one launch per block update.
+// For small models a block update takes a microsecond or two and the launches themselves dominate.
+__global__ void __launch_bounds__(256, 2) k_spin_lut_persistent(const LutArgs* steps, const uint8_t* acc, int32_t n_steps) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    for (int32_t i = 0; i < n_steps; ++i) {
+        const LutArgs a = steps[i];  // by value: the round keys stay in registers across the update's stores
+        if (__ldg(acc + i)) lut_block_update<true, true>(a, s_lut[threadIdx.x >> 5]);
+        else lut_block_update<false, true>(a, s_lut[threadIdx.x >> 5]);
+        grid.sync();
+    }
+}
+
+// Chain-sliced variant for programs small enough that four chains of every spin fit in one CTA's shared memory.
+// Chains never interact, so a CTA that owns chains 4q..4q+3 can run a whole schedule on its own: it loads one 32-bit
+// word per spin (4 chains), walks the list of block updates with a CTA barrier after each, and stores the words back.
+// No grid barrier, no launch per block.  One thread updates one node for the four chains with exactly one Philox call
+// (the four output words are the four chains' draws), so the states are the bits the other kernels produce.
+// The fused observer keeps signed per-row partial sums in shared memory (each row is owned by one node, hence by one
+// thread) and adds them to the global sums once at the end.
+struct SliceBlock {
+    const int32_t* nbr;    // [n][8]
+    const uint32_t* lut;   // [n][256]
+    const int32_t* m1_row; // [n] or null
+    const int32_t* m2_row; // [n][8] or null
+    int32_t n;
+    int32_t offset;        // first global spin position of the block
+    int32_t lut_shift;     // resident copy: 2^lut_shift table entries per node (the block's largest neighbour count)
+    int32_t smem_word;     // resident copy: first word of this block's tables in dynamic shared memory
+};
+struct SliceStep {
+    int32_t block;
+    int32_t acc;
+    PhiloxRoundKeys rk;
+};
+static_assert(sizeof(SliceStep) == 88, "SliceStep is copied word by word");
+constexpr int SLICE_MAX_BLOCKS = 32;
+struct SliceArgs {
+    const SliceBlock* blocks;
+    const SliceStep* steps;
+    int32_t n_blocks;
+    int32_t n_steps;
+    int32_t n_spin;    // spins of the class (free and clamped)
+    int32_t n_rows;    // observer rows (0 without observer)
+    int32_t resident;  // 1: neighbour lists, the reachable part of the threshold tables and the observer's row maps are copied to shared memory first
+    uint32_t chain_word0;
+    uint8_t* spin;
+    int64_t ld;
+    int64_t n_chains;
+    unsigned long long* sums;
+};
+constexpr int SLICE_STEP_WORDS = sizeof(SliceStep) / 4;
+// words of dynamic shared memory a block's resident tables take: neighbours, compact thresholds, observer row maps
+// (rounded to 16 bytes; the two arrays read with 16-byte loads come first)
+inline int64_t slice_block_words(int64_t n, int lut_shift, bool acc) {
+    const int64_t n_pad = (n + 31) / 32 * 32;
+    return (n * LUT_BITS + (n_pad << lut_shift) + (acc ? n * (1 + LUT_BITS) : 0) + 3) / 4 * 4;
+}
+
+// RESIDENT: neighbour lists, the reachable part of the threshold tables and the observer's row maps are copied into
+// shared memory first (word offsets into s_dyn; thresholds entry-major with a node stride that is a multiple of 32, so
+// consecutive nodes hit distinct banks whatever their configurations); otherwise they are read from global memory.
+struct SliceView {
+    const int32_t* nbr;
+    const uint32_t* lut;
+    const int32_t* m1;
+    const int32_t* m2;
+    int32_t nbr_w, lut_w, m1_w, m2_w;  // resident: first words in s_dyn (m1_w < 0: no observer rows)
+    int32_t n, offset, n_pad;
+    int32_t deg;  // largest neighbour count in the block: slots from deg on are empty for every node
+};
+template <bool RESIDENT>
+__global__ void __launch_bounds__(512) k_spin_lut_sliced(const __grid_constant__ SliceArgs a) {
+    extern __shared__ __align__(16) uint32_t s_dyn[];
+    __shared__ SliceStep s_step[2];
+    __shared__ SliceView s_blk[SLICE_MAX_BLOCKS];
+    uint32_t* st = s_dyn;                                          // [n_spin]
+    int32_t* part = reinterpret_cast<int32_t*>(s_dyn + a.n_spin);  // [n_rows]
+    const int32_t* sw = reinterpret_cast<const int32_t*>(s_dyn);
+    const int tid = threadIdx.x, T = blockDim.x;
+    const int quad = blockIdx.x;
+    const int64_t remaining = a.n_chains - 4ll * quad;
+    const int left = remaining >= 4 ? 4 : static_cast<int>(remaining);  // chains of this slice that exist
+    const uint32_t vm = left >= 4 ? 0xffffffffu : (0xffffffffu >> (8 * (4 - left)));
+    for (int i = tid; i < a.n_spin; i += T) st[i] = *reinterpret_cast<const uint32_t*>(a.spin + static_cast<int64_t>(i) * a.ld + 4 * quad);
+    for (int i = tid; i < a.n_rows; i += T) part[i] = 0;
+    if (tid < SLICE_STEP_WORDS) reinterpret_cast<uint32_t*>(&s_step[0])[tid] = __ldg(reinterpret_cast<const uint32_t*>(a.steps) + tid);
+    if (tid < a.n_blocks) {
+        const SliceBlock b = a.blocks[tid];
+        SliceView v;
+        v.nbr = b.nbr; v.lut = b.lut; v.m1 = b.m1_row; v.m2 = b.m2_row;
+        v.n = b.n; v.offset = b.offset; v.n_pad = (b.n + 31) / 32 * 32;
+        v.deg = b.lut_shift;
+        v.nbr_w = b.smem_word;
+        v.m2_w = v.nbr_w + b.n * LUT_BITS;
+        v.lut_w = b.m1_row ? v.m2_w + b.n * LUT_BITS : v.m2_w;
+        v.m1_w = b.m1_row ? v.lut_w + (v.n_pad << b.lut_shift) : -1;
+        s_blk[tid] = v;
+    }
+    __syncthreads();
+    if (RESIDENT) {
+        for (int bi = 0; bi < a.n_blocks; ++bi) {
+            const SliceView& v = s_blk[bi];
+            const int shift = a.blocks[bi].lut_shift, per = 1 << shift;
+            int32_t* w = reinterpret_cast<int32_t*>(s_dyn);
+            for (int i = tid; i < v.n * LUT_BITS; i += T) w[v.nbr_w + i] = __ldg(v.nbr + i);
+            for (int i = tid; i < v.n * per; i += T) {
+                const int node = i >> shift, c = i & (per - 1);
+                s_dyn[v.lut_w + c * v.n_pad + node] = __ldg(v.lut + static_cast<int64_t>(node) * LUT_SIZE + c);
+            }
+            if (v.m1_w >= 0) {
+                for (int i = tid; i < v.n; i += T) w[v.m1_w + i] = __ldg(v.m1 + i);
+                for (int i = tid; i < v.n * LUT_BITS; i += T) w[v.m2_w + i] = __ldg(v.m2 + i);
+            }
+        }
+        __syncthreads();
+    }
+    for (int32_t i = 0; i < a.n_steps; ++i) {
+        const SliceStep& sp = s_step[i & 1];
+        const SliceView& v = s_blk[sp.block];
+        const int32_t n = v.n;
+        const bool acc = sp.acc != 0;
+        const bool wide = v.deg > 4;  // uniform over the CTA: blocks of degree <= 4 (lattices) skip the upper four slots
+        for (int node = tid; node < n; node += T) {
+            int4 n0, n1 = make_int4(-1, -1, -1, -1);
+            if (RESIDENT) {
+                n0 = *reinterpret_cast<const int4*>(sw + v.nbr_w + node * LUT_BITS);
+                if (wide) n1 = *reinterpret_cast<const int4*>(sw + v.nbr_w + node * LUT_BITS + 4);
+            } else {
+                n0 = __ldg(reinterpret_cast<const int4*>(v.nbr + static_cast<int64_t>(node) * LUT_BITS));
+                if (wide) n1 = __ldg(reinterpret_cast<const int4*>(v.nbr + static_cast<int64_t>(node) * LUT_BITS) + 1);
+            }
+            uint32_t cfg = 0;
+            if (n0.x >= 0) cfg += st[n0.x];
+            if (n0.y >= 0) cfg += st[n0.y] << 1;
+            if (n0.z >= 0) cfg += st[n0.z] << 2;
+            if (n0.w >= 0) cfg += st[n0.w] << 3;
+            if (wide) {
+                if (n1.x >= 0) cfg += st[n1.x] << 4;
+                if (n1.y >= 0) cfg += st[n1.y] << 5;
+                if (n1.z >= 0) cfg += st[n1.z] << 6;
+                if (n1.w >= 0) cfg += st[n1.w] << 7;
+            }
+            uint32_t t0, t1, t2, t3;
+            if (RESIDENT) {  // configuration bytes stay below 2^(neighbour count), inside the copied part of the table
+                const uint32_t* L = s_dyn + v.lut_w + node;
+                t0 = L[(cfg & 0xffu) * v.n_pad];
+                t1 = L[((cfg >> 8) & 0xffu) * v.n_pad];
+                t2 = L[((cfg >> 16) & 0xffu) * v.n_pad];
+                t3 = L[(cfg >> 24) * v.n_pad];
+            } else {
+                const uint32_t* L = v.lut + static_cast<int64_t>(node) * LUT_SIZE;
+                t0 = __ldg(L + (cfg & 0xffu));
+                t1 = __ldg(L + ((cfg >> 8) & 0xffu));
+                t2 = __ldg(L + ((cfg >> 16) & 0xffu));
+                t3 = __ldg(L + (cfg >> 24));
+            }
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, sp.rk);
+            uint32_t o = (r.x <= t0) ? 1u : 0u;
+            o |= (r.y <= t1) ? 0x100u : 0u;
+            o |= (r.z <= t2) ? 0x10000u : 0u;
+            o |= (r.w <= t3) ? 0x1000000u : 0u;
+            st[v.offset + node] = o;  // neighbours are never in the block being updated, so nobody reads this word before the barrier
+            if (acc && v.m1_w >= 0) {
+                int32_t row1;
+                int4 r0, r1 = make_int4(-1, -1, -1, -1);
+                if (RESIDENT) {
+                    row1 = sw[v.m1_w + node];
+                    r0 = *reinterpret_cast<const int4*>(sw + v.m2_w + node * LUT_BITS);
+                    if (wide) r1 = *reinterpret_cast<const int4*>(sw + v.m2_w + node * LUT_BITS + 4);
+                } else {
+                    row1 = __ldg(v.m1 + node);
+                    r0 = __ldg(reinterpret_cast<const int4*>(v.m2 + static_cast<int64_t>(node) * LUT_BITS));
+                    if (wide) r1 = __ldg(reinterpret_cast<const int4*>(v.m2 + static_cast<int64_t>(node) * LUT_BITS) + 1);
+                }
+                if (row1 >= 0) part[row1] += 2 * __popc(o & vm) - left;
+                const uint32_t d = (cfg ^ (o * 255u)) & vm;  // bit j of a byte: neighbour j differs from the new spin
+                if (r0.x >= 0) part[r0.x] += left - 2 * __popc(d & 0x01010101u);
+                if (r0.y >= 0) part[r0.y] += left - 2 * __popc(d & 0x02020202u);
+                if (r0.z >= 0) part[r0.z] += left - 2 * __popc(d & 0x04040404u);
+                if (r0.w >= 0) part[r0.w] += left - 2 * __popc(d & 0x08080808u);
+                if (wide) {
+                    if (r1.x >= 0) part[r1.x] += left - 2 * __popc(d & 0x10101010u);
+                    if (r1.y >= 0) part[r1.y] += left - 2 * __popc(d & 0x20202020u);
+                    if (r1.z >= 0) part[r1.z] += left - 2 * __popc(d & 0x40404040u);
+                    if (r1.w >= 0) part[r1.w] += left - 2 * __popc(d & 0x80808080u);
+                }
+            }
+        }
+        if (i + 1 < a.n_steps && tid < SLICE_STEP_WORDS)
+            reinterpret_cast<uint32_t*>(&s_step[(i + 1) & 1])[tid] = __ldg(reinterpret_cast<const uint32_t*>(a.steps + i + 1) + tid);
+        __syncthreads();
+    }
+    for (int i = tid; i < a.n_spin; i += T) *reinterpret_cast<uint32_t*>(a.spin + static_cast<int64_t>(i) * a.ld + 4 * quad) = st[i];
+    for (int i = tid; i < a.n_rows; i += T)
+        if (part[i] != 0) atomicAdd(a.sums + i, static_cast<unsigned long long>(static_cast<long long>(part[i])));
+}
