@@ -401,7 +401,7 @@ __global__ void __launch_bounds__(THREADS, 1) k_dense_gemm(const __grid_constant
 // Roles per CTA as in k_dense_gemm.  Hand-overs: every TMA load of either CTA completes on the LEADER's (rank 0) full
 // barrier; the leader's single MMA thread issues the pair's MMAs and commits each stage to the empty barrier of both
 // CTAs and each finished accumulator to the full barrier of both; the epilogue warps of both CTAs release an
-// accumulator on the leader's barrier.  No multicast is used anywhere.  All waits are bounded; a cluster barrier
+// accumulator on the leader's barrier.  Every load and every arrival names one destination CTA.  All waits are bounded; a cluster barrier
 // before exit keeps either CTA's shared memory alive until its peer's last remote arrival.
 // ---------------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_rank() {
