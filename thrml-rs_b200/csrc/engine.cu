@@ -1103,6 +1103,7 @@ int32_t thrml_run_blocks(thrml_state* s, uint64_t key, int64_t n_iters, const th
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
     if (n_iters < 0) return fail(THRML_ERR_INVALID_ARG, "n_iters must be non-negative");
     CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    s->pending.clear();  // sweeps queued by a call that failed half-way are not replayed
     NoiseCursor nc;
     if (inj && inj->u) { nc.u = inj->u; nc.len = inj->len; }
     if (int32_t rc = run(s, key, n_iters, nc.u ? &nc : nullptr)) return rc;
@@ -1596,6 +1597,7 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
     if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
     if (obs_out && (!obs_blocks || n_obs_blocks <= 0)) return fail(THRML_ERR_INVALID_ARG, "obs_out needs a block list");
     CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    s->pending.clear();
     int64_t obs_rows = 0;
     for (int32_t i = 0; i < n_obs_blocks; ++i) {
         if (int32_t rc = check_block(s, obs_blocks[i])) return rc;
@@ -1634,6 +1636,7 @@ int32_t thrml_sample_states_packed(thrml_state* s, uint64_t key, int64_t n_warmu
     if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
     thrml_program* p = s->prog;
     CU_TRY(cudaSetDevice(p->ctx->device));
+    s->pending.clear();
     cudaStream_t st = p->ctx->stream;
     int64_t rows = 0;
     for (int32_t i = 0; i < n_obs_blocks; ++i) {

@@ -154,10 +154,9 @@ __global__ void __launch_bounds__(256) k_cat_generic(UpdateArgs a) {
                 const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
                 if (chain < a.n_chains) a.fields[(chain * a.n + node) * K + cat] = th[c];
             }
-            continue;
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; MODE != 2 && c < 4; ++c) {  // no draws in the fields-only instantiation
             const int64_t chain = 4 * static_cast<int64_t>(quad) + c;
             float u;
             if (MODE == 1) {
