@@ -102,7 +102,9 @@ def test_kernel_selection(T, O):
     prog = T.Program(M.fill(T.Builder(cases["graph8"]["kinds"]), cases["graph8"]))
     assert all(prog.block_kernel(b) == 1 for b in range(len(cases["graph8"]["free"])))
     prog = T.Program(M.fill(T.Builder(cases["graph12"]["kinds"]), cases["graph12"]))
-    assert any(prog.block_kernel(b) == 0 for b in range(len(cases["graph12"]["free"])))
+    assert all(prog.block_kernel(b) == 4 for b in range(len(cases["graph12"]["free"])))  # 12 neighbours + a bias: too many for a threshold table
+    prog = T.Program(M.fill(T.Builder(cases["mixed"]["kinds"]), cases["mixed"]))
+    assert prog.block_kernel(0) == 0  # categorical tails and three-spin factors: the generic gather kernel
     prog = T.Program(M.fill(T.Builder(cases["potts"]["kinds"]), cases["potts"]))
     assert all(prog.block_kernel(b) == 2 for b in range(2))
 
@@ -289,3 +291,34 @@ def test_packed_state_streaming_matches_byte_observer(T, O):
         unpacked = ((bits[:, :, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(5, bytes_.shape[1], -1)[:, :, :chains]
         assert np.array_equal(unpacked.astype(np.uint8), bytes_)
         assert np.all(((bits[:, :, :, None] >> np.arange(32, dtype=np.uint32)) & 1).reshape(5, bytes_.shape[1], -1)[:, :, chains:] == 0)
+
+
+@pytest.mark.parametrize("degree,chains", [(12, 100), (20, 33), (30, 600)])
+def test_sequential_sum_kernel_matches_oracle(T, O, degree, chains):
+    """Spin blocks with 9 to 32 active slots per node: the warp-per-node kernel that adds the field entry by entry."""
+    desc, info = M.ising_random_graph(T, 260, degree, 100 + degree, w_sigma=0.4, bias_sigma=0.3)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 3)
+    assert all(prog.block_kernel(b) == 4 for b in range(len(desc["free"])))
+    gs.run_blocks(17, 6)
+    os_.run_blocks(17, 6)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    spec = moment_spec(desc, info)
+    gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    gs.sample_with_observation(5, 1, 3, 2, moments=gm)
+    os_.sample_with_observation(5, 1, 3, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(2):
+        assert np.array_equal(gm.read(t)[0], om.read(t)[0])
+    # new couplings reach the entry lists
+    J2 = (info["J"] * -0.7).astype(np.float32)
+    desc2 = dict(desc, ops=[("add_ising", np.arange(info["n"]), info["b"], info["edges"], J2, info["beta"])])
+    gb2, ob2 = M.build_both(T, O, desc2)
+    for blk in range(len(desc["free"])):
+        for t, tab in enumerate(gb2.tables(blk)):
+            prog.update_weights(blk, t, tab["w"].ravel())
+    os2 = O.State(ob2, chains)
+    for i in range(n_blocks_of(desc)):
+        os2.set_block(i, os_.get_block(i))
+    gs.run_blocks(6, 2)
+    os2.run_blocks(6, 2)
+    assert_states_equal(gs, os2, n_blocks_of(desc))

@@ -48,6 +48,7 @@ struct BlockProg {
     DevBuf d_tabs;   // DevTable[n_tabs]
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
+    DevBuf d_seq_nbr, d_seq_w, d_seq_first, d_seq_cnt;  // entry lists of the sequential-sum kernel (kernel 4)
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
     int32_t max_deg = 0;         // largest number of neighbour slots any node of the block uses (threshold-table blocks)
     int32_t order = -1;          // position of the block's superblock in the sweep; -1 for clamped blocks
@@ -128,6 +129,7 @@ struct thrml_moments {
     int64_t total_rows = 0;
     int32_t K = 0;
     DevBuf d_row_ptr, d_mem_sd, d_mem_pos;  // mode 0: CSR of members (class, position)
+    bool all_spin = false, left_all_spin = false;  // every member of every (left-over) row is a spin read as +-1: the XOR kernel serves them
     DevBuf d_node_sd, d_node_pos;           // mode 1: observed nodes
     DevBuf d_sums;                          // int64 [total_rows] (mode 0) or [nodes*K] (mode 1)
     int64_t n_obs = 0;
@@ -237,6 +239,12 @@ void* thrml_ctx_stream(thrml_ctx* ctx) { return ctx ? static_cast<void*>(ctx->st
 // ---------------------------------------------------------------------------------------------------------
 // Program.
 // ---------------------------------------------------------------------------------------------------------
+static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
+    k_build_seq<<<static_cast<unsigned>((bp.n + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n), bp.d_seq_nbr.as<int32_t>(),
+                                                                                      bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>());
+    CU_TRY(cudaGetLastError());
+    return THRML_OK;
+}
 static int32_t rebuild_lut(thrml_program* p, BlockProg& bp) {
     const int64_t total = bp.n * LUT_SIZE;
     k_build_lut<<<static_cast<unsigned>((total + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
@@ -305,6 +313,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
             bp.host_tabs.push_back(d);
         }
         if (int32_t rc = upload(bp.d_tabs, bp.host_tabs.data(), bp.host_tabs.size() * sizeof(DevTable), ctx->stream)) return rc;
+        const bool single_spin_tails = lut_ok;  // every table: scalar weights, no tail or one spin tail
         if (lut_ok) {
             // compact neighbour list in table order, slot order; a node with more than 8 neighbour slots rules the kernel out
             std::vector<int32_t> nbr(static_cast<size_t>(bp.n) * LUT_BITS, -1);
@@ -328,6 +337,24 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 if (int32_t rc = bp.d_lut.alloc(static_cast<size_t>(bp.n) * LUT_SIZE * 4)) return rc;
                 if (int32_t rc = rebuild_lut(p.get(), bp)) return rc;
                 bp.kernel = 1;
+            }
+        }
+        if (single_spin_tails && bp.kernel == 0) {
+            // too many neighbour slots for a threshold table: the sequential-sum kernel takes up to SEQ_MAX active slots per node
+            int64_t most = 0;
+            for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                int64_t cnt = 0;
+                for (const SlotTable& t : tabs)
+                    for (int32_t j = 0; j < t.k; ++j) cnt += t.active[static_cast<size_t>(i2) * t.k + j] ? 1 : 0;
+                most = std::max(most, cnt);
+            }
+            if (most <= SEQ_MAX) {
+                if (int32_t rc = bp.d_seq_nbr.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
+                if (int32_t rc = bp.d_seq_w.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
+                if (int32_t rc = bp.d_seq_first.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+                if (int32_t rc = bp.d_seq_cnt.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+                if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
+                bp.kernel = 4;
             }
         }
         bp.base_kernel = bp.kernel;
@@ -422,8 +449,10 @@ int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t,
     bp.dense_src = -1;  // the cached dense matrix no longer matches the tables
     CU_TRY(cudaSetDevice(p->ctx->device));
     CU_TRY(cudaMemcpyAsync(bp.w_bufs[t]->p, w, bp.w_len[t] * 4, cudaMemcpyHostToDevice, p->ctx->stream));
-    if (bp.kernel == 1)
+    if (bp.base_kernel == 1)
         if (int32_t rc = rebuild_lut(p, bp)) return rc;
+    if (bp.base_kernel == 4)
+        if (int32_t rc = rebuild_seq(p, bp)) return rc;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
     return THRML_OK;
 }
@@ -837,6 +866,14 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
+    if (bp.base_kernel == 4 && !inj && !fields) {
+        SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
+                  static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key)};
+        const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
+        k_spin_seq<<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        CU_TRY(cudaGetLastError());
+        return THRML_OK;
+    }
     UpdateArgs a{};
     a.tabs = bp.d_tabs.as<DevTable>();
     a.n_tabs = bp.n_tabs;
@@ -909,9 +946,14 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_momen
     if (!acc) return THRML_OK;
     if (!fuse) return observe_async(acc, s);
     if (acc->n_left > 0) {
-        k_moments<<<static_cast<unsigned>((acc->n_left + 7) / 8), dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_sd.as<int32_t>(), acc->d_left_pos.as<int32_t>(),
-                                                                                     acc->n_left, s->cls[0].as<uint8_t>(), s->cls[1].as<uint8_t>(), s->ld, s->n_chains,
-                                                                                     acc->spin_transform, acc->d_sums.as<unsigned long long>(), acc->d_left_rows.as<int64_t>());
+        const unsigned grid = static_cast<unsigned>((acc->n_left + 7) / 8);
+        if (acc->left_all_spin)
+            k_moments_spin<<<grid, dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_pos.as<int32_t>(), acc->n_left, s->rows(p->sd_spin), s->ld, s->n_chains,
+                                                         acc->d_sums.as<unsigned long long>(), acc->d_left_rows.as<int64_t>());
+        else
+            k_moments<<<grid, dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_sd.as<int32_t>(), acc->d_left_pos.as<int32_t>(), acc->n_left, s->cls[0].as<uint8_t>(),
+                                                    s->cls[1].as<uint8_t>(), s->ld, s->n_chains, acc->spin_transform, acc->d_sums.as<unsigned long long>(),
+                                                    acc->d_left_rows.as<int64_t>());
         CU_TRY(cudaGetLastError());
     }
     acc->n_obs += s->n_chains;
@@ -1452,8 +1494,10 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
             if (int32_t rc = upload(m->d_left_pos, left_pos.data(), left_pos.size() * 4, st)) return rc;
             if (int32_t rc = upload(m->d_left_rows, left_rows.data(), left_rows.size() * 8, st)) return rc;
             CU_TRY(cudaStreamSynchronize(st));
+            m->left_all_spin = m->spin_transform && p->sd_spin >= 0 && std::all_of(left_sd.begin(), left_sd.end(), [&](int32_t c) { return c == p->sd_spin; });
         }
     }
+    m->all_spin = m->spin_transform && p->sd_spin >= 0 && std::all_of(sd.begin(), sd.end(), [&](int32_t c) { return c == p->sd_spin; });
     if (int32_t rc = upload(m->d_row_ptr, m->total_rows ? row_ptr : &zero, static_cast<size_t>(m->total_rows + 1) * 8, st)) return rc;
     if (int32_t rc = upload(m->d_mem_sd, sd.data(), sd.size() * 4, st)) return rc;
     if (int32_t rc = upload(m->d_mem_pos, pos.data(), pos.size() * 4, st)) return rc;
@@ -1513,9 +1557,13 @@ static int32_t observe_async(thrml_moments* m, thrml_state* s) {
     const uint8_t* c1 = s->cls[1].as<uint8_t>();
     if (m->mode == 0) {
         if (m->total_rows > 0) {
-            k_moments<<<static_cast<unsigned>((m->total_rows + 7) / 8), dim3(32, 8), 0, st>>>(m->d_row_ptr.as<int64_t>(), m->d_mem_sd.as<int32_t>(), m->d_mem_pos.as<int32_t>(),
-                                                                                               m->total_rows, c0, c1, s->ld, s->n_chains, m->spin_transform,
-                                                                                               m->d_sums.as<unsigned long long>(), nullptr);
+            const unsigned grid = static_cast<unsigned>((m->total_rows + 7) / 8);
+            if (m->all_spin)
+                k_moments_spin<<<grid, dim3(32, 8), 0, st>>>(m->d_row_ptr.as<int64_t>(), m->d_mem_pos.as<int32_t>(), m->total_rows, s->rows(s->prog->sd_spin), s->ld, s->n_chains,
+                                                             m->d_sums.as<unsigned long long>(), nullptr);
+            else
+                k_moments<<<grid, dim3(32, 8), 0, st>>>(m->d_row_ptr.as<int64_t>(), m->d_mem_sd.as<int32_t>(), m->d_mem_pos.as<int32_t>(), m->total_rows, c0, c1, s->ld,
+                                                        s->n_chains, m->spin_transform, m->d_sums.as<unsigned long long>(), nullptr);
             CU_TRY(cudaGetLastError());
         }
     } else {

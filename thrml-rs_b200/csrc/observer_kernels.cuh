@@ -97,6 +97,33 @@ __global__ void __launch_bounds__(256) k_moments(const int64_t* row_ptr, const i
     for (int off = 16; off > 0; off >>= 1) acc += __shfl_down_sync(0xffffffffu, acc, off);
     if (threadIdx.x == 0) atomicAdd(sums + (row_ids ? row_ids[row] : row), static_cast<unsigned long long>(acc));
 }
+// The same observer for rows whose members are all spins read as +-1 (the Ising moment spec, moment.rs:125-148): the
+// product of (2x - 1) over a row is -1 exactly when an odd number of members is 0, so one XOR per member and one
+// population count per word replace the per-chain products.  One warp per row, 16 chains per lane per pass.
+__global__ void __launch_bounds__(256) k_moments_spin(const int64_t* row_ptr, const int32_t* mem_pos, int64_t n_rows, const uint8_t* spin, int64_t ld, int64_t n_chains,
+                                                      unsigned long long* sums, const int64_t* row_ids) {
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (row >= n_rows) return;
+    const int64_t b = row_ptr[row], e = row_ptr[row + 1];
+    const int64_t n_chunks = (n_chains + 15) / 16;
+    int odd = 0;  // chains whose row has an odd number of zeros
+    for (int64_t ch = threadIdx.x; ch < n_chunks; ch += 32) {
+        uint4 z = make_uint4(0, 0, 0, 0);
+        for (int64_t q = b; q < e; ++q) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(spin + static_cast<int64_t>(mem_pos[q]) * ld) + ch);
+            z.x ^= ~v.x; z.y ^= ~v.y; z.z ^= ~v.z; z.w ^= ~v.w;
+        }
+        const uint32_t wd[4] = {z.x, z.y, z.z, z.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t left = n_chains - (16 * ch + 4 * k);  // chains beyond the last one do not count
+            const uint32_t vm = left >= 4 ? 0x01010101u : (left <= 0 ? 0u : (0x01010101u >> (8 * (4 - static_cast<int>(left)))));
+            odd += __popc(wd[k] & vm);
+        }
+    }
+    odd = __reduce_add_sync(0xffffffffu, odd);
+    if (threadIdx.x == 0) atomicAdd(sums + (row_ids ? row_ids[row] : row), static_cast<unsigned long long>(static_cast<long long>(n_chains) - 2ll * odd));
+}
 // Category counts per observed node.
 __global__ void __launch_bounds__(256) k_marginals(const int32_t* node_sd, const int32_t* node_pos, int64_t n_nodes, int32_t K, const uint8_t* cls0,
                                                    const uint8_t* cls1, int64_t ld, int64_t n_chains, unsigned long long* counts) {

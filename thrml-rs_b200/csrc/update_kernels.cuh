@@ -389,6 +389,126 @@ __global__ void __launch_bounds__(256, 2) k_spin_lut_persistent(const LutArgs* s
     }
 }
 
+// Sequential-sum spin update for blocks whose nodes have more single-spin-tail neighbour slots than a threshold table
+// covers (9 to SEQ_MAX entries per node, bias entries included).  Same data movement as k_spin_lut — one warp per
+// node, 16 chains per lane per pass, one 16-byte load per neighbour row — but the field is accumulated entry by
+// entry in the canonical order (per table from zero, tables left to right), exactly as k_spin_generic does, so the
+// states are the same bits.  The sigmoid is approximated first (2^x and reciprocal units); only a draw within 4e-6 of
+// it (four times the approximation's worst error) is redone with the deterministic sigmoid.
+constexpr int SEQ_MAX = 32;
+// Entry lists from the slot tables: per node the active slots in table order, slot order; nbr = -1 for an entry
+// without a tail (a bias); bit e of first[node] marks the first entry of a table.
+__global__ void __launch_bounds__(256) k_build_seq(const DevTable* tabs, int32_t n_tabs, int32_t n, int32_t* ent_nbr, float* ent_w, uint32_t* ent_first, int32_t* ent_cnt) {
+    const int64_t node = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (node >= n) return;
+    int e = 0;
+    uint32_t first = 0;
+    for (int t = 0; t < n_tabs; ++t) {
+        const DevTable T = tabs[t];
+        bool started = false;
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = node * T.k + j;
+            if (!T.active[flat] || e >= SEQ_MAX) continue;
+            if (!started) first |= 1u << e;
+            started = true;
+            ent_nbr[node * SEQ_MAX + e] = T.n_spin == 1 ? T.idx[0][flat] : -1;
+            ent_w[node * SEQ_MAX + e] = T.w[flat];
+            ++e;
+        }
+    }
+    ent_first[node] = first;
+    ent_cnt[node] = e;
+    for (; e < SEQ_MAX; ++e) {
+        ent_nbr[node * SEQ_MAX + e] = -1;
+        ent_w[node * SEQ_MAX + e] = 0.0f;
+    }
+}
+struct SeqArgs {
+    const int32_t* nbr;     // [n][SEQ_MAX]
+    const float* w;         // [n][SEQ_MAX]
+    const uint32_t* first;  // [n]
+    const int32_t* cnt;     // [n]
+    const uint8_t* spin;
+    uint8_t* dst;
+    int64_t ld;
+    int32_t n;
+    int32_t n_chunks;       // ld / 16
+    uint32_t chain_word0;
+    PhiloxRoundKeys rk;
+};
+__global__ void __launch_bounds__(256, 3) k_spin_seq(const __grid_constant__ SeqArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
+        const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
+        const float wv = __ldg(a.w + static_cast<int64_t>(node) * SEQ_MAX + lane);
+        const uint32_t first = __ldg(a.first + node);
+        const int cnt = __ldg(a.cnt + node);
+        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+        for (int base = 0; base < a.n_chunks; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
+            const int ch = base + lane;
+            const bool live = ch < a.n_chunks;
+            float gam[16], part[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) gam[i] = part[i] = 0.0f;
+            // four neighbour rows are always in flight: the row of entry e + 4 is requested when entry e is consumed
+            const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);  // no tail: the product over tails is +1
+            auto row_of = [&](int e) {
+                const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
+                return nbe >= 0 && live ? __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch) : ones;
+            };
+            uint4 ring[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) ring[k] = k < cnt ? row_of(k) : ones;
+            for (int e0 = 0; e0 < cnt; e0 += 4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int e = e0 + k;
+                    if (e >= cnt) break;  // uniform over the warp
+                    const uint4 v = ring[k];
+                    if (e + 4 < cnt) ring[k] = row_of(e + 4);
+                    const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
+                    if ((first >> e) & 1u) {  // a new table: close the previous one
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            gam[i] = __fadd_rn(gam[i], part[i]);
+                            part[i] = 0.0f;
+                        }
+                    }
+                    const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
+                            part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
+                        }
+                }
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+                uint32_t wd = 0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float gamma = __fadd_rn(gam[4 * q + c], part[4 * q + c]);
+                    float ex, p24;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));  // 2^24 p
+                    const float d = __uint2float_rn(rr[c] >> 8) - p24;
+                    bool one = d < 0.0f;
+                    if (fabsf(d) <= 67.2f) one = u24(rr[c]) <= det_sigmoid(__fmul_rn(gamma, 2.0f));  // spin_gibbs.rs:95-97
+                    wd |= one ? (1u << (8 * c)) : 0u;
+                }
+                o[q] = wd;
+            }
+            if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
 // Chain-sliced variant for programs small enough that four chains of every spin fit in one CTA's shared memory.
 // Chains never interact, so a CTA that owns chains 4q..4q+3 can run a whole schedule on its own: it loads one 32-bit
 // word per spin (4 chains), walks the list of block updates with a CTA barrier after each, and stores the words back.
