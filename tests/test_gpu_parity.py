@@ -302,12 +302,17 @@ def test_sequential_sum_kernel_matches_oracle(T, O, degree, chains):
     gs.run_blocks(17, 6)
     os_.run_blocks(17, 6)
     assert_states_equal(gs, os_, n_blocks_of(desc))
-    spec = moment_spec(desc, info)
+    # the observer rides in the update kernel for single spins and neighbour pairs; a triple, a repeated row and a
+    # non-neighbour pair go to the separate observer kernel
+    e0 = tuple(int(x) for x in info["edges"][0])
+    spec = moment_spec(desc, info) + [[(0, 5, 9), (2,), e0, (7, 7)]]
     gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    fused, other = gm.fused_info()
+    assert fused == info["n"] + len(info["edges"]) and other == 4
     gs.sample_with_observation(5, 1, 3, 2, moments=gm)
     os_.sample_with_observation(5, 1, 3, 2, moments=om)
     assert_states_equal(gs, os_, n_blocks_of(desc))
-    for t in range(2):
+    for t in range(3):
         assert np.array_equal(gm.read(t)[0], om.read(t)[0])
     # new couplings reach the entry lists
     J2 = (info["J"] * -0.7).astype(np.float32)

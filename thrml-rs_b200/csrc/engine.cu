@@ -349,6 +349,17 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 most = std::max(most, cnt);
             }
             if (most <= SEQ_MAX) {
+                bp.h_nbr.assign(static_cast<size_t>(bp.n) * SEQ_MAX, -1);  // the entry order of k_build_seq
+                for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                    int e = 0;
+                    for (const SlotTable& t : tabs)
+                        for (int32_t j = 0; j < t.k; ++j) {
+                            const size_t flat = static_cast<size_t>(i2) * t.k + j;
+                            if (!t.active[flat]) continue;
+                            if (t.n_spin == 1) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.idx[0][flat];
+                            ++e;
+                        }
+                }
                 if (int32_t rc = bp.d_seq_nbr.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
                 if (int32_t rc = bp.d_seq_w.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
                 if (int32_t rc = bp.d_seq_first.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
@@ -868,9 +879,16 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     }
     if (bp.base_kernel == 4 && !inj && !fields) {
         SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
-                  static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key)};
+                  static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
-        k_spin_seq<<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        if (acc && acc->fused[block]) {
+            a.m1_row = acc->fused[block]->m1.as<int32_t>();
+            a.m2_row = acc->fused[block]->m2.as<int32_t>();
+            a.sums = acc->d_sums.as<long long>();
+            k_spin_seq<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else {
+            k_spin_seq<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        }
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
@@ -1444,11 +1462,13 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
                 if (!p->blocks[bi].is_cat)
                     for (int64_t j = 0; j < p->blocks[bi].n; ++j) block_of_pos[p->blocks[bi].offset + j] = static_cast<int32_t>(bi);
         }
-        auto lut_block = [&](int32_t bi) { return bi >= 0 && bi < p->n_free && p->blocks[bi].kernel == 1; };
+        // blocks whose update kernel can carry the observer: threshold-table (8 slots per node) and sequential-sum (32)
+        auto lut_block = [&](int32_t bi) { return bi >= 0 && bi < p->n_free && (p->blocks[bi].kernel == 1 || p->blocks[bi].kernel == 4); };
+        auto slots_of = [&](int32_t bi) { return p->blocks[bi].kernel == 1 ? LUT_BITS : SEQ_MAX; };
         for (int32_t bi = 0; bi < p->n_free; ++bi)
             if (lut_block(bi)) {
                 m1[bi].assign(static_cast<size_t>(p->blocks[bi].n), -1);
-                m2[bi].assign(static_cast<size_t>(p->blocks[bi].n) * LUT_BITS, -1);
+                m2[bi].assign(static_cast<size_t>(p->blocks[bi].n) * slots_of(bi), -1);
             }
         std::vector<int64_t> left_ptr(1, 0), left_rows;
         std::vector<int32_t> left_sd, left_pos;
@@ -1467,9 +1487,10 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
                 if (p->blocks[ba].order < p->blocks[bb].order) { std::swap(pa, pb); std::swap(ba, bb); }  // (pa, ba) is updated later
                 if (p->blocks[ba].order > p->blocks[bb].order && lut_block(ba)) {
                     const int64_t i = pa - p->blocks[ba].offset;
-                    for (int j = 0; j < LUT_BITS; ++j)
-                        if (p->blocks[ba].h_nbr[i * LUT_BITS + j] == pb && m2[ba][i * LUT_BITS + j] < 0) {
-                            m2[ba][i * LUT_BITS + j] = static_cast<int32_t>(r);
+                    const int ns = slots_of(ba);
+                    for (int j = 0; j < ns; ++j)
+                        if (p->blocks[ba].h_nbr[i * ns + j] == pb && m2[ba][i * ns + j] < 0) {
+                            m2[ba][i * ns + j] = static_cast<int32_t>(r);
                             taken = true;
                             break;
                         }

@@ -435,7 +435,17 @@ struct SeqArgs {
     int32_t n_chunks;       // ld / 16
     uint32_t chain_word0;
     PhiloxRoundKeys rk;
+    // fused moment observer (ACC only): row of <s_i> per node, row of <s_i s_j> per (node, entry), -1 = not owned here
+    int64_t n_chains;
+    const int32_t* m1_row;
+    const int32_t* m2_row;
+    long long* sums;
 };
+// ACC: the moment observer fused in, as in k_spin_lut<true>: this node's <s_i> row and the pair rows it owns (it is the
+// endpoint updated later in the sweep) are accumulated without atomics.  The new spin is known only after the last
+// entry, so the owned neighbours' rows are read a second time (they were loaded moments before: cache hits) and
+// compared with the new bytes.
+template <bool ACC>
 __global__ void __launch_bounds__(256, 3) k_spin_seq(const __grid_constant__ SeqArgs a) {
     const int lane = threadIdx.x & 31;
     const int warps = (gridDim.x * blockDim.x) >> 5;
@@ -445,6 +455,15 @@ __global__ void __launch_bounds__(256, 3) k_spin_seq(const __grid_constant__ Seq
         const uint32_t first = __ldg(a.first + node);
         const int cnt = __ldg(a.cnt + node);
         uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+        int32_t my_row = -1, row1 = -1;
+        uint32_t own = 0;        // entries whose pair row this node owns
+        uint32_t mine = 0;       // lane e: disagreements with the neighbour of entry e
+        uint32_t ones_total = 0; // lane 0: chains in which the new spin is 1
+        if (ACC) {
+            my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * SEQ_MAX + lane);
+            row1 = __ldg(a.m1_row + node);
+            own = __ballot_sync(0xffffffffu, my_row >= 0);
+        }
         for (int base = 0; base < a.n_chunks; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
             const int ch = base + lane;
             const bool live = ch < a.n_chunks;
@@ -505,6 +524,31 @@ __global__ void __launch_bounds__(256, 3) k_spin_seq(const __grid_constant__ Seq
                 o[q] = wd;
             }
             if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+            if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
+                uint32_t vm[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) vm[q] = live ? (valid_mask(a.n_chains, ch, q) & 0x01010101u) : 0u;  // chains that exist
+                if (row1 >= 0) {
+                    const uint32_t c = __popc(o[0] & vm[0]) + __popc(o[1] & vm[1]) + __popc(o[2] & vm[2]) + __popc(o[3] & vm[3]);
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, c);
+                    if (lane == 0) ones_total += t;
+                }
+                for (uint32_t left = own; left; left &= left - 1) {  // uniform over the warp
+                    const int e = __ffs(left) - 1;
+                    const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
+                    uint32_t c = 0;
+                    if (live) {
+                        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch);
+                        c = __popc((v.x ^ o[0]) & vm[0]) + __popc((v.y ^ o[1]) & vm[1]) + __popc((v.z ^ o[2]) & vm[2]) + __popc((v.w ^ o[3]) & vm[3]);
+                    }
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, c);
+                    if (lane == e) mine += t;
+                }
+            }
+        }
+        if (ACC) {
+            if (my_row >= 0) a.sums[my_row] += a.n_chains - 2ll * mine;
+            if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
         }
     }
 }
