@@ -139,7 +139,9 @@ def run_reference(args, model):
     sample = f"each step = one sweep + moment observation of {threads} chains (one per host thread) on the full graph; {budget_steps} steps timed"
     return {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": budget_steps, "warmup": min(args.warmup, 2),
             "ms_per_step": 1e3 * dt / budget_steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(model, threads, args.gpus),
+            # the same workload description as the CUDA arm prints (4096 chains per GPU); what was actually timed is the
+            # bounded sample that `cpu_baseline.sample` describes
+            "config": workload_config(model, args.chains, args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
 
