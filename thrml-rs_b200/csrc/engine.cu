@@ -368,6 +368,17 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 bp.kernel = 4;
             }
         }
+        if (bp.is_cat && !tabs.empty()) {
+            // categorical block with few active slots per node: the register-resident kernel (kind 5) takes the in-kernel-noise updates
+            int64_t most = 0;
+            for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                int64_t cnt = 0;
+                for (const SlotTable& t : tabs)
+                    for (int32_t j = 0; j < t.k; ++j) cnt += t.active[static_cast<size_t>(i2) * t.k + j] ? 1 : 0;
+                most = std::max(most, cnt);
+            }
+            if (most <= CAT_SLOTS) bp.kernel = 5;
+        }
         bp.base_kernel = bp.kernel;
         // Dense bipartite candidate: a spin block whose neighbours all lie in one other spin block, densely enough
         // that the field is a GEMM against that block's +-1 image.
@@ -918,6 +929,7 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     if (bp.is_cat) {
         if (fields) k_cat_generic<2><<<grid, blk, 0, st>>>(a);
         else if (inj) k_cat_generic<1><<<grid, blk, 0, st>>>(a);
+        else if (bp.kernel == 5) k_cat_fast<<<grid, blk, 0, st>>>(a);
         else k_cat_generic<0><<<grid, blk, 0, st>>>(a);
     } else {
         if (fields) k_spin_generic<2><<<grid, blk, 0, st>>>(a);

@@ -182,6 +182,140 @@ __global__ void __launch_bounds__(256) k_cat_generic(UpdateArgs a) {
     *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
 }
 
+// Exact Gumbel-argmax of ONE chain of a categorical node, the generic way (softmax.rs:586-709, 60-97).  Out of line:
+// k_cat_fast calls it for the rare draws whose two best categories its fast logarithms cannot separate.
+__device__ __noinline__ uint32_t cat_exact_argmax(const UpdateArgs& a, int node, int quad, int c) {
+    const int K = a.K;
+    const int sh = 8 * c;
+    float best = 0.f;
+    uint32_t arg = 0;
+    U4 r{0, 0, 0, 0};
+    for (int cat = 0; cat < K; ++cat) {
+        float th = 0.f;
+        for (int t = 0; t < a.n_tabs; ++t) {
+            const DevTable& T = a.tabs[t];
+            const bool has_cat = T.n_tails > T.n_spin;
+            float sum = 0.f;
+            for (int j = 0; j < T.k; ++j) {
+                const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+                if (!T.active[flat]) continue;
+                float sp = 1.f;
+                for (int tl = 0; tl < T.n_spin; ++tl) sp = __fmul_rn(sp, ((ld_word(a.spin, T.idx[tl][flat], a.ld, quad) >> sh) & 1u) ? 1.0f : -1.0f);
+                float wv;
+                if (has_cat) {
+                    uint32_t x = (ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad) >> sh) & 0xffu;
+                    if (x >= static_cast<uint32_t>(K)) x = K - 1;
+                    wv = T.w[flat * T.wdim + cat * K + x];
+                } else {
+                    wv = T.w[flat * T.wdim + cat];
+                }
+                sum = __fadd_rn(sum, __fmul_rn(sp, wv));
+            }
+            th = __fadd_rn(th, sum);
+        }
+        if ((cat & 3) == 0)
+            r = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+        const float p = __fadd_rn(th, -det_log(-det_log(u23_open(pick(r, cat & 3)))));
+        if (cat == 0 || p > best) { best = p; arg = cat; }
+    }
+    return arg;
+}
+
+// Categorical update for blocks whose nodes have at most CAT_SLOTS active slots (in-kernel noise only; more would not fit the register file).  Same results
+// as k_cat_generic<0>, organised for speed: a warp is one node x 128 chains, so the slot structure is warp-uniform.
+//  * everything that does not depend on the category is gathered once per node and thread: per active slot the
+//    neighbour's category word (clamped), the sign word of its spin tails, the weight row and whether it opens a table;
+//  * the category loop then costs one table lookup and one add per slot and chain, in the canonical order
+//    (per table from zero, tables left to right);
+//  * the Gumbel noise is screened with the hardware logarithm (k_potts_update documents the bound: each score within
+//    2e-5 of the exact one); a leader less than 6e-5 ahead of the runner-up sends that chain to cat_exact_argmax.
+constexpr int CAT_SLOTS = 8;
+__global__ void __launch_bounds__(256, 2) k_cat_fast(const __grid_constant__ UpdateArgs a) {
+    const int quad = blockIdx.y * 32 + threadIdx.x;
+    const int node = blockIdx.x * 8 + threadIdx.y;
+    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const int K = a.K;
+    uint32_t xw[CAT_SLOTS], sg[CAT_SLOTS];   // neighbour categories (4 chains), sign bits (bit 7 of a byte: the spin-tail product is -1)
+    const float* wrow[CAT_SLOTS];            // weights of the slot: [K][K] with a categorical tail, [K] without
+    uint32_t opens = 0, tailed = 0;          // bit s: slot s opens a table / has a categorical tail
+    int S = 0;
+    for (int t = 0; t < a.n_tabs; ++t) {
+        const DevTable& T = a.tabs[t];
+        bool first = true;
+        for (int j = 0; j < T.k; ++j) {
+            const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+            if (!T.active[flat]) continue;
+            uint32_t neg = 0;
+            for (int tl = 0; tl < T.n_spin; ++tl) neg ^= ~ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+            uint32_t x = 0;
+            if (T.n_tails > T.n_spin) {
+                x = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+                x = __vminu4(x, static_cast<uint32_t>(K - 1) * 0x01010101u);  // per-byte clamp, as the generic kernel does
+            }
+#pragma unroll
+            for (int s = 0; s < CAT_SLOTS; ++s)
+                if (s == S) {  // static indices keep the lists in registers
+                    xw[s] = x;
+                    sg[s] = (neg & 0x01010101u) << 7;
+                    wrow[s] = T.w + flat * T.wdim;
+                }
+            if (first) opens |= 1u << S;
+            if (T.n_tails > T.n_spin) tailed |= 1u << S;
+            first = false;
+            ++S;
+        }
+    }
+    constexpr float MARGIN = 6e-5f;
+    float best[4], second[4];
+    uint32_t arg[4] = {0, 0, 0, 0};
+    U4 r[4];
+    for (int cat = 0; cat < K; ++cat) {
+        float th[4] = {0.f, 0.f, 0.f, 0.f}, sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int s = 0; s < CAT_SLOTS; ++s) {
+            if (s >= S) break;  // uniform over the warp
+            if (s > 0 && ((opens >> s) & 1u)) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) { th[c] = __fadd_rn(th[c], sum[c]); sum[c] = 0.f; }
+            }
+            if ((tailed >> s) & 1u) {
+                const float* wk = wrow[s] + cat * K;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t wb = __float_as_uint(__ldg(wk + ((xw[s] >> (8 * c)) & 0xffu)));
+                    sum[c] = __fadd_rn(sum[c], __uint_as_float(wb ^ (((sg[s] >> (8 * c)) & 0x80u) << 24)));  // sp * w = w with the sign flipped
+                }
+            } else {
+                const uint32_t wb = __float_as_uint(__ldg(wrow[s] + cat));
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sum[c] = __fadd_rn(sum[c], __uint_as_float(wb ^ (((sg[s] >> (8 * c)) & 0x80u) << 24)));
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            th[c] = __fadd_rn(th[c], sum[c]);
+            if ((cat & 3) == 0)
+                r[c] = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+            const float u = u23_open(pick(r[c], cat & 3));
+            const float w = 1.0f - u;
+            const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
+            const float l1 = w < 0.03125f ? series : -__logf(u);
+            const float p = th[c] - __logf(l1);
+            if (cat == 0) { best[c] = p; second[c] = -3.0e38f; }
+            else if (p > best[c]) { second[c] = best[c]; best[c] = p; arg[c] = cat; }
+            else if (p > second[c]) second[c] = p;
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (!(best[c] - second[c] > MARGIN)) arg[c] = cat_exact_argmax(a, node, quad, c);
+    uint32_t out = 0;
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+        if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
+    *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+}
+
 // Threshold tables for spin blocks whose nodes see at most 8 neighbour spins through single-spin-tail tables:
 // lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
 // (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
