@@ -22,7 +22,8 @@ def explicit_potts(nx, ny, nz, K, tables, unary, beta):
     return dict(kinds=np.full(n, K, np.int32), free=[(blocks[0], 0), (blocks[1], 1)], ops=ops), blocks
 
 
-@pytest.mark.parametrize("shape,K,chains", [((4, 4, 4), 3, 8), ((2, 4, 6), 10, 37), ((6, 2, 4), 5, 64), ((4, 2, 4), 7, 20)])
+@pytest.mark.parametrize("shape,K,chains", [((4, 4, 4), 3, 8), ((2, 4, 6), 10, 37), ((6, 2, 4), 5, 64), ((4, 2, 4), 7, 20),
+                                            ((4, 4, 4), 5, 8192)])  # the last: millions of draws, hundreds of near-ties sent to the exact path
 def test_potts_lattice_matches_explicit_program(T, O, shape, K, chains):
     from thrml_rs_b200 import potts
     nx, ny, nz = shape

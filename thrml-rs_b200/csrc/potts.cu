@@ -112,10 +112,12 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
             const float w = 1.0f - u;
             const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
             const float l1 = w < 0.03125f ? series : -__logf(u);
-            const float p = th - __logf(l1);
+            const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
             if (cat == 0) { best[c] = p; second[c] = -3.0e38f; }
-            else if (p > best[c]) { second[c] = best[c]; best[c] = p; arg[c] = cat; }
-            else if (p > second[c]) second[c] = p;
+            else {
+                second[c] = fmaxf(second[c], fminf(best[c], p));  // runner-up: the smaller of the old leader and the newcomer, if it beats the old runner-up
+                if (p > best[c]) { best[c] = p; arg[c] = cat; }
+            }
         }
     }
 #pragma unroll
