@@ -87,6 +87,7 @@ __global__ void __launch_bounds__(128) k_lattice_update(const __grid_constant__ 
             const uint32_t sr = s_spread[(R[c] >> (8 * g)) & 0xffu], sd = s_spread[(D[c] >> (8 * g)) & 0xffu];
             P[c] = su + 2u * sl + 4u * sr + 8u * sd;
         }
+        uint32_t byte[4] = {0, 0, 0, 0};  // the eight new spins of this group, per chain: constant bit positions inside the group
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const int k = 8 * g + j;
@@ -99,9 +100,11 @@ __global__ void __launch_bounds__(128) k_lattice_update(const __grid_constant__ 
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const uint32_t cfg = (P[c] >> (4 * j)) & 15u;
-                out[c] |= (rnd[c] <= T[cfg] ? 1u : 0u) << k;
+                byte[c] |= rnd[c] <= T[cfg] ? (1u << j) : 0u;
             }
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) out[c] |= byte[c] << (8 * g);
     }
     *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
 }
