@@ -17,7 +17,7 @@ def test_static_upload_matches_ordinary_upload_twice(T):
     desc, _ = M.ising_random_graph(T, 400, 8, 71)
     prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
     n_blocks = len(desc["free"])
-    for chains in (37, 256):  # ragged and aligned chain counts; the second round reuses the array after a larger first one
+    for chains in (37, 256):  # ragged and aligned chain counts; the second pass reuses the array after a larger first one
         ref, sta = T.ChainState(prog, chains), T.ChainState(prog, chains)
         for call in range(2):  # two calls in a row on the same handles
             init = M.random_states(desc, chains, 100 + call)
