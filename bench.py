@@ -270,7 +270,7 @@ def main():
     traffic = 8.92 * updates_per_step / n_blocks if all(k == 1 for k in kinds) and args.degree == DEGREE else None
     result["roofline"] = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": peak_src,
                           "algorithmic_bytes_per_launch": algo_bytes / n_blocks,
-                          "kernel": "k_spin_lut" if all(k == 1 for k in kinds) else ("k_spin_seq" if all(k == 4 for k in kinds) else "k_spin_generic"), "launches_per_sweep": n_blocks, "sweep_ms": sweep_ms,
+                          "kernel": "k_spin_lut" if all(k == 1 for k in kinds) else ("k_spin_seq" if all(k == 4 for k in kinds) else ("k_spin_hybrid" if all(k in (1, 4, 6) for k in kinds) else "k_spin_generic")), "launches_per_sweep": n_blocks, "sweep_ms": sweep_ms,
                           "bytes_per_update": algo_bytes / updates_per_step}
 
     if not args.no_e2e:

@@ -50,6 +50,23 @@ def ising_random_graph(T, n, degree, seed, w_sigma=None, bias_sigma=0.05, beta=1
     return desc, dict(n=n, edges=edges, b=b, J=Jv, blocks=blocks, beta=beta, colour=colour)
 
 
+def ising_sparse_random_graph(T, n, mean_degree, seed, w_sigma=0.3, bias_sigma=0.1, beta=1.0):
+    """Erdos-Renyi-like Ising model: n * mean_degree / 2 random distinct edges, so degrees spread around the mean
+    (a few nodes far above it); greedy-coloured blocks."""
+    rng = np.random.default_rng(seed)
+    m = n * mean_degree // 2
+    a, b = rng.integers(0, n, 2 * m), rng.integers(0, n, 2 * m)
+    lo, hi = np.minimum(a, b), np.maximum(a, b)
+    edges = np.unique(np.stack([lo[lo != hi], hi[lo != hi]], axis=1), axis=0)[:m]
+    colour, n_col = T.greedy_coloring_arrays(n, edges)
+    Jv = rng.normal(0, w_sigma, len(edges)).astype(np.float32)
+    bias = rng.normal(0, bias_sigma, n).astype(np.float32)
+    blocks = [np.flatnonzero(colour == c) for c in range(n_col)]
+    desc = dict(kinds=np.zeros(n, np.int32), free=[(blk, i) for i, blk in enumerate(blocks)], ops=[("add_ising", np.arange(n), bias, edges, Jv, beta)])
+    degree = np.bincount(edges.ravel(), minlength=n)
+    return desc, dict(n=n, edges=edges, b=bias, J=Jv, blocks=blocks, beta=beta, colour=colour, degree=degree)
+
+
 def potts_lattice(T, side, K, seed, sigma=0.3, bias_sigma=0.1):
     """2-D periodic Potts model: unary [n,K,1] factor plus one [E,K,K] pair factor per direction with a shared table."""
     rng = np.random.default_rng(seed)

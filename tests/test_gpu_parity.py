@@ -339,3 +339,38 @@ def test_categorical_screen_and_exact_fallback(T, O, case):
     gs.run_blocks(41, 10)
     os_.run_blocks(41, 10)
     assert_states_equal(gs, os_, n_blocks_of(desc))
+
+
+@pytest.mark.parametrize("chains", [33, 520])
+def test_mixed_degree_blocks_match_oracle(T, O, chains):
+    """A sparse random graph with mean degree 6: most nodes keep their threshold tables, the few with more than 8
+    neighbours take the sequential sum inside the same launch (kernel kind 6)."""
+    desc, info = M.ising_sparse_random_graph(T, 600, 6, 77)
+    assert 8 < info["degree"].max() <= 31 and (info["degree"] <= 8).mean() > 0.5
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 4)
+    kinds = [prog.block_kernel(b) for b in range(len(desc["free"]))]
+    assert 6 in kinds and set(kinds) <= {1, 4, 6}
+    gs.run_blocks(3, 5)
+    os_.run_blocks(3, 5)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    e0 = tuple(int(x) for x in info["edges"][0])
+    spec = moment_spec(desc, info) + [[(1, 4, 6), e0]]
+    gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    assert gm.fused_info() == (info["n"] + len(info["edges"]), 2)
+    gs.sample_with_observation(8, 2, 4, 2, moments=gm)
+    os_.sample_with_observation(8, 2, 4, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(3):
+        assert np.array_equal(gm.read(t)[0], om.read(t)[0])
+    J2 = (info["J"] * 1.7).astype(np.float32)
+    desc2 = dict(desc, ops=[("add_ising", np.arange(info["n"]), info["b"], info["edges"], J2, info["beta"])])
+    gb2, ob2 = M.build_both(T, O, desc2)
+    for blk in range(len(desc["free"])):
+        for t, tab in enumerate(gb2.tables(blk)):
+            prog.update_weights(blk, t, tab["w"].ravel())
+    os2 = O.State(ob2, chains)
+    for i in range(n_blocks_of(desc)):
+        os2.set_block(i, os_.get_block(i))
+    gs.run_blocks(6, 2)
+    os2.run_blocks(6, 2)
+    assert_states_equal(gs, os2, n_blocks_of(desc))

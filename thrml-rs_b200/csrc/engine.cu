@@ -48,7 +48,9 @@ struct BlockProg {
     DevBuf d_tabs;   // DevTable[n_tabs]
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
-    DevBuf d_seq_nbr, d_seq_w, d_seq_first, d_seq_cnt;  // entry lists of the sequential-sum kernel (kernel 4)
+    DevBuf d_seq_nbr, d_seq_w, d_seq_first, d_seq_cnt;  // entry lists of the sequential-sum kernel (kernels 4 and 6)
+    DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
+    int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
     int32_t max_deg = 0;         // largest number of neighbour slots any node of the block uses (threshold-table blocks)
     int32_t order = -1;          // position of the block's superblock in the sweep; -1 for clamped blocks
@@ -246,9 +248,11 @@ static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
     return THRML_OK;
 }
 static int32_t rebuild_lut(thrml_program* p, BlockProg& bp) {
-    const int64_t total = bp.n * LUT_SIZE;
-    k_build_lut<<<static_cast<unsigned>((total + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
-                                                                                         bp.d_lut.as<uint32_t>());
+    const int64_t rows = bp.base_kernel == 6 || bp.kernel == 6 ? bp.n_lut : bp.n;  // a mixed block keeps tables for some of its nodes only
+    const int64_t total = rows * LUT_SIZE;
+    if (total == 0) return THRML_OK;
+    k_build_lut<<<static_cast<unsigned>((total + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(rows),
+                                                                                         bp.d_lut.as<uint32_t>(), bp.d_lut_nodes.p ? bp.d_lut_nodes.as<int32_t>() : nullptr);
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }
@@ -366,6 +370,44 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 if (int32_t rc = bp.d_seq_cnt.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
                 if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
                 bp.kernel = 4;
+                // nodes with at most 8 neighbour slots can keep a threshold table: worth a mixed block when they are many
+                std::vector<int32_t> lut_row(static_cast<size_t>(bp.n), -1), lut_nodes, nbr8;
+                for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                    int deg = 0;
+                    for (int e = 0; e < SEQ_MAX; ++e) deg += bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] >= 0 ? 1 : 0;
+                    if (deg > LUT_BITS) continue;
+                    lut_row[i2] = static_cast<int32_t>(lut_nodes.size());
+                    lut_nodes.push_back(static_cast<int32_t>(i2));
+                    int at = 0;
+                    int32_t row8[LUT_BITS];
+                    for (int e = 0; e < LUT_BITS; ++e) row8[e] = -1;
+                    for (int e = 0; e < SEQ_MAX; ++e)
+                        if (bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] >= 0) row8[at++] = bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e];
+                    nbr8.insert(nbr8.end(), row8, row8 + LUT_BITS);
+                    // the observer indexes a table node's pair rows by neighbour slot: the first 8 entries of its row
+                    for (int e = 0; e < SEQ_MAX; ++e) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = e < LUT_BITS ? row8[e] : -1;
+                }
+                if (static_cast<int64_t>(lut_nodes.size()) * 4 >= bp.n) {
+                    bp.n_lut = static_cast<int64_t>(lut_nodes.size());
+                    if (int32_t rc = upload(bp.d_lut_row, lut_row.data(), lut_row.size() * 4, ctx->stream)) return rc;
+                    if (int32_t rc = upload(bp.d_lut_nodes, lut_nodes.data(), lut_nodes.size() * 4, ctx->stream)) return rc;
+                    if (int32_t rc = upload(bp.d_nbr, nbr8.data(), nbr8.size() * 4, ctx->stream)) return rc;
+                    if (int32_t rc = bp.d_lut.alloc(static_cast<size_t>(bp.n_lut) * LUT_SIZE * 4)) return rc;
+                    bp.kernel = 6;
+                    if (int32_t rc = rebuild_lut(p.get(), bp)) return rc;
+                } else {
+                    // keep the entry order for the observer
+                    for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                        int e = 0;
+                        for (const SlotTable& t : tabs)
+                            for (int32_t j = 0; j < t.k; ++j) {
+                                const size_t flat = static_cast<size_t>(i2) * t.k + j;
+                                if (!t.active[flat]) continue;
+                                bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.n_spin == 1 ? t.idx[0][flat] : -1;
+                                ++e;
+                            }
+                    }
+                }
             }
         }
         if (bp.is_cat && !tabs.empty()) {
@@ -473,8 +515,10 @@ int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t,
     CU_TRY(cudaMemcpyAsync(bp.w_bufs[t]->p, w, bp.w_len[t] * 4, cudaMemcpyHostToDevice, p->ctx->stream));
     if (bp.base_kernel == 1)
         if (int32_t rc = rebuild_lut(p, bp)) return rc;
-    if (bp.base_kernel == 4)
+    if (bp.base_kernel == 4 || bp.base_kernel == 6)
         if (int32_t rc = rebuild_seq(p, bp)) return rc;
+    if (bp.base_kernel == 6)
+        if (int32_t rc = rebuild_lut(p, bp)) return rc;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
     return THRML_OK;
 }
@@ -884,6 +928,25 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
             k_spin_lut<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         } else {
             k_spin_lut<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        }
+        CU_TRY(cudaGetLastError());
+        return THRML_OK;
+    }
+    if (bp.base_kernel == 6 && !inj && !fields) {
+        HybridArgs a{};
+        a.lut = LutArgs{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
+                        make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
+        a.seq = SeqArgs{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
+                        static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, a.lut.rk, s->n_chains, nullptr, nullptr, nullptr};
+        a.lut_row = bp.d_lut_row.as<int32_t>();
+        const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
+        if (acc && acc->fused[block]) {
+            a.lut.m1_row = a.seq.m1_row = acc->fused[block]->m1.as<int32_t>();
+            a.lut.m2_row = a.seq.m2_row = acc->fused[block]->m2.as<int32_t>();
+            a.lut.sums = a.seq.sums = acc->d_sums.as<long long>();
+            k_spin_hybrid<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else {
+            k_spin_hybrid<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         }
         CU_TRY(cudaGetLastError());
         return THRML_OK;
@@ -1475,7 +1538,9 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
                     for (int64_t j = 0; j < p->blocks[bi].n; ++j) block_of_pos[p->blocks[bi].offset + j] = static_cast<int32_t>(bi);
         }
         // blocks whose update kernel can carry the observer: threshold-table (8 slots per node) and sequential-sum (32)
-        auto lut_block = [&](int32_t bi) { return bi >= 0 && bi < p->n_free && (p->blocks[bi].kernel == 1 || p->blocks[bi].kernel == 4); };
+        auto lut_block = [&](int32_t bi) {
+            return bi >= 0 && bi < p->n_free && (p->blocks[bi].kernel == 1 || p->blocks[bi].kernel == 4 || p->blocks[bi].kernel == 6);
+        };
         auto slots_of = [&](int32_t bi) { return p->blocks[bi].kernel == 1 ? LUT_BITS : SEQ_MAX; };
         for (int32_t bi = 0; bi < p->n_free; ++bi)
             if (lut_block(bi)) {

@@ -320,11 +320,12 @@ __global__ void __launch_bounds__(256, 2) k_cat_fast(const __grid_constant__ Upd
 // lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
 // (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
 // k_spin_generic, and u <= p  <=>  (r >> 8) <= floor(p * 2^24)  <=>  r <= (floor(p * 2^24) << 8 | 0xff).
-__global__ void __launch_bounds__(256) k_build_lut(const DevTable* tabs, int32_t n_tabs, int32_t n, uint32_t* lut) {
+// `nodes` (nullable): the block's nodes that get a table, in table order; null = every node, in node order.
+__global__ void __launch_bounds__(256) k_build_lut(const DevTable* tabs, int32_t n_tabs, int32_t n, uint32_t* lut, const int32_t* nodes) {
     const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    const int64_t node = gid >> LUT_BITS;
     const uint32_t cfg = static_cast<uint32_t>(gid) & (LUT_SIZE - 1);
-    if (node >= n) return;
+    if ((gid >> LUT_BITS) >= n) return;
+    const int64_t node = nodes ? nodes[gid >> LUT_BITS] : (gid >> LUT_BITS);
     float gamma = 0.f;
     int bit = 0;
     for (int t = 0; t < n_tabs; ++t) {
@@ -411,96 +412,101 @@ constexpr int ACC_SEGMENT_PASSES = 15;  // 15 passes x 4 words = 60 <= 63
 // slot are counted in bit-sliced counters and reduced once per node.
 // COHERENT: neighbour rows may have been written earlier in the same launch (persistent multi-sweep kernel), so they are
 // read through L2 (ld.global.cg) instead of the read-only path.
+// One node of the threshold-table update by one warp.  `row` selects the node's neighbour list and table (equal to
+// `node` unless the block keeps tables only for some of its nodes), `m2_at` the first of its pair-row entries.
 template <bool ACC, bool COHERENT>
-__device__ __forceinline__ void lut_block_update(const LutArgs& a, uint32_t* my) {
+__device__ __forceinline__ void lut_node_update(const LutArgs& a, uint32_t* my, int node, int64_t row, int64_t m2_at) {
     const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
-        const uint4* src = reinterpret_cast<const uint4*>(a.lut + static_cast<int64_t>(node) * LUT_SIZE);
-        __syncwarp();
-        reinterpret_cast<uint4*>(my)[lane] = __ldg(src + lane);
-        reinterpret_cast<uint4*>(my)[lane + 32] = __ldg(src + lane + 32);
-        int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
-        int32_t my_row = -1;
-        uint32_t own = 0;
-        if (ACC) {
-            if (lane < LUT_BITS) my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * LUT_BITS + lane);
-            else if (lane == LUT_BITS) my_row = __ldg(a.m1_row + node);
-            own = __ballot_sync(0xffffffffu, my_row >= 0);
-        }
-        __syncwarp();
-        int32_t nbj[LUT_BITS];
+    const uint4* src = reinterpret_cast<const uint4*>(a.lut + row * LUT_SIZE);
+    __syncwarp();
+    reinterpret_cast<uint4*>(my)[lane] = __ldg(src + lane);
+    reinterpret_cast<uint4*>(my)[lane + 32] = __ldg(src + lane + 32);
+    int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + row * LUT_BITS + lane) : -1;
+    int32_t my_row = -1;
+    uint32_t own = 0;
+    if (ACC) {
+        if (lane < LUT_BITS) my_row = __ldg(a.m2_row + m2_at + lane);
+        else if (lane == LUT_BITS) my_row = __ldg(a.m1_row + node);
+        own = __ballot_sync(0xffffffffu, my_row >= 0);
+    }
+    __syncwarp();
+    int32_t nbj[LUT_BITS];
 #pragma unroll
-        for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
-        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
-        uint32_t mine = 0;  // lane j < 8: disagreements with slot j; lane 8: number of ones
-        for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {
-            const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
-            SliceCounter cnt;
-            uint32_t ones = 0;
-            for (int ch = seg + lane; ch < seg_end; ch += 32) {
-                uint4 v[LUT_BITS];
+    for (int j = 0; j < LUT_BITS; ++j) nbj[j] = __shfl_sync(0xffffffffu, nb, j);
+    uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+    uint32_t mine = 0;  // lane j < 8: disagreements with slot j; lane 8: number of ones
+    for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {
+        const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
+        SliceCounter cnt;
+        uint32_t ones = 0;
+        for (int ch = seg + lane; ch < seg_end; ch += 32) {
+            uint4 v[LUT_BITS];
 #pragma unroll
-                for (int j = 0; j < LUT_BITS; ++j) {
-                    v[j] = make_uint4(0, 0, 0, 0);
-                    if (nbj[j] >= 0) {
-                        const uint4* src_row = reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch;
-                        v[j] = COHERENT ? __ldcg(src_row) : __ldg(src_row);
-                    }
-                }
-                uint32_t cfg[4] = {0, 0, 0, 0};
-#pragma unroll
-                for (int j = 0; j < LUT_BITS; ++j) {
-                    cfg[0] += v[j].x << j;
-                    cfg[1] += v[j].y << j;
-                    cfg[2] += v[j].z << j;
-                    cfg[3] += v[j].w << j;
-                }
-                uint32_t o[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
-                    uint32_t w = 0;
-                    w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
-                    w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
-                    w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
-                    w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
-                    o[q] = w;
-                }
-                reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
-                if (ACC && own) {
-                    uint32_t d[4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) d[q] = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
-                    if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {        // ragged last chunk: drop chains that do not exist
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const uint32_t vm = valid_mask(a.n_chains, ch, q);
-                            d[q] &= vm;
-                            o[q] &= vm;
-                        }
-                    }
-                    cnt.add4(d[0], d[1], d[2], d[3]);
-                    ones += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
+            for (int j = 0; j < LUT_BITS; ++j) {
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (nbj[j] >= 0) {
+                    const uint4* src_row = reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj[j]) * a.ld) + ch;
+                    v[j] = COHERENT ? __ldcg(src_row) : __ldg(src_row);
                 }
             }
+            uint32_t cfg[4] = {0, 0, 0, 0};
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j) {
+                cfg[0] += v[j].x << j;
+                cfg[1] += v[j].y << j;
+                cfg[2] += v[j].z << j;
+                cfg[3] += v[j].w << j;
+            }
+            uint32_t o[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                uint32_t w = 0;
+                w |= (r.x <= my[cfg[q] & 0xffu]) ? 1u : 0u;
+                w |= (r.y <= my[(cfg[q] >> 8) & 0xffu]) ? 0x100u : 0u;
+                w |= (r.z <= my[(cfg[q] >> 16) & 0xffu]) ? 0x10000u : 0u;
+                w |= (r.w <= my[cfg[q] >> 24]) ? 0x1000000u : 0u;
+                o[q] = w;
+            }
+            reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
             if (ACC && own) {
-                ones = __reduce_add_sync(0xffffffffu, ones);
-                if (lane == LUT_BITS) mine += ones;
+                uint32_t d[4];
 #pragma unroll
-                for (int j = 0; j < LUT_BITS; ++j)
-                    if ((own >> j) & 1u) {
-                        const uint32_t t = __reduce_add_sync(0xffffffffu, cnt.total(j));
-                        if (lane == j) mine += t;
+                for (int q = 0; q < 4; ++q) d[q] = cfg[q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+                if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {        // ragged last chunk: drop chains that do not exist
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const uint32_t vm = valid_mask(a.n_chains, ch, q);
+                        d[q] &= vm;
+                        o[q] &= vm;
                     }
+                }
+                cnt.add4(d[0], d[1], d[2], d[3]);
+                ones += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
             }
         }
-        if (ACC && my_row >= 0) {
-            const long long val = lane == LUT_BITS ? 2ll * mine - a.n_chains : a.n_chains - 2ll * mine;
-            if (COHERENT) __stcg(a.sums + my_row, __ldcg(a.sums + my_row) + val);
-            else a.sums[my_row] += val;
+        if (ACC && own) {
+            ones = __reduce_add_sync(0xffffffffu, ones);
+            if (lane == LUT_BITS) mine += ones;
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j)
+                if ((own >> j) & 1u) {
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, cnt.total(j));
+                    if (lane == j) mine += t;
+                }
         }
     }
+    if (ACC && my_row >= 0) {
+        const long long val = lane == LUT_BITS ? 2ll * mine - a.n_chains : a.n_chains - 2ll * mine;
+        if (COHERENT) __stcg(a.sums + my_row, __ldcg(a.sums + my_row) + val);
+        else a.sums[my_row] += val;
+    }
+}
+template <bool ACC, bool COHERENT>
+__device__ __forceinline__ void lut_block_update(const LutArgs& a, uint32_t* my) {
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps)
+        lut_node_update<ACC, COHERENT>(a, my, node, node, static_cast<int64_t>(node) * LUT_BITS);
 }
 
 template <bool ACC>
@@ -584,110 +590,133 @@ __device__ __noinline__ bool exact_spin_draw(float gamma, uint32_t r) { return u
 // compared with the new bytes.
 // Four CTAs per SM (64 registers, a few spilled words): measured faster than three without spills, and than 8 chains per lane.
 template <bool ACC>
-__global__ void __launch_bounds__(256, 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
+__device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
     const int lane = threadIdx.x & 31;
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) {
-        const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
-        const float wv = __ldg(a.w + static_cast<int64_t>(node) * SEQ_MAX + lane);
-        const uint32_t first = __ldg(a.first + node);
-        const int cnt = __ldg(a.cnt + node);
-        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
-        int32_t my_row = -1, row1 = -1;
-        uint32_t own = 0;        // entries whose pair row this node owns
-        uint32_t mine = 0;       // lane e: disagreements with the neighbour of entry e
-        uint32_t ones_total = 0; // lane 0: chains in which the new spin is 1
-        if (ACC) {
-            my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * SEQ_MAX + lane);
-            row1 = __ldg(a.m1_row + node);
-            own = __ballot_sync(0xffffffffu, my_row >= 0);
-        }
-        for (int base = 0; base < a.n_chunks; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
-            const int ch = base + lane;
-            const bool live = ch < a.n_chunks;
-            float gam[16], part[16];
+    const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
+    const float wv = __ldg(a.w + static_cast<int64_t>(node) * SEQ_MAX + lane);
+    const uint32_t first = __ldg(a.first + node);
+    const int cnt = __ldg(a.cnt + node);
+    uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+    int32_t my_row = -1, row1 = -1;
+    uint32_t own = 0;        // entries whose pair row this node owns
+    uint32_t mine = 0;       // lane e: disagreements with the neighbour of entry e
+    uint32_t ones_total = 0; // lane 0: chains in which the new spin is 1
+    if (ACC) {
+        my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * SEQ_MAX + lane);
+        row1 = __ldg(a.m1_row + node);
+        own = __ballot_sync(0xffffffffu, my_row >= 0);
+    }
+    for (int base = 0; base < a.n_chunks; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
+        const int ch = base + lane;
+        const bool live = ch < a.n_chunks;
+        float gam[16], part[16];
 #pragma unroll
-            for (int i = 0; i < 16; ++i) gam[i] = part[i] = 0.0f;
-            // four neighbour rows are always in flight: the row of entry e + 4 is requested when entry e is consumed
-            const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);  // no tail: the product over tails is +1
-            auto row_of = [&](int e) {
+        for (int i = 0; i < 16; ++i) gam[i] = part[i] = 0.0f;
+        // four neighbour rows are always in flight: the row of entry e + 4 is requested when entry e is consumed
+        const uint4 ones = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);  // no tail: the product over tails is +1
+        auto row_of = [&](int e) {
+            const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
+            return nbe >= 0 && live ? __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch) : ones;
+        };
+        uint4 ring[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) ring[k] = k < cnt ? row_of(k) : ones;
+        for (int e0 = 0; e0 < cnt; e0 += 4) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int e = e0 + k;
+                if (e >= cnt) break;  // uniform over the warp
+                const uint4 v = ring[k];
+                if (e + 4 < cnt) ring[k] = row_of(e + 4);
+                const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
+                if ((first >> e) & 1u) {  // a new table: close the previous one
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        gam[i] = __fadd_rn(gam[i], part[i]);
+                        part[i] = 0.0f;
+                    }
+                }
+                const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
+                        part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
+                    }
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+            const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+            uint32_t wd = 0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float gamma = __fadd_rn(gam[4 * q + c], part[4 * q + c]);
+                float ex, p24;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
+                asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));  // 2^24 p
+                const float d = __uint2float_rn(rr[c] >> 8) - p24;
+                bool one = d < 0.0f;
+                if (fabsf(d) <= 67.2f) one = exact_spin_draw(gamma, rr[c]);
+                wd |= one ? (1u << (8 * c)) : 0u;
+            }
+            o[q] = wd;
+        }
+        if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
+            uint32_t vm[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) vm[q] = live ? (valid_mask(a.n_chains, ch, q) & 0x01010101u) : 0u;  // chains that exist
+            if (row1 >= 0) {
+                const uint32_t c = __popc(o[0] & vm[0]) + __popc(o[1] & vm[1]) + __popc(o[2] & vm[2]) + __popc(o[3] & vm[3]);
+                const uint32_t t = __reduce_add_sync(0xffffffffu, c);
+                if (lane == 0) ones_total += t;
+            }
+            for (uint32_t left = own; left; left &= left - 1) {  // uniform over the warp
+                const int e = __ffs(left) - 1;
                 const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
-                return nbe >= 0 && live ? __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch) : ones;
-            };
-            uint4 ring[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ring[k] = k < cnt ? row_of(k) : ones;
-            for (int e0 = 0; e0 < cnt; e0 += 4) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    const int e = e0 + k;
-                    if (e >= cnt) break;  // uniform over the warp
-                    const uint4 v = ring[k];
-                    if (e + 4 < cnt) ring[k] = row_of(e + 4);
-                    const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
-                    if ((first >> e) & 1u) {  // a new table: close the previous one
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            gam[i] = __fadd_rn(gam[i], part[i]);
-                            part[i] = 0.0f;
-                        }
-                    }
-                    const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
-                            part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
-                        }
+                uint32_t c = 0;
+                if (live) {
+                    const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch);
+                    c = __popc((v.x ^ o[0]) & vm[0]) + __popc((v.y ^ o[1]) & vm[1]) + __popc((v.z ^ o[2]) & vm[2]) + __popc((v.w ^ o[3]) & vm[3]);
                 }
-            }
-            uint32_t o[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
-                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-                uint32_t wd = 0;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float gamma = __fadd_rn(gam[4 * q + c], part[4 * q + c]);
-                    float ex, p24;
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
-                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));  // 2^24 p
-                    const float d = __uint2float_rn(rr[c] >> 8) - p24;
-                    bool one = d < 0.0f;
-                    if (fabsf(d) <= 67.2f) one = exact_spin_draw(gamma, rr[c]);
-                    wd |= one ? (1u << (8 * c)) : 0u;
-                }
-                o[q] = wd;
-            }
-            if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
-            if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
-                uint32_t vm[4];
-#pragma unroll
-                for (int q = 0; q < 4; ++q) vm[q] = live ? (valid_mask(a.n_chains, ch, q) & 0x01010101u) : 0u;  // chains that exist
-                if (row1 >= 0) {
-                    const uint32_t c = __popc(o[0] & vm[0]) + __popc(o[1] & vm[1]) + __popc(o[2] & vm[2]) + __popc(o[3] & vm[3]);
-                    const uint32_t t = __reduce_add_sync(0xffffffffu, c);
-                    if (lane == 0) ones_total += t;
-                }
-                for (uint32_t left = own; left; left &= left - 1) {  // uniform over the warp
-                    const int e = __ffs(left) - 1;
-                    const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
-                    uint32_t c = 0;
-                    if (live) {
-                        const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch);
-                        c = __popc((v.x ^ o[0]) & vm[0]) + __popc((v.y ^ o[1]) & vm[1]) + __popc((v.z ^ o[2]) & vm[2]) + __popc((v.w ^ o[3]) & vm[3]);
-                    }
-                    const uint32_t t = __reduce_add_sync(0xffffffffu, c);
-                    if (lane == e) mine += t;
-                }
+                const uint32_t t = __reduce_add_sync(0xffffffffu, c);
+                if (lane == e) mine += t;
             }
         }
-        if (ACC) {
-            if (my_row >= 0) a.sums[my_row] += a.n_chains - 2ll * mine;
-            if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
-        }
+    }
+    if (ACC) {
+        if (my_row >= 0) a.sums[my_row] += a.n_chains - 2ll * mine;
+        if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
+    }
+}
+template <bool ACC>
+__global__ void __launch_bounds__(256, 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) seq_node_update<ACC>(a, node);
+}
+
+// Blocks that mix the two kinds of node: those with at most 8 neighbour slots take the threshold-table update, the
+// others the sequential sum, warp by warp (a sparse random graph has a few high-degree nodes in every block; they
+// should not cost the other nodes their tables).  lut_row[node] >= 0 is the node's row in the block's compact
+// neighbour-list and table arrays, -1 marks a sequential-sum node.  The observer's pair-row map has SEQ_MAX entries
+// per node for both kinds (a table node uses the first 8, indexed by neighbour slot).
+struct HybridArgs {
+    LutArgs lut;
+    SeqArgs seq;
+    const int32_t* lut_row;
+};
+template <bool ACC>
+__global__ void __launch_bounds__(256, 4) k_spin_hybrid(const __grid_constant__ HybridArgs a) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    const int warps = (gridDim.x * blockDim.x) >> 5;
+    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.seq.n; node += warps) {
+        const int32_t row = __ldg(a.lut_row + node);
+        if (row >= 0) lut_node_update<ACC, false>(a.lut, s_lut[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
+        else seq_node_update<ACC>(a.seq, node);
     }
 }
 
