@@ -49,6 +49,7 @@ struct BlockProg {
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
     DevBuf d_seq_nbr, d_seq_w, d_seq_first, d_seq_cnt;  // entry lists of the sequential-sum kernel (kernels 4 and 6)
+    DevBuf d_seq_order, d_seq_counter;                   // kernels 4 and 6: nodes by decreasing entry count; the launch's work counter
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
@@ -369,6 +370,17 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 if (int32_t rc = bp.d_seq_first.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
                 if (int32_t rc = bp.d_seq_cnt.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
                 if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
+                {
+                    std::vector<int32_t> cnt_of(static_cast<size_t>(bp.n), 0), order(static_cast<size_t>(bp.n));
+                    for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                        for (const SlotTable& t : tabs)
+                            for (int32_t j = 0; j < t.k; ++j) cnt_of[i2] += t.active[static_cast<size_t>(i2) * t.k + j] ? 1 : 0;
+                        order[i2] = static_cast<int32_t>(i2);
+                    }
+                    std::stable_sort(order.begin(), order.end(), [&](int32_t x, int32_t y) { return cnt_of[x] > cnt_of[y]; });
+                    if (int32_t rc = upload(bp.d_seq_order, order.data(), order.size() * 4, ctx->stream)) return rc;
+                    if (int32_t rc = bp.d_seq_counter.alloc(4)) return rc;
+                }
                 bp.kernel = 4;
                 // nodes with at most 8 neighbour slots can keep a threshold table: worth a mixed block when they are many
                 std::vector<int32_t> lut_row(static_cast<size_t>(bp.n), -1), lut_nodes, nbr8;
@@ -937,8 +949,11 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         a.lut = LutArgs{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
                         make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
         a.seq = SeqArgs{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
-                        static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, a.lut.rk, s->n_chains, nullptr, nullptr, nullptr};
+                        static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, a.lut.rk, s->n_chains, nullptr, nullptr, nullptr, nullptr, nullptr};
         a.lut_row = bp.d_lut_row.as<int32_t>();
+        a.seq.order = bp.d_seq_order.as<int32_t>();
+        a.seq.counter = bp.d_seq_counter.as<int32_t>();
+        CU_TRY(cudaMemsetAsync(a.seq.counter, 0, 4, st));
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
             a.lut.m1_row = a.seq.m1_row = acc->fused[block]->m1.as<int32_t>();
@@ -953,7 +968,9 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     }
     if (bp.base_kernel == 4 && !inj && !fields) {
         SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
-                  static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
+                  static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr,
+                  bp.d_seq_order.as<int32_t>(), bp.d_seq_counter.as<int32_t>()};
+        CU_TRY(cudaMemsetAsync(a.counter, 0, 4, st));
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
             a.m1_row = acc->fused[block]->m1.as<int32_t>();

@@ -580,7 +580,18 @@ struct SeqArgs {
     const int32_t* m1_row;
     const int32_t* m2_row;
     long long* sums;
+    // Work distribution: warps take nodes from a shared counter (zeroed before the launch), in the order of `order`
+    // (most entries first).  Node costs differ by the entry count, so a fixed assignment leaves a long tail.
+    const int32_t* order;   // [n] permutation of the block's nodes
+    int32_t* counter;
 };
+// Next node for this warp, or -1 when the block is done.
+__device__ __forceinline__ int take_node(const SeqArgs& a) {
+    int i = 0;
+    if ((threadIdx.x & 31) == 0) i = atomicAdd(a.counter, 1);
+    i = __shfl_sync(0xffffffffu, i, 0);
+    return i < a.n ? __ldg(a.order + i) : -1;
+}
 // The exact draw rule u <= sigmoid(2 gamma) (spin_gibbs.rs:95-97), out of line: k_spin_seq needs it for about one draw in 10^5.
 __device__ __noinline__ bool exact_spin_draw(float gamma, uint32_t r) { return u24(r) <= det_sigmoid(__fmul_rn(gamma, 2.0f)); }
 
@@ -695,8 +706,7 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
 }
 template <bool ACC>
 __global__ void __launch_bounds__(256, 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.n; node += warps) seq_node_update<ACC>(a, node);
+    for (int node = take_node(a); node >= 0; node = take_node(a)) seq_node_update<ACC>(a, node);
 }
 
 // Blocks that mix the two kinds of node: those with at most 8 neighbour slots take the threshold-table update, the
@@ -712,8 +722,7 @@ struct HybridArgs {
 template <bool ACC>
 __global__ void __launch_bounds__(256, 4) k_spin_hybrid(const __grid_constant__ HybridArgs a) {
     __shared__ uint32_t s_lut[8][LUT_SIZE];
-    const int warps = (gridDim.x * blockDim.x) >> 5;
-    for (int node = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; node < a.seq.n; node += warps) {
+    for (int node = take_node(a.seq); node >= 0; node = take_node(a.seq)) {
         const int32_t row = __ldg(a.lut_row + node);
         if (row >= 0) lut_node_update<ACC, false>(a.lut, s_lut[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
         else seq_node_update<ACC>(a.seq, node);

@@ -16,10 +16,22 @@ def random_regular_edges(n_nodes, degree, seed):
     return np.stack([code // n_nodes, code % n_nodes], axis=1)
 
 
-def sparse_ising(n_nodes=1 << 20, degree=8, seed=0x5EED0002, bias_sigma=0.05, beta=1.0):
-    """Sparse random `degree`-regular Ising model: couplings N(0, 1/degree), biases N(0, bias_sigma^2), blocks from
-    greedy colouring in node order (ascending node index inside each colour)."""
-    edges = random_regular_edges(n_nodes, degree, seed)
+def random_graph_edges(n_nodes, mean_degree, seed):
+    """Erdos-Renyi-like graph: n * mean_degree / 2 endpoint pairs drawn uniformly, self-loops and duplicates erased, so
+    degrees are Poisson-distributed around the mean.  Edges come back sorted by (min, max)."""
+    rng = np.random.default_rng(seed)
+    m = n_nodes * mean_degree // 2
+    a, b = rng.integers(0, n_nodes, m), rng.integers(0, n_nodes, m)
+    lo, hi = np.minimum(a, b), np.maximum(a, b)
+    code = np.unique(lo[lo != hi] * n_nodes + hi[lo != hi])
+    return np.stack([code // n_nodes, code % n_nodes], axis=1)
+
+
+def sparse_ising(n_nodes=1 << 20, degree=8, seed=0x5EED0002, bias_sigma=0.05, beta=1.0, regular=True):
+    """Sparse random Ising model, `degree`-regular (at most `degree` neighbours per node) or, with regular=False, a
+    random graph with that mean degree: couplings N(0, 1/degree), biases N(0, bias_sigma^2), blocks from greedy colouring
+    in node order (ascending node index inside each colour)."""
+    edges = random_regular_edges(n_nodes, degree, seed) if regular else random_graph_edges(n_nodes, degree, seed)
     rng = np.random.default_rng(seed + 1)
     J = rng.normal(0.0, np.sqrt(1.0 / degree), len(edges)).astype(np.float32)
     b = rng.normal(0.0, bias_sigma, n_nodes).astype(np.float32)
