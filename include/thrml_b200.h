@@ -167,9 +167,9 @@ int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t,
 int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding, int32_t* n_blocks_out);
 /* Which kernel a free block runs: 0 generic gather kernel, 1 threshold-table kernel (spin blocks whose
  * nodes have at most 8 single-spin-tail slots), 2 categorical kernel, 3 dense tensor-core kernel, 4 sequential-sum
- * kernel (spin blocks with single-spin-tail slots, 9 to 32 active slots per node), 5 categorical kernel for nodes with
+ * kernel (spin blocks with single-spin-tail slots, more than 8 active slots on some node), 5 categorical kernel for nodes with
  * at most 8 active slots (slot data held in registers, Gumbel noise screened with fast logarithms), 6 a spin block that
- * mixes kinds 1 and 4 node by node (at least a quarter of its nodes have at most 8 neighbour slots, the rest up to 32). */
+ * mixes kinds 1 and 4 node by node (at least a quarter of its nodes have at most 8 neighbour slots). */
 int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out);
 
 /* n_chains chains held on this device; chain_offset = global id of local chain 0 (the in-kernel random

@@ -374,3 +374,34 @@ def test_mixed_degree_blocks_match_oracle(T, O, chains):
     gs.run_blocks(6, 2)
     os2.run_blocks(6, 2)
     assert_states_equal(gs, os2, n_blocks_of(desc))
+
+
+def test_hub_nodes_continue_in_overflow_rows(T, O):
+    """A sparse graph with two hubs (200 and 70 neighbours): their entry lists span several rows of 32; everything else as usual."""
+    n = 400
+    rng = np.random.default_rng(9)
+    a, b = rng.integers(2, n, 900), rng.integers(2, n, 900)
+    pairs = [(min(x, y), max(x, y)) for x, y in zip(a, b) if x != y]
+    pairs += [(0, j) for j in range(2, 202)] + [(1, j) for j in range(202, 272)]
+    edges = np.unique(np.array(pairs, dtype=np.int64), axis=0)
+    colour, n_col = T.greedy_coloring_arrays(n, edges)
+    blocks = [np.flatnonzero(colour == c) for c in range(n_col)]
+    bias = rng.normal(0, 0.1, n).astype(np.float32)
+    Jv = rng.normal(0, 0.15, len(edges)).astype(np.float32)
+    desc = dict(kinds=np.zeros(n, np.int32), free=[(blk, i) for i, blk in enumerate(blocks)], ops=[("add_ising", np.arange(n), bias, edges, Jv, 1.0)])
+    info = dict(n=n, edges=edges)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 150, 4)
+    kinds = [prog.block_kernel(b) for b in range(n_col)]
+    assert set(kinds) <= {1, 4, 6} and kinds[int(colour[0])] in (4, 6)
+    gs.run_blocks(2, 6)
+    os_.run_blocks(2, 6)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    spec = moment_spec(desc, info)
+    gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    fused, other = gm.fused_info()
+    assert fused + other == n + len(edges) and 0 < other <= 2 + 270  # the hubs' own rows and the pairs they would own
+    gs.sample_with_observation(4, 1, 3, 2, moments=gm)
+    os_.sample_with_observation(4, 1, 3, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(2):
+        assert np.array_equal(gm.read(t)[0], om.read(t)[0])

@@ -49,6 +49,9 @@ struct BlockProg {
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
     DevBuf d_seq_nbr, d_seq_w, d_seq_first, d_seq_cnt;  // entry lists of the sequential-sum kernel (kernels 4 and 6)
+    DevBuf d_seq_overflow, d_seq_n_rows;                 // kernels 4 and 6: overflow rows of nodes with more than 32 entries
+    int64_t seq_rows = 0;
+    std::vector<char> h_hub;                             // kernels 4 and 6: nodes with overflow rows (not served by the fused observer)
     DevBuf d_seq_order, d_seq_counter;                   // kernels 4 and 6: nodes by decreasing entry count; the launch's work counter
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
@@ -243,7 +246,8 @@ void* thrml_ctx_stream(thrml_ctx* ctx) { return ctx ? static_cast<void*>(ctx->st
 // Program.
 // ---------------------------------------------------------------------------------------------------------
 static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
-    k_build_seq<<<static_cast<unsigned>((bp.n + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n), bp.d_seq_nbr.as<int32_t>(),
+    k_build_seq<<<static_cast<unsigned>((bp.n + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
+                                                                                      bp.d_seq_overflow.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(),
                                                                                       bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>());
     CU_TRY(cudaGetLastError());
     return THRML_OK;
@@ -345,30 +349,42 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
             }
         }
         if (single_spin_tails && bp.kernel == 0) {
-            // too many neighbour slots for a threshold table: the sequential-sum kernel takes up to SEQ_MAX active slots per node
-            int64_t most = 0;
+            // too many neighbour slots for a threshold table: the sequential-sum kernel, SEQ_MAX entries per row; a node with
+            // more entries continues in overflow rows (and leaves the fused observer to the separate kernel)
+            std::vector<int32_t> overflow(static_cast<size_t>(bp.n), -1), n_rows(static_cast<size_t>(bp.n), 1);
+            int64_t rows = bp.n;
+            bp.h_hub.assign(static_cast<size_t>(bp.n), 0);
             for (int64_t i2 = 0; i2 < bp.n; ++i2) {
                 int64_t cnt = 0;
                 for (const SlotTable& t : tabs)
                     for (int32_t j = 0; j < t.k; ++j) cnt += t.active[static_cast<size_t>(i2) * t.k + j] ? 1 : 0;
-                most = std::max(most, cnt);
+                if (cnt > SEQ_MAX) {
+                    const int64_t extra = (cnt - 1) / SEQ_MAX;
+                    overflow[i2] = static_cast<int32_t>(rows);
+                    n_rows[i2] = static_cast<int32_t>(1 + extra);
+                    rows += extra;
+                    bp.h_hub[i2] = 1;
+                }
             }
-            if (most <= SEQ_MAX) {
-                bp.h_nbr.assign(static_cast<size_t>(bp.n) * SEQ_MAX, -1);  // the entry order of k_build_seq
+            if (rows < (int64_t(1) << 26)) {
+                bp.h_nbr.assign(static_cast<size_t>(bp.n) * SEQ_MAX, -1);  // the entry order of k_build_seq (first row of each node)
                 for (int64_t i2 = 0; i2 < bp.n; ++i2) {
                     int e = 0;
                     for (const SlotTable& t : tabs)
                         for (int32_t j = 0; j < t.k; ++j) {
                             const size_t flat = static_cast<size_t>(i2) * t.k + j;
                             if (!t.active[flat]) continue;
-                            if (t.n_spin == 1) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.idx[0][flat];
+                            if (t.n_spin == 1 && e < SEQ_MAX) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.idx[0][flat];
                             ++e;
                         }
                 }
-                if (int32_t rc = bp.d_seq_nbr.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
-                if (int32_t rc = bp.d_seq_w.alloc(static_cast<size_t>(bp.n) * SEQ_MAX * 4)) return rc;
-                if (int32_t rc = bp.d_seq_first.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
-                if (int32_t rc = bp.d_seq_cnt.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+                bp.seq_rows = rows;
+                if (int32_t rc = bp.d_seq_nbr.alloc(static_cast<size_t>(rows) * SEQ_MAX * 4)) return rc;
+                if (int32_t rc = bp.d_seq_w.alloc(static_cast<size_t>(rows) * SEQ_MAX * 4)) return rc;
+                if (int32_t rc = bp.d_seq_first.alloc(static_cast<size_t>(rows) * 4)) return rc;
+                if (int32_t rc = bp.d_seq_cnt.alloc(static_cast<size_t>(rows) * 4)) return rc;
+                if (int32_t rc = upload(bp.d_seq_overflow, overflow.data(), overflow.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = upload(bp.d_seq_n_rows, n_rows.data(), n_rows.size() * 4, ctx->stream)) return rc;
                 if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
                 {
                     std::vector<int32_t> cnt_of(static_cast<size_t>(bp.n), 0), order(static_cast<size_t>(bp.n));
@@ -948,7 +964,8 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         HybridArgs a{};
         a.lut = LutArgs{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
                         make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
-        a.seq = SeqArgs{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
+        a.seq = SeqArgs{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), bp.d_seq_overflow.as<int32_t>(),
+                        bp.d_seq_n_rows.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
                         static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, a.lut.rk, s->n_chains, nullptr, nullptr, nullptr, nullptr, nullptr};
         a.lut_row = bp.d_lut_row.as<int32_t>();
         a.seq.order = bp.d_seq_order.as<int32_t>();
@@ -967,7 +984,8 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         return THRML_OK;
     }
     if (bp.base_kernel == 4 && !inj && !fields) {
-        SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
+        SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), bp.d_seq_overflow.as<int32_t>(),
+                  bp.d_seq_n_rows.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
                   static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr,
                   bp.d_seq_order.as<int32_t>(), bp.d_seq_counter.as<int32_t>()};
         CU_TRY(cudaMemsetAsync(a.counter, 0, 4, st));
@@ -1559,6 +1577,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
             return bi >= 0 && bi < p->n_free && (p->blocks[bi].kernel == 1 || p->blocks[bi].kernel == 4 || p->blocks[bi].kernel == 6);
         };
         auto slots_of = [&](int32_t bi) { return p->blocks[bi].kernel == 1 ? LUT_BITS : SEQ_MAX; };
+        auto is_hub = [&](int32_t bi, int64_t i) { return !p->blocks[bi].h_hub.empty() && p->blocks[bi].h_hub[static_cast<size_t>(i)] != 0; };
         for (int32_t bi = 0; bi < p->n_free; ++bi)
             if (lut_block(bi)) {
                 m1[bi].assign(static_cast<size_t>(p->blocks[bi].n), -1);
@@ -1571,7 +1590,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
             bool taken = false;
             if (m->spin_transform && len == 1 && sd[b0] == p->sd_spin) {
                 const int32_t bi = block_of_pos[pos[b0]];
-                if (lut_block(bi)) {
+                if (lut_block(bi) && !is_hub(bi, pos[b0] - p->blocks[bi].offset)) {
                     int32_t& slot = m1[bi][pos[b0] - p->blocks[bi].offset];
                     if (slot < 0) { slot = static_cast<int32_t>(r); taken = true; }
                 }
@@ -1579,7 +1598,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
                 int32_t pa = pos[b0], pb = pos[b0 + 1];
                 int32_t ba = block_of_pos[pa], bb = block_of_pos[pb];
                 if (p->blocks[ba].order < p->blocks[bb].order) { std::swap(pa, pb); std::swap(ba, bb); }  // (pa, ba) is updated later
-                if (p->blocks[ba].order > p->blocks[bb].order && lut_block(ba)) {
+                if (p->blocks[ba].order > p->blocks[bb].order && lut_block(ba) && !is_hub(ba, pa - p->blocks[ba].offset)) {
                     const int64_t i = pa - p->blocks[ba].offset;
                     const int ns = slots_of(ba);
                     for (int j = 0; j < ns; ++j)

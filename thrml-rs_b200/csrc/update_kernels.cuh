@@ -536,38 +536,52 @@ __global__ void __launch_bounds__(256, 2) k_spin_lut_persistent(const LutArgs* s
 // states are the same bits.  The sigmoid is approximated first (2^x and reciprocal units); only a draw within 4e-6 of
 // it (four times the approximation's worst error) is redone with the deterministic sigmoid.
 constexpr int SEQ_MAX = 32;
-// Entry lists from the slot tables: per node the active slots in table order, slot order; nbr = -1 for an entry
-// without a tail (a bias); bit e of first[node] marks the first entry of a table.
-__global__ void __launch_bounds__(256) k_build_seq(const DevTable* tabs, int32_t n_tabs, int32_t n, int32_t* ent_nbr, float* ent_w, uint32_t* ent_first, int32_t* ent_cnt) {
+// Entry lists from the slot tables: per node the active slots in table order, slot order, in rows of SEQ_MAX entries;
+// nbr = -1 for an entry without a tail (a bias); bit e of first[row] marks the first entry of a table; cnt[row] = entries
+// in the row.  Row `node` holds a node's first SEQ_MAX entries; a node with more continues in rows overflow[node],
+// overflow[node] + 1, ... (rows n and up; overflow[node] = -1 for the others).
+__global__ void __launch_bounds__(256) k_build_seq(const DevTable* tabs, int32_t n_tabs, int32_t n, const int32_t* overflow, int32_t* ent_nbr, float* ent_w,
+                                                   uint32_t* ent_first, int32_t* ent_cnt) {
     const int64_t node = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (node >= n) return;
-    int e = 0;
+    int e = 0;          // entry inside the current row
+    int64_t row = node;
+    int64_t next = overflow[node];
     uint32_t first = 0;
     for (int t = 0; t < n_tabs; ++t) {
         const DevTable T = tabs[t];
         bool started = false;
         for (int j = 0; j < T.k; ++j) {
             const int64_t flat = node * T.k + j;
-            if (!T.active[flat] || e >= SEQ_MAX) continue;
+            if (!T.active[flat]) continue;
+            if (e == SEQ_MAX) {  // row full: close it and continue in the node's next overflow row
+                ent_first[row] = first;
+                ent_cnt[row] = SEQ_MAX;
+                row = next++;
+                e = 0;
+                first = 0;
+            }
             if (!started) first |= 1u << e;
             started = true;
-            ent_nbr[node * SEQ_MAX + e] = T.n_spin == 1 ? T.idx[0][flat] : -1;
-            ent_w[node * SEQ_MAX + e] = T.w[flat];
+            ent_nbr[row * SEQ_MAX + e] = T.n_spin == 1 ? T.idx[0][flat] : -1;
+            ent_w[row * SEQ_MAX + e] = T.w[flat];
             ++e;
         }
     }
-    ent_first[node] = first;
-    ent_cnt[node] = e;
+    ent_first[row] = first;
+    ent_cnt[row] = e;
     for (; e < SEQ_MAX; ++e) {
-        ent_nbr[node * SEQ_MAX + e] = -1;
-        ent_w[node * SEQ_MAX + e] = 0.0f;
+        ent_nbr[row * SEQ_MAX + e] = -1;
+        ent_w[row * SEQ_MAX + e] = 0.0f;
     }
 }
 struct SeqArgs {
-    const int32_t* nbr;     // [n][SEQ_MAX]
-    const float* w;         // [n][SEQ_MAX]
-    const uint32_t* first;  // [n]
-    const int32_t* cnt;     // [n]
+    const int32_t* nbr;     // [rows][SEQ_MAX], rows = n + overflow rows
+    const float* w;         // [rows][SEQ_MAX]
+    const uint32_t* first;  // [rows]
+    const int32_t* cnt;     // [rows]
+    const int32_t* overflow;  // [n] first overflow row of a node with more than SEQ_MAX entries, -1 otherwise
+    const int32_t* n_rows;    // [n] rows of the node (1 unless it overflows)
     const uint8_t* spin;
     uint8_t* dst;
     int64_t ld;
@@ -603,10 +617,12 @@ __device__ __noinline__ bool exact_spin_draw(float gamma, uint32_t r) { return u
 template <bool ACC>
 __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
     const int lane = threadIdx.x & 31;
-    const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
-    const float wv = __ldg(a.w + static_cast<int64_t>(node) * SEQ_MAX + lane);
-    const uint32_t first = __ldg(a.first + node);
-    const int cnt = __ldg(a.cnt + node);
+    int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
+    float wv = __ldg(a.w + static_cast<int64_t>(node) * SEQ_MAX + lane);
+    uint32_t first = __ldg(a.first + node);
+    int cnt = __ldg(a.cnt + node);
+    const int n_rows = __ldg(a.n_rows + node);       // more than one only for a node with more than SEQ_MAX entries
+    const int64_t overflow = __ldg(a.overflow + node);
     uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
     int32_t my_row = -1, row1 = -1;
     uint32_t own = 0;        // entries whose pair row this node owns
@@ -629,32 +645,41 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
             const int32_t nbe = __shfl_sync(0xffffffffu, nb, e);
             return nbe >= 0 && live ? __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbe) * a.ld) + ch) : ones;
         };
-        uint4 ring[4];
+        for (int seg = 0; seg < n_rows; ++seg) {
+            if (n_rows > 1) {  // a long entry list: its rows are (re)loaded pass by pass
+                const int64_t row = seg == 0 ? node : overflow + seg - 1;
+                nb = __ldg(a.nbr + row * SEQ_MAX + lane);
+                wv = __ldg(a.w + row * SEQ_MAX + lane);
+                first = __ldg(a.first + row);
+                cnt = __ldg(a.cnt + row);
+            }
+            uint4 ring[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) ring[k] = k < cnt ? row_of(k) : ones;
-        for (int e0 = 0; e0 < cnt; e0 += 4) {
+            for (int k = 0; k < 4; ++k) ring[k] = k < cnt ? row_of(k) : ones;
+            for (int e0 = 0; e0 < cnt; e0 += 4) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const int e = e0 + k;
-                if (e >= cnt) break;  // uniform over the warp
-                const uint4 v = ring[k];
-                if (e + 4 < cnt) ring[k] = row_of(e + 4);
-                const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
-                if ((first >> e) & 1u) {  // a new table: close the previous one
+                for (int k = 0; k < 4; ++k) {
+                    const int e = e0 + k;
+                    if (e >= cnt) break;  // uniform over the warp
+                    const uint4 v = ring[k];
+                    if (e + 4 < cnt) ring[k] = row_of(e + 4);
+                    const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
+                    if ((first >> e) & 1u) {  // a new table: close the previous one
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        gam[i] = __fadd_rn(gam[i], part[i]);
-                        part[i] = 0.0f;
+                        for (int i = 0; i < 16; ++i) {
+                            gam[i] = __fadd_rn(gam[i], part[i]);
+                            part[i] = 0.0f;
+                        }
                     }
+                    const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
+                            part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
+                        }
                 }
-                const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
-                        part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
-                    }
             }
         }
         uint32_t o[4];
