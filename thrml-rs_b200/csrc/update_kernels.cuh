@@ -530,7 +530,7 @@ __global__ void __launch_bounds__(256, 2) k_spin_lut_persistent(const LutArgs* s
 }
 
 // Sequential-sum spin update for blocks whose nodes have more single-spin-tail neighbour slots than a threshold table
-// covers (9 to SEQ_MAX entries per node, bias entries included).  Same data movement as k_spin_lut — one warp per
+// covers (entry lists in rows of SEQ_MAX, bias entries included; any length).  Same data movement as k_spin_lut — one warp per
 // node, 16 chains per lane per pass, one 16-byte load per neighbour row — but the field is accumulated entry by
 // entry in the canonical order (per table from zero, tables left to right), exactly as k_spin_generic does, so the
 // states are the same bits.  The sigmoid is approximated first (2^x and reciprocal units); only a draw within 4e-6 of
