@@ -403,7 +403,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 for (int64_t i2 = 0; i2 < bp.n; ++i2) {
                     int deg = 0;
                     for (int e = 0; e < SEQ_MAX; ++e) deg += bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] >= 0 ? 1 : 0;
-                    if (deg > LUT_BITS) continue;
+                    if (deg > LUT_BITS || bp.h_hub[i2]) continue;
                     lut_row[i2] = static_cast<int32_t>(lut_nodes.size());
                     lut_nodes.push_back(static_cast<int32_t>(i2));
                     int at = 0;
@@ -431,7 +431,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                             for (int32_t j = 0; j < t.k; ++j) {
                                 const size_t flat = static_cast<size_t>(i2) * t.k + j;
                                 if (!t.active[flat]) continue;
-                                bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.n_spin == 1 ? t.idx[0][flat] : -1;
+                                if (e < SEQ_MAX) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.n_spin == 1 ? t.idx[0][flat] : -1;
                                 ++e;
                             }
                     }
