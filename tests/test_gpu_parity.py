@@ -341,7 +341,7 @@ def test_categorical_screen_and_exact_fallback(T, O, case):
     assert_states_equal(gs, os_, n_blocks_of(desc))
 
 
-@pytest.mark.parametrize("chains", [33, 520])
+@pytest.mark.parametrize("chains", [1, 33, 520])
 def test_mixed_degree_blocks_match_oracle(T, O, chains):
     """A sparse random graph with mean degree 6: most nodes keep their threshold tables, the few with more than 8
     neighbours take the sequential sum inside the same launch (kernel kind 6)."""
