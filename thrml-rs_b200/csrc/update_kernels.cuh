@@ -663,7 +663,7 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
                     if (e >= cnt) break;  // uniform over the warp
                     const uint4 v = ring[k];
                     if (e + 4 < cnt) ring[k] = row_of(e + 4);
-                    const uint32_t wbits = __float_as_uint(__shfl_sync(0xffffffffu, wv, e));
+                    const float we = __shfl_sync(0xffffffffu, wv, e);
                     if ((first >> e) & 1u) {  // a new table: close the previous one
 #pragma unroll
                         for (int i = 0; i < 16; ++i) {
@@ -671,35 +671,54 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
                             part[i] = 0.0f;
                         }
                     }
-                    const uint32_t neg[4] = {v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u};  // byte 1 where the spin is -1
+                    // 2 s - 1 as a float per chain with one byte permute: the bytes of t are 0x3f (spin +1) or 0xbf (spin -1),
+                    // the top byte of +-1.0f; the other three bytes (0x80, 0, 0) come from the constant.  Then one fused
+                    // multiply-add: w * (+-1) is exact, so the sum rounds as the reference's add does.  (The integer pipe is
+                    // the busy one: this is one of its operations per neighbour and chain instead of two.)
+                    const uint32_t t[4] = {((v.x ^ 0x01010101u) << 7) | 0x3f3f3f3fu, ((v.y ^ 0x01010101u) << 7) | 0x3f3f3f3fu,
+                                           ((v.z ^ 0x01010101u) << 7) | 0x3f3f3f3fu, ((v.w ^ 0x01010101u) << 7) | 0x3f3f3f3fu};
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
-                            const uint32_t sign = (neg[q] << (31 - 8 * c)) & 0x80000000u;
-                            part[4 * q + c] = __fadd_rn(part[4 * q + c], __uint_as_float(wbits ^ sign));  // w * (2 s - 1) is w with the sign flipped
+                            const float sp = __uint_as_float(__byte_perm(t[q], 0x00800000u, 0x0654u | (c << 12)));
+                            part[4 * q + c] = __fmaf_rn(sp, we, part[4 * q + c]);
                         }
                 }
             }
         }
+        // d = 2^24 (u - p) with the approximate sigmoid; the spin is the sign of d.  One test per pass finds the draws that
+        // are too close to call (within 4e-6 of p): only then the exact rule runs, for those draws.
         uint32_t o[4];
+        float nearest = 16777216.0f;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
             const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
-            uint32_t wd = 0;
+            o[q] = 0;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 const float gamma = __fadd_rn(gam[4 * q + c], part[4 * q + c]);
+                gam[4 * q + c] = gamma;
                 float ex, p24;
                 asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
                 asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));  // 2^24 p
                 const float d = __uint2float_rn(rr[c] >> 8) - p24;
-                bool one = d < 0.0f;
-                if (fabsf(d) <= 67.2f) one = exact_spin_draw(gamma, rr[c]);
-                wd |= one ? (1u << (8 * c)) : 0u;
+                part[4 * q + c] = d;
+                nearest = fminf(nearest, fabsf(d));
+                o[q] |= (__float_as_uint(d) >> 31) << (8 * c);
             }
-            o[q] = wd;
+        }
+        if (nearest <= 67.2f) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    if (fabsf(part[4 * q + c]) <= 67.2f)
+                        o[q] = (o[q] & ~(1u << (8 * c))) | ((exact_spin_draw(gam[4 * q + c], rr[c]) ? 1u : 0u) << (8 * c));
+            }
         }
         if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
         if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
