@@ -948,12 +948,17 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     if (bp.base_kernel == 1 && !inj && !fields) {
         LutArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
                   make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
-        const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
+        const bool few_chains = a.n_chunks <= FEW_CHAIN_CHUNKS;  // a thread per (node, 16 chains) instead of a warp per node
+        const int64_t ctas = few_chains ? std::min<int64_t>((bp.n * a.n_chunks + 255) / 256, static_cast<int64_t>(p->ctx->sm_count) * 16)
+                                        : std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
             a.m1_row = acc->fused[block]->m1.as<int32_t>();
             a.m2_row = acc->fused[block]->m2.as<int32_t>();
             a.sums = acc->d_sums.as<long long>();
-            k_spin_lut<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            if (few_chains) k_spin_lut_thread<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            else k_spin_lut<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else if (few_chains) {
+            k_spin_lut_thread<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         } else {
             k_spin_lut<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         }

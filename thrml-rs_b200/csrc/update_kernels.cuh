@@ -15,6 +15,7 @@ using namespace thrml;
 constexpr int MAX_TAILS = 8;
 constexpr int LUT_BITS = 8;              // a threshold table covers at most 8 neighbour spins
 constexpr int LUT_SIZE = 1 << LUT_BITS;  // entries per node
+constexpr int FEW_CHAIN_CHUNKS = 16;     // up to 16 chunks of 16 chains (256 chains): the thread-per-node threshold-table kernel
 
 // Device view of one slot table.
 struct DevTable {
@@ -513,6 +514,71 @@ template <bool ACC>
 __global__ void __launch_bounds__(256, 4) k_spin_lut(const __grid_constant__ LutArgs a) {
     __shared__ uint32_t s_lut[8][LUT_SIZE];
     lut_block_update<ACC, false>(a, s_lut[threadIdx.x >> 5]);
+}
+
+// Few chains (at most 256, i.e. at most 16 chunks of 16): a warp per node would leave most lanes idle and stage a whole
+// 1 KiB table for a handful of lookups.  Here one THREAD updates one node for one chunk of 16 chains: the neighbour
+// list and the table entries it needs come through the read-only cache, threads of a warp work on different nodes.
+// Same bits as k_spin_lut (same configuration byte, same table, same noise).  ACC adds each thread's share of the
+// node's <s_i> row and of the pair rows the node owns with atomics (several threads may share a node).
+template <bool ACC>
+__global__ void __launch_bounds__(256) k_spin_lut_thread(const __grid_constant__ LutArgs a) {
+    const int64_t total = static_cast<int64_t>(a.n) * a.n_chunks;
+    for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int node = static_cast<int>(t / a.n_chunks), ch = static_cast<int>(t % a.n_chunks);
+        const int4 n0 = __ldg(reinterpret_cast<const int4*>(a.nbr + static_cast<int64_t>(node) * LUT_BITS));
+        const int4 n1 = __ldg(reinterpret_cast<const int4*>(a.nbr + static_cast<int64_t>(node) * LUT_BITS) + 1);
+        const int32_t nb[LUT_BITS] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+        uint32_t cfg[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int j = 0; j < LUT_BITS; ++j)
+            if (nb[j] >= 0) {
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nb[j]) * a.ld) + ch);
+                cfg[0] += v.x << j;
+                cfg[1] += v.y << j;
+                cfg[2] += v.z << j;
+                cfg[3] += v.w << j;
+            }
+        const uint32_t* L = a.lut + static_cast<int64_t>(node) * LUT_SIZE;
+        uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            if (16ll * ch + 4 * q >= a.n_chains) continue;  // nothing but padding in this word
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+            uint32_t w = 0;
+            w |= (r.x <= __ldg(L + (cfg[q] & 0xffu))) ? 1u : 0u;
+            w |= (r.y <= __ldg(L + ((cfg[q] >> 8) & 0xffu))) ? 0x100u : 0u;
+            w |= (r.z <= __ldg(L + ((cfg[q] >> 16) & 0xffu))) ? 0x10000u : 0u;
+            w |= (r.w <= __ldg(L + (cfg[q] >> 24))) ? 0x1000000u : 0u;
+            o[q] = w;
+        }
+        reinterpret_cast<uint4*>(a.dst + static_cast<int64_t>(node) * a.ld)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (ACC) {
+            uint32_t vm[4];
+            int valid = 0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                vm[q] = valid_mask(a.n_chains, ch, q) & 0x01010101u;
+                valid += __popc(vm[q]);
+            }
+            const int32_t row1 = __ldg(a.m1_row + node);
+            if (row1 >= 0) {
+                const int ones = __popc(o[0] & vm[0]) + __popc(o[1] & vm[1]) + __popc(o[2] & vm[2]) + __popc(o[3] & vm[3]);
+                atomicAdd(reinterpret_cast<unsigned long long*>(a.sums) + row1, static_cast<unsigned long long>(static_cast<long long>(2 * ones - valid)));
+            }
+            const int4 r0 = __ldg(reinterpret_cast<const int4*>(a.m2_row + static_cast<int64_t>(node) * LUT_BITS));
+            const int4 r1 = __ldg(reinterpret_cast<const int4*>(a.m2_row + static_cast<int64_t>(node) * LUT_BITS) + 1);
+            const int32_t rows[LUT_BITS] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j)
+                if (rows[j] >= 0) {
+                    int dis = 0;  // chains in which neighbour j differs from the new spin
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) dis += __popc(((cfg[q] >> j) ^ o[q]) & vm[q]);
+                    atomicAdd(reinterpret_cast<unsigned long long*>(a.sums) + rows[j], static_cast<unsigned long long>(static_cast<long long>(valid - 2 * dis)));
+                }
+        }
+    }
 }
 
 // Persistent multi-sweep variant for cache-resident programs: one cooperative launch walks a list of block updates
