@@ -203,7 +203,18 @@ static int32_t upload(DevBuf& buf, const void* host, size_t bytes, cudaStream_t 
     if (bytes) CU_TRY(cudaMemcpyAsync(buf.p, host, bytes, cudaMemcpyHostToDevice, st));
     return THRML_OK;
 }
-static dim3 grid_nq(int64_t n, int64_t ld) { return dim3(static_cast<unsigned>((n + 7) / 8), static_cast<unsigned>((ld / 4 + 31) / 32)); }
+// Launch shape of the kernels whose thread is one node x four chains: 256 threads as (chain quads, nodes).  With 128 chains
+// or more a warp spans 32 quads of one node; with fewer the block is narrower and a warp covers several nodes, so a
+// single-chain state (the reference's usual call) does not idle 31 lanes of 32.
+static dim3 block_nq(int64_t ld) {
+    unsigned qx = 1;
+    while (qx < 32 && static_cast<int64_t>(qx) * 4 < ld) qx *= 2;
+    return dim3(qx, 256 / qx);
+}
+static dim3 grid_nq(int64_t n, int64_t ld) {
+    const dim3 b = block_nq(ld);
+    return dim3(static_cast<unsigned>((n + b.y - 1) / b.y), static_cast<unsigned>((ld / 4 + b.x - 1) / b.x));
+}
 static int32_t need_scratch(thrml_state* s, size_t bytes) {
     if (s->scratch.bytes >= bytes) return THRML_OK;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
@@ -760,7 +771,7 @@ int32_t thrml_hinton_init(thrml_state* s, const int32_t* blocks, int32_t n_block
     int64_t boff = 0;
     for (int32_t i = 0; i < n_blocks; ++i) {
         const BlockProg& bp = s->prog->blocks[blocks[i]];
-        k_hinton<<<grid_nq(bp.n, s->ld), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), d_bias + boff, beta,
+        k_hinton<<<grid_nq(bp.n, s->ld), block_nq(s->ld), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), d_bias + boff, beta,
                                                                  static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[i]),
                                                                  static_cast<uint32_t>(keys[i] >> 32), d_inj ? d_inj + boff * s->n_chains : nullptr);
         CU_TRY(cudaGetLastError());
@@ -779,7 +790,7 @@ int32_t thrml_state_randomize(thrml_state* s, uint64_t key) {
     rng_split(key, nf, keys.data());
     for (int32_t b = 0; b < nf; ++b) {
         const BlockProg& bp = s->prog->blocks[b];
-        k_randomize<<<grid_nq(bp.n, s->ld), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), bp.kind,
+        k_randomize<<<grid_nq(bp.n, s->ld), block_nq(s->ld), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n), bp.kind,
                                                                     static_cast<uint32_t>(s->chain_offset >> 2), static_cast<uint32_t>(keys[b]),
                                                                     static_cast<uint32_t>(keys[b] >> 32));
         CU_TRY(cudaGetLastError());
@@ -1028,7 +1039,7 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         inj->pos += need;
         a.inj = s->scratch.as<float>();
     }
-    const dim3 grid = grid_nq(bp.n, s->ld), blk(32, 8);
+    const dim3 grid = grid_nq(bp.n, s->ld), blk = block_nq(s->ld);
     if (bp.is_cat) {
         if (fields) k_cat_generic<2><<<grid, blk, 0, st>>>(a);
         else if (inj) k_cat_generic<1><<<grid, blk, 0, st>>>(a);

@@ -10,8 +10,8 @@ using namespace thrml;
 // hinton_init (ising.rs:602-673) and uniform start.  One thread = one node x four chains.
 __global__ void __launch_bounds__(256) k_hinton(uint8_t* dst, int64_t ld, int64_t n_chains, int32_t n, const float* bias, float beta,
                                                 uint32_t chain_word0, uint32_t k0, uint32_t k1, const float* inj) {
-    const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int node = blockIdx.x * 8 + threadIdx.y;
+    const int quad = blockIdx.y * blockDim.x + threadIdx.x;
+    const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= n || 4 * static_cast<int64_t>(quad) >= ld) return;
     const float p = det_sigmoid(__fmul_rn(bias[node], beta));  // ising.rs:650
     const U4 r = philox4x32_10(static_cast<uint32_t>(node), chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_HINT, k0, k1);
@@ -27,8 +27,8 @@ __global__ void __launch_bounds__(256) k_hinton(uint8_t* dst, int64_t ld, int64_
 }
 __global__ void __launch_bounds__(256) k_randomize(uint8_t* dst, int64_t ld, int64_t n_chains, int32_t n, int32_t kind, uint32_t chain_word0,
                                                    uint32_t k0, uint32_t k1) {
-    const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int node = blockIdx.x * 8 + threadIdx.y;
+    const int quad = blockIdx.y * blockDim.x + threadIdx.x;
+    const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= n || 4 * static_cast<int64_t>(quad) >= ld) return;
     const U4 r = philox4x32_10(static_cast<uint32_t>(node), chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_RAND, k0, k1);
     uint32_t out = 0;

@@ -50,8 +50,8 @@ __device__ __forceinline__ uint32_t ld_word(const uint8_t* base, int64_t row, in
 // Field accumulation order: per table, slots left to right from zero; tables left to right (spin_gibbs.rs:527-582).
 template <int MODE>
 __global__ void __launch_bounds__(256) k_spin_generic(UpdateArgs a) {
-    const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int node = blockIdx.x * 8 + threadIdx.y;
+    const int quad = blockIdx.y * blockDim.x + threadIdx.x;
+    const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
     float gamma[4] = {0.f, 0.f, 0.f, 0.f};
     for (int t = 0; t < a.n_tabs; ++t) {
@@ -110,8 +110,8 @@ __global__ void __launch_bounds__(256) k_spin_generic(UpdateArgs a) {
 // active * prod(2s-1) * W[own c, neighbour category]; draw = argmax_c(theta[c] - ln(-ln u_c)), first maximum wins.
 template <int MODE>
 __global__ void __launch_bounds__(256) k_cat_generic(UpdateArgs a) {
-    const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int node = blockIdx.x * 8 + threadIdx.y;
+    const int quad = blockIdx.y * blockDim.x + threadIdx.x;
+    const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
     const int K = a.K;
     float best[4] = {0.f, 0.f, 0.f, 0.f};
@@ -223,7 +223,7 @@ __device__ __noinline__ uint32_t cat_exact_argmax(const UpdateArgs& a, int node,
 }
 
 // Categorical update for blocks whose nodes have at most CAT_SLOTS active slots (in-kernel noise only; more would not fit the register file).  Same results
-// as k_cat_generic<0>, organised for speed: a warp is one node x 128 chains, so the slot structure is warp-uniform.
+// as k_cat_generic<0>, organised for speed (with 128 chains or more a warp is one node, so the slot structure is warp-uniform).
 //  * everything that does not depend on the category is gathered once per node and thread: per active slot the
 //    neighbour's category word (clamped), the sign word of its spin tails, the weight row and whether it opens a table;
 //  * the category loop then costs one table lookup and one add per slot and chain, in the canonical order
@@ -232,8 +232,8 @@ __device__ __noinline__ uint32_t cat_exact_argmax(const UpdateArgs& a, int node,
 //    2e-5 of the exact one); a leader less than 6e-5 ahead of the runner-up sends that chain to cat_exact_argmax.
 constexpr int CAT_SLOTS = 8;
 __global__ void __launch_bounds__(256, 2) k_cat_fast(const __grid_constant__ UpdateArgs a) {
-    const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int node = blockIdx.x * 8 + threadIdx.y;
+    const int quad = blockIdx.y * blockDim.x + threadIdx.x;
+    const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
     const int K = a.K;
     uint32_t xw[CAT_SLOTS], sg[CAT_SLOTS];   // neighbour categories (4 chains), sign bits (bit 7 of a byte: the spin-tail product is -1)
