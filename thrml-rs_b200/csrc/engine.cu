@@ -976,7 +976,10 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
-    if (bp.base_kernel == 6 && !inj && !fields) {
+    // With few chains the warp-per-node kernels idle most lanes (16 chains per lane); the node x quad gather kernel, which
+    // then packs several nodes into a warp, is the faster one unless the observer has to ride along.
+    const bool narrow = s->ld / 16 <= NARROW_CHUNKS && !(acc && acc->fused[block]);
+    if (bp.base_kernel == 6 && !inj && !fields && !narrow) {
         HybridArgs a{};
         a.lut = LutArgs{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), s->rows(p->sd_spin), dst, s->ld, static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0,
                         make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr};
@@ -999,7 +1002,7 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
-    if (bp.base_kernel == 4 && !inj && !fields) {
+    if (bp.base_kernel == 4 && !inj && !fields && !narrow) {
         SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), bp.d_seq_overflow.as<int32_t>(),
                   bp.d_seq_n_rows.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
                   static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr,

@@ -15,6 +15,7 @@ using namespace thrml;
 constexpr int MAX_TAILS = 8;
 constexpr int LUT_BITS = 8;              // a threshold table covers at most 8 neighbour spins
 constexpr int LUT_SIZE = 1 << LUT_BITS;  // entries per node
+constexpr int NARROW_CHUNKS = 4;         // up to 64 chains: blocks of the sequential-sum kinds run the node x quad gather kernel
 constexpr int FEW_CHAIN_CHUNKS = 16;     // up to 16 chunks of 16 chains (256 chains): the thread-per-node threshold-table kernel
 
 // Device view of one slot table.
