@@ -39,7 +39,7 @@ def parse():
     ap.add_argument("--chains", type=int, default=CHAINS_PER_GPU, help="chains per GPU")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts", "small_lattice"],
+    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts", "potts_program", "small_lattice"],
                     help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores (1 GPU); "
                          "lattice = one bit-packed 2-D Ising lattice sharded by row stripes with halo exchange")
     ap.add_argument("--side", type=int, default=32768, help="lattice side (lattice workload)")
@@ -185,6 +185,10 @@ def main():
     if args.workload == "small_lattice":
         if rank == 0:
             print(json.dumps(run_small_lattice(T, torch, args, local_rank)), flush=True)
+        return
+    if args.workload == "potts_program":
+        if rank == 0:
+            print(json.dumps(run_potts_program(T, torch, args, local_rank)), flush=True)
         return
     if args.workload == "potts":
         if rank == 0:
@@ -402,6 +406,50 @@ def run_small_lattice(T, torch, args, device):
                        "l2": "cache-resident (256 KiB of state): bound by launches and grid-wide barriers, not by bandwidth"},
             # one k_hinton per block and step, plus the update launches the state counted (per-block and persistent)
             "gpu_launches": reps * 2 + sum(launches1) - sum(launches0), "e2e": None}
+
+
+def run_potts_program(T, torch, args, device):
+    """The same kind of model as `potts`, but as the explicit factor program the reference would build
+    (FactorSamplingProgram over a unary CategoricalEBMFactor and one [n, K, K] pair factor per direction, crates/thrml-models/src/
+    factor.rs:153-184), at 32^3 nodes (the per-edge weight tensors are 39 MB there; 2.5 GB per block at 128^3): the general
+    categorical kernels instead of the implicit lattice."""
+    side, K, chains = (args.side if args.side != 32768 else 32), 10, 1024
+    n = side ** 3
+    rng = np.random.default_rng(0x5EED0004)
+    tables = rng.normal(0, 0.3, (3, K, K)).astype(np.float32)
+    unary = rng.normal(0, 0.1, (n, K, 1)).astype(np.float32)
+    idx = np.arange(n).reshape(side, side, side)
+    colour = (np.add.outer(np.add.outer(np.arange(side), np.arange(side)), np.arange(side)) % 2).ravel()
+    ctx = T.default_context(device)
+    bld = T.Builder(np.full(n, K, np.int32))
+    for c in (0, 1):
+        bld.add_free_block(np.flatnonzero(colour == c))
+    bld.add_discrete_factor([], [np.arange(n)], unary)
+    for d in range(3):
+        bld.add_discrete_factor([], [idx.ravel(), np.roll(idx, -1, axis=d).ravel()], np.broadcast_to(tables[d], (n, K, K)).copy())
+    bld.compile()
+    program = T.Program(bld, ctx)
+    kinds = [program.block_kernel(b) for b in range(2)]
+    state = T.ChainState(program, chains)
+    state.randomize(5)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+    for i in range(max(args.warmup, 3)):
+        state.sample_blocks(i)
+    ctx.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record(stream)
+    for i in range(args.steps):
+        state.sample_blocks(100 + i)
+    ev1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1) / args.steps
+    updates = float(n) * chains
+    return {"metric": METRIC, "value": updates / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8 categories, f32 logits", "data": "synthetic",
+            "config": {"workload": "3-D periodic Potts-like lattice as an explicit factor program (unary factor + one pair factor per direction)", "side": side,
+                       "categories": K, "chains": chains, "block_kernels": kinds, "l2": "state 32 MiB, weights 39 MB: cache-resident; an instruction-bound kernel"},
+            "gpu_launches": args.steps * 2, "e2e": None}
 
 
 def run_potts(T, torch, args, device):

@@ -232,7 +232,7 @@ __device__ __noinline__ uint32_t cat_exact_argmax(const UpdateArgs& a, int node,
 //  * the Gumbel noise is screened with the hardware logarithm (k_potts_update documents the bound: each score within
 //    2e-5 of the exact one); a leader less than 6e-5 ahead of the runner-up sends that chain to cat_exact_argmax.
 constexpr int CAT_SLOTS = 8;
-__global__ void __launch_bounds__(256, 2) k_cat_fast(const __grid_constant__ UpdateArgs a) {
+__global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ UpdateArgs a) {
     const int quad = blockIdx.y * blockDim.x + threadIdx.x;
     const int node = blockIdx.x * blockDim.y + threadIdx.y;
     if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
@@ -268,53 +268,44 @@ __global__ void __launch_bounds__(256, 2) k_cat_fast(const __grid_constant__ Upd
         }
     }
     constexpr float MARGIN = 6e-5f;
-    float best[4], second[4];
-    uint32_t arg[4] = {0, 0, 0, 0};
-    U4 r[4];
-    for (int cat = 0; cat < K; ++cat) {
-        float th[4] = {0.f, 0.f, 0.f, 0.f}, sum[4] = {0.f, 0.f, 0.f, 0.f};
+    uint32_t out = 0;
+    // One chain at a time (not unrolled): the four chains of a thread share nothing in this loop but the slot data, and the
+    // smaller live set (one Philox block, one leader / runner-up pair) lets three CTAs share an SM instead of two.
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+        if (4 * static_cast<int64_t>(quad) + c >= a.n_chains) break;
+        const int sh = 8 * c;
+        float best = 0.f, second = -3.0e38f;
+        uint32_t lead = 0;
+        U4 r{0, 0, 0, 0};
+        for (int cat = 0; cat < K; ++cat) {
+            float th = 0.f, sum = 0.f;
 #pragma unroll
-        for (int s = 0; s < CAT_SLOTS; ++s) {
-            if (s >= S) break;  // uniform over the warp
-            if (s > 0 && ((opens >> s) & 1u)) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) { th[c] = __fadd_rn(th[c], sum[c]); sum[c] = 0.f; }
+            for (int s = 0; s < CAT_SLOTS; ++s) {
+                if (s >= S) break;  // uniform over the threads of a node
+                if (s > 0 && ((opens >> s) & 1u)) { th = __fadd_rn(th, sum); sum = 0.f; }
+                const float* wk = ((tailed >> s) & 1u) ? wrow[s] + cat * K + ((xw[s] >> sh) & 0xffu) : wrow[s] + cat;
+                const uint32_t wb = __float_as_uint(__ldg(wk));
+                sum = __fadd_rn(sum, __uint_as_float(wb ^ (((sg[s] >> sh) & 0x80u) << 24)));  // sp * w = w with the sign flipped
             }
-            if ((tailed >> s) & 1u) {
-                const float* wk = wrow[s] + cat * K;
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint32_t wb = __float_as_uint(__ldg(wk + ((xw[s] >> (8 * c)) & 0xffu)));
-                    sum[c] = __fadd_rn(sum[c], __uint_as_float(wb ^ (((sg[s] >> (8 * c)) & 0x80u) << 24)));  // sp * w = w with the sign flipped
-                }
-            } else {
-                const uint32_t wb = __float_as_uint(__ldg(wrow[s] + cat));
-#pragma unroll
-                for (int c = 0; c < 4; ++c) sum[c] = __fadd_rn(sum[c], __uint_as_float(wb ^ (((sg[s] >> (8 * c)) & 0x80u) << 24)));
-            }
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            th[c] = __fadd_rn(th[c], sum[c]);
+            th = __fadd_rn(th, sum);
             if ((cat & 3) == 0)
-                r[c] = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
-            const float u = u23_open(pick(r[c], cat & 3));
+                r = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
+            const float u = u23_open(pick(r, cat & 3));
             const float w = 1.0f - u;
             const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
             const float l1 = w < 0.03125f ? series : -__logf(u);
-            const float p = th[c] - __logf(l1);
-            if (cat == 0) { best[c] = p; second[c] = -3.0e38f; }
-            else if (p > best[c]) { second[c] = best[c]; best[c] = p; arg[c] = cat; }
-            else if (p > second[c]) second[c] = p;
+            const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
+            if (cat == 0) {
+                best = p;
+            } else {
+                second = fmaxf(second, fminf(best, p));
+                if (p > best) { best = p; lead = cat; }
+            }
         }
+        if (!(best - second > MARGIN)) lead = cat_exact_argmax(a, node, quad, c);
+        out |= lead << sh;
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-        if (!(best[c] - second[c] > MARGIN)) arg[c] = cat_exact_argmax(a, node, quad, c);
-    uint32_t out = 0;
-#pragma unroll
-    for (int c = 0; c < 4; ++c)
-        if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
     *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
 }
 
