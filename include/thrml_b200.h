@@ -150,6 +150,12 @@ int32_t thrml_debug_wait_timeout(thrml_ctx* ctx);
  * per launch from the shape (pairs for long reductions without much row padding).  All give the same results; tests
  * run both tilings.  Returns the previous setting.  No counterpart in the reference. */
 int32_t thrml_debug_dense_pair_mode(int32_t mode);
+/* Widens (units of 2^-24 of probability, process-wide, >= 0) the window around each draw's probability inside which the
+ * split-field-table update of sequential-sum nodes recomputes the field in the canonical order; applies to programs
+ * created or re-weighted afterwards.  0 (the default) keeps the derived bound; 2^25 sends every draw through the exact
+ * route.  Results never depend on it; tests use it to run both routes.  Returns the previous value.  No counterpart in
+ * the reference. */
+float thrml_debug_split_margin(float extra_units);
 /* cudaStream_t of the context, for callers that time with their own events. */
 void* thrml_ctx_stream(thrml_ctx* ctx);
 

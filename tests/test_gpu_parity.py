@@ -405,3 +405,42 @@ def test_hub_nodes_continue_in_overflow_rows(T, O):
     assert_states_equal(gs, os_, n_blocks_of(desc))
     for t in range(2):
         assert np.array_equal(gm.read(t)[0], om.read(t)[0])
+
+
+@pytest.mark.parametrize("degree,chains,extra", [(12, 300, 0.0), (16, 1040, 0.0), (10, 4100, 0.0), (12, 300, 2.0 ** 25), (14, 530, 300000.0)])
+def test_split_field_tables_match_oracle(T, O, degree, chains, extra):
+    """Sequential-sum nodes with at most 16 neighbour entries, 256 chains or more: the field comes from two 256-entry
+    tables and only draws close to the probability take the canonical sum.  `extra` widens that window: 0 = the derived
+    bound, 2^25 = every draw through the exact route, 3e5 (2 % of the unit interval) = a mixture."""
+    before = T.lib().thrml_debug_split_margin(extra)
+    try:
+        desc, info = M.ising_random_graph(T, 260, degree, 300 + degree, w_sigma=0.4, bias_sigma=0.3)
+        prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 3)
+    finally:
+        T.lib().thrml_debug_split_margin(before)
+    assert all(prog.block_kernel(b) == 4 for b in range(len(desc["free"])))
+    gs.run_blocks(23, 8)
+    os_.run_blocks(23, 8)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    e0 = tuple(int(x) for x in info["edges"][0])
+    spec = moment_spec(desc, info) + [[(0, 5, 9), e0]]
+    gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    assert gm.fused_info() == (info["n"] + len(info["edges"]), 2)
+    gs.sample_with_observation(5, 1, 3, 2, moments=gm)
+    os_.sample_with_observation(5, 1, 3, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(3):
+        assert np.array_equal(gm.read(t)[0], om.read(t)[0])
+    # new couplings rebuild the tables (larger ones: wider windows)
+    J2 = (info["J"] * -2.5).astype(np.float32)
+    desc2 = dict(desc, ops=[("add_ising", np.arange(info["n"]), info["b"], info["edges"], J2, info["beta"])])
+    gb2, ob2 = M.build_both(T, O, desc2)
+    for blk in range(len(desc["free"])):
+        for t, tab in enumerate(gb2.tables(blk)):
+            prog.update_weights(blk, t, tab["w"].ravel())
+    os2 = O.State(ob2, chains)
+    for i in range(n_blocks_of(desc)):
+        os2.set_block(i, os_.get_block(i))
+    gs.run_blocks(6, 3)
+    os2.run_blocks(6, 3)
+    assert_states_equal(gs, os2, n_blocks_of(desc))

@@ -53,6 +53,8 @@ struct BlockProg {
     int64_t seq_rows = 0;
     std::vector<char> h_hub;                             // kernels 4 and 6: nodes with overflow rows (not served by the fused observer)
     DevBuf d_seq_order, d_seq_counter;                   // kernels 4 and 6: nodes by decreasing entry count; the launch's work counter
+    DevBuf d_split_row, d_split_nodes, d_split_tab, d_split_margin;  // kernels 4 and 6: split field tables of nodes with at most 16 neighbour entries
+    int64_t n_split = 0;
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
@@ -256,11 +258,17 @@ void* thrml_ctx_stream(thrml_ctx* ctx) { return ctx ? static_cast<void*>(ctx->st
 // ---------------------------------------------------------------------------------------------------------
 // Program.
 // ---------------------------------------------------------------------------------------------------------
+static float g_split_extra_margin = 0.0f;
 static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
     k_build_seq<<<static_cast<unsigned>((bp.n + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
                                                                                       bp.d_seq_overflow.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(),
                                                                                       bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>());
     CU_TRY(cudaGetLastError());
+    if (bp.n_split > 0) {
+        k_build_split<<<static_cast<unsigned>(bp.n_split), 256, 0, p->ctx->stream>>>(bp.d_split_nodes.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(),
+                                                                                    bp.d_seq_cnt.as<int32_t>(), bp.d_split_tab.as<float>(), bp.d_split_margin.as<float>(), g_split_extra_margin);
+        CU_TRY(cudaGetLastError());
+    }
     return THRML_OK;
 }
 static int32_t rebuild_lut(thrml_program* p, BlockProg& bp) {
@@ -445,6 +453,26 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                                 if (e < SEQ_MAX) bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] = t.n_spin == 1 ? t.idx[0][flat] : -1;
                                 ++e;
                             }
+                    }
+                }
+                // sequential-sum nodes with at most 16 neighbour entries (one entry row) look their field up in two tables
+                {
+                    std::vector<int32_t> split_row(static_cast<size_t>(bp.n), -1), split_nodes;
+                    for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                        if (bp.h_hub[i2] || (bp.kernel == 6 && lut_row[i2] >= 0)) continue;
+                        int deg = 0;
+                        for (int e = 0; e < SEQ_MAX; ++e) deg += bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] >= 0 ? 1 : 0;
+                        if (deg > SPLIT_BITS) continue;
+                        split_row[i2] = static_cast<int32_t>(split_nodes.size());
+                        split_nodes.push_back(static_cast<int32_t>(i2));
+                    }
+                    if (!split_nodes.empty() && split_nodes.size() * SPLIT_TAB * 4 <= (size_t(8) << 30)) {
+                        bp.n_split = static_cast<int64_t>(split_nodes.size());
+                        if (int32_t rc = upload(bp.d_split_row, split_row.data(), split_row.size() * 4, ctx->stream)) return rc;
+                        if (int32_t rc = upload(bp.d_split_nodes, split_nodes.data(), split_nodes.size() * 4, ctx->stream)) return rc;
+                        if (int32_t rc = bp.d_split_tab.alloc(static_cast<size_t>(bp.n_split) * SPLIT_TAB * 4)) return rc;
+                        if (int32_t rc = bp.d_split_margin.alloc(static_cast<size_t>(bp.n_split) * 4)) return rc;
+                        if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
                     }
                 }
             }
@@ -989,6 +1017,11 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         a.lut_row = bp.d_lut_row.as<int32_t>();
         a.seq.order = bp.d_seq_order.as<int32_t>();
         a.seq.counter = bp.d_seq_counter.as<int32_t>();
+        if (bp.n_split > 0 && a.seq.n_chunks >= SPLIT_MIN_CHUNKS) {
+            a.seq.split_row = bp.d_split_row.as<int32_t>();
+            a.seq.split_tab = bp.d_split_tab.as<float>();
+            a.seq.split_margin = bp.d_split_margin.as<float>();
+        }
         CU_TRY(cudaMemsetAsync(a.seq.counter, 0, 4, st));
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
@@ -1006,7 +1039,12 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         SeqArgs a{bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>(), bp.d_seq_overflow.as<int32_t>(),
                   bp.d_seq_n_rows.as<int32_t>(), s->rows(p->sd_spin), dst, s->ld,
                   static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, make_round_keys(key), s->n_chains, nullptr, nullptr, nullptr,
-                  bp.d_seq_order.as<int32_t>(), bp.d_seq_counter.as<int32_t>()};
+                  bp.d_seq_order.as<int32_t>(), bp.d_seq_counter.as<int32_t>(), nullptr, nullptr, nullptr};
+        if (bp.n_split > 0 && a.n_chunks >= SPLIT_MIN_CHUNKS) {
+            a.split_row = bp.d_split_row.as<int32_t>();
+            a.split_tab = bp.d_split_tab.as<float>();
+            a.split_margin = bp.d_split_margin.as<float>();
+        }
         CU_TRY(cudaMemsetAsync(a.counter, 0, 4, st));
         const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8);
         if (acc && acc->fused[block]) {
@@ -1764,6 +1802,11 @@ int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, 
 int32_t thrml_debug_dense_pair_mode(int32_t mode) {
     const int32_t before = g_dense_pair_mode;
     g_dense_pair_mode = mode < 0 || mode > 2 ? 2 : mode;
+    return before;
+}
+float thrml_debug_split_margin(float extra_units) {
+    const float before = g_split_extra_margin;
+    g_split_extra_margin = extra_units >= 0.0f ? extra_units : 0.0f;
     return before;
 }
 int32_t thrml_state_launch_counts(const thrml_state* s, int64_t* block_launches, int64_t* persistent_launches) {

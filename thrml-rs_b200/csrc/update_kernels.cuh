@@ -656,6 +656,10 @@ struct SeqArgs {
     // (most entries first).  Node costs differ by the entry count, so a fixed assignment leaves a long tail.
     const int32_t* order;   // [n] permutation of the block's nodes
     int32_t* counter;
+    // Split field tables (nullptr = none): split_row[node] >= 0 is the node's row in split_tab / split_margin.
+    const int32_t* split_row;
+    const float* split_tab;     // [rows][2][256]
+    const float* split_margin;  // [rows]
 };
 // Next node for this warp, or -1 when the block is done.
 __device__ __forceinline__ int take_node(const SeqArgs& a) {
@@ -806,9 +810,197 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
         if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
     }
 }
+// Split field tables for sequential-sum nodes with at most 16 neighbour entries (one entry row): the field is looked
+// up as A[configuration of neighbours 0..7] + B[configuration of neighbours 8..15] instead of being added entry by
+// entry.  A (which also carries the entries without a tail) and B are the real partial sums rounded once, so the
+// looked-up field differs from the canonical sequential f32 sum by a few rounding errors of the summed |w| at most.
+// The draw is decided from it only when u is farther from the probability than that bound allows (split_margin, in
+// units of 2^-24: the approximate sigmoid's 67.2 plus the field bound pushed through the sigmoid's steepest slope);
+// the other draws — a few in 10^5 — take the canonical sum (exact_seq_gamma) and the exact rule, so the states are
+// the bits of k_spin_generic.
+constexpr int SPLIT_BITS = 16;
+constexpr int SPLIT_TAB = 512;  // floats per node: A[256] then B[256]
+constexpr int SPLIT_MIN_CHUNKS = 16;  // states with fewer than 256 chains would read 2 KiB of tables per node for a handful of lookups
+__global__ void __launch_bounds__(256) k_build_split(const int32_t* split_nodes, const int32_t* ent_nbr, const float* ent_w, const int32_t* ent_cnt,
+                                                     float* tab, float* margin, float extra_margin) {
+    const int64_t row = blockIdx.x;
+    const int node = split_nodes[row];
+    const int c = threadIdx.x;  // configuration byte
+    const int cnt = ent_cnt[node];
+    double A = 0.0, B = 0.0, mag = 0.0;
+    int rank = 0;
+    for (int e = 0; e < cnt; ++e) {
+        const double w = static_cast<double>(ent_w[static_cast<int64_t>(node) * SEQ_MAX + e]);
+        mag += fabs(w);
+        if (ent_nbr[static_cast<int64_t>(node) * SEQ_MAX + e] < 0) {
+            A += w;
+        } else {
+            if (rank < 8) A += ((c >> rank) & 1) ? w : -w;
+            else B += ((c >> (rank - 8)) & 1) ? w : -w;
+            ++rank;
+        }
+    }
+    tab[row * SPLIT_TAB + c] = static_cast<float>(A);
+    tab[row * SPLIT_TAB + 256 + c] = static_cast<float>(B);
+    // |looked-up field - canonical field| <= (2 cnt + 4) 2^-24 sum|w| (one rounding per add of either route, table
+    // closings included); times 2 (the sigmoid's argument is twice the field) times 1/4 (its steepest slope) times 2^24,
+    // with a tenth on top for the second-order terms.
+    if (c == 0) margin[row] = 67.2f + 1.0f + static_cast<float>(0.55 * (2.0 * cnt + 4.0) * mag) + extra_margin;
+}
+// The canonical field of one node and chain: per table from zero, entries left to right, tables left to right.
+__device__ __noinline__ float exact_seq_gamma(const SeqArgs& a, int node, int64_t chain) {
+    const int64_t at = static_cast<int64_t>(node) * SEQ_MAX;
+    const uint32_t first = __ldg(a.first + node);
+    const int cnt = __ldg(a.cnt + node);
+    float gam = 0.0f, part = 0.0f;
+    for (int e = 0; e < cnt; ++e) {
+        if ((first >> e) & 1u) {
+            gam = __fadd_rn(gam, part);
+            part = 0.0f;
+        }
+        const int32_t nbe = __ldg(a.nbr + at + e);
+        float sp = 1.0f;
+        if (nbe >= 0) sp = a.spin[static_cast<int64_t>(nbe) * a.ld + chain] ? 1.0f : -1.0f;
+        part = __fmaf_rn(sp, __ldg(a.w + at + e), part);
+    }
+    return __fadd_rn(gam, part);
+}
+// d = 2^24 (u - p) from the looked-up field and the approximate sigmoid.
+__device__ __forceinline__ float split_screen(const float* tab, uint32_t ia, uint32_t ib, uint32_t r) {
+    const float gamma = tab[ia] + tab[256 + ib];
+    float ex, p24;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));
+    return __uint2float_rn(r >> 8) - p24;
+}
+template <bool ACC>
+__device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, int node, int64_t srow) {
+    const int lane = threadIdx.x & 31;
+    const uint4* src = reinterpret_cast<const uint4*>(a.split_tab + srow * SPLIT_TAB);
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(tab)[lane + 32 * k] = __ldg(src + lane + 32 * k);
+    const float margin = __ldg(a.split_margin + srow);
+    const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
+    const uint32_t tails = __ballot_sync(0xffffffffu, nb >= 0);
+    // lane j: the neighbour whose spin is bit j of the configuration (the j-th entry with a tail)
+    const uint32_t src_lane = __fns(tails, 0, lane + 1);
+    int32_t tnb = __shfl_sync(0xffffffffu, nb, static_cast<int>(src_lane & 31u));
+    if (src_lane > 31u) tnb = -1;
+    uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+    int32_t my_row = -1, row1 = -1;
+    uint32_t own = 0, mine = 0, ones_total = 0;
+    if (ACC) {
+        my_row = __ldg(a.m2_row + static_cast<int64_t>(node) * SEQ_MAX + lane);
+        row1 = __ldg(a.m1_row + node);
+        own = __ballot_sync(0xffffffffu, my_row >= 0);
+    }
+    __syncwarp();
+    for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {  // the observer's counters hold 15 passes
+    const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
+    SliceCounter cnt_lo, cnt_hi;  // disagreements of the new spin with neighbours 0..7 and 8..15, bit-sliced
+    for (int base = seg; base < seg_end; base += 32) {  // every lane runs every pass: the broadcasts are warp-wide
+        const int ch = base + lane;
+        const bool live = ch < a.n_chunks;
+        uint32_t cfg[2][4];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int32_t nbj = __shfl_sync(0xffffffffu, tnb, 8 * h + j);
+                v[j] = make_uint4(0, 0, 0, 0);
+                if (nbj >= 0 && live) v[j] = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nbj) * a.ld) + ch);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) cfg[h][q] = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                cfg[h][0] += v[j].x << j;
+                cfg[h][1] += v[j].y << j;
+                cfg[h][2] += v[j].z << j;
+                cfg[h][3] += v[j].w << j;
+            }
+        }
+        uint32_t o[4];
+        float nearest = 16777216.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+            const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+            o[q] = 0;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float d = split_screen(tab, (cfg[0][q] >> (8 * c)) & 0xffu, (cfg[1][q] >> (8 * c)) & 0xffu, rr[c]);
+                nearest = fminf(nearest, fabsf(d));
+                o[q] |= (__float_as_uint(d) >> 31) << (8 * c);
+            }
+        }
+        if (live && nearest <= margin) {
+#pragma unroll 1
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float d = split_screen(tab, (cfg[0][q] >> (8 * c)) & 0xffu, (cfg[1][q] >> (8 * c)) & 0xffu, rr[c]);
+                    if (fabsf(d) <= margin) {
+                        const float gamma = exact_seq_gamma(a, node, 16 * static_cast<int64_t>(ch) + 4 * q + c);
+                        o[q] = (o[q] & ~(1u << (8 * c))) | ((exact_spin_draw(gamma, rr[c]) ? 1u : 0u) << (8 * c));
+                    }
+                }
+            }
+        }
+        if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+        if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
+            uint32_t dl[4], dh[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                dl[q] = cfg[0][q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
+                dh[q] = cfg[1][q] ^ (o[q] * 255u);
+            }
+            if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {  // ragged last chunk or an idle lane: drop chains that do not exist
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint32_t vm = live ? valid_mask(a.n_chains, ch, q) : 0u;
+                    dl[q] &= vm;
+                    dh[q] &= vm;
+                    o[q] &= vm;
+                }
+            }
+            cnt_lo.add4(dl[0], dl[1], dl[2], dl[3]);
+            cnt_hi.add4(dh[0], dh[1], dh[2], dh[3]);
+            ones_total += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
+        }
+    }
+    if (ACC) {
+        for (uint32_t left = own; left; left &= left - 1) {  // uniform over the warp
+            const int e = __ffs(left) - 1;
+            const int rank = __popc(tails & ((1u << e) - 1u));  // the entry's bit in the configuration
+            const uint32_t t = __reduce_add_sync(0xffffffffu, rank < 8 ? cnt_lo.total(rank) : cnt_hi.total(rank - 8));
+            if (lane == e) mine += t;
+        }
+    }
+    }
+    if (ACC) {
+        if (my_row >= 0) a.sums[my_row] += a.n_chains - 2ll * mine;
+        if (row1 >= 0) {
+            ones_total = __reduce_add_sync(0xffffffffu, ones_total);
+            if (lane == 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
+        }
+    }
+}
+// A sequential-sum node by whichever of the two routes its block prepared for it.
+template <bool ACC>
+__device__ __forceinline__ void seq_or_split_update(const SeqArgs& a, float* tab, int node) {
+    const int32_t srow = a.split_row ? __ldg(a.split_row + node) : -1;
+    if (srow >= 0) split_node_update<ACC>(a, tab, node, srow);
+    else seq_node_update<ACC>(a, node);
+}
 template <bool ACC>
 __global__ void __launch_bounds__(256, 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
-    for (int node = take_node(a); node >= 0; node = take_node(a)) seq_node_update<ACC>(a, node);
+    __shared__ float s_tab[8][SPLIT_TAB];
+    for (int node = take_node(a); node >= 0; node = take_node(a)) seq_or_split_update<ACC>(a, s_tab[threadIdx.x >> 5], node);
 }
 
 // Blocks that mix the two kinds of node: those with at most 8 neighbour slots take the threshold-table update, the
@@ -823,11 +1015,11 @@ struct HybridArgs {
 };
 template <bool ACC>
 __global__ void __launch_bounds__(256, 4) k_spin_hybrid(const __grid_constant__ HybridArgs a) {
-    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    __shared__ uint32_t s_tab[8][SPLIT_TAB];  // a warp's threshold table (256 words) or its two field tables (512 floats)
     for (int node = take_node(a.seq); node >= 0; node = take_node(a.seq)) {
         const int32_t row = __ldg(a.lut_row + node);
-        if (row >= 0) lut_node_update<ACC, false>(a.lut, s_lut[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
-        else seq_node_update<ACC>(a.seq, node);
+        if (row >= 0) lut_node_update<ACC, false>(a.lut, s_tab[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
+        else seq_or_split_update<ACC>(a.seq, reinterpret_cast<float*>(s_tab[threadIdx.x >> 5]), node);
     }
 }
 
