@@ -407,11 +407,12 @@ def test_hub_nodes_continue_in_overflow_rows(T, O):
         assert np.array_equal(gm.read(t)[0], om.read(t)[0])
 
 
-@pytest.mark.parametrize("degree,chains,extra", [(12, 300, 0.0), (16, 1040, 0.0), (10, 4100, 0.0), (12, 300, 2.0 ** 25), (14, 530, 300000.0)])
+@pytest.mark.parametrize("degree,chains,extra", [(12, 300, 0.0), (16, 1040, 0.0), (10, 4100, 0.0), (12, 300, 2.0 ** 25), (14, 530, 300000.0),
+                                                 (17, 1040, 0.0), (24, 520, 0.0), (31, 300, 2.0 ** 25), (20, 1040, 300000.0)])
 def test_split_field_tables_match_oracle(T, O, degree, chains, extra):
-    """Sequential-sum nodes with at most 16 neighbour entries, 256 chains or more: the field comes from two 256-entry
-    tables and only draws close to the probability take the canonical sum.  `extra` widens that window: 0 = the derived
-    bound, 2^25 = every draw through the exact route, 3e5 (2 % of the unit interval) = a mixture."""
+    """Sequential-sum nodes with at most 32 neighbour entries, 256 chains or more: the field comes from two (up to 16
+    neighbours) or four 256-entry tables and only draws close to the probability take the canonical sum.  `extra` widens
+    that window: 0 = the derived bound, 2^25 = every draw through the exact route, 3e5 (2 % of the unit interval) = a mixture."""
     before = T.lib().thrml_debug_split_margin(extra)
     try:
         desc, info = M.ising_random_graph(T, 260, degree, 300 + degree, w_sigma=0.4, bias_sigma=0.3)

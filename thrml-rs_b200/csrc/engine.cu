@@ -53,8 +53,9 @@ struct BlockProg {
     int64_t seq_rows = 0;
     std::vector<char> h_hub;                             // kernels 4 and 6: nodes with overflow rows (not served by the fused observer)
     DevBuf d_seq_order, d_seq_counter;                   // kernels 4 and 6: nodes by decreasing entry count; the launch's work counter
-    DevBuf d_split_row, d_split_nodes, d_split_tab, d_split_margin;  // kernels 4 and 6: split field tables of nodes with at most 16 neighbour entries
+    DevBuf d_split_row, d_split_nodes, d_split_tab, d_split_margin;  // kernels 4 and 6: split field tables of the nodes with one entry row
     int64_t n_split = 0;
+    bool split_wide = false;  // some node has four tables
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
@@ -265,7 +266,7 @@ static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
                                                                                       bp.d_seq_w.as<float>(), bp.d_seq_first.as<uint32_t>(), bp.d_seq_cnt.as<int32_t>());
     CU_TRY(cudaGetLastError());
     if (bp.n_split > 0) {
-        k_build_split<<<static_cast<unsigned>(bp.n_split), 256, 0, p->ctx->stream>>>(bp.d_split_nodes.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(),
+        k_build_split<<<static_cast<unsigned>(bp.n_split), 256, 0, p->ctx->stream>>>(bp.d_split_nodes.as<int32_t>(), bp.d_split_row.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(),
                                                                                     bp.d_seq_cnt.as<int32_t>(), bp.d_split_tab.as<float>(), bp.d_split_margin.as<float>(), g_split_extra_margin);
         CU_TRY(cudaGetLastError());
     }
@@ -455,23 +456,27 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                             }
                     }
                 }
-                // sequential-sum nodes with at most 16 neighbour entries (one entry row) look their field up in two tables
+                // sequential-sum nodes with one entry row look their field up in two (at most 16 neighbours) or four tables
                 {
                     std::vector<int32_t> split_row(static_cast<size_t>(bp.n), -1), split_nodes;
+                    int64_t tables = 0;
                     for (int64_t i2 = 0; i2 < bp.n; ++i2) {
                         if (bp.h_hub[i2] || (bp.kernel == 6 && lut_row[i2] >= 0)) continue;
                         int deg = 0;
                         for (int e = 0; e < SEQ_MAX; ++e) deg += bp.h_nbr[static_cast<size_t>(i2) * SEQ_MAX + e] >= 0 ? 1 : 0;
-                        if (deg > SPLIT_BITS) continue;
-                        split_row[i2] = static_cast<int32_t>(split_nodes.size());
+                        if (deg > SPLIT_BITS || tables + 4 >= (int64_t(1) << 30)) continue;
+                        const int groups = deg > 16 ? 4 : 2;
+                        split_row[i2] = static_cast<int32_t>(2 * tables + (groups == 4 ? 1 : 0));
                         split_nodes.push_back(static_cast<int32_t>(i2));
+                        tables += groups;
+                        if (groups == 4) bp.split_wide = true;
                     }
-                    if (!split_nodes.empty() && split_nodes.size() * SPLIT_TAB * 4 <= (size_t(8) << 30)) {
+                    if (!split_nodes.empty() && static_cast<size_t>(tables) * 1024 <= (size_t(8) << 30)) {
                         bp.n_split = static_cast<int64_t>(split_nodes.size());
                         if (int32_t rc = upload(bp.d_split_row, split_row.data(), split_row.size() * 4, ctx->stream)) return rc;
                         if (int32_t rc = upload(bp.d_split_nodes, split_nodes.data(), split_nodes.size() * 4, ctx->stream)) return rc;
-                        if (int32_t rc = bp.d_split_tab.alloc(static_cast<size_t>(bp.n_split) * SPLIT_TAB * 4)) return rc;
-                        if (int32_t rc = bp.d_split_margin.alloc(static_cast<size_t>(bp.n_split) * 4)) return rc;
+                        if (int32_t rc = bp.d_split_tab.alloc(static_cast<size_t>(tables) * 1024)) return rc;
+                        if (int32_t rc = bp.d_split_margin.alloc(static_cast<size_t>(bp.n) * 4)) return rc;
                         if (int32_t rc = rebuild_seq(p.get(), bp)) return rc;
                     }
                 }
@@ -1028,9 +1033,12 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
             a.lut.m1_row = a.seq.m1_row = acc->fused[block]->m1.as<int32_t>();
             a.lut.m2_row = a.seq.m2_row = acc->fused[block]->m2.as<int32_t>();
             a.lut.sums = a.seq.sums = acc->d_sums.as<long long>();
-            k_spin_hybrid<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            if (bp.split_wide) k_spin_hybrid<true, true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            else k_spin_hybrid<true, false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else if (bp.split_wide) {
+            k_spin_hybrid<false, true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         } else {
-            k_spin_hybrid<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            k_spin_hybrid<false, false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         }
         CU_TRY(cudaGetLastError());
         return THRML_OK;
@@ -1051,9 +1059,12 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
             a.m1_row = acc->fused[block]->m1.as<int32_t>();
             a.m2_row = acc->fused[block]->m2.as<int32_t>();
             a.sums = acc->d_sums.as<long long>();
-            k_spin_seq<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            if (bp.split_wide) k_spin_seq<true, true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            else k_spin_seq<true, false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        } else if (bp.split_wide) {
+            k_spin_seq<false, true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         } else {
-            k_spin_seq<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+            k_spin_seq<false, false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
         }
         CU_TRY(cudaGetLastError());
         return THRML_OK;

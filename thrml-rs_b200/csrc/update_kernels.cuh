@@ -810,42 +810,52 @@ __device__ __forceinline__ void seq_node_update(const SeqArgs& a, int node) {
         if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
     }
 }
-// Split field tables for sequential-sum nodes with at most 16 neighbour entries (one entry row): the field is looked
-// up as A[configuration of neighbours 0..7] + B[configuration of neighbours 8..15] instead of being added entry by
-// entry.  A (which also carries the entries without a tail) and B are the real partial sums rounded once, so the
-// looked-up field differs from the canonical sequential f32 sum by a few rounding errors of the summed |w| at most.
-// The draw is decided from it only when u is farther from the probability than that bound allows (split_margin, in
-// units of 2^-24: the approximate sigmoid's 67.2 plus the field bound pushed through the sigmoid's steepest slope);
-// the other draws — a few in 10^5 — take the canonical sum (exact_seq_gamma) and the exact rule, so the states are
-// the bits of k_spin_generic.
-constexpr int SPLIT_BITS = 16;
-constexpr int SPLIT_TAB = 512;  // floats per node: A[256] then B[256]
-constexpr int SPLIT_MIN_CHUNKS = 16;  // states with fewer than 256 chains would read 2 KiB of tables per node for a handful of lookups
-__global__ void __launch_bounds__(256) k_build_split(const int32_t* split_nodes, const int32_t* ent_nbr, const float* ent_w, const int32_t* ent_cnt,
-                                                     float* tab, float* margin, float extra_margin) {
-    const int64_t row = blockIdx.x;
-    const int node = split_nodes[row];
+// Split field tables for sequential-sum nodes with one entry row (at most 32 neighbour entries): the field is looked
+// up as T0[configuration of neighbours 0..7] + T1[neighbours 8..15] (+ T2[16..23] + T3[24..31] for a node with more than
+// 16 neighbours) instead of being added entry by entry.  The tables (T0 also carries the entries without a tail) are
+// the real partial sums rounded once, so the looked-up field differs from the canonical sequential f32 sum by a few
+// rounding errors of the summed |w| at most.  The draw is decided from it only when u is farther from the probability
+// than that bound allows (split_margin, in units of 2^-24: the approximate sigmoid's 67.2 plus the field bound pushed
+// through the sigmoid's steepest slope); the other draws — a few in 10^5 — take the canonical sum (exact_seq_gamma)
+// and the exact rule, so the states are the bits of k_spin_generic.
+// split_row[node] = 2 * (first 256-entry table of the node) + (1 if the node has four tables, 0 if two), -1 = none.
+constexpr int SPLIT_BITS = 32;
+constexpr int SPLIT_TAB = 1024;  // floats a warp stages at most: four tables of 256
+constexpr int SPLIT_MIN_CHUNKS = 16;  // states with fewer than 256 chains would read kilobytes of tables per node for a handful of lookups
+__global__ void __launch_bounds__(256) k_build_split(const int32_t* split_nodes, const int32_t* split_row, const int32_t* ent_nbr, const float* ent_w,
+                                                     const int32_t* ent_cnt, float* tab, float* margin, float extra_margin) {
+    const int node = split_nodes[blockIdx.x];
+    const int32_t code = split_row[node];
+    const int64_t at = static_cast<int64_t>(code >> 1) * 256;
+    const int groups = (code & 1) ? 4 : 2;
     const int c = threadIdx.x;  // configuration byte
     const int cnt = ent_cnt[node];
-    double A = 0.0, B = 0.0, mag = 0.0;
+    double S0 = 0.0, S1 = 0.0, S2 = 0.0, S3 = 0.0, mag = 0.0;
     int rank = 0;
     for (int e = 0; e < cnt; ++e) {
         const double w = static_cast<double>(ent_w[static_cast<int64_t>(node) * SEQ_MAX + e]);
         mag += fabs(w);
         if (ent_nbr[static_cast<int64_t>(node) * SEQ_MAX + e] < 0) {
-            A += w;
+            S0 += w;
         } else {
-            if (rank < 8) A += ((c >> rank) & 1) ? w : -w;
-            else B += ((c >> (rank - 8)) & 1) ? w : -w;
+            const double t = ((c >> (rank & 7)) & 1) ? w : -w;
+            if (rank < 8) S0 += t;
+            else if (rank < 16) S1 += t;
+            else if (rank < 24) S2 += t;
+            else S3 += t;
             ++rank;
         }
     }
-    tab[row * SPLIT_TAB + c] = static_cast<float>(A);
-    tab[row * SPLIT_TAB + 256 + c] = static_cast<float>(B);
-    // |looked-up field - canonical field| <= (2 cnt + 4) 2^-24 sum|w| (one rounding per add of either route, table
+    tab[at + c] = static_cast<float>(S0);
+    tab[at + 256 + c] = static_cast<float>(S1);
+    if (groups == 4) {
+        tab[at + 512 + c] = static_cast<float>(S2);
+        tab[at + 768 + c] = static_cast<float>(S3);
+    }
+    // |looked-up field - canonical field| <= (2 cnt + 6) 2^-24 sum|w| (one rounding per add of either route, table
     // closings included); times 2 (the sigmoid's argument is twice the field) times 1/4 (its steepest slope) times 2^24,
     // with a tenth on top for the second-order terms.
-    if (c == 0) margin[row] = 67.2f + 1.0f + static_cast<float>(0.55 * (2.0 * cnt + 4.0) * mag) + extra_margin;
+    if (c == 0) margin[node] = 67.2f + 1.0f + static_cast<float>(0.55 * (2.0 * cnt + 6.0) * mag) + extra_margin;
 }
 // The canonical field of one node and chain: per table from zero, entries left to right, tables left to right.
 __device__ __noinline__ float exact_seq_gamma(const SeqArgs& a, int node, int64_t chain) {
@@ -866,21 +876,23 @@ __device__ __noinline__ float exact_seq_gamma(const SeqArgs& a, int node, int64_
     return __fadd_rn(gam, part);
 }
 // d = 2^24 (u - p) from the looked-up field and the approximate sigmoid.
-__device__ __forceinline__ float split_screen(const float* tab, uint32_t ia, uint32_t ib, uint32_t r) {
-    const float gamma = tab[ia] + tab[256 + ib];
+template <int NH>
+__device__ __forceinline__ float split_screen(const float* tab, const uint32_t (&cfg)[NH][4], int q, int c, uint32_t r) {
+    float gamma = tab[(cfg[0][q] >> (8 * c)) & 0xffu] + tab[256 + ((cfg[1][q] >> (8 * c)) & 0xffu)];
+    if (NH == 4) gamma += tab[512 + ((cfg[2][q] >> (8 * c)) & 0xffu)] + tab[768 + ((cfg[3][q] >> (8 * c)) & 0xffu)];
     float ex, p24;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));
     return __uint2float_rn(r >> 8) - p24;
 }
-template <bool ACC>
-__device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, int node, int64_t srow) {
+template <bool ACC, int NH>
+__device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, int node, int64_t first_table) {
     const int lane = threadIdx.x & 31;
-    const uint4* src = reinterpret_cast<const uint4*>(a.split_tab + srow * SPLIT_TAB);
+    const uint4* src = reinterpret_cast<const uint4*>(a.split_tab + first_table * 256);
     __syncwarp();
 #pragma unroll
-    for (int k = 0; k < 4; ++k) reinterpret_cast<uint4*>(tab)[lane + 32 * k] = __ldg(src + lane + 32 * k);
-    const float margin = __ldg(a.split_margin + srow);
+    for (int k = 0; k < 2 * NH; ++k) reinterpret_cast<uint4*>(tab)[lane + 32 * k] = __ldg(src + lane + 32 * k);
+    const float margin = __ldg(a.split_margin + node);
     const int32_t nb = __ldg(a.nbr + static_cast<int64_t>(node) * SEQ_MAX + lane);
     const uint32_t tails = __ballot_sync(0xffffffffu, nb >= 0);
     // lane j: the neighbour whose spin is bit j of the configuration (the j-th entry with a tail)
@@ -898,13 +910,13 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
     __syncwarp();
     for (int seg = 0; seg < a.n_chunks; seg += 32 * ACC_SEGMENT_PASSES) {  // the observer's counters hold 15 passes
     const int seg_end = min(a.n_chunks, seg + 32 * ACC_SEGMENT_PASSES);
-    SliceCounter cnt_lo, cnt_hi;  // disagreements of the new spin with neighbours 0..7 and 8..15, bit-sliced
+    SliceCounter c0, c1, c2, c3;  // disagreements of the new spin with neighbours 0..7, 8..15, (16..23, 24..31), bit-sliced
     for (int base = seg; base < seg_end; base += 32) {  // every lane runs every pass: the broadcasts are warp-wide
         const int ch = base + lane;
         const bool live = ch < a.n_chunks;
-        uint32_t cfg[2][4];
+        uint32_t cfg[NH][4];
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int h = 0; h < NH; ++h) {
             uint4 v[8];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -923,7 +935,7 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
             }
         }
         uint32_t o[4];
-        float nearest = 16777216.0f;
+        bool close = false;  // some draw of this pass is inside the window (or not a number: non-finite weights)
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
@@ -931,20 +943,20 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
             o[q] = 0;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const float d = split_screen(tab, (cfg[0][q] >> (8 * c)) & 0xffu, (cfg[1][q] >> (8 * c)) & 0xffu, rr[c]);
-                nearest = fminf(nearest, fabsf(d));
+                const float d = split_screen<NH>(tab, cfg, q, c, rr[c]);
+                close |= !(fabsf(d) > margin);
                 o[q] |= (__float_as_uint(d) >> 31) << (8 * c);
             }
         }
-        if (live && nearest <= margin) {
+        if (live && close) {
 #pragma unroll 1
             for (int q = 0; q < 4; ++q) {
                 const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
                 const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    const float d = split_screen(tab, (cfg[0][q] >> (8 * c)) & 0xffu, (cfg[1][q] >> (8 * c)) & 0xffu, rr[c]);
-                    if (fabsf(d) <= margin) {
+                    const float d = split_screen<NH>(tab, cfg, q, c, rr[c]);
+                    if (!(fabsf(d) > margin)) {
                         const float gamma = exact_seq_gamma(a, node, 16 * static_cast<int64_t>(ch) + 4 * q + c);
                         o[q] = (o[q] & ~(1u << (8 * c))) | ((exact_spin_draw(gamma, rr[c]) ? 1u : 0u) << (8 * c));
                     }
@@ -953,23 +965,23 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
         }
         if (live) reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
         if (ACC && (own | static_cast<uint32_t>(row1 >= 0))) {
-            uint32_t dl[4], dh[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                dl[q] = cfg[0][q] ^ (o[q] * 255u);  // bit j of a byte: neighbour j differs from the new spin
-                dh[q] = cfg[1][q] ^ (o[q] * 255u);
-            }
             if (16 * static_cast<int64_t>(ch + 1) > a.n_chains) {  // ragged last chunk or an idle lane: drop chains that do not exist
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const uint32_t vm = live ? valid_mask(a.n_chains, ch, q) : 0u;
-                    dl[q] &= vm;
-                    dh[q] &= vm;
                     o[q] &= vm;
+#pragma unroll
+                    for (int h = 0; h < NH; ++h) cfg[h][q] &= vm;
                 }
             }
-            cnt_lo.add4(dl[0], dl[1], dl[2], dl[3]);
-            cnt_hi.add4(dh[0], dh[1], dh[2], dh[3]);
+            const uint32_t f[4] = {o[0] * 255u, o[1] * 255u, o[2] * 255u, o[3] * 255u};
+            // bit j of a byte: neighbour 8 h + j differs from the new spin
+            c0.add4(cfg[0][0] ^ f[0], cfg[0][1] ^ f[1], cfg[0][2] ^ f[2], cfg[0][3] ^ f[3]);
+            c1.add4(cfg[1][0] ^ f[0], cfg[1][1] ^ f[1], cfg[1][2] ^ f[2], cfg[1][3] ^ f[3]);
+            if (NH == 4) {
+                c2.add4(cfg[NH - 2][0] ^ f[0], cfg[NH - 2][1] ^ f[1], cfg[NH - 2][2] ^ f[2], cfg[NH - 2][3] ^ f[3]);
+                c3.add4(cfg[NH - 1][0] ^ f[0], cfg[NH - 1][1] ^ f[1], cfg[NH - 1][2] ^ f[2], cfg[NH - 1][3] ^ f[3]);
+            }
             ones_total += __popc(o[0] + (o[1] << 1) + (o[2] << 2) + (o[3] << 3));
         }
     }
@@ -977,7 +989,9 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
         for (uint32_t left = own; left; left &= left - 1) {  // uniform over the warp
             const int e = __ffs(left) - 1;
             const int rank = __popc(tails & ((1u << e) - 1u));  // the entry's bit in the configuration
-            const uint32_t t = __reduce_add_sync(0xffffffffu, rank < 8 ? cnt_lo.total(rank) : cnt_hi.total(rank - 8));
+            uint32_t mine_here = rank < 8 ? c0.total(rank) : c1.total(rank & 7);
+            if (NH == 4 && rank >= 16) mine_here = rank < 24 ? c2.total(rank & 7) : c3.total(rank & 7);
+            const uint32_t t = __reduce_add_sync(0xffffffffu, mine_here);
             if (lane == e) mine += t;
         }
     }
@@ -991,16 +1005,19 @@ __device__ __forceinline__ void split_node_update(const SeqArgs& a, float* tab, 
     }
 }
 // A sequential-sum node by whichever of the two routes its block prepared for it.
-template <bool ACC>
+// WIDE: the block has nodes with four tables (more than 16 neighbours).  Blocks without them run the instantiation that
+// does not carry that code (fewer spilled registers, half the shared memory).
+template <bool ACC, bool WIDE>
 __device__ __forceinline__ void seq_or_split_update(const SeqArgs& a, float* tab, int node) {
-    const int32_t srow = a.split_row ? __ldg(a.split_row + node) : -1;
-    if (srow >= 0) split_node_update<ACC>(a, tab, node, srow);
-    else seq_node_update<ACC>(a, node);
+    const int32_t code = a.split_row ? __ldg(a.split_row + node) : -1;
+    if (code < 0) seq_node_update<ACC>(a, node);
+    else if (WIDE && (code & 1)) split_node_update<ACC, 4>(a, tab, node, code >> 1);
+    else split_node_update<ACC, 2>(a, tab, node, code >> 1);
 }
-template <bool ACC>
-__global__ void __launch_bounds__(256, 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
-    __shared__ float s_tab[8][SPLIT_TAB];
-    for (int node = take_node(a); node >= 0; node = take_node(a)) seq_or_split_update<ACC>(a, s_tab[threadIdx.x >> 5], node);
+template <bool ACC, bool WIDE>
+__global__ void __launch_bounds__(256, ACC && WIDE ? 3 : 4) k_spin_seq(const __grid_constant__ SeqArgs a) {
+    __shared__ float s_tab[8][WIDE ? SPLIT_TAB : SPLIT_TAB / 2];
+    for (int node = take_node(a); node >= 0; node = take_node(a)) seq_or_split_update<ACC, WIDE>(a, s_tab[threadIdx.x >> 5], node);
 }
 
 // Blocks that mix the two kinds of node: those with at most 8 neighbour slots take the threshold-table update, the
@@ -1013,13 +1030,13 @@ struct HybridArgs {
     SeqArgs seq;
     const int32_t* lut_row;
 };
-template <bool ACC>
-__global__ void __launch_bounds__(256, 4) k_spin_hybrid(const __grid_constant__ HybridArgs a) {
-    __shared__ uint32_t s_tab[8][SPLIT_TAB];  // a warp's threshold table (256 words) or its two field tables (512 floats)
+template <bool ACC, bool WIDE>
+__global__ void __launch_bounds__(256, ACC && WIDE ? 3 : 4) k_spin_hybrid(const __grid_constant__ HybridArgs a) {
+    __shared__ uint32_t s_tab[8][WIDE ? SPLIT_TAB : SPLIT_TAB / 2];  // a warp's threshold table (256 words) or its two or four field tables
     for (int node = take_node(a.seq); node >= 0; node = take_node(a.seq)) {
         const int32_t row = __ldg(a.lut_row + node);
         if (row >= 0) lut_node_update<ACC, false>(a.lut, s_tab[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
-        else seq_or_split_update<ACC>(a.seq, reinterpret_cast<float*>(s_tab[threadIdx.x >> 5]), node);
+        else seq_or_split_update<ACC, WIDE>(a.seq, reinterpret_cast<float*>(s_tab[threadIdx.x >> 5]), node);
     }
 }
 
