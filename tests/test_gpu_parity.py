@@ -408,7 +408,7 @@ def test_hub_nodes_continue_in_overflow_rows(T, O):
 
 
 @pytest.mark.parametrize("degree,chains,extra", [(12, 300, 0.0), (16, 1040, 0.0), (10, 4100, 0.0), (12, 300, 2.0 ** 25), (14, 530, 300000.0),
-                                                 (17, 1040, 0.0), (24, 520, 0.0), (31, 300, 2.0 ** 25), (20, 1040, 300000.0)])
+                                                 (17, 1040, 0.0), (24, 520, 0.0), (31, 300, 2.0 ** 25), (20, 1040, 300000.0), (12, 8100, 0.0), (18, 7700, 0.0)])  # 7700+ chains: two counter segments
 def test_split_field_tables_match_oracle(T, O, degree, chains, extra):
     """Sequential-sum nodes with at most 32 neighbour entries, 256 chains or more: the field comes from two (up to 16
     neighbours) or four 256-entry tables and only draws close to the probability take the canonical sum.  `extra` widens
@@ -445,3 +445,35 @@ def test_split_field_tables_match_oracle(T, O, degree, chains, extra):
     gs.run_blocks(6, 3)
     os2.run_blocks(6, 3)
     assert_states_equal(gs, os2, n_blocks_of(desc))
+
+
+def test_split_tables_with_isolated_and_leaf_nodes(T, O):
+    """Blocks of the sequential-sum kind that also hold nodes with no neighbour at all (a bias only), with one neighbour
+    and with no entry at all (zero bias is still an entry; the leaf's weight is exactly zero in one case): all of them
+    take the table route with mostly empty configuration bytes."""
+    n_core, rng = 240, np.random.default_rng(5)
+    core = M.random_regular_graph(n_core, 12, 77)
+    leaves = np.array([[int(rng.integers(0, n_core)), n_core + 4 + k] for k in range(6)], dtype=np.int64)
+    edges = np.concatenate([np.asarray(core, dtype=np.int64), leaves])
+    edges = np.stack([edges.min(axis=1), edges.max(axis=1)], axis=1)
+    n = n_core + 10  # nodes n_core .. n_core + 3 are isolated
+    colour, n_col = T.greedy_coloring_arrays(n, edges)
+    blocks = [np.flatnonzero(colour == c) for c in range(n_col)]
+    bias = rng.normal(0, 0.4, n).astype(np.float32)
+    bias[n_core] = 0.0
+    Jv = rng.normal(0, 0.4, len(edges)).astype(np.float32)
+    Jv[-1] = 0.0
+    desc = dict(kinds=np.zeros(n, np.int32), free=[(blk, i) for i, blk in enumerate(blocks)], ops=[("add_ising", np.arange(n), bias, edges, Jv, 1.0)])
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, 300, 11)
+    kinds = [prog.block_kernel(b) for b in range(n_col)]
+    assert 4 in kinds and set(kinds) <= {1, 4, 6}
+    gs.run_blocks(9, 10)
+    os_.run_blocks(9, 10)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    spec = moment_spec(desc, dict(n=n, edges=edges))
+    gm, om = T.Moments(prog, spec, True), O.Moments(ob, spec, True)
+    gs.sample_with_observation(3, 1, 4, 2, moments=gm)
+    os_.sample_with_observation(3, 1, 4, 2, moments=om)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    for t in range(2):
+        assert np.array_equal(gm.read(t)[0], om.read(t)[0])
