@@ -10,6 +10,7 @@
 // the sampled states equal the explicit program's bit for bit, without its [N,6,K*K] weight tensors (2.5 GB per block at
 // 128^3, K = 10).  Node index = (x*ny + y)*nz + z; state = one byte per node and chain, chains innermost.
 #include <algorithm>
+#include <cmath>
 #include <memory>
 #include <vector>
 
@@ -29,6 +30,8 @@ struct PottsArgs {
     int32_t nx, ny, nz, K, colour;
     int64_t ld, n_chains;
     uint32_t chain_word0, k0, k1;
+    const float* pair_tables;  // [3][K][K][K]: P_d[c][s_plus][s_minus] = T_d[c][s_plus] + T_d[s_minus][c] rounded once (PAIR kernels only)
+    float table_mag;           // 2 (max|T_x| + max|T_y| + max|T_z|): bound of the six table terms of a field
 };
 
 // Exact Gumbel-argmax of one chain (byte `sh / 8` of the neighbour words): the rule of softmax.rs:60-97 with the
@@ -57,16 +60,23 @@ __device__ __noinline__ uint32_t potts_exact_argmax(const float* s_tab, const fl
 
 // KT > 0: the category count as a compile-time constant.  The category loop then unrolls completely, which turns the
 // table offsets cat * K and the choice of the Philox word into immediates (the integer pipe is the busy one here).
-template <int KT>
+// PAIR: the screen reads one pre-added entry per direction, P_d[c][s_plus][s_minus], instead of two table entries: three
+// lookups and adds per category and chain instead of six.  The re-associated field differs from the canonical one by at
+// most 12 roundings of (|unary| + table_mag), which widens the window inside which the exact rule decides.
+// CTAs stride over the colour's nodes (eight per pass), so the tables are staged once per CTA.
+template <int KT, bool PAIR>
 __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
-    extern __shared__ float s_tab[];  // [3][K][K]
+    extern __shared__ float s_tab[];  // [3][K][K], then (PAIR) [3][K][K][K]
     for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[i] = a.tables[i];
+    if (PAIR)
+        for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[3 * a.K * a.K + i] = a.pair_tables[i];
     __syncthreads();
     const int quad = blockIdx.y * 32 + threadIdx.x;
-    const int64_t in_block = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;  // index among the nodes of this colour
     const int half_z = a.nz >> 1;
     const int64_t n_block = static_cast<int64_t>(a.nx) * a.ny * half_z;
-    if (in_block >= n_block || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    if (4 * static_cast<int64_t>(quad) >= a.ld) return;
+    // index among the nodes of this colour
+    for (int64_t in_block = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y; in_block < n_block; in_block += static_cast<int64_t>(gridDim.x) * 8) {
     const int zz = static_cast<int>(in_block % half_z);
     const int y = static_cast<int>((in_block / half_z) % a.ny);
     const int x = static_cast<int>(in_block / (static_cast<int64_t>(half_z) * a.ny));
@@ -101,12 +111,29 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     float best[4], second[4];
     uint32_t arg[4] = {0, 0, 0, 0};
     U4 r[4];
+    uint32_t ix[3][4];  // PAIR: s_plus * K + s_minus per direction and chain
+    if (PAIR) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            ix[0][c] = ((px >> (8 * c)) & 0xffu) * K + ((mx >> (8 * c)) & 0xffu);
+            ix[1][c] = ((py >> (8 * c)) & 0xffu) * K + ((my >> (8 * c)) & 0xffu);
+            ix[2][c] = ((pz >> (8 * c)) & 0xffu) * K + ((mz >> (8 * c)) & 0xffu);
+        }
+    }
+    float unmax = 0.0f;
 #pragma unroll
     for (int cat = 0; cat < (KT > 0 ? KT : K); ++cat) {
         const float un = __ldg(a.unary + node * K + cat);
+        if (PAIR) unmax = fmaxf(unmax, fabsf(un));
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float th = theta(cat, 8 * c, un);
+            float th;
+            if (PAIR) {
+                const float* pt = s_tab + 3 * KK + cat * KK;
+                th = ((un + pt[ix[0][c]]) + pt[K * KK + ix[1][c]]) + pt[2 * K * KK + ix[2][c]];
+            } else {
+                th = theta(cat, 8 * c, un);
+            }
             if ((cat & 3) == 0) r[c] = noise(c, cat);
             const float u = u23_open(pick(r[c], cat & 3));
             const float w = 1.0f - u;
@@ -120,9 +147,11 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
             }
         }
     }
+    // each PAIR score is off by at most 12 x 2^-24 (|unary| + table_mag) more; twice that for leader and runner-up, and a third on top
+    const float margin = PAIR ? fmaf(2.0e-6f, unmax + a.table_mag, MARGIN) : MARGIN;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
-        if (!(best[c] - second[c] > MARGIN))
+        if (!(best[c] - second[c] > margin))
             arg[c] = potts_exact_argmax(s_tab, a.unary + node * K, K, 8 * c, px, mx, py, my, pz, mz, static_cast<uint32_t>(in_block),
                                         4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1);
     uint32_t out = 0;
@@ -130,6 +159,7 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     for (int c = 0; c < 4; ++c)
         if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
     *reinterpret_cast<uint32_t*>(a.state + node * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+    }
 }
 
 __global__ void __launch_bounds__(256) k_potts_randomize(uint8_t* state, int32_t nx, int32_t ny, int32_t nz, int32_t K, int32_t colour, int64_t ld, int64_t n_chains,
@@ -218,7 +248,9 @@ struct thrml_potts {
     int device = 0;
     int32_t nx = 0, ny = 0, nz = 0, K = 0;
     int64_t n = 0, n_chains = 0, chain_offset = 0, ld = 0, n_obs = 0;
-    PBuf state, tables, unary, counts, scratch;
+    PBuf state, tables, pair_tables, unary, counts, scratch;
+    float table_mag = 0.0f;
+    bool pair = false;  // pre-added direction tables exist (category counts with a compile-time kernel and 3 K^3 floats of shared memory to spare)
 };
 
 extern "C" {
@@ -243,12 +275,30 @@ int32_t thrml_potts_create(thrml_ctx* ctx, int32_t nx, int32_t ny, int32_t nz, i
     if (int32_t rc = palloc(P->state, static_cast<size_t>(n) * P->ld)) return rc;
     if (int32_t rc = palloc(P->tables, tab.size() * 4)) return rc;
     if (int32_t rc = palloc(P->unary, un.size() * 4)) return rc;
+    std::vector<float> pair;
+    for (int d = 0; d < 3; ++d) {
+        float m = 0.0f;
+        for (int i = 0; i < K * K; ++i) m = std::max(m, std::fabs(tab[static_cast<size_t>(d) * K * K + i]));
+        P->table_mag += 2.0f * m;
+    }
+    P->pair = (K == 3 || K == 4 || K == 5 || K == 8 || K == 10) && std::isfinite(P->table_mag);
+    if (P->pair) {
+        pair.resize(static_cast<size_t>(3) * K * K * K);
+        for (int d = 0; d < 3; ++d)
+            for (int c = 0; c < K; ++c)
+                for (int sp = 0; sp < K; ++sp)
+                    for (int sm = 0; sm < K; ++sm)
+                        pair[((static_cast<size_t>(d) * K + c) * K + sp) * K + sm] =
+                            static_cast<float>(static_cast<double>(tab[(static_cast<size_t>(d) * K + c) * K + sp]) + static_cast<double>(tab[(static_cast<size_t>(d) * K + sm) * K + c]));
+        if (int32_t rc = palloc(P->pair_tables, pair.size() * 4)) return rc;
+    }
     if (int32_t rc = palloc(P->counts, static_cast<size_t>(n) * K * 4)) return rc;
     cudaStream_t st = ctx->stream;
     CU_TRY(cudaMemsetAsync(P->state.p, 0, P->state.bytes, st));
     CU_TRY(cudaMemsetAsync(P->counts.p, 0, P->counts.bytes, st));
     CU_TRY(cudaMemcpyAsync(P->tables.p, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, st));
     CU_TRY(cudaMemcpyAsync(P->unary.p, un.data(), un.size() * 4, cudaMemcpyHostToDevice, st));
+    if (P->pair) CU_TRY(cudaMemcpyAsync(P->pair_tables.p, pair.data(), pair.size() * 4, cudaMemcpyHostToDevice, st));
     CU_TRY(cudaStreamSynchronize(st));
     *out = P.release();
     return THRML_OK;
@@ -279,15 +329,21 @@ int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
     CU_TRY(cudaSetDevice(P->device));
     PottsArgs a{static_cast<uint8_t*>(P->state.p), static_cast<const float*>(P->tables.p), static_cast<const float*>(P->unary.p), P->nx, P->ny, P->nz, P->K, colour, P->ld, P->n_chains,
                 static_cast<uint32_t>(P->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
-    const dim3 grid = potts_grid(P), block(32, 8);
-    const size_t smem = static_cast<size_t>(3) * P->K * P->K * 4;
-    switch (P->K) {
-        case 3: k_potts_update<3><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 4: k_potts_update<4><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 5: k_potts_update<5><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 8: k_potts_update<8><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 10: k_potts_update<10><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        default: k_potts_update<0><<<grid, block, smem, P->ctx->stream>>>(a); break;
+    a.pair_tables = static_cast<const float*>(P->pair_tables.p);
+    a.table_mag = P->table_mag;
+    // CTAs stride over the nodes: about four waves of resident CTAs (three per SM), so each stages the tables a few times at most
+    dim3 grid = potts_grid(P);
+    const dim3 block(32, 8);
+    const unsigned resident = static_cast<unsigned>(P->ctx->sm_count) * 3u * 4u;
+    grid.x = std::min(grid.x, std::max(1u, resident / grid.y));
+    const size_t smem = static_cast<size_t>(3) * P->K * P->K * (P->pair ? 1 + P->K : 1) * 4;
+    switch (P->pair ? P->K : 0) {
+        case 3: k_potts_update<3, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 4: k_potts_update<4, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 5: k_potts_update<5, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 8: k_potts_update<8, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 10: k_potts_update<10, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        default: k_potts_update<0, false><<<grid, block, smem, P->ctx->stream>>>(a); break;
     }
     CU_TRY(cudaGetLastError());
     return THRML_OK;
