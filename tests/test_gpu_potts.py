@@ -25,12 +25,23 @@ def explicit_potts(nx, ny, nz, K, tables, unary, beta):
 @pytest.mark.parametrize("shape,K,chains", [((4, 4, 4), 3, 8), ((2, 4, 6), 10, 37), ((6, 2, 4), 5, 64), ((4, 2, 4), 7, 20),
                                             ((4, 4, 4), 5, 8192)])  # the last: millions of draws, hundreds of near-ties sent to the exact path
 def test_potts_lattice_matches_explicit_program(T, O, shape, K, chains):
+    check_against_explicit_program(T, O, shape, K, chains, 0.3, 0.1)
+
+
+@pytest.mark.parametrize("shape,K,chains,sigma,usigma", [((2, 4, 6), 10, 4096, 3.0, 1.0), ((4, 4, 2), 8, 4096, 1.0, 4.0), ((2, 2, 4), 10, 4096, 30.0, 0.1)])
+def test_potts_strong_couplings(T, O, shape, K, chains, sigma, usigma):
+    """Large table and unary magnitudes: the pre-added direction tables round differently from the canonical six adds by
+    an amount that grows with the magnitudes, and the near-tie window has to grow with it."""
+    check_against_explicit_program(T, O, shape, K, chains, sigma, usigma)
+
+
+def check_against_explicit_program(T, O, shape, K, chains, sigma, usigma):
     from thrml_rs_b200 import potts
     nx, ny, nz = shape
     n = nx * ny * nz
     rng = np.random.default_rng(n + K)
-    tables = rng.normal(0, 0.3, (3, K, K)).astype(np.float32)
-    unary = rng.normal(0, 0.1, (n, K)).astype(np.float32)
+    tables = rng.normal(0, sigma, (3, K, K)).astype(np.float32)
+    unary = rng.normal(0, usigma, (n, K)).astype(np.float32)
     beta = 0.8
     desc, blocks = explicit_potts(nx, ny, nz, K, tables, unary, beta)
     om = M.fill(O.Model(desc["kinds"]), desc)
