@@ -1095,7 +1095,12 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     if (bp.is_cat) {
         if (fields) k_cat_generic<2><<<grid, blk, 0, st>>>(a);
         else if (inj) k_cat_generic<1><<<grid, blk, 0, st>>>(a);
-        else if (bp.kernel == 5) k_cat_fast<<<grid, blk, 0, st>>>(a);
+        else if (bp.kernel == 5) {
+            // weight rows staged in shared memory when CAT_SLOTS x K x K floats per node of the CTA fit in 48 KiB
+            const size_t smem = static_cast<size_t>(blk.y) * CAT_SLOTS * bp.kind * bp.kind * 4;
+            if (smem <= 48 * 1024 && 32 % blk.x == 0) k_cat_fast<true><<<grid, blk, smem, st>>>(a);
+            else k_cat_fast<false><<<grid, blk, 0, st>>>(a);
+        }
         else k_cat_generic<0><<<grid, blk, 0, st>>>(a);
     } else {
         if (fields) k_spin_generic<2><<<grid, blk, 0, st>>>(a);

@@ -231,26 +231,34 @@ __device__ __noinline__ uint32_t cat_exact_argmax(const UpdateArgs& a, int node,
 //    (per table from zero, tables left to right);
 //  * the Gumbel noise is screened with the hardware logarithm (k_potts_update documents the bound: each score within
 //    2e-5 of the exact one); a leader less than 6e-5 ahead of the runner-up sends that chain to cat_exact_argmax.
+//  * STAGE: the threads of a node (they share a warp) first copy the node's weight rows into shared memory — K x K floats
+//    per slot, coalesced — so the lookups of the category loop are shared-memory reads instead of dependent global
+//    gathers (the launch picks it when CAT_SLOTS x K x K floats per node of the CTA fit in 48 KiB).
 constexpr int CAT_SLOTS = 8;
+template <bool STAGE>
 __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ UpdateArgs a) {
+    extern __shared__ float s_w[];  // STAGE: [blockDim.y][CAT_SLOTS][K * K]
     const int quad = blockIdx.y * blockDim.x + threadIdx.x;
     const int node = blockIdx.x * blockDim.y + threadIdx.y;
-    if (node >= a.n || 4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const bool valid = node < a.n && 4 * static_cast<int64_t>(quad) < a.ld;
+    const bool walks = STAGE ? node < a.n : valid;  // STAGE: every thread of a live node helps to copy its weights
+    if (!STAGE && !valid) return;
     const int K = a.K;
+    float* mine = s_w + static_cast<size_t>(threadIdx.y) * CAT_SLOTS * K * K;
     uint32_t xw[CAT_SLOTS], sg[CAT_SLOTS];   // neighbour categories (4 chains), sign bits (bit 7 of a byte: the spin-tail product is -1)
     const float* wrow[CAT_SLOTS];            // weights of the slot: [K][K] with a categorical tail, [K] without
     uint32_t opens = 0, tailed = 0;          // bit s: slot s opens a table / has a categorical tail
     int S = 0;
-    for (int t = 0; t < a.n_tabs; ++t) {
+    for (int t = 0; t < (walks ? a.n_tabs : 0); ++t) {
         const DevTable& T = a.tabs[t];
         bool first = true;
         for (int j = 0; j < T.k; ++j) {
             const int64_t flat = static_cast<int64_t>(node) * T.k + j;
             if (!T.active[flat]) continue;
             uint32_t neg = 0;
-            for (int tl = 0; tl < T.n_spin; ++tl) neg ^= ~ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+            for (int tl = 0; tl < (valid ? T.n_spin : 0); ++tl) neg ^= ~ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
             uint32_t x = 0;
-            if (T.n_tails > T.n_spin) {
+            if (valid && T.n_tails > T.n_spin) {
                 x = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
                 x = __vminu4(x, static_cast<uint32_t>(K - 1) * 0x01010101u);  // per-byte clamp, as the generic kernel does
             }
@@ -261,11 +269,20 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
                     sg[s] = (neg & 0x01010101u) << 7;
                     wrow[s] = T.w + flat * T.wdim;
                 }
+            if (STAGE) {  // the node's threads copy the slot's weights: every thread of the node walks the same slots
+                const int len = T.n_tails > T.n_spin ? K * K : K;
+                const float* src = T.w + flat * T.wdim;
+                for (int i = threadIdx.x; i < len; i += blockDim.x) mine[S * K * K + i] = __ldg(src + i);
+            }
             if (first) opens |= 1u << S;
             if (T.n_tails > T.n_spin) tailed |= 1u << S;
             first = false;
             ++S;
         }
+    }
+    if (STAGE) {
+        __syncwarp();  // a node's threads lie in one warp (blockDim.x divides 32)
+        if (!valid) return;
     }
     constexpr float MARGIN = 6e-5f;
     uint32_t out = 0;
@@ -284,8 +301,13 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
             for (int s = 0; s < CAT_SLOTS; ++s) {
                 if (s >= S) break;  // uniform over the threads of a node
                 if (s > 0 && ((opens >> s) & 1u)) { th = __fadd_rn(th, sum); sum = 0.f; }
-                const float* wk = ((tailed >> s) & 1u) ? wrow[s] + cat * K + ((xw[s] >> sh) & 0xffu) : wrow[s] + cat;
-                const uint32_t wb = __float_as_uint(__ldg(wk));
+                uint32_t wb;
+                if (STAGE) {
+                    wb = __float_as_uint(mine[s * K * K + (((tailed >> s) & 1u) ? cat * K + ((xw[s] >> sh) & 0xffu) : cat)]);
+                } else {
+                    const float* wk = ((tailed >> s) & 1u) ? wrow[s] + cat * K + ((xw[s] >> sh) & 0xffu) : wrow[s] + cat;
+                    wb = __float_as_uint(__ldg(wk));
+                }
                 sum = __fadd_rn(sum, __uint_as_float(wb ^ (((sg[s] >> sh) & 0x80u) << 24)));  // sp * w = w with the sign flipped
             }
             th = __fadd_rn(th, sum);
