@@ -249,35 +249,75 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
     const float* wrow[CAT_SLOTS];            // weights of the slot: [K][K] with a categorical tail, [K] without
     uint32_t opens = 0, tailed = 0;          // bit s: slot s opens a table / has a categorical tail
     int S = 0;
-    for (int t = 0; t < (walks ? a.n_tabs : 0); ++t) {
-        const DevTable& T = a.tabs[t];
-        bool first = true;
-        for (int j = 0; j < T.k; ++j) {
-            const int64_t flat = static_cast<int64_t>(node) * T.k + j;
-            if (!T.active[flat]) continue;
-            uint32_t neg = 0;
-            for (int tl = 0; tl < (valid ? T.n_spin : 0); ++tl) neg ^= ~ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
-            uint32_t x = 0;
-            if (valid && T.n_tails > T.n_spin) {
-                x = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
-                x = __vminu4(x, static_cast<uint32_t>(K - 1) * 0x01010101u);  // per-byte clamp, as the generic kernel does
-            }
+    // One active slot: its neighbour words, sign word, weight row (and the copy of its weights) under the static index S.
+    auto take_slot = [&](const DevTable& T, int64_t flat, bool first, int at) {
+        uint32_t neg = 0;
+        for (int tl = 0; tl < (valid ? T.n_spin : 0); ++tl) neg ^= ~ld_word(a.spin, T.idx[tl][flat], a.ld, quad);
+        uint32_t x = 0;
+        if (valid && T.n_tails > T.n_spin) {
+            x = ld_word(a.cat, T.idx[T.n_spin][flat], a.ld, quad);
+            x = __vminu4(x, static_cast<uint32_t>(K - 1) * 0x01010101u);  // per-byte clamp, as the generic kernel does
+        }
 #pragma unroll
-            for (int s = 0; s < CAT_SLOTS; ++s)
-                if (s == S) {  // static indices keep the lists in registers
-                    xw[s] = x;
-                    sg[s] = (neg & 0x01010101u) << 7;
-                    wrow[s] = T.w + flat * T.wdim;
-                }
-            if (STAGE) {  // the node's threads copy the slot's weights: every thread of the node walks the same slots
-                const int len = T.n_tails > T.n_spin ? K * K : K;
-                const float* src = T.w + flat * T.wdim;
-                for (int i = threadIdx.x; i < len; i += blockDim.x) mine[S * K * K + i] = __ldg(src + i);
+        for (int s = 0; s < CAT_SLOTS; ++s)
+            if (s == at) {  // static indices keep the lists in registers
+                xw[s] = x;
+                sg[s] = (neg & 0x01010101u) << 7;
+                wrow[s] = T.w + flat * T.wdim;
             }
-            if (first) opens |= 1u << S;
-            if (T.n_tails > T.n_spin) tailed |= 1u << S;
-            first = false;
-            ++S;
+        if (STAGE) {  // the node's threads copy the slot's weights: every thread of the node walks the same slots
+            const int len = T.n_tails > T.n_spin ? K * K : K;
+            const float* src = T.w + flat * T.wdim;
+            for (int i = threadIdx.x; i < len; i += blockDim.x) mine[at * K * K + i] = __ldg(src + i);
+        }
+        if (first) opens |= 1u << at;
+        if (T.n_tails > T.n_spin) tailed |= 1u << at;
+    };
+    // Which slots are active.  With a warp per node (128 chains or more) lane L looks at candidate L of the node's
+    // (table, slot) list, one ballot gives the active ones in the canonical order, and the per-slot loads below are
+    // independent of each other; walking the tables slot by slot instead makes every load wait for the previous flag.
+    bool listed = false;
+    if (STAGE && blockDim.x == 32) {
+        int ct = -1, cj = 0, total = 0;
+        for (int t = 0; t < a.n_tabs; ++t) {
+            const int k = a.tabs[t].k;
+            if (static_cast<int>(threadIdx.x) >= total && static_cast<int>(threadIdx.x) < total + k) {
+                ct = t;
+                cj = static_cast<int>(threadIdx.x) - total;
+            }
+            total += k;
+        }
+        if (total <= 32) {  // uniform over the CTA
+            listed = true;
+            bool act = false;
+            if (walks && ct >= 0) act = a.tabs[ct].active[static_cast<int64_t>(node) * a.tabs[ct].k + cj] != 0;
+            const uint32_t mask = __ballot_sync(0xffffffffu, act);
+            const int n_act = min(__popc(mask), CAT_SLOTS);
+            int t_prev = -1;
+#pragma unroll
+            for (int s = 0; s < CAT_SLOTS; ++s) {
+                const uint32_t src = __fns(mask, 0, s + 1) & 31u;
+                const int ts = __shfl_sync(0xffffffffu, ct, static_cast<int>(src)), js = __shfl_sync(0xffffffffu, cj, static_cast<int>(src));
+                if (s < n_act) {  // uniform over the warp
+                    const DevTable& T = a.tabs[ts];
+                    take_slot(T, static_cast<int64_t>(node) * T.k + js, ts != t_prev, s);
+                    t_prev = ts;
+                }
+            }
+            S = n_act;
+        }
+    }
+    if (!listed) {
+        for (int t = 0; t < (walks ? a.n_tabs : 0); ++t) {
+            const DevTable& T = a.tabs[t];
+            bool first = true;
+            for (int j = 0; j < T.k; ++j) {
+                const int64_t flat = static_cast<int64_t>(node) * T.k + j;
+                if (!T.active[flat]) continue;
+                take_slot(T, flat, first, S);
+                ++S;
+                first = false;
+            }
         }
     }
     if (STAGE) {
