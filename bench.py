@@ -94,7 +94,7 @@ def measured_peak():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         return float(json.load(open(path))["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
-    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return 6650.0, "fallback (6.65 TB/s; MEASURED_PEAKS.json absent)"
 
 
 def cpu_baseline(model, threads, target_seconds=12.0):
@@ -303,7 +303,7 @@ def run_rbm(T, torch, W, args, device):
     builder = W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model)
     program = T.Program(builder, ctx)
     assert program.enable_dense(False) == 2
-    T.lib().thrml_debug_dense_pair_mode({"single": 0, "pair": 1, "auto": 2}[args.dense_tiles])
+    program.set_option(T.OPT_DENSE_TILES, {"single": 0, "pair": 1, "auto": 2}[args.dense_tiles])
     rng = np.random.default_rng(3)
     v0 = (rng.random((chains, nv)) < 0.13).astype(np.uint8)
     data, state = T.ChainState(program, chains), T.ChainState(program, chains)

@@ -145,17 +145,6 @@ int32_t thrml_ctx_synchronize(thrml_ctx* ctx);
  * kernel waits on a pipeline barrier that nothing signals; its bounded wait runs out, it returns, and this call
  * reports THRML_ERR_TIMEOUT.  The context remains usable. */
 int32_t thrml_debug_wait_timeout(thrml_ctx* ctx);
-/* Tile shape of the dense (tensor-core) kernels, process-wide: 1 = CTA pairs sharing 256-row tiles through
- * tcgen05 cta_group::2 (each CTA stages half of the B operand), 0 = one CTA per 128-row tile, 2 (the default) = chosen
- * per launch from the shape (pairs for long reductions without much row padding).  All give the same results; tests
- * run both tilings.  Returns the previous setting.  No counterpart in the reference. */
-int32_t thrml_debug_dense_pair_mode(int32_t mode);
-/* Widens (units of 2^-24 of probability, process-wide, >= 0) the window around each draw's probability inside which the
- * split-field-table update of sequential-sum nodes recomputes the field in the canonical order; applies to programs
- * created or re-weighted afterwards.  0 (the default) keeps the derived bound; 2^25 sends every draw through the exact
- * route.  Results never depend on it; tests use it to run both routes.  Returns the previous value.  No counterpart in
- * the reference. */
-float thrml_debug_split_margin(float extra_units);
 /* cudaStream_t of the context, for callers that time with their own events. */
 void* thrml_ctx_stream(thrml_ctx* ctx);
 
@@ -164,6 +153,20 @@ void* thrml_ctx_stream(thrml_ctx* ctx);
 int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out);
 void thrml_program_destroy(thrml_program* p);
 int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w);
+/* Per-program tuning options (no counterpart in the reference; results never depend on them, tests use them to run
+ * every route).  They belong to the handle: other programs and other host threads are not affected.
+ *   THRML_OPT_DENSE_TILES   tile shape of the dense (tensor-core) kernels: 1 = CTA pairs sharing 256-row tiles through
+ *                           tcgen05 cta_group::2 (each CTA stages half of the B operand), 0 = one CTA per 128-row tile,
+ *                           2 (the default) = chosen per launch from the shape (pairs for long reductions without much
+ *                           row padding).
+ *   THRML_OPT_SPLIT_MARGIN  widens (units of 2^-24 of probability, >= 0) the window around each draw's probability inside
+ *                           which the split-field-table update of sequential-sum nodes recomputes the field in the
+ *                           canonical order; 0 (the default) keeps the derived bound, 2^25 sends every draw through the
+ *                           exact route.  Setting it rebuilds the affected blocks' tables. */
+#define THRML_OPT_DENSE_TILES 1
+#define THRML_OPT_SPLIT_MARGIN 2
+int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value);
+int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double* value_out);
 /* Dense bipartite path.  A spin block whose neighbours all lie in one other spin block (a layer of an RBM-style model:
  * IsingEBM with bipartite edges, crates/thrml-models/src/ising.rs:105-143, which the reference samples as a padded
  * gather, program.rs:159-300) can compute its local fields as one tensor-core GEMM against the other block's +-1 states
@@ -246,6 +249,9 @@ int32_t thrml_pair_correlation(thrml_state* s, int32_t block_a, int32_t block_b,
  * [n_visible][n_hidden] f32, nullable. */
 int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_block, const uint8_t* v0_host, uint64_t key,
                        float* pos_host, float* neg_host);
+/* Bring-up check of the CTA-pair tensor-core kernels (no reference counterpart): after a pair launch on this state, both
+ * CTAs of a pair must have been given the same tensor-memory base address; THRML_ERR_CUDA if they differ. */
+int32_t thrml_debug_pair_tmem_check(thrml_state* s);
 /* Local field gamma[chain][node] (spin block) or logits theta[chain][node][K] (categorical block) of a free
  * block in the current state — spin_gibbs.rs:512-611 / softmax.rs:586-709. */
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out);

@@ -16,9 +16,10 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True)
 def single_cta_tiles(T):
     """This file exercises the one-CTA tiles; tests/test_gpu_dense_pair.py re-runs the same checks with CTA pairs."""
-    before = T.lib().thrml_debug_dense_pair_mode(0)
+    before = dict(T.Program.default_options)
+    T.Program.default_options = {**before, T.OPT_DENSE_TILES: 0}
     yield
-    T.lib().thrml_debug_dense_pair_mode(before)
+    T.Program.default_options = before
 
 
 def to_bf16(x):
@@ -101,6 +102,7 @@ def test_dense_update_matches_oracle(T, O, n_v, n_h, chains):
     p = 1 / (1 + np.exp(-2 * o64))
     z = (h.mean(axis=0) - p.mean(axis=0)) / np.sqrt((p * (1 - p)).mean(axis=0) / chains + 1e-12)
     assert np.abs(z).max() < 5.5
+    gs.pair_tmem_check()
 
 
 def test_dense_refuses_inexact_weights_unless_allowed(T, O):
@@ -137,6 +139,7 @@ def test_pair_correlation_is_exact(T, n_a, n_b, chains):
     assert np.array_equal(got, want)
     got_t = st.pair_correlation(1, 0)
     assert np.array_equal(got_t, want.T)
+    st.pair_tmem_check()
 
 
 def test_cd1_step_composition_and_statistics(T, O):

@@ -10,9 +10,10 @@ pytestmark = pytest.mark.gpu
 
 @pytest.fixture(autouse=True)
 def pair_mode(T):
-    before = T.lib().thrml_debug_dense_pair_mode(1)
+    before = dict(T.Program.default_options)
+    T.Program.default_options = {**before, T.OPT_DENSE_TILES: 1}
     yield
-    T.lib().thrml_debug_dense_pair_mode(before)
+    T.Program.default_options = before
 
 
 # tile widths: 128 columns for narrow blocks, 208 where that pads least (784 -> 832), 256 for wide ones; chains below and
@@ -35,11 +36,11 @@ def test_cd1_step_composition_and_statistics(T, O):
 def test_auto_mode_correlations(T, n_a, n_b, chains):
     """Mode 2 picks the tiling per launch; when only the second block fills 256-row tiles well the operands are swapped and
     the epilogue writes the transposed result.  Integer arithmetic: every route gives the same exact matrix."""
-    T.lib().thrml_debug_dense_pair_mode(2)
+    T.Program.default_options = {T.OPT_DENSE_TILES: 2}
     D.test_pair_correlation_is_exact(T, n_a, n_b, chains)
 
 
 def test_auto_mode_update_and_cd1(T, O):
-    T.lib().thrml_debug_dense_pair_mode(2)
+    T.Program.default_options = {T.OPT_DENSE_TILES: 2}
     D.test_dense_update_matches_oracle(T, O, 96, 2100, 300)   # long reduction for the visible layer: pair tiles there only
     D.test_cd1_step_composition_and_statistics(T, O)

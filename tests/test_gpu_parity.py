@@ -413,12 +413,14 @@ def test_split_field_tables_match_oracle(T, O, degree, chains, extra):
     """Sequential-sum nodes with at most 32 neighbour entries, 256 chains or more: the field comes from two (up to 16
     neighbours) or four 256-entry tables and only draws close to the probability take the canonical sum.  `extra` widens
     that window: 0 = the derived bound, 2^25 = every draw through the exact route, 3e5 (2 % of the unit interval) = a mixture."""
-    before = T.lib().thrml_debug_split_margin(extra)
+    before = dict(T.Program.default_options)
+    T.Program.default_options = {**before, T.OPT_SPLIT_MARGIN: extra}
     try:
         desc, info = M.ising_random_graph(T, 260, degree, 300 + degree, w_sigma=0.4, bias_sigma=0.3)
         prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 3)
     finally:
-        T.lib().thrml_debug_split_margin(before)
+        T.Program.default_options = before
+    assert prog.get_option(T.OPT_SPLIT_MARGIN) == extra
     assert all(prog.block_kernel(b) == 4 for b in range(len(desc["free"])))
     gs.run_blocks(23, 8)
     os_.run_blocks(23, 8)

@@ -45,9 +45,15 @@ def test_two_rank_chain_sharding(T, O, tmp_path):
     import models as M
     from thrml_rs_b200 import sharding
     total = 40
-    assert [sharding.shard_chains(total, r, 2) for r in range(2)] == [(32, 0), (8, 32)]
+    assert [sharding.shard_chains(total, r, 2) for r in range(2)] == [(16, 0), (24, 16)]
     assert [sharding.shard_chains(4096 * 8, r, 8) for r in (0, 7)] == [(4096, 0), (4096, 4096 * 7)]
-    assert sharding.shard_chains(10, 1, 2) == (0, 10)
+    assert [sharding.shard_chains(160, r, 8) for r in range(8)] == [(32, 0), (32, 32)] + [(16, 64 + 16 * i) for i in range(6)]
+    # fewer than one 16-chain unit per rank: every rank raises before any collective, none is left with zero chains
+    for r in range(8):
+        with pytest.raises(ValueError, match="cannot be sharded"):
+            sharding.shard_chains(96, r, 8)
+    with pytest.raises(ValueError, match="cannot be sharded"):
+        sharding.shard_chains(10, 1, 2)
     out = str(tmp_path / "sums.npy")
     port = 29500 + (os.getpid() % 2000)
     mp.spawn(_worker, args=(2, port, total, out), nprocs=2, join=True)

@@ -41,8 +41,9 @@ _SIGNATURES = {
     "thrml_ctx_synchronize": (C.c_int32, [_P]),
     "thrml_ctx_stream": (C.c_void_p, [_P]),
     "thrml_debug_wait_timeout": (C.c_int32, [_P]),
-    "thrml_debug_dense_pair_mode": (C.c_int32, [C.c_int32]),
-    "thrml_debug_split_margin": (C.c_float, [C.c_float]),
+    "thrml_program_set_option": (C.c_int32, [_P, C.c_int32, C.c_double]),
+    "thrml_program_get_option": (C.c_int32, [_P, C.c_int32, _P]),
+    "thrml_debug_pair_tmem_check": (C.c_int32, [_P]),
     "thrml_program_create": (C.c_int32, [_P, _P, _P]),
     "thrml_program_destroy": (None, [_P]),
     "thrml_program_update_weights": (C.c_int32, [_P, C.c_int32, C.c_int32, _P]),

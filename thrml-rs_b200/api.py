@@ -277,9 +277,11 @@ class BlockSamplingProgram:
 # Drivers: crates/thrml-samplers/src/sampling.rs
 # ---------------------------------------------------------------------------------------------------------
 def _batch_of(states):
+    """(chains, batched): batched when any entry is `[chains, n]`; 1-D entries then stand for every chain."""
     for s in states:
         s = np.asarray(s)
-        return (s.shape[0], True) if s.ndim == 2 else (1, False)
+        if s.ndim == 2:
+            return s.shape[0], True
     return 1, False
 
 
@@ -291,7 +293,12 @@ def _make_state(program, state_free, state_clamp, chain_offset=0):
     chains, batched = _batch_of(list(state_free) + list(state_clamp))
     st = _eng.ChainState(program.device_program, chains, chain_offset)
     for i, s in enumerate(list(state_free) + list(state_clamp)):
-        st.upload(i, np.asarray(s).reshape(chains, -1))
+        s = np.asarray(s)
+        if s.ndim == 2 and s.shape[0] != chains:
+            raise ThrmlError(-1, "batched block states must share the leading dimension")
+        if s.ndim == 1 and batched:  # one row for every chain (a clamped or conditioning block given once)
+            s = np.broadcast_to(s, (chains, s.shape[0]))
+        st.upload(i, np.ascontiguousarray(s).reshape(chains, -1))
     return st, chains, batched
 
 

@@ -6,7 +6,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libthrml_b200.so")
 SOURCES = ["engine.cu", "lattice.cu", "potts.cu", "builder.cpp"]
-HEADERS = ["tables.h", "ctx.h", "dense.cuh", "device_math.cuh", "update_kernels.cuh", "observer_kernels.cuh", os.path.join("..", "..", "include", "thrml_b200.h")]
+HEADERS = ["tables.h", "ctx.h", "devbuf.h", "dense.cuh", "device_math.cuh", "update_kernels.cuh", "observer_kernels.cuh", os.path.join("..", "..", "include", "thrml_b200.h")]
 
 
 def _stale() -> bool:

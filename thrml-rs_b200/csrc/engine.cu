@@ -8,31 +8,13 @@
 
 #include "ctx.h"
 #include "dense.cuh"
+#include "devbuf.h"
 #include "device_math.cuh"
 #include "observer_kernels.cuh"
 #include "tables.h"
 #include "update_kernels.cuh"
 
 using namespace thrml;
-
-struct DevBuf {
-    void* p = nullptr;
-    size_t bytes = 0;
-    DevBuf() = default;
-    DevBuf(const DevBuf&) = delete;
-    DevBuf& operator=(const DevBuf&) = delete;
-    DevBuf(DevBuf&& o) noexcept : p(o.p), bytes(o.bytes) { o.p = nullptr; o.bytes = 0; }
-    ~DevBuf() { if (p) cudaFree(p); }
-    int32_t alloc(size_t n) {
-        if (p) { cudaFree(p); p = nullptr; }
-        bytes = n;
-        if (n == 0) return THRML_OK;
-        cudaError_t e = cudaMalloc(&p, n);
-        if (e != cudaSuccess) { p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
-        return THRML_OK;
-    }
-    template <class T> T* as() const { return static_cast<T*>(p); }
-};
 
 struct BlockProg {
     int32_t kind = 0;     // 0 spin, K categorical
@@ -90,6 +72,8 @@ struct thrml_program {
     std::vector<uint8_t> is_dense_source;  // per block: some dense block reads its +-1 image
     bool any_dense = false;
     int32_t kernel_epoch = 0;  // bumped whenever a block changes kernel; observers built before that stop fusing
+    int32_t dense_tiles = 2;         // THRML_OPT_DENSE_TILES
+    float split_extra_margin = 0.f;  // THRML_OPT_SPLIT_MARGIN
 };
 
 struct thrml_state {
@@ -183,9 +167,8 @@ static int32_t pair_tile_width(int64_t n) {
 // 0 = one CTA per 128-row tile, 1 = CTA pairs on 256-row tiles, 2 = per launch, whichever suits the shape: pairs halve the
 // B-operand traffic per SM, which pays when the GEMM is bound by its operand feed (long K); a short-K update is bound
 // by its sampling epilogue and runs a little faster without the cluster hand-overs.
-static int g_dense_pair_mode = 2;
-static bool use_pair_tiles(int64_t m_rows, int64_t k_elems) {
-    if (g_dense_pair_mode != 2) return g_dense_pair_mode == 1;
+static bool use_pair_tiles(int32_t mode, int64_t m_rows, int64_t k_elems) {
+    if (mode != 2) return mode == 1;
     const int64_t pad_pair = (m_rows + 255) / 256 * 256, pad_single = (m_rows + 127) / 128 * 128;
     return k_elems >= 2048 && pad_pair * 10 <= pad_single * 11;
 }
@@ -219,7 +202,7 @@ static dim3 grid_nq(int64_t n, int64_t ld) {
     return dim3(static_cast<unsigned>((n + b.y - 1) / b.y), static_cast<unsigned>((ld / 4 + b.x - 1) / b.x));
 }
 static int32_t need_scratch(thrml_state* s, size_t bytes) {
-    if (s->scratch.bytes >= bytes) return THRML_OK;
+    if (s->scratch.holds(bytes)) return THRML_OK;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
     return s->scratch.alloc(bytes);
 }
@@ -259,7 +242,6 @@ void* thrml_ctx_stream(thrml_ctx* ctx) { return ctx ? static_cast<void*>(ctx->st
 // ---------------------------------------------------------------------------------------------------------
 // Program.
 // ---------------------------------------------------------------------------------------------------------
-static float g_split_extra_margin = 0.0f;
 static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
     k_build_seq<<<static_cast<unsigned>((bp.n + 255) / 256), 256, 0, p->ctx->stream>>>(bp.d_tabs.as<DevTable>(), bp.n_tabs, static_cast<int32_t>(bp.n),
                                                                                       bp.d_seq_overflow.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(),
@@ -267,7 +249,7 @@ static int32_t rebuild_seq(thrml_program* p, BlockProg& bp) {
     CU_TRY(cudaGetLastError());
     if (bp.n_split > 0) {
         k_build_split<<<static_cast<unsigned>(bp.n_split), 256, 0, p->ctx->stream>>>(bp.d_split_nodes.as<int32_t>(), bp.d_split_row.as<int32_t>(), bp.d_seq_nbr.as<int32_t>(), bp.d_seq_w.as<float>(),
-                                                                                    bp.d_seq_cnt.as<int32_t>(), bp.d_split_tab.as<float>(), bp.d_split_margin.as<float>(), g_split_extra_margin);
+                                                                                    bp.d_seq_cnt.as<int32_t>(), bp.d_split_tab.as<float>(), bp.d_split_margin.as<float>(), p->split_extra_margin);
         CU_TRY(cudaGetLastError());
     }
     return THRML_OK;
@@ -855,12 +837,6 @@ static int32_t check_err_flag(thrml_state* s) {
     if (!s->d_err.p) return THRML_OK;
     int code = 0;
     CU_TRY(cudaMemcpy(&code, s->d_err.p, sizeof(int), cudaMemcpyDeviceToHost));
-    if (g_dense_pair_mode) {  // both CTAs of a pair must hold the accumulators at the same TMEM address
-        uint32_t base[2] = {0, 0};
-        CU_TRY(cudaMemcpy(base, s->d_dense_debug.p, sizeof(base), cudaMemcpyDeviceToHost));
-        if (base[0] != base[1])
-            return fail(THRML_ERR_CUDA, "the two CTAs of a pair got different tensor-memory addresses (" + std::to_string(base[0]) + ", " + std::to_string(base[1]) + ")");
-    }
     if (code == 0) return THRML_OK;
     CU_TRY(cudaMemset(s->d_err.p, 0, sizeof(int)));
     return fail(THRML_ERR_TIMEOUT, "a tensor-core kernel gave up waiting on a pipeline barrier (role " + std::to_string(code) + ")");
@@ -960,7 +936,7 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, p->ctx->stream));
     g.ones_out = s->ones[block]->as<int32_t>();
     int32_t rc = THRML_OK;
-    if (use_pair_tiles(s->n_chains, p->blocks[bp.dense_src].n)) {
+    if (use_pair_tiles(p->dense_tiles, s->n_chains, p->blocks[bp.dense_src].n)) {
         if (bp.dense_bn_pair == 256) rc = launch_dense_pair<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
         else if (bp.dense_bn_pair == 208) rc = launch_dense_pair<dense::EPI_SAMPLE, 208>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
         else rc = launch_dense_pair<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
@@ -1236,9 +1212,9 @@ static int32_t flush_sliced(thrml_state* s) {
     }
     s->pending.clear();
     for (int32_t m = 0; m < p->n_free; ++m) s->touch(m);
-    if (s->d_slice_blocks.bytes < blocks.size() * sizeof(SliceBlock))
+    if (!s->d_slice_blocks.holds(blocks.size() * sizeof(SliceBlock)))
         if (int32_t rc = s->d_slice_blocks.alloc(blocks.size() * sizeof(SliceBlock))) return rc;
-    if (s->d_plan.bytes < steps.size() * sizeof(SliceStep))
+    if (!s->d_plan.holds(steps.size() * sizeof(SliceStep)))
         if (int32_t rc = s->d_plan.alloc(std::max(steps.size() * sizeof(SliceStep), PERSIST_MAX_STEPS * sizeof(LutArgs)))) return rc;
     // pageable sources: the copies have been staged by the time the calls return
     CU_TRY(cudaMemcpyAsync(s->d_slice_blocks.p, blocks.data(), blocks.size() * sizeof(SliceBlock), cudaMemcpyHostToDevice, st));
@@ -1296,9 +1272,9 @@ static int32_t flush_pending(thrml_state* s) {
     const int grid = s->persist_grid;
     for (size_t at = 0; at < steps.size(); at += PERSIST_MAX_STEPS) {
         const size_t cnt = std::min(PERSIST_MAX_STEPS, steps.size() - at);
-        if (s->d_plan.bytes < cnt * sizeof(LutArgs))
+        if (!s->d_plan.holds(cnt * sizeof(LutArgs)))
             if (int32_t rc = s->d_plan.alloc(PERSIST_MAX_STEPS * sizeof(LutArgs))) return rc;
-        if (s->d_plan_acc.bytes < cnt)
+        if (!s->d_plan_acc.holds(cnt))
             if (int32_t rc = s->d_plan_acc.alloc(PERSIST_MAX_STEPS)) return rc;
         // pageable sources: both copies have been staged by the time the calls return, so `steps` may be reused
         CU_TRY(cudaMemcpyAsync(s->d_plan.p, steps.data() + at, cnt * sizeof(LutArgs), cudaMemcpyHostToDevice, st));
@@ -1485,8 +1461,8 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
     if (int32_t rc = ensure_err_flag(s)) return rc;
     // Rows of the GEMM come from block a unless only block b fills 256-row pair tiles well: then the operands swap
     // and the epilogue writes the transposed result, which lands in the same [n_a][n_b] layout.
-    bool pair = use_pair_tiles(p->blocks[block_a].n, s->n_chains), swapped = false;
-    if (!pair && g_dense_pair_mode == 2 && use_pair_tiles(p->blocks[block_b].n, s->n_chains)) pair = swapped = true;
+    bool pair = use_pair_tiles(p->dense_tiles, p->blocks[block_a].n, s->n_chains), swapped = false;
+    if (!pair && p->dense_tiles == 2 && use_pair_tiles(2, p->blocks[block_b].n, s->n_chains)) pair = swapped = true;
     const int32_t row_block = swapped ? block_b : block_a, col_block = swapped ? block_a : block_b;
     const BlockProg& br = p->blocks[row_block];
     const BlockProg& bc = p->blocks[col_block];
@@ -1530,7 +1506,7 @@ int32_t thrml_pair_correlation(thrml_state* s, int32_t block_a, int32_t block_b,
     if (int32_t rc = check_block(s, block_b)) return rc;
     CU_TRY(cudaSetDevice(s->prog->ctx->device));
     const size_t cnt = static_cast<size_t>(s->prog->blocks[block_a].n) * s->prog->blocks[block_b].n;
-    if (s->d_corr.bytes < 2 * cnt * 4)
+    if (!s->d_corr.holds(2 * cnt * 4))
         if (int32_t rc = s->d_corr.alloc(2 * cnt * 4)) return rc;
     if (int32_t rc = pair_correlation_async(s, block_a, block_b, s->d_corr.as<float>())) return rc;
     CU_TRY(cudaMemcpyAsync(host_out, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, s->prog->ctx->stream));
@@ -1546,7 +1522,7 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
     CU_TRY(cudaSetDevice(s->prog->ctx->device));
     cudaStream_t st = s->prog->ctx->stream;
     const size_t cnt = static_cast<size_t>(s->prog->blocks[visible_block].n) * s->prog->blocks[hidden_block].n;
-    if (s->d_corr.bytes < 2 * cnt * 4)
+    if (!s->d_corr.holds(2 * cnt * 4))
         if (int32_t rc = s->d_corr.alloc(2 * cnt * 4)) return rc;
     if (v0_host)
         if (int32_t rc = thrml_state_upload_u8(s, visible_block, v0_host)) return rc;
@@ -1815,15 +1791,44 @@ int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, 
     if (n_other_rows) *n_other_rows = other;
     return THRML_OK;
 }
-int32_t thrml_debug_dense_pair_mode(int32_t mode) {
-    const int32_t before = g_dense_pair_mode;
-    g_dense_pair_mode = mode < 0 || mode > 2 ? 2 : mode;
-    return before;
+int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value) {
+    if (!p) return fail(THRML_ERR_INVALID_ARG, "null program");
+    if (option == THRML_OPT_DENSE_TILES) {
+        if (value != 0.0 && value != 1.0 && value != 2.0) return fail(THRML_ERR_INVALID_ARG, "dense tiles: 0 (one CTA per tile), 1 (CTA pairs) or 2 (per launch)");
+        p->dense_tiles = static_cast<int32_t>(value);
+        return THRML_OK;
+    }
+    if (option == THRML_OPT_SPLIT_MARGIN) {
+        if (!(value >= 0.0)) return fail(THRML_ERR_INVALID_ARG, "the split margin is a non-negative number of 2^-24 units");
+        p->split_extra_margin = static_cast<float>(value);
+        CU_TRY(cudaSetDevice(p->device));
+        for (int32_t bi = 0; bi < p->n_free; ++bi)
+            if (p->blocks[bi].n_split > 0)
+                if (int32_t rc = rebuild_seq(p, p->blocks[bi])) return rc;
+        CU_TRY(cudaStreamSynchronize(p->ctx->stream));
+        return THRML_OK;
+    }
+    return fail(THRML_ERR_INVALID_ARG, "unknown program option " + std::to_string(option));
 }
-float thrml_debug_split_margin(float extra_units) {
-    const float before = g_split_extra_margin;
-    g_split_extra_margin = extra_units >= 0.0f ? extra_units : 0.0f;
-    return before;
+int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double* value_out) {
+    if (!p || !value_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (option == THRML_OPT_DENSE_TILES) *value_out = p->dense_tiles;
+    else if (option == THRML_OPT_SPLIT_MARGIN) *value_out = p->split_extra_margin;
+    else return fail(THRML_ERR_INVALID_ARG, "unknown program option " + std::to_string(option));
+    return THRML_OK;
+}
+// Bring-up check of the CTA-pair kernels: both CTAs of a pair must have been given the same tensor-memory base address
+// (the two-CTA MMA writes both accumulators at one address).  Reads the two words the last pair launch recorded.
+int32_t thrml_debug_pair_tmem_check(thrml_state* s) {
+    if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (!s->d_dense_debug.p) return THRML_OK;  // no tensor-core kernel has run on this state
+    CU_TRY(cudaSetDevice(s->device));
+    CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
+    uint32_t base[2] = {0, 0};
+    CU_TRY(cudaMemcpy(base, s->d_dense_debug.p, sizeof(base), cudaMemcpyDeviceToHost));
+    if (base[0] != base[1])
+        return fail(THRML_ERR_CUDA, "the two CTAs of a pair got different tensor-memory addresses (" + std::to_string(base[0]) + ", " + std::to_string(base[1]) + ")");
+    return THRML_OK;
 }
 int32_t thrml_state_launch_counts(const thrml_state* s, int64_t* block_launches, int64_t* persistent_launches) {
     if (!s) return fail(THRML_ERR_INVALID_ARG, "null state");

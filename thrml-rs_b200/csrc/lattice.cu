@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "ctx.h"
+#include "devbuf.h"
 #include "device_math.cuh"
 
 using namespace thrml;
@@ -193,12 +194,6 @@ __global__ void k_lattice_unpack(const uint32_t* p0, const uint32_t* p1, uint8_t
     }
 }
 
-struct Buf {
-    void* p = nullptr;
-    size_t bytes = 0;
-    ~Buf() { if (p) cudaFree(p); }
-};
-
 }  // namespace
 
 struct thrml_lattice {
@@ -206,17 +201,12 @@ struct thrml_lattice {
     int device = 0;
     int64_t H = 0, W = 0, row0 = 0, n_rows = 0, n_chains = 0, chain_offset = 0;
     int32_t words = 0;
-    Buf plane[2], lut, order, obs, scratch;
+    DevBuf plane[2], lut, order, obs, scratch;
     size_t row_bytes = 0;  // one row of one colour
     uint32_t* p(int c) const { return static_cast<uint32_t*>(plane[c].p); }
 };
 
-static int32_t lat_alloc(Buf& b, size_t bytes) {
-    cudaError_t e = cudaMalloc(&b.p, bytes);
-    if (e != cudaSuccess) { b.p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
-    b.bytes = bytes;
-    return THRML_OK;
-}
+static int32_t lat_alloc(DevBuf& b, size_t bytes) { return b.alloc(bytes); }
 
 extern "C" {
 
@@ -287,10 +277,9 @@ int32_t thrml_lattice_randomize(thrml_lattice* L, uint64_t key) {
 }
 
 static int32_t lat_scratch(thrml_lattice* L, size_t bytes) {
-    if (L->scratch.bytes >= bytes) return THRML_OK;
+    if (L->scratch.holds(bytes)) return THRML_OK;
     CU_TRY(cudaStreamSynchronize(L->ctx->stream));
-    if (L->scratch.p) { cudaFree(L->scratch.p); L->scratch.p = nullptr; L->scratch.bytes = 0; }
-    return lat_alloc(L->scratch, bytes);
+    return L->scratch.alloc(bytes);
 }
 int32_t thrml_lattice_upload(thrml_lattice* L, const uint8_t* host) {
     if (!L || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");

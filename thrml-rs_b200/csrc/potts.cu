@@ -15,6 +15,7 @@
 #include <vector>
 
 #include "ctx.h"
+#include "devbuf.h"
 #include "device_math.cuh"
 
 using namespace thrml;
@@ -228,18 +229,7 @@ __global__ void k_potts_transpose_out(const uint8_t* src, uint8_t* dst, int64_t 
     }
 }
 
-struct PBuf {
-    void* p = nullptr;
-    size_t bytes = 0;
-    ~PBuf() { if (p) cudaFree(p); }
-};
-int32_t palloc(PBuf& b, size_t bytes) {
-    if (b.p) { cudaFree(b.p); b.p = nullptr; b.bytes = 0; }
-    cudaError_t e = cudaMalloc(&b.p, bytes);
-    if (e != cudaSuccess) { b.p = nullptr; return fail(e == cudaErrorMemoryAllocation ? THRML_ERR_OOM : THRML_ERR_CUDA, std::string("cudaMalloc: ") + cudaGetErrorString(e)); }
-    b.bytes = bytes;
-    return THRML_OK;
-}
+int32_t palloc(DevBuf& b, size_t bytes) { return b.alloc(bytes); }
 
 }  // namespace
 
@@ -248,7 +238,7 @@ struct thrml_potts {
     int device = 0;
     int32_t nx = 0, ny = 0, nz = 0, K = 0;
     int64_t n = 0, n_chains = 0, chain_offset = 0, ld = 0, n_obs = 0;
-    PBuf state, tables, pair_tables, unary, counts, scratch;
+    DevBuf state, tables, pair_tables, unary, counts, scratch;
     float table_mag = 0.0f;
     bool pair = false;  // pre-added direction tables exist (category counts with a compile-time kernel and 3 K^3 floats of shared memory to spare)
 };
@@ -366,7 +356,7 @@ int32_t thrml_potts_read_marginals(thrml_potts* P, int32_t* counts_out, int64_t*
     return THRML_OK;
 }
 static int32_t potts_scratch(thrml_potts* P, size_t bytes) {
-    if (P->scratch.bytes >= bytes) return THRML_OK;
+    if (P->scratch.holds(bytes)) return THRML_OK;
     CU_TRY(cudaStreamSynchronize(P->ctx->stream));
     return palloc(P->scratch, bytes);
 }

@@ -174,14 +174,32 @@ class Builder:
         return out
 
 
+OPT_DENSE_TILES = 1
+OPT_SPLIT_MARGIN = 2
+
+
 class Program:
     """Compiled tables resident on the device (thrml_program)."""
+
+    # Options applied to every program this class creates afterwards ({option id: value}); a host-side convenience of
+    # this wrapper (tests use it to run every kernel route) — the library itself keeps options per program handle.
+    default_options = {}
 
     def __init__(self, builder, ctx=None):
         self.ctx = ctx or default_context()
         self.builder = builder
         self.h = C.c_void_p()
         check(lib().thrml_program_create(self.ctx.h, builder.h, C.byref(self.h)))
+        for opt, value in self.default_options.items():
+            self.set_option(opt, value)
+
+    def set_option(self, option, value):
+        check(lib().thrml_program_set_option(self.h, C.c_int32(option), C.c_double(value)))
+
+    def get_option(self, option):
+        v = C.c_double()
+        check(lib().thrml_program_get_option(self.h, C.c_int32(option), C.byref(v)))
+        return v.value
 
     def __del__(self):
         h, self.h = getattr(self, "h", None), None
@@ -314,6 +332,11 @@ class ChainState:
         out = np.zeros(shape, dtype=np.float32)
         check(lib().thrml_fields_debug(self.h, C.c_int32(block), ptr(out)))
         return out
+
+    def pair_tmem_check(self):
+        """Bring-up check of the CTA-pair kernels: raises if the two CTAs of the last pair launch disagreed on their
+        tensor-memory base."""
+        check(lib().thrml_debug_pair_tmem_check(self.h))
 
     def launch_counts(self):
         """(per-block update launches, persistent multi-sweep launches) issued by this state so far."""
