@@ -53,6 +53,7 @@ typedef struct thrml_builder thrml_builder;
 typedef struct thrml_program thrml_program;
 typedef struct thrml_state thrml_state;
 typedef struct thrml_moments thrml_moments;
+typedef struct thrml_comm thrml_comm;
 
 /* Message of the last failing call on this thread (empty string if none). */
 const char* thrml_last_error(void);
@@ -148,6 +149,21 @@ int32_t thrml_debug_wait_timeout(thrml_ctx* ctx);
 /* cudaStream_t of the context, for callers that time with their own events. */
 void* thrml_ctx_stream(thrml_ctx* ctx);
 
+/* ------------------------------------------------------------------------------------------------
+ * Multi-GPU (no counterpart in the reference, which drives one device from one thread): one process per GPU, one
+ * thrml_comm per process = one rank of a NCCL communicator.  NCCL is loaded at run time (libnccl.so.2) by the first of
+ * these calls; a failing NCCL call returns THRML_ERR_NCCL with NCCL's message.  Rank 0 calls thrml_comm_unique_id and the
+ * host distributes the 128 bytes to the other ranks by its own means (a file, a socket, MPI, torch.distributed ...);
+ * every rank then calls thrml_comm_create (collective: returns once all world_size ranks have joined).
+ * thrml_comm_adopt wraps an ncclComm_t the host already owns (it is not destroyed with the handle).
+ * ---------------------------------------------------------------------------------------------- */
+#define THRML_COMM_ID_BYTES 128
+int32_t thrml_comm_unique_id(uint8_t* id_out /* [THRML_COMM_ID_BYTES] */);
+int32_t thrml_comm_create(thrml_ctx* ctx, const uint8_t* id, int32_t rank, int32_t world_size, thrml_comm** out);
+int32_t thrml_comm_adopt(thrml_ctx* ctx, void* nccl_comm, thrml_comm** out);
+void thrml_comm_destroy(thrml_comm* c);
+int32_t thrml_comm_info(const thrml_comm* c, int32_t* rank_out, int32_t* world_out, int32_t* nccl_version_out);
+
 /* Uploads the compiled tables.  The program snapshots the weights (as the reference does,
  * program.rs:216-235); thrml_program_update_weights refreshes table t of a block explicitly. */
 int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out);
@@ -191,6 +207,15 @@ int32_t thrml_state_upload_f32(thrml_state* s, int32_t block, const float* host)
 int32_t thrml_state_download_f32(thrml_state* s, int32_t block, float* host);
 int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host);
 int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host);
+/* Chains [chain_begin, chain_begin + n_chains) of one block only: host[chain - chain_begin][node]. */
+int32_t thrml_state_download_chains_u8(thrml_state* s, int32_t block, int64_t chain_begin, int64_t n_chains, uint8_t* host);
+/* Several blocks per call (block ids in `blocks`, one host pointer each): all copies and layout kernels are queued on the
+ * context's stream and the host waits once at the end.  _u8_many: hosts[i] = [chain][node] bytes as in
+ * thrml_state_upload_u8.  _packed (spin blocks only; the mirror of thrml_sample_states_packed): bits[i] = [node][word] u32,
+ * word w = chains 32w .. 32w+31, bit c & 31 — one bit per spin over the host link, no transpose on the device.
+ * No counterpart in the reference, whose states are f32 tensors (crates/thrml-core/src/state_tree.rs:32-73). */
+int32_t thrml_state_upload_u8_many(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const uint8_t* const* hosts);
+int32_t thrml_state_upload_packed(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const uint32_t* const* bits);
 /* Device-to-device copy of one block's state between two states of the same program and chain count (asynchronous on
  * the context's stream; the reference's equivalent is cloning a state tensor, e.g. sampling.rs:237). */
 int32_t thrml_state_copy_block(thrml_state* dst, const thrml_state* src, int32_t block);
@@ -275,6 +300,12 @@ int32_t thrml_moments_read(thrml_moments* m, int32_t type, int64_t* sums_out, in
  * multi-GPU host hands to its single allreduce(sum). */
 int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_t* count_out);
 int32_t thrml_moments_add_observations(thrml_moments* m, int64_t n_obs);
+/* The single collective of the chain-parallel deployment (chains sharded over the ranks of `comm`, program replicated,
+ * noise keyed by the global chain id): adds the sums and the observation count over all ranks, in place on every rank,
+ * with ncclAllReduce on the context's stream.  Collective: every rank calls it with an observer of the same spec.  The
+ * sums travel as int32 when the reduced observation counts prove that every total fits, else as int64.  The reduction of
+ * the sums is asynchronous; thrml_moments_read waits for it. */
+int32_t thrml_moments_allreduce(thrml_moments* m, thrml_comm* comm);
 /* How the rows are served when the observer follows a sweep: rows the update kernels accumulate themselves (single
  * spins and neighbour pairs of threshold-table blocks) and rows left to the separate observer kernel. */
 int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, int64_t* n_other_rows);
@@ -322,6 +353,10 @@ int32_t thrml_lattice_randomize(thrml_lattice* lat, uint64_t key);
 /* Stripe state as bytes 0/1, host layout [chain][stripe row][column]. */
 int32_t thrml_lattice_upload(thrml_lattice* lat, const uint8_t* host);
 int32_t thrml_lattice_download(thrml_lattice* lat, uint8_t* host);
+/* The same state as bits, host layout [chain][stripe row][width / 32] u32, bit k of word v = column 32 v + k: one bit per
+ * spin over the host link. */
+int32_t thrml_lattice_upload_bits(thrml_lattice* lat, const uint32_t* host);
+int32_t thrml_lattice_download_bits(thrml_lattice* lat, uint32_t* host);
 /* Update one colour of stripe rows [row_begin, row_end) with the block key (asynchronous).  The other colour's halo
  * rows must be current. */
 int32_t thrml_lattice_update(thrml_lattice* lat, int32_t colour, uint64_t block_key, int64_t row_begin, int64_t row_end);
@@ -335,6 +370,23 @@ int32_t thrml_lattice_wrap_halo(thrml_lattice* lat, int32_t colour);
 /* sums_out[2][n_chains] (host, int64): per chain the sum of spins and the sum of s_i s_j over the bonds this stripe owns
  * (each bond is owned by its colour-0 end), from which magnetisation and energy follow. */
 int32_t thrml_lattice_observe(thrml_lattice* lat, int64_t* sums_out);
+/* The sweep driver inside the library: run_blocks (sampling.rs:81-106) = n_iters sweeps with keys key.split(n_iters), each
+ * sweep as described above.  comm = NULL (or a communicator of one rank): the stripe must hold the whole lattice and wraps
+ * onto itself.  Otherwise rank r of `comm` holds rows [r H / world, (r + 1) H / world) and the halo rows travel by grouped
+ * ncclSend / ncclRecv between ring neighbours: per colour the two boundary rows are updated first and exchanged on a side
+ * stream while the interior rows are updated.  record != 0 appends, after every sweep, this stripe's per-chain sum of spins
+ * and sum of bond products to a series kept on the device (thrml_lattice_observe's sums, without the host round trip).
+ * Asynchronous; collective over `comm`. */
+int32_t thrml_lattice_run_blocks(thrml_lattice* lat, uint64_t key, int64_t n_iters, thrml_comm* comm, int32_t record);
+/* Both colours' halo rows brought up to date (after an upload or a randomize): wrap, or one exchange per colour. */
+int32_t thrml_lattice_refresh_halos(thrml_lattice* lat, thrml_comm* comm);
+/* The recorded series, summed over the stripes of `comm` by ONE allreduce: series_out[record][2][chain] (host, int64) =
+ * whole-lattice (sum of spins, sum of bond products) after each recorded sweep; n_records_out = records held.  series_out
+ * may be NULL to query the count.  thrml_lattice_moments reduces the same series to the first and second moments over the
+ * recorded sweeps of m = sum s / N and e = -(J sum_bonds s_i s_j + b sum s) / N: moments_out[4][chain] = <m>, <m^2>, <e>, <e^2>. */
+int32_t thrml_lattice_read_series(thrml_lattice* lat, thrml_comm* comm, int64_t* series_out, int64_t capacity_records, int64_t* n_records_out);
+int32_t thrml_lattice_moments(thrml_lattice* lat, thrml_comm* comm, double* moments_out, int64_t* n_records_out);
+int32_t thrml_lattice_series_reset(thrml_lattice* lat);
 int32_t thrml_lattice_synchronize(thrml_lattice* lat);
 
 /* ------------------------------------------------------------------------------------------------
@@ -359,6 +411,13 @@ int32_t thrml_potts_update(thrml_potts* p, int32_t colour, uint64_t block_key);
 /* Category-marginal observer: counts[node][category] += chains in that category (asynchronous); read as int32. */
 int32_t thrml_potts_observe_marginals(thrml_potts* p);
 int32_t thrml_potts_read_marginals(thrml_potts* p, int32_t* counts_out, int64_t* n_obs_out);
+/* Drivers inside the library: run_blocks (sampling.rs:81-106, asynchronous) and sample_with_observation
+ * (sampling.rs:178-320) with the category-marginal observer — warm-up, observe, then n_samples - 1 times
+ * (steps_per_sample sweeps, observe).  With chains sharded over ranks, thrml_potts_marginals_allreduce adds the counts and
+ * the observation count over `comm` in place (one grouped ncclAllReduce). */
+int32_t thrml_potts_run_blocks(thrml_potts* p, uint64_t key, int64_t n_iters);
+int32_t thrml_potts_sample_with_marginals(thrml_potts* p, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample);
+int32_t thrml_potts_marginals_allreduce(thrml_potts* p, thrml_comm* comm);
 int32_t thrml_potts_synchronize(thrml_potts* p);
 
 #ifdef __cplusplus

@@ -71,3 +71,52 @@ def test_lattice_argument_checks(T):
         lattice.LatticeStripe(8, 64, 0, 8, 0.4, 0.0, 1.0, 6)
     with pytest.raises(T.ThrmlError, match="out of range"):
         lattice.LatticeStripe(8, 64, 4, 8, 0.4, 0.0, 1.0, 16)
+
+
+@pytest.mark.parametrize("H,W,chains", [(8, 64, 16), (6, 192, 4), (16, 128, 32)])
+def test_library_sweep_driver_bits_and_series(T, H, W, chains):
+    """thrml_lattice_run_blocks on a whole lattice = the per-colour calls driven from the host; the bit-packed transfers
+    round-trip; the recorded series holds, per sweep, the sums thrml_lattice_observe would report; moments follow."""
+    from thrml_rs_b200 import lattice
+    J, b, beta = 0.4407, 0.05, 1.0
+    rng = np.random.default_rng(H + W)
+    spins = rng.integers(0, 2, (chains, H, W)).astype(np.uint8)
+    host_driven = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=1)
+    host_driven.upload(spins)
+    lib = lattice.DistributedStripe(H, W, J, b, beta, chains, None)
+    bits = np.packbits(spins.reshape(chains, H, W // 32, 32), axis=3, bitorder="little").view("<u4").reshape(chains, H, W // 32)
+    lib.upload_bits(bits)
+    assert np.array_equal(lib.download_local(), spins)
+    assert np.array_equal(lib.stripe.download_bits(), bits)
+    want_series = []
+    for k in T.rng_split(31, 3):
+        host_driven.sample_blocks(int(k))
+        want_series.append(host_driven.observe())
+    lib.run_blocks(31, 3, record=True)
+    assert np.array_equal(lib.download_local(), host_driven.download())
+    series = lib.series()
+    assert series.shape == (3, 2, chains) and np.array_equal(series, np.stack(want_series))
+    mom, n_rec = lib.moments()
+    N = H * W
+    m = series[:, 0, :] / N
+    e = -(J * series[:, 1, :] + b * series[:, 0, :]) / N
+    assert n_rec == 3
+    assert np.allclose(mom, np.stack([m.mean(0), (m * m).mean(0), e.mean(0), (e * e).mean(0)]), rtol=1e-12, atol=1e-15)
+    lib.series_reset()
+    lib.run_blocks(32, 1, record=True)
+    assert lib.series().shape == (1, 2, chains)
+    # the series keeps growing past its first allocation
+    lib.series_reset()
+    lib.run_blocks(33, 1100, record=True)
+    s = 2 * lib.download_local().astype(np.int64) - 1
+    last = np.stack([s.sum(axis=(1, 2)), (s * np.roll(s, -1, axis=1)).sum(axis=(1, 2)) + (s * np.roll(s, -1, axis=2)).sum(axis=(1, 2))])
+    series = lib.series()
+    assert series.shape[0] == 1100 and np.array_equal(series[-1], last)
+
+
+def test_partial_stripe_needs_a_communicator(T):
+    from thrml_rs_b200 import lattice
+    s = lattice.LatticeStripe(8, 64, 0, 4, 0.4, 0.0, 1.0, 16)
+    from thrml_rs_b200._ffi import check
+    with pytest.raises(T.ThrmlError, match="communicator"):
+        check(T.lib().thrml_lattice_run_blocks(s.h, 1, 1, None, 0))

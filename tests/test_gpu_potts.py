@@ -80,3 +80,29 @@ def test_potts_randomize_and_schedule(T, O):
     s = lat.download().reshape(chains, 4, 4, 4)
     agree = np.mean([(s == np.roll(s, -1, axis=a)).mean() for a in (1, 2, 3)])
     assert agree > 0.6  # T = 2 I favours equal neighbours (uniform would give 0.25)
+
+
+def test_library_drivers_match_per_colour_calls(T):
+    """thrml_potts_run_blocks / thrml_potts_sample_with_marginals = the same key schedule driven colour by colour."""
+    from thrml_rs_b200 import potts
+    K, chains = 5, 48
+    rng = np.random.default_rng(4)
+    tables = rng.normal(0, 0.4, (3, K, K)).astype(np.float32)
+    unary = rng.normal(0, 0.2, (6 * 4 * 8, K)).astype(np.float32)
+    a = potts.PottsLattice(6, 4, 8, K, tables, unary, 0.8, chains)
+    b = potts.PottsLattice(6, 4, 8, K, tables, unary, 0.8, chains)
+    a.randomize(3)
+    b.randomize(3)
+    a.sample_with_marginals(21, 2, 3, 2)
+    k_warm, k_samp = [int(k) for k in T.rng_split(21, 2)]
+    for k in T.rng_split(k_warm, 2):
+        b.sample_blocks(int(k))
+    b.observe_marginals()
+    for ks in T.rng_split(k_samp, 2):
+        for k in T.rng_split(int(ks), 2):
+            b.sample_blocks(int(k))
+        b.observe_marginals()
+    assert np.array_equal(a.download(), b.download())
+    ca, na = a.read_marginals()
+    cb, nb = b.read_marginals()
+    assert na == nb == 3 * chains and np.array_equal(ca, cb)

@@ -22,6 +22,18 @@ def _worker(rank, world, port, total_chains, out_path):
     from oracle import oracle as O
     import models as M
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    # the product's communicator bootstrap: rank 0 draws the id inside the library (NCCL loaded at run time), the host
+    # group broadcasts it, every rank ends up with the same 128 bytes (joining the communicator itself needs GPUs)
+    box = [T.Comm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    uid = box[0]
+    assert isinstance(uid, bytes) and len(uid) == 128 and any(uid)
+    ids = [None] * world
+    dist.all_gather_object(ids, uid)
+    assert all(i == uid for i in ids)
+    from thrml_rs_b200 import lattice
+    rows = lattice.stripe_rows(64, world)
+    assert rows[rank] == (rank * 64 // world, 64 // world)
     desc, info = M.ising_random_graph(T, 80, 6, 9)
     om = M.fill(O.Model(desc["kinds"]), desc)
     n_local, start = sharding.shard_chains(total_chains, rank, world)

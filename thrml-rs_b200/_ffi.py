@@ -60,7 +60,16 @@ _SIGNATURES = {
     "thrml_state_download_f32": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_state_upload_u8": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_state_download_u8": (C.c_int32, [_P, C.c_int32, _P]),
+    "thrml_state_download_chains_u8": (C.c_int32, [_P, C.c_int32, C.c_int64, C.c_int64, _P]),
     "thrml_state_upload_u8_static": (C.c_int32, [_P, C.c_int32, _P]),
+    "thrml_state_upload_u8_many": (C.c_int32, [_P, _P, C.c_int32, _P]),
+    "thrml_state_upload_packed": (C.c_int32, [_P, _P, C.c_int32, _P]),
+    "thrml_comm_unique_id": (C.c_int32, [_P]),
+    "thrml_comm_create": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, _P]),
+    "thrml_comm_adopt": (C.c_int32, [_P, _P, _P]),
+    "thrml_comm_destroy": (None, [_P]),
+    "thrml_comm_info": (C.c_int32, [_P, _P, _P, _P]),
+    "thrml_moments_allreduce": (C.c_int32, [_P, _P]),
     "thrml_state_copy_block": (C.c_int32, [_P, _P, C.c_int32]),
     "thrml_hinton_init": (C.c_int32, [_P, _P, C.c_int32, _P, C.c_float, C.c_uint64, _P]),
     "thrml_state_randomize": (C.c_int32, [_P, C.c_uint64]),
@@ -83,12 +92,19 @@ _SIGNATURES = {
     "thrml_lattice_randomize": (C.c_int32, [_P, C.c_uint64]),
     "thrml_lattice_upload": (C.c_int32, [_P, _P]),
     "thrml_lattice_download": (C.c_int32, [_P, _P]),
+    "thrml_lattice_upload_bits": (C.c_int32, [_P, _P]),
+    "thrml_lattice_download_bits": (C.c_int32, [_P, _P]),
     "thrml_lattice_update": (C.c_int32, [_P, C.c_int32, C.c_uint64, C.c_int64, C.c_int64]),
     "thrml_lattice_halo_info": (C.c_int32, [_P, C.c_int32, _P, _P, _P, _P, _P]),
     "thrml_lattice_copy_halo": (C.c_int32, [_P, C.c_int32, _P, C.c_int32, C.c_int32]),
     "thrml_lattice_wrap_halo": (C.c_int32, [_P, C.c_int32]),
     "thrml_lattice_observe": (C.c_int32, [_P, _P]),
     "thrml_lattice_synchronize": (C.c_int32, [_P]),
+    "thrml_lattice_run_blocks": (C.c_int32, [_P, C.c_uint64, C.c_int64, _P, C.c_int32]),
+    "thrml_lattice_refresh_halos": (C.c_int32, [_P, _P]),
+    "thrml_lattice_read_series": (C.c_int32, [_P, _P, _P, C.c_int64, _P]),
+    "thrml_lattice_moments": (C.c_int32, [_P, _P, _P, _P]),
+    "thrml_lattice_series_reset": (C.c_int32, [_P]),
     "thrml_potts_create": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, C.c_float, C.c_int64, C.c_int64, _P]),
     "thrml_potts_destroy": (None, [_P]),
     "thrml_potts_randomize": (C.c_int32, [_P, C.c_uint64]),
@@ -98,6 +114,9 @@ _SIGNATURES = {
     "thrml_potts_observe_marginals": (C.c_int32, [_P]),
     "thrml_potts_read_marginals": (C.c_int32, [_P, _P, _P]),
     "thrml_potts_synchronize": (C.c_int32, [_P]),
+    "thrml_potts_run_blocks": (C.c_int32, [_P, C.c_uint64, C.c_int64]),
+    "thrml_potts_sample_with_marginals": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64]),
+    "thrml_potts_marginals_allreduce": (C.c_int32, [_P, _P]),
     "thrml_sample_with_observation": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, _P, _P, C.c_int32, _P, _P]),
 }
 

@@ -6,6 +6,7 @@
 #include <cstring>
 #include <memory>
 
+#include "comm.h"
 #include "ctx.h"
 #include "dense.cuh"
 #include "devbuf.h"
@@ -124,8 +125,10 @@ struct thrml_moments {
     DevBuf d_row_ptr, d_mem_sd, d_mem_pos;  // mode 0: CSR of members (class, position)
     bool all_spin = false, left_all_spin = false;  // every member of every (left-over) row is a spin read as +-1: the XOR kernel serves them
     DevBuf d_node_sd, d_node_pos;           // mode 1: observed nodes
-    DevBuf d_sums;                          // int64 [total_rows] (mode 0) or [nodes*K] (mode 1)
+    DevBuf d_sums;                          // int64 [total_rows] (mode 0) or [nodes*K] (mode 1), then two spare slots for the allreduce
+    DevBuf d_narrow;                        // int32 copy of the sums for the allreduce when every total fits 32 bits
     int64_t n_obs = 0;
+    int64_t sum_slots() const { return std::max<int64_t>(total_rows, 1); }
 };
 
 // ---------------------------------------------------------------------------------------------------------
@@ -678,6 +681,62 @@ int32_t thrml_state_upload_u8(thrml_state* s, int32_t block, const uint8_t* host
     s->touch(block);
     return THRML_OK;
 }
+// Several blocks in one call: every copy and layout kernel is queued on the context's stream and the host waits once at
+// the end instead of once per block.  hosts[i] is block blocks[i]'s [chain][node] byte array.
+int32_t thrml_state_upload_u8_many(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const uint8_t* const* hosts) {
+    if (!s || n_blocks < 0 || (n_blocks > 0 && (!blocks || !hosts))) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    size_t most = 0;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        if (int32_t rc = check_block(s, blocks[i])) return rc;
+        if (!hosts[i]) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+        most = std::max(most, static_cast<size_t>(s->prog->blocks[blocks[i]].n) * s->n_chains);
+    }
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    if (int32_t rc = need_scratch(s, most)) return rc;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        const BlockProg& bp = s->prog->blocks[blocks[i]];
+        // the scratch is reused block after block: stream order keeps each copy behind the previous block's transpose
+        CU_TRY(cudaMemcpyAsync(s->scratch.p, hosts[i], static_cast<size_t>(bp.n) * s->n_chains, cudaMemcpyHostToDevice, st));
+        dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((s->ld + 31) / 32));
+        k_transpose_in<<<grid, dim3(32, 8), 0, st>>>(s->scratch.as<uint8_t>(), s->rows(bp.sd) + bp.offset * s->ld, bp.n, s->n_chains, s->ld);
+        CU_TRY(cudaGetLastError());
+        s->touch(blocks[i]);
+    }
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+// Spin blocks as bits, the mirror of thrml_sample_states_packed: bits[i] is block blocks[i]'s [node][word] u32 array, word w
+// holding chains 32w .. 32w+31 (bit c & 31).  One bit per spin crosses the host link, and the device layout is already
+// chains-innermost, so the expansion is a streaming kernel with no transpose.
+int32_t thrml_state_upload_packed(thrml_state* s, const int32_t* blocks, int32_t n_blocks, const uint32_t* const* bits) {
+    if (!s || n_blocks < 0 || (n_blocks > 0 && (!blocks || !bits))) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    const int64_t words = (s->n_chains + 31) / 32;
+    size_t total = 0;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        if (int32_t rc = check_block(s, blocks[i])) return rc;
+        if (!bits[i]) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+        if (s->prog->blocks[blocks[i]].is_cat) return fail(THRML_ERR_UNSUPPORTED, "bit-packed upload is for spin blocks");
+        total += static_cast<size_t>(s->prog->blocks[blocks[i]].n) * words * 4;
+    }
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    if (int32_t rc = need_scratch(s, total)) return rc;  // all blocks side by side: the copies need not wait for the kernels
+    size_t at = 0;
+    for (int32_t i = 0; i < n_blocks; ++i) {
+        const BlockProg& bp = s->prog->blocks[blocks[i]];
+        const size_t bytes = static_cast<size_t>(bp.n) * words * 4;
+        uint32_t* stage = reinterpret_cast<uint32_t*>(s->scratch.as<uint8_t>() + at);
+        CU_TRY(cudaMemcpyAsync(stage, bits[i], bytes, cudaMemcpyHostToDevice, st));
+        const int64_t threads = bp.n * (s->ld >> 4);
+        k_unpack_rows<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, st>>>(stage, words, bp.n, s->ld, s->n_chains, s->rows(bp.sd) + bp.offset * s->ld);
+        CU_TRY(cudaGetLastError());
+        s->touch(blocks[i]);
+        at += bytes;
+    }
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
 // ---------------------------------------------------------------------------------------------------------
 // Upload without any allocation.
 //
@@ -734,6 +793,23 @@ int32_t thrml_state_download_u8(thrml_state* s, int32_t block, uint8_t* host) {
     if (int32_t rc = need_scratch(s, bytes)) return rc;
     dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((s->n_chains + 31) / 32));
     k_transpose_out<<<grid, dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->scratch.as<uint8_t>(), bp.n, s->n_chains, s->ld);
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(host, s->scratch.p, bytes, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
+}
+// A range of chains of one block, host layout [chain - chain_begin][node].
+int32_t thrml_state_download_chains_u8(thrml_state* s, int32_t block, int64_t chain_begin, int64_t n_chains, uint8_t* host) {
+    if (int32_t rc = check_block(s, block)) return rc;
+    if (!host) return fail(THRML_ERR_INVALID_ARG, "null host buffer");
+    if (chain_begin < 0 || n_chains < 1 || chain_begin + n_chains > s->n_chains) return fail(THRML_ERR_INVALID_ARG, "chain range out of the state");
+    const BlockProg& bp = s->prog->blocks[block];
+    cudaStream_t st = s->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    const size_t bytes = static_cast<size_t>(bp.n) * n_chains;
+    if (int32_t rc = need_scratch(s, bytes)) return rc;
+    dim3 grid(static_cast<unsigned>((bp.n + 31) / 32), static_cast<unsigned>((n_chains + 31) / 32));
+    k_transpose_out<<<grid, dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld + chain_begin, s->scratch.as<uint8_t>(), bp.n, n_chains, s->ld);
     CU_TRY(cudaGetLastError());
     CU_TRY(cudaMemcpyAsync(host, s->scratch.p, bytes, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));
@@ -1684,7 +1760,7 @@ int32_t thrml_moments_create(thrml_program* p, int32_t n_types, const int64_t* r
     if (int32_t rc = upload(m->d_row_ptr, m->total_rows ? row_ptr : &zero, static_cast<size_t>(m->total_rows + 1) * 8, st)) return rc;
     if (int32_t rc = upload(m->d_mem_sd, sd.data(), sd.size() * 4, st)) return rc;
     if (int32_t rc = upload(m->d_mem_pos, pos.data(), pos.size() * 4, st)) return rc;
-    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(std::max<int64_t>(m->total_rows, 1)) * 8)) return rc;
+    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(m->sum_slots() + 2) * 8)) return rc;
     CU_TRY(cudaMemsetAsync(m->d_sums.p, 0, m->d_sums.bytes, st));
     CU_TRY(cudaStreamSynchronize(st));
     *out = m.release();
@@ -1712,7 +1788,7 @@ int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t 
     cudaStream_t st = p->ctx->stream;
     if (int32_t rc = upload(m->d_node_sd, sd.data(), sd.size() * 4, st)) return rc;
     if (int32_t rc = upload(m->d_node_pos, pos.data(), pos.size() * 4, st)) return rc;
-    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(m->total_rows) * 8)) return rc;
+    if (int32_t rc = m->d_sums.alloc(static_cast<size_t>(m->sum_slots() + 2) * 8)) return rc;
     CU_TRY(cudaMemsetAsync(m->d_sums.p, 0, m->d_sums.bytes, st));
     CU_TRY(cudaStreamSynchronize(st));
     *out = m.release();
@@ -1782,6 +1858,48 @@ int32_t thrml_moments_device_buffer(thrml_moments* m, void** dev_ptr_out, int64_
     if (!m) return fail(THRML_ERR_INVALID_ARG, "null moments");
     if (dev_ptr_out) *dev_ptr_out = m->d_sums.p;
     if (count_out) *count_out = m->total_rows;
+    return THRML_OK;
+}
+// The one collective of the chain-parallel path: sums (and the observation count) added over the ranks of `comm`, in
+// place on every rank.  Two tiny reductions first agree on the total and the largest per-rank observation count; when
+// no total can leave 32 bits the sums travel as int32 (half the bytes), else as int64.  Every rank takes the same branch
+// because the decision uses only reduced values.
+int32_t thrml_moments_allreduce(thrml_moments* m, thrml_comm* comm) {
+    if (!m || !comm) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (comm->ctx != m->prog->ctx) return fail(THRML_ERR_INVALID_ARG, "communicator and observer belong to different contexts");
+    if (comm->world == 1) return THRML_OK;
+    const NcclApi* api = nccl_api();
+    if (!api) return THRML_ERR_NCCL;
+    CU_TRY(cudaSetDevice(m->device));
+    cudaStream_t st = m->prog->ctx->stream;
+    long long* sums = m->d_sums.as<long long>();
+    long long* slots = sums + m->sum_slots();
+    const long long mine[2] = {m->n_obs, m->n_obs};
+    CU_TRY(cudaMemcpyAsync(slots, mine, sizeof(mine), cudaMemcpyHostToDevice, st));
+    NCCL_TRY(api, GroupStart());
+    NCCL_TRY(api, AllReduce(slots, slots, 1, ncclInt64, ncclSum, comm->nccl, st));
+    NCCL_TRY(api, AllReduce(slots + 1, slots + 1, 1, ncclInt64, ncclMax, comm->nccl, st));
+    NCCL_TRY(api, GroupEnd());
+    long long got[2] = {0, 0};
+    CU_TRY(cudaMemcpyAsync(got, slots, sizeof(got), cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    const int64_t rows = m->total_rows;
+    if (rows > 0) {
+        // |sum| of a row on one rank <= that rank's observation count (products of +-1, or category counts)
+        const bool fits32 = (m->spin_transform || m->mode == 1) && got[1] * static_cast<long long>(comm->world) < (1LL << 31);
+        if (fits32) {
+            if (int32_t rc = m->d_narrow.reserve(static_cast<size_t>(rows) * 4)) return rc;
+            const unsigned grid = static_cast<unsigned>((rows + 255) / 256);
+            k_narrow_i64<<<grid, 256, 0, st>>>(sums, m->d_narrow.as<int32_t>(), rows);
+            CU_TRY(cudaGetLastError());
+            NCCL_TRY(api, AllReduce(m->d_narrow.p, m->d_narrow.p, static_cast<size_t>(rows), ncclInt32, ncclSum, comm->nccl, st));
+            k_widen_i32<<<grid, 256, 0, st>>>(m->d_narrow.as<int32_t>(), sums, rows);
+            CU_TRY(cudaGetLastError());
+        } else {
+            NCCL_TRY(api, AllReduce(sums, sums, static_cast<size_t>(rows), ncclInt64, ncclSum, comm->nccl, st));
+        }
+    }
+    m->n_obs = got[0];
     return THRML_OK;
 }
 int32_t thrml_moments_fused_info(const thrml_moments* m, int64_t* n_fused_rows, int64_t* n_other_rows) {

@@ -14,6 +14,7 @@
 #include <memory>
 #include <vector>
 
+#include "comm.h"
 #include "ctx.h"
 #include "devbuf.h"
 #include "device_math.cuh"
@@ -196,6 +197,48 @@ __global__ void k_lattice_unpack(const uint32_t* p0, const uint32_t* p1, uint8_t
 
 }  // namespace
 
+// Bit-packed host layout: bits[chain][stripe row][W / 32] u32, bit k of word v = column 32 v + k.  A plane word holds 32
+// spins of one colour: columns 2 (32 w + k) + p, i.e. the bits of parity p of host words 2w and 2w + 1.
+__device__ __forceinline__ uint32_t even_bits(uint32_t x) {  // bits 0, 2, 4, ... of x packed into the low 16 bits
+    x &= 0x55555555u;
+    x = (x | (x >> 1)) & 0x33333333u;
+    x = (x | (x >> 2)) & 0x0f0f0f0fu;
+    x = (x | (x >> 4)) & 0x00ff00ffu;
+    x = (x | (x >> 8)) & 0x0000ffffu;
+    return x;
+}
+__device__ __forceinline__ uint32_t spread_bits(uint32_t x) {  // the low 16 bits of x moved to bits 0, 2, 4, ...
+    x &= 0x0000ffffu;
+    x = (x | (x << 8)) & 0x00ff00ffu;
+    x = (x | (x << 4)) & 0x0f0f0f0fu;
+    x = (x | (x << 2)) & 0x33333333u;
+    x = (x | (x << 1)) & 0x55555555u;
+    return x;
+}
+__global__ void k_lattice_pack_bits(const uint32_t* host_order, uint32_t* p0, uint32_t* p1, int64_t row0, int32_t n_rows, int32_t words, int32_t chains) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= static_cast<int64_t>(n_rows) * words * chains) return;
+    const int chain = static_cast<int>(gid % chains), w = static_cast<int>((gid / chains) % words), r = static_cast<int>(gid / (static_cast<int64_t>(chains) * words));
+    const uint32_t* src = host_order + (static_cast<int64_t>(chain) * n_rows + r) * (2 * words) + 2 * w;
+    const uint32_t a = src[0], b = src[1];
+    const uint32_t even = even_bits(a) | (even_bits(b) << 16), odd = even_bits(a >> 1) | (even_bits(b >> 1) << 16);
+    const int p = static_cast<int>((row0 + r) & 1);  // colour 0 sits on the columns of parity p in this row
+    const int64_t at = (static_cast<int64_t>(r + 1) * words + w) * chains + chain;
+    p0[at] = p ? odd : even;
+    p1[at] = p ? even : odd;
+}
+__global__ void k_lattice_unpack_bits(const uint32_t* p0, const uint32_t* p1, uint32_t* host_order, int64_t row0, int32_t n_rows, int32_t words, int32_t chains) {
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= static_cast<int64_t>(n_rows) * words * chains) return;
+    const int chain = static_cast<int>(gid % chains), w = static_cast<int>((gid / chains) % words), r = static_cast<int>(gid / (static_cast<int64_t>(chains) * words));
+    const int64_t at = (static_cast<int64_t>(r + 1) * words + w) * chains + chain;
+    const int p = static_cast<int>((row0 + r) & 1);
+    const uint32_t even = p ? p1[at] : p0[at], odd = p ? p0[at] : p1[at];
+    uint32_t* dst = host_order + (static_cast<int64_t>(chain) * n_rows + r) * (2 * words) + 2 * w;
+    dst[0] = spread_bits(even) | (spread_bits(odd) << 1);
+    dst[1] = spread_bits(even >> 16) | (spread_bits(odd >> 16) << 1);
+}
+
 struct thrml_lattice {
     thrml_ctx* ctx = nullptr;
     int device = 0;
@@ -203,7 +246,19 @@ struct thrml_lattice {
     int32_t words = 0;
     DevBuf plane[2], lut, order, obs, scratch;
     size_t row_bytes = 0;  // one row of one colour
+    float coupling = 0.f, bias = 0.f;
+    // sweep driver: halo exchange on a side stream, overlapped with the interior rows
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_edge = nullptr, ev_halo = nullptr;
+    // per-sweep observable series: record t holds, per chain, this stripe's sum of spins and sum of bond products
+    DevBuf series;
+    int64_t series_len = 0, series_cap = 0;
     uint32_t* p(int c) const { return static_cast<uint32_t*>(plane[c].p); }
+    ~thrml_lattice() {
+        if (ev_edge) cudaEventDestroy(ev_edge);
+        if (ev_halo) cudaEventDestroy(ev_halo);
+        if (side) cudaStreamDestroy(side);
+    }
 };
 
 static int32_t lat_alloc(DevBuf& b, size_t bytes) { return b.alloc(bytes); }
@@ -224,6 +279,7 @@ int32_t thrml_lattice_create(thrml_ctx* ctx, int64_t height, int64_t width, int6
     L->ctx = ctx;
     L->device = ctx->device;
     L->H = height; L->W = width; L->row0 = row_begin; L->n_rows = n_rows; L->n_chains = n_chains; L->chain_offset = chain_offset;
+    L->coupling = coupling; L->bias = bias;
     L->words = static_cast<int32_t>(width / 64);
     L->row_bytes = static_cast<size_t>(L->words) * n_chains * 4;
     for (int c = 0; c < 2; ++c) {
@@ -308,6 +364,35 @@ int32_t thrml_lattice_download(thrml_lattice* L, uint8_t* host) {
     return THRML_OK;
 }
 
+// The same state as bits: host layout bits[chain][stripe row][W / 32] u32, bit k of word v = column 32 v + k (one bit per spin
+// over the host link instead of one byte).
+int32_t thrml_lattice_upload_bits(thrml_lattice* L, const uint32_t* host) {
+    if (!L || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(L->device));
+    const size_t bytes = static_cast<size_t>(L->n_chains) * L->n_rows * (L->W / 8);
+    if (int32_t rc = lat_scratch(L, bytes)) return rc;
+    CU_TRY(cudaMemcpyAsync(L->scratch.p, host, bytes, cudaMemcpyHostToDevice, L->ctx->stream));
+    const int64_t threads = L->n_rows * L->words * L->n_chains;
+    k_lattice_pack_bits<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, L->ctx->stream>>>(static_cast<const uint32_t*>(L->scratch.p), L->p(0), L->p(1), L->row0,
+                                                                                                static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+int32_t thrml_lattice_download_bits(thrml_lattice* L, uint32_t* host) {
+    if (!L || !host) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    CU_TRY(cudaSetDevice(L->device));
+    const size_t bytes = static_cast<size_t>(L->n_chains) * L->n_rows * (L->W / 8);
+    if (int32_t rc = lat_scratch(L, bytes)) return rc;
+    const int64_t threads = L->n_rows * L->words * L->n_chains;
+    k_lattice_unpack_bits<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), static_cast<uint32_t*>(L->scratch.p), L->row0,
+                                                                                                  static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains));
+    CU_TRY(cudaGetLastError());
+    CU_TRY(cudaMemcpyAsync(host, L->scratch.p, bytes, cudaMemcpyDeviceToHost, L->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+
 int32_t thrml_lattice_halo_info(thrml_lattice* L, int32_t colour, void** send_top, void** send_bottom, void** recv_top, void** recv_bottom, int64_t* row_bytes) {
     if (!L || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad halo query");
     uint8_t* base = static_cast<uint8_t*>(L->plane[colour].p);
@@ -370,6 +455,170 @@ int32_t thrml_lattice_copy_halo(thrml_lattice* dst, int32_t which_dst, const thr
     CU_TRY(cudaMemcpyAsync(d, s_, dst->row_bytes, cudaMemcpyDeviceToDevice, dst->ctx->stream));
     return THRML_OK;
 }
+// ---------------------------------------------------------------------------------------------------------
+// Sweep driver inside the library (run_blocks, sampling.rs:81-106, over sample_blocks, sampling.rs:28-63).
+// ---------------------------------------------------------------------------------------------------------
+static int32_t lat_update_rows(thrml_lattice* L, int32_t colour, uint64_t block_key, int64_t r0, int64_t r1) { return thrml_lattice_update(L, colour, block_key, r0, r1); }
+
+// This stripe's first row of `colour` goes to the stripe above (into its lower halo), its last row to the stripe below
+// (into its upper halo); the matching rows arrive from both.  One NCCL group on `st`.  With two stripes both neighbours
+// are the same rank and messages between one pair match in issue order, so the receives are posted in the order the
+// peer sends: its first row (this stripe's lower halo), then its last row (this stripe's upper halo).
+static int32_t lat_exchange(thrml_lattice* L, int32_t colour, thrml_comm* comm, cudaStream_t st) {
+    const NcclApi* api = nccl_api();
+    if (!api) return THRML_ERR_NCCL;
+    uint8_t* base = static_cast<uint8_t*>(L->plane[colour].p);
+    const int up = (comm->rank + comm->world - 1) % comm->world, down = (comm->rank + 1) % comm->world;
+    NCCL_TRY(api, GroupStart());
+    NCCL_TRY(api, Send(base + L->row_bytes, L->row_bytes, ncclUint8, up, comm->nccl, st));
+    NCCL_TRY(api, Send(base + L->row_bytes * L->n_rows, L->row_bytes, ncclUint8, down, comm->nccl, st));
+    NCCL_TRY(api, Recv(base + L->row_bytes * (L->n_rows + 1), L->row_bytes, ncclUint8, down, comm->nccl, st));
+    NCCL_TRY(api, Recv(base, L->row_bytes, ncclUint8, up, comm->nccl, st));
+    NCCL_TRY(api, GroupEnd());
+    return THRML_OK;
+}
+static int32_t lat_check_comm(const thrml_lattice* L, const thrml_comm* comm) {
+    const bool whole = L->n_rows == L->H;
+    if (!comm || comm->world == 1) {
+        if (!whole) return fail(THRML_ERR_INVALID_ARG, "a stripe that holds part of the lattice needs a communicator for its halo rows");
+        return THRML_OK;
+    }
+    if (comm->ctx != L->ctx) return fail(THRML_ERR_INVALID_ARG, "communicator and lattice belong to different contexts");
+    if (whole || L->H % comm->world || L->n_rows != L->H / comm->world || L->row0 != comm->rank * L->n_rows)
+        return fail(THRML_ERR_INVALID_ARG, "with a communicator, rank r must hold rows [r * H / world, (r + 1) * H / world)");
+    return THRML_OK;
+}
+static int32_t lat_refresh_halos(thrml_lattice* L, int32_t colour, thrml_comm* comm) {
+    if (!comm || comm->world == 1) return thrml_lattice_wrap_halo(L, colour);
+    return lat_exchange(L, colour, comm, L->ctx->stream);
+}
+static int32_t lat_record(thrml_lattice* L) {
+    const size_t rec = static_cast<size_t>(2 * L->n_chains) * 8;
+    if (L->series_len == L->series_cap) {  // grow, keeping the records
+        const int64_t cap = std::max<int64_t>(1024, 2 * L->series_cap);
+        DevBuf bigger;
+        if (int32_t rc = bigger.alloc(static_cast<size_t>(cap) * rec)) return rc;
+        CU_TRY(cudaMemsetAsync(bigger.p, 0, bigger.bytes, L->ctx->stream));
+        if (L->series_len > 0) CU_TRY(cudaMemcpyAsync(bigger.p, L->series.p, static_cast<size_t>(L->series_len) * rec, cudaMemcpyDeviceToDevice, L->ctx->stream));
+        CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+        std::swap(L->series.p, bigger.p);
+        std::swap(L->series.bytes, bigger.bytes);
+        L->series_cap = cap;
+    }
+    const int64_t cells = L->n_rows * L->words;
+    const int ctas = static_cast<int>(std::min<int64_t>((cells * L->n_chains + 255) / 256, 4096));
+    k_lattice_observe<<<ctas, 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), L->row0, static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains),
+                                                        static_cast<long long*>(L->series.p) + L->series_len * 2 * L->n_chains);
+    CU_TRY(cudaGetLastError());
+    ++L->series_len;
+    return THRML_OK;
+}
+
+int32_t thrml_lattice_refresh_halos(thrml_lattice* L, thrml_comm* comm) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (int32_t rc = lat_check_comm(L, comm)) return rc;
+    CU_TRY(cudaSetDevice(L->device));
+    for (int colour = 0; colour < 2; ++colour)
+        if (int32_t rc = lat_refresh_halos(L, colour, comm)) return rc;
+    return THRML_OK;
+}
+
+int32_t thrml_lattice_run_blocks(thrml_lattice* L, uint64_t key, int64_t n_iters, thrml_comm* comm, int32_t record) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (n_iters < 0) return fail(THRML_ERR_INVALID_ARG, "n_iters must be non-negative");
+    if (int32_t rc = lat_check_comm(L, comm)) return rc;
+    CU_TRY(cudaSetDevice(L->device));
+    const bool dist = comm && comm->world > 1;
+    const bool overlap = dist && L->n_rows >= 4;
+    if (overlap && !L->side) {
+        CU_TRY(cudaStreamCreateWithFlags(&L->side, cudaStreamNonBlocking));
+        CU_TRY(cudaEventCreateWithFlags(&L->ev_edge, cudaEventDisableTiming));
+        CU_TRY(cudaEventCreateWithFlags(&L->ev_halo, cudaEventDisableTiming));
+    }
+    cudaStream_t st = L->ctx->stream;
+    std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
+    rng_split(key, n_iters, keys.data());  // run_blocks: key.split(n_iters)
+    for (int64_t it = 0; it < n_iters; ++it) {
+        uint64_t k2[2];
+        rng_split(keys[it], 2, k2);  // sample_blocks: one key per free block
+        for (int colour = 0; colour < 2; ++colour) {
+            if (!overlap) {
+                if (int32_t rc = lat_update_rows(L, colour, k2[colour], 0, L->n_rows)) return rc;
+                if (int32_t rc = lat_refresh_halos(L, colour, comm)) return rc;
+                continue;
+            }
+            // boundary rows first; they travel on the side stream while the interior rows are updated
+            if (int32_t rc = lat_update_rows(L, colour, k2[colour], 0, 1)) return rc;
+            if (int32_t rc = lat_update_rows(L, colour, k2[colour], L->n_rows - 1, L->n_rows)) return rc;
+            CU_TRY(cudaEventRecord(L->ev_edge, st));
+            CU_TRY(cudaStreamWaitEvent(L->side, L->ev_edge, 0));
+            if (int32_t rc = lat_exchange(L, colour, comm, L->side)) return rc;
+            CU_TRY(cudaEventRecord(L->ev_halo, L->side));
+            if (int32_t rc = lat_update_rows(L, colour, k2[colour], 1, L->n_rows - 1)) return rc;
+            CU_TRY(cudaStreamWaitEvent(st, L->ev_halo, 0));  // the other colour reads these halo rows next
+        }
+        if (record)
+            if (int32_t rc = lat_record(L)) return rc;
+    }
+    return THRML_OK;
+}
+
+int32_t thrml_lattice_series_reset(thrml_lattice* L) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(L->device));
+    if (L->series.p) CU_TRY(cudaMemsetAsync(L->series.p, 0, L->series.bytes, L->ctx->stream));
+    L->series_len = 0;
+    return THRML_OK;
+}
+
+// The recorded series summed over the stripes of `comm` (one allreduce of the whole series), on the host:
+// series_out[record][2][chain] int64 = (sum of spins, sum of bond products) of the whole lattice after each recorded sweep.
+int32_t thrml_lattice_read_series(thrml_lattice* L, thrml_comm* comm, int64_t* series_out, int64_t capacity_records, int64_t* n_records_out) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (int32_t rc = lat_check_comm(L, comm)) return rc;
+    if (n_records_out) *n_records_out = L->series_len;
+    if (!series_out || L->series_len == 0) return THRML_OK;
+    if (capacity_records < L->series_len) return fail(THRML_ERR_INVALID_ARG, "series buffer holds fewer records than were recorded");
+    CU_TRY(cudaSetDevice(L->device));
+    const size_t count = static_cast<size_t>(L->series_len) * 2 * L->n_chains;
+    const void* src = L->series.p;
+    if (comm && comm->world > 1) {
+        const NcclApi* api = nccl_api();
+        if (!api) return THRML_ERR_NCCL;
+        if (int32_t rc = lat_scratch(L, count * 8)) return rc;
+        NCCL_TRY(api, AllReduce(L->series.p, L->scratch.p, count, ncclInt64, ncclSum, comm->nccl, L->ctx->stream));
+        src = L->scratch.p;
+    }
+    CU_TRY(cudaMemcpyAsync(series_out, src, count * 8, cudaMemcpyDeviceToHost, L->ctx->stream));
+    CU_TRY(cudaStreamSynchronize(L->ctx->stream));
+    return THRML_OK;
+}
+
+// First and second moments over the recorded sweeps of the magnetisation per spin m = sum s / N and the energy per spin
+// e = -(J sum_bonds s_i s_j + b sum s) / N (J, b without beta): moments_out[4][chain] = <m>, <m^2>, <e>, <e^2>.
+int32_t thrml_lattice_moments(thrml_lattice* L, thrml_comm* comm, double* moments_out, int64_t* n_records_out) {
+    if (!L || !moments_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    std::vector<int64_t> series(static_cast<size_t>(std::max<int64_t>(L->series_len, 1)) * 2 * L->n_chains);
+    int64_t n = 0;
+    if (int32_t rc = thrml_lattice_read_series(L, comm, series.data(), L->series_len, &n)) return rc;
+    if (n_records_out) *n_records_out = n;
+    const double N = static_cast<double>(L->H) * static_cast<double>(L->W);
+    for (int64_t c = 0; c < L->n_chains; ++c) {
+        double m1 = 0, m2 = 0, e1 = 0, e2 = 0;
+        for (int64_t t = 0; t < n; ++t) {
+            const double S = static_cast<double>(series[(t * 2 + 0) * L->n_chains + c]), B = static_cast<double>(series[(t * 2 + 1) * L->n_chains + c]);
+            const double m = S / N, e = -(static_cast<double>(L->coupling) * B + static_cast<double>(L->bias) * S) / N;
+            m1 += m; m2 += m * m; e1 += e; e2 += e * e;
+        }
+        const double inv = n > 0 ? 1.0 / static_cast<double>(n) : 0.0;
+        moments_out[0 * L->n_chains + c] = m1 * inv;
+        moments_out[1 * L->n_chains + c] = m2 * inv;
+        moments_out[2 * L->n_chains + c] = e1 * inv;
+        moments_out[3 * L->n_chains + c] = e2 * inv;
+    }
+    return THRML_OK;
+}
+
 int32_t thrml_lattice_synchronize(thrml_lattice* L) {
     if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(L->device));

@@ -231,3 +231,32 @@ __global__ void __launch_bounds__(256) k_pack_rows(const uint8_t* rows, int64_t 
         if (threadIdx.x == 0) out[row * words + wd] = word;
     }
 }
+
+// The inverse of k_pack_rows, for uploads: in[row][word] bit (c & 31) -> one byte per chain.  One thread expands 16
+// chains (one 16-byte store); chains beyond n_chains are written as zero.
+__global__ void __launch_bounds__(256) k_unpack_rows(const uint32_t* in, int64_t words, int64_t n_rows, int64_t ld, int64_t n_chains, uint8_t* rows) {
+    const int64_t chunks = ld >> 4;
+    const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (gid >= n_rows * chunks) return;
+    const int64_t row = gid / chunks, chunk = gid % chunks;
+    uint32_t bits = (__ldg(in + row * words + (chunk >> 1)) >> (16 * static_cast<int>(chunk & 1))) & 0xffffu;
+    const int64_t left = n_chains - 16 * chunk;
+    if (left < 16) bits &= left > 0 ? ((1u << static_cast<int>(left)) - 1u) : 0u;
+    uint32_t w[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const uint32_t nib = (bits >> (4 * q)) & 15u;
+        w[q] = (nib & 1u) | ((nib & 2u) << 7) | ((nib & 4u) << 14) | ((nib & 8u) << 21);
+    }
+    *reinterpret_cast<uint4*>(rows + row * ld + 16 * chunk) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// int64 <-> int32 views of the moment sums for the allreduce (used only when every total provably fits 32 bits).
+__global__ void k_narrow_i64(const long long* src, int32_t* dst, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = static_cast<int32_t>(src[i]);
+}
+__global__ void k_widen_i32(const int32_t* src, long long* dst, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = static_cast<long long>(src[i]);
+}

@@ -14,6 +14,7 @@
 #include <memory>
 #include <vector>
 
+#include "comm.h"
 #include "ctx.h"
 #include "devbuf.h"
 #include "device_math.cuh"
@@ -238,7 +239,7 @@ struct thrml_potts {
     int device = 0;
     int32_t nx = 0, ny = 0, nz = 0, K = 0;
     int64_t n = 0, n_chains = 0, chain_offset = 0, ld = 0, n_obs = 0;
-    DevBuf state, tables, pair_tables, unary, counts, scratch;
+    DevBuf state, tables, pair_tables, unary, counts, scratch, n_obs_dev;
     float table_mag = 0.0f;
     bool pair = false;  // pre-added direction tables exist (category counts with a compile-time kernel and 3 K^3 floats of shared memory to spare)
 };
@@ -353,6 +354,64 @@ int32_t thrml_potts_read_marginals(thrml_potts* P, int32_t* counts_out, int64_t*
     if (counts_out) CU_TRY(cudaMemcpyAsync(counts_out, P->counts.p, P->counts.bytes, cudaMemcpyDeviceToHost, P->ctx->stream));
     CU_TRY(cudaStreamSynchronize(P->ctx->stream));
     if (n_obs_out) *n_obs_out = P->n_obs;
+    return THRML_OK;
+}
+// run_blocks (sampling.rs:81-106): keys = key.split(n_iters); each sweep (sample_blocks, sampling.rs:28-63) splits its key
+// in two block keys, colour 0 then colour 1.  Asynchronous.
+int32_t thrml_potts_run_blocks(thrml_potts* P, uint64_t key, int64_t n_iters) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (n_iters < 0) return fail(THRML_ERR_INVALID_ARG, "n_iters must be non-negative");
+    std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
+    rng_split(key, n_iters, keys.data());
+    for (int64_t it = 0; it < n_iters; ++it) {
+        uint64_t k2[2];
+        rng_split(keys[it], 2, k2);
+        for (int colour = 0; colour < 2; ++colour)
+            if (int32_t rc = thrml_potts_update(P, colour, k2[colour])) return rc;
+    }
+    return THRML_OK;
+}
+// sample_with_observation (sampling.rs:178-320) with the category-marginal observer: key.split_two -> warm-up, observe,
+// then n_samples - 1 times (steps_per_sample sweeps, observe); nothing after the first observation when n_samples <= 1.
+int32_t thrml_potts_sample_with_marginals(thrml_potts* P, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
+    uint64_t two[2];
+    rng_split(key, 2, two);
+    if (int32_t rc = thrml_potts_run_blocks(P, two[0], n_warmup)) return rc;
+    if (int32_t rc = thrml_potts_observe_marginals(P)) return rc;
+    if (n_samples > 1) {
+        std::vector<uint64_t> keys(static_cast<size_t>(n_samples - 1));
+        rng_split(two[1], n_samples - 1, keys.data());
+        for (int64_t i = 0; i < n_samples - 1; ++i) {
+            if (int32_t rc = thrml_potts_run_blocks(P, keys[i], steps_per_sample)) return rc;
+            if (int32_t rc = thrml_potts_observe_marginals(P)) return rc;
+        }
+    }
+    CU_TRY(cudaStreamSynchronize(P->ctx->stream));
+    return THRML_OK;
+}
+// Chains sharded over the ranks of `comm`: one ncclAllReduce adds the category counts (int32) in place on every rank; the
+// observation counts are added alongside.
+int32_t thrml_potts_marginals_allreduce(thrml_potts* P, thrml_comm* comm) {
+    if (!P || !comm) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (comm->ctx != P->ctx) return fail(THRML_ERR_INVALID_ARG, "communicator and lattice belong to different contexts");
+    if (comm->world == 1) return THRML_OK;
+    const NcclApi* api = nccl_api();
+    if (!api) return THRML_ERR_NCCL;
+    CU_TRY(cudaSetDevice(P->device));
+    cudaStream_t st = P->ctx->stream;
+    if (int32_t rc = P->n_obs_dev.reserve(8)) return rc;
+    const long long mine = P->n_obs;
+    CU_TRY(cudaMemcpyAsync(P->n_obs_dev.p, &mine, 8, cudaMemcpyHostToDevice, st));
+    NCCL_TRY(api, GroupStart());
+    NCCL_TRY(api, AllReduce(P->n_obs_dev.p, P->n_obs_dev.p, 1, ncclInt64, ncclSum, comm->nccl, st));
+    NCCL_TRY(api, AllReduce(P->counts.p, P->counts.p, static_cast<size_t>(P->n) * P->K, ncclInt32, ncclSum, comm->nccl, st));
+    NCCL_TRY(api, GroupEnd());
+    long long total = 0;
+    CU_TRY(cudaMemcpyAsync(&total, P->n_obs_dev.p, 8, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    P->n_obs = total;
     return THRML_OK;
 }
 static int32_t potts_scratch(thrml_potts* P, size_t bytes) {

@@ -53,6 +53,51 @@ def default_context(device_id=None):
     return _default_ctx[device_id]
 
 
+class Comm:
+    """One rank of the library's NCCL communicator (thrml_comm); one process per GPU.
+
+    `Comm.unique_id()` is called on rank 0 and the 128 bytes are handed to the other ranks by the host's own means;
+    `Comm.from_torch(dist, ctx)` does that through an initialised torch.distributed group (any backend)."""
+
+    def __init__(self, ctx, unique_id, rank, world_size):
+        self.ctx, self.rank, self.world_size = ctx, int(rank), int(world_size)
+        uid = np.ascontiguousarray(np.frombuffer(bytes(unique_id), dtype=np.uint8))
+        if uid.size != 128:
+            raise ValueError("a communicator id is 128 bytes")
+        self.h = C.c_void_p()
+        check(lib().thrml_comm_create(ctx.h, ptr(uid), C.c_int32(rank), C.c_int32(world_size), C.byref(self.h)))
+
+    @staticmethod
+    def unique_id():
+        uid = np.zeros(128, dtype=np.uint8)
+        check(lib().thrml_comm_unique_id(ptr(uid)))
+        return uid.tobytes()
+
+    @classmethod
+    def from_torch(cls, dist, ctx):
+        """Rank 0 draws the id, torch.distributed broadcasts it, every rank joins."""
+        rank, world = dist.get_rank(), dist.get_world_size()
+        box = [cls.unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        return cls(ctx, box[0], rank, world)
+
+    def info(self):
+        r, w, v = C.c_int32(), C.c_int32(), C.c_int32()
+        check(lib().thrml_comm_info(self.h, C.byref(r), C.byref(w), C.byref(v)))
+        return dict(rank=r.value, world_size=w.value, nccl_version=v.value)
+
+    def close(self):
+        h, self.h = getattr(self, "h", None), None
+        if h and lib is not None:
+            lib().thrml_comm_destroy(h)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def rng_split(key, n):
     out = np.zeros(max(int(n), 0), dtype=np.uint64)
     check(lib().thrml_rng_split(C.c_uint64(int(key)), C.c_int64(int(n)), ptr(out)))
@@ -74,6 +119,16 @@ def greedy_coloring_arrays(n_nodes, edges):
     nc = C.c_int32()
     check(lib().thrml_greedy_coloring(C.c_int64(n_nodes), C.c_int64(len(edges)), ptr(edges), ptr(colour), C.byref(nc)))
     return colour, nc.value
+
+
+def pack_chains(state):
+    """`[chain][node]` 0/1 bytes -> uint32 `[node][ceil(chains / 32)]` with chain c at bit c & 31 of word c // 32."""
+    a = np.ascontiguousarray(state, dtype=np.uint8)
+    chains, n = a.shape
+    words = (chains + 31) // 32
+    padded = np.zeros((n, words * 32), dtype=np.uint8)
+    padded[:, :chains] = a.T
+    return np.packbits(padded, axis=1, bitorder="little").view("<u4").reshape(n, words)
 
 
 class Builder:
@@ -255,6 +310,22 @@ class ChainState:
             host = f32(host).reshape(self.n_chains, n)
             check(lib().thrml_state_upload_f32(self.h, C.c_int32(block), ptr(host)))
 
+    def upload_many(self, blocks, hosts):
+        """thrml_state_upload_u8_many: several blocks' `[chain][node]` byte arrays, one host wait for all of them."""
+        blocks = i32(blocks)
+        hosts = [np.ascontiguousarray(h, dtype=np.uint8).reshape(self.n_chains, self.program.block_len(int(b))) for b, h in zip(blocks, hosts)]
+        ptrs = (C.c_void_p * len(hosts))(*[h.ctypes.data for h in hosts])
+        check(lib().thrml_state_upload_u8_many(self.h, ptr(blocks), C.c_int32(len(hosts)), ptrs))
+
+    def upload_packed(self, blocks, bits):
+        """thrml_state_upload_packed: spin blocks as bits, `bits[i]` = uint32 `[node][ceil(chains / 32)]`, bit c & 31 of word
+        c // 32 = chain c (the layout `sample_states_packed` returns and `pack_chains` produces)."""
+        blocks = i32(blocks)
+        words = (self.n_chains + 31) // 32
+        bits = [np.ascontiguousarray(b, dtype=np.uint32).reshape(self.program.block_len(int(k)), words) for k, b in zip(blocks, bits)]
+        ptrs = (C.c_void_p * len(bits))(*[b.ctypes.data for b in bits])
+        check(lib().thrml_state_upload_packed(self.h, ptr(blocks), C.c_int32(len(bits)), ptrs))
+
     def upload_static(self, block, host):
         """thrml_state_upload_u8_static: the same upload staged in the library's fixed 4 MiB device array, for hosts that
         must not allocate device memory while running.  Blocks above 4 MiB (nodes x chains) raise ThrmlError."""
@@ -272,6 +343,12 @@ class ChainState:
             check(lib().thrml_state_download_u8(self.h, C.c_int32(block), ptr(out)))
         else:
             check(lib().thrml_state_download_f32(self.h, C.c_int32(block), ptr(out)))
+        return out
+
+    def download_chains(self, block, chain_begin, n_chains):
+        """uint8 `[n_chains][node]` of chains chain_begin .. chain_begin + n_chains - 1 of one block."""
+        out = np.zeros((int(n_chains), self.program.block_len(block)), dtype=np.uint8)
+        check(lib().thrml_state_download_chains_u8(self.h, C.c_int32(block), C.c_int64(chain_begin), C.c_int64(n_chains), ptr(out)))
         return out
 
     def hinton_init(self, blocks, biases, beta, key, inj_u=None):
@@ -422,6 +499,10 @@ class Moments:
         n = C.c_int64()
         check(lib().thrml_moments_read(self.h, C.c_int32(t), ptr(out), C.byref(n)))
         return out, n.value
+
+    def allreduce(self, comm):
+        """thrml_moments_allreduce: the one collective of the chain-parallel path (sums and observation count, in place)."""
+        check(lib().thrml_moments_allreduce(self.h, comm.h))
 
     def fused_info(self):
         """(rows accumulated by the update kernels, rows left to the observer kernel)."""

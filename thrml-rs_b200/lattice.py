@@ -1,10 +1,10 @@
 """Implicit bit-packed Ising lattice (thrml_lattice): stripes, halo refresh, sweep driver.
 
-`LatticeStripe` wraps one stripe handle.  `StripedLattice` drives the stripes of one process (a whole lattice, or several
-stripes on one device); `run_distributed_sweeps` drives one stripe per process with the halo rows exchanged point to
-point over torch.distributed (NCCL over NVLink on a multi-GPU box, gloo on CPU tensors is not applicable: stripes live on
-GPUs).  Key handling mirrors run_blocks / sample_blocks (crates/thrml-samplers/src/sampling.rs:28-106): keys =
-key.split(n_iters), then per sweep key.split(2) gives the two colours' block keys.
+`LatticeStripe` wraps one stripe handle.  `StripedLattice` drives several stripes inside one process (device-to-device
+halo copies; used to test that striping is invisible); `DistributedStripe` is one stripe per process, swept by the
+library's own driver (thrml_lattice_run_blocks: NCCL point-to-point halo rows between ring neighbours).  Key handling
+mirrors run_blocks / sample_blocks (crates/thrml-samplers/src/sampling.rs:28-106): keys = key.split(n_iters), then per
+sweep key.split(2) gives the two colours' block keys.
 """
 import ctypes as C
 
@@ -38,6 +38,16 @@ class LatticeStripe:
     def download(self):
         out = np.zeros((self.n_chains, self.n_rows, self.width), dtype=np.uint8)
         check(lib().thrml_lattice_download(self.h, ptr(out)))
+        return out
+
+    def upload_bits(self, bits):
+        """bits: uint32 [chain][stripe row][width / 32], bit k of word v = column 32 v + k."""
+        a = np.ascontiguousarray(bits, dtype=np.uint32).reshape(self.n_chains, self.n_rows, self.width // 32)
+        check(lib().thrml_lattice_upload_bits(self.h, ptr(a)))
+
+    def download_bits(self):
+        out = np.zeros((self.n_chains, self.n_rows, self.width // 32), dtype=np.uint32)
+        check(lib().thrml_lattice_download_bits(self.h, ptr(out)))
         return out
 
     def update(self, colour, block_key, row_begin=0, row_end=None):
@@ -126,98 +136,79 @@ class StripedLattice:
             s.synchronize()
 
 
-def _as_tensor(torch, addr, nbytes):
-    class _View:
-        __cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (addr, False), "version": 3}
-
-    return torch.as_tensor(_View(), device="cuda")
-
-
 class DistributedStripe:
-    """One stripe per process; halo rows travel with torch.distributed point-to-point operations (ring of stripes)."""
+    """One stripe per process (rank r of `comm` holds rows [r H / world, (r + 1) H / world)).  Everything that runs per
+    sweep — the colour updates, the boundary-rows-first halo exchange over NCCL, the observable series — is the
+    library's thrml_lattice_run_blocks; this class only holds the handles.  `comm` = None for a single process holding
+    the whole lattice."""
 
-    def __init__(self, height, width, coupling, bias, beta, n_chains, torch, dist, ctx=None):
-        self.torch, self.dist = torch, dist
-        self.rank, self.world = dist.get_rank(), dist.get_world_size()
+    def __init__(self, height, width, coupling, bias, beta, n_chains, comm=None, ctx=None):
+        self.comm = comm
+        self.rank = comm.rank if comm is not None else 0
+        self.world = comm.world_size if comm is not None else 1
         r0, n = stripe_rows(height, self.world)[self.rank]
         self.stripe = LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx)
-        self.stream = torch.cuda.ExternalStream(self.stripe.ctx.stream)
-        self.side = torch.cuda.Stream()
-        self.views = []
-        for colour in (0, 1):
-            info = self.stripe.halo_info(colour)
-            self.views.append({k: _as_tensor(torch, info[k], info["row_bytes"]) for k in ("send_top", "send_bottom", "recv_top", "recv_bottom")})
+        self.n_chains = n_chains
 
-    def refresh_halos(self, colour):
-        v, dist = self.views[colour], self.dist
-        up, down = (self.rank - 1) % self.world, (self.rank + 1) % self.world
-        with self.torch.cuda.stream(self.stream):
-            if self.world == 1:
-                self.stripe.wrap_halo(colour)
-                return
-            # My first row goes up and lands in the upper stripe's lower halo; my last row goes down into the lower
-            # stripe's upper halo.  With two stripes both neighbours are the same process and point-to-point messages
-            # between one pair match in issue order, so the receives are listed in the order the peer sends:
-            # its first row (my lower halo) before its last row (my upper halo).
-            ops = [dist.P2POp(dist.isend, v["send_top"], up), dist.P2POp(dist.isend, v["send_bottom"], down),
-                   dist.P2POp(dist.irecv, v["recv_bottom"], down), dist.P2POp(dist.irecv, v["recv_top"], up)]
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
+    def _comm(self):
+        return self.comm.h if self.comm is not None else None
+
+    def refresh_halos(self):
+        check(lib().thrml_lattice_refresh_halos(self.stripe.h, self._comm()))
 
     def randomize(self, key):
         self.stripe.randomize(key)
-        self.refresh_halos(0)
-        self.refresh_halos(1)
+        self.refresh_halos()
+
+    def upload(self, spins):
+        """spins: uint8 [chain][row][column] of the WHOLE lattice; this rank keeps its rows."""
+        s = self.stripe
+        s.upload(np.asarray(spins, dtype=np.uint8)[:, s.row_begin:s.row_begin + s.n_rows, :])
+        self.refresh_halos()
+
+    def upload_bits(self, bits):
+        """bits: uint32 [chain][row][width / 32] of THIS rank's rows."""
+        self.stripe.upload_bits(bits)
+        self.refresh_halos()
+
+    def run_blocks(self, key, n_iters, record=False):
+        check(lib().thrml_lattice_run_blocks(self.stripe.h, C.c_uint64(int(key)), C.c_int64(n_iters), self._comm(), C.c_int32(int(record))))
 
     def sample_blocks(self, key):
-        """One sweep.  Per colour the two boundary rows are updated first and sent while the interior rows are still
-        being updated: the exchange runs on a side stream and the next colour waits for it."""
+        """One sweep with the sweep key itself (run_blocks over one iteration would split it once more)."""
         k = _eng.rng_split(key, 2)
         n = self.stripe.n_rows
-        torch = self.torch
-        for colour in (0, 1):
-            if self.world == 1 or n < 4:
+        if self.world == 1:
+            for colour in (0, 1):
                 self.stripe.update(colour, int(k[colour]))
-                self.refresh_halos(colour)
-                continue
-            self.stripe.update(colour, int(k[colour]), 0, 1)
-            self.stripe.update(colour, int(k[colour]), n - 1, n)
-            self.side.wait_stream(self.stream)             # boundary rows are final
-            self._exchange(colour, self.side)
-            self.stripe.update(colour, int(k[colour]), 1, n - 1)
-            self.stream.wait_stream(self.side)             # halos of this colour are in place before the other colour reads them
+                self.stripe.wrap_halo(colour)
+            return
+        raise NotImplementedError("multi-rank stripes sweep through run_blocks")
 
-    def _exchange(self, colour, stream):
-        v, dist = self.views[colour], self.dist
-        up, down = (self.rank - 1) % self.world, (self.rank + 1) % self.world
-        with self.torch.cuda.stream(stream):
-            ops = [dist.P2POp(dist.isend, v["send_top"], up), dist.P2POp(dist.isend, v["send_bottom"], down),
-                   dist.P2POp(dist.irecv, v["recv_bottom"], down), dist.P2POp(dist.irecv, v["recv_top"], up)]
-            for req in dist.batch_isend_irecv(ops):
-                req.wait()
+    def series(self):
+        """Whole-lattice (sum of spins, sum of bond products) per recorded sweep and chain: int64 [records][2][chains]."""
+        n = C.c_int64()
+        check(lib().thrml_lattice_read_series(self.stripe.h, self._comm(), None, C.c_int64(0), C.byref(n)))
+        out = np.zeros((n.value, 2, self.n_chains), dtype=np.int64)
+        if n.value:
+            check(lib().thrml_lattice_read_series(self.stripe.h, self._comm(), ptr(out), C.c_int64(n.value), C.byref(n)))
+        return out
 
-    def run_blocks(self, key, n_iters):
-        for k in _eng.rng_split(key, n_iters) if n_iters > 0 else []:
-            self.sample_blocks(int(k))
+    def moments(self):
+        """(<m>, <m^2>, <e>, <e^2>) per chain over the recorded sweeps, float64 [4][chains], and the record count."""
+        out = np.zeros((4, self.n_chains), dtype=np.float64)
+        n = C.c_int64()
+        check(lib().thrml_lattice_moments(self.stripe.h, self._comm(), ptr(out), C.byref(n)))
+        return out, n.value
 
-    def observe(self):
-        """Whole-lattice sums: the stripes' sums added with one small allreduce."""
-        self.stream.synchronize()
-        local = self.torch.from_numpy(self.stripe.observe()).cuda()
-        if self.world > 1:
-            self.dist.all_reduce(local)
-        return local.cpu().numpy()
+    def series_reset(self):
+        check(lib().thrml_lattice_series_reset(self.stripe.h))
 
+    def observe_local(self):
+        return self.stripe.observe()
 
-def distributed_self_check(torch, dist, ctx=None, height=64, width=128, chains=16, sweeps=3):
-    """Small lattice sampled once as stripes over all ranks and once whole on every rank: the observables must agree
-    exactly (the states are a function of the keys alone, however the rows are sharded)."""
-    whole = StripedLattice(height, width, 0.4407, 0.05, 1.0, chains, 1, ctx)
-    whole.randomize(3)
-    whole.run_blocks(4, sweeps)
-    want = whole.observe()
-    part = DistributedStripe(height, width, 0.4407, 0.05, 1.0, chains, torch, dist, ctx)
-    part.randomize(3)
-    part.run_blocks(4, sweeps)
-    got = part.observe()
-    return bool(np.array_equal(got, want))
+    def download_local(self):
+        return self.stripe.download()
+
+    def synchronize(self):
+        self.stripe.synchronize()

@@ -1,7 +1,7 @@
-"""Implicit 3-D Potts lattice (thrml_potts): handle wrapper and the sweep / schedule driver.
-
-Key handling mirrors sample_blocks / run_blocks / sample_with_observation
-(crates/thrml-samplers/src/sampling.rs:28-320): per sweep key.split(2) gives the two colours' block keys.
+"""Implicit 3-D Potts lattice (thrml_potts): handle wrapper.  The sweep and schedule drivers live in the library
+(thrml_potts_run_blocks, thrml_potts_sample_with_marginals); key handling mirrors sample_blocks / run_blocks /
+sample_with_observation (crates/thrml-samplers/src/sampling.rs:28-320): per sweep key.split(2) gives the two colours'
+block keys.
 """
 import ctypes as C
 
@@ -45,22 +45,18 @@ class PottsLattice:
             check(lib().thrml_potts_update(self.h, C.c_int32(colour), C.c_uint64(int(k[colour]))))
 
     def run_blocks(self, key, n_iters):
-        for k in _eng.rng_split(key, n_iters) if n_iters > 0 else []:
-            self.sample_blocks(int(k))
+        """thrml_potts_run_blocks (asynchronous)."""
+        check(lib().thrml_potts_run_blocks(self.h, C.c_uint64(int(key)), C.c_int64(n_iters)))
 
     def observe_marginals(self):
         check(lib().thrml_potts_observe_marginals(self.h))
 
     def sample_with_marginals(self, key, n_warmup, n_samples, steps_per_sample):
-        """sample_with_observation with the category-marginal observer: observe after warm-up, then n_samples-1 times
-        (steps_per_sample sweeps, observe)."""
-        k_warm, k_samp = [int(k) for k in _eng.rng_split(key, 2)]
-        self.run_blocks(k_warm, n_warmup)
-        self.observe_marginals()
-        if n_samples > 1:
-            for k in _eng.rng_split(k_samp, n_samples - 1):
-                self.run_blocks(int(k), steps_per_sample)
-                self.observe_marginals()
+        """thrml_potts_sample_with_marginals: sample_with_observation with the category-marginal observer."""
+        check(lib().thrml_potts_sample_with_marginals(self.h, C.c_uint64(int(key)), C.c_int64(n_warmup), C.c_int64(n_samples), C.c_int64(steps_per_sample)))
+
+    def allreduce_marginals(self, comm):
+        check(lib().thrml_potts_marginals_allreduce(self.h, comm.h))
 
     def read_marginals(self):
         out = np.zeros((self.n, self.K), dtype=np.int32)
