@@ -517,6 +517,7 @@ def sparse_end_to_end(T, torch, program, model, chains, rank, ctx, args, dist, c
     d2h = (model["n"] + len(model["edges"])) * 8
     blocks = list(range(n_blocks))
     spec = W.ising_moment_arrays(model)
+    sums_host = [torch.empty(int(k), dtype=torch.int64, pin_memory=True) for k in spec[0]]
 
     def run(upload):
         best = None
@@ -528,11 +529,11 @@ def sparse_end_to_end(T, torch, program, model, chains, rank, ctx, args, dist, c
                 dist.barrier()
             t0 = time.perf_counter()
             upload(state)
-            state.sample_with_observation(5, 0, steps + 1, 1, moments=moments)  # observe, then `steps` x (sweep, observe)
+            state.sample_with_observation(5, 1, steps, 1, moments=moments)  # `steps` x (sweep, observe)
             if comm:
                 moments.allreduce(comm)
-            moments.read(0)
-            moments.read(1)
+            for t, buf in enumerate(sums_host):
+                moments.read(t, buf.numpy())
             ctx.synchronize()
             dt = max_over_ranks(torch, dist, time.perf_counter() - t0)
             best = dt if best is None else min(best, dt)
@@ -610,6 +611,12 @@ def run_rbm(T, torch, args, rank, world, device, dist, ctx, comm):
                         "call": "thrml_cd1_step with the visible data in pinned host memory and both correlation matrices read back"}})
     if not args.no_cpu_baseline:
         out["cpu_baseline"], _ = cpu_baseline(args, os.cpu_count() or 1)
+    if not args.no_parity:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import fullsize_checks as F
+        from oracle import oracle as O
+        del state, data
+        out["parity_check"] = F.dense_check(T, O, n_visible=nv, n_hidden=nh, chains=1024, tiles={"single": 0, "pair": 1, "auto": 2}[args.dense_tiles], ctx=ctx)
     return out
 
 

@@ -167,3 +167,92 @@ def lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4, ctx=None, J=0
     out["ok"] = bool(ok)
     out["seconds"] = round(time.time() - t0, 1)
     return out
+
+
+def _philox(c0, c1, c2, c3, k0, k1):
+    c0, c1, c2, c3 = [np.asarray(x, dtype=np.uint64) for x in np.broadcast_arrays(c0, c1, c2, c3)]
+    k0, k1 = np.uint64(k0), np.uint64(k1)
+    m32 = np.uint64(0xFFFFFFFF)
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * c0
+        p1 = np.uint64(0xCD9E8D57) * c2
+        c0, c1, c2, c3 = ((p1 >> np.uint64(32)) ^ c1 ^ k0) & m32, p1 & m32, ((p0 >> np.uint64(32)) ^ c3 ^ k1) & m32, p0 & m32
+        k0 = (k0 + np.uint64(0x9E3779B9)) & m32
+        k1 = (k1 + np.uint64(0xBB67AE85)) & m32
+    return c0, c1, c2, c3
+
+
+def spin_uniforms(n_nodes, chain_ids, key):
+    """u[chain][node] of the engine's spin noise mapping (24-bit uniforms), for the given global chain ids."""
+    node = np.arange(n_nodes, dtype=np.uint64)[None, :]
+    chain = np.asarray(chain_ids, dtype=np.uint64)[:, None]
+    words = _philox(node, chain >> np.uint64(2), 0, 0x5350494E, key & 0xFFFFFFFF, key >> 32)
+    sel = (chain & np.uint64(3)) + np.zeros_like(node)
+    r = np.choose(sel.astype(np.int64), words)
+    return (r >> np.uint64(8)).astype(np.float64) * 2.0 ** -24
+
+
+def dense_check(T, O, n_visible=784, n_hidden=4096, chains=1024, slice_chains=16, tiles=2, ctx=None):
+    """Dense bipartite path at the RBM configuration's layer sizes.  (1) The local fields the tensor-core kernel draws
+    from (bias + the f32 accumulator read out of tensor memory) against the oracle's f64 fields on two chain slices.
+    (2) The draws of both layers against the oracle's sampler on the same slices: a draw may differ only where the uniform
+    lies inside the window the two f32 fields' own errors open around the threshold; the window actually needed is
+    reported beside the count of draws that fall within 1e-6 of their threshold."""
+    from thrml_rs_b200 import workloads as W
+    t0 = time.time()
+    model = W.rbm_ising(n_visible, n_hidden)
+    program = T.Program(W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model), ctx)
+    assert program.enable_dense(False) == 2
+    program.set_option(T.OPT_DENSE_TILES, tiles)
+    om = W.fill_ising(O.Model(np.zeros(model["n"], np.int32)), model)
+    rng = np.random.default_rng(17)
+    init = [(rng.random((chains, n_visible)) < 0.13).astype(np.uint8), rng.integers(0, 2, (chains, n_hidden)).astype(np.uint8)]
+    state = T.ChainState(program, chains)
+    for b, a in enumerate(init):
+        state.upload(b, a)
+    Wm = model["W"].astype(np.float64)
+    sum_abs = [np.abs(Wm).sum(axis=1) + np.abs(model["b"][:n_visible]), np.abs(Wm).sum(axis=0) + np.abs(model["b"][n_visible:])]  # per node of block 0 / 1
+    out = {"workload": "rbm", "visible": n_visible, "hidden": n_hidden, "chains": chains, "tiles": {0: "single", 1: "pair", 2: "auto"}[tiles], "blocks": []}
+    ok = True
+    starts = sorted({0, (chains - slice_chains) // 16 * 16})
+    for block, key in ((1, 0xD0D0_0001), (0, 0xD0D0_0002)):
+        g_fields = state.fields(block)  # all chains, from tensor memory
+        rec = {"block": "hidden" if block == 1 else "visible", "reduction_length": int(n_visible if block == 1 else n_hidden)}
+        worst_abs = worst_rel = worst_scaled = 0.0
+        mism = within_1e6 = draws = 0
+        window_needed = 0.0
+        slices = []
+        for start in starts:
+            cnt = min(slice_chains, chains - start)
+            os_ = O.State(om, cnt, start, threads=cnt)
+            for b in range(2):
+                os_.set_block(b, state.download_chains(b, start, cnt).astype(np.float32))
+            o64, o32 = os_.fields(block)
+            g = g_fields[start:start + cnt].astype(np.float64)
+            err = np.abs(g - o64)
+            big = np.abs(o64) >= 0.01 * sum_abs[block][None, :]  # sums that do not cancel: the relative bound applies
+            worst_abs = max(worst_abs, float(err.max()))
+            worst_rel = max(worst_rel, float((err[big] / np.abs(o64[big])).max()) if big.any() else 0.0)
+            worst_scaled = max(worst_scaled, float((err / sum_abs[block][None, :]).max()))
+            slices.append((start, cnt, os_, o64, o32, g))
+        rec.update({"max_abs_field_error": worst_abs, "max_rel_field_error_where_not_cancelling": worst_rel, "max_field_error_over_sum_abs_terms": worst_scaled})
+        ok &= worst_rel <= 1e-5 and worst_scaled <= 1e-6
+        state.sample_single_block(block, key)
+        for start, cnt, os_, o64, o32, g in slices:
+            os_.sample_single_block(block, key)
+            got, want = state.download_chains(block, start, cnt), os_.get_block(block).astype(np.uint8)
+            u = np.clip(spin_uniforms(got.shape[1], np.arange(start, start + cnt), key), 1e-12, 1 - 1e-12)
+            gap = np.abs(np.log(u / (1 - u)) - 2 * o64)
+            draws += got.size
+            within_1e6 += int(np.count_nonzero(gap < 1e-6))
+            bad = got != want
+            mism += int(bad.sum())
+            if bad.any():
+                allowed = 2 * (np.abs(g - o64) + np.abs(o32.astype(np.float64) - o64)) + 2e-6
+                ok &= bool(np.all(gap[bad] <= allowed[bad]))
+                window_needed = max(window_needed, float(gap[bad].max()))
+        rec.update({"draws_checked": draws, "draws_within_1e-6_of_threshold": within_1e6, "mismatched_draws": mism, "largest_gap_of_a_mismatch": window_needed})
+        out["blocks"].append(rec)  # the next block's oracles are rebuilt from the device state, so a differing draw does not propagate
+    out["ok"] = bool(ok)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out

@@ -1,9 +1,11 @@
 """The dense bipartite (RBM-style) path: tcgen05 GEMM + sampling epilogue, integer tensor-core pair correlations, CD-1.
 
-Tolerances.  The tensor cores add the same exact products (bf16 coupling x +-1) as the gather kernel but in another order,
-so a local field can differ from the oracle's f64 field by about 1e-6 of the summed coupling magnitudes.  A sampled spin
-may therefore differ from the oracle's only where the uniform lies within that distance of the threshold:
-|logit(u) - 2*gamma| <= 2*(2e-6 * sum|w|) + 1e-6.  Pair correlations are integer counts and must match exactly.
+Tolerances.  The tensor cores add the same exact products (bf16 coupling x +-1) as the gather kernel but in another order.
+The fields the kernel draws from are read back out of tensor memory (thrml_fields_debug on a dense block) and compared
+with the oracle's f64 fields: within 1e-5 relative wherever the sum does not cancel, within 1e-6 of the summed term
+magnitudes everywhere.  A sampled spin may differ from the oracle's only where the uniform lies inside the window those
+two f32 fields' own measured errors open around the threshold: |logit(u) - 2 gamma_f64| <= 2 (|gamma_gpu - gamma_f64| +
+|gamma_oracle_f32 - gamma_f64|) + 2e-6.  Pair correlations are integer counts and must match exactly.
 """
 import numpy as np
 import pytest
@@ -63,19 +65,24 @@ def rbm(T, n_v, n_h, seed, sigma=0.1):
 
 def check_update(gs, os_, block, key, W_in, chains, n_blocks):
     """GPU dense update of `block` vs the oracle from the same state; returns the mismatch count."""
-    o64, _ = os_.fields(block)
+    o64, o32 = os_.fields(block)
+    gf = gs.fields(block).astype(np.float64)  # bias + f32 accumulator, out of tensor memory
+    scale = (np.abs(W_in).sum(axis=0) if block == 1 else np.abs(W_in).sum(axis=1)) + 0.2
+    err = np.abs(gf - o64)
+    assert (err / scale[None, :]).max() <= 1e-6
+    big = np.abs(o64) >= 0.01 * scale[None, :]
+    assert (err[big] / np.abs(o64[big])).max() <= 1e-5
     gs.sample_single_block(block, key)
     os_.sample_single_block(block, key)
     g, o = gs.download(block), os_.get_block(block)
     bad = np.argwhere(g != o)
     if len(bad):
         u = spin_uniforms(g.shape[1], chains, key)
-        scale = np.abs(W_in).sum(axis=0) if block == 1 else np.abs(W_in).sum(axis=1)
         for c, i in bad:
             uu = min(max(u[c, i], 1e-12), 1 - 1e-12)
             gap = abs(np.log(uu / (1 - uu)) - 2 * o64[c, i])
-            assert gap <= 2 * (2e-6 * scale[i]) + 1e-6, (c, i, gap)
-    assert len(bad) <= max(2, g.size // 2000)
+            assert gap <= 2 * (err[c, i] + abs(float(o32[c, i]) - o64[c, i])) + 2e-6, (c, i, gap)
+    assert len(bad) <= max(2, g.size // 20000)
     # resynchronise so later steps compare like with like
     gs.upload(block, o.astype(np.uint8))
     return len(bad)

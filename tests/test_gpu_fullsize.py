@@ -44,3 +44,11 @@ def test_potts_64_cubed(T, O):
 def test_lattice_2048_squared_whole_and_striped(T, O):
     res = F.lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4)
     assert res["ok"], res
+
+
+@pytest.mark.parametrize("tiles", [2, 0])
+def test_rbm_layer_sizes_fields_and_draws(T, O, tiles):
+    res = F.dense_check(T, O, n_visible=784, n_hidden=4096, chains=1024, tiles=tiles)
+    assert res["ok"], res
+    for blk in res["blocks"]:
+        assert blk["mismatched_draws"] <= 2, res

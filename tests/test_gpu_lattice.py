@@ -99,7 +99,7 @@ def test_library_sweep_driver_bits_and_series(T, H, W, chains):
     mom, n_rec = lib.moments()
     N = H * W
     m = series[:, 0, :] / N
-    e = -(J * series[:, 1, :] + b * series[:, 0, :]) / N
+    e = -(float(np.float32(J)) * series[:, 1, :] + float(np.float32(b)) * series[:, 0, :]) / N  # the handle keeps J and b as f32
     assert n_rec == 3
     assert np.allclose(mom, np.stack([m.mean(0), (m * m).mean(0), e.mean(0), (e * e).mean(0)]), rtol=1e-12, atol=1e-15)
     lib.series_reset()

@@ -34,7 +34,7 @@ constexpr int EPI_WARPS = 16;
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 24;  // hard cap on the number of parked waits of one mbar_wait (the time bound normally ends it first)
 
-enum Epilogue { EPI_SAMPLE = 0, EPI_CORR = 1 };
+enum Epilogue { EPI_SAMPLE = 0, EPI_CORR = 1, EPI_FIELDS = 2 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -153,6 +153,8 @@ struct GemmArgs {
     int32_t n_chains;
     int32_t corr_transposed;
     uint32_t* debug;          // nullable: the pair kernel records each CTA's TMEM base address here
+    // EPI_FIELDS
+    float* fields_out;        // [m_total = chains][n_total]: bias + accumulator, the local field the sampling epilogue would draw from
 };
 
 // In-quad 4x4 transpose: on return x[k] is the word this lane's position in its quad selects, taken from quad lane k.
@@ -254,6 +256,14 @@ __device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[
                 dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
                 dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
             }
+        }
+    } else if (EPI == EPI_FIELDS) {
+        // row = chain, columns = nodes: the field exactly as the sampling epilogue forms it (bias + f32 accumulator)
+        if (row < g.m_total) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (col0 + j < g.n_total)
+                    g.fields_out[static_cast<int64_t>(row) * g.n_total + col0 + j] = __fadd_rn(__ldg(g.bias + col0 + j), __uint_as_float(acc[j]));
         }
     } else {
         // row = node of block a, columns = nodes of block b; acc = N11 (int32)

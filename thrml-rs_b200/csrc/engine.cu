@@ -985,7 +985,34 @@ static int32_t launch_dense_pair(thrml_state* s, const CUtensorMap& ma, const CU
     return THRML_OK;
 }
 }  // extern "C++"
-// Tensor-core update of a dense bipartite block, in place.
+// Tensor-core update of a dense bipartite block, in place; with `fields` the same GEMM writes the local fields
+// (bias + accumulator, [chain][node] f32) instead of sampling.
+extern "C++" {
+template <int EPI>
+static int32_t dense_launch_any(thrml_state* s, const BlockProg& bp, const dense::GemmArgs& g) {
+    thrml_program* p = s->prog;
+    if (use_pair_tiles(p->dense_tiles, s->n_chains, p->blocks[bp.dense_src].n)) {
+        if (bp.dense_bn_pair == 256) return launch_dense_pair<EPI, 256>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+        if (bp.dense_bn_pair == 208) return launch_dense_pair<EPI, 208>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+        return launch_dense_pair<EPI, 128>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+    }
+    if (bp.dense_bn == 256) return launch_dense<EPI, 256>(s, s->map_image[bp.dense_src], bp.map_w, g);
+    return launch_dense<EPI, 128>(s, s->map_image[bp.dense_src], bp.map_w, g);
+}
+}  // extern "C++"
+static int32_t dense_fields(thrml_state* s, int32_t block, float* d_fields) {
+    thrml_program* p = s->prog;
+    const BlockProg& bp = p->blocks[block];
+    if (int32_t rc = ensure_err_flag(s)) return rc;
+    if (int32_t rc = ensure_image(s, bp.dense_src, true)) return rc;
+    dense::GemmArgs g{};
+    g.m_total = static_cast<int32_t>(s->n_chains);
+    g.n_total = static_cast<int32_t>(bp.n);
+    g.k_bytes = static_cast<int32_t>(p->blocks[bp.dense_src].n * 2);
+    g.bias = bp.d_dense_bias.as<float>();
+    g.fields_out = d_fields;
+    return dense_launch_any<dense::EPI_FIELDS>(s, bp, g);
+}
 static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t k1) {
     thrml_program* p = s->prog;
     const BlockProg& bp = p->blocks[block];
@@ -1011,17 +1038,7 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     }
     CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, p->ctx->stream));
     g.ones_out = s->ones[block]->as<int32_t>();
-    int32_t rc = THRML_OK;
-    if (use_pair_tiles(p->dense_tiles, s->n_chains, p->blocks[bp.dense_src].n)) {
-        if (bp.dense_bn_pair == 256) rc = launch_dense_pair<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
-        else if (bp.dense_bn_pair == 208) rc = launch_dense_pair<dense::EPI_SAMPLE, 208>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
-        else rc = launch_dense_pair<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
-    } else if (bp.dense_bn == 256) {
-        rc = launch_dense<dense::EPI_SAMPLE, 256>(s, s->map_image[bp.dense_src], bp.map_w, g);
-    } else {
-        rc = launch_dense<dense::EPI_SAMPLE, 128>(s, s->map_image[bp.dense_src], bp.map_w, g);
-    }
-    if (rc) return rc;
+    if (int32_t rc = dense_launch_any<dense::EPI_SAMPLE>(s, bp, g)) return rc;
     s->image_fresh[block] = write_image ? 1 : 0;
     s->ones_fresh[block] = 1;
     return THRML_OK;
@@ -1653,10 +1670,14 @@ int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out) {
     const size_t cnt = static_cast<size_t>(bp.n) * s->n_chains * (bp.is_cat ? bp.kind : 1);
     DevBuf tmp;
     if (int32_t rc = tmp.alloc(cnt * 4)) return rc;
-    if (int32_t rc = launch_block(s, block, 0, nullptr, nullptr, tmp.as<float>())) return rc;
+    if (bp.kernel == 3) {  // a block on the dense path reports the fields its tensor-core kernel draws from
+        if (int32_t rc = dense_fields(s, block, tmp.as<float>())) return rc;
+    } else if (int32_t rc = launch_block(s, block, 0, nullptr, nullptr, tmp.as<float>())) {
+        return rc;
+    }
     CU_TRY(cudaMemcpyAsync(out, tmp.p, cnt * 4, cudaMemcpyDeviceToHost, s->prog->ctx->stream));
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
-    return THRML_OK;
+    return check_err_flag(s);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -494,8 +494,12 @@ class Moments:
     def observe(self, state):
         check(lib().thrml_moments_observe(self.h, state.h))
 
-    def read(self, t):
-        out = np.zeros(int(self.rows_per_type[t]), dtype=np.int64)
+    def read(self, t, out=None):
+        """(int64 sums of moment type t, observations x chains).  `out` may be a caller-owned int64 array (pinned host
+        memory makes the copy run at link speed)."""
+        if out is None:
+            out = np.zeros(int(self.rows_per_type[t]), dtype=np.int64)
+        assert out.dtype == np.int64 and out.size >= int(self.rows_per_type[t])
         n = C.c_int64()
         check(lib().thrml_moments_read(self.h, C.c_int32(t), ptr(out), C.byref(n)))
         return out, n.value
