@@ -47,6 +47,9 @@ extern "C" {
 /* sampler kinds, one per free block (crates/thrml-samplers/src/sampler.rs:58-71 is the trait they implement) */
 #define THRML_SAMPLER_SPIN_GIBBS 0        /* SpinGibbsConditional, spin_gibbs.rs:59-100 */
 #define THRML_SAMPLER_CATEGORICAL_GIBBS 1 /* CategoricalGibbsConditional, softmax.rs:228-271 */
+#define THRML_SAMPLER_SOFTMAX 2           /* SoftmaxConditional, softmax.rs:103-222: logits = the block's per-category weights summed \
+                                             over active slots (tables whose weights are not [rows, K, 1] are skipped, neighbour  \
+                                             states are not read), then the same Gumbel-argmax draw */
 
 typedef struct thrml_ctx thrml_ctx;
 typedef struct thrml_builder thrml_builder;
@@ -169,6 +172,15 @@ int32_t thrml_comm_info(const thrml_comm* c, int32_t* rank_out, int32_t* world_o
 int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_program** out);
 void thrml_program_destroy(thrml_program* p);
 int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w);
+/* The same refresh without the host-side gather: every table compiled from interaction group `group` (its index in the
+ * builder's flat list — groups are appended in the order of the add_* calls, thrml_builder_counts reports how many exist)
+ * re-reads its slot weights on the device from the group's parameter rows: slot s takes
+ * scale * w[(row(s) mod period)][0 .. wdim), row(s) as in program.rs:216-235.  w: host, [period][wdim], in the group's own
+ * weight layout.  The group of a factor with S spin node groups repeats the factor's rows S times (discrete_ebm.rs:391-453),
+ * hence `period`: for a model built by thrml_builder_add_ising, the bias factor's group takes b[N] with period N and the
+ * edge factor's group takes J[E] with period E, both with scale = beta — an SGD step (train_mnist.rs:616-732,
+ * IsingEBM::update_weights, ising.rs:71-86) uploads N + E floats.  Derived tables are rebuilt on the device. */
+int32_t thrml_program_update_group(thrml_program* p, int32_t group, const float* w, int64_t period, int32_t wdim, float scale);
 /* Per-program tuning options (no counterpart in the reference; results never depend on them, tests use them to run
  * every route).  They belong to the handle: other programs and other host threads are not affected.
  *   THRML_OPT_DENSE_TILES   tile shape of the dense (tensor-core) kernels: 1 = CTA pairs sharing 256-row tiles through
@@ -327,6 +339,19 @@ int32_t thrml_marginals_create(thrml_program* p, const int32_t* blocks, int32_t 
 int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_warmup, int64_t n_samples,
                                       int64_t steps_per_sample, thrml_moments* moments, const int32_t* obs_blocks,
                                       int32_t n_obs_blocks, uint8_t* obs_out, const thrml_noise* inj);
+
+/* estimate_kl_grad (crates/thrml-models/src/ising.rs:531-594): key.split_two -> (key_pos, key_neg); each phase is
+ * estimate_moments (ising.rs:455-505) = sample_with_observation with a MomentAccumulatorObserver over
+ * ising_moment_spec(bias_nodes, weight_edges); the gradient -beta (mean_pos - mean_neg) is formed on the device and only
+ * the two gradient vectors come back.  `pos` / `neg`: states of the positive and the negative program (IsingTrainingSpec,
+ * ising.rs:392-433) already holding their initial free-block states and their clamped blocks (for `pos` the data row the
+ * reference picks, row key_pos mod batch of each data array, ising.rs:549-559, then the conditioning values; for `neg` the
+ * conditioning values).  moments_pos / moments_neg: observers created on the respective programs with the same two moment
+ * types (single nodes, then pairs); they are reset first.  Means divide by samples x chains.  grad_w_out[n_edges],
+ * grad_b_out[n_nodes]: host f32, either may be NULL. */
+int32_t thrml_estimate_kl_grad(thrml_state* pos, thrml_state* neg, thrml_moments* moments_pos, thrml_moments* moments_neg, uint64_t key,
+                               int64_t warmup_pos, int64_t samples_pos, int64_t steps_pos, int64_t warmup_neg, int64_t samples_neg, int64_t steps_neg,
+                               float beta, float* grad_w_out, float* grad_b_out);
 
 /* sample_states (sampling.rs:128-156) with the StateObserver output (state_observer.rs:25-47) streamed bit-packed:
  * bits_out[sample][observed node][word] (host, u32), word w = chains 32w .. 32w+31, bit c & 31; observed nodes = the

@@ -724,6 +724,30 @@ static int cat_field_f32(const Model* m, const std::vector<std::vector<float>>& 
     return 0;
 }
 
+// SoftmaxConditional::compute_parameters — softmax.rs:147-222: theta = sum over the interactions whose weights carry one
+// entry per category (dims[2] == n_categories, others are skipped, :183-187) of sum_slots W * active; neighbour states
+// are not read.
+static void softmax_field_f32(const Model* m, int block, int K, std::vector<float>& theta) {
+    size_t n = m->free_blocks[block].size();
+    theta.assign(n * K, 0.0f);
+    for (const Table& T : m->tables[block]) {
+        if (T.wdim != K) continue;
+        for (size_t i = 0; i < n; i++)
+            for (int c = 0; c < K; c++) {
+                float sum = 0.0f;
+                for (int j = 0; j < T.k; j++) {
+                    size_t f = i * T.k + j;
+                    sum += T.w[f * T.wdim + c] * (float)T.active[f];
+                }
+                theta[i * K + c] += sum;
+            }
+    }
+}
+static int cat_or_softmax_field(const Model* m, const std::vector<std::vector<float>>& g, int block, int K, std::vector<float>& theta) {
+    if (m->sampler_of[block] == 2) { softmax_field_f32(m, block, K, theta); return 0; }
+    return cat_field_f32(m, g, block, K, theta);
+}
+
 ORC_API int orc_fields(OState* s, int32_t block, double* out64, float* out32) {
     const Model* m = s->m;
     size_t n = m->free_blocks[block].size();
@@ -737,7 +761,7 @@ ORC_API int orc_fields(OState* s, int32_t block, double* out64, float* out32) {
     } else {
         for (int64_t c = 0; c < s->n_chains; c++) {
             std::vector<float> th;
-            if (cat_field_f32(m, s->g[c], block, kind, th)) return -1;
+            if (cat_or_softmax_field(m, s->g[c], block, kind, th)) return -1;
             if (out32) memcpy(out32 + c * n * kind, th.data(), n * kind * 4);
             if (out64) for (size_t i = 0; i < n * kind; i++) out64[c * n * kind + i] = th[i];
         }
@@ -782,7 +806,7 @@ static int update_block(OState* s, int block, uint64_t key, Noise* inj, std::vec
         std::atomic<int> bad(0);
         par_chains(s, [&](int64_t c) {
             std::vector<float> theta;
-            if (cat_field_f32(m, s->g[c], block, K, theta)) { bad = 1; return; }
+            if (cat_or_softmax_field(m, s->g[c], block, K, theta)) { bad = 1; return; }
             uint64_t gc = (uint64_t)(s->chain_offset + c);
             std::vector<float>& out = new_state[c];
             out.resize(n);

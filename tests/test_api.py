@@ -214,3 +214,59 @@ def test_ising_energy(T):
     want = -0.7 * (s @ b.astype(np.float64) + (s[:, ea] * s[:, eb]) @ J.astype(np.float64))
     assert np.allclose(batched, want, rtol=1e-6, atol=1e-6)
     assert abs(ebm.energy([states[5]])[0] - batched[5]) < 1e-5
+
+
+def test_grid_helpers_known_answers(T):
+    # crates/thrml-examples/src/lib.rs:255-330: 3 x 4 grid = 12 nodes, 9 + 8 = 17 edges; a 3 x 3 grid two-colours with no
+    # monochromatic edge; a 2 x 2 grid gives two blocks of two; a chain of five is two-colourable by the greedy rule
+    nodes, edges, grid = T.generate_lattice_graph(3, 4)
+    assert len(nodes) == 12 and len(edges) == 17 and len(grid) == 3 and len(grid[0]) == 4
+    nodes, edges, grid = T.generate_lattice_graph(3, 3)
+    colour = T.bipartite_coloring(grid)
+    assert set(colour.tolist()) == {0, 1} and all(colour[a] != colour[b] for a, b in edges)
+    nodes, edges, grid = T.generate_lattice_graph(2, 2)
+    blocks = T.coloring_to_blocks(nodes, T.bipartite_coloring(grid))
+    assert [len(b) for b in blocks] == [2, 2]
+    nodes, edges = T.generate_chain_graph(5)
+    assert len(edges) == 4 and int(T.greedy_coloring(5, edges).max()) + 1 == 2
+
+
+@pytest.mark.gpu
+def test_softmax_conditional_block(T, O):
+    """A block sampled by SoftmaxConditional (softmax.rs:103-222) next to one sampled by CategoricalGibbsConditional: same
+    states as the oracle's restatement, and logits that ignore the neighbours."""
+    import models as M
+    K, side = 5, 6
+    desc, info = M.potts_lattice(T, side, K, 3)
+    results = []
+    for cls in (T.Builder, O.Model):
+        bld = cls(desc["kinds"])
+        bld.add_free_block(info["blocks"][0], superblock=0, sampler=2)  # SoftmaxConditional
+        bld.add_free_block(info["blocks"][1], superblock=1, sampler=1)  # CategoricalGibbsConditional
+        for op in desc["ops"]:
+            getattr(bld, op[0])(*op[1:])
+        bld.compile()
+        results.append(bld)
+    gb, ob = results
+    chains = 70
+    prog = T.Program(gb)
+    gs, os_ = T.ChainState(prog, chains), O.State(ob, chains)
+    init = M.random_states(desc, chains, 2)
+    for i, a in enumerate(init):
+        gs.upload(i, a)
+        os_.set_block(i, a.astype(np.float32))
+    th_g, (th64, th32) = gs.fields(0), os_.fields(0)
+    assert np.array_equal(th_g, th32)
+    assert np.array_equal(th_g[0], th_g[-1])  # no dependence on the chains' neighbour states
+    gs.run_blocks(8, 3)
+    os_.run_blocks(8, 3)
+    for i in range(2):
+        assert np.array_equal(gs.download(i), os_.get_block(i))
+    # the API mirror accepts the sampler
+    cats = [T.Node(T.NodeType.Categorical(3)) for _ in range(4)]
+    spec = T.BlockGibbsSpec([[T.Block(cats)]], [], [T.NodeType.Categorical(3)])
+    w = np.zeros((4, 3, 1), np.float32)
+    w[:, 2, 0] = 40.0
+    prog2 = T.BlockSamplingProgram(spec, [T.SoftmaxConditional(3)], [T.InteractionGroup(w, T.Block(cats), [], 0)])
+    out = T.run_blocks(T.RngKey(1), prog2, [np.zeros(4, np.float32)], [], 2)
+    assert np.array_equal(out[0], np.full(4, 2.0, np.float32))

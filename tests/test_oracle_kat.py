@@ -139,3 +139,34 @@ def test_factor_energy_restatement(O):
     assert np.allclose(e, [-(w[0, 2, 1] - w[1, 0, 2]), -(-w[0, 1, 0] - w[1, 1, 2])])
     w1 = np.arange(6, dtype=np.float64).reshape(2, 3, 1)
     assert O.factor_energy(w1, [], [np.array([2, 1])]) == -(w1[0, 2, 0] + w1[1, 1, 0])
+
+
+def test_softmax_conditional_logits_ignore_neighbours(O):
+    """SoftmaxConditional (softmax.rs:147-222): per-category weights summed over active slots; interactions whose weights
+    are not [rows, K, 1] are skipped and neighbour states never enter.  Checked against numpy on a small model."""
+    K, n = 4, 6
+    rng = np.random.default_rng(0)
+    unary_a = rng.normal(0, 1, (n, K, 1)).astype(np.float32)
+    unary_b = rng.normal(0, 1, (3, K, 1)).astype(np.float32)
+    pair = rng.normal(0, 1, (n - 1, K, K)).astype(np.float32)
+    m = O.Model(np.full(n, K, np.int32))
+    m.add_free_block(np.arange(n), sampler=2)
+    m.add_discrete_factor([], [np.arange(n)], unary_a)
+    m.add_discrete_factor([], [np.array([0, 2, 2])], unary_b)            # node 2 heads two rows of this group
+    m.add_discrete_factor([], [np.arange(n - 1), np.arange(1, n)], pair)  # [rows, K, K]: skipped by this sampler
+    m.compile()
+    st = O.State(m, 3)
+    st.set_block(0, rng.integers(0, K, (3, n)).astype(np.float32))
+    _, th = st.fields(0)
+    want = unary_a[:, :, 0].copy()
+    want[0] += unary_b[0, :, 0]
+    want[2] += unary_b[1, :, 0] + unary_b[2, :, 0]
+    assert np.allclose(th, np.broadcast_to(want, (3, n, K)), rtol=0, atol=1e-6)
+    # the draw is the usual Gumbel-argmax of those logits: overwhelming logits decide it
+    m2 = O.Model(np.full(2, 3, np.int32))
+    m2.add_free_block(np.arange(2), sampler=2)
+    m2.add_discrete_factor([], [np.arange(2)], np.array([[[-30.0], [30.0], [-30.0]], [[30.0], [-30.0], [-30.0]]], np.float32))
+    m2.compile()
+    s2 = O.State(m2, 5)
+    s2.sample_blocks(1)
+    assert np.array_equal(s2.get_block(0), np.broadcast_to(np.array([1.0, 0.0], np.float32), (5, 2)))

@@ -9,8 +9,8 @@ from .engine import (OPT_DENSE_TILES, OPT_SPLIT_MARGIN, Builder, ChainState, Com
 from .api import (Block, BlockGibbsSpec, BlockSamplingProgram, BlockSpec, CategoricalEBMFactor,  # noqa: F401
                   CategoricalGibbsConditional, DiscreteEBMFactor, FactorizedEBM, FactorSamplingProgram, InteractionGroup, IsingEBM,
                   IsingSamplingProgram, IsingTrainingSpec, MomentAccumulatorObserver, Node, NodeType, RngKey, SamplingSchedule,
-                  SpinEBMFactor, SpinGibbsConditional, SquareDiscreteEBMFactor, StateObserver, coloring_to_blocks, estimate_kl_grad, estimate_moments,
-                  greedy_coloring, hinton_init, make_nearest_neighbor_lattice, run_blocks, sample_blocks,
+                  SoftmaxConditional, SpinEBMFactor, SpinGibbsConditional, SquareDiscreteEBMFactor, StateObserver, coloring_to_blocks, estimate_kl_grad, estimate_moments,
+                  bipartite_coloring, generate_chain_graph, generate_lattice_graph, greedy_coloring, hinton_init, make_nearest_neighbor_lattice, run_blocks, sample_blocks,
                   sample_states, sample_with_observation)
 
 lib()  # fail at import time when the compiled library is absent: there is no other compute path

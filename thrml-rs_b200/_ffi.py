@@ -41,6 +41,8 @@ _SIGNATURES = {
     "thrml_ctx_synchronize": (C.c_int32, [_P]),
     "thrml_ctx_stream": (C.c_void_p, [_P]),
     "thrml_debug_wait_timeout": (C.c_int32, [_P]),
+    "thrml_program_update_group": (C.c_int32, [_P, C.c_int32, _P, C.c_int64, C.c_int32, C.c_float]),
+    "thrml_estimate_kl_grad": (C.c_int32, [_P, _P, _P, _P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_float, _P, _P]),
     "thrml_program_set_option": (C.c_int32, [_P, C.c_int32, C.c_double]),
     "thrml_program_get_option": (C.c_int32, [_P, C.c_int32, _P]),
     "thrml_debug_pair_tmem_check": (C.c_int32, [_P]),

@@ -208,6 +208,15 @@ class CategoricalGibbsConditional:
         self.n_spin = n_spin
 
 
+class SoftmaxConditional:
+    """crates/thrml-samplers/src/softmax.rs:103-222: logits = the per-category weights of the block's interactions summed
+    over active slots; neighbour states are not read and interactions whose weights are not `[rows, K, 1]` are skipped."""
+    kind = _eng.SAMPLER_SOFTMAX
+
+    def __init__(self, n_categories):
+        self.n_categories = n_categories
+
+
 class BlockGibbsSpec:
     """crates/thrml-samplers/src/program.rs:17-64."""
 
@@ -608,6 +617,18 @@ class IsingSamplingProgram:
         for f in ebm.get_factors():
             groups.extend(f.to_interaction_groups())
         self.program = BlockSamplingProgram(gibbs_spec, samplers, groups, ctx)
+        self._has_bias_group = bool(ebm.nodes)
+
+    def refresh_weights(self, ebm):
+        """The explicit counterpart of IsingEBM::update_weights (ising.rs:71-86) for a program that already exists: the
+        reference's programs keep the beta-scaled weights they were built with (train_mnist.rs:600-612 rebuilds them), here
+        the device tables re-read b[N] and J[E] through thrml_program_update_group — N + E floats cross the host link."""
+        dp, beta, g = self.program.device_program, ebm.beta_value(), 0
+        if self._has_bias_group:
+            dp.update_group(g, ebm.biases, scale=beta)
+            g += 1
+        if ebm.edges:
+            dp.update_group(g, ebm.weights, scale=beta)
 
 
 def hinton_init(key, model, blocks, batch_shape, ctx=None, noise=None):
@@ -643,24 +664,36 @@ class IsingTrainingSpec:
         self.schedule_positive = schedule_positive
         self.schedule_negative = schedule_negative
 
+    def refresh_weights(self):
+        """Push the EBM's current biases, couplings and beta into both programs' device tables."""
+        self.program_positive.refresh_weights(self.ebm)
+        self.program_negative.refresh_weights(self.ebm)
+
 
 def estimate_kl_grad(key, training_spec, bias_nodes, weight_edges, data, conditioning_values, init_state_positive, init_state_negative):
     """ising.rs:531-594: grad = -beta (<.>_data - <.>_model), returned as (grad_weights, grad_biases).  `data` is one
     `[batch, n]` array per data block; like the reference, the positive phase clamps the single row `key_pos % batch`
-    (ising.rs:549-559).  Chains batch through the init states as everywhere else."""
-    key_pos, key_neg = key.split_two()
-    beta = training_spec.ebm.beta_value()
-    chains, batched = _batch_of(list(init_state_positive) + list(init_state_negative))
+    (ising.rs:549-559).  Chains batch through the init states as everywhere else; 1-D clamped or conditioning arrays then
+    stand for every chain.  Both phases and the difference run on the device (thrml_estimate_kl_grad)."""
+    key_pos, _ = key.split_two()
     clamped_pos = []
     for d in data:
         d = np.asarray(d)
-        row = d[key_pos.seed() % d.shape[0]]
-        clamped_pos.append(np.broadcast_to(row, (chains, row.shape[0])).copy() if batched else row)
+        clamped_pos.append(d[key_pos.seed() % d.shape[0]])
     cond = [np.asarray(c) for c in conditioning_values]
     clamped_pos += cond
-    b_pos, w_pos = estimate_moments(key_pos, bias_nodes, weight_edges, training_spec.program_positive.program, training_spec.schedule_positive, init_state_positive, clamped_pos)
-    b_neg, w_neg = estimate_moments(key_neg, bias_nodes, weight_edges, training_spec.program_negative.program, training_spec.schedule_negative, init_state_negative, cond)
-    return (w_pos - w_neg) * np.float32(-beta), (b_pos - b_neg) * np.float32(-beta)
+    prog_pos, prog_neg = training_spec.program_positive.program, training_spec.program_negative.program
+    st_pos, _, _ = _make_state(prog_pos, init_state_positive, clamped_pos)
+    st_neg, _, _ = _make_state(prog_neg, init_state_negative, cond)
+    spec = MomentAccumulatorObserver.ising_moment_spec(list(bias_nodes), list(weight_edges))
+    if len(spec) != 2:  # ising_moment_spec drops an empty type; the device entry wants both, possibly empty
+        spec = [[(n,) for n in bias_nodes], [tuple(e) for e in weight_edges]]
+    moms = []
+    for prog in (prog_pos, prog_neg):
+        moms.append(_eng.Moments(prog.device_program, [[[prog.dense_id(n) for n in row] for row in t] for t in spec], True))
+    sp, sn = training_spec.schedule_positive, training_spec.schedule_negative
+    return _eng.estimate_kl_grad(st_pos, st_neg, moms[0], moms[1], key.seed(), (sp.n_warmup, sp.n_samples, sp.steps_per_sample),
+                                 (sn.n_warmup, sn.n_samples, sn.steps_per_sample), training_spec.ebm.beta_value())
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -675,6 +708,42 @@ def make_nearest_neighbor_lattice(side_len, torus):
     upper = Block([n for n, c in zip(nodes, colour) if c == 0])
     lower = Block([n for n, c in zip(nodes, colour) if c == 1])
     return nodes, edges, upper, lower
+
+
+def generate_lattice_graph(rows, cols, node_type=None):
+    """lib.rs:34-71: `rows x cols` grid with 4-connectivity, no wrap-around.  Returns (nodes, edges, node_grid): nodes in
+    row-major creation order, edges as index pairs in the reference's insertion order (for each cell: right, then down),
+    node_grid[row][col] = index into nodes."""
+    if node_type is None:
+        node_type = NodeType.Spin()
+    nodes = [Node(node_type) for _ in range(rows * cols)]
+    grid = [[r * cols + c for c in range(cols)] for r in range(rows)]
+    edges = []
+    for r in range(rows):
+        for c in range(cols):
+            if c + 1 < cols:
+                edges.append((grid[r][c], grid[r][c + 1]))
+            if r + 1 < rows:
+                edges.append((grid[r][c], grid[r + 1][c]))
+    return nodes, np.array(edges, dtype=np.int64).reshape(-1, 2), grid
+
+
+def generate_chain_graph(length, node_type=None):
+    """lib.rs:83-101: a path of `length` nodes.  Returns (nodes, edges as index pairs)."""
+    if node_type is None:
+        node_type = NodeType.Spin()
+    nodes = [Node(node_type) for _ in range(length)]
+    return nodes, np.array([(i, i + 1) for i in range(max(length - 1, 0))], dtype=np.int64).reshape(-1, 2)
+
+
+def bipartite_coloring(node_grid):
+    """lib.rs:160-173: checkerboard colouring of a grid, colour = (row + col) % 2, as an array indexed by node index."""
+    n = sum(len(r) for r in node_grid)
+    colour = np.zeros(n, dtype=np.int32)
+    for r, row in enumerate(node_grid):
+        for c, idx in enumerate(row):
+            colour[idx] = (r + c) % 2
+    return colour
 
 
 def greedy_coloring(n_nodes, edges):

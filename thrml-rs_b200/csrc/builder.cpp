@@ -202,7 +202,7 @@ int32_t thrml_builder_add_free_block(thrml_builder* b, const int64_t* nodes, int
     if (int32_t rc = validate_block(b, nodes, n)) return rc;
     if (!b->free_blocks.empty() && superblock < b->free_blocks.back().superblock)
         return fail(THRML_ERR_INVALID_ARG, "superblock ids must be non-decreasing");
-    if (sampler_kind != THRML_SAMPLER_SPIN_GIBBS && sampler_kind != THRML_SAMPLER_CATEGORICAL_GIBBS)
+    if (sampler_kind != THRML_SAMPLER_SPIN_GIBBS && sampler_kind != THRML_SAMPLER_CATEGORICAL_GIBBS && sampler_kind != THRML_SAMPLER_SOFTMAX)
         return fail(THRML_ERR_INVALID_ARG, "unknown sampler kind");
     BlockInfo bi;
     bi.nodes.assign(nodes, nodes + n);
@@ -395,7 +395,8 @@ int32_t thrml_builder_compile(thrml_builder* b) {
     for (auto& blk : b->clamped_blocks)
         if (int32_t rc = place(blk)) return rc;
     for (auto& blk : b->free_blocks) {
-        const bool ok = (blk.sampler == THRML_SAMPLER_SPIN_GIBBS && blk.kind == 0) || (blk.sampler == THRML_SAMPLER_CATEGORICAL_GIBBS && blk.kind > 0);
+        const bool ok = (blk.sampler == THRML_SAMPLER_SPIN_GIBBS && blk.kind == 0) ||
+                        ((blk.sampler == THRML_SAMPLER_CATEGORICAL_GIBBS || blk.sampler == THRML_SAMPLER_SOFTMAX) && blk.kind > 0);
         if (!ok) return fail(THRML_ERR_UNSUPPORTED, "sampler kind does not match the block's node type");
     }
     for (int64_t v : b->class_size)

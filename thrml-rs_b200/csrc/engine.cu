@@ -28,6 +28,8 @@ struct BlockProg {
     std::vector<DevTable> host_tabs;
     std::vector<DevBuf*> w_bufs;                // per table, for update_weights
     std::vector<size_t> w_len;
+    std::vector<DevBuf*> rows_bufs;             // per table: int32 [n*k], the row of the source group each slot copies (program.rs:216-235)
+    std::vector<int32_t> src_group, tab_wdim;   // per table: index of the source interaction group, weights per slot
     DevBuf d_tabs;   // DevTable[n_tabs]
     DevBuf d_nbr;    // int32 [n][8] (threshold-table kernel)
     DevBuf d_lut;    // uint32 [n][256]
@@ -293,7 +295,21 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
         bp.n = static_cast<int64_t>(bi.nodes.size());
         bp.offset = bi.offset;
         if (i >= p->n_free) continue;
-        const auto& tabs = b->tables[i];
+        // SoftmaxConditional (softmax.rs:147-222) keeps only the tables with one weight per category and never reads a
+        // neighbour: its block runs the categorical kernels on those tables with their tails dropped.
+        std::vector<SlotTable> softmax_tabs;
+        if (bi.sampler == THRML_SAMPLER_SOFTMAX) {
+            for (const SlotTable& t : b->tables[i]) {
+                if (t.wdim != bi.kind) continue;
+                SlotTable c = t;
+                c.idx.clear();
+                c.tail_sd.clear();
+                c.tail_is_cat.clear();
+                c.n_spin = 0;
+                softmax_tabs.push_back(std::move(c));
+            }
+        }
+        const auto& tabs = bi.sampler == THRML_SAMPLER_SOFTMAX ? softmax_tabs : b->tables[i];
         bp.n_tabs = static_cast<int32_t>(tabs.size());
         bp.kernel = bp.is_cat ? 2 : 0;
         bool lut_ok = !bp.is_cat && !tabs.empty();
@@ -324,6 +340,11 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
             d.w = bp.bufs.back()->as<float>();
             bp.w_bufs.push_back(bp.bufs.back().get());
             bp.w_len.push_back(t.w.size());
+            bp.bufs.emplace_back(new DevBuf());
+            if (int32_t rc = upload(*bp.bufs.back(), t.rows.data(), t.rows.size() * 4, ctx->stream)) return rc;
+            bp.rows_bufs.push_back(bp.bufs.back().get());
+            bp.src_group.push_back(t.source_group);
+            bp.tab_wdim.push_back(t.wdim);
             bp.host_tabs.push_back(d);
         }
         if (int32_t rc = upload(bp.d_tabs, bp.host_tabs.data(), bp.host_tabs.size() * sizeof(DevTable), ctx->stream)) return rc;
@@ -561,6 +582,16 @@ void thrml_program_destroy(thrml_program* p) {
     cudaDeviceSynchronize();
     delete p;
 }
+// The derived tables (thresholds, entry lists, split field tables) of a block whose slot weights changed.
+static int32_t rebuild_derived(thrml_program* p, BlockProg& bp) {
+    if (bp.base_kernel == 1)
+        if (int32_t rc = rebuild_lut(p, bp)) return rc;
+    if (bp.base_kernel == 4 || bp.base_kernel == 6)
+        if (int32_t rc = rebuild_seq(p, bp)) return rc;
+    if (bp.base_kernel == 6)
+        if (int32_t rc = rebuild_lut(p, bp)) return rc;
+    return THRML_OK;
+}
 int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t, const float* w) {
     if (!p || !w) return fail(THRML_ERR_INVALID_ARG, "null argument");
     if (block < 0 || block >= p->n_free) return fail(THRML_ERR_INVALID_ARG, "block index out of range");
@@ -570,13 +601,49 @@ int32_t thrml_program_update_weights(thrml_program* p, int32_t block, int32_t t,
     bp.dense_src = -1;  // the cached dense matrix no longer matches the tables
     CU_TRY(cudaSetDevice(p->ctx->device));
     CU_TRY(cudaMemcpyAsync(bp.w_bufs[t]->p, w, bp.w_len[t] * 4, cudaMemcpyHostToDevice, p->ctx->stream));
-    if (bp.base_kernel == 1)
-        if (int32_t rc = rebuild_lut(p, bp)) return rc;
-    if (bp.base_kernel == 4 || bp.base_kernel == 6)
-        if (int32_t rc = rebuild_seq(p, bp)) return rc;
-    if (bp.base_kernel == 6)
-        if (int32_t rc = rebuild_lut(p, bp)) return rc;
+    if (int32_t rc = rebuild_derived(p, bp)) return rc;
     CU_TRY(cudaStreamSynchronize(p->ctx->stream));
+    return THRML_OK;
+}
+// Slot s of a table copies row rows[s] of its source group (program.rs:216-235); the group's rows repeat the factor's
+// `period` parameter rows once per head group (discrete_ebm.rs:391-453).
+__global__ void k_regather(const int32_t* rows, const float* param, int64_t period, int32_t wdim, float scale, int64_t n_slots, float* w) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n_slots * wdim) return;
+    const int64_t s = i / wdim, d = i % wdim;
+    w[i] = __fmul_rn(scale, param[(static_cast<int64_t>(rows[s]) % period) * wdim + d]);
+}
+int32_t thrml_program_update_group(thrml_program* p, int32_t group, const float* w, int64_t period, int32_t wdim, float scale) {
+    if (!p || !w) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (period < 1 || wdim < 1) return fail(THRML_ERR_INVALID_ARG, "period and wdim must be positive");
+    CU_TRY(cudaSetDevice(p->ctx->device));
+    cudaStream_t st = p->ctx->stream;
+    DevBuf d_param;
+    bool found = false, uploaded = false;
+    for (int32_t bi = 0; bi < p->n_free; ++bi) {
+        BlockProg& bp = p->blocks[bi];
+        bool touched = false;
+        for (int32_t t = 0; t < bp.n_tabs; ++t) {
+            if (bp.src_group[t] != group) continue;
+            if (bp.tab_wdim[t] != wdim) return fail(THRML_ERR_INVALID_ARG, "wdim does not match the group's weights per row");
+            if (bp.dense_on) return fail(THRML_ERR_UNSUPPORTED, "weights of a block on the dense path are fixed; create a new program to change them");
+            if (!uploaded) {
+                if (int32_t rc = upload(d_param, w, static_cast<size_t>(period) * wdim * 4, st)) return rc;
+                uploaded = true;
+            }
+            const int64_t total = static_cast<int64_t>(bp.w_len[t]);
+            k_regather<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(bp.rows_bufs[t]->as<int32_t>(), d_param.as<float>(), period, wdim, scale, total / wdim,
+                                                                                 bp.w_bufs[t]->as<float>());
+            CU_TRY(cudaGetLastError());
+            found = touched = true;
+        }
+        if (touched) {
+            bp.dense_src = -1;
+            if (int32_t rc = rebuild_derived(p, bp)) return rc;
+        }
+    }
+    CU_TRY(cudaStreamSynchronize(st));  // d_param is released on return
+    if (!found) return fail(THRML_ERR_INVALID_ARG, "no free block has a table compiled from interaction group " + std::to_string(group));
     return THRML_OK;
 }
 int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding, int32_t* n_blocks_out) {
@@ -2029,6 +2096,47 @@ int32_t thrml_sample_with_observation(thrml_state* s, uint64_t key, int64_t n_wa
     if (int32_t rc = flush_pending(s)) return rc;
     CU_TRY(cudaStreamSynchronize(s->prog->ctx->stream));
     return check_err_flag(s);
+}
+
+// grad[r] = -beta (sum_pos[r] / denom_pos - sum_neg[r] / denom_neg), the means rounded to f32 first as estimate_moments
+// returns them (ising.rs:489-502, 589-591).
+__global__ void k_kl_grad(const long long* pos, const long long* neg, double denom_pos, double denom_neg, float neg_beta, int64_t n, float* out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float mp = static_cast<float>(static_cast<double>(pos[i]) / denom_pos), mn = static_cast<float>(static_cast<double>(neg[i]) / denom_neg);
+    out[i] = __fmul_rn(__fsub_rn(mp, mn), neg_beta);
+}
+// estimate_kl_grad (ising.rs:531-594): both phases and the gradient on the device; see the header.
+int32_t thrml_estimate_kl_grad(thrml_state* pos, thrml_state* neg, thrml_moments* moments_pos, thrml_moments* moments_neg, uint64_t key, int64_t warmup_pos,
+                               int64_t samples_pos, int64_t steps_pos, int64_t warmup_neg, int64_t samples_neg, int64_t steps_neg, float beta, float* grad_w_out,
+                               float* grad_b_out) {
+    if (!pos || !neg || !moments_pos || !moments_neg) return fail(THRML_ERR_INVALID_ARG, "null argument");
+    if (moments_pos->prog != pos->prog || moments_neg->prog != neg->prog) return fail(THRML_ERR_INVALID_ARG, "each observer must belong to its phase's program");
+    if (pos->prog->ctx != neg->prog->ctx) return fail(THRML_ERR_INVALID_ARG, "both phases must run on one context");
+    if (moments_pos->mode != 0 || moments_neg->mode != 0 || moments_pos->rows_per_type != moments_neg->rows_per_type || moments_pos->rows_per_type.size() != 2)
+        return fail(THRML_ERR_INVALID_ARG, "both observers must hold the same two moment types: bias nodes, then weight edges (ising_moment_spec)");
+    if (samples_pos < 1 || samples_neg < 1) return fail(THRML_ERR_INVALID_ARG, "each phase needs at least one sample");
+    uint64_t two[2];
+    rng_split(key, 2, two);  // key.split_two(), ising.rs:543
+    if (int32_t rc = thrml_moments_reset(moments_pos)) return rc;
+    if (int32_t rc = thrml_moments_reset(moments_neg)) return rc;
+    if (int32_t rc = thrml_sample_with_observation(pos, two[0], warmup_pos, samples_pos, steps_pos, moments_pos, nullptr, 0, nullptr, nullptr)) return rc;
+    if (int32_t rc = thrml_sample_with_observation(neg, two[1], warmup_neg, samples_neg, steps_neg, moments_neg, nullptr, 0, nullptr, nullptr)) return rc;
+    cudaStream_t st = pos->prog->ctx->stream;
+    CU_TRY(cudaSetDevice(pos->device));
+    const int64_t n_b = moments_pos->rows_per_type[0], n_w = moments_pos->rows_per_type[1], total = n_b + n_w;
+    if (total == 0) return THRML_OK;
+    DevBuf d_grad;
+    if (int32_t rc = d_grad.alloc(static_cast<size_t>(total) * 4)) return rc;
+    // estimate_moments divides by n_samples (ising.rs:489-502); a batch of chains is averaged as well
+    k_kl_grad<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(moments_pos->d_sums.as<long long>(), moments_neg->d_sums.as<long long>(),
+                                                                        static_cast<double>(moments_pos->n_obs), static_cast<double>(moments_neg->n_obs), -beta, total,
+                                                                        d_grad.as<float>());
+    CU_TRY(cudaGetLastError());
+    if (grad_b_out && n_b > 0) CU_TRY(cudaMemcpyAsync(grad_b_out, d_grad.p, static_cast<size_t>(n_b) * 4, cudaMemcpyDeviceToHost, st));
+    if (grad_w_out && n_w > 0) CU_TRY(cudaMemcpyAsync(grad_w_out, d_grad.as<float>() + n_b, static_cast<size_t>(n_w) * 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return THRML_OK;
 }
 
 // sample_states (sampling.rs:128-156) with the samples streamed to the host bit-packed: bits_out[sample][observed node][word],

@@ -13,6 +13,7 @@ from ._ffi import check, f32, i32, i64, lib, ptr
 
 SAMPLER_SPIN = 0
 SAMPLER_CATEGORICAL = 1
+SAMPLER_SOFTMAX = 2
 
 _default_ctx = {}
 
@@ -265,6 +266,13 @@ class Program:
         w = f32(w)
         check(lib().thrml_program_update_weights(self.h, C.c_int32(block), C.c_int32(table), ptr(w)))
 
+    def update_group(self, group, w, period=None, scale=1.0):
+        """thrml_program_update_group: refresh on the device every table compiled from interaction group `group` from the
+        group's parameter rows `w` (`[period]` or `[period, wdim]`)."""
+        w = f32(w)
+        w = w.reshape(w.shape[0], -1)
+        check(lib().thrml_program_update_group(self.h, C.c_int32(group), ptr(w), C.c_int64(w.shape[0] if period is None else period), C.c_int32(w.shape[1]), C.c_float(scale)))
+
     def enable_dense(self, allow_bf16_rounding=False):
         """Switch every qualifying bipartite spin block to the tensor-core kernel; returns how many were switched."""
         n = C.c_int32()
@@ -441,6 +449,16 @@ class ChainState:
                                                   moments.h if moments is not None else None, ptr(ob), C.c_int32(0 if ob is None else len(ob)), ptr(obs),
                                                   C.byref(nz) if nz else None))
         return obs
+
+
+def estimate_kl_grad(pos_state, neg_state, moments_pos, moments_neg, key, schedule_pos, schedule_neg, beta):
+    """thrml_estimate_kl_grad: both phases and -beta (mean_pos - mean_neg) on the device; schedules are
+    (n_warmup, n_samples, steps_per_sample).  Returns (grad_w, grad_b) as f32 arrays."""
+    n_b, n_w = int(moments_pos.rows_per_type[0]), int(moments_pos.rows_per_type[1])
+    gw, gb = np.zeros(max(n_w, 1), dtype=np.float32), np.zeros(max(n_b, 1), dtype=np.float32)
+    check(lib().thrml_estimate_kl_grad(pos_state.h, neg_state.h, moments_pos.h, moments_neg.h, C.c_uint64(int(key)), *[C.c_int64(int(x)) for x in schedule_pos],
+                                       *[C.c_int64(int(x)) for x in schedule_neg], C.c_float(beta), ptr(gw), ptr(gb)))
+    return gw[:n_w], gb[:n_b]
 
 
 class Moments:
