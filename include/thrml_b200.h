@@ -370,6 +370,22 @@ int32_t thrml_sample_states_packed(thrml_state* s, uint64_t key, int64_t n_warmu
  * neighbouring stripes, update colour 1 with keys[1], refresh colour 1's halos.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct thrml_lattice thrml_lattice;
+/* How a block key becomes the noise of each (spin, chain) is this engine's own definition (the reference never consumes its
+ * RngKey: spin_gibbs.rs:61,82-83 draw from the backend's global generator).  Two mappings:
+ *   THRML_LATTICE_NOISE_PROGRAM  the explicit program's: the draw of spin n (index inside its colour block) and chain c is
+ *       word c & 3 of Philox4x32-10(counter (n, c >> 2, 0, tag), block key); states then equal the explicit program's.
+ *   THRML_LATTICE_NOISE_PACKED (the default)  the 32-bit draw is assembled from calls shared as widely as the bit-packed layout
+ *       allows: bit b of its top byte is bit n & 31 of word b & 3 of counter (n >> 5, c, 1 + (b >> 2), tag) — two calls give the
+ *       top bytes of 32 spins as eight bit planes, compared with the thresholds bit-sliced — and, only when the top byte equals
+ *       the threshold's, the low 24 bits of word c & 3 of counter (n, c >> 2, 3, tag).  Same rule (draw <= threshold), same
+ *       24-bit resolution, a sixteenth of the generator work per update. */
+#define THRML_LATTICE_NOISE_PROGRAM 0
+#define THRML_LATTICE_NOISE_PACKED 1
+/* The PACKED mapping evaluated spin by spin from the threshold table: the route taken by itself when a threshold's top byte
+ * does not depend on the neighbour configuration through the number of up neighbours alone (the bit-sliced comparison needs
+ * that); selectable so that tests can run it.  Same noise, same states as PACKED. */
+#define THRML_LATTICE_NOISE_PACKED_TABLE 2
+int32_t thrml_lattice_set_noise(thrml_lattice* lat, int32_t mapping);
 int32_t thrml_lattice_create(thrml_ctx* ctx, int64_t height, int64_t width, int64_t row_begin, int64_t n_rows, float coupling,
                              float bias, float beta, int64_t n_chains, int64_t chain_offset, thrml_lattice** out);
 void thrml_lattice_destroy(thrml_lattice* lat);

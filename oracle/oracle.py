@@ -281,6 +281,11 @@ class State:
             lib().orc_state_destroy(self.h)
             self.h = None
 
+    def set_spin_noise(self, mapping):
+        """0 = one 32-bit word per (spin, chain) (the gather kernels' mapping), 1 = the implicit lattice engine's bit-sliced
+        mapping, 2 = the dense (tensor-core) path's mapping."""
+        lib().orc_state_set_spin_noise(self.h, C.c_int32(mapping))
+
     def _block_len(self, block):
         nf = len(self.model.free_blocks)
         return len(self.model.free_blocks[block]) if block < nf else len(self.model.clamped_blocks[block - nf])

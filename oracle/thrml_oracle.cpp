@@ -601,6 +601,7 @@ struct OState {
     Model* m;
     int64_t n_chains, chain_offset;
     int threads = 1;
+    int spin_noise = 0;  // 0: one 32-bit word per (spin, chain); 1: the packed mapping of the implicit lattice engine
     std::vector<std::vector<std::vector<float>>> g;  // [chain][class][position], f32 as in the reference
 };
 ORC_API int orc_state_create(Model* m, int64_t n_chains, int64_t chain_offset, OState** out) {
@@ -614,6 +615,13 @@ ORC_API int orc_state_create(Model* m, int64_t n_chains, int64_t chain_offset, O
 }
 ORC_API void orc_state_destroy(OState* s) { delete s; }
 ORC_API void orc_state_set_threads(OState* s, int32_t t) { s->threads = t < 1 ? 1 : t; }
+// The reference never consumes its RngKey (spin_gibbs.rs:61,82-83), so the key -> noise mapping belongs to the engine under
+// test.  Mapping 1 restates the implicit lattice engine's bit-sliced mapping: for spin n (index in its block) and global
+// chain c, bit b of the draw's top byte is bit (n & 31) of word (b & 3) of Philox(n >> 5, c, 1 + (b >> 2), TAG_SPIN), and
+// the low 24 bits are those of word (c & 3) of Philox(n, c >> 2, 3, TAG_SPIN); the uniform is the draw's top 24 bits, as
+// for mapping 0.  Mapping 2 restates the dense (tensor-core) path's mapping: top 16 bits = half (n & 1) of word ((n >> 1) & 3) of
+// Philox(n >> 3, c, 1, TAG_SPIN), low 16 bits = low half of word (c & 3) of Philox(n, c >> 2, 2, TAG_SPIN).
+ORC_API void orc_state_set_spin_noise(OState* s, int32_t mapping) { s->spin_noise = mapping; }
 static const std::vector<int64_t>& block_nodes(const Model* m, int b) {
     return b < (int)m->free_blocks.size() ? m->free_blocks[b] : m->clamped_blocks[b - m->free_blocks.size()];
 }
@@ -793,6 +801,22 @@ static int update_block(OState* s, int block, uint64_t key, Noise* inj, std::vec
             for (size_t i = 0; i < n; i++) {
                 float u;
                 if (u_inj) u = u_inj[i * C + c];
+                else if (s->spin_noise == 1) {
+                    uint32_t pl[8], lo[4];
+                    philox4x32_10((uint32_t)(i >> 5), (uint32_t)gc, 1, TAG_SPIN, k0, k1, pl);
+                    philox4x32_10((uint32_t)(i >> 5), (uint32_t)gc, 2, TAG_SPIN, k0, k1, pl + 4);
+                    philox4x32_10((uint32_t)i, (uint32_t)(gc >> 2), 3, TAG_SPIN, k0, k1, lo);
+                    uint32_t top = 0;
+                    for (int b = 0; b < 8; b++) top |= ((pl[b] >> (i & 31)) & 1u) << b;
+                    u = u24((top << 24) | (lo[gc & 3] & 0xffffffu));
+                }
+                else if (s->spin_noise == 2) {
+                    uint32_t tp[4], lo[4];
+                    philox4x32_10((uint32_t)(i >> 3), (uint32_t)gc, 1, TAG_SPIN, k0, k1, tp);
+                    philox4x32_10((uint32_t)i, (uint32_t)(gc >> 2), 2, TAG_SPIN, k0, k1, lo);
+                    uint32_t top = (tp[(i >> 1) & 3] >> (16 * (i & 1))) & 0xffffu;
+                    u = u24((top << 16) | (lo[gc & 3] & 0xffffu));
+                }
                 else { uint32_t r[4]; philox4x32_10((uint32_t)i, (uint32_t)(gc >> 2), 0, TAG_SPIN, k0, k1, r); u = u24(r[gc & 3]); }
                 float p = det_sigmoid(gamma[i] * 2.0f);  // spin_gibbs.rs:95
                 out[i] = (u <= p) ? 1.0f : 0.0f;          // spin_gibbs.rs:97

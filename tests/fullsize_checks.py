@@ -120,22 +120,23 @@ def potts_check(T, O, side=64, K=10, chains=1024, slice_chains=8, sweeps=2, seed
     return out
 
 
-def lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4, ctx=None, J=0.4407, b=0.0, beta=1.0):
+def lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4, ctx=None, J=0.4407, b=0.0, beta=1.0, noise=1):
     """Bit-packed implicit lattice at side^2 spins, held whole and as `stripes` stripes, against the oracle's explicit
-    Ising program on the same torus (every chain); the recorded observable series against numpy on the final state."""
+    Ising program on the same torus (every chain) under the same key -> noise mapping (1 = the lattice engine's packed
+    mapping, 0 = the explicit program's); the recorded observable series against numpy on the final state."""
     from thrml_rs_b200 import lattice
     t0 = time.time()
     n = side * side
-    whole = lattice.DistributedStripe(side, side, J, b, beta, chains, None, ctx)
+    whole = lattice.DistributedStripe(side, side, J, b, beta, chains, None, ctx, noise=noise)
     whole.randomize(11)
     start = whole.download_local()  # [chain][row][col]
     whole.run_blocks(99, sweeps, record=True)
     final = whole.download_local()
     series = whole.series()
-    out = {"workload": "lattice", "side": side, "chains": chains, "sweeps": sweeps}
+    out = {"workload": "lattice", "side": side, "chains": chains, "sweeps": sweeps, "noise_mapping": "packed" if noise == 1 else "program"}
     ok = True
     if stripes > 1:
-        part = lattice.StripedLattice(side, side, J, b, beta, chains, n_stripes=stripes, ctx=ctx)
+        part = lattice.StripedLattice(side, side, J, b, beta, chains, n_stripes=stripes, ctx=ctx, noise=noise)
         part.upload(start)
         part.run_blocks(99, sweeps)
         bad = int(np.count_nonzero(part.download() != final))
@@ -151,6 +152,7 @@ def lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4, ctx=None, J=0
     om.add_ising(np.arange(n), np.full(n, b, np.float32), edges, np.full(len(edges), J, np.float32), beta)
     om.compile()
     os_ = O.State(om, chains, 0, threads=chains)
+    os_.set_spin_noise(noise)
     flat0, flat1 = start.reshape(chains, n), final.reshape(chains, n)
     for bi, blk in enumerate(blocks):
         os_.set_block(bi, flat0[:, blk].astype(np.float32))
@@ -182,13 +184,22 @@ def _philox(c0, c1, c2, c3, k0, k1):
     return c0, c1, c2, c3
 
 
-def spin_uniforms(n_nodes, chain_ids, key):
-    """u[chain][node] of the engine's spin noise mapping (24-bit uniforms), for the given global chain ids."""
+def spin_uniforms(n_nodes, chain_ids, key, mapping=0):
+    """u[chain][node] (24-bit uniforms) for the given global chain ids.  mapping 0: the gather kernels' (one 32-bit word per
+    draw, word c & 3 of Philox(n, c >> 2, 0, tag)); mapping 2: the dense path's (top 16 bits = half n & 1 of word (n >> 1) & 3
+    of Philox(n >> 3, c, 1, tag), low 16 bits = low half of word c & 3 of Philox(n, c >> 2, 2, tag))."""
     node = np.arange(n_nodes, dtype=np.uint64)[None, :]
     chain = np.asarray(chain_ids, dtype=np.uint64)[:, None]
-    words = _philox(node, chain >> np.uint64(2), 0, 0x5350494E, key & 0xFFFFFFFF, key >> 32)
-    sel = (chain & np.uint64(3)) + np.zeros_like(node)
-    r = np.choose(sel.astype(np.int64), words)
+    k0, k1 = key & 0xFFFFFFFF, key >> 32
+    TAG = 0x5350494E
+    pick = lambda words, sel: np.choose((sel + np.zeros((len(chain_ids), n_nodes), dtype=np.uint64)).astype(np.int64), words)
+    if mapping == 0:
+        r = pick(_philox(node, chain >> np.uint64(2), 0, TAG, k0, k1), chain & np.uint64(3))
+    else:
+        tw = pick(_philox(node >> np.uint64(3), chain, 1, TAG, k0, k1), (node >> np.uint64(1)) & np.uint64(3))
+        top = (tw >> (np.uint64(16) * (node & np.uint64(1)))) & np.uint64(0xFFFF)
+        low = pick(_philox(node, chain >> np.uint64(2), 2, TAG, k0, k1), chain & np.uint64(3)) & np.uint64(0xFFFF)
+        r = (top << np.uint64(16)) | low
     return (r >> np.uint64(8)).astype(np.float64) * 2.0 ** -24
 
 
@@ -225,6 +236,7 @@ def dense_check(T, O, n_visible=784, n_hidden=4096, chains=1024, slice_chains=16
         for start in starts:
             cnt = min(slice_chains, chains - start)
             os_ = O.State(om, cnt, start, threads=cnt)
+            os_.set_spin_noise(2)  # the dense path's key -> noise mapping
             for b in range(2):
                 os_.set_block(b, state.download_chains(b, start, cnt).astype(np.float32))
             o64, o32 = os_.fields(block)
@@ -241,7 +253,7 @@ def dense_check(T, O, n_visible=784, n_hidden=4096, chains=1024, slice_chains=16
         for start, cnt, os_, o64, o32, g in slices:
             os_.sample_single_block(block, key)
             got, want = state.download_chains(block, start, cnt), os_.get_block(block).astype(np.uint8)
-            u = np.clip(spin_uniforms(got.shape[1], np.arange(start, start + cnt), key), 1e-12, 1 - 1e-12)
+            u = np.clip(spin_uniforms(got.shape[1], np.arange(start, start + cnt), key, mapping=2), 1e-12, 1 - 1e-12)
             gap = np.abs(np.log(u / (1 - u)) - 2 * o64)
             draws += got.size
             within_1e6 += int(np.count_nonzero(gap < 1e-6))

@@ -10,6 +10,7 @@ two f32 fields' own measured errors open around the threshold: |logit(u) - 2 gam
 import numpy as np
 import pytest
 
+import fullsize_checks as F
 import models as M
 
 pytestmark = pytest.mark.gpu
@@ -30,27 +31,9 @@ def to_bf16(x):
     return u.astype(np.uint32).view(np.float32)
 
 
-def philox(c0, c1, c2, c3, k0, k1):
-    c0, c1, c2, c3 = [np.asarray(x, dtype=np.uint64) for x in np.broadcast_arrays(c0, c1, c2, c3)]
-    k0, k1 = np.uint64(k0), np.uint64(k1)
-    m32 = np.uint64(0xFFFFFFFF)
-    for _ in range(10):
-        p0 = np.uint64(0xD2511F53) * c0
-        p1 = np.uint64(0xCD9E8D57) * c2
-        c0, c1, c2, c3 = ((p1 >> np.uint64(32)) ^ c1 ^ k0) & m32, p1 & m32, ((p0 >> np.uint64(32)) ^ c3 ^ k1) & m32, p0 & m32
-        k0 = (k0 + np.uint64(0x9E3779B9)) & m32
-        k1 = (k1 + np.uint64(0xBB67AE85)) & m32
-    return c0, c1, c2, c3
-
-
 def spin_uniforms(n_nodes, chains, key, chain_offset=0):
-    """u[chain][node] of the engine's spin noise mapping."""
-    node = np.arange(n_nodes, dtype=np.uint64)[None, :]
-    chain = (np.arange(chains, dtype=np.uint64) + np.uint64(chain_offset))[:, None]
-    words = philox(node, chain >> np.uint64(2), 0, 0x5350494E, key & 0xFFFFFFFF, key >> 32)
-    sel = (chain & np.uint64(3)) + np.zeros_like(node)
-    r = np.choose(sel.astype(np.int64), words)
-    return (r >> np.uint64(8)).astype(np.float64) * 2.0 ** -24
+    """u[chain][node] of the dense path's key -> noise mapping."""
+    return F.spin_uniforms(n_nodes, np.arange(chains) + chain_offset, key, mapping=2)
 
 
 def rbm(T, n_v, n_h, seed, sigma=0.1):
@@ -96,6 +79,7 @@ def test_dense_update_matches_oracle(T, O, n_v, n_h, chains):
     assert prog.enable_dense(False) == 2
     assert [prog.block_kernel(i) for i in range(2)] == [3, 3]
     gs, os_ = T.ChainState(prog, chains), O.State(ob, chains)
+    os_.set_spin_noise(2)  # blocks on the dense path draw their noise under that path's own mapping
     for i, a in enumerate(M.random_states(desc, chains, 5)):
         gs.upload(i, a)
         os_.set_block(i, a.astype(np.float32))
@@ -176,6 +160,7 @@ def test_cd1_step_composition_and_statistics(T, O):
     assert np.array_equal(neg, (s(v1).T @ s(h1) / chains).astype(np.float32))
     # against the oracle's chain (same keys, same noise mapping): statistics agree within Monte-Carlo error
     os_ = O.State(ob, chains)
+    os_.set_spin_noise(2)
     os_.set_block(0, v0.astype(np.float32))
     os_.set_block(1, np.zeros((chains, n_h), np.float32))
     os_.sample_single_block(1, k0)

@@ -41,8 +41,9 @@ def test_potts_64_cubed(T, O):
     assert res["ok"], res
 
 
-def test_lattice_2048_squared_whole_and_striped(T, O):
-    res = F.lattice_check(T, O, side=2048, chains=16, sweeps=2, stripes=4)
+@pytest.mark.parametrize("side,noise", [(2048, 1), (1024, 0)])
+def test_lattice_whole_and_striped(T, O, side, noise):
+    res = F.lattice_check(T, O, side=side, chains=16, sweeps=2, stripes=4, noise=noise)
     assert res["ok"], res
 
 

@@ -20,19 +20,23 @@ def torus_model(H, W, J, b, beta):
     return desc, blocks, e
 
 
-@pytest.mark.parametrize("H,W,chains,stripes", [(8, 64, 16, 1), (6, 128, 4, 1), (8, 64, 16, 2), (12, 64, 8, 3), (4, 192, 32, 2)])
-def test_lattice_matches_explicit_program(T, O, H, W, chains, stripes):
+@pytest.mark.parametrize("noise", [0, 1, 2])
+@pytest.mark.parametrize("H,W,chains,stripes", [(8, 64, 16, 1), (6, 128, 4, 1), (8, 64, 16, 2), (12, 64, 8, 3), (4, 192, 32, 2), (16, 256, 64, 1)])
+def test_lattice_matches_explicit_program(T, O, H, W, chains, stripes, noise):
+    """noise 0: the explicit program's key -> noise mapping; noise 1: the lattice engine's packed mapping, which the oracle
+    restates for its explicit program (set_spin_noise).  Fields, thresholds and the draw rule are the same in both."""
     from thrml_rs_b200 import lattice
     J, b, beta = 0.4407, 0.07, 0.9
     desc, blocks, edges = torus_model(H, W, J, b, beta)
     om = M.fill(O.Model(desc["kinds"]), desc)
     os_ = O.State(om, chains)
+    os_.set_spin_noise(min(noise, 1))  # 2 = mapping 1 through the table route
     rng = np.random.default_rng(H * W + chains)
     spins = rng.integers(0, 2, (chains, H, W)).astype(np.uint8)
     flat = spins.reshape(chains, H * W)
     for bi, blk in enumerate(blocks):
         os_.set_block(bi, flat[:, blk].astype(np.float32))
-    lat = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=stripes)
+    lat = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=stripes, noise=noise)
     lat.upload(spins)
     assert np.array_equal(lat.download(), spins)
     for step, n_iters in enumerate([1, 3]):
@@ -56,7 +60,7 @@ def test_lattice_randomize_matches_explicit_randomize(T, O):
     prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
     st = T.ChainState(prog, chains)
     st.randomize(5)
-    lat = lattice.StripedLattice(H, W, 0.3, 0.0, 1.0, chains)
+    lat = lattice.StripedLattice(H, W, 0.3, 0.0, 1.0, chains, noise=lattice.NOISE_PROGRAM)
     lat.randomize(5)
     got = lat.download().reshape(chains, H * W)
     for bi, blk in enumerate(blocks):
@@ -73,17 +77,18 @@ def test_lattice_argument_checks(T):
         lattice.LatticeStripe(8, 64, 4, 8, 0.4, 0.0, 1.0, 16)
 
 
-@pytest.mark.parametrize("H,W,chains", [(8, 64, 16), (6, 192, 4), (16, 128, 32)])
-def test_library_sweep_driver_bits_and_series(T, H, W, chains):
+@pytest.mark.parametrize("noise", [0, 1, 2])
+@pytest.mark.parametrize("H,W,chains", [(8, 64, 16), (6, 192, 4), (16, 128, 32), (4, 64, 256)])
+def test_library_sweep_driver_bits_and_series(T, H, W, chains, noise):
     """thrml_lattice_run_blocks on a whole lattice = the per-colour calls driven from the host; the bit-packed transfers
     round-trip; the recorded series holds, per sweep, the sums thrml_lattice_observe would report; moments follow."""
     from thrml_rs_b200 import lattice
-    J, b, beta = 0.4407, 0.05, 1.0
+    J, b, beta = (0.4407, 0.05, 1.0) if chains != 32 else (1.7, -0.6, 1.0)  # the second set saturates some thresholds (probabilities near 0 and 1)
     rng = np.random.default_rng(H + W)
     spins = rng.integers(0, 2, (chains, H, W)).astype(np.uint8)
-    host_driven = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=1)
+    host_driven = lattice.StripedLattice(H, W, J, b, beta, chains, n_stripes=1, noise=noise)
     host_driven.upload(spins)
-    lib = lattice.DistributedStripe(H, W, J, b, beta, chains, None)
+    lib = lattice.DistributedStripe(H, W, J, b, beta, chains, None, noise=noise)
     bits = np.packbits(spins.reshape(chains, H, W // 32, 32), axis=3, bitorder="little").view("<u4").reshape(chains, H, W // 32)
     lib.upload_bits(bits)
     assert np.array_equal(lib.download_local(), spins)

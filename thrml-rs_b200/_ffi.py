@@ -94,6 +94,7 @@ _SIGNATURES = {
     "thrml_lattice_randomize": (C.c_int32, [_P, C.c_uint64]),
     "thrml_lattice_upload": (C.c_int32, [_P, _P]),
     "thrml_lattice_download": (C.c_int32, [_P, _P]),
+    "thrml_lattice_set_noise": (C.c_int32, [_P, C.c_int32]),
     "thrml_lattice_upload_bits": (C.c_int32, [_P, _P]),
     "thrml_lattice_download_bits": (C.c_int32, [_P, _P]),
     "thrml_lattice_update": (C.c_int32, [_P, C.c_int32, C.c_uint64, C.c_int64, C.c_int64]),

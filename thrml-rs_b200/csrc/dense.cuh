@@ -3,9 +3,9 @@
 // A spin block whose every neighbour lies in one other block (an RBM layer) has the local field
 //     gamma[chain][i] = bias[i] + sum_j W[i][j] * (2 s[chain][j] - 1)            (spin_gibbs.rs:512-611 for a complete bipartite table)
 // which is the GEMM  D[chains x n_out] = S[chains x n_in] * W^T  with S = +-1 in bf16 and W in bf16, f32 accumulation.
-// k_dense_gemm<EPI_SAMPLE> runs that GEMM and finishes each output tile in registers: bias, sigmoid, the same
-// counter-based noise as every other kernel, Bernoulli draw, and stores of the new state (bytes, engine layout) and
-// of its +-1 bf16 image (the next layer's S operand).
+// k_dense_gemm<EPI_SAMPLE> runs that GEMM and finishes each output tile in registers: bias, sigmoid, counter-based noise
+// under this path's own key -> noise mapping (one generator call gives a lane the top halves of eight draws of its chain),
+// Bernoulli draw, and stores of the new state (bytes, engine layout) and of its +-1 bf16 image (the next layer's S operand).
 // k_dense_gemm<EPI_CORR> computes pair correlations <s_a s_b> over chains straight from the engine's byte state
 // (0/1 bytes, chains contiguous = K-major) with the 8-bit integer MMA: N11 = sum_c x_a x_b, then
 // sum_c s_a s_b = 4 N11 - 2 N1a - 2 N1b + C exactly.
@@ -157,18 +157,6 @@ struct GemmArgs {
     float* fields_out;        // [m_total = chains][n_total]: bias + accumulator, the local field the sampling epilogue would draw from
 };
 
-// In-quad 4x4 transpose: on return x[k] is the word this lane's position in its quad selects, taken from quad lane k.
-__device__ __forceinline__ void quad_transpose(uint32_t (&x)[4], int lane) {
-    uint32_t a = (lane & 1) ? x[0] : x[1], b = (lane & 1) ? x[2] : x[3];
-    a = __shfl_xor_sync(0xffffffffu, a, 1);
-    b = __shfl_xor_sync(0xffffffffu, b, 1);
-    if (lane & 1) { x[0] = a; x[2] = b; } else { x[1] = a; x[3] = b; }
-    uint32_t c = (lane & 2) ? x[0] : x[2], d = (lane & 2) ? x[1] : x[3];
-    c = __shfl_xor_sync(0xffffffffu, c, 2);
-    d = __shfl_xor_sync(0xffffffffu, d, 2);
-    if (lane & 2) { x[0] = c; x[1] = d; } else { x[2] = c; x[3] = d; }
-}
-
 // Finishes 16 accumulator columns of one warp's 32 rows: `acc` holds this lane's row (row_base + lane), columns
 // col0..col0+15 of the whole problem.
 template <int EPI>
@@ -176,7 +164,6 @@ __device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[
     const int row = row_base + lane;
     if (EPI == EPI_SAMPLE) {
         // row = chain, columns = nodes of the updated block
-        uint32_t rnd[16];
         float bias[16];
         if (col0 + 16 <= g.n_total) {
 #pragma unroll
@@ -188,37 +175,50 @@ __device__ __forceinline__ void finish_chunk(const GemmArgs& g, uint32_t (&acc)[
 #pragma unroll
             for (int j = 0; j < 16; ++j) bias[j] = col0 + j < g.n_total ? __ldg(g.bias + col0 + j) : 0.0f;
         }
+        // Noise of the dense path (its own key -> noise mapping; the reference never consumes its keys).  The 32-bit draw of
+        // node n and global chain c is
+        //     top 16 bits = half (n & 1) of word ((n >> 1) & 3) of Philox(n >> 3, c, 1, TAG_SPIN)   -- one call: 8 nodes of one chain
+        //     low 16 bits = low half of word (c & 3) of Philox(n, c >> 2, 2, TAG_SPIN)
+        // and the spin is 1 iff the draw's top 24 bits, as a uniform, are <= sigmoid(2 gamma).  A lane owns one chain and 16
+        // consecutive nodes here, so two calls give it every top half it needs and nothing crosses lanes; the low half is
+        // fetched only for a draw whose top half cannot decide.
+        const uint32_t chain = 4u * g.chain_word0 + static_cast<uint32_t>(row);
+        uint32_t top[16];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            const int my_col = col0 + 4 * t + (lane & 3);
-            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(my_col), g.chain_word0 + static_cast<uint32_t>(row >> 2), 0u, TAG_SPIN, g.rk);
-            uint32_t x[4] = {r.x, r.y, r.z, r.w};
-            quad_transpose(x, lane);
+        for (int t = 0; t < 2; ++t) {
+            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(col0 >> 3) + t, chain, 1u, TAG_SPIN, g.rk);
+            const uint32_t wds[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) rnd[4 * t + j] = x[j];
+            for (int i = 0; i < 4; ++i) {
+                top[8 * t + 2 * i] = wds[i] & 0xffffu;
+                top[8 * t + 2 * i + 1] = wds[i] >> 16;
+            }
         }
-        // d = 2^24 (u - p) with the approximate sigmoid p = 1 / (1 + 2^(-2 log2(e) gamma)), as (r >> 8) - 1 / (2^-24 (1 + e))
-        // (a huge exponential gives p = 0, a vanishing one p = 1); the spin is the sign of d.  Draws within 4e-6 of p (four
-        // times the approximation's worst error) are redone with the exact sigmoid.  The integer pipe is the busy one
-        // here, so the decisions stay in the sign bits of d: no per-element bit masks are built.
-        constexpr float NEAR = 67.2f;  // 4e-6 * 2^24
+        // d = 2^16 (u_top - p) with the approximate sigmoid p = 1 / (1 + 2^(-2 log2(e) gamma)), as top - 1 / (2^-16 (1 + e))
+        // (a huge exponential gives p = 0, a vanishing one p = 1).  The full uniform lies in [top, top + 1) 2^-16, so the spin is
+        // 1 for d <= -1 and 0 for d >= 0 once the approximation's error (below 0.3 of these units: four times its worst 1e-6)
+        // is allowed for; inside (-1.3, 0.3) the low half is drawn and the exact sigmoid decides.  The decisions stay in the
+        // sign bits of d: no per-element bit masks are built.
+        constexpr float ZONE_MID = 0.5f, ZONE_HALF = 0.8f;
         float d[16];
-        float nearest = 16777216.0f;
+        float nearest = 65536.0f;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
             const float gamma = __fadd_rn(bias[j], __uint_as_float(acc[j]));
-            float e, p24;
+            float e, p16;
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(gamma * -2.885390081777927f));
-            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(e, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));
-            d[j] = __uint2float_rn(rnd[j] >> 8) - p24;
-            nearest = fminf(nearest, fabsf(d[j]));
+            asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p16) : "f"(fmaf(e, 1.52587890625e-5f, 1.52587890625e-5f)));
+            d[j] = __uint2float_rn(top[j]) - p16;
+            nearest = fminf(nearest, fabsf(d[j] + ZONE_MID));
         }
-        if (__any_sync(0xffffffffu, nearest <= NEAR)) {
+        if (__any_sync(0xffffffffu, nearest <= ZONE_HALF)) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-                if (fabsf(d[j]) <= NEAR) {
+                if (fabsf(d[j] + ZONE_MID) <= ZONE_HALF) {
+                    const U4 rr = philox4x32_10_rk(static_cast<uint32_t>(col0 + j), chain >> 2, 2u, TAG_SPIN, g.rk);
+                    const uint32_t draw = (top[j] << 16) | (pick(rr, chain & 3u) & 0xffffu);
                     const float xx = __fmul_rn(__fadd_rn(bias[j], __uint_as_float(acc[j])), 2.0f);
-                    d[j] = u24(rnd[j]) <= det_sigmoid(xx) ? -1.0f : 1.0f;
+                    d[j] = u24(draw) <= det_sigmoid(xx) ? -1.0f : 1.0f;
                 }
         }
         // state bytes: lane L takes column L&15 and the 16 chains of half L>>4 of this warp's 32 rows

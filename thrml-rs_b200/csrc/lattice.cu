@@ -11,6 +11,7 @@
 // Layout: plane[colour][stripe row + 1][word][chain] u32, 32 spins of one colour and one row per word, chains innermost;
 // stripe rows 0 and n_rows+1 are halo rows holding the neighbouring stripes' boundary rows.
 #include <algorithm>
+#include <cstring>
 #include <memory>
 #include <vector>
 
@@ -35,6 +36,8 @@ struct LatArgs {
     int32_t n_rows, words, chains, colour;
     uint32_t chain_word0;
     PhiloxRoundKeys rk;  // round keys of the block key, computed once on the host
+    uint32_t vmask[8][5];  // bit-sliced mapping: all-ones where bit b of the threshold's top byte is set for s up neighbours
+    long long* record;     // [2][chains] sums to add this pass's observables to, or null
 };
 
 // One thread = one word (32 spins of one row and colour) x four chains.  The four neighbour bits of each spin are
@@ -109,6 +112,128 @@ __global__ void __launch_bounds__(128) k_lattice_update(const __grid_constant__ 
         for (int c = 0; c < 4; ++c) out[c] |= byte[c] << (8 * g);
     }
     *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// The update with the engine's bit-sliced noise mapping (thrml_lattice_set_noise, mapping 1).  The 32-bit word a spin's draw
+// compares with its threshold is assembled from counter-based calls that are shared as widely as the layout allows:
+//     top byte, bit b  = bit (n & 31) of word (b & 3) of Philox(n >> 5, chain, 1 + (b >> 2), TAG_SPIN)   -- two calls serve 32 spins
+//     low 24 bits      = low 24 bits of word (chain & 3) of Philox(n, chain >> 2, 3, TAG_SPIN)
+// (n = index of the spin inside its colour block, chain = global chain id).  The top byte alone decides unless it equals
+// the threshold's top byte (one draw in 256); only then is the third call made.  Same rule `word <= threshold`, same
+// 24-bit resolution of the uniform.
+// The top bytes of 32 spins arrive as eight bit planes, so the comparison runs bit-sliced on whole words: the four neighbour
+// words are added into three sum planes, the threshold's top byte — when it depends on the configuration only through the
+// number of up neighbours (SYM, checked on the host for every seam class) — becomes eight planes of a five-way select, and
+// a ripple comparator from the low bit up yields `less` and `equal` for 32 spins in two logic operations per bit.  Without
+// that symmetry the same mapping is evaluated spin by spin from the threshold table.
+// RECORD (the second colour of a sweep): every bond joins the two colours, so this pass sees each bond once and each word
+// of the other colour once; per chain it adds the sum of spins and the sum of bond products to `record`.
+// CTAs stride over the words; a thread keeps its chain quad for the whole launch.
+template <bool SYM, bool RECORD>
+__global__ void __launch_bounds__(128, 4) k_lattice_update_sliced(const __grid_constant__ LatArgs a, int32_t row_begin, int32_t row_end) {
+    __shared__ uint32_t s_lut[9 * 16];
+    for (int i = threadIdx.x; i < 9 * 16; i += blockDim.x) s_lut[i] = a.lut[i];
+    __syncthreads();
+    const int quads = a.chains >> 2;
+    const int64_t per_row = static_cast<int64_t>(a.words) * quads;
+    const int64_t total = static_cast<int64_t>(row_end - row_begin) * per_row;
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;  // a multiple of 128, hence of `quads`
+    int32_t spins[4] = {0, 0, 0, 0}, agree[4] = {0, 0, 0, 0};
+    const int q = static_cast<int>((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) % quads);
+    for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < total; gid += step) {
+        const int r = row_begin + static_cast<int>(gid / per_row);
+        const int w = static_cast<int>((gid % per_row) / quads);
+        const int64_t gi = a.row0 + r;
+        const int p = static_cast<int>((gi + a.colour) & 1);
+        auto at = [&](const uint32_t* plane, int srow, int word) {
+            return *reinterpret_cast<const uint4*>(plane + (static_cast<int64_t>(srow) * a.words + word) * a.chains + 4 * q);
+        };
+        const uint4 up = at(a.other, r, w), down = at(a.other, r + 2, w), same = at(a.other, r + 1, w);
+        const int wadj = p == 0 ? (w == 0 ? a.words - 1 : w - 1) : (w == a.words - 1 ? 0 : w + 1);
+        const uint4 adj = at(a.other, r + 1, wadj);
+        const uint32_t U[4] = {up.x, up.y, up.z, up.w}, D[4] = {down.x, down.y, down.z, down.w};
+        const uint32_t S[4] = {same.x, same.y, same.z, same.w}, A[4] = {adj.x, adj.y, adj.z, adj.w};
+        const int row_cls = gi == 0 ? 1 : (gi == a.H - 1 ? 2 : 0);
+        const bool first_col = p == 0 && w == 0, last_col = p == 1 && w == a.words - 1;
+        const uint32_t node_base = static_cast<uint32_t>(gi * (a.W >> 1) + 32 * static_cast<int64_t>(w));  // a multiple of 32
+        uint32_t out[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint32_t Lc = p == 0 ? ((S[c] << 1) | (A[c] >> 31)) : S[c], Rc = p == 0 ? S[c] : ((S[c] >> 1) | (A[c] << 31));
+            const uint32_t chain = 4u * (a.chain_word0 + static_cast<uint32_t>(q)) + c;
+            const U4 ra = philox4x32_10_rk(node_base >> 5, chain, 1u, TAG_SPIN, a.rk), rb = philox4x32_10_rk(node_base >> 5, chain, 2u, TAG_SPIN, a.rk);
+            const uint32_t rnd[8] = {ra.x, ra.y, ra.z, ra.w, rb.x, rb.y, rb.z, rb.w};  // plane b: bit k = bit b of spin k's top byte
+            uint32_t lt = 0u, eq = 0xffffffffu;
+            if (SYM) {
+                // number of up neighbours per spin as three planes (0..4)
+                const uint32_t x0 = U[c] ^ Lc, x1 = U[c] & Lc, y0 = Rc ^ D[c], y1 = Rc & D[c];
+                const uint32_t s0 = x0 ^ y0, c0 = x0 & y0, s1 = x1 ^ y1 ^ c0, s2 = x1 & y1;
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    const uint32_t lo = (s0 & a.vmask[b][1]) | (~s0 & a.vmask[b][0]), hi = (s0 & a.vmask[b][3]) | (~s0 & a.vmask[b][2]);
+                    const uint32_t mid = (s1 & hi) | (~s1 & lo);
+                    const uint32_t t = (s2 & a.vmask[b][4]) | (~s2 & mid);  // bit b of the threshold's top byte, per spin
+                    const uint32_t x = rnd[b] ^ t;
+                    lt = (t & ~rnd[b]) | (~x & lt);  // less so far, from the low bit up: a higher bit overrides
+                    eq &= ~x;
+                }
+            } else {
+                lt = 0u;
+                eq = 0u;
+#pragma unroll 1
+                for (int k = 0; k < 32; ++k) {
+                    uint32_t h8 = 0;
+#pragma unroll
+                    for (int b = 0; b < 8; ++b) h8 |= ((rnd[b] >> k) & 1u) << b;
+                    const uint32_t cfg = ((U[c] >> k) & 1u) | (((Lc >> k) & 1u) << 1) | (((Rc >> k) & 1u) << 2) | (((D[c] >> k) & 1u) << 3);
+                    const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
+                    const uint32_t T8 = s_lut[(row_cls * 3 + col_cls) * 16 + cfg] >> 24;
+                    lt |= (h8 < T8 ? 1u : 0u) << k;
+                    eq |= (h8 == T8 ? 1u : 0u) << k;
+                }
+            }
+            uint32_t o = lt;
+            // ties (top bytes equal): the low 24 bits of the draw decide, from a call of their own
+            uint32_t m = eq;
+            while (m) {
+                const int k = __ffs(m) - 1;
+                m &= m - 1u;
+                const uint32_t cfg = ((U[c] >> k) & 1u) | (((Lc >> k) & 1u) << 1) | (((Rc >> k) & 1u) << 2) | (((D[c] >> k) & 1u) << 3);
+                const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
+                const uint32_t T = s_lut[(row_cls * 3 + col_cls) * 16 + cfg];
+                const U4 rr = philox4x32_10_rk(node_base + k, a.chain_word0 + q, 3u, TAG_SPIN, a.rk);
+                const uint32_t low = pick(rr, c) & 0xffffffu;
+                o |= (low <= (T & 0xffffffu) ? 1u : 0u) << k;
+            }
+            out[c] = o;
+            if (RECORD) {
+                spins[c] += __popc(o) + __popc(S[c]);
+                agree[c] += __popc(~(o ^ U[c])) + __popc(~(o ^ D[c])) + __popc(~(o ^ Lc)) + __popc(~(o ^ Rc));
+            }
+        }
+        *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
+    }
+    if (RECORD) {
+        // words seen by this thread: every one holds 32 spins of each colour and 128 bonds
+        int64_t items = 0;
+        {
+            const int64_t first = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            if (first < total) items = (total - first + step - 1) / step;
+        }
+        const int lane = threadIdx.x & 31;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            long long sp = 2LL * spins[c] - 64LL * items, bo = 2LL * agree[c] - 128LL * items;
+            for (int off = 16; off >= quads && off >= 1; off >>= 1) {  // lanes that share the chain quad
+                sp += __shfl_xor_sync(0xffffffffu, sp, off);
+                bo += __shfl_xor_sync(0xffffffffu, bo, off);
+            }
+            if (lane < quads || quads > 32) {
+                atomicAdd(reinterpret_cast<unsigned long long*>(a.record + 4 * q + c), static_cast<unsigned long long>(sp));
+                atomicAdd(reinterpret_cast<unsigned long long*>(a.record + a.chains + 4 * q + c), static_cast<unsigned long long>(bo));
+            }
+        }
+    }
 }
 
 // Threshold tables: gamma = (0 + b) + (((0 + t1) + t2) + t3) + t4 with the neighbours taken in `order`, exactly as the
@@ -247,12 +372,17 @@ struct thrml_lattice {
     DevBuf plane[2], lut, order, obs, scratch;
     size_t row_bytes = 0;  // one row of one colour
     float coupling = 0.f, bias = 0.f;
+    int32_t noise = 1;  // THRML_LATTICE_NOISE_*
+    bool force_table = false;   // THRML_LATTICE_NOISE_PACKED_TABLE: take the table route even when the bit-sliced one applies
+    bool symmetric = false;     // the thresholds' top bytes depend on the configuration only through the number of up neighbours
+    uint32_t vmask[8][5] = {};  // the planes of that dependence
     // sweep driver: halo exchange on a side stream, overlapped with the interior rows
     cudaStream_t side = nullptr;
     cudaEvent_t ev_edge = nullptr, ev_halo = nullptr;
     // per-sweep observable series: record t holds, per chain, this stripe's sum of spins and sum of bond products
     DevBuf series;
     int64_t series_len = 0, series_cap = 0;
+    long long* record_into = nullptr;  // set by the sweep driver around the second colour's launches: the update records the observables itself
     uint32_t* p(int c) const { return static_cast<uint32_t*>(plane[c].p); }
     ~thrml_lattice() {
         if (ev_edge) cudaEventDestroy(ev_edge);
@@ -306,7 +436,25 @@ int32_t thrml_lattice_create(thrml_ctx* ctx, int64_t height, int64_t width, int6
     CU_TRY(cudaMemcpyAsync(L->order.p, order.data(), order.size() * 4, cudaMemcpyHostToDevice, ctx->stream));
     k_lattice_build_lut<<<1, 9 * 16, 0, ctx->stream>>>(beta * coupling, beta * bias, static_cast<const int32_t*>(L->order.p), static_cast<uint32_t*>(L->lut.p));
     CU_TRY(cudaGetLastError());
-    CU_TRY(cudaStreamSynchronize(ctx->stream));
+    {
+        uint32_t h_lut[9 * 16];
+        CU_TRY(cudaMemcpyAsync(h_lut, L->lut.p, sizeof(h_lut), cudaMemcpyDeviceToHost, ctx->stream));
+        CU_TRY(cudaStreamSynchronize(ctx->stream));
+        uint32_t top[5];
+        bool sym = true;
+        for (int sdx = 0; sdx <= 4; ++sdx) top[sdx] = 0x100u;  // unset
+        for (int cls = 0; cls < 9 && sym; ++cls)
+            for (int cfg = 0; cfg < 16; ++cfg) {
+                const int ups = __builtin_popcount(static_cast<unsigned>(cfg));
+                const uint32_t t8 = h_lut[cls * 16 + cfg] >> 24;
+                if (top[ups] == 0x100u) top[ups] = t8;
+                else if (top[ups] != t8) { sym = false; break; }
+            }
+        L->symmetric = sym;
+        if (sym)
+            for (int b = 0; b < 8; ++b)
+                for (int sdx = 0; sdx <= 4; ++sdx) L->vmask[b][sdx] = ((top[sdx] >> b) & 1u) ? 0xffffffffu : 0u;
+    }
     *out = L.release();
     return THRML_OK;
 }
@@ -317,6 +465,14 @@ void thrml_lattice_destroy(thrml_lattice* L) {
     delete L;
 }
 
+int32_t thrml_lattice_set_noise(thrml_lattice* L, int32_t mapping) {
+    if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (mapping != THRML_LATTICE_NOISE_PROGRAM && mapping != THRML_LATTICE_NOISE_PACKED && mapping != THRML_LATTICE_NOISE_PACKED_TABLE)
+        return fail(THRML_ERR_INVALID_ARG, "unknown noise mapping");
+    L->noise = mapping == THRML_LATTICE_NOISE_PROGRAM ? THRML_LATTICE_NOISE_PROGRAM : THRML_LATTICE_NOISE_PACKED;
+    L->force_table = mapping == THRML_LATTICE_NOISE_PACKED_TABLE;
+    return THRML_OK;
+}
 int32_t thrml_lattice_randomize(thrml_lattice* L, uint64_t key) {
     if (!L) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(L->device));
@@ -423,7 +579,21 @@ int32_t thrml_lattice_update(thrml_lattice* L, int32_t colour, uint64_t block_ke
     LatArgs a{L->p(colour), L->p(1 - colour), static_cast<const uint32_t*>(L->lut.p), L->H, L->W, L->row0, static_cast<int32_t>(L->n_rows), L->words,
               static_cast<int32_t>(L->n_chains), colour, static_cast<uint32_t>(L->chain_offset >> 2), make_round_keys(block_key)};
     const int64_t threads = (row_end - row_begin) * L->words * (L->n_chains / 4);
-    k_lattice_update<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(a, static_cast<int32_t>(row_begin), static_cast<int32_t>(row_end));
+    if (L->noise == THRML_LATTICE_NOISE_PACKED) {
+        std::memcpy(a.vmask, L->vmask, sizeof(a.vmask));
+        a.record = L->record_into;
+        const unsigned grid = static_cast<unsigned>(std::min<int64_t>((threads + 127) / 128, static_cast<int64_t>(L->ctx->sm_count) * 12));
+        const int32_t rb = static_cast<int32_t>(row_begin), re = static_cast<int32_t>(row_end);
+        if (L->symmetric && !L->force_table) {
+            if (a.record) k_lattice_update_sliced<true, true><<<grid, 128, 0, L->ctx->stream>>>(a, rb, re);
+            else k_lattice_update_sliced<true, false><<<grid, 128, 0, L->ctx->stream>>>(a, rb, re);
+        } else {
+            if (a.record) k_lattice_update_sliced<false, true><<<grid, 128, 0, L->ctx->stream>>>(a, rb, re);
+            else k_lattice_update_sliced<false, false><<<grid, 128, 0, L->ctx->stream>>>(a, rb, re);
+        }
+    } else {
+        k_lattice_update<<<static_cast<unsigned>((threads + 127) / 128), 128, 0, L->ctx->stream>>>(a, static_cast<int32_t>(row_begin), static_cast<int32_t>(row_end));
+    }
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }
@@ -492,7 +662,8 @@ static int32_t lat_refresh_halos(thrml_lattice* L, int32_t colour, thrml_comm* c
     if (!comm || comm->world == 1) return thrml_lattice_wrap_halo(L, colour);
     return lat_exchange(L, colour, comm, L->ctx->stream);
 }
-static int32_t lat_record(thrml_lattice* L) {
+// Next free record of the observable series (zeroed), growing the buffer when it is full.
+static int32_t lat_next_record(thrml_lattice* L, long long** slot) {
     const size_t rec = static_cast<size_t>(2 * L->n_chains) * 8;
     if (L->series_len == L->series_cap) {  // grow, keeping the records
         const int64_t cap = std::max<int64_t>(1024, 2 * L->series_cap);
@@ -505,12 +676,16 @@ static int32_t lat_record(thrml_lattice* L) {
         std::swap(L->series.bytes, bigger.bytes);
         L->series_cap = cap;
     }
+    *slot = static_cast<long long*>(L->series.p) + L->series_len * 2 * L->n_chains;
+    ++L->series_len;
+    return THRML_OK;
+}
+// The observable kernel on its own (noise mapping 0, whose update kernel does not record).
+static int32_t lat_observe_into(thrml_lattice* L, long long* slot) {
     const int64_t cells = L->n_rows * L->words;
     const int ctas = static_cast<int>(std::min<int64_t>((cells * L->n_chains + 255) / 256, 4096));
-    k_lattice_observe<<<ctas, 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), L->row0, static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains),
-                                                        static_cast<long long*>(L->series.p) + L->series_len * 2 * L->n_chains);
+    k_lattice_observe<<<ctas, 256, 0, L->ctx->stream>>>(L->p(0), L->p(1), L->row0, static_cast<int32_t>(L->n_rows), L->words, static_cast<int32_t>(L->n_chains), slot);
     CU_TRY(cudaGetLastError());
-    ++L->series_len;
     return THRML_OK;
 }
 
@@ -538,10 +713,20 @@ int32_t thrml_lattice_run_blocks(thrml_lattice* L, uint64_t key, int64_t n_iters
     cudaStream_t st = L->ctx->stream;
     std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
     rng_split(key, n_iters, keys.data());  // run_blocks: key.split(n_iters)
+    struct ClearRecord {  // no later per-colour call may inherit the record pointer, whichever way this function returns
+        thrml_lattice* lat;
+        ~ClearRecord() { lat->record_into = nullptr; }
+    } clear_record{L};
+    const bool fused_record = record && L->noise == THRML_LATTICE_NOISE_PACKED;  // that mapping's update kernel records while it updates
     for (int64_t it = 0; it < n_iters; ++it) {
         uint64_t k2[2];
         rng_split(keys[it], 2, k2);  // sample_blocks: one key per free block
+        long long* slot = nullptr;
+        if (record)
+            if (int32_t rc = lat_next_record(L, &slot)) return rc;
         for (int colour = 0; colour < 2; ++colour) {
+            // the second colour's pass sees every bond and every word of the first colour exactly once
+            L->record_into = fused_record && colour == 1 ? slot : nullptr;
             if (!overlap) {
                 if (int32_t rc = lat_update_rows(L, colour, k2[colour], 0, L->n_rows)) return rc;
                 if (int32_t rc = lat_refresh_halos(L, colour, comm)) return rc;
@@ -557,8 +742,9 @@ int32_t thrml_lattice_run_blocks(thrml_lattice* L, uint64_t key, int64_t n_iters
             if (int32_t rc = lat_update_rows(L, colour, k2[colour], 1, L->n_rows - 1)) return rc;
             CU_TRY(cudaStreamWaitEvent(st, L->ev_halo, 0));  // the other colour reads these halo rows next
         }
-        if (record)
-            if (int32_t rc = lat_record(L)) return rc;
+        L->record_into = nullptr;
+        if (record && !fused_record)
+            if (int32_t rc = lat_observe_into(L, slot)) return rc;
     }
     return THRML_OK;
 }

@@ -14,13 +14,19 @@ from . import engine as _eng
 from ._ffi import check, lib, ptr
 
 
+NOISE_PROGRAM = 0  # the explicit program's key -> noise mapping: states equal IsingSamplingProgram's on the same torus
+NOISE_PACKED = 1   # the lattice engine's own mapping (default): two generator calls give the top bytes of 32 spins as bit planes
+NOISE_PACKED_TABLE = 2  # the same mapping, thresholds looked up spin by spin (the route for thresholds the bit-sliced compare cannot take)
+
+
 class LatticeStripe:
-    def __init__(self, height, width, row_begin, n_rows, coupling, bias, beta, n_chains, chain_offset=0, ctx=None):
+    def __init__(self, height, width, row_begin, n_rows, coupling, bias, beta, n_chains, chain_offset=0, ctx=None, noise=NOISE_PACKED):
         self.ctx = ctx or _eng.default_context()
         self.height, self.width, self.row_begin, self.n_rows, self.n_chains = height, width, row_begin, n_rows, n_chains
         self.h = C.c_void_p()
         check(lib().thrml_lattice_create(self.ctx.h, C.c_int64(height), C.c_int64(width), C.c_int64(row_begin), C.c_int64(n_rows), C.c_float(coupling),
                                          C.c_float(bias), C.c_float(beta), C.c_int64(n_chains), C.c_int64(chain_offset), C.byref(self.h)))
+        check(lib().thrml_lattice_set_noise(self.h, C.c_int32(noise)))
 
     def __del__(self):
         h, self.h = getattr(self, "h", None), None
@@ -86,9 +92,9 @@ def stripe_rows(height, n_stripes):
 class StripedLattice:
     """All stripes of a lattice inside one process (one stripe = the whole lattice, or several on one device)."""
 
-    def __init__(self, height, width, coupling, bias, beta, n_chains, n_stripes=1, ctx=None):
+    def __init__(self, height, width, coupling, bias, beta, n_chains, n_stripes=1, ctx=None, noise=NOISE_PACKED):
         self.height, self.width, self.n_chains = height, width, n_chains
-        self.stripes = [LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx) for r0, n in stripe_rows(height, n_stripes)]
+        self.stripes = [LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx, noise) for r0, n in stripe_rows(height, n_stripes)]
 
     def refresh_halos(self, colour):
         n = len(self.stripes)
@@ -142,12 +148,12 @@ class DistributedStripe:
     library's thrml_lattice_run_blocks; this class only holds the handles.  `comm` = None for a single process holding
     the whole lattice."""
 
-    def __init__(self, height, width, coupling, bias, beta, n_chains, comm=None, ctx=None):
+    def __init__(self, height, width, coupling, bias, beta, n_chains, comm=None, ctx=None, noise=NOISE_PACKED):
         self.comm = comm
         self.rank = comm.rank if comm is not None else 0
         self.world = comm.world_size if comm is not None else 1
         r0, n = stripe_rows(height, self.world)[self.rank]
-        self.stripe = LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx)
+        self.stripe = LatticeStripe(height, width, r0, n, coupling, bias, beta, n_chains, 0, ctx, noise)
         self.n_chains = n_chains
 
     def _comm(self):
