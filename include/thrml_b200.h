@@ -289,6 +289,10 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
 /* Bring-up check of the CTA-pair tensor-core kernels (no reference counterpart): after a pair launch on this state, both
  * CTAs of a pair must have been given the same tensor-memory base address; THRML_ERR_CUDA if they differ. */
 int32_t thrml_debug_pair_tmem_check(thrml_state* s);
+/* thrml_cd1_step with the visible data held in another state of the same program and chain count (a resident data set that
+ * many steps start from): `data`'s visible block is read for h0 and <v0 h0> and is not modified; v1 and h1 land in `s`. */
+int32_t thrml_cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, float* pos_host,
+                            float* neg_host);
 /* Local field gamma[chain][node] (spin block) or logits theta[chain][node][K] (categorical block) of a free
  * block in the current state — spin_gibbs.rs:512-611 / softmax.rs:586-709. */
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out);

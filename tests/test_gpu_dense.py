@@ -198,3 +198,24 @@ def test_moment_observer_survives_enabling_the_dense_path(T, O):
     for t in range(2):
         assert np.array_equal(mom.read(t)[0], mom_b.read(t)[0]) and mom.read(t)[1] == mom_b.read(t)[1] == 3 * 64
     assert np.array_equal(mom2.read(1)[0], np.array([(s_all[:, a] * s_all[:, c]).sum() for a, c in spec[1]]))
+
+
+def test_cd1_step_from_a_resident_data_state(T):
+    """thrml_cd1_step_from reads the visible data in place from another state: same correlations and same final state as
+    copying the data block over and running thrml_cd1_step; the data state is left untouched."""
+    n_v, n_h, chains = 96, 160, 300
+    desc, W, b = rbm(T, n_v, n_h, 13)
+    prog = T.Program(M.fill(T.Builder(desc["kinds"]), desc))
+    assert prog.enable_dense(False) == 2
+    rng = np.random.default_rng(4)
+    v0 = (rng.random((chains, n_v)) < 0.13).astype(np.uint8)
+    data, a, c = T.ChainState(prog, chains), T.ChainState(prog, chains), T.ChainState(prog, chains)
+    data.upload(0, v0)
+    for key in (41, 42):  # two steps in a row from the same data
+        pos_a, neg_a = a.cd1_step(0, 1, None, key, data=data)
+        c.copy_block_from(data, 0)
+        pos_c, neg_c = c.cd1_step(0, 1, None, key)
+        assert np.array_equal(pos_a, pos_c) and np.array_equal(neg_a, neg_c)
+        for blk in (0, 1):
+            assert np.array_equal(a.download(blk, np.uint8), c.download(blk, np.uint8))
+        assert np.array_equal(data.download(0, np.uint8), v0)

@@ -1056,15 +1056,16 @@ static int32_t launch_dense_pair(thrml_state* s, const CUtensorMap& ma, const CU
 // (bias + accumulator, [chain][node] f32) instead of sampling.
 extern "C++" {
 template <int EPI>
-static int32_t dense_launch_any(thrml_state* s, const BlockProg& bp, const dense::GemmArgs& g) {
+static int32_t dense_launch_any(thrml_state* s, const BlockProg& bp, const dense::GemmArgs& g, const thrml_state* image_from = nullptr) {
     thrml_program* p = s->prog;
+    const CUtensorMap& src = (image_from ? image_from : s)->map_image[bp.dense_src];  // the +-1 image of the neighbour block
     if (use_pair_tiles(p->dense_tiles, s->n_chains, p->blocks[bp.dense_src].n)) {
-        if (bp.dense_bn_pair == 256) return launch_dense_pair<EPI, 256>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
-        if (bp.dense_bn_pair == 208) return launch_dense_pair<EPI, 208>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
-        return launch_dense_pair<EPI, 128>(s, s->map_image[bp.dense_src], bp.map_w_pair, g);
+        if (bp.dense_bn_pair == 256) return launch_dense_pair<EPI, 256>(s, src, bp.map_w_pair, g);
+        if (bp.dense_bn_pair == 208) return launch_dense_pair<EPI, 208>(s, src, bp.map_w_pair, g);
+        return launch_dense_pair<EPI, 128>(s, src, bp.map_w_pair, g);
     }
-    if (bp.dense_bn == 256) return launch_dense<EPI, 256>(s, s->map_image[bp.dense_src], bp.map_w, g);
-    return launch_dense<EPI, 128>(s, s->map_image[bp.dense_src], bp.map_w, g);
+    if (bp.dense_bn == 256) return launch_dense<EPI, 256>(s, src, bp.map_w, g);
+    return launch_dense<EPI, 128>(s, src, bp.map_w, g);
 }
 }  // extern "C++"
 static int32_t dense_fields(thrml_state* s, int32_t block, float* d_fields) {
@@ -1080,11 +1081,13 @@ static int32_t dense_fields(thrml_state* s, int32_t block, float* d_fields) {
     g.fields_out = d_fields;
     return dense_launch_any<dense::EPI_FIELDS>(s, bp, g);
 }
-static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t k1) {
+// `neighbours_from` (nullable): another state of the same program and chain count whose copy of the neighbour block is read
+// instead of this state's.
+static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t k1, thrml_state* neighbours_from = nullptr) {
     thrml_program* p = s->prog;
     const BlockProg& bp = p->blocks[block];
     if (int32_t rc = ensure_err_flag(s)) return rc;
-    if (int32_t rc = ensure_image(s, bp.dense_src, true)) return rc;
+    if (int32_t rc = ensure_image(neighbours_from ? neighbours_from : s, bp.dense_src, true)) return rc;
     const bool write_image = p->is_dense_source[block] != 0 && block != s->no_image_block;
     if (write_image)
         if (int32_t rc = ensure_image(s, block, false)) return rc;
@@ -1105,7 +1108,7 @@ static int32_t dense_update(thrml_state* s, int32_t block, uint32_t k0, uint32_t
     }
     CU_TRY(cudaMemsetAsync(s->ones[block]->p, 0, static_cast<size_t>(bp.n) * 4, p->ctx->stream));
     g.ones_out = s->ones[block]->as<int32_t>();
-    if (int32_t rc = dense_launch_any<dense::EPI_SAMPLE>(s, bp, g)) return rc;
+    if (int32_t rc = dense_launch_any<dense::EPI_SAMPLE>(s, bp, g, neighbours_from)) return rc;
     s->image_fresh[block] = write_image ? 1 : 0;
     s->ones_fresh[block] = 1;
     return THRML_OK;
@@ -1497,9 +1500,26 @@ int32_t thrml_state_copy_block(thrml_state* dst, const thrml_state* src, int32_t
     if (int32_t rc = check_block(dst, block)) return rc;
     CU_TRY(cudaSetDevice(dst->device));
     const BlockProg& bp = dst->prog->blocks[block];
-    CU_TRY(cudaMemcpyAsync(dst->rows(bp.sd) + bp.offset * dst->ld, src->rows(bp.sd) + bp.offset * src->ld, static_cast<size_t>(bp.n) * dst->ld, cudaMemcpyDeviceToDevice,
-                           dst->prog->ctx->stream));
+    cudaStream_t st = dst->prog->ctx->stream;
+    CU_TRY(cudaMemcpyAsync(dst->rows(bp.sd) + bp.offset * dst->ld, src->rows(bp.sd) + bp.offset * src->ld, static_cast<size_t>(bp.n) * dst->ld, cudaMemcpyDeviceToDevice, st));
     dst->touch(block);
+    if (dst->prog->is_dense_source[block]) {
+        // A dense block reads this block as a +-1 bf16 image: the source state keeps its image (built once, it is a cache of
+        // the bytes) and the copy carries it along with the per-node one counts, so the destination need not rebuild them.
+        thrml_state* from = const_cast<thrml_state*>(src);
+        if (int32_t rc = ensure_image(from, block, true)) return rc;
+        if (int32_t rc = ensure_image(dst, block, false)) return rc;
+        CU_TRY(cudaMemcpyAsync(dst->image[block]->p, from->image[block]->p, from->image[block]->bytes, cudaMemcpyDeviceToDevice, st));
+        dst->image_fresh[block] = 1;
+        if (from->ones_fresh[block] && from->ones[block]) {
+            if (!dst->ones[block]) {
+                dst->ones[block].reset(new DevBuf());
+                if (int32_t rc = dst->ones[block]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+            }
+            CU_TRY(cudaMemcpyAsync(dst->ones[block]->p, from->ones[block]->p, static_cast<size_t>(bp.n) * 4, cudaMemcpyDeviceToDevice, st));
+            dst->ones_fresh[block] = 1;
+        }
+    }
     return THRML_OK;
 }
 int32_t thrml_ising_energy(thrml_state* s, int64_t n_nodes, const int64_t* nodes, const float* biases, int64_t n_edges, const int64_t* edges, const float* weights,
@@ -1614,8 +1634,10 @@ int32_t thrml_sample_single_block(thrml_state* s, int32_t block, uint64_t key) {
 
 // <s_a s_b> over this device's chains for every node pair of two spin blocks, on the tensor cores (asynchronous; result in
 // s->d_corr as f32 [n_a][n_b]).
-static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t block_b, float* d_out) {
+// `a_from` (nullable): another state of the same program and chain count that supplies block a.
+static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t block_b, float* d_out, thrml_state* a_from = nullptr) {
     thrml_program* p = s->prog;
+    auto state_of = [&](int32_t blk) -> thrml_state* { return a_from && blk == block_a ? a_from : s; };
     if (p->blocks[block_a].is_cat || p->blocks[block_b].is_cat) return fail(THRML_ERR_INVALID_ARG, "pair correlations are defined for spin blocks");
     cudaStream_t st = p->ctx->stream;
     if (int32_t rc = ensure_err_flag(s)) return rc;
@@ -1627,28 +1649,30 @@ static int32_t pair_correlation_async(thrml_state* s, int32_t block_a, int32_t b
     const BlockProg& br = p->blocks[row_block];
     const BlockProg& bc = p->blocks[col_block];
     CUtensorMap map_a, map_b;  // encoded per call: kernel parameters are copied at launch
-    if (int32_t rc = make_operand_map(&map_a, s->rows(br.sd) + br.offset * s->ld, true, s->n_chains, br.n, s->ld, dense::BM)) return rc;
+    if (int32_t rc = make_operand_map(&map_a, state_of(row_block)->rows(br.sd) + br.offset * s->ld, true, s->n_chains, br.n, s->ld, dense::BM)) return rc;
     const int bn = pair ? pair_tile_width(bc.n) : (bc.n >= 2048 ? 256 : 64);
-    if (int32_t rc = make_operand_map(&map_b, s->rows(bc.sd) + bc.offset * s->ld, true, s->n_chains, bc.n, s->ld, pair ? bn / 2 : bn)) return rc;
+    if (int32_t rc = make_operand_map(&map_b, state_of(col_block)->rows(bc.sd) + bc.offset * s->ld, true, s->n_chains, bc.n, s->ld, pair ? bn / 2 : bn)) return rc;
     for (int32_t blk : {block_a, block_b}) {
         const BlockProg& bp = p->blocks[blk];
-        if (!s->ones[blk]) {
-            s->ones[blk].reset(new DevBuf());
-            if (int32_t rc = s->ones[blk]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
+        thrml_state* o = state_of(blk);
+        if (o->ones_fresh.empty()) return fail(THRML_ERR_INVALID_ARG, "state without block bookkeeping");
+        if (!o->ones[blk]) {
+            o->ones[blk].reset(new DevBuf());
+            if (int32_t rc = o->ones[blk]->alloc(static_cast<size_t>(bp.n) * 4)) return rc;
         }
-        if (!s->ones_fresh[blk]) {
-            dense::k_row_ones<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(s->rows(bp.sd) + bp.offset * s->ld, s->ld, s->n_chains, static_cast<int32_t>(bp.n),
-                                                                                             s->ones[blk]->as<int32_t>());
+        if (!o->ones_fresh[blk]) {
+            dense::k_row_ones<<<static_cast<unsigned>((bp.n + 7) / 8), dim3(32, 8), 0, st>>>(o->rows(bp.sd) + bp.offset * o->ld, o->ld, o->n_chains, static_cast<int32_t>(bp.n),
+                                                                                             o->ones[blk]->as<int32_t>());
             CU_TRY(cudaGetLastError());
-            s->ones_fresh[blk] = 1;
+            o->ones_fresh[blk] = 1;
         }
     }
     dense::GemmArgs g{};
     g.m_total = static_cast<int32_t>(br.n);
     g.n_total = static_cast<int32_t>(bc.n);
     g.k_bytes = static_cast<int32_t>(s->n_chains);
-    g.ones_a = s->ones[row_block]->as<int32_t>();
-    g.ones_b = s->ones[col_block]->as<int32_t>();
+    g.ones_a = state_of(row_block)->ones[row_block]->as<int32_t>();
+    g.ones_b = state_of(col_block)->ones[col_block]->as<int32_t>();
     g.corr_out = d_out;
     g.corr_transposed = swapped ? 1 : 0;
     g.n_chains = static_cast<int32_t>(s->n_chains);
@@ -1691,6 +1715,42 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
     const BlockProg& hb = s->prog->blocks[hidden_block];
     if (int32_t rc = launch_block(s, hidden_block, keys[0], nullptr, s->rows(hb.sd) + hb.offset * s->ld, nullptr)) return rc;
     if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>())) return rc;
+    s->no_image_block = hidden_block;  // h1 feeds only the correlations, which read the byte state
+    const int32_t rc_sweep = sweep(s, keys[1], nullptr);
+    s->no_image_block = -1;
+    if (rc_sweep) return rc_sweep;
+    if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>() + cnt)) return rc;
+    if (pos_host) CU_TRY(cudaMemcpyAsync(pos_host, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, st));
+    if (neg_host) CU_TRY(cudaMemcpyAsync(neg_host, s->d_corr.as<float>() + cnt, cnt * 4, cudaMemcpyDeviceToHost, st));
+    CU_TRY(cudaStreamSynchronize(st));
+    return check_err_flag(s);
+}
+
+// The same step with the visible data read from another state of the program (`data`, same chain count) instead of being
+// copied in first: h0 ~ P(h | data's visible block) and <v0 h0> read `data`; the sweep then writes v1 and h1 into `s`, whose
+// own visible block is never read before it is overwritten.  `data` is not modified (its cached +-1 image and one counts
+// are built on first use).
+int32_t thrml_cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, float* pos_host, float* neg_host) {
+    if (!s || !data) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (s == data) return thrml_cd1_step(s, visible_block, hidden_block, nullptr, key, pos_host, neg_host);
+    if (s->prog != data->prog || s->n_chains != data->n_chains) return fail(THRML_ERR_INVALID_ARG, "states must share the program and the chain count");
+    if (visible_block < 0 || visible_block >= s->prog->n_free || hidden_block < 0 || hidden_block >= s->prog->n_free || visible_block == hidden_block)
+        return fail(THRML_ERR_INVALID_ARG, "visible and hidden must be two distinct free blocks");
+    const BlockProg& hb = s->prog->blocks[hidden_block];
+    if (hb.kernel != 3 || hb.dense_src != visible_block) {  // not on the dense path: bring the data over and run the ordinary step
+        if (int32_t rc = thrml_state_copy_block(s, data, visible_block)) return rc;
+        return thrml_cd1_step(s, visible_block, hidden_block, nullptr, key, pos_host, neg_host);
+    }
+    CU_TRY(cudaSetDevice(s->prog->ctx->device));
+    cudaStream_t st = s->prog->ctx->stream;
+    const size_t cnt = static_cast<size_t>(s->prog->blocks[visible_block].n) * hb.n;
+    if (!s->d_corr.holds(2 * cnt * 4))
+        if (int32_t rc = s->d_corr.alloc(2 * cnt * 4)) return rc;
+    uint64_t keys[2];
+    rng_split(key, 2, keys);
+    ++s->block_launches;
+    if (int32_t rc = dense_update(s, hidden_block, static_cast<uint32_t>(keys[0]), static_cast<uint32_t>(keys[0] >> 32), data)) return rc;
+    if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>(), data)) return rc;
     s->no_image_block = hidden_block;  // h1 feeds only the correlations, which read the byte state
     const int32_t rc_sweep = sweep(s, keys[1], nullptr);
     s->no_image_block = -1;

@@ -104,13 +104,13 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
         return philox4x32_10(static_cast<uint32_t>(in_block), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
     };
     // First pass with fast logarithms.  The exact rule is argmax_c fl(theta_c - ln(-ln u_c)) with the deterministic
-    // logarithm (softmax.rs:84) and the first maximum winning (gumbel_argmax/kernel.rs:81-83).  Here -ln u comes from
-    // its series in w = 1 - u (exact in f32) when w < 2^-5, else from the intrinsic, whose absolute error of 2^-21.41
-    // then is at most 1.2e-5 of -ln u >= 0.0317; the outer intrinsic adds at most 3.6e-6.  Each score is therefore
-    // within 2e-5 of the exact one, and a leader more than 6e-5 ahead of the runner-up is the exact argmax.  Anything
-    // closer (about one update in 10^4) is recomputed exactly for that chain.
-    constexpr float MARGIN = 6e-5f;
-    float best[4], second[4];
+    // logarithm (softmax.rs:84) and the first maximum winning (gumbel_argmax/kernel.rs:81-83).  Here l = -ln u comes from
+    // the hardware base-2 logarithm, whose absolute error (2^-22 in log2 u, 1.7e-7 in ln u) becomes a relative error of
+    // 1.7e-7 / l in l and therefore an absolute error of 1.7e-7 / l in ln l; the outer logarithm adds at most 3.6e-6.  Each
+    // score is within 4e-6 + 2e-7 / l of the exact one, so a leader more than 3 (4e-6 + 2e-7 / l_min) ahead of the runner-up
+    // (l_min = the smallest l among the chain's categories) is the exact argmax.  Anything closer (about one update in 10^4)
+    // is recomputed exactly for that chain.
+    float best[4], second[4], lmin[4];
     uint32_t arg[4] = {0, 0, 0, 0};
     U4 r[4];
     uint32_t ix[3][4];  // PAIR: s_plus * K + s_minus per direction and chain
@@ -137,23 +137,23 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
                 th = theta(cat, 8 * c, un);
             }
             if ((cat & 3) == 0) r[c] = noise(c, cat);
-            const float u = u23_open(pick(r[c], cat & 3));
-            const float w = 1.0f - u;
-            const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
-            const float l1 = w < 0.03125f ? series : -__logf(u);
+            // the 23-bit uniform (m + 0.5) 2^-23 of u23_open, formed exactly as (1 + m 2^-23) - (1 - 2^-24)
+            const float u = __uint_as_float(0x3f800000u | (pick(r[c], cat & 3) >> 9)) - 0.99999994039535522461f;
+            const float l1 = __log2f(u) * -0.6931471805599453f;  // -ln u > 0
             const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
-            if (cat == 0) { best[c] = p; second[c] = -3.0e38f; }
+            if (cat == 0) { best[c] = p; second[c] = -3.0e38f; lmin[c] = l1; }
             else {
+                lmin[c] = fminf(lmin[c], l1);
                 second[c] = fmaxf(second[c], fminf(best[c], p));  // runner-up: the smaller of the old leader and the newcomer, if it beats the old runner-up
                 if (p > best[c]) { best[c] = p; arg[c] = cat; }
             }
         }
     }
     // each PAIR score is off by at most 12 x 2^-24 (|unary| + table_mag) more; twice that for leader and runner-up, and a third on top
-    const float margin = PAIR ? fmaf(2.0e-6f, unmax + a.table_mag, MARGIN) : MARGIN;
+    const float base = PAIR ? fmaf(2.0e-6f, unmax + a.table_mag, 1.2e-5f) : 1.2e-5f;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
-        if (!(best[c] - second[c] > margin))
+        if (!(best[c] - second[c] > base + __fdividef(6.0e-7f, lmin[c])))
             arg[c] = potts_exact_argmax(s_tab, a.unary + node * K, K, 8 * c, px, mx, py, my, pz, mz, static_cast<uint32_t>(in_block),
                                         4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1);
     uint32_t out = 0;
@@ -201,6 +201,28 @@ __global__ void __launch_bounds__(256) k_potts_marginals(const uint8_t* state, i
         }
     }
     if (threadIdx.x < K) counts[node * K + threadIdx.x] += total;  // one warp owns the node: no atomics
+}
+
+// The same counts for K <= 10 and at most 2016 chains: a lane keeps the counts of all categories of its chains in one
+// 64-bit word (ten 6-bit fields, at most 63 each), so the warp reduces once per category instead of once per category and
+// 128 chains.
+__global__ void __launch_bounds__(256) k_potts_marginals_packed(const uint8_t* state, int64_t n_nodes, int32_t K, int64_t ld, int64_t n_chains, int32_t* counts) {
+    const int64_t node = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
+    if (node >= n_nodes) return;
+    unsigned long long acc = 0ull;
+    // 16 chains per lane and pass (one 16-byte load; rows are padded to a multiple of 16 bytes)
+    for (int64_t chain = 16 * static_cast<int64_t>(threadIdx.x); chain < n_chains; chain += 512) {
+        const uint4 v = *reinterpret_cast<const uint4*>(state + node * ld + chain);
+        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
+        const int live = static_cast<int>(min(static_cast<int64_t>(16), n_chains - chain));
+#pragma unroll
+        for (int b = 0; b < 16; ++b)
+            if (b < live) acc += 1ull << (6u * min((wds[b >> 2] >> (8 * (b & 3))) & 0xffu, 10u));  // a byte that is no category lands in the unused top field
+    }
+    for (int k = 0; k < K; ++k) {
+        const int sum = __reduce_add_sync(0xffffffffu, static_cast<int>((acc >> (6 * k)) & 63ull));
+        if (threadIdx.x == k) counts[node * K + k] += sum;  // one warp owns the node: no atomics
+    }
 }
 
 __global__ void k_potts_transpose_in(const uint8_t* src, uint8_t* dst, int64_t n, int64_t n_chains, int64_t ld) {
@@ -342,8 +364,12 @@ int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
 int32_t thrml_potts_observe_marginals(thrml_potts* P) {
     if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(P->device));
-    k_potts_marginals<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld, P->n_chains,
-                                                                                                static_cast<int32_t*>(P->counts.p));
+    if (P->K <= 10 && P->n_chains <= 2016)
+        k_potts_marginals_packed<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld,
+                                                                                                           P->n_chains, static_cast<int32_t*>(P->counts.p));
+    else
+        k_potts_marginals<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld, P->n_chains,
+                                                                                                    static_cast<int32_t*>(P->counts.p));
     CU_TRY(cudaGetLastError());
     P->n_obs += P->n_chains;
     return THRML_OK;
