@@ -34,6 +34,11 @@ UNIT = "site-updates/s"
 # 2^18-spin, 4096-chain, 8-regular case (profiles/k_spin_lut_sparse_ising.md), divided by that launch's site updates.
 # A random graph has no cross-node reuse, so the traffic of a launch grows in proportion to its site updates.
 LUT_DRAM_BYTES_PER_UPDATE = 8.92
+# The same for one k_lattice_update_sliced launch on a 16384^2 lattice, 16 chains (profiles/k_lattice_update_sliced_ising_bitpacked.md)
+# and one k_potts_update launch on a 64^3 lattice, 1024 chains (profiles/k_potts_update_potts128.md); both kernels stream
+# their state once per launch, so the traffic of a launch grows in proportion to its site updates.
+LATTICE_DRAM_BYTES_PER_UPDATE = 0.2375
+POTTS_DRAM_BYTES_PER_UPDATE = 2.0
 
 
 def parse():
@@ -508,9 +513,10 @@ def sparse_end_to_end(T, torch, program, model, chains, rank, ctx, args, dist, c
     from thrml_rs_b200 import workloads as W
     n_blocks = len(model["blocks"])
     rng = np.random.default_rng(1 + rank)
-    init = [rng.integers(0, 2, (chains, len(blk)), dtype=np.uint8) for blk in model["blocks"]]
-    host_u8 = [pinned(torch, a) for a in init]
-    host_bits = [pinned_u32(torch, T.pack_chains(a)) for a in init]
+    words = (chains + 31) // 32
+    # independent random start states per variant, generated directly in each variant's host layout
+    host_u8 = [pinned(torch, rng.integers(0, 2, (chains, len(blk)), dtype=np.uint8)) for blk in model["blocks"]]
+    host_bits = [pinned_u32(torch, rng.integers(0, 1 << 32, (len(blk), words), dtype=np.uint32)) for blk in model["blocks"]]
     biases = np.concatenate([model["b"][blk] for blk in model["blocks"]])
     steps = args.steps
     world = dist.get_world_size() if dist else 1
@@ -775,7 +781,10 @@ def run_potts(T, torch, args, rank, world, device, dist, ctx, comm):
     out = base_line(args, updates / (ms * 1e-3), ms, 1, "u8 categories, f32 logits")
     out.update({"config": workload_config(args), "clocks": clocks, "gpu_launches": args.steps * 3,
                 "roofline": hbm_roofline(updates / 2, 2 + 120.0 / chains, update_ms, "k_potts_update",
-                                         note="instruction-bound by construction: a Gumbel draw (two logarithms, a 23-bit uniform) per category and update"),
+                                         note="instruction-bound by construction: a Gumbel draw (two logarithms, a 23-bit uniform) per category and update",
+                                         dram_bytes_per_update=POTTS_DRAM_BYTES_PER_UPDATE if (K, chains) == (10, 1024) else None,
+                                         dram_provenance="ncu dram__bytes_read.sum + dram__bytes_write.sum of one k_potts_update launch on a 64^3 lattice, 1024 chains "
+                                                         "(profiles/k_potts_update_potts128.md), scaled by site updates"),
                 "marginal_check": {"observations_per_node": int(n_obs), "rows_sum_to_observations": bool(np.all(counts.sum(axis=1) == n_obs))}})
     del counts
     if not args.no_e2e:
@@ -837,8 +846,12 @@ def run_lattice(T, torch, args, rank, world, device, dist, ctx, comm):
     out = base_line(args, updates / (ms * 1e-3), ms / args.steps, world, "1-bit spins, u32 thresholds", scaling="strong")
     out.update({"config": workload_config(args, world=world), "clocks": clocks,
                 "gpu_launches": args.steps * (3 if world == 1 else 7),  # per sweep: two colour updates (boundary rows apart when striped) and the observable kernel
-                "roofline": hbm_roofline(n_spins * chains / 2 / world, 0.25, ms / args.steps / 2, "k_lattice_update",
-                                         note="0.25 B per update: this kernel is bound by instruction issue (noise and one table lookup per spin), not by HBM; launch_ms includes the halo exchange and half of the observable kernel"),
+                "roofline": hbm_roofline(n_spins * chains / 2 / world, 0.25, ms / args.steps / 2, "k_lattice_update_sliced",
+                                         note="0.25 B per update: this kernel is bound by instruction issue (8.6 instructions per update: noise planes, bit-sliced compare), not by HBM; "
+                                              "launch_ms is half a sweep, halo exchange and observable recording included",
+                                         dram_bytes_per_update=LATTICE_DRAM_BYTES_PER_UPDATE if chains == 16 else None,
+                                         dram_provenance="ncu dram__bytes_read.sum + dram__bytes_write.sum of one k_lattice_update_sliced launch on a 16384^2 lattice, 16 chains "
+                                                         "(profiles/k_lattice_update_sliced_ising_bitpacked.md), scaled by site updates"),
                 "observables": {"records": int(n_rec), "m_mean": float(np.mean(mom[0])), "m2_mean": float(np.mean(mom[1])), "e_mean": float(np.mean(mom[2])), "e2_mean": float(np.mean(mom[3]))}})
     if not args.no_e2e:
         # end to end: this rank's rows of the initial state from pinned host memory as bits, the sweeps with the observable

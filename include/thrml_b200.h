@@ -444,6 +444,13 @@ int32_t thrml_lattice_synchronize(thrml_lattice* lat);
  * tables[3][K][K] (energy term T_d[x_u][x_{u+e_d}]), unary[N][K] (nullable = zeros), node index (x*ny + y)*nz + z.
  * ---------------------------------------------------------------------------------------------- */
 typedef struct thrml_potts thrml_potts;
+/* Key -> noise mapping of this engine (see thrml_lattice_set_noise for why it is the engine's to define):
+ *   THRML_POTTS_NOISE_PROGRAM  the explicit program's: the Gumbel uniform of (node n, chain c, category k) is word k & 3 of
+ *       Philox4x32-10(counter (n, c, k >> 2, tag), block key); states then equal the explicit factor program's.
+ *   THRML_POTTS_NOISE_QUAD (the default)  word c & 3 of counter (n, c >> 2, k, tag): one call per category serves four chains. */
+#define THRML_POTTS_NOISE_PROGRAM 0
+#define THRML_POTTS_NOISE_QUAD 1
+int32_t thrml_potts_set_noise(thrml_potts* p, int32_t mapping);
 int32_t thrml_potts_create(thrml_ctx* ctx, int32_t nx, int32_t ny, int32_t nz, int32_t n_categories, const float* tables,
                            const float* unary, float beta, int64_t n_chains, int64_t chain_offset, thrml_potts** out);
 void thrml_potts_destroy(thrml_potts* p);

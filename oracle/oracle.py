@@ -286,6 +286,10 @@ class State:
         mapping, 2 = the dense (tensor-core) path's mapping."""
         lib().orc_state_set_spin_noise(self.h, C.c_int32(mapping))
 
+    def set_cat_noise(self, mapping):
+        """0 = the explicit categorical kernels' mapping, 1 = the implicit Potts engine's (one call per category and chain quad)."""
+        lib().orc_state_set_cat_noise(self.h, C.c_int32(mapping))
+
     def _block_len(self, block):
         nf = len(self.model.free_blocks)
         return len(self.model.free_blocks[block]) if block < nf else len(self.model.clamped_blocks[block - nf])

@@ -602,6 +602,7 @@ struct OState {
     int64_t n_chains, chain_offset;
     int threads = 1;
     int spin_noise = 0;  // 0: one 32-bit word per (spin, chain); 1: the packed mapping of the implicit lattice engine
+    int cat_noise = 0;   // 0: word k & 3 of Philox(n, c, k >> 2); 1: word c & 3 of Philox(n, c >> 2, k) (the implicit Potts engine's)
     std::vector<std::vector<std::vector<float>>> g;  // [chain][class][position], f32 as in the reference
 };
 ORC_API int orc_state_create(Model* m, int64_t n_chains, int64_t chain_offset, OState** out) {
@@ -622,6 +623,9 @@ ORC_API void orc_state_set_threads(OState* s, int32_t t) { s->threads = t < 1 ? 
 // for mapping 0.  Mapping 2 restates the dense (tensor-core) path's mapping: top 16 bits = half (n & 1) of word ((n >> 1) & 3) of
 // Philox(n >> 3, c, 1, TAG_SPIN), low 16 bits = low half of word (c & 3) of Philox(n, c >> 2, 2, TAG_SPIN).
 ORC_API void orc_state_set_spin_noise(OState* s, int32_t mapping) { s->spin_noise = mapping; }
+// Categorical blocks: mapping 1 restates the implicit Potts engine's own mapping — the Gumbel uniform of (node n, chain c,
+// category k) is word (c & 3) of Philox(n, c >> 2, k, TAG_CAT).
+ORC_API void orc_state_set_cat_noise(OState* s, int32_t mapping) { s->cat_noise = mapping; }
 static const std::vector<int64_t>& block_nodes(const Model* m, int b) {
     return b < (int)m->free_blocks.size() ? m->free_blocks[b] : m->clamped_blocks[b - m->free_blocks.size()];
 }
@@ -839,6 +843,7 @@ static int update_block(OState* s, int block, uint64_t key, Noise* inj, std::vec
                 for (int k = 0; k < K; k++) {
                     float u;
                     if (u_inj) u = u_inj[(i * K + k) * C + c];
+                    else if (s->cat_noise == 1) { philox4x32_10((uint32_t)i, (uint32_t)(gc >> 2), (uint32_t)k, TAG_CAT, k0, k1, r); u = u23_open(r[gc & 3]); }
                     else { if ((k & 3) == 0) philox4x32_10((uint32_t)i, (uint32_t)gc, (uint32_t)(k >> 2), TAG_CAT, k0, k1, r); u = u23_open(r[k & 3]); }
                     float gmb = -det_log(-det_log(u));  // softmax.rs:84
                     float p = theta[i * K + k] + gmb;

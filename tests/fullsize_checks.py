@@ -105,6 +105,7 @@ def potts_check(T, O, side=64, K=10, chains=1024, slice_chains=8, sweeps=2, seed
     for start in sorted({0, (chains - slice_chains) // 16 * 16}):
         cnt = min(slice_chains, chains - start)
         os_ = O.State(om, cnt, start, threads=cnt)
+        os_.set_cat_noise(1)  # the implicit engine's own key -> noise mapping (its default)
         for bi, blk in enumerate(blocks):
             os_.set_block(bi, start_state[start:start + cnt][:, blk].astype(np.float32))
         os_.run_blocks(77, sweeps)

@@ -22,20 +22,24 @@ def explicit_potts(nx, ny, nz, K, tables, unary, beta):
     return dict(kinds=np.full(n, K, np.int32), free=[(blocks[0], 0), (blocks[1], 1)], ops=ops), blocks
 
 
+@pytest.mark.parametrize("noise", [0, 1])
 @pytest.mark.parametrize("shape,K,chains", [((4, 4, 4), 3, 8), ((2, 4, 6), 10, 37), ((6, 2, 4), 5, 64), ((4, 2, 4), 7, 20),
                                             ((4, 4, 4), 5, 8192)])  # the last: millions of draws, hundreds of near-ties sent to the exact path
-def test_potts_lattice_matches_explicit_program(T, O, shape, K, chains):
-    check_against_explicit_program(T, O, shape, K, chains, 0.3, 0.1)
+def test_potts_lattice_matches_explicit_program(T, O, shape, K, chains, noise):
+    """noise 0: the explicit program's key -> noise mapping; noise 1: the Potts engine's own (one call per category and chain
+    quad), which the oracle restates for its explicit program (set_cat_noise)."""
+    check_against_explicit_program(T, O, shape, K, chains, 0.3, 0.1, noise)
 
 
+@pytest.mark.parametrize("noise", [0, 1])
 @pytest.mark.parametrize("shape,K,chains,sigma,usigma", [((2, 4, 6), 10, 4096, 3.0, 1.0), ((4, 4, 2), 8, 4096, 1.0, 4.0), ((2, 2, 4), 10, 4096, 30.0, 0.1)])
-def test_potts_strong_couplings(T, O, shape, K, chains, sigma, usigma):
+def test_potts_strong_couplings(T, O, shape, K, chains, sigma, usigma, noise):
     """Large table and unary magnitudes: the pre-added direction tables round differently from the canonical six adds by
     an amount that grows with the magnitudes, and the near-tie window has to grow with it."""
-    check_against_explicit_program(T, O, shape, K, chains, sigma, usigma)
+    check_against_explicit_program(T, O, shape, K, chains, sigma, usigma, noise)
 
 
-def check_against_explicit_program(T, O, shape, K, chains, sigma, usigma):
+def check_against_explicit_program(T, O, shape, K, chains, sigma, usigma, noise=1):
     from thrml_rs_b200 import potts
     nx, ny, nz = shape
     n = nx * ny * nz
@@ -46,10 +50,11 @@ def check_against_explicit_program(T, O, shape, K, chains, sigma, usigma):
     desc, blocks = explicit_potts(nx, ny, nz, K, tables, unary, beta)
     om = M.fill(O.Model(desc["kinds"]), desc)
     os_ = O.State(om, chains)
+    os_.set_cat_noise(noise)
     cats = rng.integers(0, K, (chains, n)).astype(np.uint8)
     for bi, blk in enumerate(blocks):
         os_.set_block(bi, cats[:, blk].astype(np.float32))
-    lat = potts.PottsLattice(nx, ny, nz, K, tables, unary, beta, chains)
+    lat = potts.PottsLattice(nx, ny, nz, K, tables, unary, beta, chains, noise=noise)
     lat.upload(cats)
     assert np.array_equal(lat.download(), cats)
     want = np.zeros((n, K), dtype=np.int64)

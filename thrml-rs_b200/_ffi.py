@@ -111,6 +111,7 @@ _SIGNATURES = {
     "thrml_lattice_series_reset": (C.c_int32, [_P]),
     "thrml_potts_create": (C.c_int32, [_P, C.c_int32, C.c_int32, C.c_int32, C.c_int32, _P, _P, C.c_float, C.c_int64, C.c_int64, _P]),
     "thrml_potts_destroy": (None, [_P]),
+    "thrml_potts_set_noise": (C.c_int32, [_P, C.c_int32]),
     "thrml_potts_randomize": (C.c_int32, [_P, C.c_uint64]),
     "thrml_potts_upload": (C.c_int32, [_P, _P]),
     "thrml_potts_download": (C.c_int32, [_P, _P]),

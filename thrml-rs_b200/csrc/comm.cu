@@ -86,6 +86,7 @@ int32_t thrml_comm_create(thrml_ctx* ctx, const uint8_t* id, int32_t rank, int32
     NCCL_TRY(api, CommInitRank(&c, world_size, uid, rank));
     auto* h = new thrml_comm();
     h->ctx = ctx;
+    h->device = ctx->device;
     h->nccl = c;
     h->rank = rank;
     h->world = world_size;
@@ -103,6 +104,7 @@ int32_t thrml_comm_adopt(thrml_ctx* ctx, void* nccl_comm, thrml_comm** out) {
     NCCL_TRY(api, CommCount(static_cast<ncclComm_t>(nccl_comm), &world));
     auto* h = new thrml_comm();
     h->ctx = ctx;
+    h->device = ctx->device;
     h->nccl = static_cast<ncclComm_t>(nccl_comm);
     h->rank = rank;
     h->world = world;
@@ -113,9 +115,9 @@ int32_t thrml_comm_adopt(thrml_ctx* ctx, void* nccl_comm, thrml_comm** out) {
 
 void thrml_comm_destroy(thrml_comm* c) {
     if (!c) return;
-    if (c->owned && c->nccl) {
-        cudaSetDevice(c->ctx->device);
-        cudaStreamSynchronize(c->ctx->stream);
+    if (c->owned && c->nccl) {  // handles may be destroyed in any order: the context is not touched here
+        cudaSetDevice(c->device);
+        cudaDeviceSynchronize();
         if (const NcclApi* api = nccl_api()) api->CommDestroy(c->nccl);
     }
     delete c;

@@ -38,7 +38,8 @@ int32_t nccl_fail(const char* what, ncclResult_t r);
     } while (0)
 
 struct thrml_comm {
-    thrml_ctx* ctx = nullptr;
+    thrml_ctx* ctx = nullptr;  // identity only (collectives check that their handles share it); never dereferenced after creation
+    int device = 0;
     ncclComm_t nccl = nullptr;
     int32_t rank = 0, world = 1;
     bool owned = false;  // created by thrml_comm_create (destroyed with the handle) or adopted from the host

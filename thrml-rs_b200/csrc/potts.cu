@@ -39,7 +39,7 @@ struct PottsArgs {
 // Exact Gumbel-argmax of one chain (byte `sh / 8` of the neighbour words): the rule of softmax.rs:60-97 with the
 // deterministic logarithm.  Kept out of line: the update kernel calls it for about one update in 10^4.
 __device__ __noinline__ uint32_t potts_exact_argmax(const float* s_tab, const float* unary_row, int K, int sh, uint32_t px, uint32_t mx, uint32_t py, uint32_t my,
-                                                    uint32_t pz, uint32_t mz, uint32_t in_block, uint32_t chain, uint32_t k0, uint32_t k1) {
+                                                    uint32_t pz, uint32_t mz, uint32_t in_block, uint32_t chain, uint32_t k0, uint32_t k1, bool quad_noise) {
     const int KK = K * K;
     float top = 0.f;
     uint32_t arg = 0;
@@ -52,8 +52,15 @@ __device__ __noinline__ uint32_t potts_exact_argmax(const float* s_tab, const fl
         th = __fadd_rn(th, s_tab[KK + ((my >> sh) & 0xffu) * K + cat]);
         th = __fadd_rn(th, s_tab[2 * KK + cat * K + ((pz >> sh) & 0xffu)]);
         th = __fadd_rn(th, s_tab[2 * KK + ((mz >> sh) & 0xffu) * K + cat]);
-        if ((cat & 3) == 0) rr = philox4x32_10(in_block, chain, static_cast<uint32_t>(cat >> 2), TAG_CAT, k0, k1);
-        const float u = u23_open(pick(rr, cat & 3));
+        uint32_t word;
+        if (quad_noise) {  // one call per category serves the four chains of a quad
+            rr = philox4x32_10(in_block, chain >> 2, static_cast<uint32_t>(cat), TAG_CAT, k0, k1);
+            word = pick(rr, chain & 3u);
+        } else {
+            if ((cat & 3) == 0) rr = philox4x32_10(in_block, chain, static_cast<uint32_t>(cat >> 2), TAG_CAT, k0, k1);
+            word = pick(rr, cat & 3);
+        }
+        const float u = u23_open(word);
         const float p = __fadd_rn(th, -det_log(-det_log(u)));
         if (cat == 0 || p > top) { top = p; arg = cat; }
     }
@@ -66,7 +73,9 @@ __device__ __noinline__ uint32_t potts_exact_argmax(const float* s_tab, const fl
 // lookups and adds per category and chain instead of six.  The re-associated field differs from the canonical one by at
 // most 12 roundings of (|unary| + table_mag), which widens the window inside which the exact rule decides.
 // CTAs stride over the colour's nodes (eight per pass), so the tables are staged once per CTA.
-template <int KT, bool PAIR>
+// QUAD: the engine's own key -> noise mapping (thrml_potts_set_noise): the uniform of (node, chain c, category k) is word c & 3
+// of Philox(node, c >> 2, k, tag), so one call per category serves the thread's four chains (10 calls instead of 12 at K = 10).
+template <int KT, bool PAIR, bool QUAD>
 __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     extern __shared__ float s_tab[];  // [3][K][K], then (PAIR) [3][K][K][K]
     for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[i] = a.tables[i];
@@ -112,7 +121,7 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     // is recomputed exactly for that chain.
     float best[4], second[4], lmin[4];
     uint32_t arg[4] = {0, 0, 0, 0};
-    U4 r[4];
+    U4 r[4], rq;
     uint32_t ix[3][4];  // PAIR: s_plus * K + s_minus per direction and chain
     if (PAIR) {
 #pragma unroll
@@ -136,9 +145,11 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
             } else {
                 th = theta(cat, 8 * c, un);
             }
-            if ((cat & 3) == 0) r[c] = noise(c, cat);
+            if (QUAD) { if (c == 0) rq = philox4x32_10(static_cast<uint32_t>(in_block), a.chain_word0 + static_cast<uint32_t>(quad), static_cast<uint32_t>(cat), TAG_CAT, a.k0, a.k1); }
+            else if ((cat & 3) == 0) r[c] = noise(c, cat);
+            const uint32_t word = QUAD ? pick(rq, c) : pick(r[c], cat & 3);
             // the 23-bit uniform (m + 0.5) 2^-23 of u23_open, formed exactly as (1 + m 2^-23) - (1 - 2^-24)
-            const float u = __uint_as_float(0x3f800000u | (pick(r[c], cat & 3) >> 9)) - 0.99999994039535522461f;
+            const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;
             const float l1 = __log2f(u) * -0.6931471805599453f;  // -ln u > 0
             const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
             if (cat == 0) { best[c] = p; second[c] = -3.0e38f; lmin[c] = l1; }
@@ -155,7 +166,7 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     for (int c = 0; c < 4; ++c)
         if (!(best[c] - second[c] > base + __fdividef(6.0e-7f, lmin[c])))
             arg[c] = potts_exact_argmax(s_tab, a.unary + node * K, K, 8 * c, px, mx, py, my, pz, mz, static_cast<uint32_t>(in_block),
-                                        4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1);
+                                        4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1, QUAD);
     uint32_t out = 0;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
@@ -205,23 +216,46 @@ __global__ void __launch_bounds__(256) k_potts_marginals(const uint8_t* state, i
 
 // The same counts for K <= 10 and at most 2016 chains: a lane keeps the counts of all categories of its chains in one
 // 64-bit word (ten 6-bit fields, at most 63 each), so the warp reduces once per category instead of once per category and
-// 128 chains.
+// 128 chains.  A warp takes two nodes per pass and issues every load (state rows and old counts) before it counts, so
+// enough bytes are in flight to stream the state at memory speed.
 __global__ void __launch_bounds__(256) k_potts_marginals_packed(const uint8_t* state, int64_t n_nodes, int32_t K, int64_t ld, int64_t n_chains, int32_t* counts) {
-    const int64_t node = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y;
-    if (node >= n_nodes) return;
-    unsigned long long acc = 0ull;
-    // 16 chains per lane and pass (one 16-byte load; rows are padded to a multiple of 16 bytes)
-    for (int64_t chain = 16 * static_cast<int64_t>(threadIdx.x); chain < n_chains; chain += 512) {
-        const uint4 v = *reinterpret_cast<const uint4*>(state + node * ld + chain);
-        const uint32_t wds[4] = {v.x, v.y, v.z, v.w};
-        const int live = static_cast<int>(min(static_cast<int64_t>(16), n_chains - chain));
+    constexpr int NODES = 2, PASSES = 4;  // 4 passes of 512 chains cover the 2016-chain limit
+    const int lane = threadIdx.x;
+    const int64_t node0 = (static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y) * NODES;
+    if (node0 >= n_nodes) return;
+    uint4 v[NODES][PASSES];
+    int32_t old[NODES];
 #pragma unroll
-        for (int b = 0; b < 16; ++b)
-            if (b < live) acc += 1ull << (6u * min((wds[b >> 2] >> (8 * (b & 3))) & 0xffu, 10u));  // a byte that is no category lands in the unused top field
+    for (int i = 0; i < NODES; ++i) {
+        const int64_t node = node0 + i;
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int64_t chain = 16 * static_cast<int64_t>(lane) + 512 * p;
+            v[i][p] = make_uint4(0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu);  // bytes that are no category: counted nowhere
+            if (node < n_nodes && chain < n_chains) v[i][p] = *reinterpret_cast<const uint4*>(state + node * ld + chain);
+        }
+        old[i] = (node < n_nodes && lane < K) ? counts[node * K + lane] : 0;
     }
-    for (int k = 0; k < K; ++k) {
-        const int sum = __reduce_add_sync(0xffffffffu, static_cast<int>((acc >> (6 * k)) & 63ull));
-        if (threadIdx.x == k) counts[node * K + k] += sum;  // one warp owns the node: no atomics
+#pragma unroll
+    for (int i = 0; i < NODES; ++i) {
+        const int64_t node = node0 + i;
+        if (node >= n_nodes) break;
+        unsigned long long acc = 0ull;
+#pragma unroll
+        for (int p = 0; p < PASSES; ++p) {
+            const int64_t chain = 16 * static_cast<int64_t>(lane) + 512 * p;
+            const int live = static_cast<int>(max(static_cast<int64_t>(0), min(static_cast<int64_t>(16), n_chains - chain)));  // the row's padding bytes are zero, not 0xff
+            const uint32_t wds[4] = {v[i][p].x, v[i][p].y, v[i][p].z, v[i][p].w};
+#pragma unroll
+            for (int b = 0; b < 16; ++b)
+                if (b < live) acc += 1ull << (6u * min((wds[b >> 2] >> (8 * (b & 3))) & 0xffu, 10u));
+        }
+        int32_t mine = 0;
+        for (int k = 0; k < K; ++k) {
+            const int sum = __reduce_add_sync(0xffffffffu, static_cast<int>((acc >> (6 * k)) & 63ull));
+            if (lane == k) mine = sum;
+        }
+        if (lane < K) counts[node * K + lane] = old[i] + mine;  // one warp owns the node: no atomics
     }
 }
 
@@ -263,6 +297,7 @@ struct thrml_potts {
     int64_t n = 0, n_chains = 0, chain_offset = 0, ld = 0, n_obs = 0;
     DevBuf state, tables, pair_tables, unary, counts, scratch, n_obs_dev;
     float table_mag = 0.0f;
+    int32_t noise = THRML_POTTS_NOISE_QUAD;
     bool pair = false;  // pre-added direction tables exist (category counts with a compile-time kernel and 3 K^3 floats of shared memory to spare)
 };
 
@@ -322,6 +357,12 @@ void thrml_potts_destroy(thrml_potts* P) {
     cudaDeviceSynchronize();
     delete P;
 }
+int32_t thrml_potts_set_noise(thrml_potts* P, int32_t mapping) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    if (mapping != THRML_POTTS_NOISE_PROGRAM && mapping != THRML_POTTS_NOISE_QUAD) return fail(THRML_ERR_INVALID_ARG, "unknown noise mapping");
+    P->noise = mapping;
+    return THRML_OK;
+}
 static dim3 potts_grid(const thrml_potts* P) { return dim3(static_cast<unsigned>((P->n / 2 + 7) / 8), static_cast<unsigned>((P->ld / 4 + 31) / 32)); }
 
 int32_t thrml_potts_randomize(thrml_potts* P, uint64_t key) {
@@ -350,14 +391,21 @@ int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
     const unsigned resident = static_cast<unsigned>(P->ctx->sm_count) * 3u * 4u;
     grid.x = std::min(grid.x, std::max(1u, resident / grid.y));
     const size_t smem = static_cast<size_t>(3) * P->K * P->K * (P->pair ? 1 + P->K : 1) * 4;
+    const bool quad = P->noise == THRML_POTTS_NOISE_QUAD;
+#define POTTS_LAUNCH(KT, PAIR)                                                          \
+    do {                                                                                \
+        if (quad) k_potts_update<KT, PAIR, true><<<grid, block, smem, P->ctx->stream>>>(a);  \
+        else k_potts_update<KT, PAIR, false><<<grid, block, smem, P->ctx->stream>>>(a);      \
+    } while (0)
     switch (P->pair ? P->K : 0) {
-        case 3: k_potts_update<3, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 4: k_potts_update<4, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 5: k_potts_update<5, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 8: k_potts_update<8, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        case 10: k_potts_update<10, true><<<grid, block, smem, P->ctx->stream>>>(a); break;
-        default: k_potts_update<0, false><<<grid, block, smem, P->ctx->stream>>>(a); break;
+        case 3: POTTS_LAUNCH(3, true); break;
+        case 4: POTTS_LAUNCH(4, true); break;
+        case 5: POTTS_LAUNCH(5, true); break;
+        case 8: POTTS_LAUNCH(8, true); break;
+        case 10: POTTS_LAUNCH(10, true); break;
+        default: POTTS_LAUNCH(0, false); break;
     }
+#undef POTTS_LAUNCH
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }
@@ -365,7 +413,7 @@ int32_t thrml_potts_observe_marginals(thrml_potts* P) {
     if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(P->device));
     if (P->K <= 10 && P->n_chains <= 2016)
-        k_potts_marginals_packed<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld,
+        k_potts_marginals_packed<<<static_cast<unsigned>((P->n + 15) / 16), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld,
                                                                                                            P->n_chains, static_cast<int32_t*>(P->counts.p));
     else
         k_potts_marginals<<<static_cast<unsigned>((P->n + 7) / 8), dim3(32, 8), 0, P->ctx->stream>>>(static_cast<const uint8_t*>(P->state.p), P->n, P->K, P->ld, P->n_chains,

@@ -11,8 +11,12 @@ from . import engine as _eng
 from ._ffi import check, f32, lib, ptr
 
 
+NOISE_PROGRAM = 0  # the explicit factor program's key -> noise mapping: states equal FactorSamplingProgram's on the same torus
+NOISE_QUAD = 1     # the engine's own mapping (default): one generator call per category serves four chains
+
+
 class PottsLattice:
-    def __init__(self, nx, ny, nz, n_categories, tables, unary, beta, n_chains, chain_offset=0, ctx=None):
+    def __init__(self, nx, ny, nz, n_categories, tables, unary, beta, n_chains, chain_offset=0, ctx=None, noise=NOISE_QUAD):
         self.ctx = ctx or _eng.default_context()
         self.shape, self.K, self.n_chains = (nx, ny, nz), n_categories, n_chains
         self.n = nx * ny * nz
@@ -21,6 +25,7 @@ class PottsLattice:
         self.h = C.c_void_p()
         check(lib().thrml_potts_create(self.ctx.h, C.c_int32(nx), C.c_int32(ny), C.c_int32(nz), C.c_int32(n_categories), ptr(tables), ptr(unary), C.c_float(beta),
                                        C.c_int64(n_chains), C.c_int64(chain_offset), C.byref(self.h)))
+        check(lib().thrml_potts_set_noise(self.h, C.c_int32(noise)))
 
     def __del__(self):
         h, self.h = getattr(self, "h", None), None
