@@ -36,6 +36,55 @@ def run_case(O, M, desc, chains=12):
     return states, np.concatenate(tables).astype(np.int64)
 
 
+def torus_case():
+    """8 x 64 periodic Ising lattice, one coupling and one bias: the model both the explicit program and the implicit bit-packed
+    lattice engine can run."""
+    H, W, J, b, beta = 8, 64, 0.4407, 0.07, 0.9
+    idx = np.arange(H * W).reshape(H, W)
+    pairs = np.concatenate([np.stack([idx.ravel(), np.roll(idx, -1, axis=1).ravel()], 1), np.stack([idx.ravel(), np.roll(idx, -1, axis=0).ravel()], 1)])
+    e = np.unique(np.sort(pairs, axis=1), axis=0)
+    colour = (np.add.outer(np.arange(H), np.arange(W)) % 2).ravel()
+    blocks = [np.flatnonzero(colour == c) for c in (0, 1)]
+    n = H * W
+    desc = dict(kinds=np.zeros(n, np.int32), free=[(blocks[0], 0), (blocks[1], 1)],
+                ops=[("add_ising", np.arange(n), np.full(n, b, np.float32), e, np.full(len(e), J, np.float32), beta)])
+    return desc, dict(H=H, W=W, J=J, b=b, beta=beta, blocks=blocks)
+
+
+def potts_cube_case():
+    """4 x 4 x 4 periodic Potts model, K = 3, shared direction tables: explicit factor program and implicit Potts engine alike."""
+    side, K, beta = 4, 3, 0.8
+    rng = np.random.default_rng(105)
+    tables = rng.normal(0, 0.3, (3, K, K)).astype(np.float32)
+    unary = rng.normal(0, 0.1, (side ** 3, K)).astype(np.float32)
+    n = side ** 3
+    idx = np.arange(n).reshape(side, side, side)
+    colour = (np.add.outer(np.add.outer(np.arange(side), np.arange(side)), np.arange(side)) % 2).ravel()
+    blocks = [np.flatnonzero(colour == c) for c in (0, 1)]
+    ops = [("add_discrete_factor", [], [np.arange(n)], (np.float32(beta) * unary).reshape(n, K, 1).astype(np.float32))]
+    for d in range(3):
+        ops.append(("add_discrete_factor", [], [idx.ravel(), np.roll(idx, -1, axis=d).ravel()], np.broadcast_to((np.float32(beta) * tables[d]).astype(np.float32), (n, K, K)).copy()))
+    desc = dict(kinds=np.full(n, K, np.int32), free=[(blocks[0], 0), (blocks[1], 1)], ops=ops)
+    return desc, dict(side=side, K=K, beta=beta, tables=tables, unary=unary, blocks=blocks)
+
+
+def run_mapped(O, M, desc, chains, sweeps, spin_noise=0, cat_noise=0, samplers=None):
+    """States after `sweeps` sweeps under an engine-specific key -> noise mapping (or sampler kinds), from seeded random states."""
+    om = O.Model(desc["kinds"], desc.get("dtype_order"))
+    for i, (nodes, sb) in enumerate(desc["free"]):
+        om.add_free_block(nodes, superblock=sb, sampler=None if samplers is None else samplers[i])
+    for op in desc["ops"]:
+        getattr(om, op[0])(*op[1:])
+    om.compile()
+    st = O.State(om, chains)
+    st.set_spin_noise(spin_noise)
+    st.set_cat_noise(cat_noise)
+    for i, a in enumerate(M.random_states(desc, chains, 7)):
+        st.set_block(i, a.astype(np.float32))
+    st.run_blocks(0xC0FFEE, sweeps)
+    return [st.get_block(i).astype(np.uint8) for i in range(len(desc["free"]))]
+
+
 def build():
     graft.build()
     T = graft.load_package()
@@ -50,6 +99,16 @@ def build():
         out[f"{name}_tables"] = tables
         for i, s in enumerate(states):
             out[f"{name}_state{i}"] = s
+    # the engine-specific key -> noise mappings and the third sampler kind
+    torus, _ = torus_case()
+    for mapping in (1, 2):  # 1: the implicit lattice engine's bit-sliced mapping, 2: the dense path's
+        for i, s in enumerate(run_mapped(O, M, torus, 8, 3, spin_noise=mapping)):
+            out[f"torus_spin_noise{mapping}_state{i}"] = s
+    cube, _ = potts_cube_case()
+    for i, s in enumerate(run_mapped(O, M, cube, 12, 3, cat_noise=1)):  # the implicit Potts engine's mapping
+        out[f"cube_cat_noise1_state{i}"] = s
+    for i, s in enumerate(run_mapped(O, M, cube, 12, 3, samplers=[2, 1])):  # block 0 sampled by SoftmaxConditional
+        out[f"cube_softmax_state{i}"] = s
     return out
 
 

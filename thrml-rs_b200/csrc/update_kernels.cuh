@@ -324,7 +324,7 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
         __syncwarp();  // a node's threads lie in one warp (blockDim.x divides 32)
         if (!valid) return;
     }
-    constexpr float MARGIN = 6e-5f;
+    constexpr float MARGIN = 1.2e-5f;
     uint32_t out = 0;
     // One chain at a time (not unrolled): the four chains of a thread share nothing in this loop but the slot data, and the
     // smaller live set (one Philox block, one leader / runner-up pair) lets three CTAs share an SM instead of two.
@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
     for (int c = 0; c < 4; ++c) {
         if (4 * static_cast<int64_t>(quad) + c >= a.n_chains) break;
         const int sh = 8 * c;
-        float best = 0.f, second = -3.0e38f;
+        float best = 0.f, second = -3.0e38f, lmin = 1.0f;
         uint32_t lead = 0;
         U4 r{0, 0, 0, 0};
         for (int cat = 0; cat < K; ++cat) {
@@ -353,19 +353,23 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
             th = __fadd_rn(th, sum);
             if ((cat & 3) == 0)
                 r = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
-            const float u = u23_open(pick(r, cat & 3));
-            const float w = 1.0f - u;
-            const float series = w * fmaf(w, fmaf(w, fmaf(w, fmaf(w, 0.2f, 0.25f), 0.33333334f), 0.5f), 1.0f);
-            const float l1 = w < 0.03125f ? series : -__logf(u);
+            // the 23-bit uniform (m + 0.5) 2^-23 of u23_open, formed exactly as (1 + m 2^-23) - (1 - 2^-24)
+            const float u = __uint_as_float(0x3f800000u | (pick(r, cat & 3) >> 9)) - 0.99999994039535522461f;
+            const float l1 = __log2f(u) * -0.6931471805599453f;            // -ln u > 0
             const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
             if (cat == 0) {
                 best = p;
+                lmin = l1;
             } else {
+                lmin = fminf(lmin, l1);
                 second = fmaxf(second, fminf(best, p));
                 if (p > best) { best = p; lead = cat; }
             }
         }
-        if (!(best - second > MARGIN)) lead = cat_exact_argmax(a, node, quad, c);
+        // The hardware logarithm's absolute error (1.7e-7 in ln u) is a relative error of 1.7e-7 / l in l = -ln u and so an
+        // absolute error of that size in ln l; the outer logarithm and the final add stay below 4e-6.  A leader more than
+        // three such bounds ahead (taken at the chain's smallest l) is the exact argmax; anything closer is recomputed exactly.
+        if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a, node, quad, c);
         out |= lead << sh;
     }
     *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
