@@ -145,6 +145,18 @@ int32_t thrml_builder_table_data(const thrml_builder* b, int32_t block, int32_t 
 int32_t thrml_ctx_create(int32_t device_id, thrml_ctx** out);
 void thrml_ctx_destroy(thrml_ctx* ctx);
 int32_t thrml_ctx_synchronize(thrml_ctx* ctx);
+
+/* The two steps before the sampling path, on the device.
+ * thrml_builder_compile_device: same result as thrml_builder_compile, table for table and byte for byte; the layout
+ *   (BlockSpec::new, crates/thrml-core/src/blockspec.rs:15-66) stays on the host, the slot tables of
+ *   BlockSamplingProgram::new (crates/thrml-samplers/src/program.rs:88-318) are built per interaction group by a stable
+ *   radix sort of (head node, row), a run-length scan for the slot numbers and one scatter, then read back into the builder.
+ * thrml_greedy_coloring_device: same colours as thrml_greedy_coloring (crates/thrml-examples/src/lib.rs:114-147), computed
+ *   as a dataflow over the edges directed from lower to higher node index; n_passes_out (may be NULL) receives the number
+ *   of passes launched, a multiple of 8 that bounds the longest index-increasing path of the graph from above. */
+int32_t thrml_builder_compile_device(thrml_builder* b, thrml_ctx* ctx);
+int32_t thrml_greedy_coloring_device(thrml_ctx* ctx, int64_t n_nodes, int64_t n_edges, const int64_t* edges,
+                                     int32_t* colour_out, int32_t* n_colours_out, int32_t* n_passes_out);
 /* Failure-detection self test (no reference counterpart; the reference's errors are Result<_, String> / panics): a
  * kernel waits on a pipeline barrier that nothing signals; its bounded wait runs out, it returns, and this call
  * reports THRML_ERR_TIMEOUT.  The context remains usable. */

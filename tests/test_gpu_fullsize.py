@@ -27,10 +27,12 @@ def test_sparse_ising_full_size_chain_slices(T, O):
 
 
 def test_sparse_ising_full_size_with_chain_offset(T, O):
-    """The shard a rank of an 8-GPU run holds: 512 chains whose global ids start at 3584."""
+    """The shard a rank of an 8-GPU run holds: 512 chains whose global ids start at 3584.  Colouring and slot tables come
+    from the device here, the oracle compiles the same blocks on the host."""
     from thrml_rs_b200 import workloads as W
-    model = W.sparse_ising(1 << 18, 8, 0x5EED0002)
-    program = T.Program(W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model))
+    ctx = T.default_context()
+    model = W.sparse_ising(1 << 18, 8, 0x5EED0002, ctx=ctx)
+    program = T.Program(W.fill_ising(T.Builder(np.zeros(model["n"], np.int32)), model, ctx=ctx), ctx)
     state = T.ChainState(program, 512, chain_offset=3584)
     res = F.sparse_ising_check(T, O, model, program, state, 512, chain_base=3584)
     assert res["ok"], res

@@ -38,6 +38,8 @@ _SIGNATURES = {
     "thrml_builder_table_data": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, _P, _P, _P, _P]),
     "thrml_ctx_create": (C.c_int32, [C.c_int32, _P]),
     "thrml_ctx_destroy": (None, [_P]),
+    "thrml_builder_compile_device": (C.c_int32, [_P, _P]),
+    "thrml_greedy_coloring_device": (C.c_int32, [_P, C.c_int64, C.c_int64, _P, _P, _P, _P]),
     "thrml_ctx_synchronize": (C.c_int32, [_P]),
     "thrml_ctx_stream": (C.c_void_p, [_P]),
     "thrml_debug_wait_timeout": (C.c_int32, [_P]),

@@ -746,9 +746,9 @@ def bipartite_coloring(node_grid):
     return colour
 
 
-def greedy_coloring(n_nodes, edges):
-    """lib.rs:114-147 on index arrays: colour per node."""
-    return _eng.greedy_coloring_arrays(n_nodes, edges)[0]
+def greedy_coloring(n_nodes, edges, ctx=None):
+    """lib.rs:114-147 on index arrays: colour per node (on the device of `ctx` when one is given)."""
+    return _eng.greedy_coloring_arrays(n_nodes, edges, ctx)[0]
 
 
 def coloring_to_blocks(nodes, coloring):

@@ -11,7 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 OUT = os.path.join(HERE, "libthrml_b200.so")
-SOURCES = ["engine.cu", "lattice.cu", "potts.cu", "comm.cu", "builder.cpp"]
+SOURCES = ["engine.cu", "lattice.cu", "potts.cu", "comm.cu", "compile_device.cu", "builder.cpp"]
 HEADERS = ["tables.h", "ctx.h", "comm.h", "devbuf.h", "dense.cuh", "device_math.cuh", "update_kernels.cuh", "observer_kernels.cuh",
            os.path.join("..", "..", "include", "thrml_b200.h")]
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-Xcompiler", "-fPIC,-fvisibility=default"]

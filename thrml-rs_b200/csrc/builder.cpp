@@ -353,7 +353,11 @@ int32_t thrml_builder_add_ising(thrml_builder* b, const int64_t* nodes, int64_t 
     return THRML_OK;
 }
 
-int32_t thrml_builder_compile(thrml_builder* b) {
+}  // extern "C"
+
+// BlockGibbsSpec::new + BlockSpec::new (program.rs:28-64, blockspec.rs:15-66): classes, sampling order, node positions and the
+// checks that do not depend on the slot tables.  O(nodes) host work shared by the host and the device table compilers.
+int32_t thrml::compile_layout(thrml_builder* b) {
     if (!b) return fail(THRML_ERR_INVALID_ARG, "null builder");
     b->compiled = false;
     // --- classes: distinct TensorSpecs of node_shape_dtypes, first-seen order (blockspec.rs:19-28).  Spin -> Bool scalar,
@@ -406,6 +410,14 @@ int32_t thrml_builder_compile(thrml_builder* b) {
         for (const auto& tail : g.tails)
             for (int64_t nd : tail)
                 if (b->loc_sd[nd] < 0) return fail(THRML_ERR_INVALID_ARG, "Node not found in global location map");
+    return THRML_OK;
+}
+
+extern "C" {
+
+int32_t thrml_builder_compile(thrml_builder* b) {
+    if (int32_t rc = thrml::compile_layout(b)) return rc;
+    const int64_t n_nodes = static_cast<int64_t>(b->kinds.size());
     // --- head_node_map (program.rs:101-108) as a CSR over nodes: entries (group, row), ordered by group then row.
     std::vector<int64_t> hptr(static_cast<size_t>(n_nodes) + 1, 0);
     for (const GroupDesc& g : b->groups)

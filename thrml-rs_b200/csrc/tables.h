@@ -6,6 +6,8 @@
 
 #include "../../include/thrml_b200.h"
 
+struct thrml_builder;
+
 namespace thrml {
 
 // Thread-local error slot behind thrml_last_error().
@@ -48,6 +50,11 @@ struct BlockInfo {
     int32_t sampler = 0;     // free blocks only
 };
 
+}  // namespace thrml
+
+namespace thrml {
+// Layout half of the index compilation (classes, sampling order, node positions, argument checks), on the host.
+int32_t compile_layout(thrml_builder* b);
 }  // namespace thrml
 
 struct thrml_builder {

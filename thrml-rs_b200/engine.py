@@ -114,11 +114,15 @@ def lattice_edges(side_len, torus):
     return side.value, edges, colour
 
 
-def greedy_coloring_arrays(n_nodes, edges):
+def greedy_coloring_arrays(n_nodes, edges, ctx=None):
+    """Colour per node and the colour count; with a device context the dataflow form runs on that device (same colours)."""
     edges = i64(edges).reshape(-1, 2)
     colour = np.zeros(n_nodes, dtype=np.int32)
     nc = C.c_int32()
-    check(lib().thrml_greedy_coloring(C.c_int64(n_nodes), C.c_int64(len(edges)), ptr(edges), ptr(colour), C.byref(nc)))
+    if ctx is None:
+        check(lib().thrml_greedy_coloring(C.c_int64(n_nodes), C.c_int64(len(edges)), ptr(edges), ptr(colour), C.byref(nc)))
+    else:
+        check(lib().thrml_greedy_coloring_device(ctx.h, C.c_int64(n_nodes), C.c_int64(len(edges)), ptr(edges), ptr(colour), C.byref(nc), None))
     return colour, nc.value
 
 
@@ -189,8 +193,12 @@ class Builder:
         edges, weights = i64(edges).reshape(-1, 2), f32(weights)
         check(lib().thrml_builder_add_ising(self.h, ptr(nodes), C.c_int64(len(nodes)), ptr(biases), ptr(edges), C.c_int64(len(edges)), ptr(weights), C.c_float(beta)))
 
-    def compile(self):
-        check(lib().thrml_builder_compile(self.h))
+    def compile(self, ctx=None):
+        """Index compilation; with a device context the slot tables are built on that device (identical tables)."""
+        if ctx is None:
+            check(lib().thrml_builder_compile(self.h))
+        else:
+            check(lib().thrml_builder_compile_device(self.h, ctx.h))
 
     def counts(self):
         a, b, c, d = C.c_int32(), C.c_int32(), C.c_int32(), C.c_int32()

@@ -27,25 +27,26 @@ def random_graph_edges(n_nodes, mean_degree, seed):
     return np.stack([code // n_nodes, code % n_nodes], axis=1)
 
 
-def sparse_ising(n_nodes=1 << 20, degree=8, seed=0x5EED0002, bias_sigma=0.05, beta=1.0, regular=True):
+def sparse_ising(n_nodes=1 << 20, degree=8, seed=0x5EED0002, bias_sigma=0.05, beta=1.0, regular=True, ctx=None):
     """Sparse random Ising model, `degree`-regular (at most `degree` neighbours per node) or, with regular=False, a
     random graph with that mean degree: couplings N(0, 1/degree), biases N(0, bias_sigma^2), blocks from greedy colouring
-    in node order (ascending node index inside each colour)."""
+    in node order (ascending node index inside each colour).  With a device context the colouring runs on that device."""
     edges = random_regular_edges(n_nodes, degree, seed) if regular else random_graph_edges(n_nodes, degree, seed)
     rng = np.random.default_rng(seed + 1)
     J = rng.normal(0.0, np.sqrt(1.0 / degree), len(edges)).astype(np.float32)
     b = rng.normal(0.0, bias_sigma, n_nodes).astype(np.float32)
-    colour, n_colours = _eng.greedy_coloring_arrays(n_nodes, edges)
+    colour, n_colours = _eng.greedy_coloring_arrays(n_nodes, edges, ctx)
     blocks = [np.flatnonzero(colour == c).astype(np.int64) for c in range(n_colours)]
     return dict(n=n_nodes, edges=edges, J=J, b=b, beta=float(beta), colour=colour, blocks=blocks)
 
 
-def fill_ising(builder, model):
-    """Feed a sparse_ising() model to a builder (the library's or any object with the same methods)."""
+def fill_ising(builder, model, ctx=None):
+    """Feed a sparse_ising() model to a builder (the library's or any object with the same methods); with a device context
+    the library's builder compiles its slot tables on that device."""
     for i, blk in enumerate(model["blocks"]):
         builder.add_free_block(blk, superblock=i)
     builder.add_ising(np.arange(model["n"], dtype=np.int64), model["b"], model["edges"], model["J"], model["beta"])
-    builder.compile()
+    builder.compile() if ctx is None else builder.compile(ctx)
     return builder
 
 
