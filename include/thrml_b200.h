@@ -202,9 +202,13 @@ int32_t thrml_program_update_group(thrml_program* p, int32_t group, const float*
  *   THRML_OPT_SPLIT_MARGIN  widens (units of 2^-24 of probability, >= 0) the window around each draw's probability inside
  *                           which the split-field-table update of sequential-sum nodes recomputes the field in the
  *                           canonical order; 0 (the default) keeps the derived bound, 2^25 sends every draw through the
- *                           exact route.  Setting it rebuilds the affected blocks' tables. */
+ *                           exact route.  Setting it rebuilds the affected blocks' tables.
+ *   THRML_OPT_GATHER_ONLY   1 = blocks whose default kernel is the general spin kernel (kind 7) or the register-resident
+ *                           categorical kernel (kind 5) run the node x four-chain gather kernels (kinds 0 and 2) instead;
+ *                           0 (the default) = each block's own kernel.  The states are the same either way. */
 #define THRML_OPT_DENSE_TILES 1
 #define THRML_OPT_SPLIT_MARGIN 2
+#define THRML_OPT_GATHER_ONLY 3
 int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value);
 int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double* value_out);
 /* Dense bipartite path.  A spin block whose neighbours all lie in one other spin block (a layer of an RBM-style model:
@@ -218,7 +222,9 @@ int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding
  * nodes have at most 8 single-spin-tail slots), 2 categorical kernel, 3 dense tensor-core kernel, 4 sequential-sum
  * kernel (spin blocks with single-spin-tail slots, more than 8 active slots on some node), 5 categorical kernel for nodes with
  * at most 8 active slots (slot data held in registers, Gumbel noise screened with fast logarithms), 6 a spin block that
- * mixes kinds 1 and 4 node by node (at least a quarter of its nodes have at most 8 neighbour slots). */
+ * mixes kinds 1 and 4 node by node (at least a quarter of its nodes have at most 8 neighbour slots), 7 the general spin
+ * kernel (slots whose tail is a product of up to three spins or a categorical node that selects the weight, at most 32
+ * active slots per node; warp per node, 16 chains per lane). */
 int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out);
 
 /* n_chains chains held on this device; chain_offset = global id of local chain 0 (the in-kernel random

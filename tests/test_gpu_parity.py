@@ -97,6 +97,27 @@ def test_in_kernel_stream_states(T, O, case, chains):
     assert_states_equal(gs, os_, n_blocks_of(desc))
 
 
+@pytest.mark.parametrize("chains", [130, 1040])
+@pytest.mark.parametrize("seed", [21, 22])
+def test_general_spin_kernel_on_larger_mixed_models(T, O, seed, chains):
+    """Spin blocks with three-spin factors and categorical tails, enough chains for the warp-per-node kernel (several passes
+    at 1040 chains, dead lanes at 130)."""
+    desc, _ = M.mixed_model(seed, n_spin=90, n_cat=40, K=5, with_clamped=bool(seed % 2))
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 17)
+    assert prog.block_kernel(0) == 7
+    gs.run_blocks(4321, 3)
+    os_.run_blocks(4321, 3)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    # the node x four-chain gather kernels on the same program give the same states
+    prog.set_option(T.OPT_GATHER_ONLY, 1)
+    gg = T.ChainState(prog, chains)
+    for i, a in enumerate(M.random_states(desc, chains, 17)):
+        gg.upload(i, a)
+    gg.run_blocks(4321, 3)
+    for i in range(n_blocks_of(desc)):
+        assert np.array_equal(gg.download(i), gs.download(i))
+
+
 def test_kernel_selection(T, O):
     cases = model_cases(T)
     prog = T.Program(M.fill(T.Builder(cases["graph8"]["kinds"]), cases["graph8"]))
@@ -104,7 +125,7 @@ def test_kernel_selection(T, O):
     prog = T.Program(M.fill(T.Builder(cases["graph12"]["kinds"]), cases["graph12"]))
     assert all(prog.block_kernel(b) == 4 for b in range(len(cases["graph12"]["free"])))  # 12 neighbours + a bias: too many for a threshold table
     prog = T.Program(M.fill(T.Builder(cases["mixed"]["kinds"]), cases["mixed"]))
-    assert prog.block_kernel(0) == 0  # categorical tails and three-spin factors: the generic gather kernel
+    assert prog.block_kernel(0) == 7  # categorical tails and three-spin factors: the warp-per-node general spin kernel
     prog = T.Program(M.fill(T.Builder(cases["potts"]["kinds"]), cases["potts"]))
     assert all(prog.block_kernel(b) == 5 for b in range(2))  # five active slots per node (8 at most): the register-resident categorical kernel
 

@@ -41,6 +41,9 @@ struct BlockProg {
     DevBuf d_split_row, d_split_nodes, d_split_tab, d_split_margin;  // kernels 4 and 6: split field tables of the nodes with one entry row
     int64_t n_split = 0;
     bool split_wide = false;  // some node has four tables
+    DevBuf d_wide_ent, d_wide_first, d_wide_cnt;         // kernel 7: entry lists (table and slot) of the wide general spin kernel
+    bool wide_has_cat = false;                           // kernel 7: some table has a categorical tail
+    bool cat_warp = false;                               // kernel 5: entry lists (d_wide_*) exist for the warp-per-node categorical kernel
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
     std::vector<int32_t> h_nbr;  // host copy of d_nbr
@@ -77,6 +80,7 @@ struct thrml_program {
     int32_t kernel_epoch = 0;  // bumped whenever a block changes kernel; observers built before that stop fusing
     int32_t dense_tiles = 2;         // THRML_OPT_DENSE_TILES
     float split_extra_margin = 0.f;  // THRML_OPT_SPLIT_MARGIN
+    bool gather_only = false;        // THRML_OPT_GATHER_ONLY
 };
 
 struct thrml_state {
@@ -488,6 +492,41 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 }
             }
         }
+        if (!bp.is_cat && bp.kernel == 0 && !tabs.empty() && tabs.size() <= 127) {
+            // spin block with multi-spin or categorical tails: the warp-per-node general kernel (kind 7) when every node has at
+            // most SEQ_MAX active slots and no slot multiplies more than WIDE_SPIN_TAILS spins
+            bool ok = true;
+            for (const SlotTable& t : tabs) ok = ok && t.k < (1 << 24) && t.n_spin <= WIDE_SPIN_TAILS;
+            std::vector<int32_t> ent, cnt;
+            std::vector<uint32_t> first;
+            if (ok) {
+                ent.assign(static_cast<size_t>(bp.n) * SEQ_MAX, -1);
+                cnt.assign(static_cast<size_t>(bp.n), 0);
+                first.assign(static_cast<size_t>(bp.n), 0);
+            }
+            for (int64_t i2 = 0; i2 < bp.n && ok; ++i2) {
+                int e = 0;
+                for (size_t ti = 0; ti < tabs.size() && ok; ++ti) {
+                    const SlotTable& t = tabs[ti];
+                    bool started = false;
+                    for (int32_t j = 0; j < t.k; ++j) {
+                        if (!t.active[static_cast<size_t>(i2) * t.k + j]) continue;
+                        if (e == SEQ_MAX) { ok = false; break; }
+                        if (!started) first[i2] |= 1u << e;
+                        started = true;
+                        ent[static_cast<size_t>(i2) * SEQ_MAX + e++] = static_cast<int32_t>(ti << 24) | j;
+                    }
+                }
+                if (ok) cnt[i2] = e;
+            }
+            if (ok) {
+                if (int32_t rc = upload(bp.d_wide_ent, ent.data(), ent.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = upload(bp.d_wide_first, first.data(), first.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = upload(bp.d_wide_cnt, cnt.data(), cnt.size() * 4, ctx->stream)) return rc;
+                for (const SlotTable& t : tabs) bp.wide_has_cat = bp.wide_has_cat || static_cast<int32_t>(t.idx.size()) > t.n_spin;
+                bp.kernel = 7;
+            }
+        }
         if (bp.is_cat && !tabs.empty()) {
             // categorical block with few active slots per node: the register-resident kernel (kind 5) takes the in-kernel-noise updates
             int64_t most = 0;
@@ -498,6 +537,31 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 most = std::max(most, cnt);
             }
             if (most <= CAT_SLOTS) bp.kernel = 5;
+            // entry lists for the warp-per-node form (K <= 16, at most three spin tails per slot)
+            bool ok = bp.kernel == 5 && bp.kind <= 16 && tabs.size() <= 127;
+            for (const SlotTable& t : tabs) ok = ok && t.k < (1 << 24) && t.n_spin <= WIDE_SPIN_TAILS;
+            if (ok) {
+                std::vector<int32_t> ent(static_cast<size_t>(bp.n) * CAT_SLOTS, -1), cnt(static_cast<size_t>(bp.n), 0);
+                std::vector<uint32_t> first(static_cast<size_t>(bp.n), 0);
+                for (int64_t i2 = 0; i2 < bp.n; ++i2) {
+                    int e = 0;
+                    for (size_t ti = 0; ti < tabs.size(); ++ti) {
+                        const SlotTable& t = tabs[ti];
+                        bool started = false;
+                        for (int32_t j = 0; j < t.k; ++j) {
+                            if (!t.active[static_cast<size_t>(i2) * t.k + j]) continue;
+                            if (!started) first[i2] |= 1u << e;
+                            started = true;
+                            ent[static_cast<size_t>(i2) * CAT_SLOTS + e++] = static_cast<int32_t>(ti << 24) | j;
+                        }
+                    }
+                    cnt[i2] = e;
+                }
+                if (int32_t rc = upload(bp.d_wide_ent, ent.data(), ent.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = upload(bp.d_wide_first, first.data(), first.size() * 4, ctx->stream)) return rc;
+                if (int32_t rc = upload(bp.d_wide_cnt, cnt.data(), cnt.size() * 4, ctx->stream)) return rc;
+                bp.cat_warp = true;
+            }
         }
         bp.base_kernel = bp.kernel;
         // Dense bipartite candidate: a spin block whose neighbours all lie in one other spin block, densely enough
@@ -1208,6 +1272,16 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
         CU_TRY(cudaGetLastError());
         return THRML_OK;
     }
+    if (bp.base_kernel == 7 && !inj && !fields && !narrow && !p->gather_only) {
+        WideArgs a{bp.d_tabs.as<DevTable>(), bp.d_wide_ent.as<int32_t>(), bp.d_wide_first.as<uint32_t>(), bp.d_wide_cnt.as<int32_t>(),
+                   p->sd_spin >= 0 ? s->rows(p->sd_spin) : nullptr, p->sd_cat >= 0 ? s->rows(p->sd_cat) : nullptr, dst, s->ld,
+                   static_cast<int32_t>(bp.n), static_cast<int32_t>(s->ld / 16), word0, s->n_chains, make_round_keys(key)};
+        const int64_t ctas = std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 6);
+        if (bp.wide_has_cat) k_spin_wide<true><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        else k_spin_wide<false><<<static_cast<unsigned>(ctas), 256, 0, st>>>(a);
+        CU_TRY(cudaGetLastError());
+        return THRML_OK;
+    }
     UpdateArgs a{};
     a.tabs = bp.d_tabs.as<DevTable>();
     a.n_tabs = bp.n_tabs;
@@ -1234,7 +1308,25 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
     if (bp.is_cat) {
         if (fields) k_cat_generic<2><<<grid, blk, 0, st>>>(a);
         else if (inj) k_cat_generic<1><<<grid, blk, 0, st>>>(a);
-        else if (bp.kernel == 5) {
+        else if (bp.kernel == 5 && !p->gather_only && bp.cat_warp && s->ld >= 128) {
+            CatWarpArgs w{a, bp.d_wide_ent.as<int32_t>(), bp.d_wide_first.as<uint32_t>(), bp.d_wide_cnt.as<int32_t>(), static_cast<int32_t>(s->ld / 4), make_round_keys(key)};
+            const int K = bp.kind, KP = (K + 3) & ~3;
+            const size_t smem = static_cast<size_t>(8) * CAT_SLOTS * K * KP * 4;
+            const unsigned ctas = static_cast<unsigned>(std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8));
+            auto go = [&](auto kernel) -> int32_t {
+                if (smem > 48 * 1024) CU_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                kernel<<<ctas, 256, smem, st>>>(w);
+                return THRML_OK;
+            };
+            int32_t rc;
+            if (K <= 4) rc = go(k_cat_warp<4>);
+            else if (K <= 8) rc = go(k_cat_warp<8>);
+            else if (K <= 10) rc = go(k_cat_warp<10>);
+            else if (K <= 12) rc = go(k_cat_warp<12>);
+            else rc = go(k_cat_warp<16>);
+            if (rc) return rc;
+        }
+        else if (bp.kernel == 5 && !p->gather_only) {
             // weight rows staged in shared memory when CAT_SLOTS x K x K floats per node of the CTA fit in 48 KiB
             const size_t smem = static_cast<size_t>(blk.y) * CAT_SLOTS * bp.kind * bp.kind * 4;
             if (smem <= 48 * 1024 && 32 % blk.x == 0) k_cat_fast<true><<<grid, blk, smem, st>>>(a);
@@ -2074,12 +2166,18 @@ int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value)
         CU_TRY(cudaStreamSynchronize(p->ctx->stream));
         return THRML_OK;
     }
+    if (option == THRML_OPT_GATHER_ONLY) {
+        if (value != 0.0 && value != 1.0) return fail(THRML_ERR_INVALID_ARG, "gather only: 0 or 1");
+        p->gather_only = value != 0.0;
+        return THRML_OK;
+    }
     return fail(THRML_ERR_INVALID_ARG, "unknown program option " + std::to_string(option));
 }
 int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double* value_out) {
     if (!p || !value_out) return fail(THRML_ERR_INVALID_ARG, "null argument");
     if (option == THRML_OPT_DENSE_TILES) *value_out = p->dense_tiles;
     else if (option == THRML_OPT_SPLIT_MARGIN) *value_out = p->split_extra_margin;
+    else if (option == THRML_OPT_GATHER_ONLY) *value_out = p->gather_only ? 1.0 : 0.0;
     else return fail(THRML_ERR_INVALID_ARG, "unknown program option " + std::to_string(option));
     return THRML_OK;
 }

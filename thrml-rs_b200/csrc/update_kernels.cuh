@@ -375,6 +375,149 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
     *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
 }
 
+// Warp-per-node form of k_cat_fast for K <= 16 and 128 chains or more: same states, a quarter of its instructions.
+//  * a warp owns a node for ALL chains: it stages the node's weight rows in shared memory once (a slot with a categorical
+//    tail transposed to [neighbour category][own category], rows padded to a multiple of four floats) and then walks the
+//    chains 128 at a time, instead of one CTA per 128 chains staging the same weights again;
+//  * the logits of one chain live in registers (th[KT]): per slot the row of the neighbour's category is fetched with
+//    16-byte shared-memory loads and added with the sign of the spin tails, so a slot costs about three instructions per
+//    category instead of twenty (no per-category slot bookkeeping, no address arithmetic);
+//  * the canonical order is kept: a table's slots are summed from zero and the table sums are added left to right (a
+//    table with a single active slot adds its weight directly: 0 + w = w);
+//  * entry lists (table and slot of the node's active slots) come from the host, as for k_spin_wide;
+//  * noise, screen and exact fallback are k_cat_fast's.
+struct CatWarpArgs {
+    UpdateArgs u;
+    const int32_t* ent;     // [n][CAT_SLOTS]: table << 24 | slot, -1 = none
+    const uint32_t* first;  // [n] bit e: entry e opens a table
+    const int32_t* cnt;     // [n]
+    int32_t n_chunks4;      // ld / 4: four-chain words per state row
+    PhiloxRoundKeys rk;
+};
+template <int KT>
+__global__ void __launch_bounds__(256, 2) k_cat_warp(const __grid_constant__ CatWarpArgs a) {
+    extern __shared__ float4 s_w4[];  // [8 warps][CAT_SLOTS][K][KP], KP = K rounded up to a multiple of 4
+    constexpr int NV = (KT + 3) / 4;
+    constexpr float MARGIN = 1.2e-5f;
+    const int lane = threadIdx.x & 31;
+    const int K = a.u.K;
+    const int KP = (K + 3) & ~3;
+    float* mine = reinterpret_cast<float*>(s_w4) + static_cast<size_t>(threadIdx.x >> 5) * CAT_SLOTS * K * KP;
+    for (int node = blockIdx.x * 8 + (threadIdx.x >> 5); node < a.u.n; node += gridDim.x * 8) {
+        const int cnt = __ldg(a.cnt + node);
+        const uint32_t first = __ldg(a.first + node);
+        // lane e < cnt: entry e's tail positions and weight row
+        int32_t nb0 = -1, nb1 = -1, nb2 = -1, nbc = -1;
+        const float* wp = nullptr;
+        if (lane < cnt) {
+            const int32_t code = __ldg(a.ent + static_cast<int64_t>(node) * CAT_SLOTS + lane);
+            const DevTable& T = a.u.tabs[code >> 24];
+            const int64_t flat = static_cast<int64_t>(node) * T.k + (code & 0xffffff);
+            if (T.n_spin > 0) nb0 = __ldg(T.idx[0] + flat);
+            if (T.n_spin > 1) nb1 = __ldg(T.idx[1] + flat);
+            if (T.n_spin > 2) nb2 = __ldg(T.idx[2] + flat);
+            if (T.n_tails > T.n_spin) nbc = __ldg(T.idx[T.n_spin] + flat);
+            wp = T.w + flat * T.wdim;
+        }
+        const uint32_t tailed = __ballot_sync(0xffffffffu, nbc >= 0);
+        __syncwarp();  // the previous node's lookups are done
+        for (int s = 0; s < cnt; ++s) {
+            const float* src = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(wp), s));
+            float* dst = mine + s * K * KP;
+            if ((tailed >> s) & 1u) {
+                for (int i = lane; i < K * K; i += 32) {
+                    const int own = i / K, x = i - own * K;
+                    dst[x * KP + own] = __ldg(src + i);
+                }
+            } else {
+                for (int i = lane; i < K; i += 32) dst[i] = __ldg(src + i);
+            }
+        }
+        __syncwarp();
+        uint8_t* drow = a.u.dst + static_cast<int64_t>(node) * a.u.ld;
+        for (int base = 0; base < a.n_chunks4; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
+            const int quad = base + lane;
+            const bool live = quad < a.n_chunks4;
+            uint32_t xw[CAT_SLOTS], sg[CAT_SLOTS];  // neighbour categories of 4 chains (clamped); bit 0 of a byte: the spin-tail product is -1
+#pragma unroll
+            for (int s = 0; s < CAT_SLOTS; ++s) {
+                xw[s] = sg[s] = 0;
+                if (s < cnt) {  // uniform over the warp
+                    const int32_t n0 = __shfl_sync(0xffffffffu, nb0, s), n1 = __shfl_sync(0xffffffffu, nb1, s), n2 = __shfl_sync(0xffffffffu, nb2, s);
+                    const int32_t nc = __shfl_sync(0xffffffffu, nbc, s);
+                    if (live) {
+                        uint32_t neg = 0;
+                        if (n0 >= 0) neg ^= ~ld_word(a.u.spin, n0, a.u.ld, quad);
+                        if (n1 >= 0) neg ^= ~ld_word(a.u.spin, n1, a.u.ld, quad);
+                        if (n2 >= 0) neg ^= ~ld_word(a.u.spin, n2, a.u.ld, quad);
+                        sg[s] = neg & 0x01010101u;
+                        if (nc >= 0) xw[s] = __vminu4(ld_word(a.u.cat, nc, a.u.ld, quad), static_cast<uint32_t>(K - 1) * 0x01010101u);
+                    }
+                }
+            }
+            uint32_t out = 0;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                if (!live || 4 * static_cast<int64_t>(quad) + c >= a.u.n_chains) break;
+                const int sh = 8 * c;
+                float th[KT], sm[KT];
+#pragma unroll
+                for (int k = 0; k < KT; ++k) th[k] = sm[k] = 0.0f;
+#pragma unroll
+                for (int s = 0; s < CAT_SLOTS; ++s) {
+                    if (s >= cnt) break;  // uniform over the warp
+                    const bool opens = (first >> s) & 1u;
+                    const bool closes = s + 1 >= cnt || ((first >> (s + 1)) & 1u);
+                    const uint32_t flip = ((sg[s] >> sh) & 1u) << 31;
+                    const float4* row = reinterpret_cast<const float4*>(mine + s * K * KP + ((xw[s] >> sh) & 0xffu) * KP);
+                    float w[4 * NV];
+#pragma unroll
+                    for (int v = 0; v < NV; ++v) {
+                        const float4 q = row[v];
+                        w[4 * v] = q.x; w[4 * v + 1] = q.y; w[4 * v + 2] = q.z; w[4 * v + 3] = q.w;
+                    }
+                    if (opens && closes) {  // a table with one active slot: its sum is the weight itself
+#pragma unroll
+                        for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < KT; ++k) {
+                            const float t = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                            sm[k] = opens ? __fadd_rn(0.0f, t) : __fadd_rn(sm[k], t);
+                            if (closes) th[k] = __fadd_rn(th[k], sm[k]);
+                        }
+                    }
+                }
+                float best = 0.f, second = -3.0e38f, lmin = 1.0f;
+                uint32_t lead = 0;
+                U4 r{0, 0, 0, 0};
+#pragma unroll
+                for (int k = 0; k < KT; ++k) {
+                    if (k >= K) break;
+                    if ((k & 3) == 0)
+                        r = philox4x32_10_rk(static_cast<uint32_t>(node), 4u * (a.u.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(k >> 2), TAG_CAT, a.rk);
+                    const uint32_t word = (k & 3) == 0 ? r.x : ((k & 3) == 1 ? r.y : ((k & 3) == 2 ? r.z : r.w));
+                    const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;  // the 23-bit uniform of u23_open
+                    const float l1 = __log2f(u) * -0.6931471805599453f;               // -ln u > 0
+                    const float p = fmaf(__log2f(l1), -0.6931471805599453f, th[k]);   // th - ln(l1)
+                    if (k == 0) {
+                        best = p;
+                        lmin = l1;
+                    } else {
+                        lmin = fminf(lmin, l1);
+                        second = fmaxf(second, fminf(best, p));
+                        if (p > best) { best = p; lead = k; }
+                    }
+                }
+                // k_cat_fast's bound: a leader closer to the runner-up than the screen's error is recomputed exactly
+                if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
+                out |= lead << sh;
+            }
+            if (live) *reinterpret_cast<uint32_t*>(drow + 4 * static_cast<int64_t>(quad)) = out;
+        }
+    }
+}
+
 // Threshold tables for spin blocks whose nodes see at most 8 neighbour spins through single-spin-tail tables:
 // lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
 // (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
@@ -1103,6 +1246,147 @@ __global__ void __launch_bounds__(256, ACC && WIDE ? 3 : 4) k_spin_hybrid(const 
         const int32_t row = __ldg(a.lut_row + node);
         if (row >= 0) lut_node_update<ACC, false>(a.lut, s_tab[threadIdx.x >> 5], node, row, static_cast<int64_t>(node) * SEQ_MAX);
         else seq_or_split_update<ACC, WIDE>(a.seq, reinterpret_cast<float*>(s_tab[threadIdx.x >> 5]), node);
+    }
+}
+
+// Spin update for blocks the threshold-table and sequential-sum kernels cannot take: slots whose tail is a product of up to
+// three spins, and slots with a categorical tail that selects the weight (spin_gibbs.rs:527-582).  Same states as
+// k_spin_generic<0>, organised like k_spin_seq: one warp per node, 16 chains per lane per pass, one 16-byte load per
+// neighbour row.  Lane e holds entry e of the node's list (its table and slot, in the canonical order) and fetches that
+// entry's tail positions and weight once; the entry loop broadcasts them.  The product of the spin tails is the XOR of
+// their sign bits; a categorical tail costs one weight lookup per chain.  Weights are read from the slot tables
+// themselves, so a weight refresh needs no rebuild.  The sigmoid is screened as in k_spin_seq.
+constexpr int WIDE_SPIN_TAILS = 3;
+struct WideArgs {
+    const DevTable* tabs;
+    const int32_t* ent;     // [n][SEQ_MAX]: table << 24 | slot of the node's active slots in canonical order, -1 = none
+    const uint32_t* first;  // [n] bit e: entry e is the first of its table
+    const int32_t* cnt;     // [n]
+    const uint8_t* spin;
+    const uint8_t* cat;
+    uint8_t* dst;
+    int64_t ld;
+    int32_t n;
+    int32_t n_chunks;  // ld / 16
+    uint32_t chain_word0;
+    int64_t n_chains;
+    PhiloxRoundKeys rk;
+};
+template <bool CAT>
+__global__ void __launch_bounds__(256, 3) k_spin_wide(const __grid_constant__ WideArgs a) {
+    const int lane = threadIdx.x & 31;
+    const uint4 zeros = make_uint4(0, 0, 0, 0);
+    for (int node = blockIdx.x * 8 + (threadIdx.x >> 5); node < a.n; node += gridDim.x * 8) {
+        const int32_t code = __ldg(a.ent + static_cast<int64_t>(node) * SEQ_MAX + lane);
+        const uint32_t first = __ldg(a.first + node);
+        const int cnt = __ldg(a.cnt + node);
+        int32_t nb0 = -1, nb1 = -1, nb2 = -1, nbc = -1, wdim = 1;
+        float wv = 0.0f;
+        const float* wp = nullptr;
+        if (code >= 0) {
+            const DevTable& T = a.tabs[code >> 24];
+            const int64_t flat = static_cast<int64_t>(node) * T.k + (code & 0xffffff);
+            if (T.n_spin > 0) nb0 = __ldg(T.idx[0] + flat);
+            if (T.n_spin > 1) nb1 = __ldg(T.idx[1] + flat);
+            if (T.n_spin > 2) nb2 = __ldg(T.idx[2] + flat);
+            wp = T.w + flat * T.wdim;
+            wdim = T.wdim;
+            if (CAT && T.n_tails > T.n_spin) nbc = __ldg(T.idx[T.n_spin] + flat);
+            else wv = __ldg(wp);
+        }
+        uint8_t* drow = a.dst + static_cast<int64_t>(node) * a.ld;
+        for (int base = 0; base < a.n_chunks; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
+            const int ch = base + lane;
+            const bool live = ch < a.n_chunks;
+            float gam[16], part[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) gam[i] = part[i] = 0.0f;
+            auto sign_row = [&](int32_t nb) {  // bit 0 of a byte: that chain's spin is -1
+                if (nb < 0 || !live) return zeros;
+                const uint4 v = __ldg(reinterpret_cast<const uint4*>(a.spin + static_cast<int64_t>(nb) * a.ld) + ch);
+                return make_uint4(v.x ^ 0x01010101u, v.y ^ 0x01010101u, v.z ^ 0x01010101u, v.w ^ 0x01010101u);
+            };
+            for (int e = 0; e < cnt; ++e) {  // uniform over the warp
+                const uint4 s0 = sign_row(__shfl_sync(0xffffffffu, nb0, e));
+                const uint4 s1 = sign_row(__shfl_sync(0xffffffffu, nb1, e));
+                const uint4 s2 = sign_row(__shfl_sync(0xffffffffu, nb2, e));
+                const int32_t nce = CAT ? __shfl_sync(0xffffffffu, nbc, e) : -1;
+                const float we = __shfl_sync(0xffffffffu, wv, e);
+                if ((first >> e) & 1u) {  // a new table: close the previous one
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        gam[i] = __fadd_rn(gam[i], part[i]);
+                        part[i] = 0.0f;
+                    }
+                }
+                // +-1.0f per chain from the sign bit with one byte permute, as in k_spin_seq
+                const uint32_t t[4] = {((s0.x ^ s1.x ^ s2.x) << 7) | 0x3f3f3f3fu, ((s0.y ^ s1.y ^ s2.y) << 7) | 0x3f3f3f3fu,
+                                       ((s0.z ^ s1.z ^ s2.z) << 7) | 0x3f3f3f3fu, ((s0.w ^ s1.w ^ s2.w) << 7) | 0x3f3f3f3fu};
+                if (CAT && nce >= 0) {  // the neighbour's category selects the weight; out of range selects none
+                    const uint64_t wpe = __shfl_sync(0xffffffffu, reinterpret_cast<uint64_t>(wp), e);
+                    const float* wrow = reinterpret_cast<const float*>(wpe);
+                    const uint32_t wd = static_cast<uint32_t>(__shfl_sync(0xffffffffu, wdim, e));
+                    uint4 xv = zeros;
+                    if (live) xv = __ldg(reinterpret_cast<const uint4*>(a.cat + static_cast<int64_t>(nce) * a.ld) + ch);
+                    const uint32_t x[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const uint32_t xi = (x[q] >> (8 * c)) & 0xffu;
+                            const float wc = xi < wd ? __ldg(wrow + xi) : 0.0f;
+                            const float sp = __uint_as_float(__byte_perm(t[q], 0x00800000u, 0x0654u | (c << 12)));
+                            part[4 * q + c] = __fmaf_rn(sp, wc, part[4 * q + c]);
+                        }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const float sp = __uint_as_float(__byte_perm(t[q], 0x00800000u, 0x0654u | (c << 12)));
+                            part[4 * q + c] = __fmaf_rn(sp, we, part[4 * q + c]);
+                        }
+                }
+            }
+            // d = 2^24 (u - p) with the approximate sigmoid; draws within 4e-6 of p are redone with the exact rule
+            uint32_t o[4];
+            float nearest = 16777216.0f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+                o[q] = 0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float gamma = __fadd_rn(gam[4 * q + c], part[4 * q + c]);
+                    gam[4 * q + c] = gamma;
+                    float ex, p24;
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(ex) : "f"(gamma * -2.885390081777927f));
+                    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(p24) : "f"(fmaf(ex, 5.9604644775390625e-8f, 5.9604644775390625e-8f)));  // 2^24 p
+                    const float d = __uint2float_rn(rr[c] >> 8) - p24;
+                    part[4 * q + c] = d;
+                    nearest = fminf(nearest, fabsf(d));
+                    o[q] |= (__float_as_uint(d) >> 31) << (8 * c);
+                }
+            }
+            if (nearest <= 67.2f) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 4u * ch + q, 0u, TAG_SPIN, a.rk);
+                    const uint32_t rr[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        if (fabsf(part[4 * q + c]) <= 67.2f)
+                            o[q] = (o[q] & ~(1u << (8 * c))) | ((exact_spin_draw(gam[4 * q + c], rr[c]) ? 1u : 0u) << (8 * c));
+                }
+            }
+            if (live) {
+                // chains past the last one stay 0, as every other kernel leaves them
+#pragma unroll
+                for (int q = 0; q < 4; ++q) o[q] &= valid_mask(a.n_chains, ch, q);
+                reinterpret_cast<uint4*>(drow)[ch] = make_uint4(o[0], o[1], o[2], o[3]);
+            }
+        }
     }
 }
 

@@ -240,6 +240,7 @@ class Builder:
 
 OPT_DENSE_TILES = 1
 OPT_SPLIT_MARGIN = 2
+OPT_GATHER_ONLY = 3
 
 
 class Program:
