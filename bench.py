@@ -744,7 +744,7 @@ def run_potts_program(T, torch, args, rank, world, device, dist, ctx, comm):
     cfg = workload_config(args)
     cfg["block_kernels"] = kinds
     out.update({"config": cfg, "gpu_launches": args.steps * 2,
-                "roofline": hbm_roofline(updates / 2, 7.0 + 6.0 * K * K * 4 / chains, ms / 2, "k_cat_fast" if all(k == 5 for k in kinds) else "k_cat_generic",
+                "roofline": hbm_roofline(updates / 2, 7.0 + 6.0 * K * K * 4 / chains, ms / 2, "k_cat_warp" if all(k == 5 for k in kinds) and K <= 16 and chains >= 128 else "k_cat_generic",
                                          note="gather of six neighbour bytes and six K x K weight rows per node; instruction-issue bound"),
                 "e2e": {"value": updates * args.steps / dt, "unit": UNIT, "h2d_bytes_per_step": chains * n / args.steps, "d2h_bytes_per_step": chains * n / args.steps, "seconds": dt,
                         "call": "thrml_state_upload_u8_many + thrml_run_blocks + thrml_state_download_u8"}})

@@ -395,7 +395,7 @@ struct CatWarpArgs {
     PhiloxRoundKeys rk;
 };
 template <int KT>
-__global__ void __launch_bounds__(256, 2) k_cat_warp(const __grid_constant__ CatWarpArgs a) {
+__global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ CatWarpArgs a) {
     extern __shared__ float4 s_w4[];  // [8 warps][CAT_SLOTS][K][KP], KP = K rounded up to a multiple of 4
     constexpr int NV = (KT + 3) / 4;
     constexpr float MARGIN = 1.2e-5f;
