@@ -118,6 +118,26 @@ def test_general_spin_kernel_on_larger_mixed_models(T, O, seed, chains):
         assert np.array_equal(gg.download(i), gs.download(i))
 
 
+@pytest.mark.parametrize("K,chains", [(2, 128), (7, 144), (11, 260), (13, 160), (16, 130), (17, 130), (40, 130)])
+def test_categorical_kernels_across_category_counts(T, O, K, chains):
+    """Explicit Potts programs on the warp-per-node categorical kernel: every template width, the guard for K below the
+    width, the opt-in shared-memory size at K = 16, and K > 16 (register-resident slots, any K) — against the oracle and
+    against the gather kernel."""
+    desc, _ = M.potts_lattice(T, 6, K, 30 + K)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 19)
+    assert all(prog.block_kernel(b) == 5 for b in range(2))
+    gs.run_blocks(99, 3)
+    os_.run_blocks(99, 3)
+    assert_states_equal(gs, os_, 2)
+    prog.set_option(T.OPT_GATHER_ONLY, 1)
+    gg = T.ChainState(prog, chains)
+    for i, a in enumerate(M.random_states(desc, chains, 19)):
+        gg.upload(i, a)
+    gg.run_blocks(99, 3)
+    for i in range(2):
+        assert np.array_equal(gg.download(i), gs.download(i))
+
+
 def test_kernel_selection(T, O):
     cases = model_cases(T)
     prog = T.Program(M.fill(T.Builder(cases["graph8"]["kinds"]), cases["graph8"]))

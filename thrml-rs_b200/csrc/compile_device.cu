@@ -48,11 +48,19 @@ __global__ void k_run_starts(const uint32_t* __restrict__ key, int64_t rows, int
 }
 __global__ void k_block_kmax(const uint32_t* __restrict__ key, const int32_t* __restrict__ start, const int32_t* __restrict__ fid_blk, int64_t rows,
                              int32_t* __restrict__ kmax) {
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < rows; i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
-        if (key[i] == KEY_NONE) continue;
-        // only the last entry of a run carries the run's length
-        if (i + 1 < rows && key[i + 1] == key[i]) continue;
-        atomicMax(&kmax[fid_blk[key[i]]], static_cast<int32_t>(i) - start[i] + 1);
+    // the keys are sorted block-major, so the lanes of a warp mostly see one block: one atomic per warp and block
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t base = blockIdx.x * static_cast<int64_t>(blockDim.x); base < rows; base += stride) {  // uniform trip count over a warp
+        const int64_t i = base + threadIdx.x;
+        int32_t blk = -1, len = 0;
+        if (i < rows && key[i] != KEY_NONE) {
+            blk = fid_blk[key[i]];
+            // only the last entry of a run carries the run's length
+            if (i + 1 >= rows || key[i + 1] != key[i]) len = static_cast<int32_t>(i) - start[i] + 1;
+        }
+        const unsigned peers = __match_any_sync(0xffffffffu, blk);
+        const int32_t longest = __reduce_max_sync(peers, len);
+        if (blk >= 0 && longest > 0 && (threadIdx.x & 31) == __ffs(peers) - 1) atomicMax(&kmax[blk], longest);
     }
 }
 struct ScatterArgs {
