@@ -49,6 +49,9 @@ def parse():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--nodes", type=int, default=N_NODES, help="graph size (default: the benchmark configuration)")
     ap.add_argument("--chains", type=int, default=None, help="chains per GPU (default: the configuration's)")
+    ap.add_argument("--state-format", default="int8", choices=["int8", "bitpacked"],
+                    help="sparse_ising: int8 (default) = one byte per spin and chain, the HBM-bound format the roofline target is quoted on; "
+                         "bitpacked = sweeps on the bit-packed mirror (THRML_OPT_STATE_FORMAT), more site updates per second, bound by instruction issue")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle's check of a chain slice of the benchmarked state")
@@ -434,6 +437,8 @@ def run_sparse(T, torch, args, rank, world, device, dist, ctx, comm):
     builder = W.fill_ising(T.Builder(np.zeros(n, np.int32)), model, ctx=ctx)
     prepare = {"where": "device", "graph_and_colouring_s": round(t1 - t0, 3), "add_factors_and_compile_s": round(time.perf_counter() - t1, 3)}
     program = T.Program(builder, ctx)
+    if args.state_format == "bitpacked":
+        program.set_option(T.OPT_STATE_FORMAT, 1)
     n_blocks = len(model["blocks"])
     state = T.ChainState(program, chains, chain_offset=rank * chains)
     moments = T.Moments.from_arrays(program, *W.ising_moment_arrays(model))
@@ -487,7 +492,13 @@ def run_sparse(T, torch, args, rank, world, device, dist, ctx, comm):
     kinds = [program.block_kernel(b) for b in range(n_blocks)]
     mean_deg = 2.0 * len(model["edges"]) / n
     bytes_per_update = (mean_deg + 1.0) + 10.0 * mean_deg / chains
-    kernel = "k_spin_lut" if all(k == 1 for k in kinds) else ("k_spin_seq" if all(k == 4 for k in kinds) else ("k_spin_hybrid" if all(k in (1, 4, 6) for k in kinds) else "k_spin_generic"))
+    packed = args.state_format == "bitpacked" and all(k == 1 for k in kinds) and chains > 1008
+    if packed:  # one bit per neighbour read and one written; the same parameters
+        bytes_per_update = (mean_deg + 1.0) / 8.0 + 10.0 * mean_deg / chains
+    result["config"]["state_format"] = "bit-packed mirror (THRML_OPT_STATE_FORMAT = 1)" if packed else "int8"
+    kernel = "k_packed_lut" if packed else "k_spin_lut" if all(k == 1 for k in kinds) else ("k_spin_seq" if all(k == 4 for k in kinds) else ("k_spin_hybrid" if all(k in (1, 4, 6) for k in kinds) else "k_spin_generic"))
+    if packed:
+        result["dtype"] = "1-bit spins, u32 thresholds"
     profiled = kernel == "k_spin_lut" and args.degree == DEGREE and args.graph == "regular" and chains == CHAINS_PER_GPU
     result["roofline"] = hbm_roofline(updates_per_step / n_blocks, bytes_per_update, sweep_ms / n_blocks, kernel,
                                       dram_bytes_per_update=LUT_DRAM_BYTES_PER_UPDATE if profiled else None,

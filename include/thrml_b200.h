@@ -205,10 +205,17 @@ int32_t thrml_program_update_group(thrml_program* p, int32_t group, const float*
  *                           exact route.  Setting it rebuilds the affected blocks' tables.
  *   THRML_OPT_GATHER_ONLY   1 = blocks whose default kernel is the general spin kernel (kind 7) or the register-resident
  *                           categorical kernel (kind 5) run the node x four-chain gather kernels (kinds 0 and 2) instead;
- *                           0 (the default) = each block's own kernel.  The states are the same either way. */
+ *                           0 (the default) = each block's own kernel.  The states are the same either way.
+ *   THRML_OPT_STATE_FORMAT  0 (the default) = sweeps read and write the state as one byte per spin and chain; 1 = when every
+ *                           free block runs the threshold-table kernel (kind 1), nothing is staged and the state holds at
+ *                           least 1009 chains, sweeps (and a moment observer whose rows the update kernels own) run on a
+ *                           bit-packed mirror of the spin state (1.125 bytes of traffic per update instead of 9, the same
+ *                           noise, the same states); the byte copy is brought up to date by the first call that needs
+ *                           it (downloads, other observers, energies, uploads), and the mirror by the next sweep. */
 #define THRML_OPT_DENSE_TILES 1
 #define THRML_OPT_SPLIT_MARGIN 2
 #define THRML_OPT_GATHER_ONLY 3
+#define THRML_OPT_STATE_FORMAT 4
 int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value);
 int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double* value_out);
 /* Dense bipartite path.  A spin block whose neighbours all lie in one other spin block (a layer of an RBM-style model:

@@ -4,7 +4,7 @@ The directory name contains a hyphen, so the package is imported under the modul
 `__graft_entry__.load_package()` (tests and bench.py do this) or by putting an importlib spec on it directly.
 """
 from ._ffi import ThrmlError, lib  # noqa: F401
-from .engine import (OPT_DENSE_TILES, OPT_GATHER_ONLY, OPT_SPLIT_MARGIN, Builder, ChainState, Comm, Context, Moments, Program, default_context, greedy_coloring_arrays,  # noqa: F401
+from .engine import (OPT_DENSE_TILES, OPT_GATHER_ONLY, OPT_SPLIT_MARGIN, OPT_STATE_FORMAT, Builder, ChainState, Comm, Context, Moments, Program, default_context, greedy_coloring_arrays,  # noqa: F401
                      lattice_edges, pack_chains, rng_split)
 from .api import (Block, BlockGibbsSpec, BlockSamplingProgram, BlockSpec, CategoricalEBMFactor,  # noqa: F401
                   CategoricalGibbsConditional, DiscreteEBMFactor, FactorizedEBM, FactorSamplingProgram, InteractionGroup, IsingEBM,

@@ -81,6 +81,7 @@ struct thrml_program {
     int32_t dense_tiles = 2;         // THRML_OPT_DENSE_TILES
     float split_extra_margin = 0.f;  // THRML_OPT_SPLIT_MARGIN
     bool gather_only = false;        // THRML_OPT_GATHER_ONLY
+    int32_t state_format = 0;        // THRML_OPT_STATE_FORMAT: 1 = sweeps of all-threshold-table programs run on a bit-packed mirror
 };
 
 struct thrml_state {
@@ -105,8 +106,40 @@ struct thrml_state {
     int64_t persist_epoch = -1;  // program kernel_epoch persist_grid was computed for
     int64_t persistent_launches = 0, block_launches = 0;
     int64_t image_rows = 0;
+    // Bit-packed mirror of the spin class (THRML_OPT_STATE_FORMAT = 1): uint32 [position][pw], chain c at bit c & 31 of word
+    // c >> 5.  At most one of the two copies is stale; every access to either goes through rows() / packed_rows(), which
+    // make the requested copy current first and assume the caller will write it.
+    mutable DevBuf packed;
+    int64_t pw = 0;
+    mutable bool bytes_valid = true, packed_valid = false;
     void touch(int32_t block) { if (!image_fresh.empty()) { image_fresh[block] = 0; ones_fresh[block] = 0; } }
-    uint8_t* rows(int sd) const { return cls[sd].as<uint8_t>(); }
+    uint8_t* rows(int sd) const {
+        if (packed.p && sd == prog->sd_spin) {
+            if (!bytes_valid) {
+                const int64_t n_rows = prog->class_size[sd], units = n_rows * (ld >> 4);
+                k_unpack_rows<<<static_cast<unsigned>((units + 255) / 256), 256, 0, prog->ctx->stream>>>(packed.as<uint32_t>(), pw, n_rows, ld, n_chains, cls[sd].as<uint8_t>());
+                bytes_valid = true;
+            }
+            packed_valid = false;
+        }
+        return cls[sd].as<uint8_t>();
+    }
+    int32_t packed_rows(uint32_t** out) {
+        const int sd = prog->sd_spin;
+        const int64_t n_rows = prog->class_size[sd];
+        if (!packed.p) {
+            pw = (ld + 31) / 32;
+            if (int32_t rc = packed.alloc(static_cast<size_t>(n_rows) * pw * 4)) return rc;
+            packed_valid = false;
+        }
+        if (!packed_valid) {
+            k_pack_rows<<<static_cast<unsigned>((n_rows + 7) / 8), dim3(32, 8), 0, prog->ctx->stream>>>(cls[sd].as<uint8_t>(), ld, n_chains, n_rows, pw, packed.as<uint32_t>());
+            packed_valid = true;
+        }
+        bytes_valid = false;
+        *out = packed.as<uint32_t>();
+        return THRML_OK;
+    }
 };
 
 struct FusedMaps {
@@ -1347,7 +1380,46 @@ static int32_t observe_async(thrml_moments* m, thrml_state* s);
 
 // sample_blocks (sampling.rs:28-63), asynchronous.  With `acc` the sweep is followed by an observation of `acc`:
 // the threshold-table kernels accumulate their rows while they update, one k_moments launch covers the other rows.
+// Bit-packed route (THRML_OPT_STATE_FORMAT = 1): every free block on the threshold-table kernel, nothing staged, rows wide
+// enough to fill a warp with words (1024 chains), and an observer (if any) whose rows the update kernels own entirely.
+static bool packed_route(const thrml_state* s, const thrml_moments* acc) {
+    const thrml_program* p = s->prog;
+    if (p->state_format != 1 || p->sd_spin < 0 || p->n_free < 1 || s->ld < 1024) return false;
+    for (size_t g = 0; g < p->sampling_order.size(); ++g) {
+        if (p->staged[g]) return false;
+        for (int32_t m : p->sampling_order[g])
+            if (p->blocks[m].kernel != 1 || p->blocks[m].base_kernel != 1) return false;
+    }
+    if (acc && !(acc->mode == 0 && acc->any_fused && acc->n_left == 0 && acc->kernel_epoch == p->kernel_epoch && acc->prog == p)) return false;
+    return true;
+}
+static int32_t sweep_packed(thrml_state* s, uint64_t key, thrml_moments* acc) {
+    thrml_program* p = s->prog;
+    std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
+    rng_split(key, p->n_free, keys.data());
+    cudaStream_t st = p->ctx->stream;
+    uint32_t* rows = nullptr;
+    if (int32_t rc = s->packed_rows(&rows)) return rc;
+    for (const auto& members : p->sampling_order)
+        for (int32_t m : members) {
+            const BlockProg& bp = p->blocks[m];
+            const bool f = acc && acc->fused[m];
+            PackedArgs a{bp.d_nbr.as<int32_t>(), bp.d_lut.as<uint32_t>(), rows, rows + bp.offset * s->pw, s->pw, static_cast<int32_t>(bp.n),
+                         static_cast<int32_t>((s->n_chains + 31) / 32), static_cast<uint32_t>(s->chain_offset >> 2), s->n_chains, make_round_keys(keys[m]),
+                         f ? acc->fused[m]->m1.as<int32_t>() : nullptr, f ? acc->fused[m]->m2.as<int32_t>() : nullptr, f ? acc->d_sums.as<long long>() : nullptr};
+            const unsigned ctas = static_cast<unsigned>(std::min<int64_t>((bp.n + 7) / 8, static_cast<int64_t>(p->ctx->sm_count) * 8));
+            if (f) k_packed_lut<true><<<ctas, 256, 0, st>>>(a);
+            else k_packed_lut<false><<<ctas, 256, 0, st>>>(a);
+            CU_TRY(cudaGetLastError());
+            s->touch(m);
+            ++s->block_launches;
+        }
+    if (acc) acc->n_obs += s->n_chains;
+    return THRML_OK;
+}
+
 static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_moments* acc = nullptr) {
+    if (!inj && packed_route(s, acc)) return sweep_packed(s, key, acc);
     const bool fuse = acc && acc->mode == 0 && acc->any_fused && !inj && acc->kernel_epoch == s->prog->kernel_epoch;
     thrml_program* p = s->prog;
     std::vector<uint64_t> keys(static_cast<size_t>(p->n_free));
@@ -1383,8 +1455,8 @@ static int32_t sweep(thrml_state* s, uint64_t key, NoiseCursor* inj, thrml_momen
             k_moments_spin<<<grid, dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_pos.as<int32_t>(), acc->n_left, s->rows(p->sd_spin), s->ld, s->n_chains,
                                                          acc->d_sums.as<unsigned long long>(), acc->d_left_rows.as<int64_t>());
         else
-            k_moments<<<grid, dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_sd.as<int32_t>(), acc->d_left_pos.as<int32_t>(), acc->n_left, s->cls[0].as<uint8_t>(),
-                                                    s->cls[1].as<uint8_t>(), s->ld, s->n_chains, acc->spin_transform, acc->d_sums.as<unsigned long long>(),
+            k_moments<<<grid, dim3(32, 8), 0, st>>>(acc->d_left_ptr.as<int64_t>(), acc->d_left_sd.as<int32_t>(), acc->d_left_pos.as<int32_t>(), acc->n_left, s->rows(0),
+                                                    s->rows(1), s->ld, s->n_chains, acc->spin_transform, acc->d_sums.as<unsigned long long>(),
                                                     acc->d_left_rows.as<int64_t>());
         CU_TRY(cudaGetLastError());
     }
@@ -1549,7 +1621,7 @@ static int32_t run(thrml_state* s, uint64_t key, int64_t n_iters, NoiseCursor* i
     if (n_iters <= 0) return acc ? observe_async(acc, s) : THRML_OK;
     std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
     rng_split(key, n_iters, keys.data());
-    const bool queue = !inj && persistent_grid(s) > 0;
+    const bool queue = !inj && !packed_route(s, nullptr) && persistent_grid(s) > 0;  // an explicit bit-packed format outranks the queued kernels
     for (int64_t i = 0; i < n_iters; ++i) {
         thrml_moments* a = i + 1 == n_iters ? acc : nullptr;
         if (queue && (!a || observer_rides_along(a, s))) {
@@ -2052,8 +2124,8 @@ static int32_t observe_async(thrml_moments* m, thrml_state* s) {
     if (m->prog != s->prog) return fail(THRML_ERR_INVALID_ARG, "observer and state belong to different programs");
     if (int32_t rc = flush_pending(s)) return rc;
     cudaStream_t st = s->prog->ctx->stream;
-    const uint8_t* c0 = s->cls[0].as<uint8_t>();
-    const uint8_t* c1 = s->cls[1].as<uint8_t>();
+    const uint8_t* c0 = s->rows(0);
+    const uint8_t* c1 = s->rows(1);
     if (m->mode == 0) {
         if (m->total_rows > 0) {
             const unsigned grid = static_cast<unsigned>((m->total_rows + 7) / 8);
@@ -2166,6 +2238,11 @@ int32_t thrml_program_set_option(thrml_program* p, int32_t option, double value)
         CU_TRY(cudaStreamSynchronize(p->ctx->stream));
         return THRML_OK;
     }
+    if (option == THRML_OPT_STATE_FORMAT) {
+        if (value != 0.0 && value != 1.0) return fail(THRML_ERR_INVALID_ARG, "state format: 0 (one byte per spin) or 1 (bit-packed mirror)");
+        p->state_format = static_cast<int32_t>(value);
+        return THRML_OK;
+    }
     if (option == THRML_OPT_GATHER_ONLY) {
         if (value != 0.0 && value != 1.0) return fail(THRML_ERR_INVALID_ARG, "gather only: 0 or 1");
         p->gather_only = value != 0.0;
@@ -2178,6 +2255,7 @@ int32_t thrml_program_get_option(const thrml_program* p, int32_t option, double*
     if (option == THRML_OPT_DENSE_TILES) *value_out = p->dense_tiles;
     else if (option == THRML_OPT_SPLIT_MARGIN) *value_out = p->split_extra_margin;
     else if (option == THRML_OPT_GATHER_ONLY) *value_out = p->gather_only ? 1.0 : 0.0;
+    else if (option == THRML_OPT_STATE_FORMAT) *value_out = p->state_format;
     else return fail(THRML_ERR_INVALID_ARG, "unknown program option " + std::to_string(option));
     return THRML_OK;
 }

@@ -1249,6 +1249,123 @@ __global__ void __launch_bounds__(256, ACC && WIDE ? 3 : 4) k_spin_hybrid(const 
     }
 }
 
+// Threshold-table update on a BIT-PACKED spin state (one bit per node and chain: word w of a row holds chains 32 w .. 32 w + 31),
+// the same function of the same noise as k_spin_lut, so the states are the same bits.  One warp per node; a lane takes one
+// word of each of the 8 neighbour rows (32 chains; the warp reads 128 contiguous bytes per row), transposes the 8 x 32 bit
+// matrix into 32 configuration bytes (byte permutes to collect 8 x 8 blocks, three masked-shift steps to transpose each),
+// looks the thresholds up in the node's table (staged in shared memory once per node) and compares them with the Philox
+// words of the four-chain groups.  1.125 bytes of state per update instead of 9, at about the instruction count of the
+// byte kernel: this kernel is bound by instruction issue, not by HBM.
+// ACC: the fused moment observer; pair rows are population counts of XORed words.
+struct PackedArgs {
+    const int32_t* nbr;   // [n][8] global spin positions, -1 = unused slot
+    const uint32_t* lut;  // [n][256]
+    const uint32_t* src;  // packed rows of the spin class
+    uint32_t* dst;        // first packed row of the block
+    int64_t pw;           // words per packed row
+    int32_t n;
+    int32_t n_words;      // words that hold chains: ceil(n_chains / 32)
+    uint32_t chain_word0;
+    int64_t n_chains;
+    PhiloxRoundKeys rk;
+    const int32_t* m1_row;
+    const int32_t* m2_row;
+    long long* sums;
+};
+// 8 x 8 bit transpose of the matrix held as bytes of (lo, hi): bit b of byte i becomes bit i of byte b.
+__device__ __forceinline__ void transpose_8x8(uint32_t& lo, uint32_t& hi) {
+    uint32_t t;
+    t = (lo ^ (lo << 7)) & 0x55005500u; lo ^= t ^ (t >> 7);
+    t = (hi ^ (hi << 7)) & 0x55005500u; hi ^= t ^ (t >> 7);
+    t = (lo ^ (lo << 14)) & 0x33330000u; lo ^= t ^ (t >> 14);
+    t = (hi ^ (hi << 14)) & 0x33330000u; hi ^= t ^ (t >> 14);
+    t = (hi ^ (lo >> 4)) & 0x0f0f0f0fu; hi ^= t; lo ^= t << 4;
+}
+template <bool ACC>
+__global__ void __launch_bounds__(256, 4) k_packed_lut(const __grid_constant__ PackedArgs a) {
+    __shared__ uint32_t s_lut[8][LUT_SIZE];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    uint32_t* tab = s_lut[warp];
+    for (int node = blockIdx.x * 8 + warp; node < a.n; node += gridDim.x * 8) {
+        __syncwarp();  // the previous node's lookups are done
+        const uint4* src = reinterpret_cast<const uint4*>(a.lut + static_cast<int64_t>(node) * LUT_SIZE);
+        {  // the table is staged complemented: draw > threshold  <=>  draw + ~threshold carries out of 32 bits
+            const uint4 q0 = __ldg(src + lane), q1 = __ldg(src + lane + 32);
+            reinterpret_cast<uint4*>(tab)[lane] = make_uint4(~q0.x, ~q0.y, ~q0.z, ~q0.w);
+            reinterpret_cast<uint4*>(tab)[lane + 32] = make_uint4(~q1.x, ~q1.y, ~q1.z, ~q1.w);
+        }
+        const int32_t nb = lane < LUT_BITS ? __ldg(a.nbr + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
+        int32_t my_row = -1, row1 = -1;
+        uint32_t own = 0, mine = 0, ones_total = 0;
+        if (ACC) {
+            my_row = lane < LUT_BITS ? __ldg(a.m2_row + static_cast<int64_t>(node) * LUT_BITS + lane) : -1;
+            row1 = __ldg(a.m1_row + node);
+            own = __ballot_sync(0xffffffffu, my_row >= 0);
+        }
+        __syncwarp();
+        uint32_t* drow = a.dst + static_cast<int64_t>(node) * a.pw;
+        for (int base = 0; base < a.n_words; base += 32) {  // every lane runs every pass: the broadcasts are warp-wide
+            const int word = base + lane;
+            const bool live = word < a.n_words;
+            uint32_t w[LUT_BITS];
+#pragma unroll
+            for (int j = 0; j < LUT_BITS; ++j) {
+                const int32_t nbj = __shfl_sync(0xffffffffu, nb, j);
+                w[j] = (nbj >= 0 && live) ? __ldg(a.src + static_cast<int64_t>(nbj) * a.pw + word) : 0u;
+            }
+            // configuration bytes of the 32 chains: idx[g] holds chains 4 g .. 4 g + 3
+            uint32_t idx[8];
+            {
+                const uint32_t a0 = __byte_perm(w[0], w[1], 0x5140), a1 = __byte_perm(w[2], w[3], 0x5140);
+                const uint32_t a2 = __byte_perm(w[0], w[1], 0x7362), a3 = __byte_perm(w[2], w[3], 0x7362);
+                const uint32_t b0 = __byte_perm(w[4], w[5], 0x5140), b1 = __byte_perm(w[6], w[7], 0x5140);
+                const uint32_t b2 = __byte_perm(w[4], w[5], 0x7362), b3 = __byte_perm(w[6], w[7], 0x7362);
+                idx[0] = __byte_perm(a0, a1, 0x5410); idx[1] = __byte_perm(b0, b1, 0x5410);
+                idx[2] = __byte_perm(a0, a1, 0x7632); idx[3] = __byte_perm(b0, b1, 0x7632);
+                idx[4] = __byte_perm(a2, a3, 0x5410); idx[5] = __byte_perm(b2, b3, 0x5410);
+                idx[6] = __byte_perm(a2, a3, 0x7632); idx[7] = __byte_perm(b2, b3, 0x7632);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) transpose_8x8(idx[2 * q], idx[2 * q + 1]);
+            }
+            // Chains 31 down to 0: each comparison is an add whose carry (draw > threshold: the spin becomes 0) is shifted into
+            // the word by an add-with-carry, two integer operations per chain; the word is inverted at the end.
+            uint32_t out = 0;
+#pragma unroll
+            for (int g = 7; g >= 0; --g) {
+                const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + 8u * static_cast<uint32_t>(word) + g, 0u, TAG_SPIN, a.rk);
+                const uint32_t c = idx[g];
+                const uint32_t t0 = tab[c & 0xffu], t1 = tab[(c >> 8) & 0xffu], t2 = tab[(c >> 16) & 0xffu], t3 = tab[c >> 24];
+                uint32_t scratch;
+                asm("add.cc.u32 %1, %2, %3;\n\taddc.u32 %0, %0, %0;" : "+r"(out), "=r"(scratch) : "r"(t3), "r"(r.w));
+                asm("add.cc.u32 %1, %2, %3;\n\taddc.u32 %0, %0, %0;" : "+r"(out), "=r"(scratch) : "r"(t2), "r"(r.z));
+                asm("add.cc.u32 %1, %2, %3;\n\taddc.u32 %0, %0, %0;" : "+r"(out), "=r"(scratch) : "r"(t1), "r"(r.y));
+                asm("add.cc.u32 %1, %2, %3;\n\taddc.u32 %0, %0, %0;" : "+r"(out), "=r"(scratch) : "r"(t0), "r"(r.x));
+            }
+            out = ~out;
+            const int64_t left = a.n_chains - 32 * static_cast<int64_t>(word);
+            const uint32_t vm = !live || left <= 0 ? 0u : (left >= 32 ? 0xffffffffu : ((1u << static_cast<int>(left)) - 1u));
+            out &= vm;  // chains past the last one stay 0
+            if (live) drow[word] = out;
+            if (ACC) {
+                if (row1 >= 0) {
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(__popc(out)));
+                    if (lane == 0) ones_total += t;
+                }
+#pragma unroll
+                for (int j = 0; j < LUT_BITS; ++j) {
+                    if (!((own >> j) & 1u)) continue;  // uniform over the warp
+                    const uint32_t t = __reduce_add_sync(0xffffffffu, static_cast<uint32_t>(__popc((w[j] ^ out) & vm)));
+                    if (lane == j) mine += t;
+                }
+            }
+        }
+        if (ACC) {
+            if (my_row >= 0) a.sums[my_row] += a.n_chains - 2ll * mine;
+            if (lane == 0 && row1 >= 0) a.sums[row1] += 2ll * ones_total - a.n_chains;
+        }
+    }
+}
+
 // Spin update for blocks the threshold-table and sequential-sum kernels cannot take: slots whose tail is a product of up to
 // three spins, and slots with a categorical tail that selects the weight (spin_gibbs.rs:527-582).  Same states as
 // k_spin_generic<0>, organised like k_spin_seq: one warp per node, 16 chains per lane per pass, one 16-byte load per

@@ -241,6 +241,7 @@ class Builder:
 OPT_DENSE_TILES = 1
 OPT_SPLIT_MARGIN = 2
 OPT_GATHER_ONLY = 3
+OPT_STATE_FORMAT = 4
 
 
 class Program:
