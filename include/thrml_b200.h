@@ -204,7 +204,7 @@ int32_t thrml_program_update_group(thrml_program* p, int32_t group, const float*
  *                           canonical order; 0 (the default) keeps the derived bound, 2^25 sends every draw through the
  *                           exact route.  Setting it rebuilds the affected blocks' tables.
  *   THRML_OPT_GATHER_ONLY   1 = blocks whose default kernel is the general spin kernel (kind 7) or the register-resident
- *                           categorical kernel (kind 5) run the node x four-chain gather kernels (kinds 0 and 2) instead;
+ *                           categorical kernels (kinds 5 and 8) run the node x four-chain gather kernels (kinds 0 and 2) instead;
  *                           0 (the default) = each block's own kernel.  The states are the same either way.
  *   THRML_OPT_STATE_FORMAT  0 (the default) = sweeps read and write the state as one byte per spin and chain; 1 = when every
  *                           free block runs the threshold-table kernel (kind 1), nothing is staged and the state holds at
@@ -231,7 +231,8 @@ int32_t thrml_program_enable_dense(thrml_program* p, int32_t allow_bf16_rounding
  * at most 8 active slots (slot data held in registers, Gumbel noise screened with fast logarithms), 6 a spin block that
  * mixes kinds 1 and 4 node by node (at least a quarter of its nodes have at most 8 neighbour slots), 7 the general spin
  * kernel (slots whose tail is a product of up to three spins or a categorical node that selects the weight, at most 32
- * active slots per node; warp per node, 16 chains per lane). */
+ * active slots per node; warp per node, 16 chains per lane), 8 categorical kernel for nodes with 9 to 32 active slots and
+ * at most 16 categories (slot data in shared memory, logits in registers). */
 int32_t thrml_program_block_kernel(const thrml_program* p, int32_t block, int32_t* kind_out);
 
 /* n_chains chains held on this device; chain_offset = global id of local chain 0 (the in-kernel random

@@ -86,6 +86,26 @@ def potts_lattice(T, side, K, seed, sigma=0.3, bias_sigma=0.1):
     return desc, dict(n=n, K=K, blocks=blocks)
 
 
+def potts_random_graph(T, n, degree, K, seed, sigma=0.3, with_spins=False):
+    """K-state nodes on a random regular graph with one [K, K] table per edge and a unary factor: degree + 1 active slots per
+    node.  with_spins adds a block of spins coupled to the categorical nodes through [K]-weight factors with a spin tail."""
+    rng = np.random.default_rng(seed)
+    edges = random_regular_graph(n, degree, seed)
+    colour, n_col = T.greedy_coloring_arrays(n, edges)
+    blocks = [np.flatnonzero(colour == c) for c in range(n_col)]
+    n_all = n + (n if with_spins else 0)
+    kinds = np.concatenate([np.full(n, K, np.int32), np.zeros(n_all - n, np.int32)])
+    ops = [("add_discrete_factor", [], [np.arange(n)], rng.normal(0, 0.1, (n, K, 1)).astype(np.float32)),
+           ("add_discrete_factor", [], [edges[:, 0], edges[:, 1]], rng.normal(0, sigma, (len(edges), K, K)).astype(np.float32))]
+    free = [(blk, i) for i, blk in enumerate(blocks)]
+    if with_spins:
+        spins = np.arange(n, 2 * n)
+        free.append((spins, n_col))
+        ops.append(("add_discrete_factor", [spins], [np.arange(n)], rng.normal(0, 0.4, (n, K, 1)).astype(np.float32)))
+    desc = dict(kinds=kinds, free=free, ops=ops, dtype_order=[K, 0] if with_spins else None)
+    return desc, dict(n=n, K=K, edges=edges, blocks=blocks)
+
+
 def mixed_model(seed, n_spin=12, n_cat=10, K=4, with_clamped=True, superblock_pair=False, two_cat_tails=False):
     """Spins and categorical nodes with spin-spin, spin-cat, cat-cat and three-spin factors, random blocks."""
     rng = np.random.default_rng(seed)

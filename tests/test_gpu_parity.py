@@ -138,6 +138,26 @@ def test_categorical_kernels_across_category_counts(T, O, K, chains):
         assert np.array_equal(gg.download(i), gs.download(i))
 
 
+@pytest.mark.parametrize("K,degree,chains,with_spins", [(4, 12, 130, False), (10, 9, 1040, False), (16, 20, 160, True), (3, 30, 144, True), (16, 30, 132, False)])
+def test_many_slot_categorical_kernel(T, O, K, degree, chains, with_spins):
+    """Categorical nodes with 10 to 32 active slots (a random regular graph, one table per edge, optionally a spin tail):
+    the shared-memory slot kernel against the oracle and against the gather kernel."""
+    desc, info = M.potts_random_graph(T, 120, degree, K, 40 + K, with_spins=with_spins)
+    prog, gs, os_, gb, ob = make_pair(T, O, desc, chains, 23)
+    n_cat_blocks = len(info["blocks"])
+    assert all(prog.block_kernel(b) == 8 for b in range(n_cat_blocks))
+    gs.run_blocks(5, 3)
+    os_.run_blocks(5, 3)
+    assert_states_equal(gs, os_, n_blocks_of(desc))
+    prog.set_option(T.OPT_GATHER_ONLY, 1)
+    gg = T.ChainState(prog, chains)
+    for i, a in enumerate(M.random_states(desc, chains, 23)):
+        gg.upload(i, a)
+    gg.run_blocks(5, 3)
+    for i in range(n_blocks_of(desc)):
+        assert np.array_equal(gg.download(i), gs.download(i))
+
+
 def test_kernel_selection(T, O):
     cases = model_cases(T)
     prog = T.Program(M.fill(T.Builder(cases["graph8"]["kinds"]), cases["graph8"]))

@@ -43,6 +43,7 @@ struct BlockProg {
     bool split_wide = false;  // some node has four tables
     DevBuf d_wide_ent, d_wide_first, d_wide_cnt;         // kernel 7: entry lists (table and slot) of the wide general spin kernel
     bool wide_has_cat = false;                           // kernel 7: some table has a categorical tail
+    int32_t cat_most = 0;                                // kernels 5 and 8: largest active slot count of a node
     bool cat_warp = false;                               // kernel 5: entry lists (d_wide_*) exist for the warp-per-node categorical kernel
     DevBuf d_lut_row, d_lut_nodes;                       // kernel 6: table row of each node (-1 = sequential-sum node) and its inverse
     int64_t n_lut = 0;                                   // kernel 6: nodes that have a threshold table
@@ -570,11 +571,15 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                 most = std::max(most, cnt);
             }
             if (most <= CAT_SLOTS) bp.kernel = 5;
-            // entry lists for the warp-per-node form (K <= 16, at most three spin tails per slot)
-            bool ok = bp.kernel == 5 && bp.kind <= 16 && tabs.size() <= 127;
+            bp.cat_most = static_cast<int32_t>(std::min<int64_t>(most, CAT_MANY_SLOTS));
+            // entry lists for the warp-per-node forms (K <= 16, at most three spin tails per slot): kind 5 with up to 8 slots
+            // per node keeps them in registers, kind 8 with up to 32 in shared memory
+            bool ok = bp.kind <= 16 && tabs.size() <= 127 && most <= CAT_MANY_SLOTS;
             for (const SlotTable& t : tabs) ok = ok && t.k < (1 << 24) && t.n_spin <= WIDE_SPIN_TAILS;
+            if (ok && bp.kernel != 5) bp.kernel = 8;
+            const int64_t ENT = bp.kernel == 8 ? CAT_MANY_SLOTS : CAT_SLOTS;
             if (ok) {
-                std::vector<int32_t> ent(static_cast<size_t>(bp.n) * CAT_SLOTS, -1), cnt(static_cast<size_t>(bp.n), 0);
+                std::vector<int32_t> ent(static_cast<size_t>(bp.n) * ENT, -1), cnt(static_cast<size_t>(bp.n), 0);
                 std::vector<uint32_t> first(static_cast<size_t>(bp.n), 0);
                 for (int64_t i2 = 0; i2 < bp.n; ++i2) {
                     int e = 0;
@@ -585,7 +590,7 @@ int32_t thrml_program_create(thrml_ctx* ctx, const thrml_builder* b, thrml_progr
                             if (!t.active[static_cast<size_t>(i2) * t.k + j]) continue;
                             if (!started) first[i2] |= 1u << e;
                             started = true;
-                            ent[static_cast<size_t>(i2) * CAT_SLOTS + e++] = static_cast<int32_t>(ti << 24) | j;
+                            ent[static_cast<size_t>(i2) * ENT + e++] = static_cast<int32_t>(ti << 24) | j;
                         }
                     }
                     cnt[i2] = e;
@@ -1357,6 +1362,37 @@ static int32_t launch_block(thrml_state* s, int32_t block, uint64_t key, NoiseCu
             else if (K <= 10) rc = go(k_cat_warp<10>);
             else if (K <= 12) rc = go(k_cat_warp<12>);
             else rc = go(k_cat_warp<16>);
+            if (rc) return rc;
+        }
+        else if (bp.kernel == 8 && !p->gather_only && s->ld >= 128) {
+            CatManyArgs w{CatWarpArgs{a, bp.d_wide_ent.as<int32_t>(), bp.d_wide_first.as<uint32_t>(), bp.d_wide_cnt.as<int32_t>(), static_cast<int32_t>(s->ld / 4), make_round_keys(key)},
+                          bp.cat_most};
+            // staged weights: `cat_most` rows of K x KP floats per warp; eight warps per CTA while two CTAs fit an SM, four
+            // while one does, otherwise the weights are read through L1
+            const int K = bp.kind, KP = (K + 3) & ~3;
+            const size_t per_warp = static_cast<size_t>(bp.cat_most) * K * KP * 4;
+            const int warps = per_warp * 8 <= 72 * 1024 ? 8 : (per_warp * 4 <= 160 * 1024 ? 4 : 0);
+            const size_t smem = warps ? per_warp * warps : 0;
+            const int wpc = warps ? warps : 8;
+            const unsigned ctas = static_cast<unsigned>(std::min<int64_t>((bp.n + wpc - 1) / wpc, static_cast<int64_t>(p->ctx->sm_count) * 8));
+            auto go = [&](auto kernel) -> int32_t {
+                // the kernel's static arrays take 35 KiB: the opt-in is needed well below 48 KiB of dynamic memory
+                if (smem > 8 * 1024) CU_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+                kernel<<<ctas, 32 * wpc, smem, st>>>(w);
+                return THRML_OK;
+            };
+            int32_t rc;
+            if (warps) {
+                if (K <= 4) rc = go(k_cat_many<4, true>);
+                else if (K <= 8) rc = go(k_cat_many<8, true>);
+                else if (K <= 12) rc = go(k_cat_many<12, true>);
+                else rc = go(k_cat_many<16, true>);
+            } else {
+                if (K <= 4) rc = go(k_cat_many<4, false>);
+                else if (K <= 8) rc = go(k_cat_many<8, false>);
+                else if (K <= 12) rc = go(k_cat_many<12, false>);
+                else rc = go(k_cat_many<16, false>);
+            }
             if (rc) return rc;
         }
         else if (bp.kernel == 5 && !p->gather_only) {

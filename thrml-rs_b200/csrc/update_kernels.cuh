@@ -518,6 +518,149 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
     }
 }
 
+// Categorical blocks with 9 to 32 active slots per node (K <= 16, 128 chains or more): k_cat_warp's arithmetic without its
+// per-slot registers.  Per pass a lane packs, for each slot, the neighbour's category and the sign of the spin tails of its
+// four chains into one word kept in shared memory ([slot][lane]: conflict-free); per-slot facts that are the same for
+// every lane (weight row, flags) sit beside it.  STAGE: the node's weight rows are staged in dynamic shared memory as in
+// k_cat_warp (pair slots transposed, `slots` rows of K x KP floats per warp); otherwise they are read through L1, a
+// column of K values per slot and chain (the lanes of a warp then ask for up to K different addresses per load, which
+// is what the staging avoids).
+constexpr int CAT_MANY_SLOTS = 32;
+struct CatManyArgs {
+    CatWarpArgs w;
+    int32_t slots;  // STAGE: weight rows staged per warp = the block's largest active slot count
+};
+template <int KT, bool STAGE>
+__global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ CatManyArgs args) {
+    extern __shared__ float4 s_stage4[];  // STAGE: [warps][slots][K][KP]
+    __shared__ uint32_t s_slot[8][CAT_MANY_SLOTS][32];
+    __shared__ const float* s_wp[8][CAT_MANY_SLOTS];
+    __shared__ uint32_t s_flag[8][CAT_MANY_SLOTS];  // bit 0 categorical tail, bit 1 opens a table, bit 2 closes one
+    constexpr float MARGIN = 1.2e-5f;
+    constexpr int NV = (KT + 3) / 4;
+    const CatWarpArgs& a = args.w;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int K = a.u.K;
+    const int KP = (K + 3) & ~3;
+    float* mine = reinterpret_cast<float*>(s_stage4) + static_cast<size_t>(warp) * args.slots * K * KP;
+    for (int node = blockIdx.x * warps + warp; node < a.u.n; node += gridDim.x * warps) {
+        const int cnt = __ldg(a.cnt + node);
+        const uint32_t first = __ldg(a.first + node);
+        int32_t nb0 = -1, nb1 = -1, nb2 = -1, nbc = -1;
+        __syncwarp();  // the previous node's reads of the per-slot facts and of the staged weights are done
+        if (lane < cnt) {
+            const int32_t code = __ldg(a.ent + static_cast<int64_t>(node) * CAT_MANY_SLOTS + lane);
+            const DevTable& T = a.u.tabs[code >> 24];
+            const int64_t flat = static_cast<int64_t>(node) * T.k + (code & 0xffffff);
+            if (T.n_spin > 0) nb0 = __ldg(T.idx[0] + flat);
+            if (T.n_spin > 1) nb1 = __ldg(T.idx[1] + flat);
+            if (T.n_spin > 2) nb2 = __ldg(T.idx[2] + flat);
+            if (T.n_tails > T.n_spin) nbc = __ldg(T.idx[T.n_spin] + flat);
+            s_wp[warp][lane] = T.w + flat * T.wdim;
+            const bool closes = lane + 1 >= cnt || ((first >> (lane + 1)) & 1u);
+            s_flag[warp][lane] = (nbc >= 0 ? 1u : 0u) | (((first >> lane) & 1u) << 1) | (closes ? 4u : 0u);
+        }
+        __syncwarp();
+        if (STAGE) {
+            for (int s = 0; s < cnt; ++s) {
+                const float* src = s_wp[warp][s];
+                float* dst = mine + s * K * KP;
+                if (s_flag[warp][s] & 1u) {
+                    for (int i = lane; i < K * K; i += 32) {
+                        const int own = i / K, x = i - own * K;
+                        dst[x * KP + own] = __ldg(src + i);
+                    }
+                } else {
+                    for (int i = lane; i < K; i += 32) dst[i] = __ldg(src + i);
+                }
+            }
+            __syncwarp();
+        }
+        uint8_t* drow = a.u.dst + static_cast<int64_t>(node) * a.u.ld;
+        for (int base = 0; base < a.n_chunks4; base += 32) {  // every lane runs every pass: the entry broadcasts are warp-wide
+            const int quad = base + lane;
+            const bool live = quad < a.n_chunks4;
+            for (int s = 0; s < cnt; ++s) {  // uniform over the warp
+                const int32_t n0 = __shfl_sync(0xffffffffu, nb0, s), n1 = __shfl_sync(0xffffffffu, nb1, s), n2 = __shfl_sync(0xffffffffu, nb2, s);
+                const int32_t nc = __shfl_sync(0xffffffffu, nbc, s);
+                uint32_t v = 0;
+                if (live) {
+                    uint32_t neg = 0;
+                    if (n0 >= 0) neg ^= ~ld_word(a.u.spin, n0, a.u.ld, quad);
+                    if (n1 >= 0) neg ^= ~ld_word(a.u.spin, n1, a.u.ld, quad);
+                    if (n2 >= 0) neg ^= ~ld_word(a.u.spin, n2, a.u.ld, quad);
+                    if (nc >= 0) v = __vminu4(ld_word(a.u.cat, nc, a.u.ld, quad), static_cast<uint32_t>(K - 1) * 0x01010101u);
+                    v |= (neg & 0x01010101u) << 7;  // a category is below 16: bit 7 of the byte is free for the sign
+                }
+                s_slot[warp][s][lane] = v;  // read back by this lane only
+            }
+            uint32_t out = 0;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                if (!live || 4 * static_cast<int64_t>(quad) + c >= a.u.n_chains) break;
+                const int sh = 8 * c;
+                float th[KT], sm[KT];
+#pragma unroll
+                for (int k = 0; k < KT; ++k) th[k] = sm[k] = 0.0f;
+                for (int s = 0; s < cnt; ++s) {
+                    const uint32_t b = (s_slot[warp][s][lane] >> sh) & 0xffu;
+                    const uint32_t flag = s_flag[warp][s];
+                    const uint32_t flip = (b >> 7) << 31;
+                    float w[4 * NV];
+                    if (STAGE) {
+                        const float4* row = reinterpret_cast<const float4*>(mine + s * K * KP + (b & 0x7fu) * KP);  // an untailed slot has category 0
+#pragma unroll
+                        for (int v = 0; v < NV; ++v) {
+                            const float4 q = row[v];
+                            w[4 * v] = q.x; w[4 * v + 1] = q.y; w[4 * v + 2] = q.z; w[4 * v + 3] = q.w;
+                        }
+                    } else {
+                        const float* col = s_wp[warp][s] + ((flag & 1u) ? (b & 0x7fu) : 0u);
+                        const int stride = (flag & 1u) ? K : 1;
+#pragma unroll
+                        for (int k = 0; k < KT; ++k) w[k] = k < K ? __ldg(col + k * stride) : 0.0f;
+                    }
+                    if ((flag & 6u) == 6u) {  // a table with one active slot: its sum is the weight itself
+#pragma unroll
+                        for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < KT; ++k) {
+                            const float t = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                            sm[k] = (flag & 2u) ? __fadd_rn(0.0f, t) : __fadd_rn(sm[k], t);
+                            if (flag & 4u) th[k] = __fadd_rn(th[k], sm[k]);
+                        }
+                    }
+                }
+                float best = 0.f, second = -3.0e38f, lmin = 1.0f;
+                uint32_t lead = 0;
+                U4 r{0, 0, 0, 0};
+#pragma unroll
+                for (int k = 0; k < KT; ++k) {
+                    if (k >= K) break;
+                    if ((k & 3) == 0)
+                        r = philox4x32_10_rk(static_cast<uint32_t>(node), 4u * (a.u.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(k >> 2), TAG_CAT, a.rk);
+                    const uint32_t word = (k & 3) == 0 ? r.x : ((k & 3) == 1 ? r.y : ((k & 3) == 2 ? r.z : r.w));
+                    const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;  // the 23-bit uniform of u23_open
+                    const float l1 = __log2f(u) * -0.6931471805599453f;
+                    const float p = fmaf(__log2f(l1), -0.6931471805599453f, th[k]);
+                    if (k == 0) {
+                        best = p;
+                        lmin = l1;
+                    } else {
+                        lmin = fminf(lmin, l1);
+                        second = fmaxf(second, fminf(best, p));
+                        if (p > best) { best = p; lead = k; }
+                    }
+                }
+                if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
+                out |= lead << sh;
+            }
+            if (live) *reinterpret_cast<uint32_t*>(drow + 4 * static_cast<int64_t>(quad)) = out;
+        }
+    }
+}
+
 // Threshold tables for spin blocks whose nodes see at most 8 neighbour spins through single-spin-tail tables:
 // lut[node][cfg] = the largest 32-bit random word for which the node becomes 1 when its neighbours are cfg
 // (bit j = state of the j-th active neighbour slot in table order).  gamma is accumulated exactly as in
