@@ -479,12 +479,17 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
                     if (opens && closes) {  // a table with one active slot: its sum is the weight itself
 #pragma unroll
                         for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
-                    } else {
+                    } else {  // the branches are uniform over the warp and taken outside the category loops
+                        if (opens) {  // 0 + t = t (a sum that starts at -0 instead of +0 gives the same logits: th is never -0)
 #pragma unroll
-                        for (int k = 0; k < KT; ++k) {
-                            const float t = __uint_as_float(__float_as_uint(w[k]) ^ flip);
-                            sm[k] = opens ? __fadd_rn(0.0f, t) : __fadd_rn(sm[k], t);
-                            if (closes) th[k] = __fadd_rn(th[k], sm[k]);
+                            for (int k = 0; k < KT; ++k) sm[k] = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < KT; ++k) sm[k] = __fadd_rn(sm[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                        }
+                        if (closes) {
+#pragma unroll
+                            for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], sm[k]);
                         }
                     }
                 }
@@ -623,12 +628,17 @@ __global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ Cat
                     if ((flag & 6u) == 6u) {  // a table with one active slot: its sum is the weight itself
 #pragma unroll
                         for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
-                    } else {
+                    } else {  // the branches are uniform over the warp and taken outside the category loops
+                        if (flag & 2u) {  // 0 + t = t (a sum that starts at -0 instead of +0 gives the same logits: th is never -0)
 #pragma unroll
-                        for (int k = 0; k < KT; ++k) {
-                            const float t = __uint_as_float(__float_as_uint(w[k]) ^ flip);
-                            sm[k] = (flag & 2u) ? __fadd_rn(0.0f, t) : __fadd_rn(sm[k], t);
-                            if (flag & 4u) th[k] = __fadd_rn(th[k], sm[k]);
+                            for (int k = 0; k < KT; ++k) sm[k] = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                        } else {
+#pragma unroll
+                            for (int k = 0; k < KT; ++k) sm[k] = __fadd_rn(sm[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                        }
+                        if (flag & 4u) {
+#pragma unroll
+                            for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], sm[k]);
                         }
                     }
                 }
