@@ -55,7 +55,7 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle's check of a chain slice of the benchmarked state")
-    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts", "potts_program", "small_lattice"],
+    ap.add_argument("--workload", default="sparse_ising", choices=["sparse_ising", "rbm", "lattice", "potts", "potts_program", "small_lattice", "mixed"],
                     help="sparse_ising = the headline configuration; rbm = dense bipartite CD-1 on the tensor cores; lattice = one bit-packed 2-D Ising "
                          "lattice sharded by row stripes with halo exchange; potts = implicit 3-D Potts lattice; small_lattice = 32 x 32 torus, 256 chains")
     ap.add_argument("--side", type=int, default=None, help="lattice side (lattice / potts / potts_program workloads)")
@@ -67,11 +67,11 @@ def parse():
                     help="rbm workload: CTA pairs sharing 256-row tiles (tcgen05 cta_group::2), one CTA per 128-row tile, or chosen per launch")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = {"sparse_ising": 500, "rbm": 200, "lattice": 50, "potts": 20, "potts_program": 20, "small_lattice": 20}[args.workload]
+        args.steps = {"sparse_ising": 500, "rbm": 200, "lattice": 50, "potts": 20, "potts_program": 20, "small_lattice": 20, "mixed": 20}[args.workload]
     if args.chains is None:
-        args.chains = {"sparse_ising": CHAINS_PER_GPU, "rbm": 8192, "lattice": 16, "potts": 1024, "potts_program": 1024, "small_lattice": 256}[args.workload]
+        args.chains = {"sparse_ising": CHAINS_PER_GPU, "rbm": 8192, "lattice": 16, "potts": 1024, "potts_program": 1024, "small_lattice": 256, "mixed": 4096}[args.workload]
     if args.side is None:
-        args.side = {"lattice": 32768, "potts": 128, "potts_program": 32}.get(args.workload, 0)
+        args.side = {"lattice": 32768, "potts": 128, "potts_program": 32, "mixed": 512}.get(args.workload, 0)
     return args
 
 
@@ -284,7 +284,23 @@ def cpu_lattice(args, threads):
     return step, f"one step = one sweep of {chains} chains over {threads} threads of the explicit Ising program on a {side}^2 torus (per-update cost does not depend on the side)", om
 
 
-CPU_LEGS = {"sparse_ising": cpu_sparse, "small_lattice": cpu_small_lattice, "rbm": cpu_rbm, "potts": cpu_potts, "potts_program": cpu_potts, "lattice": cpu_lattice}
+def cpu_mixed(args, threads):
+    from oracle import oracle as O
+    from thrml_rs_b200 import workloads as W
+    side = min(args.side, 256)
+    model = W.spin_category_checkerboard(side, 4)
+    om = W.fill_factors(O.Model(model["kinds"], model["dtype_order"]), model)
+    st = O.State(om, threads, 0, threads=threads)
+    st.randomize(5)
+
+    def step(i):
+        st.run_blocks(300 + i, 1)
+        return model["n"] * threads
+
+    return step, f"one step = one sweep of {threads} chains (one per host thread) of the same factor program on a {side}^2 grid (per-update cost does not depend on the side)", om
+
+
+CPU_LEGS = {"mixed": cpu_mixed, "sparse_ising": cpu_sparse, "small_lattice": cpu_small_lattice, "rbm": cpu_rbm, "potts": cpu_potts, "potts_program": cpu_potts, "lattice": cpu_lattice}
 
 
 def cpu_sample(step, target_seconds, max_steps, warmup=1):
@@ -350,6 +366,9 @@ def workload_config(args, model=None, world=None):
     if args.workload == "rbm":
         return {"workload": "bipartite RBM-style Ising EBM, CD-1 per step", "visible": 784, "hidden": 4096, "chains": int(args.chains),
                 "l2": "operands (6.4 MB couplings, 13-67 MB states) fit in L2: a tensor-pipe measurement, not an HBM one"}
+    if args.workload == "mixed":
+        return {"workload": "spin / 4-state checkerboard with three-spin terms (not a BASELINE configuration: the general spin and the warp-per-node categorical kernels)",
+                "side": int(args.side), "categories": 4, "chains": int(args.chains), "l2": "state (1 GiB at side 512, 4096 chains) larger than L2"}
     if args.workload in ("potts", "potts_program"):
         return {"workload": "3-D periodic Potts-like lattice, K = 10, shared direction tables" + (", as an explicit factor program" if args.workload == "potts_program" else ", category marginals every sweep"),
                 "side": int(args.side), "categories": 10, "chains": int(args.chains), "l2": "state (2 GiB at side 128) larger than L2" if args.side >= 64 else "cache-resident"}
@@ -388,13 +407,13 @@ def main():
     ctx = T.default_context(local_rank)
     comm = T.Comm.from_torch(dist, ctx) if dist else None
     env = dict(T=T, torch=torch, args=args, rank=rank, world=world, device=local_rank, dist=dist, ctx=ctx, comm=comm)
-    if args.workload in ("rbm", "small_lattice", "potts_program", "potts") and world > 1:
+    if args.workload in ("rbm", "small_lattice", "potts_program", "potts", "mixed") and world > 1:
         # these configurations are replicas: every rank would run the same independent problem
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unavailable": f"--workload {args.workload} runs on one GPU (replicas only); use --gpus 1"}), flush=True)
     else:
         out = {"sparse_ising": run_sparse, "rbm": run_rbm, "small_lattice": run_small_lattice, "potts_program": run_potts_program, "potts": run_potts,
-               "lattice": run_lattice}[args.workload](**env)
+               "lattice": run_lattice, "mixed": run_mixed}[args.workload](**env)
         if rank == 0:
             print(json.dumps(out), flush=True)
     if comm is not None:
@@ -762,6 +781,70 @@ def run_potts_program(T, torch, args, rank, world, device, dist, ctx, comm):
     del back
     if not args.no_cpu_baseline:
         out["cpu_baseline"], _ = cpu_baseline(args, os.cpu_count() or 1)
+    return out
+
+
+def run_mixed(T, torch, args, rank, world, device, dist, ctx, comm):
+    """Spin / K-state checkerboard with three-spin terms (workloads.spin_category_checkerboard): two spin blocks whose slots have
+    categorical tails and spin-pair tails (k_spin_wide) and one categorical block with spin tails (k_cat_warp).  Not a
+    configuration of the reference's benchmark list: it measures the kernels that serve general factor structures."""
+    from thrml_rs_b200 import workloads as W
+    side, K, chains = args.side, 4, args.chains
+    model = W.spin_category_checkerboard(side, K)
+    n = model["n"]
+    program = T.Program(W.fill_factors(T.Builder(model["kinds"], model["dtype_order"]), model, ctx=ctx), ctx)
+    kinds = [program.block_kernel(b) for b in range(3)]
+    names = {0: "k_spin_generic", 2: "k_cat_generic", 5: "k_cat_warp", 7: "k_spin_wide", 8: "k_cat_many"}
+    state = T.ChainState(program, chains)
+    state.randomize(5)
+    stream = torch.cuda.ExternalStream(ctx.stream)
+
+    def sync():
+        ctx.synchronize()
+        torch.cuda.synchronize()
+
+    for i in range(max(args.warmup, 3)):
+        state.sample_blocks(i)
+    sampler = ClockSampler(device)
+    t0 = time.time()
+    ms = timed(torch, stream, lambda: [state.sample_blocks(100 + i) for i in range(args.steps)], sync) / args.steps
+    clocks = sampler.stop(t0, time.time())
+    # each block's kernel alone.  Algorithmic bytes per update: one byte per tail read and one written, plus the node's slot
+    # parameters (position, weight row) amortised over the chains
+    tails = [4 + 2, 4, 4]          # spins of even rows: four categorical neighbours and the spin pair of the three-spin term
+    params = [5 * 8 + 4 * 4 * K + 8, 4 * 8 + 4 * 4 * K + 4, 4 * 8 + 4 * 4 * K + 4 * K]
+    per_block = []
+    for b in range(3):
+        nb = len(model["blocks"][b])
+        bms = timed(torch, stream, lambda: [state.sample_single_block(b, 7 + i) for i in range(10)], sync) / 10
+        per_block.append({"block": b, "kernel": names.get(kinds[b], str(kinds[b])), "nodes": int(nb), "ms": bms, "site_updates_per_s": nb * chains / (bms * 1e-3),
+                          "bytes_per_update": tails[b] + 1 + params[b] / chains})
+    top = max(per_block, key=lambda r: r["ms"])
+    updates = float(n) * chains
+    rng = np.random.default_rng(9)
+    host = [pinned(torch, rng.integers(0, 2 if b < 2 else K, (chains, len(model["blocks"][b])), dtype=np.uint8)) for b in range(3)]
+    sync()
+    ta = time.perf_counter()
+    state.upload_many([0, 1, 2], [h.numpy() for h in host])
+    state.run_blocks(55, args.steps)
+    back = [state.download(b, np.uint8) for b in range(3)]
+    dt = time.perf_counter() - ta
+    del back
+    out = base_line(args, updates / (ms * 1e-3), ms, 1, "u8 spins and categories, f32 fields and logits")
+    cfg = workload_config(args)
+    cfg["block_kernels"] = kinds
+    out.update({"config": cfg, "clocks": clocks, "gpu_launches": args.steps * 3, "per_block": per_block,
+                "roofline": hbm_roofline(top["nodes"] * float(chains), top["bytes_per_update"], top["ms"], top["kernel"],
+                                         note="the block that takes the most time; per_block lists all three"),
+                "e2e": {"value": updates * args.steps / dt, "unit": UNIT, "h2d_bytes_per_step": chains * n / args.steps, "d2h_bytes_per_step": chains * n / args.steps, "seconds": dt,
+                        "call": "thrml_state_upload_u8_many + thrml_run_blocks + thrml_state_download_u8"}})
+    if not args.no_cpu_baseline:
+        out["cpu_baseline"], _ = cpu_baseline(args, os.cpu_count() or 1)
+        if not args.no_parity:
+            sys.path.insert(0, os.path.join(ROOT, "tests"))
+            import fullsize_checks as F
+            from oracle import oracle as O
+            out["parity_check"] = F.mixed_check(T, O, model, program, state, chains, threads=os.cpu_count() or 1)
     return out
 
 

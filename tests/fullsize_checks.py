@@ -269,3 +269,34 @@ def dense_check(T, O, n_visible=784, n_hidden=4096, chains=1024, slice_chains=16
     out["ok"] = bool(ok)
     out["seconds"] = round(time.time() - t0, 1)
     return out
+
+
+def mixed_check(T, O, model, program, state, chains, slice_chains=16, sweeps=2, threads=16):
+    """Spin / category checkerboard (bench.py --workload mixed): `sweeps` sweeps from a seeded random start on the device, the
+    first and last `slice_chains` chains followed by the oracle from the same start.  `state` is overwritten."""
+    from thrml_rs_b200 import workloads as W
+    t0 = time.time()
+    n_blocks = len(model["blocks"])
+    state.randomize(0xC6C6_0001)
+    start = {}
+    starts = sorted({0, max(chains - slice_chains, 0) // 16 * 16})
+    for s0 in starts:
+        cnt = min(slice_chains, chains - s0)
+        start[s0] = [state.download_chains(b, s0, cnt) for b in range(n_blocks)]
+    state.run_blocks(0xC6C6_0002, sweeps)
+    om = W.fill_factors(O.Model(model["kinds"], model["dtype_order"]), model)
+    out = {"workload": "mixed", "nodes": int(model["n"]), "chains": int(chains), "sweeps": int(sweeps), "slices": [],
+           "kernels": [int(program.block_kernel(b)) for b in range(n_blocks)]}
+    ok = True
+    for s0 in starts:
+        cnt = min(slice_chains, chains - s0)
+        os_ = O.State(om, cnt, s0, threads=threads)
+        for b in range(n_blocks):
+            os_.set_block(b, start[s0][b].astype(np.float32))
+        os_.run_blocks(0xC6C6_0002, sweeps)
+        bad = sum(int(np.count_nonzero(state.download_chains(b, s0, cnt) != os_.get_block(b).astype(np.uint8))) for b in range(n_blocks))
+        out["slices"].append({"first_chain": int(s0), "chains": int(cnt), "mismatched_nodes": bad})
+        ok &= bad == 0
+    out["ok"] = bool(ok)
+    out["seconds"] = round(time.time() - t0, 1)
+    return out

@@ -55,3 +55,15 @@ def test_rbm_layer_sizes_fields_and_draws(T, O, tiles):
     assert res["ok"], res
     for blk in res["blocks"]:
         assert blk["mismatched_draws"] <= 2, res
+
+
+def test_mixed_checkerboard_256(T, O):
+    """The general spin kernel and the warp-per-node categorical kernel at 256^2 nodes x 2048 chains, chain slices against the oracle."""
+    from thrml_rs_b200 import workloads as W
+    ctx = T.default_context()
+    model = W.spin_category_checkerboard(256, 4)
+    program = T.Program(W.fill_factors(T.Builder(model["kinds"], model["dtype_order"]), model, ctx=ctx), ctx)
+    state = T.ChainState(program, 2048)
+    res = F.mixed_check(T, O, model, program, state, 2048)
+    assert res["kernels"] == [7, 7, 5]
+    assert res["ok"], res

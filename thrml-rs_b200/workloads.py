@@ -76,3 +76,39 @@ def rbm_ising(n_visible=784, n_hidden=4096, seed=0x5EED0003, w_sigma=0.01, bias_
     hid = np.arange(n_visible, n_visible + n_hidden, dtype=np.int64)
     edges = np.stack([np.repeat(vis, n_hidden), np.tile(hid, n_visible)], axis=1)
     return dict(n=n_visible + n_hidden, n_visible=n_visible, n_hidden=n_hidden, W=W, b=b, edges=edges, J=W.ravel().copy(), beta=1.0, blocks=[vis, hid])
+
+
+def spin_category_checkerboard(side=512, K=4, seed=0x5EED0006):
+    """Mixed discrete EBM on a periodic side x side grid: spins on one checkerboard colour, K-state nodes on the other, so every
+    spin has four categorical neighbours (factors with a [K] weight row and a categorical tail for the spin, a spin tail for
+    the category) and the other way round; spins of even rows also carry a three-spin term with their two diagonal spins
+    of the next row.  Three blocks: spins of even rows, spins of odd rows, all K-state nodes.  Returns the pieces a builder
+    takes: kinds, dtype_order, blocks, factor ops (method name and arguments)."""
+    rng = np.random.default_rng(seed)
+    idx = np.arange(side * side, dtype=np.int64).reshape(side, side)
+    colour = np.add.outer(np.arange(side), np.arange(side)) % 2
+    row = idx // side
+    spins, cats = np.sort(idx[colour == 0]), np.sort(idx[colour == 1])
+    even, odd = np.sort(idx[(colour == 0) & (row % 2 == 0)]), np.sort(idx[(colour == 0) & (row % 2 == 1)])
+    kinds = np.where(colour.ravel() == 0, 0, K).astype(np.int32)
+    ops = [("add_discrete_factor", [spins], [], rng.normal(0, 0.2, (spins.size, 1, 1)).astype(np.float32)),
+           ("add_discrete_factor", [], [cats], rng.normal(0, 0.2, (cats.size, K, 1)).astype(np.float32))]
+    for axis in (1, 0):
+        a, b = idx.ravel(), np.roll(idx, -1, axis=axis).ravel()
+        m = colour.ravel()[a] == 0  # a is the spin of the pair
+        ops.append(("add_discrete_factor", [a[m]], [b[m]], rng.normal(0, 0.4, (int(m.sum()), K, 1)).astype(np.float32)))
+        ops.append(("add_discrete_factor", [b[~m]], [a[~m]], rng.normal(0, 0.4, (int((~m).sum()), K, 1)).astype(np.float32)))
+    r, c = even // side, even % side
+    below = ((r + 1) % side) * side
+    ops.append(("add_discrete_factor", [even, below + (c + 1) % side, below + (c - 1) % side], [], rng.normal(0, 0.3, (even.size, 1, 1)).astype(np.float32)))
+    return dict(n=side * side, side=side, K=K, kinds=kinds, dtype_order=[0, K], blocks=[even, odd, cats], ops=ops)
+
+
+def fill_factors(builder, model, ctx=None):
+    """Feed a spin_category_checkerboard() model to a builder (the library's or any object with the same methods)."""
+    for i, blk in enumerate(model["blocks"]):
+        builder.add_free_block(blk, superblock=i)
+    for op in model["ops"]:
+        getattr(builder, op[0])(*op[1:])
+    builder.compile() if ctx is None else builder.compile(ctx)
+    return builder
