@@ -87,10 +87,12 @@ def test_potts_randomize_and_schedule(T, O):
     assert agree > 0.6  # T = 2 I favours equal neighbours (uniform would give 0.25)
 
 
-def test_library_drivers_match_per_colour_calls(T):
-    """thrml_potts_run_blocks / thrml_potts_sample_with_marginals = the same key schedule driven colour by colour."""
+@pytest.mark.parametrize("K,chains", [(5, 48), (3, 128), (10, 256), (16, 384), (12, 1024), (20, 128)])
+def test_library_drivers_match_per_colour_calls(T, K, chains):
+    """thrml_potts_run_blocks / thrml_potts_sample_with_marginals = the same key schedule driven colour by colour.  With
+    full warps of chains (a multiple of 128) and at most 16 categories the library's schedule counts the categories inside
+    the update kernels; the per-colour calls below always use the separate observer kernel."""
     from thrml_rs_b200 import potts
-    K, chains = 5, 48
     rng = np.random.default_rng(4)
     tables = rng.normal(0, 0.4, (3, K, K)).astype(np.float32)
     unary = rng.normal(0, 0.2, (6 * 4 * 8, K)).astype(np.float32)

@@ -34,6 +34,7 @@ struct PottsArgs {
     uint32_t chain_word0, k0, k1;
     const float* pair_tables;  // [3][K][K][K]: P_d[c][s_plus][s_minus] = T_d[c][s_plus] + T_d[s_minus][c] rounded once (PAIR kernels only)
     float table_mag;           // 2 (max|T_x| + max|T_y| + max|T_z|): bound of the six table terms of a field
+    int32_t* counts;           // [N][K] category counts to add this update's draws to, or null (K <= 16 only)
 };
 
 // Exact Gumbel-argmax of one chain (byte `sh / 8` of the neighbour words): the rule of softmax.rs:60-97 with the
@@ -82,12 +83,15 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     if (PAIR)
         for (int i = threadIdx.x + threadIdx.y * blockDim.x; i < 3 * a.K * a.K * a.K; i += blockDim.x * blockDim.y) s_tab[3 * a.K * a.K + i] = a.pair_tables[i];
     __syncthreads();
-    const int quad = blockIdx.y * 32 + threadIdx.x;
     const int half_z = a.nz >> 1;
     const int64_t n_block = static_cast<int64_t>(a.nx) * a.ny * half_z;
-    if (4 * static_cast<int64_t>(quad) >= a.ld) return;
+    const int n_groups = static_cast<int>((a.ld + 127) / 128);  // a warp takes its node's chains 128 at a time
     // index among the nodes of this colour
     for (int64_t in_block = static_cast<int64_t>(blockIdx.x) * 8 + threadIdx.y; in_block < n_block; in_block += static_cast<int64_t>(gridDim.x) * 8) {
+    unsigned long long cnt_lo = 0ull, cnt_hi = 0ull;  // a.counts: this lane's draws of the node, 8-bit fields per category
+    for (int group = 0; group < n_groups; ++group) {
+    const int quad = group * 32 + threadIdx.x;
+    if (4 * static_cast<int64_t>(quad) >= a.ld) continue;  // never taken when the counts ride along (ld is a multiple of 128 then)
     const int zz = static_cast<int>(in_block % half_z);
     const int y = static_cast<int>((in_block / half_z) % a.ny);
     const int x = static_cast<int>(in_block / (static_cast<int64_t>(half_z) * a.ny));
@@ -172,6 +176,39 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     for (int c = 0; c < 4; ++c)
         if (4 * static_cast<int64_t>(quad) + c < a.n_chains) out |= arg[c] << (8 * c);
     *reinterpret_cast<uint32_t*>(a.state + node * a.ld + 4 * static_cast<int64_t>(quad)) = out;
+    if (a.counts) {
+        // Category marginals of the draws just made (the observation that follows the sweep sees exactly these values: a
+        // node is updated once per sweep).  A lane counts its chains in 8-bit fields (categories 0-7 and 8-15 in two 64-bit
+        // words; at most 4 per pass, 252 over the 63 passes the launch allows).
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            if (4 * static_cast<int64_t>(quad) + c < a.n_chains) {
+                if (arg[c] < 8u) cnt_lo += 1ull << (8u * arg[c]);
+                else cnt_hi += 1ull << (8u * (arg[c] - 8u));
+            }
+    }
+    }
+    if (a.counts) {
+        // the warp adds its lanes' fields, widened to 16 bits (at most 32 x 252), and lane k adds category k's total to the
+        // node's counter; the warp owns the node: no atomics
+        const int Kc = KT > 0 ? KT : a.K;
+        const uint32_t w4[4] = {static_cast<uint32_t>(cnt_lo), static_cast<uint32_t>(cnt_lo >> 32), static_cast<uint32_t>(cnt_hi), static_cast<uint32_t>(cnt_hi >> 32)};
+        uint32_t total = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (4 * j >= Kc) break;  // uniform
+            const uint32_t even = __reduce_add_sync(0xffffffffu, w4[j] & 0x00ff00ffu), odd = __reduce_add_sync(0xffffffffu, (w4[j] >> 8) & 0x00ff00ffu);
+            const int k = static_cast<int>(threadIdx.x) - 4 * j;  // categories 4 j .. 4 j + 3 live in this word
+            if (k >= 0 && k < 4) total = ((k & 1) ? odd : even) >> (16 * (k >> 1)) & 0xffffu;
+        }
+        if (static_cast<int>(threadIdx.x) < Kc) {
+            const int zz = static_cast<int>(in_block % half_z);
+            const int y = static_cast<int>((in_block / half_z) % a.ny);
+            const int x = static_cast<int>(in_block / (static_cast<int64_t>(half_z) * a.ny));
+            const int64_t node = (static_cast<int64_t>(x) * a.ny + y) * a.nz + 2 * zz + ((x + y + a.colour) & 1);
+            a.counts[node * Kc + threadIdx.x] += static_cast<int32_t>(total);
+        }
+    }
     }
 }
 
@@ -377,19 +414,22 @@ int32_t thrml_potts_randomize(thrml_potts* P, uint64_t key) {
     }
     return THRML_OK;
 }
-// Update one colour with its block key (asynchronous).
-int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
+// The update kernel can count the categories it draws (the marginal observation that follows a sweep) when a warp's 32 lanes
+// all hold chains of the state and the categories fit the 8-bit count fields.
+static bool potts_counts_ride_along(const thrml_potts* P) { return P->K <= 16 && P->ld % 128 == 0 && P->ld <= 63 * 128; }
+// Update one colour with its block key (asynchronous); `count`: add the draws to the category counts.
+static int32_t potts_update(thrml_potts* P, int32_t colour, uint64_t block_key, bool count) {
     if (!P || colour < 0 || colour > 1) return fail(THRML_ERR_INVALID_ARG, "bad colour");
     CU_TRY(cudaSetDevice(P->device));
     PottsArgs a{static_cast<uint8_t*>(P->state.p), static_cast<const float*>(P->tables.p), static_cast<const float*>(P->unary.p), P->nx, P->ny, P->nz, P->K, colour, P->ld, P->n_chains,
                 static_cast<uint32_t>(P->chain_offset >> 2), static_cast<uint32_t>(block_key), static_cast<uint32_t>(block_key >> 32)};
     a.pair_tables = static_cast<const float*>(P->pair_tables.p);
     a.table_mag = P->table_mag;
+    a.counts = count ? static_cast<int32_t*>(P->counts.p) : nullptr;
     // CTAs stride over the nodes: about four waves of resident CTAs (three per SM), so each stages the tables a few times at most
-    dim3 grid = potts_grid(P);
+    dim3 grid(potts_grid(P).x, 1);
     const dim3 block(32, 8);
-    const unsigned resident = static_cast<unsigned>(P->ctx->sm_count) * 3u * 4u;
-    grid.x = std::min(grid.x, std::max(1u, resident / grid.y));
+    grid.x = std::min(grid.x, static_cast<unsigned>(P->ctx->sm_count) * 3u * 4u);
     const size_t smem = static_cast<size_t>(3) * P->K * P->K * (P->pair ? 1 + P->K : 1) * 4;
     const bool quad = P->noise == THRML_POTTS_NOISE_QUAD;
 #define POTTS_LAUNCH(KT, PAIR)                                                          \
@@ -409,6 +449,7 @@ int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) {
     CU_TRY(cudaGetLastError());
     return THRML_OK;
 }
+int32_t thrml_potts_update(thrml_potts* P, int32_t colour, uint64_t block_key) { return potts_update(P, colour, block_key, false); }
 int32_t thrml_potts_observe_marginals(thrml_potts* P) {
     if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(P->device));
@@ -432,19 +473,24 @@ int32_t thrml_potts_read_marginals(thrml_potts* P, int32_t* counts_out, int64_t*
 }
 // run_blocks (sampling.rs:81-106): keys = key.split(n_iters); each sweep (sample_blocks, sampling.rs:28-63) splits its key
 // in two block keys, colour 0 then colour 1.  Asynchronous.
-int32_t thrml_potts_run_blocks(thrml_potts* P, uint64_t key, int64_t n_iters) {
+// `observe`: the marginal observation that follows the last sweep (fused into that sweep's updates when they can count).
+static int32_t potts_run(thrml_potts* P, uint64_t key, int64_t n_iters, bool observe) {
     if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     if (n_iters < 0) return fail(THRML_ERR_INVALID_ARG, "n_iters must be non-negative");
     std::vector<uint64_t> keys(static_cast<size_t>(n_iters));
     rng_split(key, n_iters, keys.data());
+    const bool ride = observe && n_iters > 0 && potts_counts_ride_along(P);
     for (int64_t it = 0; it < n_iters; ++it) {
         uint64_t k2[2];
         rng_split(keys[it], 2, k2);
         for (int colour = 0; colour < 2; ++colour)
-            if (int32_t rc = thrml_potts_update(P, colour, k2[colour])) return rc;
+            if (int32_t rc = potts_update(P, colour, k2[colour], ride && it + 1 == n_iters)) return rc;
     }
+    if (ride) P->n_obs += P->n_chains;
+    else if (observe) return thrml_potts_observe_marginals(P);
     return THRML_OK;
 }
+int32_t thrml_potts_run_blocks(thrml_potts* P, uint64_t key, int64_t n_iters) { return potts_run(P, key, n_iters, false); }
 // sample_with_observation (sampling.rs:178-320) with the category-marginal observer: key.split_two -> warm-up, observe,
 // then n_samples - 1 times (steps_per_sample sweeps, observe); nothing after the first observation when n_samples <= 1.
 int32_t thrml_potts_sample_with_marginals(thrml_potts* P, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample) {
@@ -452,15 +498,12 @@ int32_t thrml_potts_sample_with_marginals(thrml_potts* P, uint64_t key, int64_t 
     if (n_warmup < 0 || n_samples < 0 || steps_per_sample < 0) return fail(THRML_ERR_INVALID_ARG, "schedule entries must be non-negative");
     uint64_t two[2];
     rng_split(key, 2, two);
-    if (int32_t rc = thrml_potts_run_blocks(P, two[0], n_warmup)) return rc;
-    if (int32_t rc = thrml_potts_observe_marginals(P)) return rc;
+    if (int32_t rc = potts_run(P, two[0], n_warmup, true)) return rc;
     if (n_samples > 1) {
         std::vector<uint64_t> keys(static_cast<size_t>(n_samples - 1));
         rng_split(two[1], n_samples - 1, keys.data());
-        for (int64_t i = 0; i < n_samples - 1; ++i) {
-            if (int32_t rc = thrml_potts_run_blocks(P, keys[i], steps_per_sample)) return rc;
-            if (int32_t rc = thrml_potts_observe_marginals(P)) return rc;
-        }
+        for (int64_t i = 0; i < n_samples - 1; ++i)
+            if (int32_t rc = potts_run(P, keys[i], steps_per_sample, true)) return rc;
     }
     CU_TRY(cudaStreamSynchronize(P->ctx->stream));
     return THRML_OK;
