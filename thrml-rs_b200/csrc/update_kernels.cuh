@@ -1804,7 +1804,8 @@ __global__ void __launch_bounds__(512) k_spin_lut_sliced(const __grid_constant__
                 t2 = __ldg(L + ((cfg >> 16) & 0xffu));
                 t3 = __ldg(L + (cfg >> 24));
             }
-            const U4 r = philox4x32_10_rk(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, sp.rk);
+            // the step's keys live in shared memory here: two loads and the per-round adds are cheaper than twenty loads
+            const U4 r = philox4x32_10(static_cast<uint32_t>(node), a.chain_word0 + static_cast<uint32_t>(quad), 0u, TAG_SPIN, sp.rk.k0[0], sp.rk.k1[0]);
             uint32_t o = (r.x <= t0) ? 1u : 0u;
             o |= (r.y <= t1) ? 0x100u : 0u;
             o |= (r.z <= t2) ? 0x10000u : 0u;
