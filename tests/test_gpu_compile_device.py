@@ -53,6 +53,16 @@ def test_heads_outside_free_blocks_and_ragged_slot_counts(T, ctx):
     assert max(t["k"] for t in dev.tables(0)) == 31  # the hub: 30 spokes + the edge from 35
 
 
+def test_degenerate_programs(T, ctx):
+    """Biases only (no tails anywhere), a block no interaction group touches, and no interaction groups at all."""
+    kinds = np.zeros(10, np.int32)
+    for ops in ([("add_ising", np.arange(6), np.linspace(-1, 1, 6).astype(np.float32), np.zeros((0, 2), np.int64), np.zeros(0, np.float32), 1.0)], []):
+        desc = dict(kinds=kinds, free=[(np.arange(0, 3), 0), (np.arange(3, 6), 1), (np.arange(6, 10), 2)], ops=ops)
+        host, dev = _host_and_device(T, desc, ctx)
+        assert_same_tables(dev, host)
+        assert dev.tables(2) == []
+
+
 def test_program_from_device_tables_samples_like_the_oracle(T, O, ctx):
     desc, _ = M.ising_random_graph(T, 200, 6, 11)
     bld = M.fill(T.Builder(desc["kinds"]), desc)

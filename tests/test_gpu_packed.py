@@ -75,6 +75,19 @@ def test_packed_observer_and_format_switch(T, O):
     _same(gs, os_, len(desc["free"]))
 
 
+def test_packed_sweeps_with_a_clamped_block(T, O):
+    """The last colour of the graph is clamped: its rows sit behind the free blocks in the spin class and are read, never written."""
+    desc = dict(M.ising_random_graph(T, 300, 8, 6)[0])
+    free = list(desc["free"])
+    desc["clamped"] = [free.pop()[0]]
+    desc["free"] = free
+    n = len(desc["free"]) + 1
+    prog, gs, os_, gb, ob = _pair(T, O, desc, 1040)
+    gs.run_blocks(17, 4)
+    os_.run_blocks(17, 4)
+    _same(gs, os_, n)
+
+
 def test_packed_route_is_declined_where_it_does_not_apply(T, O):
     """Fewer than 1009 chains, or a block on another kernel: the option is accepted and the byte kernels run."""
     desc = M.ising_random_graph(T, 200, 12, 4)[0]  # sequential-sum blocks
