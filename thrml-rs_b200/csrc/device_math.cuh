@@ -67,6 +67,22 @@ __device__ __forceinline__ U4 philox4x32_10_rk(uint32_t c0, uint32_t c1, uint32_
 
 __device__ __forceinline__ uint32_t pick(const U4& v, uint32_t i) { return i == 0 ? v.x : (i == 1 ? v.y : (i == 2 ? v.z : v.w)); }
 
+// Hardware base-2 logarithm for normal positive inputs (the screens of the Gumbel draws: u >= 2^-24 and -ln u >= 2^-24).  The
+// flush-to-zero form is one instruction; the default form adds a range test and a rescaling for subnormal inputs that
+// cannot occur here.
+__device__ __forceinline__ float lg2_normal(float x) {
+    float y;
+    asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Hardware reciprocal for normal inputs, one instruction.
+__device__ __forceinline__ float rcp_normal(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // 24-bit uniform in [0,1) and 23-bit uniform strictly inside (0,1).
 __device__ __forceinline__ float u24(uint32_t r) { return __fmul_rn(__uint2float_rn(r >> 8), 5.9604644775390625e-8f); }
 __device__ __forceinline__ float u23_open(uint32_t r) {

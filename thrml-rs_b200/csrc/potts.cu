@@ -154,8 +154,8 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
             const uint32_t word = QUAD ? pick(rq, c) : pick(r[c], cat & 3);
             // the 23-bit uniform (m + 0.5) 2^-23 of u23_open, formed exactly as (1 + m 2^-23) - (1 - 2^-24)
             const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;
-            const float l1 = __log2f(u) * -0.6931471805599453f;  // -ln u > 0
-            const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
+            const float l1 = lg2_normal(u) * -0.6931471805599453f;  // -ln u > 0
+            const float p = fmaf(lg2_normal(l1), -0.6931471805599453f, th);  // th - ln(l1)
             if (cat == 0) { best[c] = p; second[c] = -3.0e38f; lmin[c] = l1; }
             else {
                 lmin[c] = fminf(lmin[c], l1);
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256, 3) k_potts_update(PottsArgs a) {
     const float base = PAIR ? fmaf(2.0e-6f, unmax + a.table_mag, 1.2e-5f) : 1.2e-5f;
 #pragma unroll
     for (int c = 0; c < 4; ++c)
-        if (!(best[c] - second[c] > base + __fdividef(6.0e-7f, lmin[c])))
+        if (!(best[c] - second[c] > base + 6.0e-7f * rcp_normal(lmin[c])))
             arg[c] = potts_exact_argmax(s_tab, a.unary + node * K, K, 8 * c, px, mx, py, my, pz, mz, static_cast<uint32_t>(in_block),
                                         4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, a.k0, a.k1, QUAD);
     uint32_t out = 0;

@@ -355,8 +355,8 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
                 r = philox4x32_10(static_cast<uint32_t>(node), 4u * (a.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(cat >> 2), TAG_CAT, a.k0, a.k1);
             // the 23-bit uniform (m + 0.5) 2^-23 of u23_open, formed exactly as (1 + m 2^-23) - (1 - 2^-24)
             const float u = __uint_as_float(0x3f800000u | (pick(r, cat & 3) >> 9)) - 0.99999994039535522461f;
-            const float l1 = __log2f(u) * -0.6931471805599453f;            // -ln u > 0
-            const float p = fmaf(__log2f(l1), -0.6931471805599453f, th);  // th - ln(l1)
+            const float l1 = lg2_normal(u) * -0.6931471805599453f;            // -ln u > 0
+            const float p = fmaf(lg2_normal(l1), -0.6931471805599453f, th);  // th - ln(l1)
             if (cat == 0) {
                 best = p;
                 lmin = l1;
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(256, 4) k_cat_fast(const __grid_constant__ Upd
         // The hardware logarithm's absolute error (1.7e-7 in ln u) is a relative error of 1.7e-7 / l in l = -ln u and so an
         // absolute error of that size in ln l; the outer logarithm and the final add stay below 4e-6.  A leader more than
         // three such bounds ahead (taken at the chain's smallest l) is the exact argmax; anything closer is recomputed exactly.
-        if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a, node, quad, c);
+        if (!(best - second > MARGIN + 6.0e-7f * rcp_normal(lmin))) lead = cat_exact_argmax(a, node, quad, c);
         out |= lead << sh;
     }
     *reinterpret_cast<uint32_t*>(a.dst + static_cast<int64_t>(node) * a.ld + 4 * static_cast<int64_t>(quad)) = out;
@@ -503,8 +503,8 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
                         r = philox4x32_10_rk(static_cast<uint32_t>(node), 4u * (a.u.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(k >> 2), TAG_CAT, a.rk);
                     const uint32_t word = (k & 3) == 0 ? r.x : ((k & 3) == 1 ? r.y : ((k & 3) == 2 ? r.z : r.w));
                     const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;  // the 23-bit uniform of u23_open
-                    const float l1 = __log2f(u) * -0.6931471805599453f;               // -ln u > 0
-                    const float p = fmaf(__log2f(l1), -0.6931471805599453f, th[k]);   // th - ln(l1)
+                    const float l1 = lg2_normal(u) * -0.6931471805599453f;               // -ln u > 0
+                    const float p = fmaf(lg2_normal(l1), -0.6931471805599453f, th[k]);   // th - ln(l1)
                     if (k == 0) {
                         best = p;
                         lmin = l1;
@@ -515,7 +515,7 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
                     }
                 }
                 // k_cat_fast's bound: a leader closer to the runner-up than the screen's error is recomputed exactly
-                if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
+                if (!(best - second > MARGIN + 6.0e-7f * rcp_normal(lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
                 out |= lead << sh;
             }
             if (live) *reinterpret_cast<uint32_t*>(drow + 4 * static_cast<int64_t>(quad)) = out;
@@ -652,8 +652,8 @@ __global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ Cat
                         r = philox4x32_10_rk(static_cast<uint32_t>(node), 4u * (a.u.chain_word0 + static_cast<uint32_t>(quad)) + c, static_cast<uint32_t>(k >> 2), TAG_CAT, a.rk);
                     const uint32_t word = (k & 3) == 0 ? r.x : ((k & 3) == 1 ? r.y : ((k & 3) == 2 ? r.z : r.w));
                     const float u = __uint_as_float(0x3f800000u | (word >> 9)) - 0.99999994039535522461f;  // the 23-bit uniform of u23_open
-                    const float l1 = __log2f(u) * -0.6931471805599453f;
-                    const float p = fmaf(__log2f(l1), -0.6931471805599453f, th[k]);
+                    const float l1 = lg2_normal(u) * -0.6931471805599453f;
+                    const float p = fmaf(lg2_normal(l1), -0.6931471805599453f, th[k]);
                     if (k == 0) {
                         best = p;
                         lmin = l1;
@@ -663,7 +663,7 @@ __global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ Cat
                         if (p > best) { best = p; lead = k; }
                     }
                 }
-                if (!(best - second > MARGIN + __fdividef(6.0e-7f, lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
+                if (!(best - second > MARGIN + 6.0e-7f * rcp_normal(lmin))) lead = cat_exact_argmax(a.u, node, quad, c);
                 out |= lead << sh;
             }
             if (live) *reinterpret_cast<uint32_t*>(drow + 4 * static_cast<int64_t>(quad)) = out;
