@@ -140,9 +140,15 @@ __global__ void __launch_bounds__(128, 4) k_lattice_update_sliced(const __grid_c
     const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;  // a multiple of 128, hence of `quads`
     int32_t spins[4] = {0, 0, 0, 0}, agree[4] = {0, 0, 0, 0};
     const int q = static_cast<int>((static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) % quads);
-    for (int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; gid < total; gid += step) {
-        const int r = row_begin + static_cast<int>(gid / per_row);
-        const int w = static_cast<int>((gid % per_row) / quads);
+    // (row, word) of this thread's items advance by a fixed amount per iteration: no division inside the loop
+    const int64_t gid0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int step_rows = static_cast<int>(step / per_row), step_words = static_cast<int>((step % per_row) / quads);
+    int r = row_begin + static_cast<int>(gid0 / per_row), w = static_cast<int>((gid0 % per_row) / quads);
+    for (int64_t gid = gid0; gid < total; gid += step, r += step_rows, w += step_words) {
+        if (w >= a.words) {
+            w -= a.words;
+            ++r;
+        }
         const int64_t gi = a.row0 + r;
         const int p = static_cast<int>((gi + a.colour) & 1);
         auto at = [&](const uint32_t* plane, int srow, int word) {
@@ -156,7 +162,7 @@ __global__ void __launch_bounds__(128, 4) k_lattice_update_sliced(const __grid_c
         const int row_cls = gi == 0 ? 1 : (gi == a.H - 1 ? 2 : 0);
         const bool first_col = p == 0 && w == 0, last_col = p == 1 && w == a.words - 1;
         const uint32_t node_base = static_cast<uint32_t>(gi * (a.W >> 1) + 32 * static_cast<int64_t>(w));  // a multiple of 32
-        uint32_t out[4];
+        uint32_t out[4], tie[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const uint32_t Lc = p == 0 ? ((S[c] << 1) | (A[c] >> 31)) : S[c], Rc = p == 0 ? S[c] : ((S[c] >> 1) | (A[c] << 31));
@@ -192,23 +198,31 @@ __global__ void __launch_bounds__(128, 4) k_lattice_update_sliced(const __grid_c
                     eq |= (h8 == T8 ? 1u : 0u) << k;
                 }
             }
-            uint32_t o = lt;
-            // ties (top bytes equal): the low 24 bits of the draw decide, from a call of their own
-            uint32_t m = eq;
-            while (m) {
-                const int k = __ffs(m) - 1;
-                m &= m - 1u;
+            out[c] = lt;
+            tie[c] = eq;
+        }
+        // Ties (top bytes equal, one draw in 256): the low 24 bits of the draw decide.  They come from a call keyed by the spin
+        // whose four words serve the four chains, so the chains' ties are resolved together, one call per tied spin position:
+        // a warp runs this loop as often as its busiest lane has tied positions, once for the four chains instead of once each.
+        for (uint32_t m = tie[0] | tie[1] | tie[2] | tie[3]; m; m &= m - 1u) {
+            const int k = __ffs(m) - 1;
+            const U4 rr = philox4x32_10_rk(node_base + k, a.chain_word0 + q, 3u, TAG_SPIN, a.rk);
+            const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
+            const uint32_t* tab = s_lut + (row_cls * 3 + col_cls) * 16;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (!((tie[c] >> k) & 1u)) continue;
+                const uint32_t Lc = p == 0 ? ((S[c] << 1) | (A[c] >> 31)) : S[c], Rc = p == 0 ? S[c] : ((S[c] >> 1) | (A[c] << 31));
                 const uint32_t cfg = ((U[c] >> k) & 1u) | (((Lc >> k) & 1u) << 1) | (((Rc >> k) & 1u) << 2) | (((D[c] >> k) & 1u) << 3);
-                const int col_cls = (k == 0 && first_col) ? 1 : ((k == 31 && last_col) ? 2 : 0);
-                const uint32_t T = s_lut[(row_cls * 3 + col_cls) * 16 + cfg];
-                const U4 rr = philox4x32_10_rk(node_base + k, a.chain_word0 + q, 3u, TAG_SPIN, a.rk);
-                const uint32_t low = pick(rr, c) & 0xffffffu;
-                o |= (low <= (T & 0xffffffu) ? 1u : 0u) << k;
+                out[c] |= ((pick(rr, c) & 0xffffffu) <= (tab[cfg] & 0xffffffu) ? 1u : 0u) << k;
             }
-            out[c] = o;
-            if (RECORD) {
-                spins[c] += __popc(o) + __popc(S[c]);
-                agree[c] += __popc(~(o ^ U[c])) + __popc(~(o ^ D[c])) + __popc(~(o ^ Lc)) + __popc(~(o ^ Rc));
+        }
+        if (RECORD) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint32_t Lc = p == 0 ? ((S[c] << 1) | (A[c] >> 31)) : S[c], Rc = p == 0 ? S[c] : ((S[c] >> 1) | (A[c] << 31));
+                spins[c] += __popc(out[c]) + __popc(S[c]);
+                agree[c] += __popc(~(out[c] ^ U[c])) + __popc(~(out[c] ^ D[c])) + __popc(~(out[c] ^ Lc)) + __popc(~(out[c] ^ Rc));
             }
         }
         *reinterpret_cast<uint4*>(a.own + (static_cast<int64_t>(r + 1) * a.words + w) * a.chains + 4 * q) = make_uint4(out[0], out[1], out[2], out[3]);
