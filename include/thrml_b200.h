@@ -491,7 +491,8 @@ int32_t thrml_potts_observe_marginals(thrml_potts* p);
 int32_t thrml_potts_read_marginals(thrml_potts* p, int32_t* counts_out, int64_t* n_obs_out);
 /* Drivers inside the library: run_blocks (sampling.rs:81-106, asynchronous) and sample_with_observation
  * (sampling.rs:178-320) with the category-marginal observer — warm-up, observe, then n_samples - 1 times
- * (steps_per_sample sweeps, observe).  With chains sharded over ranks, thrml_potts_marginals_allreduce adds the counts and
+ * (steps_per_sample sweeps, observe).  An observation that follows a sweep is counted by that sweep's update kernels
+ * (at most 16 categories, a multiple of 128 chains up to 8064); otherwise by the observer kernel.  With chains sharded over ranks, thrml_potts_marginals_allreduce adds the counts and
  * the observation count over `comm` in place (one grouped ncclAllReduce). */
 int32_t thrml_potts_run_blocks(thrml_potts* p, uint64_t key, int64_t n_iters);
 int32_t thrml_potts_sample_with_marginals(thrml_potts* p, uint64_t key, int64_t n_warmup, int64_t n_samples, int64_t steps_per_sample);
