@@ -406,6 +406,7 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
     for (int node = blockIdx.x * 8 + (threadIdx.x >> 5); node < a.u.n; node += gridDim.x * 8) {
         const int cnt = __ldg(a.cnt + node);
         const uint32_t first = __ldg(a.first + node);
+        const uint32_t opens_mask = first, closes_mask = cnt > 0 ? ((first >> 1) | (1u << (cnt - 1))) : 0u;  // slot s closes its table when s + 1 opens one or s is the last
         // lane e < cnt: entry e's tail positions and weight row
         int32_t nb0 = -1, nb1 = -1, nb2 = -1, nbc = -1;
         const float* wp = nullptr;
@@ -466,9 +467,9 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
 #pragma unroll
                 for (int s = 0; s < CAT_SLOTS; ++s) {
                     if (s >= cnt) break;  // uniform over the warp
-                    const bool opens = (first >> s) & 1u;
-                    const bool closes = s + 1 >= cnt || ((first >> (s + 1)) & 1u);
-                    const uint32_t flip = ((sg[s] >> sh) & 1u) << 31;
+                    const bool opens = (opens_mask >> s) & 1u, closes = (closes_mask >> s) & 1u;
+                    // +-1.0f: w * sign + th in one fused multiply-add rounds exactly as th + (+-w) does
+                    const float sign = __uint_as_float(0x3f800000u | (((sg[s] >> sh) & 1u) << 31));
                     const float4* row = reinterpret_cast<const float4*>(mine + s * K * KP + ((xw[s] >> sh) & 0xffu) * KP);
                     float w[4 * NV];
 #pragma unroll
@@ -478,14 +479,14 @@ __global__ void __launch_bounds__(256, 3) k_cat_warp(const __grid_constant__ Cat
                     }
                     if (opens && closes) {  // a table with one active slot: its sum is the weight itself
 #pragma unroll
-                        for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                        for (int k = 0; k < KT; ++k) th[k] = __fmaf_rn(w[k], sign, th[k]);
                     } else {  // the branches are uniform over the warp and taken outside the category loops
                         if (opens) {  // 0 + t = t (a sum that starts at -0 instead of +0 gives the same logits: th is never -0)
 #pragma unroll
-                            for (int k = 0; k < KT; ++k) sm[k] = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                            for (int k = 0; k < KT; ++k) sm[k] = __fmul_rn(w[k], sign);
                         } else {
 #pragma unroll
-                            for (int k = 0; k < KT; ++k) sm[k] = __fadd_rn(sm[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                            for (int k = 0; k < KT; ++k) sm[k] = __fmaf_rn(w[k], sign, sm[k]);
                         }
                         if (closes) {
 #pragma unroll
@@ -610,7 +611,7 @@ __global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ Cat
                 for (int s = 0; s < cnt; ++s) {
                     const uint32_t b = (s_slot[warp][s][lane] >> sh) & 0xffu;
                     const uint32_t flag = s_flag[warp][s];
-                    const uint32_t flip = (b >> 7) << 31;
+                    const float sign = __uint_as_float(0x3f800000u | ((b >> 7) << 31));  // +-1.0f: w * sign + th rounds exactly as th + (+-w)
                     float w[4 * NV];
                     if (STAGE) {
                         const float4* row = reinterpret_cast<const float4*>(mine + s * K * KP + (b & 0x7fu) * KP);  // an untailed slot has category 0
@@ -627,14 +628,14 @@ __global__ void __launch_bounds__(256, 2) k_cat_many(const __grid_constant__ Cat
                     }
                     if ((flag & 6u) == 6u) {  // a table with one active slot: its sum is the weight itself
 #pragma unroll
-                        for (int k = 0; k < KT; ++k) th[k] = __fadd_rn(th[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                        for (int k = 0; k < KT; ++k) th[k] = __fmaf_rn(w[k], sign, th[k]);
                     } else {  // the branches are uniform over the warp and taken outside the category loops
                         if (flag & 2u) {  // 0 + t = t (a sum that starts at -0 instead of +0 gives the same logits: th is never -0)
 #pragma unroll
-                            for (int k = 0; k < KT; ++k) sm[k] = __uint_as_float(__float_as_uint(w[k]) ^ flip);
+                            for (int k = 0; k < KT; ++k) sm[k] = __fmul_rn(w[k], sign);
                         } else {
 #pragma unroll
-                            for (int k = 0; k < KT; ++k) sm[k] = __fadd_rn(sm[k], __uint_as_float(__float_as_uint(w[k]) ^ flip));
+                            for (int k = 0; k < KT; ++k) sm[k] = __fmaf_rn(w[k], sign, sm[k]);
                         }
                         if (flag & 4u) {
 #pragma unroll
