@@ -371,7 +371,8 @@ def workload_config(args, model=None, world=None):
                 "side": int(args.side), "categories": 4, "chains": int(args.chains), "l2": "state (1 GiB at side 512, 4096 chains) larger than L2"}
     if args.workload in ("potts", "potts_program"):
         return {"workload": "3-D periodic Potts-like lattice, K = 10, shared direction tables" + (", as an explicit factor program" if args.workload == "potts_program" else ", category marginals every sweep"),
-                "side": int(args.side), "categories": 10, "chains": int(args.chains), "l2": "state (2 GiB at side 128) larger than L2" if args.side >= 64 else "cache-resident"}
+                "side": int(args.side), "categories": 10, "chains_per_gpu": int(args.chains), "global_chains": int(args.chains * world),
+                "parallelism": f"chains sharded over {world} GPU(s), one allreduce of the category counts", "l2": "state (2 GiB at side 128) larger than L2" if args.side >= 64 else "cache-resident"}
     return {"workload": "2-D periodic Ising lattice, bit-packed, checkerboard blocks, row stripes with halo exchange, magnetisation and energy recorded every sweep",
             "side": int(args.side), "chains": int(args.chains), "stripe_rows": int(args.side // world), "parallelism": f"rows sharded over {world} GPU(s), halo rows by NCCL point-to-point",
             "halo_bytes_per_half_sweep_per_neighbour": int(args.side // 2 // 8 * args.chains), "l2": "state (2 GiB at side 32768) larger than L2"}
@@ -407,7 +408,7 @@ def main():
     ctx = T.default_context(local_rank)
     comm = T.Comm.from_torch(dist, ctx) if dist else None
     env = dict(T=T, torch=torch, args=args, rank=rank, world=world, device=local_rank, dist=dist, ctx=ctx, comm=comm)
-    if args.workload in ("rbm", "small_lattice", "potts_program", "potts", "mixed") and world > 1:
+    if args.workload in ("rbm", "small_lattice", "potts_program", "mixed") and world > 1:
         # these configurations are replicas: every rank would run the same independent problem
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unavailable": f"--workload {args.workload} runs on one GPU (replicas only); use --gpus 1"}), flush=True)
@@ -863,36 +864,51 @@ def run_potts(T, torch, args, rank, world, device, dist, ctx, comm):
     side, K, chains = args.side, 10, args.chains
     n = side ** 3
     tables, unary = potts_arrays(side, K)
-    lat = potts.PottsLattice(side, side, side, K, tables, unary, 1.0, chains, 0, ctx)
+    # chains are independent: with several GPUs every rank holds `chains` of them (global ids rank * chains + c, so the draws
+    # do not depend on the sharding) and the category counts are added over the ranks by one allreduce inside the timed region
+    lat = potts.PottsLattice(side, side, side, K, tables, unary, 1.0, chains, rank * chains, ctx)
     lat.randomize(5)
     stream = torch.cuda.ExternalStream(ctx.stream)
 
     def sync():
         ctx.synchronize()
         torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
 
     def step(i):  # one sweep followed by the marginal observation, as one schedule of the library's driver (the second colour's
         lat.sample_with_marginals(300 + i, 1, 1, 1)  # update and the first's count the categories they draw)
 
+    def steps_and_reduce():
+        for i in range(args.steps):
+            step(100 + i)
+        if comm:
+            lat.allreduce_marginals(comm)
+
     for i in range(max(args.warmup, 3)):
         step(i)
-    sampler = ClockSampler(device)
+    if comm:  # the communicator's first large collective, outside the timed region; the counts start again afterwards
+        lat.allreduce_marginals(comm)
+    lat.reset_marginals()
+    sampler = ClockSampler(device) if rank == 0 else None
     t0 = time.time()
-    ms = timed(torch, stream, lambda: [step(100 + i) for i in range(args.steps)], sync) / args.steps
+    ms = max_over_ranks(torch, dist, timed(torch, stream, steps_and_reduce, sync)) / args.steps
     t1 = time.time()
-    clocks = sampler.stop(t0, t1)
-    update_ms = timed(torch, stream, lambda: lat.run_blocks(9, 4), sync) / 8  # one colour update, without the observer
+    clocks = sampler.stop(t0, t1) if sampler else None
     counts, n_obs = lat.read_marginals()
-    updates = float(n) * chains
-    out = base_line(args, updates / (ms * 1e-3), ms, 1, "u8 categories, f32 logits")
-    out.update({"config": workload_config(args), "clocks": clocks, "gpu_launches": args.steps * 2,
-                "roofline": hbm_roofline(updates / 2, 2 + 120.0 / chains, update_ms, "k_potts_update",
+    update_ms = timed(torch, stream, lambda: lat.run_blocks(9, 4), sync) / 8  # one colour update, without the observer
+    updates = float(n) * chains * world
+    out = base_line(args, updates / (ms * 1e-3), ms, world, "u8 categories, f32 logits")
+    out.update({"config": workload_config(args, world=world), "clocks": clocks, "gpu_launches": args.steps * 2 + (1 if comm else 0),
+                "roofline": hbm_roofline(float(n) * chains / 2, 2 + 120.0 / chains, update_ms, "k_potts_update",
                                          note="instruction-bound by construction: a Gumbel draw (two logarithms, a 23-bit uniform) per category and update",
                                          dram_bytes_per_update=POTTS_DRAM_BYTES_PER_UPDATE if (K, chains) == (10, 1024) else None,
                                          dram_provenance="ncu dram__bytes_read.sum + dram__bytes_write.sum of one k_potts_update launch on a 64^3 lattice, 1024 chains "
                                                          "(profiles/k_potts_update_potts128.md), scaled by site updates"),
                 "marginal_check": {"observations_per_node": int(n_obs), "rows_sum_to_observations": bool(np.all(counts.sum(axis=1) == n_obs))}})
     del counts
+    if world > 1:
+        return out
     if not args.no_e2e:
         # end to end: initial categories from pinned host memory, the schedule (0 warm-up, steps + 1 samples, 1 sweep each) with
         # the marginal observer inside the library, counts read back

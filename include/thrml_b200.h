@@ -489,6 +489,8 @@ int32_t thrml_potts_update(thrml_potts* p, int32_t colour, uint64_t block_key);
 /* Category-marginal observer: counts[node][category] += chains in that category (asynchronous); read as int32. */
 int32_t thrml_potts_observe_marginals(thrml_potts* p);
 int32_t thrml_potts_read_marginals(thrml_potts* p, int32_t* counts_out, int64_t* n_obs_out);
+/* Zeroes the counts and the observation count (the observer's init, moment.rs:152-172; asynchronous). */
+int32_t thrml_potts_reset_marginals(thrml_potts* p);
 /* Drivers inside the library: run_blocks (sampling.rs:81-106, asynchronous) and sample_with_observation
  * (sampling.rs:178-320) with the category-marginal observer — warm-up, observe, then n_samples - 1 times
  * (steps_per_sample sweeps, observe).  An observation that follows a sweep is counted by that sweep's update kernels

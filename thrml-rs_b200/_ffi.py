@@ -120,6 +120,7 @@ _SIGNATURES = {
     "thrml_potts_update": (C.c_int32, [_P, C.c_int32, C.c_uint64]),
     "thrml_potts_observe_marginals": (C.c_int32, [_P]),
     "thrml_potts_read_marginals": (C.c_int32, [_P, _P, _P]),
+    "thrml_potts_reset_marginals": (C.c_int32, [_P]),
     "thrml_potts_synchronize": (C.c_int32, [_P]),
     "thrml_potts_run_blocks": (C.c_int32, [_P, C.c_uint64, C.c_int64]),
     "thrml_potts_sample_with_marginals": (C.c_int32, [_P, C.c_uint64, C.c_int64, C.c_int64, C.c_int64]),

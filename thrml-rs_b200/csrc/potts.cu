@@ -463,6 +463,13 @@ int32_t thrml_potts_observe_marginals(thrml_potts* P) {
     P->n_obs += P->n_chains;
     return THRML_OK;
 }
+int32_t thrml_potts_reset_marginals(thrml_potts* P) {
+    if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
+    CU_TRY(cudaSetDevice(P->device));
+    CU_TRY(cudaMemsetAsync(P->counts.p, 0, P->counts.bytes, P->ctx->stream));
+    P->n_obs = 0;
+    return THRML_OK;
+}
 int32_t thrml_potts_read_marginals(thrml_potts* P, int32_t* counts_out, int64_t* n_obs_out) {
     if (!P) return fail(THRML_ERR_INVALID_ARG, "null lattice");
     CU_TRY(cudaSetDevice(P->device));

@@ -69,5 +69,8 @@ class PottsLattice:
         check(lib().thrml_potts_read_marginals(self.h, ptr(out), C.byref(n)))
         return out, n.value
 
+    def reset_marginals(self):
+        check(lib().thrml_potts_reset_marginals(self.h))
+
     def synchronize(self):
         check(lib().thrml_potts_synchronize(self.h))
