@@ -82,6 +82,9 @@ def test_potts_randomize_and_schedule(T, O):
     lat.sample_with_marginals(5, 10, 4, 2)
     counts, n_obs = lat.read_marginals()
     assert n_obs == 4 * chains and np.all(counts.sum(axis=1) == n_obs)
+    lat.reset_marginals()
+    counts0, n0 = lat.read_marginals()
+    assert n0 == 0 and not counts0.any()
     s = lat.download().reshape(chains, 4, 4, 4)
     agree = np.mean([(s == np.roll(s, -1, axis=a)).mean() for a in (1, 2, 3)])
     assert agree > 0.6  # T = 2 I favours equal neighbours (uniform would give 0.25)
