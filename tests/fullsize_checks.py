@@ -4,7 +4,7 @@ Chains are independent and every kernel keys its noise by the global chain id, s
 the chains of a full-size device state at a cost of seconds: the device runs all chains, the oracle runs a few of them
 from the same start with the same keys, and the states of those chains must agree bit for bit.  Observer sums are
 checked against numpy on the downloaded device state.  Used by tests/test_gpu_fullsize.py (asserting) and by bench.py's
-CPU leg (reporting a `parity_check` object); each function returns a dict whose "ok" is the verdict.
+CPU leg (reporting a `parity_check` object); each function returns a dict whose "ok" says whether every comparison held.
 """
 import time
 
