@@ -364,7 +364,8 @@ def workload_config(args, model=None, world=None):
         return {"workload": "32 x 32 periodic Ising lattice, 256 chains, hinton_init + 1000 sweeps (200 warm-up, 801 samples) with moments per step",
                 "chains": int(args.chains), "l2": "cache-resident (256 KiB of state): L2 is not flushed, the configuration itself is cache-resident"}
     if args.workload == "rbm":
-        return {"workload": "bipartite RBM-style Ising EBM, CD-1 per step", "visible": 784, "hidden": 4096, "chains": int(args.chains),
+        return {"workload": "bipartite RBM-style Ising EBM, CD-1 per step", "visible": 784, "hidden": 4096, "chains_per_gpu": int(args.chains), "global_chains": int(args.chains * world),
+                "parallelism": f"chains sharded over {world} GPU(s), one allreduce of the two correlation matrices per step",
                 "l2": "operands (6.4 MB couplings, 13-67 MB states) fit in L2: a tensor-pipe measurement, not an HBM one"}
     if args.workload == "mixed":
         return {"workload": "spin / 4-state checkerboard with three-spin terms (not a BASELINE configuration: the general spin and the warp-per-node categorical kernels)",
@@ -408,7 +409,7 @@ def main():
     ctx = T.default_context(local_rank)
     comm = T.Comm.from_torch(dist, ctx) if dist else None
     env = dict(T=T, torch=torch, args=args, rank=rank, world=world, device=local_rank, dist=dist, ctx=ctx, comm=comm)
-    if args.workload in ("rbm", "small_lattice", "potts_program", "mixed") and world > 1:
+    if args.workload in ("small_lattice", "potts_program", "mixed") and world > 1:
         # these configurations are replicas: every rank would run the same independent problem
         if rank == 0:
             print(json.dumps({"metric": METRIC, "unavailable": f"--workload {args.workload} runs on one GPU (replicas only); use --gpus 1"}), flush=True)
@@ -617,28 +618,42 @@ def run_rbm(T, torch, args, rank, world, device, dist, ctx, comm):
     program = T.Program(builder, ctx)
     assert program.enable_dense(False) == 2
     program.set_option(T.OPT_DENSE_TILES, {"single": 0, "pair": 1, "auto": 2}[args.dense_tiles])
-    rng = np.random.default_rng(3)
+    # with several GPUs every rank holds `chains` chains of its own data (global chain ids rank * chains + c) and every step ends
+    # with one allreduce of the two correlation matrices (thrml_cd1_step_comm): weak scaling
+    rng = np.random.default_rng(3 + rank)
     v0 = (rng.random((chains, nv)) < 0.13).astype(np.uint8)
-    data, state = T.ChainState(program, chains), T.ChainState(program, chains)
+    data, state = T.ChainState(program, chains, rank * chains), T.ChainState(program, chains, rank * chains)
     data.upload(0, v0)
     stream = torch.cuda.ExternalStream(ctx.stream)
 
     def step(i):
-        state.cd1_step(0, 1, None, 500 + i, want_stats=False, data=data)  # v0 is read from the resident data state
+        state.cd1_step(0, 1, None, 500 + i, want_stats=False, data=data, comm=comm)  # v0 is read from the resident data state
 
     def sync():
         ctx.synchronize()
         torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
 
     for i in range(max(args.warmup, 3)):
         step(i)
-    sampler = ClockSampler(device)
+    sampler = ClockSampler(device) if rank == 0 else None
     t0 = time.time()
-    ms = timed(torch, stream, lambda: [step(100 + i) for i in range(args.steps)], sync) / args.steps
+    ms = max_over_ranks(torch, dist, timed(torch, stream, lambda: [step(100 + i) for i in range(args.steps)], sync)) / args.steps
     t1 = time.time()
-    clocks = sampler.stop(t0, t1)
-    flop = 5 * 2.0 * chains * nv * nh  # 3 field GEMMs + 2 correlation GEMMs
-    updates = chains * (nh + nv + nh)
+    clocks = sampler.stop(t0, t1) if sampler else None
+    flop = 5 * 2.0 * chains * nv * nh  # 3 field GEMMs + 2 correlation GEMMs, per GPU
+    updates = chains * (nh + nv + nh) * world
+    if world > 1:
+        peaks, measured = measured_peaks()
+        peak = float(peaks["bf16_tflops"])
+        achieved = flop / (ms * 1e-3) / 1e12
+        out = base_line(args, updates / (ms * 1e-3), ms, world, "bf16 couplings x +-1 states, f32 accumulate; u8 x u8 -> s32 correlations")
+        out.update({"config": workload_config(args, world=world), "clocks": clocks, "gpu_launches": args.steps * 10,  # + allreduce and scale
+                    "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak, "traffic": None,
+                                 "peak_source": "measured burst bf16 GEMM (MEASURED_PEAKS.json)" if measured else "fallback 1590 (MEASURED_PEAKS.json absent)",
+                                 "flop_per_step": flop, "note": "per GPU; the step includes one ncclAllReduce of 2 x 784 x 4096 f32"}})
+        return out
     peaks, measured = measured_peaks()
     peak = float(peaks["bf16_tflops"])
     achieved = flop / (ms * 1e-3) / 1e12

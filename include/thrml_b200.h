@@ -319,6 +319,12 @@ int32_t thrml_debug_pair_tmem_check(thrml_state* s);
  * many steps start from): `data`'s visible block is read for h0 and <v0 h0> and is not modified; v1 and h1 land in `s`. */
 int32_t thrml_cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, float* pos_host,
                             float* neg_host);
+/* thrml_cd1_step_from with the chains sharded over the ranks of `comm` (the chain-parallel form of the step: every rank
+ * holds its own data and chain states, whose chain offsets give the global chain ids): the correlation matrices returned on
+ * every rank are the means over all ranks' chains (one ncclAllReduce of 2 x n_visible x n_hidden f32 and a scale; exact when
+ * the chain count per rank is a power of two).  The hidden block must be on the dense path. */
+int32_t thrml_cd1_step_comm(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, thrml_comm* comm,
+                            float* pos_host, float* neg_host);
 /* Local field gamma[chain][node] (spin block) or logits theta[chain][node][K] (categorical block) of a free
  * block in the current state — spin_gibbs.rs:512-611 / softmax.rs:586-709. */
 int32_t thrml_fields_debug(thrml_state* s, int32_t block, float* out);

@@ -1,7 +1,8 @@
 """Two ranks on two GPUs (skipped on a single-GPU machine), everything multi-GPU going through the library's own
 communicator (thrml_comm over NCCL): chain-sharded moment sums combined by thrml_moments_allreduce equal the
 single-device sums (int32 and int64 transport), Potts marginals likewise, and a lattice split into two stripes whose
-halo rows travel inside thrml_lattice_run_blocks equals the whole lattice, state and observable series."""
+halo rows travel inside thrml_lattice_run_blocks equals the whole lattice, state and observable series; the CD-1 step with
+its chains sharded (thrml_cd1_step_comm) returns the correlation matrices of the unsharded step."""
 import os
 import sys
 
@@ -12,6 +13,25 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 LATTICES = [(64, 128, 16, 5), (4, 64, 8, 3), (8, 192, 4, 4)]  # (H, W, chains, sweeps): overlapped exchange, two-row stripes, four-row stripes
+
+
+def _rbm_case(T, ctx=None):
+    """64 visible x 96 hidden spins with bf16-valued couplings, 256 chains: a program on the dense path and its data."""
+    rng = np.random.default_rng(12)
+    nv, nh, chains = 64, 96, 256
+    W = (np.round(rng.normal(0, 0.3, (nv, nh)) * 64) / 64).astype(np.float32)
+    b = rng.normal(0, 0.2, nv + nh).astype(np.float32)
+    vis, hid = np.arange(nv), np.arange(nv, nv + nh)
+    edges = np.stack([np.repeat(vis, nh), np.tile(hid, nv)], 1)
+    bld = T.Builder(np.zeros(nv + nh, np.int32))
+    bld.add_free_block(vis, superblock=0)
+    bld.add_free_block(hid, superblock=1)
+    bld.add_ising(np.arange(nv + nh), b, edges, W.ravel(), 1.0)
+    bld.compile()
+    prog = T.Program(bld, ctx) if ctx is not None else T.Program(bld)
+    assert prog.enable_dense(False) == 2
+    v0 = (rng.random((chains, nv)) < 0.3).astype(np.uint8)
+    return prog, v0, chains
 
 
 def _potts_inputs():
@@ -65,6 +85,13 @@ def _worker(rank, world, port, out_dir):
     pl.allreduce_marginals(comm)
     counts, n_obs = pl.read_marginals()
     out["potts_counts"], out["potts_n_obs"] = counts, np.array([n_obs])
+    # CD-1 with the chains sharded: 128 of the 256 chains per rank
+    rprog, v0, rchains = _rbm_case(T, ctx)
+    half = rchains // world
+    data, chain = T.ChainState(rprog, half, rank * half), T.ChainState(rprog, half, rank * half)
+    data.upload(0, v0[rank * half:(rank + 1) * half])
+    pos, neg = chain.cd1_step(0, 1, None, 99, data=data, comm=comm)
+    out["cd1_pos"], out["cd1_neg"] = pos, neg
     # striped lattices
     for li, (H, W, chains, sweeps) in enumerate(LATTICES):
         spins = np.random.default_rng(H * W).integers(0, 2, (chains, H, W)).astype(np.uint8)
@@ -111,6 +138,12 @@ def test_two_gpus_through_the_library_communicator(T, tmp_path):
     counts, n_obs = pl.read_marginals()
     for r in (r0, r1):
         assert np.array_equal(r["potts_counts"], counts) and r["potts_n_obs"][0] == n_obs == 3 * 96
+    rprog, v0, rchains = _rbm_case(T)
+    data, chain = T.ChainState(rprog, rchains), T.ChainState(rprog, rchains)
+    data.upload(0, v0)
+    pos, neg = chain.cd1_step(0, 1, None, 99, data=data)
+    for r in (r0, r1):  # 128 chains per rank: a power of two, so the sharded means are the unsharded ones bit for bit
+        assert np.array_equal(r["cd1_pos"], pos) and np.array_equal(r["cd1_neg"], neg)
     for li, (H, W, chains, sweeps) in enumerate(LATTICES):
         spins = np.random.default_rng(H * W).integers(0, 2, (chains, H, W)).astype(np.uint8)
         whole = lattice.DistributedStripe(H, W, 0.4407, 0.03, 1.0, chains, None)

@@ -59,6 +59,7 @@ _SIGNATURES = {
     "thrml_pair_correlation": (C.c_int32, [_P, C.c_int32, C.c_int32, _P]),
     "thrml_cd1_step": (C.c_int32, [_P, C.c_int32, C.c_int32, _P, C.c_uint64, _P, _P]),
     "thrml_cd1_step_from": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_uint64, _P, _P]),
+    "thrml_cd1_step_comm": (C.c_int32, [_P, _P, C.c_int32, C.c_int32, C.c_uint64, _P, _P, _P]),
     "thrml_state_create": (C.c_int32, [_P, C.c_int64, C.c_int64, _P]),
     "thrml_state_destroy": (None, [_P]),
     "thrml_state_upload_f32": (C.c_int32, [_P, C.c_int32, _P]),

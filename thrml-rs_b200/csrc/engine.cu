@@ -1930,14 +1930,33 @@ int32_t thrml_cd1_step(thrml_state* s, int32_t visible_block, int32_t hidden_blo
 // copied in first: h0 ~ P(h | data's visible block) and <v0 h0> read `data`; the sweep then writes v1 and h1 into `s`, whose
 // own visible block is never read before it is overwritten.  `data` is not modified (its cached +-1 image and one counts
 // are built on first use).
+__global__ void k_scale_f32(float* x, int64_t n, float f) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = __fmul_rn(x[i], f);
+}
+static int32_t cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, thrml_comm* comm, float* pos_host, float* neg_host);
 int32_t thrml_cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, float* pos_host, float* neg_host) {
+    return cd1_step_from(s, data, visible_block, hidden_block, key, nullptr, pos_host, neg_host);
+}
+// Chains sharded over the ranks of `comm` (each rank its own data and chain states, global chain ids through the states'
+// chain offsets): the two correlation matrices are means over a rank's chains; one ncclAllReduce adds them and
+// a scale by 1 / ranks makes them the means over all chains (exact when the chain count per rank is a power of two).
+int32_t thrml_cd1_step_comm(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, thrml_comm* comm, float* pos_host,
+                            float* neg_host) {
+    if (!comm) return fail(THRML_ERR_INVALID_ARG, "null communicator");
+    if (s && comm->ctx != s->prog->ctx) return fail(THRML_ERR_INVALID_ARG, "communicator and state belong to different contexts");
+    return cd1_step_from(s, data, visible_block, hidden_block, key, comm, pos_host, neg_host);
+}
+static int32_t cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_block, int32_t hidden_block, uint64_t key, thrml_comm* comm, float* pos_host, float* neg_host) {
     if (!s || !data) return fail(THRML_ERR_INVALID_ARG, "null state");
+    if (comm && s == data) return fail(THRML_ERR_INVALID_ARG, "the sharded step reads its data from a second state");
     if (s == data) return thrml_cd1_step(s, visible_block, hidden_block, nullptr, key, pos_host, neg_host);
     if (s->prog != data->prog || s->n_chains != data->n_chains) return fail(THRML_ERR_INVALID_ARG, "states must share the program and the chain count");
     if (visible_block < 0 || visible_block >= s->prog->n_free || hidden_block < 0 || hidden_block >= s->prog->n_free || visible_block == hidden_block)
         return fail(THRML_ERR_INVALID_ARG, "visible and hidden must be two distinct free blocks");
     const BlockProg& hb = s->prog->blocks[hidden_block];
     if (hb.kernel != 3 || hb.dense_src != visible_block) {  // not on the dense path: bring the data over and run the ordinary step
+        if (comm) return fail(THRML_ERR_UNSUPPORTED, "the sharded CD-1 step needs the hidden block on the dense path");
         if (int32_t rc = thrml_state_copy_block(s, data, visible_block)) return rc;
         return thrml_cd1_step(s, visible_block, hidden_block, nullptr, key, pos_host, neg_host);
     }
@@ -1956,6 +1975,13 @@ int32_t thrml_cd1_step_from(thrml_state* s, thrml_state* data, int32_t visible_b
     s->no_image_block = -1;
     if (rc_sweep) return rc_sweep;
     if (int32_t rc = pair_correlation_async(s, visible_block, hidden_block, s->d_corr.as<float>() + cnt)) return rc;
+    if (comm && comm->world > 1) {
+        const NcclApi* api = nccl_api();
+        if (!api) return fail(THRML_ERR_NCCL, "NCCL is not available");
+        NCCL_TRY(api, AllReduce(s->d_corr.p, s->d_corr.p, 2 * cnt, ncclFloat32, ncclSum, comm->nccl, st));
+        k_scale_f32<<<static_cast<unsigned>((2 * cnt + 255) / 256), 256, 0, st>>>(s->d_corr.as<float>(), static_cast<int64_t>(2 * cnt), 1.0f / static_cast<float>(comm->world));
+        CU_TRY(cudaGetLastError());
+    }
     if (pos_host) CU_TRY(cudaMemcpyAsync(pos_host, s->d_corr.p, cnt * 4, cudaMemcpyDeviceToHost, st));
     if (neg_host) CU_TRY(cudaMemcpyAsync(neg_host, s->d_corr.as<float>() + cnt, cnt * 4, cudaMemcpyDeviceToHost, st));
     CU_TRY(cudaStreamSynchronize(st));

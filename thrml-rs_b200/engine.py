@@ -412,14 +412,18 @@ class ChainState:
         check(lib().thrml_pair_correlation(self.h, C.c_int32(block_a), C.c_int32(block_b), ptr(out)))
         return out
 
-    def cd1_step(self, visible_block, hidden_block, v0, key, want_stats=True, data=None, out=None):
+    def cd1_step(self, visible_block, hidden_block, v0, key, want_stats=True, data=None, out=None, comm=None):
         """One CD-1 step.  v0: host `[chain][visible]` bytes to upload first (None = keep the current visible state);
         data: another ChainState whose visible block is the data (read in place, thrml_cd1_step_from); out: optional pair of
-        caller-owned f32 `[n_visible][n_hidden]` arrays for the two correlation matrices (pinned memory copies faster)."""
+        caller-owned f32 `[n_visible][n_hidden]` arrays for the two correlation matrices (pinned memory copies faster);
+        comm: chains sharded over the communicator's ranks, the matrices are means over all of them (thrml_cd1_step_comm)."""
         nv, nh = self.program.block_len(visible_block), self.program.block_len(hidden_block)
         v0 = np.ascontiguousarray(v0, dtype=np.uint8).reshape(self.n_chains, nv) if v0 is not None else None
         pos, neg = out if out is not None else ((np.zeros((nv, nh), dtype=np.float32), np.zeros((nv, nh), dtype=np.float32)) if want_stats else (None, None))
-        if data is not None:
+        if comm is not None:
+            check(lib().thrml_cd1_step_comm(self.h, data.h if data is not None else None, C.c_int32(visible_block), C.c_int32(hidden_block), C.c_uint64(int(key)), comm.h,
+                                            ptr(pos), ptr(neg)))
+        elif data is not None:
             check(lib().thrml_cd1_step_from(self.h, data.h, C.c_int32(visible_block), C.c_int32(hidden_block), C.c_uint64(int(key)), ptr(pos), ptr(neg)))
         else:
             check(lib().thrml_cd1_step(self.h, C.c_int32(visible_block), C.c_int32(hidden_block), ptr(v0), C.c_uint64(int(key)), ptr(pos), ptr(neg)))
